@@ -1,0 +1,443 @@
+#!/usr/bin/env python
+"""Benchmark of the KV-cache write path: reshape_and_cache_flash, bf16 -> fp8_e4m3.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+                    [--workload C4|C2|C5-fp8|C5-bf16|C1] [--scaling weak|strong]
+
+One step = one call of the op over one batch (the "C4" batch by default: 16384 tokens,
+8 KV heads x 128, cache of 65536 blocks x 64 slots, fp8_e4m3 store, slots in runs of 64).
+Prints ONE JSON line (rank 0).  Fields beyond the usual ones:
+
+  value / ms_per_step   K steps replayed from CUDA graphs with inputs resident in HBM, timed
+                        with CUDA events on the launching stream, max over ranks
+  roofline              algorithmic bytes per launch / average launch duration, against the
+                        measured HBM copy bandwidth in MEASURED_PEAKS.json
+  e2e                   same metric through the C ABI's host-buffer entry point: every step
+                        copies key, value and slot_mapping from pinned host memory, runs the
+                        kernel and reads two written cache rows back
+  cpu_baseline          the CPU oracle (a C port of the reference's algorithm, all host
+                        threads) on a bounded sample of the same batch -- reported, never a target
+  clocks                SM clock / throttle reasons sampled through NVML during the timed region
+
+Under torchrun every rank runs the same per-rank batch on its own GPU and cache slice
+("weak": the model has 8 KV heads per GPU, no rank needs another rank's data), or, with
+--scaling strong, the batch's 8 heads are divided over the ranks.  There is no collective
+on the data path; NCCL only carries the barrier and the max-over-ranks of the times.
+
+--impl reference times the CPU oracle alone (rank 0 only), in the same units.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+PKG_ROOT = os.path.join(REPO, "vllm-xpu-kernels_b200")
+for _p in (REPO, PKG_ROOT, os.path.join(PKG_ROOT, "benchmark")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+import workloads  # noqa: E402
+
+METRIC = "reshape_and_cache_flash_fp8_tokens_per_s"
+NBUF = 8            # distinct input sets rotated through, so inputs come from HBM, not L2
+GRAPH_STEPS = 64    # steps captured per CUDA graph
+
+
+# --------------------------------------------------------------------------------------------
+# helpers
+# --------------------------------------------------------------------------------------------
+def measured_peaks() -> tuple[float, str]:
+    path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) in a thread."""
+
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+        0x80: "hw_power_brake", 0x2: "applications_clocks_setting", 0x100: "display_clock_setting",
+    }
+
+    def __init__(self, index: int, period_s: float = 0.004):
+        self.samples: list[tuple[int, int, float]] = []
+        self.sm_max = None
+        self._stop = threading.Event()
+        self._thr = None
+        self._h = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            # NVML enumerates physical GPUs; honour CUDA_VISIBLE_DEVICES when it lists indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            phys = index
+            if vis:
+                ids = [v.strip() for v in vis.split(",") if v.strip()]
+                if index < len(ids) and ids[index].isdigit():
+                    phys = int(ids[index])
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._h = None
+        self._period = period_s
+
+    def _loop(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                clk = int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                rs = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)) if hasattr(
+                    nv, "nvmlDeviceGetCurrentClocksEventReasons") else int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                pw = nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0
+                self.samples.append((clk, rs, pw))
+            except Exception:
+                pass
+            self._stop.wait(self._period)
+
+    def start(self):
+        if self._h is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+
+    def stop(self) -> dict:
+        if self._thr is not None:
+            self._stop.set()
+            self._thr.join()
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [], "samples": 0}
+        clks = [s[0] for s in self.samples]
+        bits = 0
+        for s in self.samples:
+            bits |= s[1]
+        reasons = sorted(name for bit, name in self.REASONS.items() if bits & bit)
+        return {"sm_mhz": statistics.median(clks), "sm_max_mhz": self.sm_max, "reasons": reasons,
+                "samples": len(clks), "power_w_max": round(max(s[2] for s in self.samples), 1)}
+
+
+def dist_setup(n_gpus: int):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return dist, rank, world, local
+    if n_gpus > 1:
+        raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    return None, 0, 1, 0
+
+
+def barrier(dist):
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(dist, v: float) -> float:
+    if dist is None:
+        return v
+    t = torch.tensor([v], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(dist, v: float) -> float:
+    if dist is None:
+        return v
+    t = torch.tensor([v], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def make_batch_sets(name: str, rank: int, world: int, scaling: str, nbuf: int):
+    """nbuf independent batches of the named workload for this rank (CPU tensors)."""
+    sets = []
+    for b in range(nbuf):
+        if scaling == "strong":
+            w = workloads.shard_heads(workloads.BY_NAME[name](variant=b), rank, world)
+        else:
+            w = workloads.BY_NAME[name](variant=b + 100 * rank)
+        sets.append(w)
+    return sets
+
+
+# --------------------------------------------------------------------------------------------
+# CPU oracle timing (cpu_baseline leg and --impl reference)
+# --------------------------------------------------------------------------------------------
+def cpu_oracle_rate(w, budget_s: float, host_blocks: int = 4096, tokens: int | None = None):
+    """tokens/s of the CPU oracle on (a prefix of) batch ``w``.  The host cache keeps the
+    batch's block size and row shape but only ``host_blocks`` blocks, so that it fits in
+    ordinary host memory; the tokens' blocks are renumbered into it, runs of slots intact."""
+    import numpy as np
+    import oracle
+    from oracle import torch_views as H  # numpy views of torch tensors
+
+    T = w.num_tokens if tokens is None else min(tokens, w.num_tokens)
+    key, value = w.key[:T].contiguous(), w.value[:T].contiguous()
+    slots = w.slot_mapping[:T].clone()
+    bs = w.block_size
+    act = slots >= 0
+    blocks = torch.div(slots[act], bs, rounding_mode="floor")
+    uniq, inv = torch.unique(blocks, return_inverse=True)
+    if uniq.numel() > host_blocks:
+        host_blocks = int(uniq.numel())
+    slots[act] = inv * bs + slots[act] % bs
+    cdt = torch.uint8 if w.kv_cache_dtype != "auto" else key.dtype
+    kc = torch.zeros(host_blocks, bs, w.num_heads, w.head_size, dtype=cdt)
+    vc = torch.zeros_like(kc)
+    threads = oracle.max_threads()
+    args = (H.as_np(key), H.as_np(value), H.as_np(kc), H.as_np(vc), slots.numpy(), w.kv_cache_dtype,
+            float(w.k_scale), float(w.v_scale), H.ORC_IN[key.dtype])
+    oracle.reshape_and_cache_flash(*args, threads=threads)  # warm-up: page in, spin up the thread pool
+    n, t0 = 0, time.perf_counter()
+    while True:
+        oracle.reshape_and_cache_flash(*args, threads=threads)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s and n >= 3:
+            break
+    return T * n / dt, threads, T, n, dt
+
+
+def run_reference_arm(ns) -> None:
+    """--impl reference: the CPU implementation of the path alone, same metric and config."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+    from oracle import torch_views as H
+    w = workloads.BY_NAME[ns.workload](variant=0)
+    # size the per-step sample so that warmup + steps end within about two minutes
+    rate0, threads, _, _, _ = cpu_oracle_rate(w, 2.0)
+    per_step = int(max(64, min(w.num_tokens, rate0 * 100.0 / max(1, ns.steps + ns.warmup))))
+    per_step -= per_step % w.block_size or 0
+    per_step = max(w.block_size, per_step)
+    T = per_step
+    key, value = w.key[:T].contiguous(), w.value[:T].contiguous()
+    slots = w.slot_mapping[:T].clone()
+    bs = w.block_size
+    act = slots >= 0
+    uniq, inv = torch.unique(torch.div(slots[act], bs, rounding_mode="floor"), return_inverse=True)
+    slots[act] = inv * bs + slots[act] % bs
+    kc = torch.zeros(max(4096, int(uniq.numel())), bs, w.num_heads, w.head_size, dtype=torch.uint8)
+    vc = torch.zeros_like(kc)
+    args = (H.as_np(key), H.as_np(value), H.as_np(kc), H.as_np(vc), slots.numpy(), w.kv_cache_dtype,
+            float(w.k_scale), float(w.v_scale), H.ORC_IN[key.dtype])
+    for _ in range(ns.warmup):
+        oracle.reshape_and_cache_flash(*args, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(ns.steps):
+        oracle.reshape_and_cache_flash(*args, threads=threads)
+    dt = time.perf_counter() - t0
+    value_tps = T * ns.steps / dt
+    sample = (f"{T} of the batch's {w.num_tokens} tokens per step into a {kc.shape[0]}-block host cache, "
+              f"{ns.steps} steps, {threads} OpenMP threads")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value_tps, "unit": "tokens/s", "n_gpus": ns.gpus,
+        "steps": ns.steps, "warmup": ns.warmup, "ms_per_step": dt / ns.steps * 1e3, "higher_is_better": True,
+        "scaling": ns.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": describe_workload(w, ns.workload), "tokens_per_step": T},
+        "cpu_baseline": {"value": value_tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value_tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def describe_workload(w, name: str) -> str:
+    return (f"{name}: reshape_and_cache_flash {str(w.key.dtype).replace('torch.', '')}->{w.kv_cache_dtype}, "
+            f"T={w.num_tokens} (active {w.num_active}), H={w.num_heads}, D={w.head_size}, "
+            f"block_size={w.block_size}, num_blocks={w.num_blocks}")
+
+
+# --------------------------------------------------------------------------------------------
+# the B200 arm
+# --------------------------------------------------------------------------------------------
+def run_b200_arm(ns) -> None:
+    from vllm_xpu_kernels import cabi  # raises if the CUDA library is not built
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU oracle")
+    dist, rank, world, local = dist_setup(ns.gpus)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    cabi.lib()
+
+    sets = make_batch_sets(ns.workload, rank, world, ns.scaling, NBUF)
+    w0 = sets[0]
+    if w0.layout != "flash":
+        raise SystemExit("bench.py times the flash-layout op; see benchmark/benchmark_reshape_and_cache.py for the paged one")
+    ksh, _ = w0.cache_shapes()
+    cdt = w0.cache_dtype
+    # torch.zeros: the allocation is touched once so first-use effects stay out of the timed region
+    key_cache = torch.zeros(ksh, dtype=torch.uint8 if cdt != w0.key.dtype else cdt, device=dev)
+    value_cache = torch.zeros_like(key_cache)
+    if cdt != w0.key.dtype:
+        key_cache, value_cache = key_cache.view(cdt), value_cache.view(cdt)
+    dsets = [(w.key.to(dev), w.value.to(dev), w.slot_mapping.to(dev), w.k_scale.to(dev), w.v_scale.to(dev)) for w in sets]
+    in_bytes = sum(k.numel() * k.element_size() * 2 for k, _, _, _, _ in dsets)
+    kv = w0.kv_cache_dtype
+
+    def step(i: int) -> None:
+        k, v, s, ks, vs = dsets[i % NBUF]
+        cabi.reshape_and_cache_flash(k, v, key_cache, value_cache, s, kv, ks, vs)
+
+    # graphs: GRAPH_STEPS steps each, plus one for the remainder so that exactly K steps are timed
+    def capture(n: int):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(n):
+                step(i)
+        return g
+
+    for i in range(NBUF):  # eager warm-up before capture (module load, first-touch)
+        step(i)
+    torch.cuda.synchronize()
+    g_full = capture(GRAPH_STEPS) if ns.steps >= GRAPH_STEPS or ns.warmup >= GRAPH_STEPS else None
+    rem = ns.steps % GRAPH_STEPS
+    g_rem = capture(rem) if rem else None
+    wrem = ns.warmup % GRAPH_STEPS
+    g_wrem = capture(wrem) if wrem else None
+
+    sampler = ClockSampler(local)
+    for _ in range(ns.warmup // GRAPH_STEPS):
+        g_full.replay()
+    if g_wrem is not None:
+        g_wrem.replay()
+    barrier(dist)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(ns.steps // GRAPH_STEPS):
+        g_full.replay()
+    if g_rem is not None:
+        g_rem.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    barrier(dist)
+    total_ms = max_over_ranks(dist, e0.elapsed_time(e1))
+    ms_per_step = total_ms / ns.steps
+    tokens_all = sum_over_ranks(dist, float(w0.num_tokens)) if ns.scaling == "weak" else float(w0.num_tokens)
+    value = tokens_all / (ms_per_step * 1e-3)
+    bytes_launch = w0.algorithmic_bytes()
+    achieved = bytes_launch / (e0.elapsed_time(e1) / ns.steps * 1e-3) / 1e9  # this rank's own kernel
+    peak, peak_src = measured_peaks()
+
+    # single launches bracketed by their own events (eager), for the launch-latency picture
+    singles = []
+    for i in range(min(200, max(8, ns.steps))):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step(i)
+        b.record()
+        singles.append((a, b))
+    torch.cuda.synchronize()
+    single_us = statistics.median(a.elapsed_time(b) for a, b in singles) * 1e3
+
+    # ---------------------------------------------------------------- end to end, host buffers
+    e2e_steps = max(1, min(ns.steps, 40))
+    hsets = [(w.key.contiguous().pin_memory(), w.value.contiguous().pin_memory(), w.slot_mapping.pin_memory())
+             for w in sets[:4]]
+    probes = [torch.empty(2, w0.num_heads * w0.head_size, dtype=torch.uint8).pin_memory() for _ in range(4)]
+    kflat = key_cache.view(torch.uint8).view(w0.num_blocks * w0.block_size, -1)
+    vflat = value_cache.view(torch.uint8).view(w0.num_blocks * w0.block_size, -1)
+    last_slots = [int(w.slot_mapping[w.slot_mapping >= 0][-1]) for w in sets[:4]]
+
+    def e2e_step(i: int) -> None:
+        j = i % 4
+        hk, hv, hs = hsets[j]
+        cabi.reshape_and_cache_flash_host(hk, hv, key_cache, value_cache, hs, kv, dsets[j][3], dsets[j][4])
+        probes[j][0].copy_(kflat[last_slots[j]], non_blocking=True)  # the step's result: last token's K and V rows
+        probes[j][1].copy_(vflat[last_slots[j]], non_blocking=True)
+
+    for i in range(4):
+        e2e_step(i)
+    barrier(dist)
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    e2e_s = max_over_ranks(dist, time.perf_counter() - t0)
+    barrier(dist)
+    e2e_value = tokens_all * e2e_steps / e2e_s
+    h2d = sets[0].key.numel() * sets[0].key.element_size() * 2 + sets[0].num_tokens * 8
+    d2h = 2 * probes[0].shape[1]
+    cabi.release_staging()
+
+    # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1)
+    cpu = None
+    if rank == 0 and world == 1 and not ns.no_cpu_baseline:
+        rate, threads, T, n, dt = cpu_oracle_rate(workloads.BY_NAME[ns.workload](variant=0), ns.cpu_seconds)
+        cpu = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": f"{n} passes over {T} tokens of the batch into a 4096-block host cache, {dt:.1f} s"}
+
+    if rank == 0:
+        head = "all 8 KV heads per rank" if ns.scaling == "weak" else f"{w0.num_heads} of 8 KV heads per rank"
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": ns.steps,
+            "warmup": ns.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": ns.scaling,
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {
+                "workload": describe_workload(sets[0], ns.workload),
+                "sharding": f"by KV head, no collective; {head}",
+                "l2": f"inputs rotate over {NBUF} batch sets ({in_bytes / 1e6:.0f} MB per rank, L2 is 126 MB); "
+                      f"each set writes its own cache blocks",
+                "timing": f"CUDA graphs of {GRAPH_STEPS} launches, events on the launching stream",
+            },
+            "hbm_gbs": achieved * (world if ns.scaling == "weak" else 1),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(ns.workload), "peak_source": peak_src,
+                         "algorithmic_bytes_per_launch": bytes_launch, "frac_of_nominal_8000": achieved / 8000.0,
+                         "single_launch_us_eager": single_us},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "api": "kvc_reshape_and_cache_flash_host (pinned host key/value/slot_mapping)"},
+            "clocks": clocks,
+            "gpu_launches": ns.steps,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu
+# summaries under profiles/; None until a capture exists for the workload.
+TRAFFIC_BYTES_PER_LAUNCH: dict[str, int | None] = {}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8192)
+    ap.add_argument("--warmup", type=int, default=128)
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--workload", choices=[k for k in workloads.BY_NAME if k != "C3"], default="C4")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0, help="time budget of the cpu_baseline leg")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ns = ap.parse_args()
+    if ns.steps < 1 or ns.warmup < 0:
+        raise SystemExit("--steps must be >= 1 and --warmup >= 0")
+    if ns.impl == "reference":
+        run_reference_arm(ns)
+    else:
+        run_b200_arm(ns)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,154 @@
+/*
+ * kvcache_b200 -- C ABI of the B200 (sm_100a) paged KV-cache write kernels.
+ *
+ * The reference plugin exposes this path only through the PyTorch dispatcher
+ * (there is no C interface in it).  Each entry point below carries, as plain
+ * pointers, sizes and strides, exactly what the reference's host launcher
+ * reads off its at::Tensor arguments before it submits the device kernel, so
+ * a binding written in any language can stand where that launcher stands.
+ * Citations are file:line inside the reference project.
+ *
+ * Conventions
+ *   - All data pointers are DEVICE pointers on the current CUDA device unless a
+ *     parameter says "host".  Strides are in ELEMENTS of the tensor's dtype.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *     stream).  Calls only enqueue work: no allocation, no host
+ *     synchronisation, no reads of device memory on the host.  They are
+ *     therefore legal during CUDA-graph stream capture.
+ *   - k_scale / v_scale point to one fp32 value each in DEVICE memory and are
+ *     read by the kernel (csrc/cache.cpp:161-162).  They are ignored, and may
+ *     be NULL, when kv_dtype is KVC_KV_AUTO.
+ *   - Return value: KVC_OK or a KVC_ERR_* code; kvc_last_error() then returns
+ *     a message (thread-local, valid until the next failing call on the thread).
+ *   - Tokens whose slot is negative are skipped (csrc/cache.cpp:49, :145).
+ *     Slots >= num_blocks*block_size and duplicate slots are undefined
+ *     behaviour, as in the reference; kvc_count_bad_slots() is the debug check.
+ *   - fp8 stores compute float(x) / scale in IEEE fp32 (correctly rounded),
+ *     then round to nearest even onto the fp8 grid and saturate at the largest
+ *     finite value (448 for e4m3, 57344 for e5m2); NaN becomes 0x7F.
+ */
+#ifndef KVCACHE_B200_H_
+#define KVCACHE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define KVC_API __attribute__((visibility("default")))
+#else
+#define KVC_API
+#endif
+
+/* dtype of key/value (the reference dispatches on key.scalar_type():
+ * csrc/quantization/fp8/quant_utils.h:136-173) */
+enum { KVC_IN_F32 = 0, KVC_IN_F16 = 1, KVC_IN_BF16 = 2 };
+
+/* what the cache stores; mirrors Fp8KVCacheDataType
+ * (csrc/quantization/fp8/quant_utils.h:10-14).  AUTO = same dtype as key. */
+enum { KVC_KV_AUTO = 0, KVC_KV_FP8_E4M3 = 1, KVC_KV_FP8_E5M2 = 2 };
+
+enum {
+  KVC_OK = 0,
+  KVC_ERR_INVALID_ARG = 1, /* NULL pointer, negative size, head_size % x != 0, ... */
+  KVC_ERR_UNSUPPORTED = 2, /* unknown dtype code or kv_cache_dtype string */
+  KVC_ERR_CUDA = 3,        /* a CUDA runtime call failed; message holds cudaGetErrorString */
+  KVC_ERR_TOO_LARGE = 4    /* request exceeds a fixed capacity of the entry point */
+};
+
+/* Library version: major*10000 + minor*100 + patch. */
+KVC_API int kvc_version(void);
+
+/* Message of the last failing call on this thread ("" if none). */
+KVC_API const char* kvc_last_error(void);
+
+/*
+ * Maps the reference's kv_cache_dtype string to a KVC_KV_* code:
+ * "auto" -> AUTO, "fp8" and "fp8_e4m3" -> FP8_E4M3, "fp8_e5m2" -> FP8_E5M2
+ * (csrc/quantization/fp8/quant_utils.h:137, :148, :160).  Any other string
+ * fails with KVC_ERR_UNSUPPORTED and the reference's message
+ * "Unsupported data type of kv cache: <s>" (quant_utils.h:171).
+ */
+KVC_API int kvc_parse_kv_cache_dtype(const char* s, int* kv_dtype_out);
+
+/*
+ * Replaces the host launcher + kernel of `reshape_and_cache_flash`
+ * (csrc/cache.cpp:461-489 host, :105-189 kernel; schema
+ * csrc/torch_bindings.cpp:116-124; prototype csrc/ops.h:51-59).
+ *
+ *   key, value    [>= num_tokens, num_heads, head_size], last dim contiguous;
+ *                 *_stride_t = stride(0), *_stride_h = stride(1)
+ *                 (reference reads stride(0) only and assumes stride(1) ==
+ *                 head_size: cache.cpp:475-476)
+ *   key_cache,    [num_blocks, block_size, num_heads, head_size] views sharing
+ *   value_cache   block_stride = stride(0), page_stride = stride(1),
+ *                 head_stride = stride(2) (cache.cpp:477-480); last dim
+ *                 contiguous.  Element type: key's dtype (AUTO) or 1 byte (fp8).
+ *   slot_mapping  int64 [num_tokens]; num_tokens is ITS length, which may be
+ *                 smaller than key's first dim (cache.cpp:470).
+ */
+KVC_API int kvc_reshape_and_cache_flash(const void* key, const void* value, void* key_cache,
+                                        void* value_cache, const int64_t* slot_mapping,
+                                        int64_t num_tokens, int64_t num_heads, int64_t head_size,
+                                        int64_t block_size, int64_t key_stride_t, int64_t key_stride_h,
+                                        int64_t value_stride_t, int64_t value_stride_h,
+                                        int64_t block_stride, int64_t page_stride, int64_t head_stride,
+                                        int in_dtype, int kv_dtype, const float* k_scale,
+                                        const float* v_scale, void* stream);
+
+/*
+ * Replaces the host launcher + kernel of `reshape_and_cache`
+ * (csrc/cache.cpp:409-434 host, :13-103 kernel; schema
+ * csrc/torch_bindings.cpp:107-113; prototype csrc/ops.h:41-49).
+ *
+ *   key_cache     contiguous [num_blocks, num_heads, head_size/x, block_size, x]
+ *   value_cache   contiguous [num_blocks, num_heads, head_size, block_size]
+ *   x             key_cache.size(4) (cache.cpp:422); must divide head_size
+ * All index arithmetic is 64-bit (the reference's is 32-bit: cache.cpp:48-67).
+ * fp8 modes DIVIDE by the scale, like the flash op.
+ */
+KVC_API int kvc_reshape_and_cache(const void* key, const void* value, void* key_cache, void* value_cache,
+                                  const int64_t* slot_mapping, int64_t num_tokens, int64_t num_heads,
+                                  int64_t head_size, int64_t block_size, int64_t x, int64_t key_stride_t,
+                                  int64_t key_stride_h, int64_t value_stride_t, int64_t value_stride_h,
+                                  int in_dtype, int kv_dtype, const float* k_scale, const float* v_scale,
+                                  void* stream);
+
+/*
+ * Same operation as kvc_reshape_and_cache_flash for callers whose key, value
+ * and slot_mapping live in HOST memory (pinned memory makes the copies
+ * asynchronous).  The rows are copied into device staging buffers owned by the
+ * library (one set per device, grown with cudaMalloc when a call needs more,
+ * so the first call and any growing call must not happen during stream
+ * capture), then scattered by the same kernel.  key/value rows are
+ * [num_tokens, num_heads*head_size] with *_stride_t elements between tokens.
+ * The caches and the two scales stay DEVICE pointers.  Work on `stream` is
+ * ordered; calls on different streams must not overlap, they share the staging.
+ * No counterpart in the reference: its callers always hold device tensors.
+ */
+KVC_API int kvc_reshape_and_cache_flash_host(const void* host_key, const void* host_value,
+                                             void* key_cache, void* value_cache,
+                                             const int64_t* host_slot_mapping, int64_t num_tokens,
+                                             int64_t num_heads, int64_t head_size, int64_t block_size,
+                                             int64_t key_stride_t, int64_t value_stride_t,
+                                             int64_t block_stride, int64_t page_stride,
+                                             int64_t head_stride, int in_dtype, int kv_dtype,
+                                             const float* k_scale, const float* v_scale, void* stream);
+
+/* Frees the staging buffers of kvc_reshape_and_cache_flash_host on the current device. */
+KVC_API int kvc_release_staging(void);
+
+/*
+ * Debug aid the reference lacks: counts entries of slot_mapping that are
+ * >= num_slots (negative entries are legal padding and not counted) into
+ * *bad_count, a DEVICE int64 the caller owns; the kernel overwrites it.
+ */
+KVC_API int kvc_count_bad_slots(const int64_t* slot_mapping, int64_t num_tokens, int64_t num_slots,
+                                int64_t* bad_count, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KVCACHE_B200_H_ */

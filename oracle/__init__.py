@@ -1,0 +1,177 @@
+"""CPU oracle for the paged KV-cache write path -- TEST INFRASTRUCTURE ONLY.
+
+Thin ctypes/numpy front end over ``kv_oracle.c`` (built by ``make -C oracle``).
+Only the test-suite, ``__graft_entry__.smoke()`` and the CPU-baseline leg of
+``bench.py`` may import this package; the shipped library never does.
+
+Arrays are numpy views; 16-bit float inputs travel as ``uint16`` bit patterns
+(``in_dtype`` says whether they are "f16" or "bf16"), fp8 caches as ``uint8``.
+Strides are taken from the numpy views, so strided key/value slices and
+``[:, 0]``-style cache views behave as in the reference's tests
+(tests/test_cache.py:92-93, tests/utils.py:200-223 of the reference).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "liborc.so")
+
+IN_DTYPES = {"f32": 0, "f16": 1, "bf16": 2}
+KV_DTYPES = {"auto": 0, "fp8": 1, "fp8_e4m3": 1, "fp8_e5m2": 2}
+
+_lib = None
+
+
+def build(force: bool = False) -> str:
+    """Compile ``liborc.so`` with gcc if it is missing (or ``force``)."""
+    if force or not os.path.exists(_LIB_PATH):
+        subprocess.run(["make", "-C", _HERE, "liborc.so"] + (["-B"] if force else []),
+                       check=True, capture_output=True)
+    return _LIB_PATH
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = ctypes.CDLL(_LIB_PATH)
+        i64, f32, vp, ci = ctypes.c_int64, ctypes.c_float, ctypes.c_void_p, ctypes.c_int
+        L.orc_reshape_and_cache_flash.restype = ci
+        L.orc_reshape_and_cache_flash.argtypes = [vp, vp, vp, vp, vp] + [i64] * 11 + [ci, ci, f32, f32, i64, ci]
+        L.orc_reshape_and_cache.restype = ci
+        L.orc_reshape_and_cache.argtypes = [vp, vp, vp, vp, vp] + [i64] * 9 + [ci, ci, f32, f32, i64, ci]
+        L.orc_convert_table.restype = None
+        L.orc_convert_table.argtypes = [ci, ci, f32, vp]
+        L.orc_convert_f32.restype = None
+        L.orc_convert_f32.argtypes = [vp, i64, ci, f32, vp]
+        L.orc_f32_to_e4m3.restype = ctypes.c_uint8
+        L.orc_f32_to_e4m3.argtypes = [f32]
+        L.orc_f32_to_e5m2.restype = ctypes.c_uint8
+        L.orc_f32_to_e5m2.argtypes = [f32]
+        L.orc_max_threads.restype = ci
+        _lib = L
+    return _lib
+
+
+def max_threads() -> int:
+    return int(lib().orc_max_threads())
+
+
+def _estrides(a: np.ndarray) -> list[int]:
+    for s in a.strides:
+        if s % a.itemsize:
+            raise ValueError("stride is not a whole number of elements")
+    return [s // a.itemsize for s in a.strides]
+
+
+def _check_in(a: np.ndarray, in_dtype: str) -> None:
+    want = np.float32 if in_dtype == "f32" else np.uint16
+    if a.dtype != want:
+        raise TypeError(f"{in_dtype} input must be a {np.dtype(want)} array, got {a.dtype}")
+    if a.ndim != 3 or (a.shape[2] > 1 and _estrides(a)[2] != 1):
+        raise ValueError("key/value must be [T, H, D] with a contiguous last dim")
+
+
+def reshape_and_cache_flash(key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype: str,
+                            k_scale: float, v_scale: float, in_dtype: str, threads: int = 1,
+                            check_slots: bool = True) -> None:
+    """In-place oracle for ``_C_cache_ops.reshape_and_cache_flash``.
+
+    key/value: [>=T, H, D]; caches: [num_blocks, block_size, H, D] views;
+    slot_mapping: int64 [T] (T, not key.shape[0], is the token count:
+    csrc/cache.cpp:470 of the reference).
+    """
+    _check_in(key, in_dtype)
+    _check_in(value, in_dtype)
+    kv = KV_DTYPES[kv_cache_dtype]
+    want = key.dtype if kv == 0 else np.uint8
+    if key_cache.dtype != want or value_cache.dtype != want:
+        raise TypeError(f"cache arrays must be {np.dtype(want)}")
+    slot_mapping = np.ascontiguousarray(slot_mapping, dtype=np.int64)
+    T = slot_mapping.shape[0]
+    H, D = key.shape[1], key.shape[2]
+    nb, bs = key_cache.shape[0], key_cache.shape[1]
+    ks, vs, cs, cvs = _estrides(key), _estrides(value), _estrides(key_cache), _estrides(value_cache)
+    if cs[:3] != cvs[:3]:
+        raise ValueError("key_cache and value_cache must share strides")
+    if T > key.shape[0] or T > value.shape[0]:
+        raise ValueError("slot_mapping is longer than key/value")
+    rc = lib().orc_reshape_and_cache_flash(
+        key.ctypes.data, value.ctypes.data, key_cache.ctypes.data, value_cache.ctypes.data,
+        slot_mapping.ctypes.data, T, H, D, bs, ks[0], ks[1], vs[0], vs[1], cs[0], cs[1], cs[2],
+        IN_DTYPES[in_dtype], kv, float(k_scale), float(v_scale), nb * bs if check_slots else -1, threads)
+    if rc != 0:
+        raise IndexError("slot_mapping holds a slot >= num_blocks * block_size")
+
+
+def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype: str,
+                      k_scale: float, v_scale: float, in_dtype: str, threads: int = 1,
+                      check_slots: bool = True) -> None:
+    """In-place oracle for ``_C_cache_ops.reshape_and_cache`` (split paged layout).
+
+    key_cache: contiguous [num_blocks, H, D/x, block_size, x];
+    value_cache: contiguous [num_blocks, H, D, block_size].
+    """
+    _check_in(key, in_dtype)
+    _check_in(value, in_dtype)
+    kv = KV_DTYPES[kv_cache_dtype]
+    want = key.dtype if kv == 0 else np.uint8
+    if key_cache.dtype != want or value_cache.dtype != want:
+        raise TypeError(f"cache arrays must be {np.dtype(want)}")
+    if not (key_cache.flags.c_contiguous and value_cache.flags.c_contiguous):
+        raise ValueError("paged caches must be contiguous")
+    slot_mapping = np.ascontiguousarray(slot_mapping, dtype=np.int64)
+    T = slot_mapping.shape[0]
+    H, D = key.shape[1], key.shape[2]
+    nb, bs, x = key_cache.shape[0], key_cache.shape[3], key_cache.shape[4]
+    if key_cache.shape != (nb, H, D // x, bs, x) or value_cache.shape != (nb, H, D, bs):
+        raise ValueError("cache shapes do not match key/value")
+    ks, vs = _estrides(key), _estrides(value)
+    rc = lib().orc_reshape_and_cache(
+        key.ctypes.data, value.ctypes.data, key_cache.ctypes.data, value_cache.ctypes.data,
+        slot_mapping.ctypes.data, T, H, D, bs, x, ks[0], ks[1], vs[0], vs[1], IN_DTYPES[in_dtype], kv,
+        float(k_scale), float(v_scale), nb * bs if check_slots else -1, threads)
+    if rc != 0:
+        raise IndexError("slot_mapping holds a slot >= num_blocks * block_size")
+
+
+def convert_table(in_dtype: str, kv_cache_dtype: str, scale: float) -> np.ndarray:
+    """fp8 byte for each of the 65536 f16/bf16 bit patterns at one scale."""
+    out = np.empty(65536, dtype=np.uint8)
+    lib().orc_convert_table(IN_DTYPES[in_dtype], KV_DTYPES[kv_cache_dtype], float(scale), out.ctypes.data)
+    return out
+
+
+def convert_f32(x: np.ndarray, kv_cache_dtype: str, scale: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint8)
+    lib().orc_convert_f32(x.ctypes.data, x.size, KV_DTYPES[kv_cache_dtype], float(scale), out.ctypes.data)
+    return out
+
+
+def np_f32_to_e4m3(x: np.ndarray) -> np.ndarray:
+    """Independent numpy restatement of RNE + saturate onto e4m3fn.
+
+    Enumerates the 127 non-negative finite codes, decodes them, and picks the
+    nearest (ties to the even code).  Used to cross-check the C converter.
+    """
+    codes = np.arange(0x7F, dtype=np.uint8)
+    e = (codes >> 3).astype(np.int32)
+    m = (codes & 7).astype(np.float64)
+    grid = np.where(e == 0, m * 2.0**-9, (1 + m / 8) * 2.0 ** (e - 7))
+    x = np.asarray(x, dtype=np.float32)
+    a = np.abs(x.astype(np.float64))
+    hi = np.clip(np.searchsorted(grid, a, side="left"), 0, 0x7E)
+    lo = np.clip(hi - 1, 0, 0x7E)
+    dlo, dhi = a - grid[lo], grid[hi] - a
+    pick_hi = (dhi < dlo) | ((dhi == dlo) & (hi % 2 == 0))
+    code = np.where(pick_hi, hi, lo).astype(np.uint8)
+    code = np.where(a >= 448.0, np.uint8(0x7E), code)
+    sign = (x.view(np.uint32) >> 24).astype(np.uint8) & np.uint8(0x80)
+    out = code | sign
+    return np.where(np.isnan(x), np.uint8(0x7F), out).astype(np.uint8)

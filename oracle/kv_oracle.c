@@ -1,0 +1,237 @@
+/*
+ * CPU oracle for the paged KV-cache write path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file restates, in plain C, what the reference plugin's two cache-write
+ * ops compute, so that the CUDA kernels can be checked byte for byte.  It is
+ * never linked into, imported by or called from the shipped library; only the
+ * test-suite, the smoke check and the benchmark's CPU-baseline leg use it.
+ *
+ * What each function follows (paths are relative to the reference project):
+ *   orc_reshape_and_cache_flash  csrc/cache.cpp:140-169 (device body) and
+ *                                csrc/cache.cpp:461-489 (host sizes/strides),
+ *                                tests/test_cache.py:284-292 (torch loop)
+ *   orc_reshape_and_cache        csrc/cache.cpp:44-85 (index formulas :57-67),
+ *                                tests/test_cache.py:155-164 (torch loop)
+ *   element conversion           csrc/quantization/fp8/quant_utils.h:62-78
+ *                                (auto: bit copy; fp8: float(src) / scale,
+ *                                then cast)
+ *
+ * The float -> fp8 cast itself is not reference code: the reference calls
+ * PyTorch's c10::Float8_e4m3fn / c10::Float8_e5m2 constructors (pinned
+ * torch==2.10.0+xpu in its pyproject.toml).  Their published algorithm is
+ * round-to-nearest-even onto the 8-bit grid; it is restated here from the
+ * format definition (e4m3fn: bias 7, 3 mantissa bits, no inf, max 448;
+ * e5m2: bias 15, 2 mantissa bits, max finite 57344) with one deliberate
+ * difference that this build's contract asks for: magnitudes above the largest
+ * finite value SATURATE to it instead of becoming NaN/inf.  The two agree for
+ * |x/scale| <= 464 (e4m3) and tests/golden pins exactly that against torch.
+ * NaN maps to the canonical 0x7F (sign dropped), which is what the hardware
+ * conversion produces.
+ *
+ * The paged op divides by the scale like the flash op; the reference's paged
+ * kernel multiplies (csrc/cache.cpp:70-79) in a branch its own tests disable.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+enum { ORC_F32 = 0, ORC_F16 = 1, ORC_BF16 = 2 };
+enum { ORC_KV_AUTO = 0, ORC_KV_E4M3 = 1, ORC_KV_E5M2 = 2 };
+
+static inline uint32_t f2u(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  return u;
+}
+static inline float u2f(uint32_t u) {
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+float orc_bf16_to_f32(uint16_t h) { return u2f((uint32_t)h << 16); }
+
+float orc_f16_to_f32(uint16_t h) {
+  uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1Fu;
+  uint32_t man = h & 0x3FFu;
+  if (exp == 0x1F) return u2f(sign | 0x7F800000u | (man << 13));
+  if (exp == 0) {
+    if (man == 0) return u2f(sign);
+    /* subnormal half: man * 2^-24, exact in float */
+    float v = (float)man * 5.9604644775390625e-08f;
+    return sign ? -v : v;
+  }
+  return u2f(sign | ((exp + 112u) << 23) | (man << 13));
+}
+
+/* Round-to-nearest-even of |f| onto a small float grid with `mbits` mantissa
+ * bits, exponent bias `bias`, saturating at the bit pattern `max_code`
+ * (whose float value has bits `max_f32`). */
+static inline uint8_t f32_to_fp8_sat(float f, int mbits, int bias, uint32_t max_f32, uint8_t max_code) {
+  const uint32_t u = f2u(f);
+  const uint8_t sign = (uint8_t)((u >> 24) & 0x80u);
+  const uint32_t a = u & 0x7FFFFFFFu;
+  if (a > 0x7F800000u) return 0x7F; /* NaN */
+  if (a >= max_f32) return (uint8_t)(sign | max_code);
+  const int e = (int)(a >> 23);                 /* biased fp32 exponent */
+  const int min_norm = 127 - bias + 1;          /* fp32 biased exp of the smallest normal */
+  if (e >= min_norm) {
+    const int sh = 23 - mbits;
+    uint32_t r = a >> sh;
+    const uint32_t rem = a & ((1u << sh) - 1u);
+    const uint32_t half = 1u << (sh - 1);
+    if (rem > half || (rem == half && (r & 1u))) r += 1u;
+    r -= (uint32_t)(min_norm - 1) << mbits;
+    if (r > max_code) r = max_code; /* rounding carried past the top: saturate */
+    return (uint8_t)(sign | r);
+  }
+  /* subnormal target: units of 2^(1 - bias - mbits) */
+  if (e == 0) return sign; /* fp32 zero / subnormal: far below half a unit */
+  const uint32_t mant = (a & 0x7FFFFFu) | 0x800000u; /* value = mant * 2^(e-150) */
+  const int sh = 150 - e + (1 - bias - mbits);       /* mant >> sh = value / unit */
+  if (sh > 25) return sign;
+  const uint32_t q0 = mant >> sh;
+  const uint32_t rem = mant & ((1u << sh) - 1u);
+  const uint32_t half = 1u << (sh - 1);
+  uint32_t q = q0;
+  if (rem > half || (rem == half && (q & 1u))) q += 1u;
+  return (uint8_t)(sign | q);
+}
+
+uint8_t orc_f32_to_e4m3(float f) { return f32_to_fp8_sat(f, 3, 7, 0x43E00000u /*448*/, 0x7E); }
+uint8_t orc_f32_to_e5m2(float f) { return f32_to_fp8_sat(f, 2, 15, 0x47600000u /*57344*/, 0x7B); }
+
+static inline float load_as_f32(const void* p, int64_t i, int dt) {
+  switch (dt) {
+    case ORC_F32: return ((const float*)p)[i];
+    case ORC_F16: return orc_f16_to_f32(((const uint16_t*)p)[i]);
+    default: return orc_bf16_to_f32(((const uint16_t*)p)[i]);
+  }
+}
+static inline int in_size(int dt) { return dt == ORC_F32 ? 4 : 2; }
+
+/* One element: quant_utils.h:62-78.  `scale` is only read in fp8 modes. */
+static inline void store_elem(void* dst, int64_t di, const void* src, int64_t si, int in_dt, int kv, float scale) {
+  if (kv == ORC_KV_AUTO) {
+    const int es = in_size(in_dt);
+    memcpy((char*)dst + di * es, (const char*)src + si * es, (size_t)es);
+  } else {
+    const float x = load_as_f32(src, si, in_dt) / scale;
+    ((uint8_t*)dst)[di] = (kv == ORC_KV_E4M3) ? orc_f32_to_e4m3(x) : orc_f32_to_e5m2(x);
+  }
+}
+
+/* Conversion table over all 65536 16-bit input patterns (in_dt F16 or BF16). */
+void orc_convert_table(int in_dt, int kv, float scale, uint8_t* out) {
+  for (uint32_t b = 0; b < 65536u; ++b) {
+    const float v = (in_dt == ORC_F16) ? orc_f16_to_f32((uint16_t)b) : orc_bf16_to_f32((uint16_t)b);
+    const float x = v / scale;
+    out[b] = (kv == ORC_KV_E5M2) ? orc_f32_to_e5m2(x) : orc_f32_to_e4m3(x);
+  }
+}
+
+/* Array conversion for float inputs: out[i] = fp8(x[i] / scale). */
+void orc_convert_f32(const float* x, int64_t n, int kv, float scale, uint8_t* out) {
+  for (int64_t i = 0; i < n; ++i) store_elem(out, i, x, i, ORC_F32, kv, scale);
+}
+
+/*
+ * Flash (NHD) layout: cache[block][offset][head][d], with arbitrary element
+ * strides for dims 0..2 (block_stride, page_stride, head_stride) and for the
+ * key/value token and head dims.  Strides are in ELEMENTS.  The reference
+ * kernel assumes head_stride == D and key head stride == D; the general form
+ * reduces to it.  Tokens with slot < 0 are skipped (cache.cpp:144-145).
+ * Returns 0, or -1 when a slot is >= num_slots (num_slots < 0 disables the check).
+ */
+int orc_reshape_and_cache_flash(const void* key, const void* value, void* key_cache, void* value_cache,
+                                const int64_t* slot_mapping, int64_t num_tokens, int64_t num_heads,
+                                int64_t head_size, int64_t block_size, int64_t key_stride_t,
+                                int64_t key_stride_h, int64_t value_stride_t, int64_t value_stride_h,
+                                int64_t block_stride, int64_t page_stride, int64_t head_stride, int in_dt,
+                                int kv, float k_scale, float v_scale, int64_t num_slots, int nthreads) {
+  int bad = 0;
+#ifdef _OPENMP
+  if (nthreads < 1) nthreads = 1;
+#pragma omp parallel for schedule(static) num_threads(nthreads) reduction(| : bad)
+#endif
+  for (int64_t t = 0; t < num_tokens; ++t) {
+    const int64_t slot = slot_mapping[t];
+    if (slot < 0) continue;
+    if (num_slots >= 0 && slot >= num_slots) {
+      bad |= 1;
+      continue;
+    }
+    const int64_t blk = slot / block_size, off = slot % block_size;
+    const int64_t dst0 = blk * block_stride + off * page_stride;
+    for (int64_t h = 0; h < num_heads; ++h) {
+      const int64_t ks = t * key_stride_t + h * key_stride_h;
+      const int64_t vs = t * value_stride_t + h * value_stride_h;
+      const int64_t d0 = dst0 + h * head_stride;
+      if (kv == ORC_KV_AUTO) {
+        const size_t es = (size_t)in_size(in_dt);
+        memcpy((char*)key_cache + d0 * es, (const char*)key + ks * es, (size_t)head_size * es);
+        memcpy((char*)value_cache + d0 * es, (const char*)value + vs * es, (size_t)head_size * es);
+      } else {
+        for (int64_t d = 0; d < head_size; ++d) {
+          store_elem(key_cache, d0 + d, key, ks + d, in_dt, kv, k_scale);
+          store_elem(value_cache, d0 + d, value, vs + d, in_dt, kv, v_scale);
+        }
+      }
+    }
+  }
+  (void)nthreads;
+  return bad ? -1 : 0;
+}
+
+/*
+ * Paged layout: key_cache [num_blocks, H, D/x, block_size, x] and
+ * value_cache [num_blocks, H, D, block_size], both contiguous
+ * (cache.cpp:57-67 index formulas, widened to 64 bits).
+ */
+int orc_reshape_and_cache(const void* key, const void* value, void* key_cache, void* value_cache,
+                          const int64_t* slot_mapping, int64_t num_tokens, int64_t num_heads,
+                          int64_t head_size, int64_t block_size, int64_t x, int64_t key_stride_t,
+                          int64_t key_stride_h, int64_t value_stride_t, int64_t value_stride_h, int in_dt,
+                          int kv, float k_scale, float v_scale, int64_t num_slots, int nthreads) {
+  int bad = 0;
+#ifdef _OPENMP
+  if (nthreads < 1) nthreads = 1;
+#pragma omp parallel for schedule(static) num_threads(nthreads) reduction(| : bad)
+#endif
+  for (int64_t t = 0; t < num_tokens; ++t) {
+    const int64_t slot = slot_mapping[t];
+    if (slot < 0) continue;
+    if (num_slots >= 0 && slot >= num_slots) {
+      bad |= 1;
+      continue;
+    }
+    const int64_t blk = slot / block_size, off = slot % block_size;
+    for (int64_t h = 0; h < num_heads; ++h) {
+      for (int64_t d = 0; d < head_size; ++d) {
+        const int64_t kdst = blk * num_heads * (head_size / x) * block_size * x +
+                             h * (head_size / x) * block_size * x + (d / x) * block_size * x + off * x +
+                             d % x;
+        const int64_t vdst =
+            blk * num_heads * head_size * block_size + h * head_size * block_size + d * block_size + off;
+        store_elem(key_cache, kdst, key, t * key_stride_t + h * key_stride_h + d, in_dt, kv, k_scale);
+        store_elem(value_cache, vdst, value, t * value_stride_t + h * value_stride_h + d, in_dt, kv,
+                   v_scale);
+      }
+    }
+  }
+  (void)nthreads;
+  return bad ? -1 : 0;
+}
+
+int orc_max_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}

@@ -1,0 +1,27 @@
+"""numpy views of CPU torch tensors for the oracle -- TEST INFRASTRUCTURE ONLY.
+
+The oracle itself is torch-free; callers that hold torch tensors (tests, the smoke check,
+the benchmark's CPU-baseline leg) use these views so strides survive the hand-over."""
+import numpy as np
+import torch
+
+ORC_IN = {torch.float16: "f16", torch.bfloat16: "bf16", torch.float32: "f32"}
+
+
+def as_np(t: torch.Tensor) -> np.ndarray:
+    """numpy view with the same strides; 16-bit floats as uint16 bit patterns, fp8 as uint8."""
+    assert not t.is_cuda
+    if t.dtype in (torch.float16, torch.bfloat16):
+        return t.view(torch.int16).numpy().view(np.uint16)
+    if t.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        return t.view(torch.uint8).numpy()
+    return t.numpy()
+
+
+def run(layout: str, key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype: str,
+        k_scale: float, v_scale: float, threads: int = 1) -> None:
+    """Runs the oracle in place on CPU torch tensors."""
+    import oracle
+    fn = oracle.reshape_and_cache_flash if layout == "flash" else oracle.reshape_and_cache
+    fn(as_np(key), as_np(value), as_np(key_cache), as_np(value_cache), slot_mapping.numpy(), kv_cache_dtype,
+       float(k_scale), float(v_scale), ORC_IN[key.dtype], threads=threads)

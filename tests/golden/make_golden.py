@@ -1,0 +1,171 @@
+"""Generates the golden fixtures in this folder from the reference project.
+
+Run where the reference checkout is available (it is NOT needed to run the tests):
+
+    python tests/golden/make_golden.py --reference /root/reference
+
+What comes from the reference, imported as Python and executed on the CPU:
+  * the cache factories ``create_kv_caches_with_random`` (paged layout) and
+    ``create_kv_caches_with_random_flash`` (flash layout, ``[:, 0]`` / ``[:, 1]``
+    views of one allocation) and ``seed_everything`` from its tests/utils.py;
+  * PyTorch's own ``float -> float8`` cast, which is the conversion the reference
+    kernels call (csrc/quantization/fp8/quant_utils.h:70-74 there).
+What is restated here because it only exists inline in GPU-only test functions:
+  * the input recipe (``qkv = randn(T, 3, H, D); _, key, value = qkv.unbind(1)``,
+    ``random.sample`` slots: tests/test_cache.py:88-93, :211-222) and
+  * the expected-result loops (tests/test_cache.py:155-164 paged, :284-292 flash).
+
+Each ``*.npz`` holds the inputs, the caches before the call and the caches the
+reference's loop produces.  16-bit floats are stored as uint16 bit patterns and
+fp8 as uint8, so the files are readable without torch.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import os
+import random
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+DT = {"half": torch.half, "bfloat16": torch.bfloat16, "float": torch.float}
+
+
+def load_reference_utils(ref_root: str):
+    spec = importlib.util.spec_from_file_location("reference_tests_utils", os.path.join(ref_root, "tests", "utils.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def bits(t: torch.Tensor) -> np.ndarray:
+    """Raw storage of a (possibly strided) tensor as a contiguous numpy array."""
+    t = t.contiguous()
+    if t.dtype in (torch.half, torch.bfloat16):
+        return t.view(torch.int16).numpy().view(np.uint16).copy()
+    if t.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        return t.view(torch.uint8).numpy().copy()
+    return t.numpy().copy()
+
+
+def quantise_like_reference(x: torch.Tensor, scale: torch.Tensor, kv_cache_dtype: str) -> torch.Tensor:
+    """float(src) / scale, then torch's cast (quant_utils.h:70-74 of the reference)."""
+    q = x.float() / scale
+    return q.to(torch.float8_e5m2 if kv_cache_dtype == "fp8_e5m2" else torch.float8_e4m3fn)
+
+
+def make_case(ru, layout: str, dtype: str, kv_cache_dtype: str, T: int, H: int, D: int, bs: int, nb: int,
+              seed: int, scale_div: float, n_skip: int = 0) -> dict:
+    tdt = DT[dtype]
+    ru.seed_everything(seed)
+    slots = random.sample(range(nb * bs), T)
+    for i in random.sample(range(T), n_skip):
+        slots[i] = -1
+    slot_mapping = torch.tensor(slots, dtype=torch.long)
+    qkv = torch.randn(T, 3, H, D, dtype=tdt)
+    _, key, value = qkv.unbind(dim=1)
+    factory = ru.create_kv_caches_with_random_flash if layout == "flash" else ru.create_kv_caches_with_random
+    kcs, vcs = factory(nb, bs, 1, H, D, kv_cache_dtype, tdt, seed=seed, device="cpu")
+    key_cache, value_cache = kcs[0], vcs[0]
+    if scale_div == 64.0:  # the reference tests' recipe (tests/test_cache.py:110-111)
+        k_scale = (key.amax() / scale_div).to(torch.float32)
+        v_scale = (value.amax() / scale_div).to(torch.float32)
+    else:  # deployment recipe: nothing saturates
+        k_scale = (key.float().abs().amax() / scale_div).to(torch.float32)
+        v_scale = (value.float().abs().amax() / scale_div).to(torch.float32)
+
+    exp_k, exp_v = key_cache.contiguous().clone(), value_cache.contiguous().clone()
+    if kv_cache_dtype == "auto":
+        src_k, src_v = key, value
+    else:
+        src_k = quantise_like_reference(key, k_scale, kv_cache_dtype)
+        src_v = quantise_like_reference(value, v_scale, kv_cache_dtype)
+    for i in range(T):
+        if slots[i] < 0:  # csrc/cache.cpp:49, :145
+            continue
+        blk, off = slots[i] // bs, slots[i] % bs
+        if layout == "flash":
+            exp_k[blk, off, :, :] = src_k[i]
+            exp_v[blk, off, :, :] = src_v[i]
+        else:
+            x = exp_k.shape[4]
+            exp_k[blk, :, :, off, :] = src_k[i].reshape(H, D // x, x)
+            exp_v[blk, :, :, off] = src_v[i]
+    return dict(
+        layout=layout, dtype=dtype, kv_cache_dtype=kv_cache_dtype, T=T, H=H, D=D, block_size=bs, num_blocks=nb,
+        qkv=bits(qkv), slot_mapping=slot_mapping.numpy(), key_cache_before=bits(key_cache),
+        value_cache_before=bits(value_cache), key_cache_after=bits(exp_k), value_cache_after=bits(exp_v),
+        k_scale=np.float32(k_scale.item()), v_scale=np.float32(v_scale.item()),
+        max_abs_scaled=np.float32(max((key.float() / k_scale).abs().max().item(),
+                                      (value.float() / v_scale).abs().max().item())),
+        cache_is_view=np.bool_(layout == "flash"))
+
+
+def make_tables() -> dict:
+    """torch's e4m3 / e5m2 cast over every bf16 and fp16 bit pattern at a few scales."""
+    out = {}
+    pats = torch.arange(65536, dtype=torch.int32).to(torch.int16)
+    scales = np.array([1.0, 0.0078125, 0.013671875, 3.7, 0.3333333432674408, 2.2321429569274187e-03], dtype=np.float32)
+    out["scales"] = scales
+    for name, tdt in (("bf16", torch.bfloat16), ("f16", torch.float16)):
+        x = pats.view(tdt).float()
+        for kv, fdt in (("e4m3", torch.float8_e4m3fn), ("e5m2", torch.float8_e5m2)):
+            rows = [(x / torch.tensor(float(s), dtype=torch.float32)).to(fdt).view(torch.uint8).numpy() for s in scales]
+            out[f"{name}_{kv}"] = np.stack(rows)
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ns = ap.parse_args()
+    ru = load_reference_utils(ns.reference)
+
+    cases = []
+    # auto: the reference's own matrix (dtypes x head sizes x block sizes, tests/test_cache.py:14-19),
+    # shrunk in tokens/heads/blocks so the fixtures stay small
+    hs_bs = [(64, 8), (80, 16), (120, 32), (256, 16), (128, 16)]
+    for layout in ("flash", "paged"):
+        for dtype in ("half", "bfloat16", "float"):
+            for D, bs in hs_bs:
+                if dtype == "float" and D in (80, 128):
+                    continue
+                cases.append(dict(layout=layout, dtype=dtype, kv_cache_dtype="auto", T=20, H=2, D=D, bs=bs,
+                                  nb=max(2, 32 // bs + 1), seed=0, scale_div=64.0))
+        # the reference's MINI profile (tests/test_cache.py:40-46): 1 token, head_size 8, 4 blocks of 8
+        cases.append(dict(layout=layout, dtype="half", kv_cache_dtype="auto", T=1, H=8, D=8, bs=8, nb=4, seed=0,
+                          scale_div=64.0))
+        # padding: a third of the tokens carry slot -1
+        cases.append(dict(layout=layout, dtype="bfloat16", kv_cache_dtype="auto", T=21, H=2, D=64, bs=16, nb=3,
+                          seed=5, scale_div=64.0, n_skip=7))
+        # fp8: scale = amax/64 as in the reference's (disabled) fp8 branch, and amax/448 as deployed
+        for dtype in ("half", "bfloat16"):
+            for div in (64.0, 448.0):
+                cases.append(dict(layout=layout, dtype=dtype, kv_cache_dtype="fp8", T=20, H=2, D=64 if div == 64.0 else 128,
+                                  bs=16, nb=3, seed=1, scale_div=div))
+        cases.append(dict(layout=layout, dtype="float", kv_cache_dtype="fp8", T=20, H=2, D=64, bs=16, nb=3, seed=2,
+                          scale_div=448.0))
+        cases.append(dict(layout=layout, dtype="bfloat16", kv_cache_dtype="fp8_e5m2", T=20, H=2, D=64, bs=16, nb=3,
+                          seed=3, scale_div=64.0))
+
+    names = []
+    for c in cases:
+        name = "{layout}_{dtype}_{kv_cache_dtype}_T{T}_H{H}_D{D}_bs{bs}_nb{nb}_s{seed}_div{d}".format(
+            d=int(c["scale_div"]), **c) + ("_skip" if c.get("n_skip") else "")
+        data = make_case(ru, **c)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **data)
+        names.append(name)
+    np.savez_compressed(os.path.join(HERE, "fp8_tables.npz"), **make_tables())
+    with open(os.path.join(HERE, "MANIFEST.txt"), "w") as f:
+        f.write("# written by make_golden.py with torch %s\n" % torch.__version__)
+        for n in names + ["fp8_tables"]:
+            f.write(n + ".npz\n")
+    total = sum(os.path.getsize(os.path.join(HERE, n + ".npz")) for n in names + ["fp8_tables"])
+    print(f"{len(names)} cases + tables, {total / 1e6:.2f} MB")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,98 @@
+"""Shared helpers of the test-suite: golden fixtures, torch <-> numpy views, oracle calls."""
+from __future__ import annotations
+
+import glob
+import os
+
+import numpy as np
+import torch
+
+import oracle
+from oracle.torch_views import ORC_IN, as_np  # noqa: F401
+from oracle import torch_views
+
+GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+TORCH_DT = {"half": torch.float16, "bfloat16": torch.bfloat16, "float": torch.float32}
+
+
+def golden_files() -> list[str]:
+    with open(os.path.join(GOLDEN_DIR, "MANIFEST.txt")) as f:
+        names = [ln.strip() for ln in f if ln.strip() and not ln.startswith("#")]
+    return [n for n in names if n != "fp8_tables.npz"]
+
+
+def from_bits(a: np.ndarray, dtype: torch.dtype) -> torch.Tensor:
+    """Inverse of the fixtures' storage: uint16 bit patterns -> half/bf16 tensor."""
+    a = np.ascontiguousarray(a)
+    if dtype in (torch.float16, torch.bfloat16):
+        return torch.from_numpy(a.view(np.int16)).view(dtype)
+    if dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        return torch.from_numpy(a).view(dtype)
+    return torch.from_numpy(a)
+
+
+def cache_torch_dtype(in_dtype: torch.dtype, kv_cache_dtype: str) -> torch.dtype:
+    if kv_cache_dtype == "auto":
+        return in_dtype
+    return torch.float8_e5m2 if kv_cache_dtype == "fp8_e5m2" else torch.float8_e4m3fn
+
+
+class GoldenCase:
+    """One fixture, rebuilt with the reference's memory layout: key/value are slices of
+    a [T, 3, H, D] tensor, flash caches are the [:, 0] and [:, 1] views of one allocation."""
+
+    def __init__(self, fname: str):
+        z = np.load(os.path.join(GOLDEN_DIR, fname))
+        self.name = fname
+        self.layout = str(z["layout"])
+        self.kv_cache_dtype = str(z["kv_cache_dtype"])
+        self.dtype = TORCH_DT[str(z["dtype"])]
+        self.block_size = int(z["block_size"])
+        self.k_scale = float(z["k_scale"])
+        self.v_scale = float(z["v_scale"])
+        self.max_abs_scaled = float(z["max_abs_scaled"])
+        self.qkv = from_bits(z["qkv"], self.dtype)
+        self.key, self.value = self.qkv[:, 1], self.qkv[:, 2]
+        self.slot_mapping = torch.from_numpy(z["slot_mapping"].astype(np.int64))
+        cdt = cache_torch_dtype(self.dtype, self.kv_cache_dtype)
+        kb, vb = from_bits(z["key_cache_before"], cdt), from_bits(z["value_cache_before"], cdt)
+        if self.layout == "flash":
+            both = torch.stack([kb.view(torch.uint8), vb.view(torch.uint8)], dim=1).contiguous()
+            both = both.view(cdt) if cdt != torch.uint8 else both
+            self.alloc = both
+            self.key_cache, self.value_cache = both[:, 0], both[:, 1]
+        else:
+            self.alloc = None
+            self.key_cache, self.value_cache = kb.clone(), vb.clone()
+        self.key_cache_after = from_bits(z["key_cache_after"], cdt)
+        self.value_cache_after = from_bits(z["value_cache_after"], cdt)
+
+
+def oracle_call(layout: str, key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype: str,
+                k_scale: float, v_scale: float, threads: int = 1) -> None:
+    """Runs the CPU oracle in place on CPU torch tensors (views keep their strides)."""
+    torch_views.run(layout, key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype, k_scale, v_scale,
+                    threads=threads)
+
+
+def same_bytes(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """Bit-for-bit equality (NaN-safe, sign-of-zero-safe)."""
+    a, b = a.contiguous(), b.contiguous()
+    if a.shape != b.shape or a.dtype != b.dtype:
+        return False
+    return bool(torch.equal(a.view(torch.uint8), b.view(torch.uint8)))
+
+
+def fill_pattern_(t: torch.Tensor, seed: int) -> torch.Tensor:
+    """Deterministic, recognisable non-constant fill of a cache (any dtype, any device)."""
+    g = torch.Generator(device=t.device)
+    g.manual_seed(seed)
+    raw = t.view(torch.uint8) if t.is_contiguous() else None
+    assert raw is not None, "fill contiguous allocations, then take views"
+    n = raw.numel()
+    src = torch.randint(0, 120, (min(n, 1 << 20),), dtype=torch.uint8, device=t.device, generator=g)
+    flat = raw.view(-1)
+    reps = (n + src.numel() - 1) // src.numel()
+    flat.copy_(src.repeat(reps)[:n])
+    return t

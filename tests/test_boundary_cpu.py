@@ -1,0 +1,90 @@
+"""What can be checked about the drop-in boundary without a GPU: the C ABI library loads
+and exports every declared symbol, argument validation answers before any CUDA call,
+and the torch extension registers the reference's schemas (CUDA only, no CPU path)."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from tests.conftest import REPO
+from vllm_xpu_kernels import cabi
+
+
+def declared_symbols() -> list[str]:
+    names = []
+    inc = os.path.join(REPO, "include")
+    for fn in sorted(os.listdir(inc)):
+        if fn.endswith(".h"):
+            text = open(os.path.join(inc, fn)).read()
+            names += re.findall(r"KVC_API\s+[\w\s\*]+?\b(kvc_\w+)\s*\(", text)
+    return names
+
+
+def test_header_symbols_are_exported():
+    names = declared_symbols()
+    assert set(names) == set(cabi.SYMBOLS) and len(names) >= 8
+    L = cabi.lib()
+    for n in names:
+        assert getattr(L, n) is not None
+    assert L.kvc_version() >= 100
+
+
+def test_kv_cache_dtype_strings():
+    assert cabi.parse_kv_cache_dtype("auto") == 0
+    assert cabi.parse_kv_cache_dtype("fp8") == 1
+    assert cabi.parse_kv_cache_dtype("fp8_e4m3") == 1
+    assert cabi.parse_kv_cache_dtype("fp8_e5m2") == 2
+    with pytest.raises(RuntimeError, match="Unsupported data type of kv cache: int8"):
+        cabi.parse_kv_cache_dtype("int8")
+
+
+def test_argument_validation_needs_no_device():
+    L = cabi.lib()
+    buf = (ctypes.c_char * 4096)()
+    p = ctypes.addressof(buf)
+    args = dict(num_tokens=4, H=2, D=16, bs=4)
+
+    def flash(key=p, slots=p, num_tokens=4, in_dtype=2, kv=0, block_size=4, k_scale=0):
+        return L.kvc_reshape_and_cache_flash(key, p, p, p, slots, num_tokens, args["H"], args["D"], block_size,
+                                             32, 16, 32, 16, 128, 32, 16, in_dtype, kv, k_scale, 0, None)
+
+    assert flash(num_tokens=0) == 0                     # nothing to do: no launch, no error
+    assert flash(key=None) == 1 and "non-NULL" in cabi.last_error()
+    assert flash(num_tokens=-1) == 1
+    assert flash(block_size=0) == 1
+    assert flash(in_dtype=7) == 2 and "Unsupported input type" in cabi.last_error()
+    assert flash(kv=9) == 2 and "Unsupported data type" in cabi.last_error()
+    assert flash(kv=1, k_scale=0) == 1 and "k_scale" in cabi.last_error()
+    assert flash(key=p + 1) == 1                         # misaligned for bf16
+    # paged: x must divide head_size
+    rc = L.kvc_reshape_and_cache(p, p, p, p, p, 4, 2, 16, 4, 5, 32, 16, 32, 16, 2, 0, None, None, None)
+    assert rc == 1 and "multiple of x" in cabi.last_error()
+    assert L.kvc_count_bad_slots(p, 4, 16, None, None) == 1
+
+
+def test_torch_extension_registers_reference_schemas():
+    import vllm_xpu_kernels._C  # noqa: F401
+    ops = torch.ops._C_cache_ops
+    # the reference's schema text (csrc/torch_bindings.cpp:107-112, :116-122), parsed by torch
+    want = ("(Tensor key, Tensor value, Tensor! key_cache, Tensor! value_cache, Tensor slot_mapping, "
+            "str kv_cache_dtype, Tensor k_scale, Tensor v_scale) -> ()")
+    for name in ("reshape_and_cache", "reshape_and_cache_flash"):
+        schema = getattr(ops, name).default._schema
+        assert str(schema) == str(torch._C.parse_schema(f"_C_cache_ops::{name}{want}"))
+        assert [a.name for a in schema.arguments] == ["key", "value", "key_cache", "value_cache", "slot_mapping",
+                                                      "kv_cache_dtype", "k_scale", "v_scale"]
+        muts = [a.name for a in schema.arguments if a.alias_info is not None and a.alias_info.is_write]
+        assert muts == ["key_cache", "value_cache"]
+    from vllm_xpu_kernels import ops as wrappers
+    assert callable(wrappers.reshape_and_cache) and callable(wrappers.reshape_and_cache_flash)
+
+
+def test_no_cpu_fallback():
+    import vllm_xpu_kernels._C  # noqa: F401
+    k = torch.zeros(2, 2, 8)
+    c = torch.zeros(2, 2, 2, 8)
+    with pytest.raises(NotImplementedError):
+        torch.ops._C_cache_ops.reshape_and_cache_flash(k, k, c, c.clone(), torch.zeros(2, dtype=torch.long), "auto",
+                                                       torch.ones(1), torch.ones(1))

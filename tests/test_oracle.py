@@ -1,0 +1,108 @@
+"""The CPU oracle against the fixtures generated from the reference (tests/golden/)."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tests import helpers as H
+
+
+@pytest.mark.parametrize("fname", H.golden_files())
+def test_oracle_reproduces_reference_fixture(fname):
+    c = H.GoldenCase(fname)
+    if c.kv_cache_dtype != "auto":
+        # the reference's cast does not saturate; the two definitions agree while |x/scale| <= 464
+        limit = 464.0 if c.kv_cache_dtype != "fp8_e5m2" else 57344.0
+        assert c.max_abs_scaled <= limit
+    H.oracle_call(c.layout, c.key, c.value, c.key_cache, c.value_cache, c.slot_mapping, c.kv_cache_dtype,
+                  c.k_scale, c.v_scale)
+    assert H.same_bytes(c.key_cache, c.key_cache_after)
+    assert H.same_bytes(c.value_cache, c.value_cache_after)
+
+
+@pytest.mark.parametrize("in_dtype,tdt", [("bf16", torch.bfloat16), ("f16", torch.float16)])
+def test_conversion_tables_match_torch_cast(in_dtype, tdt):
+    z = np.load(os.path.join(H.GOLDEN_DIR, "fp8_tables.npz"))
+    pats = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(tdt).float().numpy()
+    for si, scale in enumerate(z["scales"]):
+        q = pats / np.float32(scale)
+        finite = ~np.isnan(q)
+        for kv, name, lim in (("fp8_e4m3", "e4m3", 464.0), ("fp8_e5m2", "e5m2", 57344.0)):
+            want = z[f"{in_dtype}_{name}"][si]
+            got = oracle.convert_table(in_dtype, kv, float(scale))
+            agree = finite & (np.abs(q) <= lim)
+            assert np.array_equal(got[agree], want[agree]), (in_dtype, kv, scale)
+            # beyond that the oracle saturates where torch produces NaN / inf
+            over = finite & ~agree
+            top = 0x7E if kv == "fp8_e4m3" else 0x7B
+            assert np.all((got[over] & 0x7F) == top)
+            assert np.all((got[over] >> 7) == (q[over] < 0))
+            assert np.all(got[~finite] == 0x7F)
+
+
+def test_e4m3_converter_against_independent_numpy_restatement():
+    rng = np.random.default_rng(0)
+    x = np.concatenate([
+        rng.standard_normal(200000).astype(np.float32) * 100,
+        rng.standard_normal(200000).astype(np.float32) * 0.01,
+        (rng.integers(0, 2**32, 400000, dtype=np.uint64).astype(np.uint32)).view(np.float32),
+        np.array([0.0, -0.0, 2.0**-10, -(2.0**-10), 1.5 * 2.0**-10, 2.0**-9, 3 * 2.0**-10, 2.0**-6, 0.0165,
+                  447.9, 448.0, 463.9, 464.0, 465.0, 1e9, -1e9, np.inf, -np.inf, np.nan, 17.0, 18.0, 19.0, 0.9375 * 2**-6],
+                 dtype=np.float32),
+    ])
+    got = oracle.convert_f32(x, "fp8_e4m3", 1.0)
+    want = oracle.np_f32_to_e4m3(x)
+    assert np.array_equal(got, want)
+    # known answers
+    ka = [(0.0, 0x00), (-0.0, 0x80), (2.0**-10, 0x00), (1.5 * 2.0**-10, 0x01), (2.0**-9, 0x01),
+          (3 * 2.0**-10, 0x02), (2.0**-6, 0x08), (448.0, 0x7E), (464.0, 0x7E), (1e9, 0x7E), (-1e9, 0xFE),
+          (1.0, 0x38), (17.0, 0x58), (19.0, 0x5A)]
+    for v, code in ka:
+        assert oracle.lib().orc_f32_to_e4m3(v) == code, v
+    assert oracle.lib().orc_f32_to_e4m3(float("inf")) == 0x7E
+    assert oracle.lib().orc_f32_to_e4m3(float("nan")) == 0x7F
+
+
+def test_skip_short_slot_mapping_and_range_check():
+    T, Hh, D, bs, nb = 6, 2, 16, 4, 3
+    key = torch.randn(T + 3, Hh, D).to(torch.bfloat16)
+    value = torch.randn(T + 3, Hh, D).to(torch.bfloat16)
+    kc = torch.zeros(nb, bs, Hh, D, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    slots = torch.tensor([5, -1, 0, 11, -1, 7])
+    H.oracle_call("flash", key, value, kc, vc, slots, "auto", 1.0, 1.0)
+    flat = kc.view(nb * bs, Hh, D)
+    for i, s in enumerate(slots.tolist()):
+        if s >= 0:
+            assert H.same_bytes(flat[s], key[i])
+    untouched = [s for s in range(nb * bs) if s not in (5, 0, 11, 7)]
+    assert bool((flat[untouched] == 0).all())
+    with pytest.raises(IndexError):
+        H.oracle_call("flash", key, value, kc, vc, torch.tensor([nb * bs]), "auto", 1.0, 1.0)
+
+
+def test_threads_do_not_change_results():
+    w_key = torch.randn(300, 4, 32).to(torch.float16)
+    w_val = torch.randn(300, 4, 32).to(torch.float16)
+    slots = torch.randperm(64 * 8)[:300]
+    outs = []
+    for th in (1, 4):
+        kc = torch.zeros(64, 8, 4, 32, dtype=torch.uint8)
+        vc = torch.zeros_like(kc)
+        H.oracle_call("flash", w_key, w_val, kc, vc, slots, "fp8", 0.01, 0.02, threads=th)
+        outs.append((kc, vc))
+    assert H.same_bytes(outs[0][0], outs[1][0]) and H.same_bytes(outs[0][1], outs[1][1])
+
+
+def test_three_instruction_division_is_exact_on_a_subsample():
+    """Every 16th scale significand x every 16-bit-float significand; the full set is
+    `oracle/prove_fast_div 1` (2^33 cases, a few seconds)."""
+    exe = os.path.join(os.path.dirname(oracle.__file__), "prove_fast_div")
+    if not os.path.exists(exe):
+        subprocess.run(["make", "-C", os.path.dirname(exe), "prove_fast_div"], check=True, capture_output=True)
+    r = subprocess.run([exe, "16"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "mismatches 0" in r.stdout

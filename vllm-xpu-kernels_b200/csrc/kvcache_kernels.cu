@@ -1,0 +1,812 @@
+// Paged KV-cache write kernels for NVIDIA B200 (sm_100a) and their C ABI.
+//
+// Two scatter operations, both pure HBM traffic (no contraction, no tensor cores):
+//   flash layout   cache[block][offset][head][d]          (kvc_reshape_and_cache_flash)
+//   paged layout   K cache[block][head][d/x][offset][x],
+//                  V cache[block][head][d][offset]         (kvc_reshape_and_cache)
+// Each token's key/value row goes to the cache slot named by slot_mapping; negative
+// slots are skipped; in fp8 modes every element is divided by a per-tensor scale in
+// IEEE fp32 and rounded to nearest even with saturation by the hardware cvt.
+//
+// The reference plugin's counterparts are csrc/cache.cpp:13-189 (device code) and
+// :409-489 (host launchers); the per-element rule is
+// csrc/quantization/fp8/quant_utils.h:62-78.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <type_traits>
+
+#include "kvcache_b200.h"
+
+namespace kvc {
+
+// ---------------------------------------------------------------------------------------------
+// error plumbing
+// ---------------------------------------------------------------------------------------------
+static thread_local std::string g_last_error;
+
+static int fail(int code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+
+#define KVC_CUDA_TRY(expr)                                                                      \
+  do {                                                                                          \
+    cudaError_t _e = (expr);                                                                    \
+    if (_e != cudaSuccess)                                                                      \
+      return fail(KVC_ERR_CUDA, std::string(#expr " failed: ") + cudaGetErrorString(_e));       \
+  } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// division of a 31-bit index by a launch constant: q = umulhi(n, mul) >> shr
+// ---------------------------------------------------------------------------------------------
+struct FastDiv {
+  uint32_t d, mul, shr;
+  __host__ FastDiv(uint32_t div = 1) : d(div), mul(0), shr(0) {
+    if (div > 1) {
+      uint32_t lg = 0;
+      while ((1ull << lg) < div) ++lg;  // ceil(log2 div)
+      const uint32_t p = 31 + lg;
+      mul = static_cast<uint32_t>(((1ull << p) + div - 1) / div);
+      shr = p - 32;
+    }
+  }
+  // exact for 0 <= n < 2^31
+  __device__ __forceinline__ uint32_t div(uint32_t n) const { return d == 1 ? n : (__umulhi(n, mul) >> shr); }
+};
+
+// ---------------------------------------------------------------------------------------------
+// vector global memory access.  Loads are read-once streams: bypass L1 allocation.
+// ---------------------------------------------------------------------------------------------
+template <int BYTES>
+struct alignas(BYTES >= 16 ? 16 : BYTES) Chunk {
+  unsigned char b[BYTES];
+};
+
+template <int BYTES>
+__device__ __forceinline__ void load_chunk(Chunk<BYTES>& c, const void* gptr) {
+  if constexpr (BYTES >= 16) {
+    static_assert(BYTES % 16 == 0, "wide chunks are whole 16-byte vectors");
+    uint4* dst = reinterpret_cast<uint4*>(c.b);
+#pragma unroll
+    for (int i = 0; i < BYTES / 16; ++i) {
+      uint4 v;
+      asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                   : "l"(static_cast<const char*>(gptr) + 16 * i));
+      dst[i] = v;
+    }
+  } else if constexpr (BYTES == 8) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(gptr));
+    *reinterpret_cast<uint2*>(c.b) = v;
+  } else if constexpr (BYTES == 4) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(gptr));
+    *reinterpret_cast<uint32_t*>(c.b) = v;
+  } else if constexpr (BYTES == 2) {
+    uint16_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(gptr));
+    *reinterpret_cast<uint16_t*>(c.b) = v;
+  } else {
+    static_assert(BYTES == 1, "unsupported chunk size");
+    c.b[0] = *static_cast<const unsigned char*>(gptr);
+  }
+}
+
+// Stores PIECE bytes taken at byte offset `at` of the chunk; PIECE in {16,8,4,2,1}.
+template <int PIECE, int BYTES>
+__device__ __forceinline__ void store_piece(void* gptr, const Chunk<BYTES>& c, int at) {
+  if constexpr (PIECE == 16) {
+    *reinterpret_cast<uint4*>(gptr) = *reinterpret_cast<const uint4*>(c.b + at);
+  } else if constexpr (PIECE == 8) {
+    *reinterpret_cast<uint2*>(gptr) = *reinterpret_cast<const uint2*>(c.b + at);
+  } else if constexpr (PIECE == 4) {
+    *reinterpret_cast<uint32_t*>(gptr) = *reinterpret_cast<const uint32_t*>(c.b + at);
+  } else if constexpr (PIECE == 2) {
+    *reinterpret_cast<uint16_t*>(gptr) = *reinterpret_cast<const uint16_t*>(c.b + at);
+  } else {
+    *reinterpret_cast<unsigned char*>(gptr) = c.b[at];
+  }
+}
+
+template <int BYTES>
+__device__ __forceinline__ void store_chunk(void* gptr, const Chunk<BYTES>& c) {
+  constexpr int P = BYTES >= 16 ? 16 : BYTES;
+#pragma unroll
+  for (int i = 0; i < BYTES / P; ++i) store_piece<P>(static_cast<char*>(gptr) + P * i, c, P * i);
+}
+
+// ---------------------------------------------------------------------------------------------
+// element conversion
+// ---------------------------------------------------------------------------------------------
+template <typename Tin>
+__device__ __forceinline__ float to_f32(const unsigned char* p);
+template <>
+__device__ __forceinline__ float to_f32<float>(const unsigned char* p) {
+  return *reinterpret_cast<const float*>(p);
+}
+template <>
+__device__ __forceinline__ float to_f32<__half>(const unsigned char* p) {
+  return __half2float(*reinterpret_cast<const __half*>(p));
+}
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(const unsigned char* p) {
+  return __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(p)) << 16);
+}
+
+// Two floats -> two fp8 bytes (lo in bits 0..7), round-to-nearest-even, saturating.
+template <int KV>
+__device__ __forceinline__ uint32_t cvt_fp8x2(float lo, float hi) {
+  uint16_t r;
+  if constexpr (KV == KVC_KV_FP8_E4M3) {
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  } else {
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  }
+  return r;
+}
+
+// RN(x / s) in three instructions, given r = RN(1/s): one Newton correction of the
+// product x*r with an exact residual.  For 16-bit float x this equals the IEEE quotient
+// for every significand pair (checked exhaustively on the CPU) as long as nothing under-
+// or overflows; the callers below bound s and repair the overflow case.
+__device__ __forceinline__ float quot_fast(float x, float s, float r) {
+  const float q0 = __fmul_rn(x, r);
+  const float e = __fmaf_rn(-q0, s, x);
+  return __fmaf_rn(e, r, q0);
+}
+
+// True when one of the four bytes is a NaN code (low seven bits all set).
+__device__ __forceinline__ bool has_nan_byte(uint32_t w) {
+  return (((w & 0x7F7F7F7Fu) + 0x01010101u) & 0x80808080u) != 0u;
+}
+
+struct ScaleCtx {
+  float s;    // the scale
+  float r;    // RN(1/s)
+  bool fast;  // s is inside the window where quot_fast is exact
+};
+
+__device__ __forceinline__ ScaleCtx make_scale_ctx(const float* scale_ptr) {
+  ScaleCtx c;
+  c.s = __ldg(scale_ptr);
+  c.r = __frcp_rn(c.s);
+  const float a = fabsf(c.s);
+  // 2^-60 <= |s| <= 2^60: r is normal, and for any 16-bit float x whose quotient can
+  // round to a non-zero fp8 value the residual fma is exact (no underflow).  Larger
+  // quotients that overflow x*r surface as a NaN byte and are redone exactly.
+  c.fast = (a >= 8.673617379884035e-19f) && (a <= 1.152921504606847e18f);
+  return c;
+}
+
+// Converts VEC input elements to VEC output elements (AUTO: bit copy).
+template <typename Tin, int KV, int VEC>
+__device__ __forceinline__ void convert_chunk(const Chunk<VEC * (int)sizeof(Tin)>& in,
+                                              Chunk<(KV == KVC_KV_AUTO ? VEC * (int)sizeof(Tin) : VEC)>& out,
+                                              const ScaleCtx& sc) {
+  if constexpr (KV == KVC_KV_AUTO) {
+    out = in;
+  } else {
+    constexpr int ES = (int)sizeof(Tin);
+    if constexpr (VEC >= 4 && ES == 2) {
+      if (sc.fast) {
+#pragma unroll
+        for (int i = 0; i < VEC; i += 4) {
+          const float x0 = to_f32<Tin>(in.b + ES * (i + 0));
+          const float x1 = to_f32<Tin>(in.b + ES * (i + 1));
+          const float x2 = to_f32<Tin>(in.b + ES * (i + 2));
+          const float x3 = to_f32<Tin>(in.b + ES * (i + 3));
+          uint32_t w = cvt_fp8x2<KV>(quot_fast(x0, sc.s, sc.r), quot_fast(x1, sc.s, sc.r)) |
+                       (cvt_fp8x2<KV>(quot_fast(x2, sc.s, sc.r), quot_fast(x3, sc.s, sc.r)) << 16);
+          if (has_nan_byte(w)) {  // NaN input, or x*r overflowed: redo with the IEEE divide
+            w = cvt_fp8x2<KV>(__fdiv_rn(x0, sc.s), __fdiv_rn(x1, sc.s)) |
+                (cvt_fp8x2<KV>(__fdiv_rn(x2, sc.s), __fdiv_rn(x3, sc.s)) << 16);
+          }
+          *reinterpret_cast<uint32_t*>(out.b + i) = w;
+        }
+        return;
+      }
+    }
+    if constexpr (VEC >= 2) {
+#pragma unroll
+      for (int i = 0; i < VEC; i += 2) {
+        const float x0 = to_f32<Tin>(in.b + ES * i);
+        const float x1 = to_f32<Tin>(in.b + ES * (i + 1));
+        *reinterpret_cast<uint16_t*>(out.b + i) =
+            static_cast<uint16_t>(cvt_fp8x2<KV>(__fdiv_rn(x0, sc.s), __fdiv_rn(x1, sc.s)));
+      }
+    } else {
+      out.b[0] = static_cast<unsigned char>(cvt_fp8x2<KV>(__fdiv_rn(to_f32<Tin>(in.b), sc.s), 0.f) & 0xFFu);
+    }
+  }
+}
+
+// slot -> (block, offset).  Power-of-two block sizes (the common case) take a shift.
+__device__ __forceinline__ void split_slot(int64_t slot, int64_t block_size, int bs_shift, int64_t& blk,
+                                           int64_t& off) {
+  if (bs_shift >= 0) {
+    blk = slot >> bs_shift;
+    off = slot & (block_size - 1);
+  } else if (slot < 0x7FFFFFFFll && block_size < 0x7FFFFFFFll) {
+    const uint32_t s32 = static_cast<uint32_t>(slot), b32 = static_cast<uint32_t>(block_size);
+    blk = s32 / b32;
+    off = s32 - static_cast<uint32_t>(blk) * b32;
+  } else {
+    blk = slot / block_size;
+    off = slot - blk * block_size;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// flash layout
+// ---------------------------------------------------------------------------------------------
+struct FlashParams {
+  const void* key;
+  const void* value;
+  void* key_cache;
+  void* value_cache;
+  const int64_t* slot_mapping;
+  const float* k_scale;
+  const float* v_scale;
+  int64_t key_stride_t, key_stride_h, value_stride_t, value_stride_h;  // elements
+  int64_t block_stride, page_stride, head_stride;                      // elements
+  int64_t block_size;
+  int bs_shift;
+  uint32_t n_items;          // tokens_in_launch * rows_per_token * chunks_per_row
+  uint32_t items_per_token;  // rows_per_token * chunks_per_row
+  uint32_t chunks_per_row;
+  FastDiv div_items_per_token, div_chunks_per_row;
+};
+
+constexpr int kFlashThreads = 256;
+
+// One thread moves VEC consecutive elements of one (token, row) of K and the same VEC
+// elements of V: all loads are issued before the first store so four 16-byte requests
+// (bf16 -> fp8, VEC = 16) are in flight per thread.  A "row" is one head, or the whole
+// token when heads are contiguous on both sides (the host collapses that case).
+template <typename Tin, int KV, int VEC>
+__global__ void __launch_bounds__(kFlashThreads) flash_scatter_kernel(const FlashParams p) {
+  constexpr int IN_B = VEC * (int)sizeof(Tin);
+  constexpr int OUT_ES = (KV == KVC_KV_AUTO) ? (int)sizeof(Tin) : 1;
+  constexpr int OUT_B = VEC * OUT_ES;
+
+  const uint32_t item = blockIdx.x * kFlashThreads + threadIdx.x;
+  if (item >= p.n_items) return;
+  const uint32_t tok = p.div_items_per_token.div(item);
+  const uint32_t rem = item - tok * p.items_per_token;
+  const uint32_t row = p.div_chunks_per_row.div(rem);
+  const uint32_t chunk = rem - row * p.chunks_per_row;
+
+  const int64_t slot = __ldg(p.slot_mapping + tok);
+  if (slot < 0) return;
+
+  const int64_t d0 = static_cast<int64_t>(chunk) * VEC;
+  const Tin* ksrc = static_cast<const Tin*>(p.key) + tok * p.key_stride_t + row * p.key_stride_h + d0;
+  const Tin* vsrc = static_cast<const Tin*>(p.value) + tok * p.value_stride_t + row * p.value_stride_h + d0;
+  Chunk<IN_B> kin, vin;
+  load_chunk(kin, ksrc);
+  load_chunk(vin, vsrc);
+
+  int64_t blk, off;
+  split_slot(slot, p.block_size, p.bs_shift, blk, off);
+  const int64_t dst = blk * p.block_stride + off * p.page_stride + row * p.head_stride + d0;
+
+  ScaleCtx ks{}, vs{};
+  if constexpr (KV != KVC_KV_AUTO) {
+    ks = make_scale_ctx(p.k_scale);
+    vs = make_scale_ctx(p.v_scale);
+  }
+  Chunk<OUT_B> kout, vout;
+  convert_chunk<Tin, KV, VEC>(kin, kout, ks);
+  convert_chunk<Tin, KV, VEC>(vin, vout, vs);
+  store_chunk(static_cast<char*>(p.key_cache) + dst * OUT_ES, kout);
+  store_chunk(static_cast<char*>(p.value_cache) + dst * OUT_ES, vout);
+}
+
+// ---------------------------------------------------------------------------------------------
+// paged layout
+// ---------------------------------------------------------------------------------------------
+struct PagedParams {
+  const void* key;
+  const void* value;
+  void* key_cache;
+  void* value_cache;
+  const int64_t* slot_mapping;
+  const float* k_scale;
+  const float* v_scale;
+  int64_t key_stride_t, key_stride_h, value_stride_t, value_stride_h;  // elements
+  int64_t num_tokens;
+  int64_t block_size;
+  int bs_shift;
+  int32_t num_heads, head_size, x;
+  int32_t piece_bytes;  // K-store width: bytes of min(VEC, x)-element groups, <= 16
+  uint32_t n_warps;     // token_groups * num_heads * chunks_per_row
+  uint32_t chunks_per_row;
+  FastDiv div_chunks_per_row, div_heads;
+};
+
+constexpr int kPagedThreads = 256;
+
+// Lane = token.  A warp owns 32 consecutive tokens x one head x VEC consecutive d, so that
+// every store instruction walks the token axis: when consecutive tokens occupy consecutive
+// offsets of one block (a sequence being prefilled) the 32 lanes write one contiguous run
+// (32 x-chunks of K, 32 elements of one V row) and whole sectors leave the SM; with random
+// slots each lane's piece lands in its own sector, which the layout makes unavoidable.
+// The 8 warps of a CTA take adjacent d-chunks of the same rows, so the CTA reads whole rows.
+template <typename Tin, int KV, int VEC>
+__global__ void __launch_bounds__(kPagedThreads) paged_scatter_kernel(const PagedParams p) {
+  constexpr int ES = (int)sizeof(Tin);
+  constexpr int IN_B = VEC * ES;
+  constexpr int OUT_ES = (KV == KVC_KV_AUTO) ? ES : 1;
+  constexpr int OUT_B = VEC * OUT_ES;
+
+  const uint32_t warp = blockIdx.x * (kPagedThreads / 32) + (threadIdx.x >> 5);
+  if (warp >= p.n_warps) return;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t th = p.div_chunks_per_row.div(warp);  // token_group * H + head
+  const uint32_t chunk = warp - th * p.chunks_per_row;
+  const uint32_t tg = p.div_heads.div(th);
+  const uint32_t head = th - tg * static_cast<uint32_t>(p.num_heads);
+  const int64_t tok = static_cast<int64_t>(tg) * 32 + lane;
+  if (tok >= p.num_tokens) return;
+
+  const int64_t slot = __ldg(p.slot_mapping + tok);
+  if (slot < 0) return;
+
+  const int d0 = static_cast<int>(chunk) * VEC;
+  const Tin* ksrc = static_cast<const Tin*>(p.key) + tok * p.key_stride_t + head * p.key_stride_h + d0;
+  const Tin* vsrc = static_cast<const Tin*>(p.value) + tok * p.value_stride_t + head * p.value_stride_h + d0;
+  Chunk<IN_B> kin, vin;
+  load_chunk(kin, ksrc);
+  load_chunk(vin, vsrc);
+
+  int64_t blk, off;
+  split_slot(slot, p.block_size, p.bs_shift, blk, off);
+
+  ScaleCtx ks{}, vs{};
+  if constexpr (KV != KVC_KV_AUTO) {
+    ks = make_scale_ctx(p.k_scale);
+    vs = make_scale_ctx(p.v_scale);
+  }
+  Chunk<OUT_B> kout, vout;
+  convert_chunk<Tin, KV, VEC>(kin, kout, ks);
+  convert_chunk<Tin, KV, VEC>(vin, vout, vs);
+
+  const int64_t bh = blk * p.num_heads + head;
+  const int64_t bs = p.block_size;
+  const int x = p.x;
+
+  // K: element d lives at ((bh * (D/x) + d/x) * bs + off) * x + d%x.
+  char* kc = static_cast<char*>(p.key_cache);
+  const int64_t kbase = bh * (p.head_size / x);
+  auto k_store = [&](auto piece_tag) {
+    constexpr int PIECE = decltype(piece_tag)::value;  // bytes per store
+    constexpr int PE = PIECE / OUT_ES;                 // elements per store
+    if constexpr (PE >= 1 && PIECE <= OUT_B) {
+#pragma unroll
+      for (int j = 0; j < VEC; j += PE) {
+        const int d = d0 + j;
+        const int64_t idx = ((kbase + d / x) * bs + off) * x + d % x;
+        store_piece<PIECE>(kc + idx * OUT_ES, kout, j * OUT_ES);
+      }
+    }
+  };
+  switch (p.piece_bytes) {
+    case 16: k_store(std::integral_constant<int, 16>{}); break;
+    case 8: k_store(std::integral_constant<int, 8>{}); break;
+    case 4: k_store(std::integral_constant<int, 4>{}); break;
+    case 2: k_store(std::integral_constant<int, 2>{}); break;
+    default: k_store(std::integral_constant<int, 1>{}); break;
+  }
+
+  // V: element d lives at (bh * D + d) * bs + off.
+  char* vc = static_cast<char*>(p.value_cache);
+  const int64_t vbase = (bh * p.head_size + d0) * bs + off;
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) store_piece<OUT_ES>(vc + (vbase + j * bs) * OUT_ES, vout, j * OUT_ES);
+}
+
+// ---------------------------------------------------------------------------------------------
+// debug: count out-of-range slots
+// ---------------------------------------------------------------------------------------------
+__global__ void count_bad_slots_kernel(const int64_t* __restrict__ slots, int64_t n, int64_t num_slots,
+                                       unsigned long long* __restrict__ bad) {
+  unsigned long long local = 0;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    local += (slots[i] >= num_slots) ? 1ull : 0ull;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xFFFFFFFFu, local, o);
+  if ((threadIdx.x & 31) == 0 && local) atomicAdd(bad, local);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+static int in_elem_size(int in_dtype) { return in_dtype == KVC_IN_F32 ? 4 : 2; }
+
+static int pow2_shift(int64_t v) {
+  if (v <= 0 || (v & (v - 1))) return -1;
+  int s = 0;
+  while ((1ll << s) < v) ++s;
+  return s;
+}
+
+static bool aligned(const void* p, int64_t bytes) { return (reinterpret_cast<uintptr_t>(p) % bytes) == 0; }
+
+template <typename Tin, int KV>
+static cudaError_t launch_flash_vec(int vec, const FlashParams& p, dim3 grid, cudaStream_t st) {
+  switch (vec) {
+    case 16: flash_scatter_kernel<Tin, KV, 16><<<grid, kFlashThreads, 0, st>>>(p); break;
+    case 8: flash_scatter_kernel<Tin, KV, 8><<<grid, kFlashThreads, 0, st>>>(p); break;
+    case 4: flash_scatter_kernel<Tin, KV, 4><<<grid, kFlashThreads, 0, st>>>(p); break;
+    case 2: flash_scatter_kernel<Tin, KV, 2><<<grid, kFlashThreads, 0, st>>>(p); break;
+    default: flash_scatter_kernel<Tin, KV, 1><<<grid, kFlashThreads, 0, st>>>(p); break;
+  }
+  return cudaGetLastError();
+}
+
+template <typename Tin, int KV>
+static cudaError_t launch_paged_vec(int vec, const PagedParams& p, dim3 grid, cudaStream_t st) {
+  switch (vec) {
+    case 16: paged_scatter_kernel<Tin, KV, 16><<<grid, kPagedThreads, 0, st>>>(p); break;
+    case 8: paged_scatter_kernel<Tin, KV, 8><<<grid, kPagedThreads, 0, st>>>(p); break;
+    case 4: paged_scatter_kernel<Tin, KV, 4><<<grid, kPagedThreads, 0, st>>>(p); break;
+    case 2: paged_scatter_kernel<Tin, KV, 2><<<grid, kPagedThreads, 0, st>>>(p); break;
+    default: paged_scatter_kernel<Tin, KV, 1><<<grid, kPagedThreads, 0, st>>>(p); break;
+  }
+  return cudaGetLastError();
+}
+
+// (input dtype) x (cache mode) -> template instance; the build's counterpart of the
+// reference's DISPATCH_BY_KV_CACHE_DTYPE (csrc/quantization/fp8/quant_utils.h:136-173).
+#define KVC_DISPATCH(IN_DTYPE, KV_DTYPE, FN, ...)                                     \
+  [&]() -> cudaError_t {                                                              \
+    switch ((IN_DTYPE) * 3 + (KV_DTYPE)) {                                            \
+      case KVC_IN_F32 * 3 + KVC_KV_AUTO: return FN<float, KVC_KV_AUTO>(__VA_ARGS__);  \
+      case KVC_IN_F32 * 3 + KVC_KV_FP8_E4M3: return FN<float, KVC_KV_FP8_E4M3>(__VA_ARGS__); \
+      case KVC_IN_F32 * 3 + KVC_KV_FP8_E5M2: return FN<float, KVC_KV_FP8_E5M2>(__VA_ARGS__); \
+      case KVC_IN_F16 * 3 + KVC_KV_AUTO: return FN<__half, KVC_KV_AUTO>(__VA_ARGS__); \
+      case KVC_IN_F16 * 3 + KVC_KV_FP8_E4M3: return FN<__half, KVC_KV_FP8_E4M3>(__VA_ARGS__); \
+      case KVC_IN_F16 * 3 + KVC_KV_FP8_E5M2: return FN<__half, KVC_KV_FP8_E5M2>(__VA_ARGS__); \
+      case KVC_IN_BF16 * 3 + KVC_KV_AUTO: return FN<__nv_bfloat16, KVC_KV_AUTO>(__VA_ARGS__); \
+      case KVC_IN_BF16 * 3 + KVC_KV_FP8_E4M3: return FN<__nv_bfloat16, KVC_KV_FP8_E4M3>(__VA_ARGS__); \
+      default: return FN<__nv_bfloat16, KVC_KV_FP8_E5M2>(__VA_ARGS__);                \
+    }                                                                                 \
+  }()
+
+static int check_common(const void* key, const void* value, void* key_cache, void* value_cache,
+                        const int64_t* slot_mapping, int64_t num_tokens, int64_t num_heads,
+                        int64_t head_size, int64_t block_size, int in_dtype, int kv_dtype,
+                        const float* k_scale, const float* v_scale) {
+  if (in_dtype != KVC_IN_F32 && in_dtype != KVC_IN_F16 && in_dtype != KVC_IN_BF16)
+    return fail(KVC_ERR_UNSUPPORTED, "Unsupported input type of kv cache: code " + std::to_string(in_dtype));
+  if (kv_dtype != KVC_KV_AUTO && kv_dtype != KVC_KV_FP8_E4M3 && kv_dtype != KVC_KV_FP8_E5M2)
+    return fail(KVC_ERR_UNSUPPORTED, "Unsupported data type of kv cache: code " + std::to_string(kv_dtype));
+  if (num_tokens < 0 || num_heads < 0 || head_size < 0)
+    return fail(KVC_ERR_INVALID_ARG, "num_tokens, num_heads and head_size must be non-negative");
+  if (block_size <= 0) return fail(KVC_ERR_INVALID_ARG, "block_size must be positive");
+  if (num_tokens == 0 || num_heads == 0 || head_size == 0) return KVC_OK;
+  if (!key || !value || !key_cache || !value_cache || !slot_mapping)
+    return fail(KVC_ERR_INVALID_ARG, "key, value, key_cache, value_cache and slot_mapping must be non-NULL");
+  if (kv_dtype != KVC_KV_AUTO && (!k_scale || !v_scale))
+    return fail(KVC_ERR_INVALID_ARG, "k_scale and v_scale must be non-NULL for an fp8 cache");
+  if (!aligned(slot_mapping, 8)) return fail(KVC_ERR_INVALID_ARG, "slot_mapping must be 8-byte aligned");
+  const int es = in_elem_size(in_dtype);
+  if (!aligned(key, es) || !aligned(value, es))
+    return fail(KVC_ERR_INVALID_ARG, "key/value are not aligned to their element size");
+  if (kv_dtype == KVC_KV_AUTO && (!aligned(key_cache, es) || !aligned(value_cache, es)))
+    return fail(KVC_ERR_INVALID_ARG, "caches are not aligned to their element size");
+  if (num_heads > 0x7FFFFFFFll || head_size > 0x7FFFFFFFll)
+    return fail(KVC_ERR_INVALID_ARG, "num_heads / head_size out of range");
+  return KVC_OK;
+}
+
+// Largest power-of-two element count (<= cap) such that chunks of that many elements of
+// size `es` starting at `p` and displaced by any of `strides` stay aligned to
+// min(16, count*es) bytes, and that divides `len`.
+static int pick_vec(int cap, int64_t len, int es, const void* const* ptrs, int nptrs,
+                    const int64_t* strides, int nstrides) {
+  for (int v = cap; v > 1; v >>= 1) {
+    if (len % v) continue;
+    const int64_t a = (static_cast<int64_t>(v) * es >= 16) ? 16 : static_cast<int64_t>(v) * es;
+    bool ok = true;
+    for (int i = 0; i < nptrs && ok; ++i) ok = aligned(ptrs[i], a);
+    for (int i = 0; i < nstrides && ok; ++i) ok = ((strides[i] * es) % a) == 0;
+    if (ok) return v;
+  }
+  return 1;
+}
+
+static int flash_impl(const void* key, const void* value, void* key_cache, void* value_cache,
+                      const int64_t* slot_mapping, int64_t num_tokens, int64_t num_heads, int64_t head_size,
+                      int64_t block_size, int64_t key_stride_t, int64_t key_stride_h, int64_t value_stride_t,
+                      int64_t value_stride_h, int64_t block_stride, int64_t page_stride, int64_t head_stride,
+                      int in_dtype, int kv_dtype, const float* k_scale, const float* v_scale,
+                      cudaStream_t st) {
+  if (int rc = check_common(key, value, key_cache, value_cache, slot_mapping, num_tokens, num_heads,
+                            head_size, block_size, in_dtype, kv_dtype, k_scale, v_scale))
+    return rc;
+  if (num_tokens == 0 || num_heads == 0 || head_size == 0) return KVC_OK;
+
+  // Heads contiguous on both sides: one row per token.
+  int64_t rows = num_heads, row_len = head_size;
+  if (num_heads == 1 || (key_stride_h == head_size && value_stride_h == head_size && head_stride == head_size)) {
+    rows = 1;
+    row_len = num_heads * head_size;
+  }
+  const int es_in = in_elem_size(in_dtype);
+  const int es_out = (kv_dtype == KVC_KV_AUTO) ? es_in : 1;
+
+  // Vector width: bounded by source alignment and by destination alignment.
+  const void* in_ptrs[2] = {key, value};
+  const int64_t in_strides[4] = {key_stride_t, value_stride_t, rows > 1 ? key_stride_h : 0,
+                                 rows > 1 ? value_stride_h : 0};
+  const void* out_ptrs[2] = {key_cache, value_cache};
+  const int64_t out_strides[3] = {block_stride, page_stride, rows > 1 ? head_stride : 0};
+  int vec = pick_vec(16, row_len, es_in, in_ptrs, 2, in_strides, 4);
+  vec = pick_vec(vec, row_len, es_out, out_ptrs, 2, out_strides, 3);
+
+  const int64_t chunks_per_row = row_len / vec;
+  const int64_t items_per_token = rows * chunks_per_row;
+  if (items_per_token >= (1ll << 30)) return fail(KVC_ERR_INVALID_ARG, "num_heads * head_size too large");
+
+  FlashParams p{};
+  p.key_cache = key_cache;
+  p.value_cache = value_cache;
+  p.k_scale = k_scale;
+  p.v_scale = v_scale;
+  p.key_stride_t = key_stride_t;
+  p.key_stride_h = key_stride_h;
+  p.value_stride_t = value_stride_t;
+  p.value_stride_h = value_stride_h;
+  p.block_stride = block_stride;
+  p.page_stride = page_stride;
+  p.head_stride = head_stride;
+  p.block_size = block_size;
+  p.bs_shift = pow2_shift(block_size);
+  p.items_per_token = static_cast<uint32_t>(items_per_token);
+  p.chunks_per_row = static_cast<uint32_t>(chunks_per_row);
+  p.div_items_per_token = FastDiv(p.items_per_token);
+  p.div_chunks_per_row = FastDiv(p.chunks_per_row);
+
+  // Item indices are 31-bit: very large batches go out as several launches.
+  const int64_t max_tokens_per_launch = ((1ll << 31) - kFlashThreads) / items_per_token;
+  for (int64_t t0 = 0; t0 < num_tokens; t0 += max_tokens_per_launch) {
+    const int64_t nt = (num_tokens - t0 < max_tokens_per_launch) ? num_tokens - t0 : max_tokens_per_launch;
+    p.key = static_cast<const char*>(key) + t0 * key_stride_t * es_in;
+    p.value = static_cast<const char*>(value) + t0 * value_stride_t * es_in;
+    p.slot_mapping = slot_mapping + t0;
+    p.n_items = static_cast<uint32_t>(nt * items_per_token);
+    const dim3 grid(static_cast<unsigned>((p.n_items + kFlashThreads - 1) / kFlashThreads));
+    const cudaError_t e = KVC_DISPATCH(in_dtype, kv_dtype, launch_flash_vec, vec, p, grid, st);
+    if (e != cudaSuccess)
+      return fail(KVC_ERR_CUDA, std::string("reshape_and_cache_flash launch failed: ") + cudaGetErrorString(e));
+  }
+  return KVC_OK;
+}
+
+static int paged_impl(const void* key, const void* value, void* key_cache, void* value_cache,
+                      const int64_t* slot_mapping, int64_t num_tokens, int64_t num_heads, int64_t head_size,
+                      int64_t block_size, int64_t x, int64_t key_stride_t, int64_t key_stride_h,
+                      int64_t value_stride_t, int64_t value_stride_h, int in_dtype, int kv_dtype,
+                      const float* k_scale, const float* v_scale, cudaStream_t st) {
+  if (int rc = check_common(key, value, key_cache, value_cache, slot_mapping, num_tokens, num_heads,
+                            head_size, block_size, in_dtype, kv_dtype, k_scale, v_scale))
+    return rc;
+  if (x <= 0 || x > 0x7FFFFFFFll) return fail(KVC_ERR_INVALID_ARG, "x must be positive");
+  if (head_size % x) return fail(KVC_ERR_INVALID_ARG, "head_size must be a multiple of x (key_cache.size(4))");
+  if (num_tokens == 0 || num_heads == 0 || head_size == 0) return KVC_OK;
+
+  const int es_in = in_elem_size(in_dtype);
+  const int es_out = (kv_dtype == KVC_KV_AUTO) ? es_in : 1;
+  const void* in_ptrs[2] = {key, value};
+  const int64_t in_strides[4] = {key_stride_t, value_stride_t, key_stride_h, value_stride_h};
+  // a lane reads at most 32 bytes (one sector) of K and of V
+  const int vec = pick_vec(32 / es_in, head_size, es_in, in_ptrs, 2, in_strides, 4);
+
+  // K-store width: groups of min(vec, x) elements when x is a power of two and the cache
+  // base is aligned for it; single elements otherwise.
+  int64_t pe = 1;
+  while (pe * 2 <= vec && x % (pe * 2) == 0 && pe * 2 * es_out <= 16) pe *= 2;
+  while (pe > 1 && !aligned(key_cache, pe * es_out)) pe >>= 1;
+
+  const int64_t chunks_per_row = head_size / vec;
+  const int64_t token_groups = (num_tokens + 31) / 32;
+  const int64_t n_warps = token_groups * num_heads * chunks_per_row;
+  if (n_warps >= (1ll << 31)) return fail(KVC_ERR_INVALID_ARG, "num_tokens * num_heads * head_size too large for one call");
+
+  PagedParams p{};
+  p.key = key;
+  p.value = value;
+  p.key_cache = key_cache;
+  p.value_cache = value_cache;
+  p.slot_mapping = slot_mapping;
+  p.k_scale = k_scale;
+  p.v_scale = v_scale;
+  p.key_stride_t = key_stride_t;
+  p.key_stride_h = key_stride_h;
+  p.value_stride_t = value_stride_t;
+  p.value_stride_h = value_stride_h;
+  p.num_tokens = num_tokens;
+  p.block_size = block_size;
+  p.bs_shift = pow2_shift(block_size);
+  p.num_heads = static_cast<int32_t>(num_heads);
+  p.head_size = static_cast<int32_t>(head_size);
+  p.x = static_cast<int32_t>(x);
+  p.piece_bytes = static_cast<int32_t>(pe * es_out);
+  p.n_warps = static_cast<uint32_t>(n_warps);
+  p.chunks_per_row = static_cast<uint32_t>(chunks_per_row);
+  p.div_chunks_per_row = FastDiv(p.chunks_per_row);
+  p.div_heads = FastDiv(static_cast<uint32_t>(num_heads));
+  constexpr int wpb = kPagedThreads / 32;
+  const dim3 grid(static_cast<unsigned>((n_warps + wpb - 1) / wpb));
+  const cudaError_t e = KVC_DISPATCH(in_dtype, kv_dtype, launch_paged_vec, vec, p, grid, st);
+  if (e != cudaSuccess)
+    return fail(KVC_ERR_CUDA, std::string("reshape_and_cache launch failed: ") + cudaGetErrorString(e));
+  return KVC_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// device staging for host-resident inputs (one set per device, grown on demand)
+// ---------------------------------------------------------------------------------------------
+struct Staging {
+  void* buf = nullptr;
+  size_t cap = 0;
+};
+constexpr int kMaxDevices = 64;
+static Staging g_staging[kMaxDevices];
+static std::mutex g_staging_mu;
+
+static int staging_reserve(int dev, size_t bytes, void** out) {
+  std::lock_guard<std::mutex> lk(g_staging_mu);
+  Staging& s = g_staging[dev];
+  if (s.cap < bytes) {
+    if (s.buf) {
+      KVC_CUDA_TRY(cudaDeviceSynchronize());  // earlier calls may still read the old buffer
+      KVC_CUDA_TRY(cudaFree(s.buf));
+      s.buf = nullptr;
+      s.cap = 0;
+    }
+    KVC_CUDA_TRY(cudaMalloc(&s.buf, bytes));
+    s.cap = bytes;
+  }
+  *out = s.buf;
+  return KVC_OK;
+}
+
+static size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace kvc
+
+// ---------------------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------------------
+using namespace kvc;
+
+extern "C" {
+
+int kvc_version(void) { return 100; }
+
+const char* kvc_last_error(void) { return g_last_error.c_str(); }
+
+int kvc_parse_kv_cache_dtype(const char* s, int* out) {
+  if (!s || !out) return fail(KVC_ERR_INVALID_ARG, "kvc_parse_kv_cache_dtype: NULL argument");
+  if (!std::strcmp(s, "auto")) {
+    *out = KVC_KV_AUTO;
+  } else if (!std::strcmp(s, "fp8") || !std::strcmp(s, "fp8_e4m3")) {
+    *out = KVC_KV_FP8_E4M3;
+  } else if (!std::strcmp(s, "fp8_e5m2")) {
+    *out = KVC_KV_FP8_E5M2;
+  } else {
+    return fail(KVC_ERR_UNSUPPORTED, std::string("Unsupported data type of kv cache: ") + s);
+  }
+  return KVC_OK;
+}
+
+int kvc_reshape_and_cache_flash(const void* key, const void* value, void* key_cache, void* value_cache,
+                                const int64_t* slot_mapping, int64_t num_tokens, int64_t num_heads,
+                                int64_t head_size, int64_t block_size, int64_t key_stride_t,
+                                int64_t key_stride_h, int64_t value_stride_t, int64_t value_stride_h,
+                                int64_t block_stride, int64_t page_stride, int64_t head_stride, int in_dtype,
+                                int kv_dtype, const float* k_scale, const float* v_scale, void* stream) {
+  return flash_impl(key, value, key_cache, value_cache, slot_mapping, num_tokens, num_heads, head_size,
+                    block_size, key_stride_t, key_stride_h, value_stride_t, value_stride_h, block_stride,
+                    page_stride, head_stride, in_dtype, kv_dtype, k_scale, v_scale,
+                    static_cast<cudaStream_t>(stream));
+}
+
+int kvc_reshape_and_cache(const void* key, const void* value, void* key_cache, void* value_cache,
+                          const int64_t* slot_mapping, int64_t num_tokens, int64_t num_heads,
+                          int64_t head_size, int64_t block_size, int64_t x, int64_t key_stride_t,
+                          int64_t key_stride_h, int64_t value_stride_t, int64_t value_stride_h, int in_dtype,
+                          int kv_dtype, const float* k_scale, const float* v_scale, void* stream) {
+  return paged_impl(key, value, key_cache, value_cache, slot_mapping, num_tokens, num_heads, head_size,
+                    block_size, x, key_stride_t, key_stride_h, value_stride_t, value_stride_h, in_dtype,
+                    kv_dtype, k_scale, v_scale, static_cast<cudaStream_t>(stream));
+}
+
+int kvc_reshape_and_cache_flash_host(const void* host_key, const void* host_value, void* key_cache,
+                                     void* value_cache, const int64_t* host_slot_mapping, int64_t num_tokens,
+                                     int64_t num_heads, int64_t head_size, int64_t block_size,
+                                     int64_t key_stride_t, int64_t value_stride_t, int64_t block_stride,
+                                     int64_t page_stride, int64_t head_stride, int in_dtype, int kv_dtype,
+                                     const float* k_scale, const float* v_scale, void* stream) {
+  if (int rc = check_common(host_key, host_value, key_cache, value_cache, host_slot_mapping, num_tokens,
+                            num_heads, head_size, block_size, in_dtype, kv_dtype, k_scale, v_scale))
+    return rc;
+  if (num_tokens == 0 || num_heads == 0 || head_size == 0) return KVC_OK;
+  const int64_t row = num_heads * head_size;
+  if (key_stride_t < row || value_stride_t < row)
+    return fail(KVC_ERR_INVALID_ARG, "host key/value token stride is smaller than num_heads*head_size");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int dev = 0;
+  KVC_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(KVC_ERR_INVALID_ARG, "device ordinal out of range");
+  const size_t es = static_cast<size_t>(in_elem_size(in_dtype));
+  const size_t row_bytes = static_cast<size_t>(row) * es;
+  const size_t kv_bytes = round_up(static_cast<size_t>(num_tokens) * row_bytes, 256);
+  const size_t slot_bytes = round_up(static_cast<size_t>(num_tokens) * 8, 256);
+  void* base = nullptr;
+  if (int rc = staging_reserve(dev, 2 * kv_bytes + slot_bytes, &base)) return rc;
+  char* dkey = static_cast<char*>(base);
+  char* dval = dkey + kv_bytes;
+  int64_t* dslots = reinterpret_cast<int64_t*>(dval + kv_bytes);
+  // Rows are packed on the device whatever the host stride.
+  const void* hsrc[2] = {host_key, host_value};
+  char* ddst[2] = {dkey, dval};
+  const int64_t hstride[2] = {key_stride_t, value_stride_t};
+  for (int i = 0; i < 2; ++i) {
+    if (hstride[i] == row) {
+      KVC_CUDA_TRY(cudaMemcpyAsync(ddst[i], hsrc[i], static_cast<size_t>(num_tokens) * row_bytes,
+                                   cudaMemcpyHostToDevice, st));
+    } else {
+      KVC_CUDA_TRY(cudaMemcpy2DAsync(ddst[i], row_bytes, hsrc[i], static_cast<size_t>(hstride[i]) * es, row_bytes,
+                                     static_cast<size_t>(num_tokens), cudaMemcpyHostToDevice, st));
+    }
+  }
+  KVC_CUDA_TRY(cudaMemcpyAsync(dslots, host_slot_mapping, static_cast<size_t>(num_tokens) * 8,
+                               cudaMemcpyHostToDevice, st));
+  return flash_impl(dkey, dval, key_cache, value_cache, dslots, num_tokens, num_heads, head_size, block_size,
+                    row, head_size, row, head_size, block_stride, page_stride, head_stride, in_dtype, kv_dtype,
+                    k_scale, v_scale, st);
+}
+
+int kvc_release_staging(void) {
+  int dev = 0;
+  KVC_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(KVC_ERR_INVALID_ARG, "device ordinal out of range");
+  std::lock_guard<std::mutex> lk(g_staging_mu);
+  Staging& s = g_staging[dev];
+  if (s.buf) {
+    KVC_CUDA_TRY(cudaDeviceSynchronize());
+    KVC_CUDA_TRY(cudaFree(s.buf));
+    s.buf = nullptr;
+    s.cap = 0;
+  }
+  return KVC_OK;
+}
+
+int kvc_count_bad_slots(const int64_t* slot_mapping, int64_t num_tokens, int64_t num_slots, int64_t* bad_count,
+                        void* stream) {
+  if (!bad_count || num_tokens < 0 || (num_tokens > 0 && !slot_mapping))
+    return fail(KVC_ERR_INVALID_ARG, "kvc_count_bad_slots: bad argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  KVC_CUDA_TRY(cudaMemsetAsync(bad_count, 0, sizeof(int64_t), st));
+  if (num_tokens == 0) return KVC_OK;
+  int64_t blocks = (num_tokens + 255) / 256;
+  if (blocks > 1184) blocks = 1184;  // 8 CTAs per SM on 148 SMs; the loop strides over the rest
+  count_bad_slots_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+      slot_mapping, num_tokens, num_slots, reinterpret_cast<unsigned long long*>(bad_count));
+  KVC_CUDA_TRY(cudaGetLastError());
+  return KVC_OK;
+}
+
+}  // extern "C"

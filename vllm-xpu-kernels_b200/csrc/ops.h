@@ -1,0 +1,17 @@
+// C++ entry points registered with the PyTorch dispatcher.  Signatures are the ones the
+// reference declares in csrc/ops.h:41-59, so the schemas in torch_bindings.cpp bind
+// without adapters.
+#pragma once
+#include <ATen/core/Tensor.h>
+
+#include <string>
+
+// Paged layout: key_cache [num_blocks, H, D/x, block_size, x], value_cache [num_blocks, H, D, block_size].
+void reshape_and_cache(at::Tensor& key, at::Tensor& value, at::Tensor& key_cache, at::Tensor& value_cache,
+                       at::Tensor& slot_mapping, const std::string& kv_cache_dtype, at::Tensor& k_scale,
+                       at::Tensor& v_scale);
+
+// Flash (NHD) layout: caches [num_blocks, block_size, H, D], possibly strided views.
+void reshape_and_cache_flash(at::Tensor& key, at::Tensor& value, at::Tensor& key_cache,
+                             at::Tensor& value_cache, at::Tensor& slot_mapping,
+                             const std::string& kv_cache_dtype, at::Tensor& k_scale, at::Tensor& v_scale);

@@ -1,0 +1,37 @@
+// Registers the KV-cache write ops under torch.ops._C_cache_ops.
+//
+// Schema strings are the public interface vLLM's attention backends call and are kept
+// character-compatible with the reference's csrc/torch_bindings.cpp:107-112 and :116-122;
+// the implementations are bound for CUDA tensors.  Ops returning () need no meta kernel.
+// Only the cache-write ops of the reference's `_C` module are provided by this library.
+#include <torch/library.h>
+
+#include "core/registration.h"
+#include "ops.h"
+
+#ifndef TORCH_EXTENSION_NAME
+#define TORCH_EXTENSION_NAME _C
+#endif
+
+KVC_TORCH_LIBRARY(KVC_PP_CAT(TORCH_EXTENSION_NAME, _cache_ops), m) {
+  m.def(
+      "reshape_and_cache(Tensor key, Tensor value,"
+      "                  Tensor! key_cache, Tensor! value_cache,"
+      "                  Tensor slot_mapping,"
+      "                  str kv_cache_dtype,"
+      "                  Tensor k_scale, Tensor v_scale) -> ()");
+  m.def(
+      "reshape_and_cache_flash(Tensor key, Tensor value,"
+      "                        Tensor! key_cache,"
+      "                        Tensor! value_cache,"
+      "                        Tensor slot_mapping,"
+      "                        str kv_cache_dtype,"
+      "                        Tensor k_scale, Tensor v_scale) -> ()");
+}
+
+KVC_TORCH_LIBRARY_IMPL(KVC_PP_CAT(TORCH_EXTENSION_NAME, _cache_ops), CUDA, m) {
+  m.impl("reshape_and_cache", &reshape_and_cache);
+  m.impl("reshape_and_cache_flash", &reshape_and_cache_flash);
+}
+
+KVC_DEFINE_EMPTY_PYMODULE(TORCH_EXTENSION_NAME)

@@ -1,0 +1,150 @@
+"""ctypes binding of ``libkvcache_b200.so`` (the C ABI declared in include/kvcache_b200.h).
+
+The functions here take torch tensors only to read ``data_ptr()``, sizes and
+strides; everything crosses the boundary as plain pointers and integers, the
+way a binding in any other language would call it.  Argument meaning and error
+behaviour mirror the reference's operators (csrc/cache.cpp:409-489 there): a
+failing call raises ``RuntimeError`` with the library's message.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libkvcache_b200.so")
+
+IN_DTYPE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+# every symbol include/kvcache_b200.h declares
+SYMBOLS = (
+    "kvc_version",
+    "kvc_last_error",
+    "kvc_parse_kv_cache_dtype",
+    "kvc_reshape_and_cache_flash",
+    "kvc_reshape_and_cache",
+    "kvc_reshape_and_cache_flash_host",
+    "kvc_release_staging",
+    "kvc_count_bad_slots",
+)
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the library (once).  A missing build is an error, never a fallback."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is not built; run `python build.py` in the package root")
+        L = ctypes.CDLL(LIB_PATH)
+        i64, vp, ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
+        L.kvc_version.restype = ci
+        L.kvc_version.argtypes = []
+        L.kvc_last_error.restype = ctypes.c_char_p
+        L.kvc_last_error.argtypes = []
+        L.kvc_parse_kv_cache_dtype.restype = ci
+        L.kvc_parse_kv_cache_dtype.argtypes = [ctypes.c_char_p, ctypes.POINTER(ci)]
+        L.kvc_reshape_and_cache_flash.restype = ci
+        L.kvc_reshape_and_cache_flash.argtypes = [vp] * 5 + [i64] * 11 + [ci, ci, vp, vp, vp]
+        L.kvc_reshape_and_cache.restype = ci
+        L.kvc_reshape_and_cache.argtypes = [vp] * 5 + [i64] * 9 + [ci, ci, vp, vp, vp]
+        L.kvc_reshape_and_cache_flash_host.restype = ci
+        L.kvc_reshape_and_cache_flash_host.argtypes = [vp] * 5 + [i64] * 9 + [ci, ci, vp, vp, vp]
+        L.kvc_release_staging.restype = ci
+        L.kvc_release_staging.argtypes = []
+        L.kvc_count_bad_slots.restype = ci
+        L.kvc_count_bad_slots.argtypes = [vp, i64, i64, vp, vp]
+        _lib = L
+    return _lib
+
+
+def last_error() -> str:
+    return lib().kvc_last_error().decode()
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise RuntimeError(last_error())
+
+
+def parse_kv_cache_dtype(s: str) -> int:
+    out = ctypes.c_int(-1)
+    _check(lib().kvc_parse_kv_cache_dtype(s.encode(), ctypes.byref(out)))
+    return out.value
+
+
+def _in_dtype(t: torch.Tensor) -> int:
+    try:
+        return IN_DTYPE[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"Unsupported input type of kv cache: {t.dtype}") from None
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+
+def _scale_ptr(s, kv: int) -> int:
+    if kv == 0 or s is None:
+        return 0
+    return s.data_ptr()
+
+
+def reshape_and_cache_flash(key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype: str,
+                            k_scale=None, v_scale=None, stream=None) -> None:
+    """``kvc_reshape_and_cache_flash`` on device tensors (caches [num_blocks, block_size, H, D])."""
+    kv = parse_kv_cache_dtype(kv_cache_dtype)
+    _check(lib().kvc_reshape_and_cache_flash(
+        key.data_ptr(), value.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+        slot_mapping.data_ptr(), slot_mapping.shape[0], key.shape[1], key.shape[2], key_cache.shape[1],
+        key.stride(0), key.stride(1), value.stride(0), value.stride(1),
+        key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
+        _in_dtype(key), kv, _scale_ptr(k_scale, kv), _scale_ptr(v_scale, kv), _stream(stream)))
+
+
+def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype: str,
+                      k_scale=None, v_scale=None, stream=None) -> None:
+    """``kvc_reshape_and_cache`` on device tensors (K [nb,H,D/x,bs,x], V [nb,H,D,bs], contiguous)."""
+    kv = parse_kv_cache_dtype(kv_cache_dtype)
+    _check(lib().kvc_reshape_and_cache(
+        key.data_ptr(), value.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+        slot_mapping.data_ptr(), slot_mapping.shape[0], key.shape[1], key.shape[2],
+        key_cache.shape[3], key_cache.shape[4],
+        key.stride(0), key.stride(1), value.stride(0), value.stride(1),
+        _in_dtype(key), kv, _scale_ptr(k_scale, kv), _scale_ptr(v_scale, kv), _stream(stream)))
+
+
+def reshape_and_cache_flash_host(host_key, host_value, key_cache, value_cache, host_slot_mapping,
+                                 kv_cache_dtype: str, k_scale=None, v_scale=None, stream=None) -> None:
+    """``kvc_reshape_and_cache_flash_host``: key/value/slot_mapping are HOST tensors
+    ([T, H, D] with contiguous heads; pinned for asynchronous copies), caches and scales on the device."""
+    kv = parse_kv_cache_dtype(kv_cache_dtype)
+    for t in (host_key, host_value, host_slot_mapping):
+        if t.is_cuda:
+            raise RuntimeError("host entry point needs CPU tensors for key, value and slot_mapping")
+    H, D = host_key.shape[1], host_key.shape[2]
+    if H > 1 and (host_key.stride(1) != D or host_value.stride(1) != D):
+        raise RuntimeError("host key/value must have contiguous heads")
+    _check(lib().kvc_reshape_and_cache_flash_host(
+        host_key.data_ptr(), host_value.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+        host_slot_mapping.data_ptr(), host_slot_mapping.shape[0], H, D, key_cache.shape[1],
+        host_key.stride(0), host_value.stride(0),
+        key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
+        _in_dtype(host_key), kv, _scale_ptr(k_scale, kv), _scale_ptr(v_scale, kv), _stream(stream)))
+
+
+def release_staging() -> None:
+    _check(lib().kvc_release_staging())
+
+
+def count_bad_slots(slot_mapping, num_slots: int, stream=None) -> int:
+    """Number of slots >= num_slots (debug aid; synchronises to read the answer)."""
+    out = torch.zeros(1, dtype=torch.int64, device=slot_mapping.device)
+    _check(lib().kvc_count_bad_slots(slot_mapping.data_ptr(), slot_mapping.shape[0], num_slots,
+                                     out.data_ptr(), _stream(stream)))
+    return int(out.item())
