@@ -4,7 +4,7 @@
  *
  * Claim:  for a 16-bit float input x (bf16: 8 significant bits, fp16: 11) and
  * any fp32 scale s, with r = RN(1/s),
- *     q0 = RN(x * r);  e = RN(fma(-q0, s, x));  q = RN(fma(e, r, q0))
+ *     q0 = RN(x * r);  ne = RN(fma(q0, s, -x));  q = RN(fma(-ne, r, q0))
  * equals RN(x / s) bit for bit whenever nothing under- or overflows.
  * Scaling x or s by a power of two scales every intermediate by a power of
  * two, so it is enough to try every significand pair once:
@@ -43,8 +43,8 @@ int main(int argc, char** argv) {
     for (uint32_t xm = 0; xm < (1u << 10); ++xm) {
       const float x = u2f(0x3F800000u | (xm << 13));
       const float q0 = x * r;
-      const float e = fmaf(-q0, s, x);
-      const float q = fmaf(e, r, q0);
+      const float ne = fmaf(q0, s, -x); /* negated residual, as in the kernel */
+      const float q = fmaf(-ne, r, q0);
       const float ref = x / s;
       ++tried;
       if (f2u(q) != f2u(ref)) {
@@ -52,6 +52,25 @@ int main(int argc, char** argv) {
         if (bad < 5) fprintf(stderr, "x=%a s=%a fast=%a exact=%a\n", x, s, q, ref);
       }
     }
+  }
+  /* signed zeros: the quotient of a zero keeps the sign rule of IEEE division (s > 0) */
+  {
+    volatile float zs[2] = {0.0f, -0.0f}; /* volatile: evaluate at run time, not in the compiler */
+    volatile float ss[3] = {1.0f, 0.37f, 448.0f};
+    for (int i = 0; i < 2; ++i)
+      for (int j = 0; j < 3; ++j) {
+        const float x = zs[i], s = ss[j], r = 1.0f / s;
+        const float q0 = x * r;
+        /* volatile: gcc otherwise rewrites -fma(a,b,c) as fma(-a,b,-c), which is the
+         * same number except for the sign of an exact zero -- the very thing tested here */
+        volatile float ne = fmaf(q0, s, -x);
+        const float q = fmaf(-ne, r, q0);
+        ++tried;
+        if (f2u(q) != f2u(x / s)) {
+          ++bad;
+          fprintf(stderr, "zero case x=%a s=%a fast=%a exact=%a\n", x, s, q, x / s);
+        }
+      }
   }
   printf("tried %llu mismatches %llu\n", tried, bad);
   return bad != 0;

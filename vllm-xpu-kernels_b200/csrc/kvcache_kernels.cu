@@ -153,14 +153,17 @@ __device__ __forceinline__ uint32_t cvt_fp8x2(float lo, float hi) {
   return r;
 }
 
-// RN(x / s) in three instructions, given r = RN(1/s): one Newton correction of the
+// RN(x / s) in three instructions, given s > 0 and r = RN(1/s): one Newton correction of the
 // product x*r with an exact residual.  For 16-bit float x this equals the IEEE quotient
 // for every significand pair (checked exhaustively on the CPU) as long as nothing under-
 // or overflows; the callers below bound s and repair the overflow case.
+// The residual is formed negated (ne = q0*s - x) and subtracted: when it is exactly zero
+// it is +0, (-ne)*r is -0, and adding -0 leaves q0 unchanged even when q0 is itself -0.
+// (With e = x - q0*s the sum (+0) + (-0) would turn a -0 quotient into +0.)
 __device__ __forceinline__ float quot_fast(float x, float s, float r) {
   const float q0 = __fmul_rn(x, r);
-  const float e = __fmaf_rn(-q0, s, x);
-  return __fmaf_rn(e, r, q0);
+  const float ne = __fmaf_rn(q0, s, -x);
+  return __fmaf_rn(-ne, r, q0);
 }
 
 // True when one of the four bytes is a NaN code (low seven bits all set).
@@ -178,11 +181,11 @@ __device__ __forceinline__ ScaleCtx make_scale_ctx(const float* scale_ptr) {
   ScaleCtx c;
   c.s = __ldg(scale_ptr);
   c.r = __frcp_rn(c.s);
-  const float a = fabsf(c.s);
-  // 2^-60 <= |s| <= 2^60: r is normal, and for any 16-bit float x whose quotient can
+  // 2^-60 <= s <= 2^60: r is normal, and for any 16-bit float x whose quotient can
   // round to a non-zero fp8 value the residual fma is exact (no underflow).  Larger
   // quotients that overflow x*r surface as a NaN byte and are redone exactly.
-  c.fast = (a >= 8.673617379884035e-19f) && (a <= 1.152921504606847e18f);
+  // Negative scales (legal, never seen in practice) take the IEEE divide.
+  c.fast = (c.s >= 8.673617379884035e-19f) && (c.s <= 1.152921504606847e18f);
   return c;
 }
 
