@@ -1,0 +1,98 @@
+#!/usr/bin/env python
+"""A small, self-ending run of one KV-cache write kernel, meant to be wrapped by a profiler.
+
+    python profile_case.py --layout flash --kv fp8 --tokens 32768 --launches 6
+
+Holds well under a few GB on the device (inputs of two rotating batches plus a cache just
+large enough for them), yet each batch is larger than the 126 MB L2 so DRAM counters mean
+something.  Prints the mean launch time measured with CUDA events, which is only meaningful
+when the script is NOT running under a profiler.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))
+
+import torch  # noqa: E402
+
+from vllm_xpu_kernels import cabi  # noqa: E402
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layout", choices=["flash", "paged"], default="flash")
+    ap.add_argument("--kv", choices=["auto", "fp8", "fp8_e5m2"], default="fp8")
+    ap.add_argument("--dtype", choices=["bfloat16", "half", "float"], default="bfloat16")
+    ap.add_argument("--tokens", type=int, default=32768)
+    ap.add_argument("--heads", type=int, default=8)
+    ap.add_argument("--head-size", type=int, default=128)
+    ap.add_argument("--block-size", type=int, default=64)
+    ap.add_argument("--slots", choices=["runs", "random"], default="runs",
+                    help="runs: whole blocks in random order (a prefill); random: distinct random slots")
+    ap.add_argument("--skip-frac", type=float, default=0.0, help="fraction of slots set to -1")
+    ap.add_argument("--strided", action="store_true", help="key/value are slices of a fused qkv tensor")
+    ap.add_argument("--launches", type=int, default=6)
+    ap.add_argument("--nbuf", type=int, default=2)
+    ns = ap.parse_args()
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    torch.manual_seed(0)
+    dt = {"bfloat16": torch.bfloat16, "half": torch.float16, "float": torch.float32}[ns.dtype]
+    T, H, D, bs = ns.tokens, ns.heads, ns.head_size, ns.block_size
+    nb = 2 * ((T + bs - 1) // bs)
+    es_out = 1 if ns.kv != "auto" else torch.empty((), dtype=dt).element_size()
+    cdt = dt if ns.kv == "auto" else torch.uint8
+    if ns.layout == "flash":
+        kc = torch.zeros(nb, bs, H, D, dtype=cdt, device=dev)
+        vc = torch.zeros(nb, bs, H, D, dtype=cdt, device=dev)
+    else:
+        x = 16 // es_out
+        kc = torch.zeros(nb, H, D // x, bs, x, dtype=cdt, device=dev)
+        vc = torch.zeros(nb, H, D, bs, dtype=cdt, device=dev)
+    sets = []
+    for b in range(ns.nbuf):
+        if ns.strided:
+            qkv = torch.randn(T, 3 * H * D, device=dev).to(dt)
+            key = qkv[:, H * D:2 * H * D].view(T, H, D)
+            value = qkv[:, 2 * H * D:].view(T, H, D)
+        else:
+            key = torch.randn(T, H, D, device=dev).to(dt)
+            value = torch.randn(T, H, D, device=dev).to(dt)
+        if ns.slots == "runs":
+            perm = torch.randperm(nb, device=dev)[:(T + bs - 1) // bs]
+            slots = (perm[:, None] * bs + torch.arange(bs, device=dev)[None, :]).flatten()[:T].contiguous()
+        else:
+            slots = torch.randperm(nb * bs, device=dev)[:T]
+        if ns.skip_frac > 0:
+            slots[torch.rand(T, device=dev) < ns.skip_frac] = -1
+        sets.append((key, value, slots))
+    ks = torch.tensor(0.02, device=dev)
+    vs = torch.tensor(0.02, device=dev)
+    fn = cabi.reshape_and_cache_flash if ns.layout == "flash" else cabi.reshape_and_cache
+    active = int((sets[0][2] >= 0).sum())
+    es_in = torch.empty((), dtype=dt).element_size()
+    alg_bytes = 8 * T + active * H * D * 2 * (es_in + es_out)
+
+    evs = []
+    for i in range(ns.launches):
+        key, value, slots = sets[i % ns.nbuf]
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn(key, value, kc, vc, slots, ns.kv, ks, vs)
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    times = [a.elapsed_time(b) * 1e3 for a, b in evs]
+    best = min(times[1:]) if len(times) > 1 else times[0]
+    print(f"layout={ns.layout} kv={ns.kv} dtype={ns.dtype} T={T} H={H} D={D} bs={bs} slots={ns.slots} "
+          f"algorithmic_bytes={alg_bytes} launches={ns.launches} event_us={['%.1f' % t for t in times]} "
+          f"best_GBps={alg_bytes / best / 1e3:.0f}")
+
+
+if __name__ == "__main__":
+    main()
