@@ -27,6 +27,9 @@ def scale_set(n_random: int, seed: int) -> np.ndarray:
         1.0, 2.0, 0.5, 3.0, 1 / 3, 448.0, 1 / 448, 0.0078125, 2.0**-60, 2.0**60, np.nextafter(np.float32(2.0**-60), 0),
         np.nextafter(np.float32(2.0**60), np.float32(np.inf)), 2.0**-61, 2.0**61, 1e-30, 1e30, 1e-38, 1e-40, 1e-45,
         3.4028235e38, -1.0, -0.37, 0.0, -0.0, np.inf, -np.inf, np.nan, 2.0**-126, 2.0**-100, 2.0**100, 2.0**127,
+        # edges of the fp16 fast window [2^-20, 64] and scales where 512*s leaves the fp16 range
+        2.0**-20, np.nextafter(np.float32(2.0**-20), np.float32(0)), 64.0, np.nextafter(np.float32(64.0), np.float32(100)),
+        100.0, 127.9, 128.0, 1000.0, 2.0**-21, 2.0**-23, 2.0**-24, 0.25, np.nextafter(np.float32(0.25), np.float32(1)), 0.49, 1.07,
     ], dtype=np.float32)
     return np.concatenate([special, near_one, rnd])
 

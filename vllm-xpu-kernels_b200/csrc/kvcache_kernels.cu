@@ -62,6 +62,19 @@ struct FastDiv {
 };
 
 // ---------------------------------------------------------------------------------------------
+// programmatic dependent launch.  Every kernel here is launched with the
+// programmatic-stream-serialization attribute and starts with pdl_prologue(): it may be
+// scheduled while the previous kernel of the stream drains, then waits until that kernel
+// has completed and its writes are visible before it touches memory, and at once allows its
+// own successor to be scheduled the same way.  Without a programmatic predecessor the wait
+// returns immediately.  Launch latency and CTA scheduling thus overlap the predecessor's tail.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
 // vector global memory access.  Loads are read-once streams: bypass L1 allocation.
 // ---------------------------------------------------------------------------------------------
 template <int BYTES>
@@ -69,11 +82,29 @@ struct alignas(BYTES >= 16 ? 16 : BYTES) Chunk {
   unsigned char b[BYTES];
 };
 
+// `wide`: the address is 32-byte aligned, so 32-byte pieces go out as single 256-bit loads
+// (one full sector per lane per instruction; two 16-byte loads 32 bytes apart would make
+// both instructions of a warp touch every sector).
 template <int BYTES>
-__device__ __forceinline__ void load_chunk(Chunk<BYTES>& c, const void* gptr) {
+__device__ __forceinline__ void load_chunk(Chunk<BYTES>& c, const void* gptr, bool wide) {
   if constexpr (BYTES >= 16) {
     static_assert(BYTES % 16 == 0, "wide chunks are whole 16-byte vectors");
     uint4* dst = reinterpret_cast<uint4*>(c.b);
+    if constexpr (BYTES % 32 == 0) {
+      if (wide) {
+#pragma unroll
+        for (int i = 0; i < BYTES / 32; ++i) {
+          uint4 lo, hi;
+          asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                       : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z),
+                         "=r"(hi.w)
+                       : "l"(static_cast<const char*>(gptr) + 32 * i));
+          dst[2 * i] = lo;
+          dst[2 * i + 1] = hi;
+        }
+        return;
+      }
+    }
 #pragma unroll
     for (int i = 0; i < BYTES / 16; ++i) {
       uint4 v;
@@ -141,6 +172,31 @@ __device__ __forceinline__ float to_f32<__nv_bfloat16>(const unsigned char* p) {
   return __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(p)) << 16);
 }
 
+// The two 16-bit floats packed in `w` as fp32 (lo = bits 0..15).
+template <typename Tin>
+__device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi) {
+  if constexpr (std::is_same_v<Tin, __nv_bfloat16>) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xFFFF0000u);
+  } else {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    lo = f.x;
+    hi = f.y;
+  }
+}
+
+// sign(x) * min(|x|, c) on both 16-bit halves in one instruction; NaN stays NaN.
+template <typename Tin>
+__device__ __forceinline__ uint32_t clamp_magnitude2(uint32_t w, uint32_t c2) {
+  uint32_t d;
+  if constexpr (std::is_same_v<Tin, __nv_bfloat16>) {
+    asm("min.NaN.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(w), "r"(c2));
+  } else {
+    asm("min.NaN.xorsign.abs.f16x2 %0, %1, %2;" : "=r"(d) : "r"(w), "r"(c2));
+  }
+  return d;
+}
+
 // Two floats -> two fp8 bytes (lo in bits 0..7), round-to-nearest-even, saturating.
 template <int KV>
 __device__ __forceinline__ uint32_t cvt_fp8x2(float lo, float hi) {
@@ -156,7 +212,7 @@ __device__ __forceinline__ uint32_t cvt_fp8x2(float lo, float hi) {
 // RN(x / s) in three instructions, given s > 0 and r = RN(1/s): one Newton correction of the
 // product x*r with an exact residual.  For 16-bit float x this equals the IEEE quotient
 // for every significand pair (checked exhaustively on the CPU) as long as nothing under-
-// or overflows; the callers below bound s and repair the overflow case.
+// or overflows; make_scale_ctx() bounds s, and the caller clamps |x| so x*r stays finite.
 // The residual is formed negated (ne = q0*s - x) and subtracted: when it is exactly zero
 // it is +0, (-ne)*r is -0, and adding -0 leaves q0 unchanged even when q0 is itself -0.
 // (With e = x - q0*s the sum (+0) + (-0) would turn a -0 quotient into +0.)
@@ -166,26 +222,41 @@ __device__ __forceinline__ float quot_fast(float x, float s, float r) {
   return __fmaf_rn(-ne, r, q0);
 }
 
-// True when one of the four bytes is a NaN code (low seven bits all set).
-__device__ __forceinline__ bool has_nan_byte(uint32_t w) {
-  return (((w & 0x7F7F7F7Fu) + 0x01010101u) & 0x80808080u) != 0u;
-}
-
 struct ScaleCtx {
-  float s;    // the scale
-  float r;    // RN(1/s)
-  bool fast;  // s is inside the window where quot_fast is exact
+  float s;         // the scale
+  float r;         // RN(1/s)
+  uint32_t clamp2; // two copies of the 16-bit clamp bound c (see below)
+  bool fast;       // s is inside the window where quot_fast is exact
 };
 
+// Fast-path window of the scale, per input type (fp8_e4m3 / fp8_e5m2 store):
+//   bf16  2^-60 <= s <= 2^60            r is normal; for every x whose quotient can round to a
+//                                       non-zero fp8 value the residual fma is exact (no underflow)
+//   fp16  2^-20 <= s <= 64 / 0.25       same, and the clamp bound is a normal, finite fp16
+// Inside it |x| is first clamped to c = trunc16(m*s), m = 512 for e4m3 (largest finite 448,
+// everything above 464 saturates) and 131072 for e5m2 (57344, 61440): a clamped element has
+// |x/s| >= c/s > 0.99*m before and exactly c/s after, both beyond the saturation point, and
+// |x*r| <= 1.01*m can no longer overflow (inf inputs included).  NaN stays NaN.
+// Outside the window (and for negative scales, legal but never seen) the IEEE divide is used.
+template <typename Tin, int KV>
 __device__ __forceinline__ ScaleCtx make_scale_ctx(const float* scale_ptr) {
   ScaleCtx c;
   c.s = __ldg(scale_ptr);
   c.r = __frcp_rn(c.s);
-  // 2^-60 <= s <= 2^60: r is normal, and for any 16-bit float x whose quotient can
-  // round to a non-zero fp8 value the residual fma is exact (no underflow).  Larger
-  // quotients that overflow x*r surface as a NaN byte and are redone exactly.
-  // Negative scales (legal, never seen in practice) take the IEEE divide.
-  c.fast = (c.s >= 8.673617379884035e-19f) && (c.s <= 1.152921504606847e18f);
+  constexpr float kM = (KV == KVC_KV_FP8_E5M2) ? 131072.0f : 512.0f;
+  if constexpr (std::is_same_v<Tin, __nv_bfloat16>) {
+    c.fast = (c.s >= 8.673617379884035e-19f) && (c.s <= 1.152921504606847e18f);
+    const uint32_t h = __float_as_uint(c.s * kM) >> 16;
+    c.clamp2 = h | (h << 16);
+  } else if constexpr (std::is_same_v<Tin, __half>) {
+    constexpr float kHi = (KV == KVC_KV_FP8_E5M2) ? 0.25f : 64.0f;
+    c.fast = (c.s >= 9.5367431640625e-07f) && (c.s <= kHi);
+    const uint32_t h = __half_as_ushort(__float2half_rz(c.s * kM));
+    c.clamp2 = h | (h << 16);
+  } else {
+    c.fast = false;
+    c.clamp2 = 0;
+  }
   return c;
 }
 
@@ -202,17 +273,14 @@ __device__ __forceinline__ void convert_chunk(const Chunk<VEC * (int)sizeof(Tin)
       if (sc.fast) {
 #pragma unroll
         for (int i = 0; i < VEC; i += 4) {
-          const float x0 = to_f32<Tin>(in.b + ES * (i + 0));
-          const float x1 = to_f32<Tin>(in.b + ES * (i + 1));
-          const float x2 = to_f32<Tin>(in.b + ES * (i + 2));
-          const float x3 = to_f32<Tin>(in.b + ES * (i + 3));
-          uint32_t w = cvt_fp8x2<KV>(quot_fast(x0, sc.s, sc.r), quot_fast(x1, sc.s, sc.r)) |
-                       (cvt_fp8x2<KV>(quot_fast(x2, sc.s, sc.r), quot_fast(x3, sc.s, sc.r)) << 16);
-          if (has_nan_byte(w)) {  // NaN input, or x*r overflowed: redo with the IEEE divide
-            w = cvt_fp8x2<KV>(__fdiv_rn(x0, sc.s), __fdiv_rn(x1, sc.s)) |
-                (cvt_fp8x2<KV>(__fdiv_rn(x2, sc.s), __fdiv_rn(x3, sc.s)) << 16);
-          }
-          *reinterpret_cast<uint32_t*>(out.b + i) = w;
+          const uint32_t a = clamp_magnitude2<Tin>(*reinterpret_cast<const uint32_t*>(in.b + ES * i), sc.clamp2);
+          const uint32_t b = clamp_magnitude2<Tin>(*reinterpret_cast<const uint32_t*>(in.b + ES * (i + 2)), sc.clamp2);
+          float x0, x1, x2, x3;
+          unpack2<Tin>(a, x0, x1);
+          unpack2<Tin>(b, x2, x3);
+          *reinterpret_cast<uint32_t*>(out.b + i) =
+              cvt_fp8x2<KV>(quot_fast(x0, sc.s, sc.r), quot_fast(x1, sc.s, sc.r)) |
+              (cvt_fp8x2<KV>(quot_fast(x2, sc.s, sc.r), quot_fast(x3, sc.s, sc.r)) << 16);
         }
         return;
       }
@@ -262,6 +330,8 @@ struct FlashParams {
   int64_t block_stride, page_stride, head_stride;                      // elements
   int64_t block_size;
   int bs_shift;
+  bool linear_slots;         // block_stride == block_size * page_stride: address = slot * page_stride
+  bool wide_loads;           // every chunk address is 32-byte aligned
   uint32_t n_items;          // tokens_in_launch * rows_per_token * chunks_per_row
   uint32_t items_per_token;  // rows_per_token * chunks_per_row
   uint32_t chunks_per_row;
@@ -271,10 +341,11 @@ struct FlashParams {
 constexpr int kFlashThreads = 256;
 
 // One thread moves VEC consecutive elements of one (token, row) of K and the same VEC
-// elements of V: all loads are issued before the first store so four 16-byte requests
-// (bf16 -> fp8, VEC = 16) are in flight per thread.  A "row" is one head, or the whole
-// token when heads are contiguous on both sides (the host collapses that case).
-template <typename Tin, int KV, int VEC>
+// elements of V: both loads are issued before the first store (64 bytes in flight per
+// thread for bf16 -> fp8, VEC = 16; 32 registers, so 2048 threads per SM).  A "row" is one
+// head, or the whole token when heads are contiguous on both sides (ONE_ROW; the host
+// collapses that case).
+template <typename Tin, int KV, int VEC, bool ONE_ROW>
 __global__ void __launch_bounds__(kFlashThreads) flash_scatter_kernel(const FlashParams p) {
   constexpr int IN_B = VEC * (int)sizeof(Tin);
   constexpr int OUT_ES = (KV == KVC_KV_AUTO) ? (int)sizeof(Tin) : 1;
@@ -284,27 +355,41 @@ __global__ void __launch_bounds__(kFlashThreads) flash_scatter_kernel(const Flas
   if (item >= p.n_items) return;
   const uint32_t tok = p.div_items_per_token.div(item);
   const uint32_t rem = item - tok * p.items_per_token;
-  const uint32_t row = p.div_chunks_per_row.div(rem);
-  const uint32_t chunk = rem - row * p.chunks_per_row;
+  uint32_t row = 0, chunk = rem;
+  if constexpr (!ONE_ROW) {
+    row = p.div_chunks_per_row.div(rem);
+    chunk = rem - row * p.chunks_per_row;
+  }
+  pdl_prologue();
 
   const int64_t slot = __ldg(p.slot_mapping + tok);
   if (slot < 0) return;
 
   const int64_t d0 = static_cast<int64_t>(chunk) * VEC;
-  const Tin* ksrc = static_cast<const Tin*>(p.key) + tok * p.key_stride_t + row * p.key_stride_h + d0;
-  const Tin* vsrc = static_cast<const Tin*>(p.value) + tok * p.value_stride_t + row * p.value_stride_h + d0;
+  const Tin* ksrc = static_cast<const Tin*>(p.key) + tok * p.key_stride_t + d0;
+  const Tin* vsrc = static_cast<const Tin*>(p.value) + tok * p.value_stride_t + d0;
+  if constexpr (!ONE_ROW) {
+    ksrc += row * p.key_stride_h;
+    vsrc += row * p.value_stride_h;
+  }
   Chunk<IN_B> kin, vin;
-  load_chunk(kin, ksrc);
-  load_chunk(vin, vsrc);
+  load_chunk(kin, ksrc, p.wide_loads);
+  load_chunk(vin, vsrc, p.wide_loads);
 
-  int64_t blk, off;
-  split_slot(slot, p.block_size, p.bs_shift, blk, off);
-  const int64_t dst = blk * p.block_stride + off * p.page_stride + row * p.head_stride + d0;
+  int64_t dst;
+  if (p.linear_slots) {
+    dst = slot * p.page_stride + d0;
+  } else {
+    int64_t blk, off;
+    split_slot(slot, p.block_size, p.bs_shift, blk, off);
+    dst = blk * p.block_stride + off * p.page_stride + d0;
+  }
+  if constexpr (!ONE_ROW) dst += row * p.head_stride;
 
   ScaleCtx ks{}, vs{};
   if constexpr (KV != KVC_KV_AUTO) {
-    ks = make_scale_ctx(p.k_scale);
-    vs = make_scale_ctx(p.v_scale);
+    ks = make_scale_ctx<Tin, KV>(p.k_scale);
+    vs = make_scale_ctx<Tin, KV>(p.v_scale);
   }
   Chunk<OUT_B> kout, vout;
   convert_chunk<Tin, KV, VEC>(kin, kout, ks);
@@ -328,6 +413,7 @@ struct PagedParams {
   int64_t num_tokens;
   int64_t block_size;
   int bs_shift;
+  bool wide_loads;
   int32_t num_heads, head_size, x;
   int32_t piece_bytes;  // K-store width: bytes of min(VEC, x)-element groups, <= 16
   uint32_t n_warps;     // token_groups * num_heads * chunks_per_row
@@ -359,6 +445,7 @@ __global__ void __launch_bounds__(kPagedThreads) paged_scatter_kernel(const Page
   const uint32_t head = th - tg * static_cast<uint32_t>(p.num_heads);
   const int64_t tok = static_cast<int64_t>(tg) * 32 + lane;
   if (tok >= p.num_tokens) return;
+  pdl_prologue();
 
   const int64_t slot = __ldg(p.slot_mapping + tok);
   if (slot < 0) return;
@@ -367,16 +454,16 @@ __global__ void __launch_bounds__(kPagedThreads) paged_scatter_kernel(const Page
   const Tin* ksrc = static_cast<const Tin*>(p.key) + tok * p.key_stride_t + head * p.key_stride_h + d0;
   const Tin* vsrc = static_cast<const Tin*>(p.value) + tok * p.value_stride_t + head * p.value_stride_h + d0;
   Chunk<IN_B> kin, vin;
-  load_chunk(kin, ksrc);
-  load_chunk(vin, vsrc);
+  load_chunk(kin, ksrc, p.wide_loads);
+  load_chunk(vin, vsrc, p.wide_loads);
 
   int64_t blk, off;
   split_slot(slot, p.block_size, p.bs_shift, blk, off);
 
   ScaleCtx ks{}, vs{};
   if constexpr (KV != KVC_KV_AUTO) {
-    ks = make_scale_ctx(p.k_scale);
-    vs = make_scale_ctx(p.v_scale);
+    ks = make_scale_ctx<Tin, KV>(p.k_scale);
+    vs = make_scale_ctx<Tin, KV>(p.v_scale);
   }
   Chunk<OUT_B> kout, vout;
   convert_chunk<Tin, KV, VEC>(kin, kout, ks);
@@ -444,28 +531,49 @@ static int pow2_shift(int64_t v) {
 
 static bool aligned(const void* p, int64_t bytes) { return (reinterpret_cast<uintptr_t>(p) % bytes) == 0; }
 
-template <typename Tin, int KV>
-static cudaError_t launch_flash_vec(int vec, const FlashParams& p, dim3 grid, cudaStream_t st) {
+// All kernels go out with the programmatic-stream-serialization attribute (see pdl_prologue).
+template <typename Params>
+static cudaError_t launch_pdl(void (*kernel)(const Params), dim3 grid, int threads, const Params& p,
+                              cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(static_cast<unsigned>(threads));
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
+template <typename Tin, int KV, bool ONE_ROW>
+static cudaError_t launch_flash_vec2(int vec, const FlashParams& p, dim3 grid, cudaStream_t st) {
   switch (vec) {
-    case 16: flash_scatter_kernel<Tin, KV, 16><<<grid, kFlashThreads, 0, st>>>(p); break;
-    case 8: flash_scatter_kernel<Tin, KV, 8><<<grid, kFlashThreads, 0, st>>>(p); break;
-    case 4: flash_scatter_kernel<Tin, KV, 4><<<grid, kFlashThreads, 0, st>>>(p); break;
-    case 2: flash_scatter_kernel<Tin, KV, 2><<<grid, kFlashThreads, 0, st>>>(p); break;
-    default: flash_scatter_kernel<Tin, KV, 1><<<grid, kFlashThreads, 0, st>>>(p); break;
+    case 16: return launch_pdl(flash_scatter_kernel<Tin, KV, 16, ONE_ROW>, grid, kFlashThreads, p, st);
+    case 8: return launch_pdl(flash_scatter_kernel<Tin, KV, 8, ONE_ROW>, grid, kFlashThreads, p, st);
+    case 4: return launch_pdl(flash_scatter_kernel<Tin, KV, 4, ONE_ROW>, grid, kFlashThreads, p, st);
+    case 2: return launch_pdl(flash_scatter_kernel<Tin, KV, 2, ONE_ROW>, grid, kFlashThreads, p, st);
+    default: return launch_pdl(flash_scatter_kernel<Tin, KV, 1, ONE_ROW>, grid, kFlashThreads, p, st);
   }
-  return cudaGetLastError();
+}
+
+template <typename Tin, int KV>
+static cudaError_t launch_flash_vec(int vec, bool one_row, const FlashParams& p, dim3 grid, cudaStream_t st) {
+  return one_row ? launch_flash_vec2<Tin, KV, true>(vec, p, grid, st)
+                 : launch_flash_vec2<Tin, KV, false>(vec, p, grid, st);
 }
 
 template <typename Tin, int KV>
 static cudaError_t launch_paged_vec(int vec, const PagedParams& p, dim3 grid, cudaStream_t st) {
   switch (vec) {
-    case 16: paged_scatter_kernel<Tin, KV, 16><<<grid, kPagedThreads, 0, st>>>(p); break;
-    case 8: paged_scatter_kernel<Tin, KV, 8><<<grid, kPagedThreads, 0, st>>>(p); break;
-    case 4: paged_scatter_kernel<Tin, KV, 4><<<grid, kPagedThreads, 0, st>>>(p); break;
-    case 2: paged_scatter_kernel<Tin, KV, 2><<<grid, kPagedThreads, 0, st>>>(p); break;
-    default: paged_scatter_kernel<Tin, KV, 1><<<grid, kPagedThreads, 0, st>>>(p); break;
+    case 16: return launch_pdl(paged_scatter_kernel<Tin, KV, 16>, grid, kPagedThreads, p, st);
+    case 8: return launch_pdl(paged_scatter_kernel<Tin, KV, 8>, grid, kPagedThreads, p, st);
+    case 4: return launch_pdl(paged_scatter_kernel<Tin, KV, 4>, grid, kPagedThreads, p, st);
+    case 2: return launch_pdl(paged_scatter_kernel<Tin, KV, 2>, grid, kPagedThreads, p, st);
+    default: return launch_pdl(paged_scatter_kernel<Tin, KV, 1>, grid, kPagedThreads, p, st);
   }
-  return cudaGetLastError();
 }
 
 // (input dtype) x (cache mode) -> template instance; the build's counterpart of the
@@ -557,6 +665,10 @@ static int flash_impl(const void* key, const void* value, void* key_cache, void*
   int vec = pick_vec(16, row_len, es_in, in_ptrs, 2, in_strides, 4);
   vec = pick_vec(vec, row_len, es_out, out_ptrs, 2, out_strides, 3);
 
+  // 256-bit loads need every chunk address on a 32-byte boundary
+  bool wide = (static_cast<int64_t>(vec) * es_in) % 32 == 0 && aligned(key, 32) && aligned(value, 32);
+  for (int i = 0; i < 4 && wide; ++i) wide = ((in_strides[i] * es_in) % 32) == 0;
+
   const int64_t chunks_per_row = row_len / vec;
   const int64_t items_per_token = rows * chunks_per_row;
   if (items_per_token >= (1ll << 30)) return fail(KVC_ERR_INVALID_ARG, "num_heads * head_size too large");
@@ -575,6 +687,8 @@ static int flash_impl(const void* key, const void* value, void* key_cache, void*
   p.head_stride = head_stride;
   p.block_size = block_size;
   p.bs_shift = pow2_shift(block_size);
+  p.linear_slots = (block_stride == block_size * page_stride);
+  p.wide_loads = wide;
   p.items_per_token = static_cast<uint32_t>(items_per_token);
   p.chunks_per_row = static_cast<uint32_t>(chunks_per_row);
   p.div_items_per_token = FastDiv(p.items_per_token);
@@ -589,7 +703,7 @@ static int flash_impl(const void* key, const void* value, void* key_cache, void*
     p.slot_mapping = slot_mapping + t0;
     p.n_items = static_cast<uint32_t>(nt * items_per_token);
     const dim3 grid(static_cast<unsigned>((p.n_items + kFlashThreads - 1) / kFlashThreads));
-    const cudaError_t e = KVC_DISPATCH(in_dtype, kv_dtype, launch_flash_vec, vec, p, grid, st);
+    const cudaError_t e = KVC_DISPATCH(in_dtype, kv_dtype, launch_flash_vec, vec, rows == 1, p, grid, st);
     if (e != cudaSuccess)
       return fail(KVC_ERR_CUDA, std::string("reshape_and_cache_flash launch failed: ") + cudaGetErrorString(e));
   }
@@ -614,6 +728,9 @@ static int paged_impl(const void* key, const void* value, void* key_cache, void*
   const int64_t in_strides[4] = {key_stride_t, value_stride_t, key_stride_h, value_stride_h};
   // a lane reads at most 32 bytes (one sector) of K and of V
   const int vec = pick_vec(32 / es_in, head_size, es_in, in_ptrs, 2, in_strides, 4);
+
+  bool wide = (static_cast<int64_t>(vec) * es_in) % 32 == 0 && aligned(key, 32) && aligned(value, 32);
+  for (int i = 0; i < 4 && wide; ++i) wide = ((in_strides[i] * es_in) % 32) == 0;
 
   // K-store width: groups of min(vec, x) elements when x is a power of two and the cache
   // base is aligned for it; single elements otherwise.
@@ -641,6 +758,7 @@ static int paged_impl(const void* key, const void* value, void* key_cache, void*
   p.num_tokens = num_tokens;
   p.block_size = block_size;
   p.bs_shift = pow2_shift(block_size);
+  p.wide_loads = wide;
   p.num_heads = static_cast<int32_t>(num_heads);
   p.head_size = static_cast<int32_t>(head_size);
   p.x = static_cast<int32_t>(x);
