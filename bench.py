@@ -147,18 +147,18 @@ def barrier(dist):
     torch.cuda.synchronize()
 
 
-def max_over_ranks(dist, v: float) -> float:
+def max_over_ranks(dist, v: float, device="cuda") -> float:
     if dist is None:
         return v
-    t = torch.tensor([v], dtype=torch.float64, device="cuda")
+    t = torch.tensor([v], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
 
 
-def sum_over_ranks(dist, v: float) -> float:
+def sum_over_ranks(dist, v: float, device="cuda") -> float:
     if dist is None:
         return v
-    t = torch.tensor([v], dtype=torch.float64, device="cuda")
+    t = torch.tensor([v], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.SUM)
     return float(t.item())
 
