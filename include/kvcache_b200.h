@@ -137,6 +137,42 @@ KVC_API int kvc_reshape_and_cache_flash_host(const void* host_key, const void* h
                                              int64_t head_stride, int in_dtype, int kv_dtype,
                                              const float* k_scale, const float* v_scale, void* stream);
 
+/*
+ * Variant of kvc_reshape_and_cache_flash_host that never allocates.  It has no
+ * counterpart in the reference.
+ *
+ * Who needs it: processes in which, by the time the cache is being written, the
+ * serving framework has already claimed the GPU's free memory for its own pool
+ * (vLLM sizes the KV cache from whatever is left), so that a late cudaMalloc by
+ * a helper library can fail or eat into that budget; and callers on a latency
+ * path that must not meet the device-wide synchronisation cudaMalloc/cudaFree
+ * imply.  For them the device staging of key, value and slot_mapping is a fixed
+ * area of KVC_NOALLOC_STAGING_BYTES inside the library's own device image:
+ * every GPU that loads the library holds that much until the process exits,
+ * whether or not this entry point is ever called.
+ *
+ * Limit: 2 * round256(num_tokens*num_heads*head_size*elem_size)
+ *        + round256(8*num_tokens) must not exceed KVC_NOALLOC_STAGING_BYTES
+ * (e.g. 4088 tokens of 8 x 128 bf16).  A larger batch fails with
+ * KVC_ERR_TOO_LARGE and a message that states both numbers; nothing is enqueued.
+ *
+ * The call uses no cudaMalloc, cudaFree or other allocating routine.  The first
+ * call on each device looks up the area's device address (cudaGetSymbolAddress,
+ * with that device current) and remembers it; make that first call outside of
+ * any stream capture.  All calls on a device share the one area and it keeps
+ * whatever the last call left in it: each call overwrites every byte it later
+ * reads, so nothing needs clearing, but two calls whose work overlaps on the GPU
+ * (different streams without ordering) race on it.  Arguments, semantics and
+ * results are otherwise those of kvc_reshape_and_cache_flash_host.
+ */
+#define KVC_NOALLOC_STAGING_BYTES (16 * 1024 * 1024)
+KVC_API int kvc_reshape_and_cache_flash_host_noalloc(
+    const void* host_key, const void* host_value, void* key_cache, void* value_cache,
+    const int64_t* host_slot_mapping, int64_t num_tokens, int64_t num_heads, int64_t head_size,
+    int64_t block_size, int64_t key_stride_t, int64_t value_stride_t, int64_t block_stride,
+    int64_t page_stride, int64_t head_stride, int in_dtype, int kv_dtype, const float* k_scale,
+    const float* v_scale, void* stream);
+
 /* Frees the staging buffers of kvc_reshape_and_cache_flash_host on the current device. */
 KVC_API int kvc_release_staging(void);
 

@@ -805,6 +805,30 @@ static int staging_reserve(int dev, size_t bytes, void** out) {
 
 static size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// ---------------------------------------------------------------------------------------------
+// fixed staging for kvc_reshape_and_cache_flash_host_noalloc: lives in the module image, so
+// every device that loads this library holds KVC_NOALLOC_STAGING_BYTES of it until exit.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_fixed_staging[KVC_NOALLOC_STAGING_BYTES];
+
+// In host code `g_fixed_staging` is only a handle for the symbol, not an address a kernel or
+// a copy may use; the per-device address comes from cudaGetSymbolAddress, asked once per
+// device while that device is current.
+static void* g_fixed_staging_addr[kMaxDevices];
+static std::mutex g_fixed_staging_mu;
+
+static int fixed_staging_address(int dev, void** out) {
+  std::lock_guard<std::mutex> lk(g_fixed_staging_mu);
+  if (g_fixed_staging_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    KVC_CUDA_TRY(cudaGetSymbolAddress((void**)&ptr, g_fixed_staging));
+    if (ptr == nullptr) return fail(KVC_ERR_CUDA, "cudaGetSymbolAddress returned a null staging address");
+    g_fixed_staging_addr[dev] = ptr;
+  }
+  *out = g_fixed_staging_addr[dev];
+  return KVC_OK;
+}
+
 }  // namespace kvc
 
 // ---------------------------------------------------------------------------------------------
@@ -881,6 +905,63 @@ int kvc_reshape_and_cache_flash_host(const void* host_key, const void* host_valu
   char* dval = dkey + kv_bytes;
   int64_t* dslots = reinterpret_cast<int64_t*>(dval + kv_bytes);
   // Rows are packed on the device whatever the host stride.
+  const void* hsrc[2] = {host_key, host_value};
+  char* ddst[2] = {dkey, dval};
+  const int64_t hstride[2] = {key_stride_t, value_stride_t};
+  for (int i = 0; i < 2; ++i) {
+    if (hstride[i] == row) {
+      KVC_CUDA_TRY(cudaMemcpyAsync(ddst[i], hsrc[i], static_cast<size_t>(num_tokens) * row_bytes,
+                                   cudaMemcpyHostToDevice, st));
+    } else {
+      KVC_CUDA_TRY(cudaMemcpy2DAsync(ddst[i], row_bytes, hsrc[i], static_cast<size_t>(hstride[i]) * es, row_bytes,
+                                     static_cast<size_t>(num_tokens), cudaMemcpyHostToDevice, st));
+    }
+  }
+  KVC_CUDA_TRY(cudaMemcpyAsync(dslots, host_slot_mapping, static_cast<size_t>(num_tokens) * 8,
+                               cudaMemcpyHostToDevice, st));
+  return flash_impl(dkey, dval, key_cache, value_cache, dslots, num_tokens, num_heads, head_size, block_size,
+                    row, head_size, row, head_size, block_stride, page_stride, head_stride, in_dtype, kv_dtype,
+                    k_scale, v_scale, st);
+}
+
+int kvc_reshape_and_cache_flash_host_noalloc(const void* host_key, const void* host_value, void* key_cache,
+                                             void* value_cache, const int64_t* host_slot_mapping,
+                                             int64_t num_tokens, int64_t num_heads, int64_t head_size,
+                                             int64_t block_size, int64_t key_stride_t, int64_t value_stride_t,
+                                             int64_t block_stride, int64_t page_stride, int64_t head_stride,
+                                             int in_dtype, int kv_dtype, const float* k_scale,
+                                             const float* v_scale, void* stream) {
+  if (int rc = check_common(host_key, host_value, key_cache, value_cache, host_slot_mapping, num_tokens,
+                            num_heads, head_size, block_size, in_dtype, kv_dtype, k_scale, v_scale))
+    return rc;
+  if (num_tokens == 0 || num_heads == 0 || head_size == 0) return KVC_OK;
+  const int64_t row = num_heads * head_size;
+  if (key_stride_t < row || value_stride_t < row)
+    return fail(KVC_ERR_INVALID_ARG, "host key/value token stride is smaller than num_heads*head_size");
+  const size_t es = static_cast<size_t>(in_elem_size(in_dtype));
+  const size_t row_bytes = static_cast<size_t>(row) * es;
+  // capacity check first, in integers that cannot wrap
+  const size_t cap = static_cast<size_t>(KVC_NOALLOC_STAGING_BYTES);
+  if (row_bytes > cap || static_cast<size_t>(num_tokens) > cap / row_bytes)
+    return fail(KVC_ERR_TOO_LARGE, "kvc_reshape_and_cache_flash_host_noalloc: batch does not fit the fixed staging area");
+  const size_t kv_bytes = round_up(static_cast<size_t>(num_tokens) * row_bytes, 256);
+  const size_t slot_bytes = round_up(static_cast<size_t>(num_tokens) * 8, 256);
+  const size_t need = 2 * kv_bytes + slot_bytes;
+  if (need > cap)
+    return fail(KVC_ERR_TOO_LARGE,
+                "kvc_reshape_and_cache_flash_host_noalloc: needs " + std::to_string(need) +
+                    " bytes of staging (2 x tokens x heads x head_size x element size + 8 x tokens), the fixed "
+                    "area holds " + std::to_string(cap) + "; split the batch or use kvc_reshape_and_cache_flash_host");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int dev = 0;
+  KVC_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(KVC_ERR_INVALID_ARG, "device ordinal out of range");
+  void* base = nullptr;
+  if (int rc = fixed_staging_address(dev, &base)) return rc;
+  char* dkey = static_cast<char*>(base);
+  char* dval = dkey + kv_bytes;
+  int64_t* dslots = reinterpret_cast<int64_t*>(dval + kv_bytes);
+  // Every byte the kernel will read is overwritten here first; nothing relies on the area's old contents.
   const void* hsrc[2] = {host_key, host_value};
   char* ddst[2] = {dkey, dval};
   const int64_t hstride[2] = {key_stride_t, value_stride_t};

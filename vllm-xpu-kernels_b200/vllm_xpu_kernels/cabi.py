@@ -26,6 +26,7 @@ SYMBOLS = (
     "kvc_reshape_and_cache_flash",
     "kvc_reshape_and_cache",
     "kvc_reshape_and_cache_flash_host",
+    "kvc_reshape_and_cache_flash_host_noalloc",
     "kvc_release_staging",
     "kvc_count_bad_slots",
 )
@@ -53,6 +54,8 @@ def lib() -> ctypes.CDLL:
         L.kvc_reshape_and_cache.argtypes = [vp] * 5 + [i64] * 9 + [ci, ci, vp, vp, vp]
         L.kvc_reshape_and_cache_flash_host.restype = ci
         L.kvc_reshape_and_cache_flash_host.argtypes = [vp] * 5 + [i64] * 9 + [ci, ci, vp, vp, vp]
+        L.kvc_reshape_and_cache_flash_host_noalloc.restype = ci
+        L.kvc_reshape_and_cache_flash_host_noalloc.argtypes = [vp] * 5 + [i64] * 9 + [ci, ci, vp, vp, vp]
         L.kvc_release_staging.restype = ci
         L.kvc_release_staging.argtypes = []
         L.kvc_count_bad_slots.restype = ci
@@ -131,6 +134,31 @@ def reshape_and_cache_flash_host(host_key, host_value, key_cache, value_cache, h
     if H > 1 and (host_key.stride(1) != D or host_value.stride(1) != D):
         raise RuntimeError("host key/value must have contiguous heads")
     _check(lib().kvc_reshape_and_cache_flash_host(
+        host_key.data_ptr(), host_value.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+        host_slot_mapping.data_ptr(), host_slot_mapping.shape[0], H, D, key_cache.shape[1],
+        host_key.stride(0), host_value.stride(0),
+        key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
+        _in_dtype(host_key), kv, _scale_ptr(k_scale, kv), _scale_ptr(v_scale, kv), _stream(stream)))
+
+
+NOALLOC_STAGING_BYTES = 16 * 1024 * 1024  # KVC_NOALLOC_STAGING_BYTES in include/kvcache_b200.h
+
+
+def reshape_and_cache_flash_host_noalloc(host_key, host_value, key_cache, value_cache, host_slot_mapping,
+                                         kv_cache_dtype: str, k_scale=None, v_scale=None, stream=None) -> None:
+    """``kvc_reshape_and_cache_flash_host_noalloc``: like ``reshape_and_cache_flash_host`` but the
+    device staging is the library's fixed 16 MiB area, for processes that can no longer call
+    cudaMalloc (all free GPU memory already belongs to the serving framework's pool) or must not
+    pay its synchronisation.  Batches that do not fit raise ``RuntimeError``; calls that overlap on
+    the GPU race on the shared area; the first call per device should precede any stream capture."""
+    kv = parse_kv_cache_dtype(kv_cache_dtype)
+    for t in (host_key, host_value, host_slot_mapping):
+        if t.is_cuda:
+            raise RuntimeError("host entry point needs CPU tensors for key, value and slot_mapping")
+    H, D = host_key.shape[1], host_key.shape[2]
+    if H > 1 and (host_key.stride(1) != D or host_value.stride(1) != D):
+        raise RuntimeError("host key/value must have contiguous heads")
+    _check(lib().kvc_reshape_and_cache_flash_host_noalloc(
         host_key.data_ptr(), host_value.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
         host_slot_mapping.data_ptr(), host_slot_mapping.shape[0], H, D, key_cache.shape[1],
         host_key.stride(0), host_value.stride(0),
