@@ -163,6 +163,15 @@ def sum_over_ranks(dist, v: float, device="cuda") -> float:
     return float(t.item())
 
 
+def host_threads() -> int:
+    """Threads for the CPU legs: every core this process may run on (torchrun presets
+    OMP_NUM_THREADS=1, which the explicit thread count overrides)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def make_batch_sets(name: str, rank: int, world: int, scaling: str, nbuf: int):
     """nbuf independent batches of the named workload for this rank (CPU tensors)."""
     sets = []
@@ -199,7 +208,7 @@ def cpu_oracle_rate(w, budget_s: float, host_blocks: int = 4096, tokens: int | N
     cdt = torch.uint8 if w.kv_cache_dtype != "auto" else key.dtype
     kc = torch.zeros(host_blocks, bs, w.num_heads, w.head_size, dtype=cdt)
     vc = torch.zeros_like(kc)
-    threads = oracle.max_threads()
+    threads = host_threads()
     args = (H.as_np(key), H.as_np(value), H.as_np(kc), H.as_np(vc), slots.numpy(), w.kv_cache_dtype,
             float(w.k_scale), float(w.v_scale), H.ORC_IN[key.dtype])
     oracle.reshape_and_cache_flash(*args, threads=threads)  # warm-up: page in, spin up the thread pool
@@ -353,9 +362,9 @@ def run_b200_arm(ns) -> None:
     e2e_steps = max(1, min(ns.steps, 40))
     hsets = [(w.key.contiguous().pin_memory(), w.value.contiguous().pin_memory(), w.slot_mapping.pin_memory())
              for w in sets[:4]]
-    probes = [torch.empty(2, w0.num_heads * w0.head_size, dtype=torch.uint8).pin_memory() for _ in range(4)]
     kflat = key_cache.view(torch.uint8).view(w0.num_blocks * w0.block_size, -1)
     vflat = value_cache.view(torch.uint8).view(w0.num_blocks * w0.block_size, -1)
+    probes = [torch.empty(2, kflat.shape[1], dtype=torch.uint8).pin_memory() for _ in range(4)]
     last_slots = [int(w.slot_mapping[w.slot_mapping >= 0][-1]) for w in sets[:4]]
 
     def e2e_step(i: int) -> None:
@@ -415,9 +424,13 @@ def run_b200_arm(ns) -> None:
         dist.destroy_process_group()
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu
-# summaries under profiles/; None until a capture exists for the workload.
-TRAFFIC_BYTES_PER_LAUNCH: dict[str, int | None] = {}
+# DRAM bytes per launch from the ncu capture summarised in
+# profiles/flash_scatter_bf16_fp8.md.  The capture ran the same kernel on 32768 tokens (the
+# full-size workload holds too much memory for a multi-pass capture); traffic grows in
+# proportion to the tokens, so a 16384-token launch is half of it: dram__bytes_read.sum
+# 134 504 704 / 2, plus the 33 554 432 bytes written, all of which reach DRAM once (the capture
+# window itself saw 47 % of them leave L2 before the kernel ended, the rest are written back later).
+TRAFFIC_BYTES_PER_LAUNCH: dict[str, int | None] = {"C4": 67_252_352 + 33_554_432}
 
 
 def main() -> None:

@@ -147,8 +147,23 @@ __device__ __forceinline__ void store_piece(void* gptr, const Chunk<BYTES>& c, i
   }
 }
 
+// `wide`: the address is 32-byte aligned, so 32-byte pieces go out as single 256-bit stores
+// (a lane then fills a whole sector with one instruction instead of two half-sector writes).
 template <int BYTES>
-__device__ __forceinline__ void store_chunk(void* gptr, const Chunk<BYTES>& c) {
+__device__ __forceinline__ void store_chunk(void* gptr, const Chunk<BYTES>& c, bool wide) {
+  if constexpr (BYTES % 32 == 0) {
+    if (wide) {
+      const uint4* src = reinterpret_cast<const uint4*>(c.b);
+#pragma unroll
+      for (int i = 0; i < BYTES / 32; ++i) {
+        const uint4 lo = src[2 * i], hi = src[2 * i + 1];
+        asm volatile("st.global.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(static_cast<char*>(gptr) + 32 * i),
+                     "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                     : "memory");
+      }
+      return;
+    }
+  }
   constexpr int P = BYTES >= 16 ? 16 : BYTES;
 #pragma unroll
   for (int i = 0; i < BYTES / P; ++i) store_piece<P>(static_cast<char*>(gptr) + P * i, c, P * i);
@@ -331,7 +346,8 @@ struct FlashParams {
   int64_t block_size;
   int bs_shift;
   bool linear_slots;         // block_stride == block_size * page_stride: address = slot * page_stride
-  bool wide_loads;           // every chunk address is 32-byte aligned
+  bool wide_loads;           // every source chunk address is 32-byte aligned
+  bool wide_stores;          // every destination chunk address is 32-byte aligned
   uint32_t n_items;          // tokens_in_launch * rows_per_token * chunks_per_row
   uint32_t items_per_token;  // rows_per_token * chunks_per_row
   uint32_t chunks_per_row;
@@ -394,8 +410,8 @@ __global__ void __launch_bounds__(kFlashThreads) flash_scatter_kernel(const Flas
   Chunk<OUT_B> kout, vout;
   convert_chunk<Tin, KV, VEC>(kin, kout, ks);
   convert_chunk<Tin, KV, VEC>(vin, vout, vs);
-  store_chunk(static_cast<char*>(p.key_cache) + dst * OUT_ES, kout);
-  store_chunk(static_cast<char*>(p.value_cache) + dst * OUT_ES, vout);
+  store_chunk(static_cast<char*>(p.key_cache) + dst * OUT_ES, kout, p.wide_stores);
+  store_chunk(static_cast<char*>(p.value_cache) + dst * OUT_ES, vout, p.wide_stores);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -669,6 +685,9 @@ static int flash_impl(const void* key, const void* value, void* key_cache, void*
   bool wide = (static_cast<int64_t>(vec) * es_in) % 32 == 0 && aligned(key, 32) && aligned(value, 32);
   for (int i = 0; i < 4 && wide; ++i) wide = ((in_strides[i] * es_in) % 32) == 0;
 
+  bool wide_st = (static_cast<int64_t>(vec) * es_out) % 32 == 0 && aligned(key_cache, 32) && aligned(value_cache, 32);
+  for (int i = 0; i < 3 && wide_st; ++i) wide_st = ((out_strides[i] * es_out) % 32) == 0;
+
   const int64_t chunks_per_row = row_len / vec;
   const int64_t items_per_token = rows * chunks_per_row;
   if (items_per_token >= (1ll << 30)) return fail(KVC_ERR_INVALID_ARG, "num_heads * head_size too large");
@@ -689,6 +708,7 @@ static int flash_impl(const void* key, const void* value, void* key_cache, void*
   p.bs_shift = pow2_shift(block_size);
   p.linear_slots = (block_stride == block_size * page_stride);
   p.wide_loads = wide;
+  p.wide_stores = wide_st;
   p.items_per_token = static_cast<uint32_t>(items_per_token);
   p.chunks_per_row = static_cast<uint32_t>(chunks_per_row);
   p.div_items_per_token = FastDiv(p.items_per_token);
