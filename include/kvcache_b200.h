@@ -117,6 +117,45 @@ KVC_API int kvc_reshape_and_cache(const void* key, const void* value, void* key_
                                   void* stream);
 
 /*
+ * Replaces the host launcher + kernel of `concat_and_cache_mla`
+ * (csrc/cache.cpp:513-550 host, :191-269 kernel; schema
+ * csrc/torch_bindings.cpp:127-133).
+ *
+ *   kv_c      [>= num_tokens, kv_lora_rank], last dim contiguous, kv_c_stride = stride(0)
+ *   k_pe      [>= num_tokens, pe_dim],       last dim contiguous, k_pe_stride = stride(0)
+ *   kv_cache  [num_blocks, block_size, kv_lora_rank + pe_dim] with block_stride =
+ *             stride(0), entry_stride = stride(1); entry = kv_c row then k_pe row
+ *   scale     one fp32 value in DEVICE memory, used for both halves (fp8 modes)
+ * fp8 modes store rne_saturate(float(x) / scale), the rule of the K/V ops and of
+ * upstream vLLM; the reference's SYCL kernel multiplies (cache.cpp:240-244) in a
+ * branch its own test cannot reach.  Index arithmetic is 64-bit (reference: int).
+ */
+KVC_API int kvc_concat_and_cache_mla(const void* kv_c, const void* k_pe, void* kv_cache,
+                                     const int64_t* slot_mapping, int64_t num_tokens,
+                                     int64_t kv_lora_rank, int64_t pe_dim, int64_t block_size,
+                                     int64_t kv_c_stride, int64_t k_pe_stride, int64_t block_stride,
+                                     int64_t entry_stride, int in_dtype, int kv_dtype, const float* scale,
+                                     void* stream);
+
+/*
+ * Replaces the host launcher + kernel of `gather_cache`
+ * (csrc/cache.cpp:576-638 host, :271-382 kernel; schema
+ * csrc/torch_bindings.cpp:136-139): for every sequence b < batch_size and every
+ * j < cu_seq_lens[b+1] - cu_seq_lens[b],
+ *   dst[cu_seq_lens[b] + j] = src_cache[block_table[b][seq_starts[b]/block_size + j/block_size]][j % block_size]
+ * (seq_starts may be NULL = all zero).  A plain byte copy of entry_size elements
+ * of elem_size 1, 2 or 4 bytes; strides in elements.  Only rows below
+ * min(num_dst_rows, cu_seq_lens[batch_size]) are written, so the launch is
+ * sized from dst's row count and never reads the token total on the host.
+ * block_table, cu_seq_lens and seq_starts are int32 DEVICE arrays.
+ */
+KVC_API int kvc_gather_cache(const void* src_cache, void* dst, const int32_t* block_table,
+                             const int32_t* cu_seq_lens, const int32_t* seq_starts, int64_t batch_size,
+                             int64_t num_dst_rows, int64_t block_size, int64_t entry_size, int64_t elem_size,
+                             int64_t block_table_stride, int64_t cache_block_stride,
+                             int64_t cache_entry_stride, int64_t dst_entry_stride, void* stream);
+
+/*
  * Same operation as kvc_reshape_and_cache_flash for callers whose key, value
  * and slot_mapping live in HOST memory (pinned memory makes the copies
  * asynchronous).  The rows are copied into device staging buffers owned by the

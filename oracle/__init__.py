@@ -45,6 +45,10 @@ def lib() -> ctypes.CDLL:
         L.orc_reshape_and_cache_flash.argtypes = [vp, vp, vp, vp, vp] + [i64] * 11 + [ci, ci, f32, f32, i64, ci]
         L.orc_reshape_and_cache.restype = ci
         L.orc_reshape_and_cache.argtypes = [vp, vp, vp, vp, vp] + [i64] * 9 + [ci, ci, f32, f32, i64, ci]
+        L.orc_concat_and_cache_mla.restype = ci
+        L.orc_concat_and_cache_mla.argtypes = [vp, vp, vp, vp] + [i64] * 8 + [ci, ci, f32, i64]
+        L.orc_gather_cache.restype = None
+        L.orc_gather_cache.argtypes = [vp] * 5 + [i64] * 8
         L.orc_convert_table.restype = None
         L.orc_convert_table.argtypes = [ci, ci, f32, vp]
         L.orc_convert_f32.restype = None
@@ -138,6 +142,50 @@ def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, kv_cache
         float(k_scale), float(v_scale), nb * bs if check_slots else -1, threads)
     if rc != 0:
         raise IndexError("slot_mapping holds a slot >= num_blocks * block_size")
+
+
+def concat_and_cache_mla(kv_c, k_pe, kv_cache, slot_mapping, kv_cache_dtype: str, scale: float, in_dtype: str,
+                         check_slots: bool = True) -> None:
+    """In-place oracle for ``_C_cache_ops.concat_and_cache_mla``.
+
+    kv_c [>=T, R], k_pe [>=T, P] (last dim contiguous), kv_cache [num_blocks, block_size, R + P] view."""
+    want_in = np.float32 if in_dtype == "f32" else np.uint16
+    if kv_c.dtype != want_in or k_pe.dtype != want_in:
+        raise TypeError(f"{in_dtype} inputs must be {np.dtype(want_in)} arrays")
+    kv = KV_DTYPES[kv_cache_dtype]
+    if kv_cache.dtype != (want_in if kv == 0 else np.uint8):
+        raise TypeError("kv_cache array has the wrong dtype")
+    slot_mapping = np.ascontiguousarray(slot_mapping, dtype=np.int64)
+    T = slot_mapping.shape[0]
+    R, P = kv_c.shape[1], k_pe.shape[1]
+    nb, bs = kv_cache.shape[0], kv_cache.shape[1]
+    if kv_cache.shape[2] != R + P:
+        raise ValueError("kv_cache.shape[2] must be kv_lora_rank + pe_dim")
+    cs = _estrides(kv_cache)
+    for a in (kv_c, k_pe, kv_cache):
+        if a.shape[-1] > 1 and _estrides(a)[-1] != 1:
+            raise ValueError("last dim must be contiguous")
+    rc = lib().orc_concat_and_cache_mla(
+        kv_c.ctypes.data, k_pe.ctypes.data, kv_cache.ctypes.data, slot_mapping.ctypes.data, T, R, P, bs,
+        _estrides(kv_c)[0], _estrides(k_pe)[0], cs[0], cs[1], IN_DTYPES[in_dtype], kv, float(scale),
+        nb * bs if check_slots else -1)
+    if rc != 0:
+        raise IndexError("slot_mapping holds a slot >= num_blocks * block_size")
+
+
+def gather_cache(src_cache, dst, block_table, cu_seq_lens, batch_size: int, seq_starts=None) -> None:
+    """In-place oracle for ``_C_cache_ops.gather_cache``: src_cache [num_blocks, block_size, entry...] view
+    with contiguous entries, dst [rows, entry...] with contiguous rows, int32 tables."""
+    if src_cache.dtype != dst.dtype:
+        raise TypeError("src_cache and dst must have the same dtype")
+    block_table = np.ascontiguousarray(block_table, dtype=np.int32)
+    cu_seq_lens = np.ascontiguousarray(cu_seq_lens, dtype=np.int32)
+    ss = None if seq_starts is None else np.ascontiguousarray(seq_starts, dtype=np.int32)
+    entry_bytes = int(np.prod(src_cache.shape[2:])) * src_cache.itemsize
+    lib().orc_gather_cache(
+        src_cache.ctypes.data, dst.ctypes.data, block_table.ctypes.data, cu_seq_lens.ctypes.data,
+        None if ss is None else ss.ctypes.data, batch_size, dst.shape[0], src_cache.shape[1], entry_bytes,
+        block_table.shape[1], src_cache.strides[0], src_cache.strides[1], dst.strides[0])
 
 
 def convert_table(in_dtype: str, kv_cache_dtype: str, scale: float) -> np.ndarray:

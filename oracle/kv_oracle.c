@@ -12,6 +12,10 @@
  *                                tests/test_cache.py:284-292 (torch loop)
  *   orc_reshape_and_cache        csrc/cache.cpp:44-85 (index formulas :57-67),
  *                                tests/test_cache.py:155-164 (torch loop)
+ *   orc_concat_and_cache_mla     csrc/cache.cpp:222-253 (device body), :513-550 (host),
+ *                                tests/test_cache.py:370-375 (torch loop)
+ *   orc_gather_cache             csrc/cache.cpp:305-366 (device body), :576-638 (host),
+ *                                tests/test_cache.py:460-477 (torch loop)
  *   element conversion           csrc/quantization/fp8/quant_utils.h:62-78
  *                                (auto: bit copy; fp8: float(src) / scale,
  *                                then cast)
@@ -226,6 +230,53 @@ int orc_reshape_and_cache(const void* key, const void* value, void* key_cache, v
   }
   (void)nthreads;
   return bad ? -1 : 0;
+}
+
+/*
+ * MLA: kv_cache[block][offset][0:R] = kv_c[t], [R:R+P] = k_pe[t]; strides in elements.
+ * fp8 modes divide by the scale like the K/V ops (the reference kernel multiplies,
+ * cache.cpp:240-244, in a branch its test cannot reach).
+ */
+int orc_concat_and_cache_mla(const void* kv_c, const void* k_pe, void* kv_cache, const int64_t* slot_mapping,
+                             int64_t num_tokens, int64_t kv_lora_rank, int64_t pe_dim, int64_t block_size,
+                             int64_t kv_c_stride, int64_t k_pe_stride, int64_t block_stride,
+                             int64_t entry_stride, int in_dt, int kv, float scale, int64_t num_slots) {
+  int bad = 0;
+  for (int64_t t = 0; t < num_tokens; ++t) {
+    const int64_t slot = slot_mapping[t];
+    if (slot < 0) continue;
+    if (num_slots >= 0 && slot >= num_slots) {
+      bad = 1;
+      continue;
+    }
+    const int64_t dst0 = (slot / block_size) * block_stride + (slot % block_size) * entry_stride;
+    for (int64_t i = 0; i < kv_lora_rank; ++i) store_elem(kv_cache, dst0 + i, kv_c, t * kv_c_stride + i, in_dt, kv, scale);
+    for (int64_t i = 0; i < pe_dim; ++i)
+      store_elem(kv_cache, dst0 + kv_lora_rank + i, k_pe, t * k_pe_stride + i, in_dt, kv, scale);
+  }
+  return bad ? -1 : 0;
+}
+
+/*
+ * gather: for each sequence b and each j < cu[b+1]-cu[b]:
+ *   dst[cu[b]+j] = src[block_table[b][seq_starts[b]/bs + j/bs]][j%bs]   (cache.cpp:305-366).
+ * Byte copy of entry_bytes per row; strides in BYTES.  Rows at or beyond num_dst_rows are not written.
+ */
+void orc_gather_cache(const void* src_cache, void* dst, const int32_t* block_table, const int32_t* cu_seq_lens,
+                      const int32_t* seq_starts, int64_t batch_size, int64_t num_dst_rows, int64_t block_size,
+                      int64_t entry_bytes, int64_t block_table_stride, int64_t cache_block_stride,
+                      int64_t cache_entry_stride, int64_t dst_entry_stride) {
+  for (int64_t b = 0; b < batch_size; ++b) {
+    const int64_t start = cu_seq_lens[b], len = (int64_t)cu_seq_lens[b + 1] - start;
+    const int64_t first = seq_starts ? seq_starts[b] / block_size : 0;
+    for (int64_t j = 0; j < len; ++j) {
+      if (start + j >= num_dst_rows) break;
+      const int64_t blk = block_table[b * block_table_stride + first + j / block_size];
+      memcpy((char*)dst + (start + j) * dst_entry_stride,
+             (const char*)src_cache + blk * cache_block_stride + (j % block_size) * cache_entry_stride,
+             (size_t)entry_bytes);
+    }
+  }
 }
 
 int orc_max_threads(void) {

@@ -25,3 +25,15 @@ def run(layout: str, key, value, key_cache, value_cache, slot_mapping, kv_cache_
     fn = oracle.reshape_and_cache_flash if layout == "flash" else oracle.reshape_and_cache
     fn(as_np(key), as_np(value), as_np(key_cache), as_np(value_cache), slot_mapping.numpy(), kv_cache_dtype,
        float(k_scale), float(v_scale), ORC_IN[key.dtype], threads=threads)
+
+
+def run_mla(kv_c, k_pe, kv_cache, slot_mapping, kv_cache_dtype: str, scale: float) -> None:
+    import oracle
+    oracle.concat_and_cache_mla(as_np(kv_c), as_np(k_pe), as_np(kv_cache), slot_mapping.numpy(), kv_cache_dtype,
+                                float(scale), ORC_IN[kv_c.dtype])
+
+
+def run_gather(src_cache, dst, block_table, cu_seq_lens, batch_size: int, seq_starts=None) -> None:
+    import oracle
+    oracle.gather_cache(as_np(src_cache), as_np(dst), block_table.numpy(), cu_seq_lens.numpy(), batch_size,
+                        None if seq_starts is None else seq_starts.numpy())

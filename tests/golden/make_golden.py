@@ -11,6 +11,7 @@ What comes from the reference, imported as Python and executed on the CPU:
   * PyTorch's own ``float -> float8`` cast, which is the conversion the reference
     kernels call (csrc/quantization/fp8/quant_utils.h:70-74 there).
 What is restated here because it only exists inline in GPU-only test functions:
+  * the MLA and gather recipes and expectations (tests/test_cache.py:337-375, :423-477);
   * the input recipe (``qkv = randn(T, 3, H, D); _, key, value = qkv.unbind(1)``,
     ``random.sample`` slots: tests/test_cache.py:88-93, :211-222) and
   * the expected-result loops (tests/test_cache.py:155-164 paged, :284-292 flash).
@@ -104,6 +105,68 @@ def make_case(ru, layout: str, dtype: str, kv_cache_dtype: str, T: int, H: int, 
         cache_is_view=np.bool_(layout == "flash"))
 
 
+def make_mla_case(ru, dtype: str, kv_cache_dtype: str, T: int, R: int, P: int, bs: int, nb: int, seed: int,
+                  n_skip: int = 0) -> dict:
+    """Recipe of tests/test_cache.py:337-375 of the reference (inputs, zero cache, placement loop);
+    fp8 expectation = torch's cast of float(x) / scale."""
+    tdt = DT[dtype]
+    ru.seed_everything(seed)
+    slots = random.sample(range(nb * bs), T)
+    for i in random.sample(range(T), n_skip):
+        slots[i] = -1
+    kv_c = torch.randn(T, R, dtype=tdt)
+    k_pe = torch.randn(T, P, dtype=tdt)
+    scale = torch.tensor(0.1, dtype=torch.float32)
+    cdt = tdt if kv_cache_dtype == "auto" else torch.float8_e4m3fn
+    before = torch.zeros(nb, bs, R + P, dtype=torch.uint8 if cdt != tdt else tdt)
+    before = before.view(cdt) if cdt != tdt else before
+    after = before.clone()
+    src_c = kv_c if kv_cache_dtype == "auto" else quantise_like_reference(kv_c, scale, kv_cache_dtype)
+    src_p = k_pe if kv_cache_dtype == "auto" else quantise_like_reference(k_pe, scale, kv_cache_dtype)
+    for i in range(T):
+        if slots[i] < 0:
+            continue
+        blk, off = slots[i] // bs, slots[i] % bs
+        after[blk, off, :R] = src_c[i]
+        after[blk, off, R:] = src_p[i]
+    return dict(op="mla", dtype=dtype, kv_cache_dtype=kv_cache_dtype, kv_c=bits(kv_c), k_pe=bits(k_pe),
+                slot_mapping=np.array(slots, dtype=np.int64), block_size=bs, scale=np.float32(0.1),
+                cache_before=bits(before), cache_after=bits(after))
+
+
+def make_gather_case(ru, dtype: str, entry: int, bs: int, nb: int, batch: int, max_seq_len: int, seed: int,
+                     with_seq_starts: bool) -> dict:
+    """Recipe of tests/test_cache.py:423-477 of the reference: random cache, per-sequence block
+    permutations, expected = concatenation of the sequences' blocks (last one partial)."""
+    tdt = DT[dtype]
+    ru.seed_everything(seed)
+    src = torch.randn(nb, bs, entry, dtype=tdt)
+    seq_lens = torch.randint(0, max_seq_len + 1, (batch,))
+    cu = torch.zeros(batch + 1, dtype=torch.int32)
+    cu[1:] = seq_lens.cumsum(0).to(torch.int32)
+    block_table = torch.stack([torch.randperm(nb) for _ in range(batch)]).to(torch.int32)
+    seq_starts = None
+    if with_seq_starts:
+        seq_starts = (torch.randint(0, 3, (batch,)) * bs + torch.randint(0, bs, (batch,))).to(torch.int32)
+    rows = []
+    for b in range(batch):
+        s_len = int(seq_lens[b])
+        if s_len == 0:
+            continue
+        first = int(seq_starts[b]) // bs if with_seq_starts else 0
+        tot = (s_len + bs - 1) // bs
+        blocks = block_table[b, first:first + tot].tolist()
+        parts = [src[blk] for blk in blocks[:-1]]
+        parts.append(src[blocks[-1], :s_len - (tot - 1) * bs])
+        rows.append(torch.cat(parts, dim=0))
+    expected = torch.cat(rows, dim=0) if rows else torch.zeros(0, entry, dtype=tdt)
+    out = dict(op="gather", dtype=dtype, src_cache=bits(src), block_table=block_table.numpy(), cu_seq_lens=cu.numpy(),
+               batch_size=batch, expected=bits(expected))
+    if with_seq_starts:
+        out["seq_starts"] = seq_starts.numpy()
+    return out
+
+
 def make_tables() -> dict:
     """torch's e4m3 / e5m2 cast over every bf16 and fp16 bit pattern at a few scales."""
     out = {}
@@ -156,6 +219,18 @@ def main() -> None:
         name = "{layout}_{dtype}_{kv_cache_dtype}_T{T}_H{H}_D{D}_bs{bs}_nb{nb}_s{seed}_div{d}".format(
             d=int(c["scale_div"]), **c) + ("_skip" if c.get("n_skip") else "")
         data = make_case(ru, **c)
+        np.savez_compressed(os.path.join(HERE, name + ".npz"), **data)
+        names.append(name)
+    extra = []
+    for dtype in ("half", "bfloat16", "float"):
+        extra.append(("mla_%s_auto_T42_R512_P64_bs16_nb8" % dtype, make_mla_case(ru, dtype, "auto", 42, 512, 64, 16, 8, 0)))
+    extra.append(("mla_bfloat16_fp8_T42_R512_P64_bs16_nb8", make_mla_case(ru, "bfloat16", "fp8", 42, 512, 64, 16, 8, 1)))
+    extra.append(("mla_half_fp8_T21_R64_P16_bs8_nb4_skip", make_mla_case(ru, "half", "fp8", 21, 64, 16, 8, 4, 2, n_skip=6)))
+    extra.append(("mla_half_auto_T1_R512_P64_bs8_nb4", make_mla_case(ru, "half", "auto", 1, 512, 64, 8, 4, 0)))
+    extra.append(("gather_float_E576_bs16_nb16_B4", make_gather_case(ru, "float", 576, 16, 16, 4, 60, 0, False)))
+    extra.append(("gather_bfloat16_E576_bs16_nb24_B6_starts", make_gather_case(ru, "bfloat16", 576, 16, 24, 6, 64, 1, True)))
+    extra.append(("gather_half_E40_bs8_nb16_B5", make_gather_case(ru, "half", 40, 8, 16, 5, 30, 2, False)))
+    for name, data in extra:
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **data)
         names.append(name)
     np.savez_compressed(os.path.join(HERE, "fp8_tables.npz"), **make_tables())

@@ -16,10 +16,38 @@ GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 TORCH_DT = {"half": torch.float16, "bfloat16": torch.bfloat16, "float": torch.float32}
 
 
-def golden_files() -> list[str]:
+def golden_files(kind: str = "kv") -> list[str]:
+    """Fixture files of one kind: "kv" (flash_* and paged_*), "mla" or "gather"."""
     with open(os.path.join(GOLDEN_DIR, "MANIFEST.txt")) as f:
         names = [ln.strip() for ln in f if ln.strip() and not ln.startswith("#")]
-    return [n for n in names if n != "fp8_tables.npz"]
+    prefixes = {"kv": ("flash_", "paged_"), "mla": ("mla_",), "gather": ("gather_",)}[kind]
+    return [n for n in names if n.startswith(prefixes)]
+
+
+class MlaCase:
+    def __init__(self, fname: str):
+        z = np.load(os.path.join(GOLDEN_DIR, fname))
+        self.dtype = TORCH_DT[str(z["dtype"])]
+        self.kv_cache_dtype = str(z["kv_cache_dtype"])
+        self.kv_c = from_bits(z["kv_c"], self.dtype)
+        self.k_pe = from_bits(z["k_pe"], self.dtype)
+        self.slot_mapping = torch.from_numpy(z["slot_mapping"].astype(np.int64))
+        self.scale = float(z["scale"])
+        cdt = cache_torch_dtype(self.dtype, self.kv_cache_dtype)
+        self.cache_before = from_bits(z["cache_before"], cdt)
+        self.cache_after = from_bits(z["cache_after"], cdt)
+
+
+class GatherCase:
+    def __init__(self, fname: str):
+        z = np.load(os.path.join(GOLDEN_DIR, fname))
+        self.dtype = TORCH_DT[str(z["dtype"])]
+        self.src_cache = from_bits(z["src_cache"], self.dtype)
+        self.block_table = torch.from_numpy(z["block_table"].astype(np.int32))
+        self.cu_seq_lens = torch.from_numpy(z["cu_seq_lens"].astype(np.int32))
+        self.batch_size = int(z["batch_size"])
+        self.seq_starts = torch.from_numpy(z["seq_starts"].astype(np.int32)) if "seq_starts" in z.files else None
+        self.expected = from_bits(z["expected"], self.dtype)
 
 
 def from_bits(a: np.ndarray, dtype: torch.dtype) -> torch.Tensor:

@@ -62,6 +62,11 @@ def test_argument_validation_needs_no_device():
     rc = L.kvc_reshape_and_cache(p, p, p, p, p, 4, 2, 16, 4, 5, 32, 16, 32, 16, 2, 0, None, None, None)
     assert rc == 1 and "multiple of x" in cabi.last_error()
     assert L.kvc_count_bad_slots(p, 4, 16, None, None) == 1
+    # gather: element width must be 1, 2 or 4 bytes (message of csrc/cache.cpp:636 in the reference)
+    rc = L.kvc_gather_cache(p, p, p, p, None, 2, 8, 4, 16, 8, 4, 64, 16, 16, None)
+    assert rc == 2 and "Unsupported data type width: 64" in cabi.last_error()
+    assert L.kvc_gather_cache(p, p, p, p, None, 0, 8, 4, 16, 2, 4, 64, 16, 16, None) == 0  # empty batch
+    assert L.kvc_concat_and_cache_mla(None, p, p, p, 4, 16, 8, 4, 16, 8, 96, 24, 2, 0, None, None) == 1
 
 
 def test_torch_extension_registers_reference_schemas():
@@ -77,8 +82,18 @@ def test_torch_extension_registers_reference_schemas():
                                                       "kv_cache_dtype", "k_scale", "v_scale"]
         muts = [a.name for a in schema.arguments if a.alias_info is not None and a.alias_info.is_write]
         assert muts == ["key_cache", "value_cache"]
+    # the other two ops of the namespace (csrc/torch_bindings.cpp:127-133, :136-139 of the reference)
+    others = {
+        "concat_and_cache_mla": "(Tensor kv_c, Tensor k_pe, Tensor! kv_cache, Tensor slot_mapping, "
+                                "str kv_cache_dtype, Tensor scale) -> ()",
+        "gather_cache": "(Tensor src_cache, Tensor! dst, Tensor block_table, Tensor cu_seq_lens, int batch_size, "
+                        "Tensor? seq_starts) -> ()",
+    }
+    for name, sig in others.items():
+        assert str(getattr(ops, name).default._schema) == str(torch._C.parse_schema(f"_C_cache_ops::{name}{sig}"))
     from vllm_xpu_kernels import ops as wrappers
-    assert callable(wrappers.reshape_and_cache) and callable(wrappers.reshape_and_cache_flash)
+    for fn in ("reshape_and_cache", "reshape_and_cache_flash", "concat_and_cache_mla", "gather_cache"):
+        assert callable(getattr(wrappers, fn))
 
 
 def test_no_cpu_fallback():

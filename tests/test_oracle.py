@@ -7,6 +7,7 @@ import pytest
 import torch
 
 import oracle
+from oracle import torch_views
 from tests import helpers as H
 
 
@@ -21,6 +22,24 @@ def test_oracle_reproduces_reference_fixture(fname):
                   c.k_scale, c.v_scale)
     assert H.same_bytes(c.key_cache, c.key_cache_after)
     assert H.same_bytes(c.value_cache, c.value_cache_after)
+
+
+@pytest.mark.parametrize("fname", H.golden_files("mla"))
+def test_oracle_reproduces_reference_mla_fixture(fname):
+    c = H.MlaCase(fname)
+    cache = c.cache_before.clone()
+    torch_views.run_mla(c.kv_c, c.k_pe, cache, c.slot_mapping, c.kv_cache_dtype, c.scale)
+    assert H.same_bytes(cache, c.cache_after)
+
+
+@pytest.mark.parametrize("fname", H.golden_files("gather"))
+def test_oracle_reproduces_reference_gather_fixture(fname):
+    c = H.GatherCase(fname)
+    total = int(c.cu_seq_lens[-1])
+    dst = torch.zeros(total + 3, c.expected.shape[1], dtype=c.dtype)  # three spare rows must stay zero
+    torch_views.run_gather(c.src_cache, dst, c.block_table, c.cu_seq_lens, c.batch_size, c.seq_starts)
+    assert H.same_bytes(dst[:total], c.expected)
+    assert not bool(dst[total:].view(torch.uint8).any())
 
 
 @pytest.mark.parametrize("in_dtype,tdt", [("bf16", torch.bfloat16), ("f16", torch.float16)])

@@ -520,6 +520,130 @@ __global__ void __launch_bounds__(kPagedThreads) paged_scatter_kernel(const Page
 }
 
 // ---------------------------------------------------------------------------------------------
+// MLA: concatenate kv_c [T, R] and k_pe [T, P] into cache[block][offset][R + P]
+// ---------------------------------------------------------------------------------------------
+struct MlaParams {
+  const void* kv_c;
+  const void* k_pe;
+  void* kv_cache;
+  const int64_t* slot_mapping;
+  const float* scale;
+  int64_t kv_c_stride, k_pe_stride, block_stride, entry_stride;  // elements
+  int64_t block_size;
+  int64_t num_tokens;
+  int bs_shift;
+  bool wide_loads, wide_stores;
+  uint32_t n_items;        // ceil(T / 2) * chunks_per_token
+  uint32_t chunks_per_token;
+  uint32_t chunks_kv_c;    // chunks that come from kv_c; the rest come from k_pe
+  FastDiv div_chunks_per_token;
+};
+
+constexpr int kMlaThreads = 256;
+
+// One thread moves the same VEC-element chunk of two consecutive tokens' concatenated rows,
+// so two independent loads are in flight per thread.  Chunks below chunks_kv_c read kv_c,
+// the others k_pe; VEC divides both widths (the host picks it), so a chunk never straddles.
+template <typename Tin, int KV, int VEC>
+__global__ void __launch_bounds__(kMlaThreads) mla_scatter_kernel(const MlaParams p) {
+  constexpr int IN_B = VEC * (int)sizeof(Tin);
+  constexpr int OUT_ES = (KV == KVC_KV_AUTO) ? (int)sizeof(Tin) : 1;
+  constexpr int OUT_B = VEC * OUT_ES;
+
+  const uint32_t item = blockIdx.x * kMlaThreads + threadIdx.x;
+  if (item >= p.n_items) return;
+  const uint32_t pair = p.div_chunks_per_token.div(item);
+  const uint32_t chunk = item - pair * p.chunks_per_token;
+  pdl_prologue();
+
+  const int64_t t0 = static_cast<int64_t>(pair) * 2;
+  int64_t slot[2];
+  slot[0] = __ldg(p.slot_mapping + t0);
+  slot[1] = (t0 + 1 < p.num_tokens) ? __ldg(p.slot_mapping + t0 + 1) : -1;
+
+  const bool from_pe = chunk >= p.chunks_kv_c;
+  const Tin* base = static_cast<const Tin*>(from_pe ? p.k_pe : p.kv_c);
+  const int64_t stride = from_pe ? p.k_pe_stride : p.kv_c_stride;
+  const int64_t col = static_cast<int64_t>(from_pe ? chunk - p.chunks_kv_c : chunk) * VEC;
+
+  Chunk<IN_B> in[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+    if (slot[i] >= 0) load_chunk(in[i], base + (t0 + i) * stride + col, p.wide_loads);
+
+  ScaleCtx sc{};
+  if constexpr (KV != KVC_KV_AUTO) sc = make_scale_ctx<Tin, KV>(p.scale);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (slot[i] < 0) continue;
+    int64_t blk, off;
+    split_slot(slot[i], p.block_size, p.bs_shift, blk, off);
+    const int64_t dst = blk * p.block_stride + off * p.entry_stride + static_cast<int64_t>(chunk) * VEC;
+    Chunk<OUT_B> out;
+    convert_chunk<Tin, KV, VEC>(in[i], out, sc);
+    store_chunk(static_cast<char*>(p.kv_cache) + dst * OUT_ES, out, p.wide_stores);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// gather: dst[cu_seq_lens[b] + j] = cache[block_table[b][seq_starts[b]/bs + j/bs]][j % bs]
+// ---------------------------------------------------------------------------------------------
+struct GatherParams {
+  const void* src_cache;
+  void* dst;
+  const int32_t* block_table;
+  const int32_t* cu_seq_lens;
+  const int32_t* seq_starts;  // may be null
+  int64_t block_table_stride;
+  int64_t cache_block_stride, cache_entry_stride, dst_entry_stride;  // BYTES
+  int32_t batch_size;
+  int32_t block_size;
+  int bs_shift;
+  uint32_t n_items;  // dst_rows * chunks_per_row
+  uint32_t chunks_per_row;
+  FastDiv div_chunks_per_row, div_block_size;
+};
+
+constexpr int kGatherThreads = 256;
+
+// One thread copies one BYTES-wide piece of one destination row.  The row's sequence is found
+// by bisection over cu_seq_lens (batch_size + 1 ints, cache resident); rows at or beyond
+// cu_seq_lens[batch_size] are left alone, so the grid can be sized from dst's row count,
+// which the host knows, instead of from the token total, which lives on the device.
+template <int BYTES>
+__global__ void __launch_bounds__(kGatherThreads) gather_cache_kernel(const GatherParams p) {
+  const uint32_t item = blockIdx.x * kGatherThreads + threadIdx.x;
+  if (item >= p.n_items) return;
+  const uint32_t row = p.div_chunks_per_row.div(item);
+  const uint32_t chunk = item - row * p.chunks_per_row;
+  pdl_prologue();
+
+  // largest b in [0, batch_size) with cu[b] <= row, provided row < cu[batch_size]
+  const int32_t r = static_cast<int32_t>(row);
+  if (r >= __ldg(p.cu_seq_lens + p.batch_size)) return;
+  int lo = 0, hi = p.batch_size;  // invariant: cu[lo] <= r < cu[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(p.cu_seq_lens + mid) <= r) lo = mid; else hi = mid;
+  }
+  const int32_t j = r - __ldg(p.cu_seq_lens + lo);
+  if (j < 0) return;  // cu_seq_lens not monotone: nothing sensible to copy
+  const uint32_t jb = p.bs_shift >= 0 ? (static_cast<uint32_t>(j) >> p.bs_shift) : p.div_block_size.div(j);
+  const uint32_t off = static_cast<uint32_t>(j) - jb * static_cast<uint32_t>(p.block_size);
+  int32_t first = 0;
+  if (p.seq_starts != nullptr) first = __ldg(p.seq_starts + lo) / p.block_size;
+  const int64_t block = __ldg(p.block_table + lo * p.block_table_stride + first + jb);
+
+  const char* src = static_cast<const char*>(p.src_cache) + block * p.cache_block_stride +
+                    static_cast<int64_t>(off) * p.cache_entry_stride + static_cast<int64_t>(chunk) * BYTES;
+  char* dst = static_cast<char*>(p.dst) + static_cast<int64_t>(row) * p.dst_entry_stride +
+              static_cast<int64_t>(chunk) * BYTES;
+  Chunk<BYTES> c;
+  load_chunk(c, src, false);
+  store_chunk(dst, c, false);
+}
+
+// ---------------------------------------------------------------------------------------------
 // debug: count out-of-range slots
 // ---------------------------------------------------------------------------------------------
 __global__ void count_bad_slots_kernel(const int64_t* __restrict__ slots, int64_t n, int64_t num_slots,
@@ -795,6 +919,130 @@ static int paged_impl(const void* key, const void* value, void* key_cache, void*
   return KVC_OK;
 }
 
+template <typename Tin, int KV>
+static cudaError_t launch_mla_vec(int vec, const MlaParams& p, dim3 grid, cudaStream_t st) {
+  switch (vec) {
+    case 16: return launch_pdl(mla_scatter_kernel<Tin, KV, 16>, grid, kMlaThreads, p, st);
+    case 8: return launch_pdl(mla_scatter_kernel<Tin, KV, 8>, grid, kMlaThreads, p, st);
+    case 4: return launch_pdl(mla_scatter_kernel<Tin, KV, 4>, grid, kMlaThreads, p, st);
+    case 2: return launch_pdl(mla_scatter_kernel<Tin, KV, 2>, grid, kMlaThreads, p, st);
+    default: return launch_pdl(mla_scatter_kernel<Tin, KV, 1>, grid, kMlaThreads, p, st);
+  }
+}
+
+static int mla_impl(const void* kv_c, const void* k_pe, void* kv_cache, const int64_t* slot_mapping,
+                    int64_t num_tokens, int64_t kv_lora_rank, int64_t pe_dim, int64_t block_size,
+                    int64_t kv_c_stride, int64_t k_pe_stride, int64_t block_stride, int64_t entry_stride,
+                    int in_dtype, int kv_dtype, const float* scale, cudaStream_t st) {
+  // shares the argument rules of the K/V ops: kv_c plays key, k_pe plays value
+  if (int rc = check_common(kv_c, k_pe, kv_cache, kv_cache, slot_mapping, num_tokens, 1, kv_lora_rank + pe_dim,
+                            block_size, in_dtype, kv_dtype, scale, scale))
+    return rc;
+  if (kv_lora_rank < 0 || pe_dim < 0) return fail(KVC_ERR_INVALID_ARG, "kv_lora_rank and pe_dim must be non-negative");
+  if (num_tokens == 0 || kv_lora_rank + pe_dim == 0) return KVC_OK;
+  const int es_in = in_elem_size(in_dtype);
+  const int es_out = (kv_dtype == KVC_KV_AUTO) ? es_in : 1;
+
+  // one vector width for both sources: it must divide both widths and suit every base and stride
+  const void* in_ptrs[2] = {kv_c, k_pe};
+  const int64_t in_strides[2] = {kv_c_stride, k_pe_stride};
+  const void* out_ptrs[1] = {kv_cache};
+  const int64_t out_strides[3] = {block_stride, entry_stride, kv_lora_rank};
+  int vec = 16;
+  if (kv_lora_rank > 0) vec = pick_vec(vec, kv_lora_rank, es_in, in_ptrs, 1, in_strides, 1);
+  if (pe_dim > 0) vec = pick_vec(vec, pe_dim, es_in, in_ptrs + 1, 1, in_strides + 1, 1);
+  vec = pick_vec(vec, kv_lora_rank > 0 ? kv_lora_rank : pe_dim, es_out, out_ptrs, 1, out_strides, 3);
+  if (pe_dim > 0 && pe_dim % vec) vec = pick_vec(vec, pe_dim, es_out, out_ptrs, 1, out_strides, 3);
+  bool wide = (static_cast<int64_t>(vec) * es_in) % 32 == 0 && aligned(kv_c, 32) && aligned(k_pe, 32) &&
+              (kv_c_stride * es_in) % 32 == 0 && (k_pe_stride * es_in) % 32 == 0;
+  bool wide_st = (static_cast<int64_t>(vec) * es_out) % 32 == 0 && aligned(kv_cache, 32);
+  for (int i = 0; i < 3 && wide_st; ++i) wide_st = ((out_strides[i] * es_out) % 32) == 0;
+
+  const int64_t chunks = (kv_lora_rank + pe_dim) / vec;
+  const int64_t pairs = (num_tokens + 1) / 2;
+  if (chunks >= (1ll << 30) || pairs * chunks >= (1ll << 31) - kMlaThreads)
+    return fail(KVC_ERR_INVALID_ARG, "num_tokens * (kv_lora_rank + pe_dim) too large for one call");
+
+  MlaParams p{};
+  p.kv_c = kv_c;
+  p.k_pe = k_pe;
+  p.kv_cache = kv_cache;
+  p.slot_mapping = slot_mapping;
+  p.scale = scale;
+  p.kv_c_stride = kv_c_stride;
+  p.k_pe_stride = k_pe_stride;
+  p.block_stride = block_stride;
+  p.entry_stride = entry_stride;
+  p.block_size = block_size;
+  p.num_tokens = num_tokens;
+  p.bs_shift = pow2_shift(block_size);
+  p.wide_loads = wide;
+  p.wide_stores = wide_st;
+  p.n_items = static_cast<uint32_t>(pairs * chunks);
+  p.chunks_per_token = static_cast<uint32_t>(chunks);
+  p.chunks_kv_c = static_cast<uint32_t>(kv_lora_rank / vec);
+  p.div_chunks_per_token = FastDiv(p.chunks_per_token);
+  const dim3 grid((p.n_items + kMlaThreads - 1) / kMlaThreads);
+  const cudaError_t e = KVC_DISPATCH(in_dtype, kv_dtype, launch_mla_vec, vec, p, grid, st);
+  if (e != cudaSuccess)
+    return fail(KVC_ERR_CUDA, std::string("concat_and_cache_mla launch failed: ") + cudaGetErrorString(e));
+  return KVC_OK;
+}
+
+static int gather_impl(const void* src_cache, void* dst, const int32_t* block_table, const int32_t* cu_seq_lens,
+                       const int32_t* seq_starts, int64_t batch_size, int64_t num_dst_rows, int64_t block_size,
+                       int64_t entry_size, int64_t elem_size, int64_t block_table_stride,
+                       int64_t cache_block_stride, int64_t cache_entry_stride, int64_t dst_entry_stride,
+                       cudaStream_t st) {
+  if (elem_size != 1 && elem_size != 2 && elem_size != 4)
+    return fail(KVC_ERR_UNSUPPORTED, "Unsupported data type width: " + std::to_string(elem_size * 8));
+  if (batch_size < 0 || num_dst_rows < 0 || entry_size < 0 || batch_size > 0x7FFFFFFFll)
+    return fail(KVC_ERR_INVALID_ARG, "gather_cache: negative or oversized batch_size / rows / entry_size");
+  if (block_size <= 0 || block_size > 0x7FFFFFFFll) return fail(KVC_ERR_INVALID_ARG, "block_size must be positive");
+  if (batch_size == 0 || num_dst_rows == 0 || entry_size == 0) return KVC_OK;
+  if (!src_cache || !dst || !block_table || !cu_seq_lens)
+    return fail(KVC_ERR_INVALID_ARG, "src_cache, dst, block_table and cu_seq_lens must be non-NULL");
+  if (num_dst_rows > 0x7FFFFFFFll) return fail(KVC_ERR_INVALID_ARG, "dst has too many rows (cu_seq_lens is int32)");
+
+  const int64_t row_bytes = entry_size * elem_size;
+  const void* ptrs[2] = {src_cache, dst};
+  const int64_t strides[3] = {cache_block_stride * elem_size, cache_entry_stride * elem_size,
+                              dst_entry_stride * elem_size};
+  const int piece = pick_vec(16, row_bytes, 1, ptrs, 2, strides, 3);  // bytes per thread, power of two <= 16
+  const int64_t chunks = row_bytes / piece;
+  if (chunks >= (1ll << 30) || num_dst_rows * chunks >= (1ll << 31) - kGatherThreads)
+    return fail(KVC_ERR_INVALID_ARG, "gather_cache: dst too large for one call");
+
+  GatherParams p{};
+  p.src_cache = src_cache;
+  p.dst = dst;
+  p.block_table = block_table;
+  p.cu_seq_lens = cu_seq_lens;
+  p.seq_starts = seq_starts;
+  p.block_table_stride = block_table_stride;
+  p.cache_block_stride = cache_block_stride * elem_size;
+  p.cache_entry_stride = cache_entry_stride * elem_size;
+  p.dst_entry_stride = dst_entry_stride * elem_size;
+  p.batch_size = static_cast<int32_t>(batch_size);
+  p.block_size = static_cast<int32_t>(block_size);
+  p.bs_shift = pow2_shift(block_size);
+  p.n_items = static_cast<uint32_t>(num_dst_rows * chunks);
+  p.chunks_per_row = static_cast<uint32_t>(chunks);
+  p.div_chunks_per_row = FastDiv(p.chunks_per_row);
+  p.div_block_size = FastDiv(static_cast<uint32_t>(block_size));
+  const dim3 grid((p.n_items + kGatherThreads - 1) / kGatherThreads);
+  cudaError_t e;
+  switch (piece) {
+    case 16: e = launch_pdl(gather_cache_kernel<16>, grid, kGatherThreads, p, st); break;
+    case 8: e = launch_pdl(gather_cache_kernel<8>, grid, kGatherThreads, p, st); break;
+    case 4: e = launch_pdl(gather_cache_kernel<4>, grid, kGatherThreads, p, st); break;
+    case 2: e = launch_pdl(gather_cache_kernel<2>, grid, kGatherThreads, p, st); break;
+    default: e = launch_pdl(gather_cache_kernel<1>, grid, kGatherThreads, p, st); break;
+  }
+  if (e != cudaSuccess) return fail(KVC_ERR_CUDA, std::string("gather_cache launch failed: ") + cudaGetErrorString(e));
+  return KVC_OK;
+}
+
 // ---------------------------------------------------------------------------------------------
 // device staging for host-resident inputs (one set per device, grown on demand)
 // ---------------------------------------------------------------------------------------------
@@ -896,6 +1144,24 @@ int kvc_reshape_and_cache(const void* key, const void* value, void* key_cache, v
   return paged_impl(key, value, key_cache, value_cache, slot_mapping, num_tokens, num_heads, head_size,
                     block_size, x, key_stride_t, key_stride_h, value_stride_t, value_stride_h, in_dtype,
                     kv_dtype, k_scale, v_scale, static_cast<cudaStream_t>(stream));
+}
+
+int kvc_concat_and_cache_mla(const void* kv_c, const void* k_pe, void* kv_cache, const int64_t* slot_mapping,
+                             int64_t num_tokens, int64_t kv_lora_rank, int64_t pe_dim, int64_t block_size,
+                             int64_t kv_c_stride, int64_t k_pe_stride, int64_t block_stride, int64_t entry_stride,
+                             int in_dtype, int kv_dtype, const float* scale, void* stream) {
+  return mla_impl(kv_c, k_pe, kv_cache, slot_mapping, num_tokens, kv_lora_rank, pe_dim, block_size, kv_c_stride,
+                  k_pe_stride, block_stride, entry_stride, in_dtype, kv_dtype, scale,
+                  static_cast<cudaStream_t>(stream));
+}
+
+int kvc_gather_cache(const void* src_cache, void* dst, const int32_t* block_table, const int32_t* cu_seq_lens,
+                     const int32_t* seq_starts, int64_t batch_size, int64_t num_dst_rows, int64_t block_size,
+                     int64_t entry_size, int64_t elem_size, int64_t block_table_stride, int64_t cache_block_stride,
+                     int64_t cache_entry_stride, int64_t dst_entry_stride, void* stream) {
+  return gather_impl(src_cache, dst, block_table, cu_seq_lens, seq_starts, batch_size, num_dst_rows, block_size,
+                     entry_size, elem_size, block_table_stride, cache_block_stride, cache_entry_stride,
+                     dst_entry_stride, static_cast<cudaStream_t>(stream));
 }
 
 int kvc_reshape_and_cache_flash_host(const void* host_key, const void* host_value, void* key_cache,

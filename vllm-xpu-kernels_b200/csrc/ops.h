@@ -4,6 +4,7 @@
 #pragma once
 #include <ATen/core/Tensor.h>
 
+#include <optional>
 #include <string>
 
 // Paged layout: key_cache [num_blocks, H, D/x, block_size, x], value_cache [num_blocks, H, D, block_size].
@@ -15,3 +16,11 @@ void reshape_and_cache(at::Tensor& key, at::Tensor& value, at::Tensor& key_cache
 void reshape_and_cache_flash(at::Tensor& key, at::Tensor& value, at::Tensor& key_cache,
                              at::Tensor& value_cache, at::Tensor& slot_mapping,
                              const std::string& kv_cache_dtype, at::Tensor& k_scale, at::Tensor& v_scale);
+
+// MLA: cache entry = kv_c row followed by k_pe row; kv_cache [num_blocks, block_size, kv_lora_rank + pe_dim].
+void concat_and_cache_mla(at::Tensor& kv_c, at::Tensor& k_pe, at::Tensor& kv_cache, at::Tensor& slot_mapping,
+                          const std::string& kv_cache_dtype, at::Tensor& scale);
+
+// Inverse direction: paged entries -> dense [tot_tokens, entry...] through block_table / cu_seq_lens.
+void gather_cache(at::Tensor const& src_cache, at::Tensor const& dst, at::Tensor const& block_table,
+                  at::Tensor const& cu_seq_lens, int64_t batch_size, std::optional<at::Tensor> seq_starts);

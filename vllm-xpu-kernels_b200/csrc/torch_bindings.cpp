@@ -1,9 +1,10 @@
 // Registers the KV-cache write ops under torch.ops._C_cache_ops.
 //
 // Schema strings are the public interface vLLM's attention backends call and are kept
-// character-compatible with the reference's csrc/torch_bindings.cpp:107-112 and :116-122;
+// character-compatible with the reference's csrc/torch_bindings.cpp:107-112, :116-122, :127-133
+// and :136-139;
 // the implementations are bound for CUDA tensors.  Ops returning () need no meta kernel.
-// Only the cache-write ops of the reference's `_C` module are provided by this library.
+// Only the `_C_cache_ops` namespace of the reference's `_C` module is provided by this library.
 #include <torch/library.h>
 
 #include "core/registration.h"
@@ -27,11 +28,22 @@ KVC_TORCH_LIBRARY(KVC_PP_CAT(TORCH_EXTENSION_NAME, _cache_ops), m) {
       "                        Tensor slot_mapping,"
       "                        str kv_cache_dtype,"
       "                        Tensor k_scale, Tensor v_scale) -> ()");
+  m.def(
+      "concat_and_cache_mla(Tensor kv_c, Tensor k_pe,"
+      "                     Tensor! kv_cache,"
+      "                     Tensor slot_mapping,"
+      "                     str kv_cache_dtype,"
+      "                     Tensor scale) -> ()");
+  m.def(
+      "gather_cache(Tensor src_cache, Tensor! dst, Tensor block_table, "
+      "Tensor cu_seq_lens, int batch_size, Tensor? seq_starts) -> ()");
 }
 
 KVC_TORCH_LIBRARY_IMPL(KVC_PP_CAT(TORCH_EXTENSION_NAME, _cache_ops), CUDA, m) {
   m.impl("reshape_and_cache", &reshape_and_cache);
   m.impl("reshape_and_cache_flash", &reshape_and_cache_flash);
+  m.impl("concat_and_cache_mla", &concat_and_cache_mla);
+  m.impl("gather_cache", &gather_cache);
 }
 
 KVC_DEFINE_EMPTY_PYMODULE(TORCH_EXTENSION_NAME)

@@ -25,6 +25,8 @@ SYMBOLS = (
     "kvc_parse_kv_cache_dtype",
     "kvc_reshape_and_cache_flash",
     "kvc_reshape_and_cache",
+    "kvc_concat_and_cache_mla",
+    "kvc_gather_cache",
     "kvc_reshape_and_cache_flash_host",
     "kvc_reshape_and_cache_flash_host_noalloc",
     "kvc_release_staging",
@@ -52,6 +54,10 @@ def lib() -> ctypes.CDLL:
         L.kvc_reshape_and_cache_flash.argtypes = [vp] * 5 + [i64] * 11 + [ci, ci, vp, vp, vp]
         L.kvc_reshape_and_cache.restype = ci
         L.kvc_reshape_and_cache.argtypes = [vp] * 5 + [i64] * 9 + [ci, ci, vp, vp, vp]
+        L.kvc_concat_and_cache_mla.restype = ci
+        L.kvc_concat_and_cache_mla.argtypes = [vp] * 4 + [i64] * 8 + [ci, ci, vp, vp]
+        L.kvc_gather_cache.restype = ci
+        L.kvc_gather_cache.argtypes = [vp] * 5 + [i64] * 9 + [vp]
         L.kvc_reshape_and_cache_flash_host.restype = ci
         L.kvc_reshape_and_cache_flash_host.argtypes = [vp] * 5 + [i64] * 9 + [ci, ci, vp, vp, vp]
         L.kvc_reshape_and_cache_flash_host_noalloc.restype = ci
@@ -120,6 +126,27 @@ def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, kv_cache
         key_cache.shape[3], key_cache.shape[4],
         key.stride(0), key.stride(1), value.stride(0), value.stride(1),
         _in_dtype(key), kv, _scale_ptr(k_scale, kv), _scale_ptr(v_scale, kv), _stream(stream)))
+
+
+def concat_and_cache_mla(kv_c, k_pe, kv_cache, slot_mapping, kv_cache_dtype: str, scale=None, stream=None) -> None:
+    """``kvc_concat_and_cache_mla`` on device tensors (kv_cache [num_blocks, block_size, R + P])."""
+    kv = parse_kv_cache_dtype(kv_cache_dtype)
+    _check(lib().kvc_concat_and_cache_mla(
+        kv_c.data_ptr(), k_pe.data_ptr(), kv_cache.data_ptr(), slot_mapping.data_ptr(), slot_mapping.shape[0],
+        kv_c.shape[1], k_pe.shape[1], kv_cache.shape[1], kv_c.stride(0), k_pe.stride(0),
+        kv_cache.stride(0), kv_cache.stride(1), _in_dtype(kv_c), kv, _scale_ptr(scale, kv), _stream(stream)))
+
+
+def gather_cache(src_cache, dst, block_table, cu_seq_lens, batch_size: int, seq_starts=None, stream=None) -> None:
+    """``kvc_gather_cache`` on device tensors (src_cache [num_blocks, block_size, entry], dst [rows, entry])."""
+    entry = 1
+    for d in src_cache.shape[2:]:
+        entry *= d
+    _check(lib().kvc_gather_cache(
+        src_cache.data_ptr(), dst.data_ptr(), block_table.data_ptr(), cu_seq_lens.data_ptr(),
+        0 if seq_starts is None else seq_starts.data_ptr(), batch_size, dst.shape[0], src_cache.shape[1], entry,
+        src_cache.element_size(), block_table.stride(0), src_cache.stride(0), src_cache.stride(1), dst.stride(0),
+        _stream(stream)))
 
 
 def reshape_and_cache_flash_host(host_key, host_value, key_cache, value_cache, host_slot_mapping,
