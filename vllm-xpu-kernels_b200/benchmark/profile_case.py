@@ -24,7 +24,8 @@ from vllm_xpu_kernels import cabi  # noqa: E402
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--layout", choices=["flash", "paged"], default="flash")
+    ap.add_argument("--layout", choices=["flash", "paged", "mla", "gather"], default="flash",
+                    help="mla: concat_and_cache_mla (512 + 64 wide entries); gather: gather_cache of such entries")
     ap.add_argument("--kv", choices=["auto", "fp8", "fp8_e5m2"], default="fp8")
     ap.add_argument("--dtype", choices=["bfloat16", "half", "float"], default="bfloat16")
     ap.add_argument("--tokens", type=int, default=32768)
@@ -42,6 +43,9 @@ def main() -> None:
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     torch.manual_seed(0)
+    if ns.layout in ("mla", "gather"):
+        run_mla_or_gather(ns, dev)
+        return
     dt = {"bfloat16": torch.bfloat16, "half": torch.float16, "float": torch.float32}[ns.dtype]
     T, H, D, bs = ns.tokens, ns.heads, ns.head_size, ns.block_size
     nb = 2 * ((T + bs - 1) // bs)
@@ -92,6 +96,53 @@ def main() -> None:
     print(f"layout={ns.layout} kv={ns.kv} dtype={ns.dtype} T={T} H={H} D={D} bs={bs} slots={ns.slots} "
           f"algorithmic_bytes={alg_bytes} launches={ns.launches} event_us={['%.1f' % t for t in times]} "
           f"best_GBps={alg_bytes / best / 1e3:.0f}")
+
+
+def run_mla_or_gather(ns, dev) -> None:
+    dt = {"bfloat16": torch.bfloat16, "half": torch.float16, "float": torch.float32}[ns.dtype]
+    T, bs, R, P = ns.tokens, ns.block_size, 512, 64
+    nb = 2 * ((T + bs - 1) // bs)
+    es_in = torch.empty((), dtype=dt).element_size()
+    es_out = 1 if ns.kv != "auto" else es_in
+    cache = torch.zeros(nb, bs, R + P, dtype=dt if ns.kv == "auto" else torch.uint8, device=dev)
+    scale = torch.tensor(0.02, device=dev)
+    sets = []
+    for b in range(ns.nbuf):
+        perm = torch.randperm(nb, device=dev)[:(T + bs - 1) // bs]
+        if ns.layout == "mla":
+            kv_c = torch.randn(T, R, device=dev).to(dt)
+            k_pe = torch.randn(T, P, device=dev).to(dt)
+            slots = (perm[:, None] * bs + torch.arange(bs, device=dev)[None, :]).flatten()[:T].contiguous()
+            if ns.slots == "random":
+                slots = torch.randperm(nb * bs, device=dev)[:T]
+            sets.append((kv_c, k_pe, slots))
+        else:
+            batch = 64
+            per = T // batch
+            cu = torch.arange(batch + 1, device=dev, dtype=torch.int32) * per
+            table = perm[:batch * ((per + bs - 1) // bs)].view(batch, -1).to(torch.int32).contiguous()
+            dst = torch.zeros(batch * per, R + P, dtype=cache.dtype, device=dev)
+            sets.append((dst, table, cu, batch))
+    if ns.layout == "gather":
+        cache.view(torch.uint8).random_(0, 120)
+    alg = T * (R + P) * (es_in + es_out) + 8 * T if ns.layout == "mla" else 2 * sets[0][0].numel() * es_out
+    evs = []
+    for i in range(ns.launches):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        if ns.layout == "mla":
+            kv_c, k_pe, slots = sets[i % ns.nbuf]
+            cabi.concat_and_cache_mla(kv_c, k_pe, cache, slots, ns.kv, scale)
+        else:
+            dst, table, cu, batch = sets[i % ns.nbuf]
+            cabi.gather_cache(cache, dst, table, cu, batch)
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    times = [a.elapsed_time(b) * 1e3 for a, b in evs]
+    best = min(times[1:]) if len(times) > 1 else times[0]
+    print(f"layout={ns.layout} kv={ns.kv} dtype={ns.dtype} T={T} entry=576 bs={bs} algorithmic_bytes={alg} "
+          f"launches={ns.launches} event_us={['%.1f' % t for t in times]} best_GBps={alg / best / 1e3:.0f}")
 
 
 if __name__ == "__main__":

@@ -596,51 +596,86 @@ struct GatherParams {
   const int32_t* seq_starts;  // may be null
   int64_t block_table_stride;
   int64_t cache_block_stride, cache_entry_stride, dst_entry_stride;  // BYTES
+  int64_t num_rows;  // rows of dst
   int32_t batch_size;
   int32_t block_size;
   int bs_shift;
-  uint32_t n_items;  // dst_rows * chunks_per_row
+  uint32_t n_warps;  // ceil(num_rows / kGatherRowsPerWarp)
   uint32_t chunks_per_row;
-  FastDiv div_chunks_per_row, div_block_size;
+  FastDiv div_block_size;
 };
 
 constexpr int kGatherThreads = 256;
+constexpr int kGatherRowsPerWarp = 8;
 
-// One thread copies one BYTES-wide piece of one destination row.  The row's sequence is found
-// by bisection over cu_seq_lens (batch_size + 1 ints, cache resident); rows at or beyond
-// cu_seq_lens[batch_size] are left alone, so the grid can be sized from dst's row count,
-// which the host knows, instead of from the token total, which lives on the device.
+// A warp copies kGatherRowsPerWarp consecutive destination rows.  Lanes 0..7 each locate one
+// row's source entry (bisection over cu_seq_lens: batch_size + 1 ints, cache resident), all
+// at once, so the search costs one pass per eight rows; the addresses are handed round with
+// shuffles and every lane then copies BYTES-wide pieces lane, lane + 32, ... of each row, two
+// rows at a time.  Rows at or beyond cu_seq_lens[batch_size] have no source and are left
+// alone, so the grid can be sized from dst's row count, which the host knows, instead of
+// from the token total, which lives on the device.
 template <int BYTES>
 __global__ void __launch_bounds__(kGatherThreads) gather_cache_kernel(const GatherParams p) {
-  const uint32_t item = blockIdx.x * kGatherThreads + threadIdx.x;
-  if (item >= p.n_items) return;
-  const uint32_t row = p.div_chunks_per_row.div(item);
-  const uint32_t chunk = item - row * p.chunks_per_row;
+  const uint32_t warp = blockIdx.x * (kGatherThreads / 32) + (threadIdx.x >> 5);
+  if (warp >= p.n_warps) return;
+  const uint32_t lane = threadIdx.x & 31u;
+  const int64_t row0 = static_cast<int64_t>(warp) * kGatherRowsPerWarp;
   pdl_prologue();
 
-  // largest b in [0, batch_size) with cu[b] <= row, provided row < cu[batch_size]
-  const int32_t r = static_cast<int32_t>(row);
-  if (r >= __ldg(p.cu_seq_lens + p.batch_size)) return;
-  int lo = 0, hi = p.batch_size;  // invariant: cu[lo] <= r < cu[hi]
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (__ldg(p.cu_seq_lens + mid) <= r) lo = mid; else hi = mid;
+  unsigned long long src_addr = 0;  // 0 = this row has no source
+  if (lane < kGatherRowsPerWarp && row0 + lane < p.num_rows) {
+    const int32_t r = static_cast<int32_t>(row0 + lane);
+    if (r < __ldg(p.cu_seq_lens + p.batch_size)) {
+      int lo = 0, hi = p.batch_size;  // invariant: cu[lo] <= r < cu[hi]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (__ldg(p.cu_seq_lens + mid) <= r) lo = mid; else hi = mid;
+      }
+      const int32_t j = r - __ldg(p.cu_seq_lens + lo);
+      if (j >= 0) {  // negative only if cu_seq_lens does not start at <= r: nothing sensible to copy
+        const uint32_t jb = p.bs_shift >= 0 ? (static_cast<uint32_t>(j) >> p.bs_shift) : p.div_block_size.div(j);
+        const uint32_t off = static_cast<uint32_t>(j) - jb * static_cast<uint32_t>(p.block_size);
+        int32_t first = 0;
+        if (p.seq_starts != nullptr) first = __ldg(p.seq_starts + lo) / p.block_size;
+        const int64_t block = __ldg(p.block_table + lo * p.block_table_stride + first + jb);
+        src_addr = reinterpret_cast<unsigned long long>(static_cast<const char*>(p.src_cache) +
+                                                        block * p.cache_block_stride +
+                                                        static_cast<int64_t>(off) * p.cache_entry_stride);
+      }
+    }
   }
-  const int32_t j = r - __ldg(p.cu_seq_lens + lo);
-  if (j < 0) return;  // cu_seq_lens not monotone: nothing sensible to copy
-  const uint32_t jb = p.bs_shift >= 0 ? (static_cast<uint32_t>(j) >> p.bs_shift) : p.div_block_size.div(j);
-  const uint32_t off = static_cast<uint32_t>(j) - jb * static_cast<uint32_t>(p.block_size);
-  int32_t first = 0;
-  if (p.seq_starts != nullptr) first = __ldg(p.seq_starts + lo) / p.block_size;
-  const int64_t block = __ldg(p.block_table + lo * p.block_table_stride + first + jb);
 
-  const char* src = static_cast<const char*>(p.src_cache) + block * p.cache_block_stride +
-                    static_cast<int64_t>(off) * p.cache_entry_stride + static_cast<int64_t>(chunk) * BYTES;
-  char* dst = static_cast<char*>(p.dst) + static_cast<int64_t>(row) * p.dst_entry_stride +
-              static_cast<int64_t>(chunk) * BYTES;
-  Chunk<BYTES> c;
-  load_chunk(c, src, false);
-  store_chunk(dst, c, false);
+  char* drow = static_cast<char*>(p.dst) + row0 * p.dst_entry_stride;
+#pragma unroll
+  for (int k = 0; k < kGatherRowsPerWarp; k += 2) {
+    const char* s0 = reinterpret_cast<const char*>(__shfl_sync(0xFFFFFFFFu, src_addr, k));
+    const char* s1 = reinterpret_cast<const char*>(__shfl_sync(0xFFFFFFFFu, src_addr, k + 1));
+    char* d0 = drow + k * p.dst_entry_stride;
+    char* d1 = d0 + p.dst_entry_stride;
+    // three pieces of each of the two rows per pass: up to six loads in flight per lane
+    for (uint32_t c0 = lane; c0 < p.chunks_per_row; c0 += 96) {
+      Chunk<BYTES> x0[3], x1[3];
+#pragma unroll
+      for (int u = 0; u < 3; ++u) {
+        const uint32_t c = c0 + 32 * u;
+        if (c < p.chunks_per_row) {
+          const int64_t at = static_cast<int64_t>(c) * BYTES;
+          if (s0) load_chunk(x0[u], s0 + at, false);
+          if (s1) load_chunk(x1[u], s1 + at, false);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 3; ++u) {
+        const uint32_t c = c0 + 32 * u;
+        if (c < p.chunks_per_row) {
+          const int64_t at = static_cast<int64_t>(c) * BYTES;
+          if (s0) store_chunk(d0 + at, x0[u], false);
+          if (s1) store_chunk(d1 + at, x1[u], false);
+        }
+      }
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1010,8 +1045,8 @@ static int gather_impl(const void* src_cache, void* dst, const int32_t* block_ta
                               dst_entry_stride * elem_size};
   const int piece = pick_vec(16, row_bytes, 1, ptrs, 2, strides, 3);  // bytes per thread, power of two <= 16
   const int64_t chunks = row_bytes / piece;
-  if (chunks >= (1ll << 30) || num_dst_rows * chunks >= (1ll << 31) - kGatherThreads)
-    return fail(KVC_ERR_INVALID_ARG, "gather_cache: dst too large for one call");
+  const int64_t n_warps = (num_dst_rows + kGatherRowsPerWarp - 1) / kGatherRowsPerWarp;
+  if (chunks >= (1ll << 31)) return fail(KVC_ERR_INVALID_ARG, "gather_cache: entries too large");
 
   GatherParams p{};
   p.src_cache = src_cache;
@@ -1026,11 +1061,12 @@ static int gather_impl(const void* src_cache, void* dst, const int32_t* block_ta
   p.batch_size = static_cast<int32_t>(batch_size);
   p.block_size = static_cast<int32_t>(block_size);
   p.bs_shift = pow2_shift(block_size);
-  p.n_items = static_cast<uint32_t>(num_dst_rows * chunks);
+  p.num_rows = num_dst_rows;
+  p.n_warps = static_cast<uint32_t>(n_warps);
   p.chunks_per_row = static_cast<uint32_t>(chunks);
-  p.div_chunks_per_row = FastDiv(p.chunks_per_row);
   p.div_block_size = FastDiv(static_cast<uint32_t>(block_size));
-  const dim3 grid((p.n_items + kGatherThreads - 1) / kGatherThreads);
+  constexpr int wpb = kGatherThreads / 32;
+  const dim3 grid(static_cast<unsigned>((n_warps + wpb - 1) / wpb));
   cudaError_t e;
   switch (piece) {
     case 16: e = launch_pdl(gather_cache_kernel<16>, grid, kGatherThreads, p, st); break;
