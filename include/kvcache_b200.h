@@ -216,6 +216,33 @@ KVC_API int kvc_reshape_and_cache_flash_host_noalloc(
 KVC_API int kvc_release_staging(void);
 
 /*
+ * fp8 activation quantisation (the reference's csrc/quantization/fp8/fp8_quant.cpp;
+ * schemas csrc/torch_bindings.cpp:67-88).  Element rule, from
+ * csrc/quantization/fp8/quant_utils.h:80-91 with an inverted scale:
+ *     byte = rne_fp8( fmax(-M, fmin(float(x) * (1.0f / scale), M)) ),  M = 448 | 57344.
+ * That is a product with a rounded reciprocal -- the rule the reference's tests pin
+ * (tests/test_fp8_quant.py:20-38) -- not the correctly rounded division of the cache ops.
+ * in_dtype: KVC_IN_*; fp8_dtype: KVC_KV_FP8_E4M3 or KVC_KV_FP8_E5M2.  Inputs and
+ * outputs are contiguous.
+ *
+ * kvc_static_scaled_fp8_quant            fp8_quant.cpp:135-164: `scale` is given (device fp32).
+ * kvc_dynamic_scaled_fp8_quant           fp8_quant.cpp:166-203: first *scale = max(*scale,
+ *                                        absmax(x) / M) (atomic; the caller zero-initialises
+ *                                        *scale, as the reference's wrapper does), then as static.
+ * kvc_dynamic_per_token_scaled_fp8_quant fp8_quant.cpp:205-250: per row of hidden_size elements,
+ *                                        scales[t] = max(min(absmax_t, *scale_ub) / M, 1/(512 M))
+ *                                        (scale_ub may be NULL), then the row is quantised with it.
+ */
+KVC_API int kvc_static_scaled_fp8_quant(void* out, const void* input, const float* scale, int64_t num_elems,
+                                        int in_dtype, int fp8_dtype, void* stream);
+KVC_API int kvc_dynamic_scaled_fp8_quant(void* out, const void* input, float* scale, int64_t num_elems,
+                                         int in_dtype, int fp8_dtype, void* stream);
+KVC_API int kvc_dynamic_per_token_scaled_fp8_quant(void* out, const void* input, float* scales,
+                                                   const float* scale_ub, int64_t num_tokens,
+                                                   int64_t hidden_size, int in_dtype, int fp8_dtype,
+                                                   void* stream);
+
+/*
  * Debug aid the reference lacks: counts entries of slot_mapping that are
  * >= num_slots (negative entries are legal padding and not counted) into
  * *bad_count, a DEVICE int64 the caller owns; the kernel overwrites it.

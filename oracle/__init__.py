@@ -49,6 +49,12 @@ def lib() -> ctypes.CDLL:
         L.orc_concat_and_cache_mla.argtypes = [vp, vp, vp, vp] + [i64] * 8 + [ci, ci, f32, i64]
         L.orc_gather_cache.restype = None
         L.orc_gather_cache.argtypes = [vp] * 5 + [i64] * 8
+        L.orc_static_scaled_fp8_quant.restype = None
+        L.orc_static_scaled_fp8_quant.argtypes = [vp, vp, i64, ci, ci, f32]
+        L.orc_absmax_scale.restype = f32
+        L.orc_absmax_scale.argtypes = [vp, i64, ci, ci]
+        L.orc_per_token_fp8_quant.restype = None
+        L.orc_per_token_fp8_quant.argtypes = [vp, vp, vp, i64, i64, ci, ci, vp]
         L.orc_convert_table.restype = None
         L.orc_convert_table.argtypes = [ci, ci, f32, vp]
         L.orc_convert_f32.restype = None
@@ -186,6 +192,32 @@ def gather_cache(src_cache, dst, block_table, cu_seq_lens, batch_size: int, seq_
         src_cache.ctypes.data, dst.ctypes.data, block_table.ctypes.data, cu_seq_lens.ctypes.data,
         None if ss is None else ss.ctypes.data, batch_size, dst.shape[0], src_cache.shape[1], entry_bytes,
         block_table.shape[1], src_cache.strides[0], src_cache.strides[1], dst.strides[0])
+
+
+def static_scaled_fp8_quant(x: np.ndarray, scale: float, in_dtype: str, fp8: str) -> np.ndarray:
+    """fp8 bytes of ``clamp(x * (1/scale))`` for a contiguous array (the reference's static quant)."""
+    x = np.ascontiguousarray(x)
+    out = np.empty(x.shape, dtype=np.uint8)
+    lib().orc_static_scaled_fp8_quant(out.ctypes.data, x.ctypes.data, x.size, IN_DTYPES[in_dtype], KV_DTYPES[fp8],
+                                      float(scale))
+    return out
+
+
+def absmax_scale(x: np.ndarray, in_dtype: str, fp8: str) -> np.float32:
+    x = np.ascontiguousarray(x)
+    return np.float32(lib().orc_absmax_scale(x.ctypes.data, x.size, IN_DTYPES[in_dtype], KV_DTYPES[fp8]))
+
+
+def per_token_fp8_quant(x: np.ndarray, in_dtype: str, fp8: str, scale_ub=None):
+    """(bytes, scales[T, 1]) of the reference's dynamic per-token quant for x [T, hidden]."""
+    x = np.ascontiguousarray(x)
+    T, hidden = x.shape
+    out = np.empty((T, hidden), dtype=np.uint8)
+    scales = np.empty((T, 1), dtype=np.float32)
+    ub = None if scale_ub is None else ctypes.byref(ctypes.c_float(float(scale_ub)))
+    lib().orc_per_token_fp8_quant(out.ctypes.data, scales.ctypes.data, x.ctypes.data, T, hidden, IN_DTYPES[in_dtype],
+                                  KV_DTYPES[fp8], ctypes.cast(ub, ctypes.c_void_p) if ub is not None else None)
+    return out, scales
 
 
 def convert_table(in_dtype: str, kv_cache_dtype: str, scale: float) -> np.ndarray:

@@ -16,6 +16,10 @@
  *                                tests/test_cache.py:370-375 (torch loop)
  *   orc_gather_cache             csrc/cache.cpp:305-366 (device body), :576-638 (host),
  *                                tests/test_cache.py:460-477 (torch loop)
+ *   orc_static_scaled_fp8_quant, orc_absmax_scale, orc_per_token_fp8_quant
+ *                                csrc/quantization/fp8/fp8_quant.cpp:15-45, :47-131,
+ *                                fp8_quant.h:56-102; element rule quant_utils.h:80-91
+ *                                (multiply by 1.0f/scale, clamp, cast)
  *   element conversion           csrc/quantization/fp8/quant_utils.h:62-78
  *                                (auto: bit copy; fp8: float(src) / scale,
  *                                then cast)
@@ -276,6 +280,46 @@ void orc_gather_cache(const void* src_cache, void* dst, const int32_t* block_tab
              (const char*)src_cache + blk * cache_block_stride + (j % block_size) * cache_entry_stride,
              (size_t)entry_bytes);
     }
+  }
+}
+
+/*
+ * fp8 activation quantisation.  quant_utils.h:80-91 with an inverted scale:
+ * r = fmax(-M, fmin(x * inv, M)), then the fp8 cast; inv = 1.0f / scale in fp32
+ * (fp8_quant.cpp:34).  fminf/fmaxf return the non-NaN operand like sycl::fmin/fmax.
+ */
+static inline float fp8_max_of(int kv) { return kv == ORC_KV_E5M2 ? 57344.0f : 448.0f; }
+
+static inline uint8_t quant_elem(float x, float inv, int kv) {
+  const float m = fp8_max_of(kv);
+  const float r = fmaxf(-m, fminf(x * inv, m));
+  return kv == ORC_KV_E5M2 ? orc_f32_to_e5m2(r) : orc_f32_to_e4m3(r);
+}
+
+void orc_static_scaled_fp8_quant(uint8_t* out, const void* in, int64_t n, int in_dt, int kv, float scale) {
+  const float inv = 1.0f / scale;
+  for (int64_t i = 0; i < n; ++i) out[i] = quant_elem(load_as_f32(in, i, in_dt), inv, kv);
+}
+
+/* fp8_quant.h:56-102: max over |x| (NaN never wins a max), divided by M */
+float orc_absmax_scale(const void* in, int64_t n, int in_dt, int kv) {
+  float m = 0.0f;
+  for (int64_t i = 0; i < n; ++i) m = fmaxf(m, fabsf(load_as_f32(in, i, in_dt)));
+  return m / fp8_max_of(kv);
+}
+
+/* fp8_quant.cpp:70-129: scale_t = max(min(absmax_t, ub) / M, 1 / (M * 512)) */
+void orc_per_token_fp8_quant(uint8_t* out, float* scales, const void* in, int64_t tokens, int64_t hidden,
+                             int in_dt, int kv, const float* scale_ub) {
+  const float m = fp8_max_of(kv);
+  for (int64_t t = 0; t < tokens; ++t) {
+    float a = 0.0f;
+    for (int64_t i = 0; i < hidden; ++i) a = fmaxf(a, fabsf(load_as_f32(in, t * hidden + i, in_dt)));
+    if (scale_ub) a = fminf(a, *scale_ub);
+    const float s = fmaxf(a / m, 1.0f / (m * 512.0f));
+    scales[t] = s;
+    const float inv = 1.0f / s;
+    for (int64_t i = 0; i < hidden; ++i) out[t * hidden + i] = quant_elem(load_as_f32(in, t * hidden + i, in_dt), inv, kv);
   }
 }
 

@@ -167,6 +167,32 @@ def make_gather_case(ru, dtype: str, entry: int, bs: int, nb: int, batch: int, m
     return out
 
 
+def make_quant_case(ru, dtype: str, fp8: str, T: int, hidden: int, seed: int, with_ub: bool) -> dict:
+    """The torch recipes of tests/test_fp8_quant.py:20-75 of the reference, run on the CPU:
+    dynamic per-tensor (out = cast(clamp(x * (1/scale))), scale = absmax / fp8_max) and dynamic per-token
+    (scales = clamp(min(absmax_t, ub) / fp8_max, min = 1/(512 fp8_max)), out = cast(clamp(x / scales)))."""
+    tdt = DT[dtype]
+    fdt = torch.float8_e5m2 if fp8 == "fp8_e5m2" else torch.float8_e4m3fn
+    fi = torch.finfo(fdt)
+    ru.seed_everything(seed)
+    x = torch.rand(T, hidden, dtype=tdt) + 1e-6
+    fp8_max = torch.as_tensor(fi.max, dtype=torch.float32)
+    one = torch.as_tensor(1.0, dtype=torch.float32)
+    scale = x.abs().max().to(torch.float32) / fp8_max
+    out_tensor = (x.to(torch.float32) * (one / scale)).clamp(fi.min, fi.max).to(fdt)
+    tok_max = x.abs().max(dim=-1)[0].to(torch.float32)
+    ub = torch.mean(x).to(torch.float32) if with_ub else None
+    if ub is not None:
+        tok_max = tok_max.clamp(max=ub)
+    scales = (tok_max / fp8_max)[:, None].clamp(min=one / (fp8_max * 512.0))
+    out_token = (x.to(torch.float32) / scales).clamp(fi.min, fi.max).to(fdt)
+    d = dict(op="quant", dtype=dtype, fp8=fp8, x=bits(x), scale=np.float32(scale.item()), out_tensor=bits(out_tensor),
+             scales=scales.numpy(), out_token=bits(out_token))
+    if ub is not None:
+        d["scale_ub"] = np.float32(ub.item())
+    return d
+
+
 def make_tables() -> dict:
     """torch's e4m3 / e5m2 cast over every bf16 and fp16 bit pattern at a few scales."""
     out = {}
@@ -230,6 +256,13 @@ def main() -> None:
     extra.append(("gather_float_E576_bs16_nb16_B4", make_gather_case(ru, "float", 576, 16, 16, 4, 60, 0, False)))
     extra.append(("gather_bfloat16_E576_bs16_nb24_B6_starts", make_gather_case(ru, "bfloat16", 576, 16, 24, 6, 64, 1, True)))
     extra.append(("gather_half_E40_bs8_nb16_B5", make_gather_case(ru, "half", 40, 8, 16, 5, 30, 2, False)))
+    qi = 0
+    for dtype in ("half", "bfloat16", "float"):
+        for fp8 in ("fp8_e4m3", "fp8_e5m2"):
+            for T, hidden in ((7, 67), (5, 1024), (3, 1031)):
+                extra.append(("quant_%s_%s_T%d_h%d" % (dtype, fp8, T, hidden),
+                              make_quant_case(ru, dtype, fp8, T, hidden, qi, with_ub=bool(qi % 2))))
+                qi += 1
     for name, data in extra:
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **data)
         names.append(name)

@@ -20,7 +20,7 @@ def golden_files(kind: str = "kv") -> list[str]:
     """Fixture files of one kind: "kv" (flash_* and paged_*), "mla" or "gather"."""
     with open(os.path.join(GOLDEN_DIR, "MANIFEST.txt")) as f:
         names = [ln.strip() for ln in f if ln.strip() and not ln.startswith("#")]
-    prefixes = {"kv": ("flash_", "paged_"), "mla": ("mla_",), "gather": ("gather_",)}[kind]
+    prefixes = {"kv": ("flash_", "paged_"), "mla": ("mla_",), "gather": ("gather_",), "quant": ("quant_",)}[kind]
     return [n for n in names if n.startswith(prefixes)]
 
 
@@ -36,6 +36,20 @@ class MlaCase:
         cdt = cache_torch_dtype(self.dtype, self.kv_cache_dtype)
         self.cache_before = from_bits(z["cache_before"], cdt)
         self.cache_after = from_bits(z["cache_after"], cdt)
+
+
+class QuantCase:
+    def __init__(self, fname: str):
+        z = np.load(os.path.join(GOLDEN_DIR, fname))
+        self.dtype = TORCH_DT[str(z["dtype"])]
+        self.fp8 = str(z["fp8"])
+        self.fp8_dtype = torch.float8_e5m2 if self.fp8 == "fp8_e5m2" else torch.float8_e4m3fn
+        self.x = from_bits(z["x"], self.dtype)
+        self.scale = float(z["scale"])
+        self.out_tensor = torch.from_numpy(z["out_tensor"])
+        self.scales = torch.from_numpy(z["scales"])
+        self.out_token = torch.from_numpy(z["out_token"])
+        self.scale_ub = float(z["scale_ub"]) if "scale_ub" in z.files else None
 
 
 class GatherCase:
@@ -124,3 +138,18 @@ def fill_pattern_(t: torch.Tensor, seed: int) -> torch.Tensor:
     reps = (n + src.numel() - 1) // src.numel()
     flat.copy_(src.repeat(reps)[:n])
     return t
+
+
+OPCHECK_UTILS = ("test_schema", "test_autograd_registration", "test_faketensor", "test_aot_dispatch_dynamic")
+
+
+def opcheck(op, args, kwargs=None, test_utils=OPCHECK_UTILS):
+    """``torch.library.opcheck`` with ``torch.allclose`` replaced by a comparison in float64, so that
+    fp8 tensors can be compared (what the reference's tests/utils.py:21-67 does for the same reason)."""
+    import unittest.mock
+
+    def allclose64(a, b, rtol=1e-05, atol=1e-08, equal_nan=False):
+        return bool(torch.all(torch.isclose(a.double(), b.double(), rtol=rtol, atol=atol, equal_nan=equal_nan)).item())
+
+    with unittest.mock.patch("torch.allclose", new=allclose64):
+        return torch.library.opcheck(op, args, kwargs, test_utils=test_utils)

@@ -24,7 +24,7 @@ def declared_symbols() -> list[str]:
 
 def test_header_symbols_are_exported():
     names = declared_symbols()
-    assert set(names) == set(cabi.SYMBOLS) and len(names) >= 8
+    assert set(names) == set(cabi.SYMBOLS) and len(names) >= 14
     L = cabi.lib()
     for n in names:
         assert getattr(L, n) is not None
@@ -91,6 +91,13 @@ def test_torch_extension_registers_reference_schemas():
     }
     for name, sig in others.items():
         assert str(getattr(ops, name).default._schema) == str(torch._C.parse_schema(f"_C_cache_ops::{name}{sig}"))
+    quant = {
+        "static_scaled_fp8_quant": "(Tensor! result, Tensor input, Tensor scale) -> ()",
+        "dynamic_scaled_fp8_quant": "(Tensor! result, Tensor input, Tensor! scale) -> ()",
+        "dynamic_per_token_scaled_fp8_quant": "(Tensor! result, Tensor input, Tensor! scale, Tensor? scale_ub) -> ()",
+    }
+    for name, sig in quant.items():  # csrc/torch_bindings.cpp:67-88 of the reference
+        assert str(getattr(torch.ops._C, name).default._schema) == str(torch._C.parse_schema(f"_C::{name}{sig}"))
     from vllm_xpu_kernels import ops as wrappers
     for fn in ("reshape_and_cache", "reshape_and_cache_flash", "concat_and_cache_mla", "gather_cache"):
         assert callable(getattr(wrappers, fn))

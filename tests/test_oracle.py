@@ -42,6 +42,20 @@ def test_oracle_reproduces_reference_gather_fixture(fname):
     assert not bool(dst[total:].view(torch.uint8).any())
 
 
+@pytest.mark.parametrize("fname", H.golden_files("quant"))
+def test_oracle_reproduces_reference_quant_recipes(fname):
+    c = H.QuantCase(fname)
+    xn, name = torch_views.as_np(c.x), torch_views.ORC_IN[c.dtype]
+    # dynamic per-tensor: same arithmetic as the reference's recipe -> bit-exact, scale included
+    assert float(oracle.absmax_scale(xn, name, c.fp8)) == c.scale
+    assert np.array_equal(oracle.static_scaled_fp8_quant(xn, c.scale, name, c.fp8), c.out_tensor.numpy())
+    # dynamic per-token: the reference's recipe divides where its kernel multiplies by the reciprocal; its own
+    # test allows 0.5 % of the bytes to differ (tests/test_fp8_quant.py:199-203) and exact scales
+    got, scales = oracle.per_token_fp8_quant(xn, name, c.fp8, c.scale_ub)
+    assert np.array_equal(scales, c.scales.numpy())
+    assert (got != c.out_token.numpy()).mean() <= 0.005
+
+
 @pytest.mark.parametrize("in_dtype,tdt", [("bf16", torch.bfloat16), ("f16", torch.float16)])
 def test_conversion_tables_match_torch_cast(in_dtype, tdt):
     z = np.load(os.path.join(H.GOLDEN_DIR, "fp8_tables.npz"))

@@ -24,14 +24,16 @@ INCLUDE = os.path.join(REPO, "include")
 CUDA_LIB = os.path.join(PKG, "libkvcache_b200.so")
 TORCH_EXT = os.path.join(PKG, "_C.abi3.so")
 
-CUDA_SOURCES = [os.path.join(CSRC, "kvcache_kernels.cu")]
-EXT_SOURCES = [os.path.join(CSRC, "cache.cpp"), os.path.join(CSRC, "torch_bindings.cpp")]
+CUDA_SOURCES = [os.path.join(CSRC, "kvcache_kernels.cu"), os.path.join(CSRC, "fp8_quant_kernels.cu")]
+EXT_SOURCES = [os.path.join(CSRC, "cache.cpp"), os.path.join(CSRC, "fp8_quant.cpp"),
+               os.path.join(CSRC, "torch_bindings.cpp")]
 HEADERS = [
     os.path.join(INCLUDE, "kvcache_b200.h"),
     os.path.join(CSRC, "ops.h"),
     os.path.join(CSRC, "dispatch_utils.h"),
     os.path.join(CSRC, "core", "registration.h"),
 ]
+CUDA_HEADERS = [HEADERS[0], os.path.join(CSRC, "kvc_common.cuh")]
 
 
 def _stale(target: str, sources: list[str]) -> bool:
@@ -59,10 +61,10 @@ def _nvcc() -> str:
 
 
 def build_cuda_lib(force: bool = False, verbose: bool = False) -> str:
-    if force or _stale(CUDA_LIB, CUDA_SOURCES + HEADERS[:1]):
+    if force or _stale(CUDA_LIB, CUDA_SOURCES + CUDA_HEADERS):
         cmd = [
             _nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-            "-shared", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", INCLUDE, "-o", CUDA_LIB,
+            "-shared", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", INCLUDE, "-I", CSRC, "-o", CUDA_LIB,
         ]
         if verbose:
             cmd += ["-Xptxas", "-v"]

@@ -11,217 +11,22 @@
 // The reference plugin's counterparts are csrc/cache.cpp:13-189 (device code) and
 // :409-489 (host launchers); the per-element rule is
 // csrc/quantization/fp8/quant_utils.h:62-78.
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
-#include <cuda_runtime.h>
-
-#include <cstdint>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
-#include <string>
-#include <type_traits>
 
-#include "kvcache_b200.h"
+#include "kvc_common.cuh"
 
 namespace kvc {
 
 // ---------------------------------------------------------------------------------------------
-// error plumbing
+// error plumbing (declared in kvc_common.cuh)
 // ---------------------------------------------------------------------------------------------
 static thread_local std::string g_last_error;
 
-static int fail(int code, const std::string& msg) {
+int fail(int code, const std::string& msg) {
   g_last_error = msg;
   return code;
-}
-
-#define KVC_CUDA_TRY(expr)                                                                      \
-  do {                                                                                          \
-    cudaError_t _e = (expr);                                                                    \
-    if (_e != cudaSuccess)                                                                      \
-      return fail(KVC_ERR_CUDA, std::string(#expr " failed: ") + cudaGetErrorString(_e));       \
-  } while (0)
-
-// ---------------------------------------------------------------------------------------------
-// division of a 31-bit index by a launch constant: q = umulhi(n, mul) >> shr
-// ---------------------------------------------------------------------------------------------
-struct FastDiv {
-  uint32_t d, mul, shr;
-  __host__ FastDiv(uint32_t div = 1) : d(div), mul(0), shr(0) {
-    if (div > 1) {
-      uint32_t lg = 0;
-      while ((1ull << lg) < div) ++lg;  // ceil(log2 div)
-      const uint32_t p = 31 + lg;
-      mul = static_cast<uint32_t>(((1ull << p) + div - 1) / div);
-      shr = p - 32;
-    }
-  }
-  // exact for 0 <= n < 2^31
-  __device__ __forceinline__ uint32_t div(uint32_t n) const { return d == 1 ? n : (__umulhi(n, mul) >> shr); }
-};
-
-// ---------------------------------------------------------------------------------------------
-// programmatic dependent launch.  Every kernel here is launched with the
-// programmatic-stream-serialization attribute and starts with pdl_prologue(): it may be
-// scheduled while the previous kernel of the stream drains, then waits until that kernel
-// has completed and its writes are visible before it touches memory, and at once allows its
-// own successor to be scheduled the same way.  Without a programmatic predecessor the wait
-// returns immediately.  Launch latency and CTA scheduling thus overlap the predecessor's tail.
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void pdl_prologue() {
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-}
-
-// ---------------------------------------------------------------------------------------------
-// vector global memory access.  Loads are read-once streams: bypass L1 allocation.
-// ---------------------------------------------------------------------------------------------
-template <int BYTES>
-struct alignas(BYTES >= 16 ? 16 : BYTES) Chunk {
-  unsigned char b[BYTES];
-};
-
-// `wide`: the address is 32-byte aligned, so 32-byte pieces go out as single 256-bit loads
-// (one full sector per lane per instruction; two 16-byte loads 32 bytes apart would make
-// both instructions of a warp touch every sector).
-template <int BYTES>
-__device__ __forceinline__ void load_chunk(Chunk<BYTES>& c, const void* gptr, bool wide) {
-  if constexpr (BYTES >= 16) {
-    static_assert(BYTES % 16 == 0, "wide chunks are whole 16-byte vectors");
-    uint4* dst = reinterpret_cast<uint4*>(c.b);
-    if constexpr (BYTES % 32 == 0) {
-      if (wide) {
-#pragma unroll
-        for (int i = 0; i < BYTES / 32; ++i) {
-          uint4 lo, hi;
-          asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                       : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z),
-                         "=r"(hi.w)
-                       : "l"(static_cast<const char*>(gptr) + 32 * i));
-          dst[2 * i] = lo;
-          dst[2 * i + 1] = hi;
-        }
-        return;
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < BYTES / 16; ++i) {
-      uint4 v;
-      asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                   : "l"(static_cast<const char*>(gptr) + 16 * i));
-      dst[i] = v;
-    }
-  } else if constexpr (BYTES == 8) {
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(gptr));
-    *reinterpret_cast<uint2*>(c.b) = v;
-  } else if constexpr (BYTES == 4) {
-    uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(gptr));
-    *reinterpret_cast<uint32_t*>(c.b) = v;
-  } else if constexpr (BYTES == 2) {
-    uint16_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(gptr));
-    *reinterpret_cast<uint16_t*>(c.b) = v;
-  } else {
-    static_assert(BYTES == 1, "unsupported chunk size");
-    c.b[0] = *static_cast<const unsigned char*>(gptr);
-  }
-}
-
-// Stores PIECE bytes taken at byte offset `at` of the chunk; PIECE in {16,8,4,2,1}.
-template <int PIECE, int BYTES>
-__device__ __forceinline__ void store_piece(void* gptr, const Chunk<BYTES>& c, int at) {
-  if constexpr (PIECE == 16) {
-    *reinterpret_cast<uint4*>(gptr) = *reinterpret_cast<const uint4*>(c.b + at);
-  } else if constexpr (PIECE == 8) {
-    *reinterpret_cast<uint2*>(gptr) = *reinterpret_cast<const uint2*>(c.b + at);
-  } else if constexpr (PIECE == 4) {
-    *reinterpret_cast<uint32_t*>(gptr) = *reinterpret_cast<const uint32_t*>(c.b + at);
-  } else if constexpr (PIECE == 2) {
-    *reinterpret_cast<uint16_t*>(gptr) = *reinterpret_cast<const uint16_t*>(c.b + at);
-  } else {
-    *reinterpret_cast<unsigned char*>(gptr) = c.b[at];
-  }
-}
-
-// `wide`: the address is 32-byte aligned, so 32-byte pieces go out as single 256-bit stores
-// (a lane then fills a whole sector with one instruction instead of two half-sector writes).
-template <int BYTES>
-__device__ __forceinline__ void store_chunk(void* gptr, const Chunk<BYTES>& c, bool wide) {
-  if constexpr (BYTES % 32 == 0) {
-    if (wide) {
-      const uint4* src = reinterpret_cast<const uint4*>(c.b);
-#pragma unroll
-      for (int i = 0; i < BYTES / 32; ++i) {
-        const uint4 lo = src[2 * i], hi = src[2 * i + 1];
-        asm volatile("st.global.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(static_cast<char*>(gptr) + 32 * i),
-                     "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
-                     : "memory");
-      }
-      return;
-    }
-  }
-  constexpr int P = BYTES >= 16 ? 16 : BYTES;
-#pragma unroll
-  for (int i = 0; i < BYTES / P; ++i) store_piece<P>(static_cast<char*>(gptr) + P * i, c, P * i);
-}
-
-// ---------------------------------------------------------------------------------------------
-// element conversion
-// ---------------------------------------------------------------------------------------------
-template <typename Tin>
-__device__ __forceinline__ float to_f32(const unsigned char* p);
-template <>
-__device__ __forceinline__ float to_f32<float>(const unsigned char* p) {
-  return *reinterpret_cast<const float*>(p);
-}
-template <>
-__device__ __forceinline__ float to_f32<__half>(const unsigned char* p) {
-  return __half2float(*reinterpret_cast<const __half*>(p));
-}
-template <>
-__device__ __forceinline__ float to_f32<__nv_bfloat16>(const unsigned char* p) {
-  return __uint_as_float(static_cast<uint32_t>(*reinterpret_cast<const uint16_t*>(p)) << 16);
-}
-
-// The two 16-bit floats packed in `w` as fp32 (lo = bits 0..15).
-template <typename Tin>
-__device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi) {
-  if constexpr (std::is_same_v<Tin, __nv_bfloat16>) {
-    lo = __uint_as_float(w << 16);
-    hi = __uint_as_float(w & 0xFFFF0000u);
-  } else {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
-    lo = f.x;
-    hi = f.y;
-  }
-}
-
-// sign(x) * min(|x|, c) on both 16-bit halves in one instruction; NaN stays NaN.
-template <typename Tin>
-__device__ __forceinline__ uint32_t clamp_magnitude2(uint32_t w, uint32_t c2) {
-  uint32_t d;
-  if constexpr (std::is_same_v<Tin, __nv_bfloat16>) {
-    asm("min.NaN.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(w), "r"(c2));
-  } else {
-    asm("min.NaN.xorsign.abs.f16x2 %0, %1, %2;" : "=r"(d) : "r"(w), "r"(c2));
-  }
-  return d;
-}
-
-// Two floats -> two fp8 bytes (lo in bits 0..7), round-to-nearest-even, saturating.
-template <int KV>
-__device__ __forceinline__ uint32_t cvt_fp8x2(float lo, float hi) {
-  uint16_t r;
-  if constexpr (KV == KVC_KV_FP8_E4M3) {
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-  } else {
-    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
-  }
-  return r;
 }
 
 // RN(x / s) in three instructions, given s > 0 and r = RN(1/s): one Newton correction of the
@@ -695,34 +500,6 @@ __global__ void count_bad_slots_kernel(const int64_t* __restrict__ slots, int64_
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-static int in_elem_size(int in_dtype) { return in_dtype == KVC_IN_F32 ? 4 : 2; }
-
-static int pow2_shift(int64_t v) {
-  if (v <= 0 || (v & (v - 1))) return -1;
-  int s = 0;
-  while ((1ll << s) < v) ++s;
-  return s;
-}
-
-static bool aligned(const void* p, int64_t bytes) { return (reinterpret_cast<uintptr_t>(p) % bytes) == 0; }
-
-// All kernels go out with the programmatic-stream-serialization attribute (see pdl_prologue).
-template <typename Params>
-static cudaError_t launch_pdl(void (*kernel)(const Params), dim3 grid, int threads, const Params& p,
-                              cudaStream_t st) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(static_cast<unsigned>(threads));
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, p);
-}
-
 template <typename Tin, int KV, bool ONE_ROW>
 static cudaError_t launch_flash_vec2(int vec, const FlashParams& p, dim3 grid, cudaStream_t st) {
   switch (vec) {

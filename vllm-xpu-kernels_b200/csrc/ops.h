@@ -24,3 +24,9 @@ void concat_and_cache_mla(at::Tensor& kv_c, at::Tensor& k_pe, at::Tensor& kv_cac
 // Inverse direction: paged entries -> dense [tot_tokens, entry...] through block_table / cu_seq_lens.
 void gather_cache(at::Tensor const& src_cache, at::Tensor const& dst, at::Tensor const& block_table,
                   at::Tensor const& cu_seq_lens, int64_t batch_size, std::optional<at::Tensor> seq_starts);
+
+// fp8 activation quantisation (namespace `_C`; the reference's csrc/ops.h + fp8_quant.cpp:135-250).
+void static_scaled_fp8_quant(at::Tensor& out, at::Tensor const& input, at::Tensor const& scale);
+void dynamic_scaled_fp8_quant(at::Tensor& out, at::Tensor const& input, at::Tensor& scale);
+void dynamic_per_token_scaled_fp8_quant(at::Tensor& out, at::Tensor const& input, at::Tensor& scales,
+                                        std::optional<at::Tensor> const& scale_ub);

@@ -1,4 +1,4 @@
-// Registers the KV-cache write ops under torch.ops._C_cache_ops.
+// Registers the KV-cache ops under torch.ops._C_cache_ops and the fp8 quantisation ops under torch.ops._C.
 //
 // Schema strings are the public interface vLLM's attention backends call and are kept
 // character-compatible with the reference's csrc/torch_bindings.cpp:107-112, :116-122, :127-133
@@ -13,6 +13,22 @@
 #ifndef TORCH_EXTENSION_NAME
 #define TORCH_EXTENSION_NAME _C
 #endif
+
+// Namespace `_C`: only the fp8 quantisation ops of the reference's much larger set
+// (csrc/torch_bindings.cpp:67-88 there).
+KVC_TORCH_LIBRARY(TORCH_EXTENSION_NAME, m) {
+  m.def("static_scaled_fp8_quant(Tensor! result, Tensor input, Tensor scale) -> ()");
+  m.def("dynamic_scaled_fp8_quant(Tensor! result, Tensor input, Tensor! scale) -> ()");
+  m.def(
+      "dynamic_per_token_scaled_fp8_quant(Tensor! result, Tensor input, "
+      "Tensor! scale, Tensor? scale_ub) -> ()");
+}
+
+KVC_TORCH_LIBRARY_IMPL(TORCH_EXTENSION_NAME, CUDA, m) {
+  m.impl("static_scaled_fp8_quant", &static_scaled_fp8_quant);
+  m.impl("dynamic_scaled_fp8_quant", &dynamic_scaled_fp8_quant);
+  m.impl("dynamic_per_token_scaled_fp8_quant", &dynamic_per_token_scaled_fp8_quant);
+}
 
 KVC_TORCH_LIBRARY(KVC_PP_CAT(TORCH_EXTENSION_NAME, _cache_ops), m) {
   m.def(

@@ -31,6 +31,9 @@ SYMBOLS = (
     "kvc_reshape_and_cache_flash_host_noalloc",
     "kvc_release_staging",
     "kvc_count_bad_slots",
+    "kvc_static_scaled_fp8_quant",
+    "kvc_dynamic_scaled_fp8_quant",
+    "kvc_dynamic_per_token_scaled_fp8_quant",
 )
 
 _lib = None
@@ -64,6 +67,12 @@ def lib() -> ctypes.CDLL:
         L.kvc_reshape_and_cache_flash_host_noalloc.argtypes = [vp] * 5 + [i64] * 9 + [ci, ci, vp, vp, vp]
         L.kvc_release_staging.restype = ci
         L.kvc_release_staging.argtypes = []
+        L.kvc_static_scaled_fp8_quant.restype = ci
+        L.kvc_static_scaled_fp8_quant.argtypes = [vp, vp, vp, i64, ci, ci, vp]
+        L.kvc_dynamic_scaled_fp8_quant.restype = ci
+        L.kvc_dynamic_scaled_fp8_quant.argtypes = [vp, vp, vp, i64, ci, ci, vp]
+        L.kvc_dynamic_per_token_scaled_fp8_quant.restype = ci
+        L.kvc_dynamic_per_token_scaled_fp8_quant.argtypes = [vp, vp, vp, vp, i64, i64, ci, ci, vp]
         L.kvc_count_bad_slots.restype = ci
         L.kvc_count_bad_slots.argtypes = [vp, i64, i64, vp, vp]
         _lib = L
@@ -203,3 +212,27 @@ def count_bad_slots(slot_mapping, num_slots: int, stream=None) -> int:
     _check(lib().kvc_count_bad_slots(slot_mapping.data_ptr(), slot_mapping.shape[0], num_slots,
                                      out.data_ptr(), _stream(stream)))
     return int(out.item())
+
+
+FP8_CODE = {torch.float8_e4m3fn: 1, torch.float8_e5m2: 2}
+
+
+def static_scaled_fp8_quant(out, input, scale, stream=None) -> None:
+    """``kvc_static_scaled_fp8_quant``: out (fp8) <- clamp(input * (1/scale)); all contiguous, on the device."""
+    _check(lib().kvc_static_scaled_fp8_quant(out.data_ptr(), input.data_ptr(), scale.data_ptr(), input.numel(),
+                                             _in_dtype(input), FP8_CODE[out.dtype], _stream(stream)))
+
+
+def dynamic_scaled_fp8_quant(out, input, scale, stream=None) -> None:
+    """``kvc_dynamic_scaled_fp8_quant``: scale (zero-initialised by the caller) <- absmax / fp8_max, then as static."""
+    _check(lib().kvc_dynamic_scaled_fp8_quant(out.data_ptr(), input.data_ptr(), scale.data_ptr(), input.numel(),
+                                              _in_dtype(input), FP8_CODE[out.dtype], _stream(stream)))
+
+
+def dynamic_per_token_scaled_fp8_quant(out, input, scales, scale_ub=None, stream=None) -> None:
+    """``kvc_dynamic_per_token_scaled_fp8_quant`` for input [..., hidden]: one scale per row."""
+    hidden = input.shape[-1]
+    tokens = input.numel() // hidden if hidden else 0
+    _check(lib().kvc_dynamic_per_token_scaled_fp8_quant(
+        out.data_ptr(), input.data_ptr(), scales.data_ptr(), 0 if scale_ub is None else scale_ub.data_ptr(), tokens,
+        hidden, _in_dtype(input), FP8_CODE[out.dtype], _stream(stream)))
