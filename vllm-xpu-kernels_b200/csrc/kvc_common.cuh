@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <string>
 #include <type_traits>
 
@@ -57,6 +58,17 @@ __device__ __forceinline__ void pdl_prologue() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
+
+// Work that is legal BEFORE the wait: asking L2 to fetch lines this thread will read.  A prefetch
+// has no architectural effect, so it cannot observe or disturb the predecessor; CTAs that are
+// resident while the predecessor drains thereby start the memory system early and find their
+// inputs in L2 once the wait returns.  Only the first CTAs of a grid can be in that position
+// (`blockIdx.x < prefetch_ctas`); later ones would pay two requests for one line.
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// A slot read before the wait is only a HINT for what to prefetch (the predecessor may still be
+// writing slot_mapping); the value is read again, for real, after the wait.
+__device__ __forceinline__ int64_t slot_hint(const int64_t* p) { return *reinterpret_cast<const volatile int64_t*>(p); }
 
 // ---------------------------------------------------------------------------------------------
 // vector global memory access.  Loads are read-once streams: bypass L1 allocation.
@@ -223,6 +235,28 @@ static inline int pow2_shift(int64_t v) {
 static inline bool aligned(const void* p, int64_t bytes) { return (reinterpret_cast<uintptr_t>(p) % bytes) == 0; }
 
 // All kernels go out with the programmatic-stream-serialization attribute (see pdl_prologue).
+// How many CTAs of a grid prefetch before the dependency wait: half of what the device holds at
+// once for a 256-thread, <= 32-register kernel (8 per SM), i.e. sms * 4.  While a same-shaped
+// predecessor runs its last, partly filled wave, about that many of this grid's CTAs are already
+// resident and waiting; on B200 the measured optimum for back-to-back launches is flat between
+// 0.4 and 0.55 of a wave.  KVC_PREFETCH_CTAS overrides the count (0 switches the prefetch off).
+static inline uint32_t prefetch_cta_count() {
+  static const long override_count = [] {
+    const char* e = getenv("KVC_PREFETCH_CTAS");
+    return e ? strtol(e, nullptr, 10) : -1L;
+  }();
+  if (override_count >= 0) return static_cast<uint32_t>(override_count);
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return 0;
+    cached[dev] = sms * 4;
+  }
+  return static_cast<uint32_t>(cached[dev]);
+}
+
 template <typename Params>
 static inline cudaError_t launch_pdl(void (*kernel)(const Params), dim3 grid, int threads, const Params& p,
                               cudaStream_t st) {

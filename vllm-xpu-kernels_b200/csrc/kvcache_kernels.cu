@@ -153,6 +153,7 @@ struct FlashParams {
   bool linear_slots;         // block_stride == block_size * page_stride: address = slot * page_stride
   bool wide_loads;           // every source chunk address is 32-byte aligned
   bool wide_stores;          // every destination chunk address is 32-byte aligned
+  uint32_t prefetch_ctas;  // CTAs that may prefetch before the dependency wait
   uint32_t n_items;          // tokens_in_launch * rows_per_token * chunks_per_row
   uint32_t items_per_token;  // rows_per_token * chunks_per_row
   uint32_t chunks_per_row;
@@ -181,11 +182,6 @@ __global__ void __launch_bounds__(kFlashThreads) flash_scatter_kernel(const Flas
     row = p.div_chunks_per_row.div(rem);
     chunk = rem - row * p.chunks_per_row;
   }
-  pdl_prologue();
-
-  const int64_t slot = __ldg(p.slot_mapping + tok);
-  if (slot < 0) return;
-
   const int64_t d0 = static_cast<int64_t>(chunk) * VEC;
   const Tin* ksrc = static_cast<const Tin*>(p.key) + tok * p.key_stride_t + d0;
   const Tin* vsrc = static_cast<const Tin*>(p.value) + tok * p.value_stride_t + d0;
@@ -193,6 +189,15 @@ __global__ void __launch_bounds__(kFlashThreads) flash_scatter_kernel(const Flas
     ksrc += row * p.key_stride_h;
     vsrc += row * p.value_stride_h;
   }
+  if (blockIdx.x < p.prefetch_ctas && slot_hint(p.slot_mapping + tok) >= 0) {
+    prefetch_l2(ksrc);
+    prefetch_l2(vsrc);
+  }
+  pdl_prologue();
+
+  const int64_t slot = __ldg(p.slot_mapping + tok);
+  if (slot < 0) return;
+
   Chunk<IN_B> kin, vin;
   load_chunk(kin, ksrc, p.wide_loads);
   load_chunk(vin, vsrc, p.wide_loads);
@@ -235,6 +240,7 @@ struct PagedParams {
   int64_t block_size;
   int bs_shift;
   bool wide_loads;
+  uint32_t prefetch_ctas;  // CTAs that may prefetch before the dependency wait
   int32_t num_heads, head_size, x;
   int32_t piece_bytes;  // K-store width: bytes of min(VEC, x)-element groups, <= 16
   uint32_t n_warps;     // token_groups * num_heads * chunks_per_row
@@ -266,14 +272,18 @@ __global__ void __launch_bounds__(kPagedThreads) paged_scatter_kernel(const Page
   const uint32_t head = th - tg * static_cast<uint32_t>(p.num_heads);
   const int64_t tok = static_cast<int64_t>(tg) * 32 + lane;
   if (tok >= p.num_tokens) return;
+  const int d0 = static_cast<int>(chunk) * VEC;
+  const Tin* ksrc = static_cast<const Tin*>(p.key) + tok * p.key_stride_t + head * p.key_stride_h + d0;
+  const Tin* vsrc = static_cast<const Tin*>(p.value) + tok * p.value_stride_t + head * p.value_stride_h + d0;
+  if (blockIdx.x < p.prefetch_ctas && slot_hint(p.slot_mapping + tok) >= 0) {
+    prefetch_l2(ksrc);
+    prefetch_l2(vsrc);
+  }
   pdl_prologue();
 
   const int64_t slot = __ldg(p.slot_mapping + tok);
   if (slot < 0) return;
 
-  const int d0 = static_cast<int>(chunk) * VEC;
-  const Tin* ksrc = static_cast<const Tin*>(p.key) + tok * p.key_stride_t + head * p.key_stride_h + d0;
-  const Tin* vsrc = static_cast<const Tin*>(p.value) + tok * p.value_stride_t + head * p.value_stride_h + d0;
   Chunk<IN_B> kin, vin;
   load_chunk(kin, ksrc, p.wide_loads);
   load_chunk(vin, vsrc, p.wide_loads);
@@ -338,6 +348,7 @@ struct MlaParams {
   int64_t num_tokens;
   int bs_shift;
   bool wide_loads, wide_stores;
+  uint32_t prefetch_ctas;  // CTAs that may prefetch before the dependency wait
   uint32_t n_items;        // ceil(T / 2) * chunks_per_token
   uint32_t chunks_per_token;
   uint32_t chunks_kv_c;    // chunks that come from kv_c; the rest come from k_pe
@@ -359,17 +370,20 @@ __global__ void __launch_bounds__(kMlaThreads) mla_scatter_kernel(const MlaParam
   if (item >= p.n_items) return;
   const uint32_t pair = p.div_chunks_per_token.div(item);
   const uint32_t chunk = item - pair * p.chunks_per_token;
-  pdl_prologue();
-
   const int64_t t0 = static_cast<int64_t>(pair) * 2;
-  int64_t slot[2];
-  slot[0] = __ldg(p.slot_mapping + t0);
-  slot[1] = (t0 + 1 < p.num_tokens) ? __ldg(p.slot_mapping + t0 + 1) : -1;
-
   const bool from_pe = chunk >= p.chunks_kv_c;
   const Tin* base = static_cast<const Tin*>(from_pe ? p.k_pe : p.kv_c);
   const int64_t stride = from_pe ? p.k_pe_stride : p.kv_c_stride;
   const int64_t col = static_cast<int64_t>(from_pe ? chunk - p.chunks_kv_c : chunk) * VEC;
+  if (blockIdx.x < p.prefetch_ctas) {
+    if (slot_hint(p.slot_mapping + t0) >= 0) prefetch_l2(base + t0 * stride + col);
+    if (t0 + 1 < p.num_tokens && slot_hint(p.slot_mapping + t0 + 1) >= 0) prefetch_l2(base + (t0 + 1) * stride + col);
+  }
+  pdl_prologue();
+
+  int64_t slot[2];
+  slot[0] = __ldg(p.slot_mapping + t0);
+  slot[1] = (t0 + 1 < p.num_tokens) ? __ldg(p.slot_mapping + t0 + 1) : -1;
 
   Chunk<IN_B> in[2];
 #pragma unroll
@@ -645,6 +659,7 @@ static int flash_impl(const void* key, const void* value, void* key_cache, void*
   p.linear_slots = (block_stride == block_size * page_stride);
   p.wide_loads = wide;
   p.wide_stores = wide_st;
+  p.prefetch_ctas = prefetch_cta_count();
   p.items_per_token = static_cast<uint32_t>(items_per_token);
   p.chunks_per_row = static_cast<uint32_t>(chunks_per_row);
   p.div_items_per_token = FastDiv(p.items_per_token);
@@ -715,6 +730,7 @@ static int paged_impl(const void* key, const void* value, void* key_cache, void*
   p.block_size = block_size;
   p.bs_shift = pow2_shift(block_size);
   p.wide_loads = wide;
+  p.prefetch_ctas = prefetch_cta_count();
   p.num_heads = static_cast<int32_t>(num_heads);
   p.head_size = static_cast<int32_t>(head_size);
   p.x = static_cast<int32_t>(x);
@@ -790,6 +806,7 @@ static int mla_impl(const void* kv_c, const void* k_pe, void* kv_cache, const in
   p.bs_shift = pow2_shift(block_size);
   p.wide_loads = wide;
   p.wide_stores = wide_st;
+  p.prefetch_ctas = prefetch_cta_count();
   p.n_items = static_cast<uint32_t>(pairs * chunks);
   p.chunks_per_token = static_cast<uint32_t>(chunks);
   p.chunks_kv_c = static_cast<uint32_t>(kv_lora_rank / vec);
