@@ -127,6 +127,29 @@ class ClockSampler:
                 "samples": len(clks), "power_w_max": round(max(s[2] for s in self.samples), 1)}
 
 
+class LibraryChatterToStderr:
+    """Points file descriptor 1 at stderr while libraries initialise (NCCL prints a version banner
+    on stdout), so that stdout carries the JSON line and nothing else; C stdio is flushed before
+    the descriptor is restored."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self._saved = os.dup(1)
+        os.dup2(2, 1)
+        return self
+
+    def __exit__(self, *exc):
+        import ctypes
+        sys.stdout.flush()
+        try:
+            ctypes.CDLL(None).fflush(None)
+        except Exception:
+            pass
+        os.dup2(self._saved, 1)
+        os.close(self._saved)
+        return False
+
+
 def dist_setup(n_gpus: int):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -276,7 +299,7 @@ def describe_workload(w, name: str) -> str:
 # --------------------------------------------------------------------------------------------
 # the B200 arm
 # --------------------------------------------------------------------------------------------
-def run_b200_arm(ns) -> None:
+def run_b200_arm(ns):
     from vllm_xpu_kernels import cabi  # raises if the CUDA library is not built
 
     if not torch.cuda.is_available():
@@ -395,6 +418,7 @@ def run_b200_arm(ns) -> None:
         cpu = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
                "sample": f"{n} passes over {T} tokens of the batch into a 4096-block host cache, {dt:.1f} s"}
 
+    line = None
     if rank == 0:
         head = "all 8 KV heads per rank" if ns.scaling == "weak" else f"{w0.num_heads} of 8 KV heads per rank"
         line = {
@@ -419,9 +443,9 @@ def run_b200_arm(ns) -> None:
             "clocks": clocks,
             "gpu_launches": ns.steps,
         }
-        print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+    return line
 
 
 # DRAM bytes per launch from the ncu capture summarised in
@@ -449,7 +473,10 @@ def main() -> None:
     if ns.impl == "reference":
         run_reference_arm(ns)
     else:
-        run_b200_arm(ns)
+        with LibraryChatterToStderr():
+            line = run_b200_arm(ns)
+        if line is not None:
+            print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":
