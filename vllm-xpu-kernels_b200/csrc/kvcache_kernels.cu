@@ -762,6 +762,9 @@ static int mla_impl(const void* kv_c, const void* k_pe, void* kv_cache, const in
                     int64_t num_tokens, int64_t kv_lora_rank, int64_t pe_dim, int64_t block_size,
                     int64_t kv_c_stride, int64_t k_pe_stride, int64_t block_stride, int64_t entry_stride,
                     int in_dtype, int kv_dtype, const float* scale, cudaStream_t st) {
+  // an empty half (width 0) may come with a NULL pointer: it is never dereferenced
+  if (kv_lora_rank == 0 && kv_c == nullptr) kv_c = k_pe;
+  if (pe_dim == 0 && k_pe == nullptr) k_pe = kv_c;
   // shares the argument rules of the K/V ops: kv_c plays key, k_pe plays value
   if (int rc = check_common(kv_c, k_pe, kv_cache, kv_cache, slot_mapping, num_tokens, 1, kv_lora_rank + pe_dim,
                             block_size, in_dtype, kv_dtype, scale, scale))
