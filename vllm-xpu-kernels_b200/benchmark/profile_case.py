@@ -24,7 +24,7 @@ from vllm_xpu_kernels import cabi  # noqa: E402
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--layout", choices=["flash", "paged", "mla", "gather"], default="flash",
+    ap.add_argument("--layout", choices=["flash", "paged", "mla", "gather", "quant-static", "quant-dynamic", "quant-token"], default="flash",
                     help="mla: concat_and_cache_mla (512 + 64 wide entries); gather: gather_cache of such entries")
     ap.add_argument("--kv", choices=["auto", "fp8", "fp8_e5m2"], default="fp8")
     ap.add_argument("--dtype", choices=["bfloat16", "half", "float"], default="bfloat16")
@@ -45,6 +45,9 @@ def main() -> None:
     torch.manual_seed(0)
     if ns.layout in ("mla", "gather"):
         run_mla_or_gather(ns, dev)
+        return
+    if ns.layout.startswith("quant"):
+        run_quant(ns, dev)
         return
     dt = {"bfloat16": torch.bfloat16, "half": torch.float16, "float": torch.float32}[ns.dtype]
     T, H, D, bs = ns.tokens, ns.heads, ns.head_size, ns.block_size
@@ -142,6 +145,40 @@ def run_mla_or_gather(ns, dev) -> None:
     times = [a.elapsed_time(b) * 1e3 for a, b in evs]
     best = min(times[1:]) if len(times) > 1 else times[0]
     print(f"layout={ns.layout} kv={ns.kv} dtype={ns.dtype} T={T} entry=576 bs={bs} algorithmic_bytes={alg} "
+          f"launches={ns.launches} event_us={['%.1f' % t for t in times]} best_GBps={alg / best / 1e3:.0f}")
+
+
+def run_quant(ns, dev) -> None:
+    """fp8 activation quantisation of a [tokens, heads * head_size] activation."""
+    dt = {"bfloat16": torch.bfloat16, "half": torch.float16, "float": torch.float32}[ns.dtype]
+    T, hidden = ns.tokens, ns.heads * ns.head_size
+    f8 = torch.float8_e5m2 if ns.kv == "fp8_e5m2" else torch.float8_e4m3fn
+    xs = [torch.randn(T, hidden, device=dev).to(dt) for _ in range(ns.nbuf)]
+    out = torch.empty(T, hidden, dtype=f8, device=dev)
+    scale = torch.tensor([0.02], device=dev)
+    scales = torch.zeros(T, 1, device=dev)
+    es = xs[0].element_size()
+    n = T * hidden
+    alg = {"quant-static": n * (es + 1), "quant-dynamic": n * (2 * es + 1), "quant-token": n * (es + 1) + 4 * T}[ns.layout]
+    evs = []
+    for i in range(ns.launches):
+        x = xs[i % ns.nbuf]
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if ns.layout == "quant-dynamic":
+            scale.zero_()
+        a.record()
+        if ns.layout == "quant-static":
+            cabi.static_scaled_fp8_quant(out, x, scale)
+        elif ns.layout == "quant-dynamic":
+            cabi.dynamic_scaled_fp8_quant(out, x, scale)
+        else:
+            cabi.dynamic_per_token_scaled_fp8_quant(out, x, scales)
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    times = [a.elapsed_time(b) * 1e3 for a, b in evs]
+    best = min(times[1:]) if len(times) > 1 else times[0]
+    print(f"layout={ns.layout} fp8={ns.kv} dtype={ns.dtype} T={T} hidden={hidden} algorithmic_bytes={alg} "
           f"launches={ns.launches} event_us={['%.1f' % t for t in times]} best_GBps={alg / best / 1e3:.0f}")
 
 

@@ -187,6 +187,62 @@ __global__ void __launch_bounds__(kQuantThreads) per_token_fp8_quant_kernel(cons
   }
 }
 
+// Register-resident form of the per-token op: the row is read from HBM ONCE, kept in registers
+// (up to kRowChunks chunks per thread) across the reduction, and quantised from there.
+//   WARP = true   a warp per token (rows of at most 32 * kRowChunks chunks): shuffles only, no barrier,
+//                 eight tokens per CTA
+//   WARP = false  a CTA of 64, 128 or 256 threads per token (the smallest that holds the row with
+//                 kRowChunks chunks per thread, so every thread has several loads in flight):
+//                 shuffles, one shared-memory step, one barrier
+// VEC divides hidden_size (the host sees to it), so rows have no scalar tail here.
+constexpr int kRowChunks = 4;
+
+template <typename Tin, int F8, int VEC, bool WARP>
+__global__ void __launch_bounds__(kQuantThreads) per_token_fp8_quant_regs_kernel(const TokenQuantParams p,
+                                                                                  int64_t num_tokens) {
+  const int G = WARP ? 32 : static_cast<int>(blockDim.x);
+  __shared__ float warp_part[kQuantThreads / 32];
+  const int g = WARP ? (threadIdx.x & 31) : threadIdx.x;
+  const int64_t tok = WARP ? static_cast<int64_t>(blockIdx.x) * (kQuantThreads / 32) + (threadIdx.x >> 5)
+                           : static_cast<int64_t>(blockIdx.x);
+  if (WARP && tok >= num_tokens) return;  // whole warps leave together; no barrier is used in this mode
+  pdl_prologue();
+  const Tin* row = static_cast<const Tin*>(p.input) + tok * p.hidden_size;
+  unsigned char* orow = static_cast<unsigned char*>(p.out) + tok * p.hidden_size;
+
+  Chunk<VEC * (int)sizeof(Tin)> in[kRowChunks];
+#pragma unroll
+  for (int u = 0; u < kRowChunks; ++u) {
+    const int64_t c = g + u * G;
+    if (c < p.n_chunks) load_chunk(in[u], row + c * VEC, p.wide_loads);
+  }
+  float m = 0.0f;
+#pragma unroll
+  for (int u = 0; u < kRowChunks; ++u)
+    if (g + u * G < p.n_chunks) m = chunk_absmax<Tin, VEC>(in[u], m);
+  m = warp_max(m);
+  if constexpr (!WARP) {
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = m;
+    __syncthreads();
+    float v = (threadIdx.x & 31) < (blockDim.x >> 5) ? warp_part[threadIdx.x & 31] : 0.0f;
+    m = warp_max(v);  // every warp reduces the partials itself: no second barrier, no broadcast
+  }
+  if (p.scale_ub != nullptr) m = fminf(m, __ldg(p.scale_ub));
+  constexpr float M = fp8_max<F8>();
+  const float s = fmaxf(__fdiv_rn(m, M), __fdiv_rn(1.0f, M * 512.0f));
+  if (g == 0) p.scales[tok] = s;
+  const float inv = 1.0f / s;
+#pragma unroll
+  for (int u = 0; u < kRowChunks; ++u) {
+    const int64_t c = g + u * G;
+    if (c < p.n_chunks) {
+      Chunk<VEC> out;
+      quantise_chunk<Tin, F8, VEC>(in[u], out, inv);
+      store_chunk(orow + c * VEC, out, false);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
@@ -260,8 +316,36 @@ static cudaError_t launch_absmax(const QuantParams& p, float* scale_out, cudaStr
   return cudaLaunchKernelEx(&cfg, absmax_to_scale_kernel<Tin, F8, VEC>, p, scale_out);
 }
 
+template <typename K>
+static cudaError_t launch_pdl2(K kernel, dim3 grid, int threads, const TokenQuantParams& p, int64_t num_tokens,
+                               cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(static_cast<unsigned>(threads));
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, p, num_tokens);
+}
+
 template <typename Tin, int F8, int VEC>
 static cudaError_t launch_per_token(const TokenQuantParams& p, int64_t num_tokens, cudaStream_t st) {
+  if constexpr (VEC >= 8) {  // wide chunks: keep the row in registers when it fits
+    if (p.n_chunks <= 32 * kRowChunks) {
+      const int64_t ctas = (num_tokens + kQuantThreads / 32 - 1) / (kQuantThreads / 32);
+      return launch_pdl2(per_token_fp8_quant_regs_kernel<Tin, F8, VEC, true>, dim3(static_cast<unsigned>(ctas)),
+                         kQuantThreads, p, num_tokens, st);
+    }
+    if (p.n_chunks <= kQuantThreads * kRowChunks) {
+      int threads = 64;
+      while (static_cast<int64_t>(threads) * kRowChunks < p.n_chunks) threads *= 2;
+      return launch_pdl2(per_token_fp8_quant_regs_kernel<Tin, F8, VEC, false>, dim3(static_cast<unsigned>(num_tokens)),
+                         threads, p, num_tokens, st);
+    }
+  }
   return launch_pdl(per_token_fp8_quant_kernel<Tin, F8, VEC>, dim3(static_cast<unsigned>(num_tokens)), kQuantThreads,
                     p, st);
 }
@@ -338,7 +422,7 @@ int kvc_dynamic_per_token_scaled_fp8_quant(void* out, const void* input, float* 
   p.scale_ub = scale_ub;
   p.hidden_size = hidden_size;
   p.n_chunks = hidden_size / vec;
-  p.wide_loads = false;
+  p.wide_loads = (static_cast<int64_t>(vec) * es) % 32 == 0 && aligned(input, 32) && (hidden_size * es) % 32 == 0;
   const cudaError_t e = KVC_QUANT_DISPATCH(in_dtype, fp8_dtype, vec, launch_per_token, p, num_tokens,
                                            static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess)
