@@ -36,6 +36,14 @@
  * NaN maps to the canonical 0x7F (sign dropped), which is what the hardware
  * conversion produces.
  *
+ * Pinning.  Slot placement and the unquantised ("auto") results are pinned by fixtures
+ * generated with the reference's own test utilities and expected-result loops
+ * (tests/golden/make_golden.py); the fp8 results are pinned against PyTorch's cast, the
+ * conversion the reference calls, because the reference's own cache tests switch fp8 off
+ * (tests/test_cache.py:37 there) -- there is no reference test vector for fp8 cache bytes.
+ * The fp8 quantisation ops are pinned by the torch recipes of the reference's
+ * tests/test_fp8_quant.py:20-75.
+ *
  * The paged op divides by the scale like the flash op; the reference's paged
  * kernel multiplies (csrc/cache.cpp:70-79) in a branch its own tests disable.
  */
