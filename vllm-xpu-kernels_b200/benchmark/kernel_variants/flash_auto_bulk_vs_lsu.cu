@@ -1,8 +1,8 @@
 // Stand-alone comparison for the UNQUANTISED flash-layout scatter (bf16 -> bf16, 2 KB rows):
 // 256-bit LSU loads/stores (what the library does) against bulk asynchronous copies
 // (cp.async.bulk global -> shared -> global) driven by one thread per CTA through a ring of stages.
-// Not part of the library; it records the measurement behind the choice.  No cluster launch, no
-// multicast; every mbarrier wait is bounded and reports through an error flag.
+// Not part of the library; it records the measurement behind the choice.  Plain CTA-local copies, no
+// cluster launch; every mbarrier wait is bounded and reports through an error flag.
 //
 //   nvcc -gencode arch=compute_100a,code=sm_100a -O3 -std=c++17 -lineinfo -o flash_auto_bulk_vs_lsu flash_auto_bulk_vs_lsu.cu
 //   ./flash_auto_bulk_vs_lsu [num_tokens=16384]
