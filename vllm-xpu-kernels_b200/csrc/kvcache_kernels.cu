@@ -425,7 +425,7 @@ struct GatherParams {
 };
 
 constexpr int kGatherThreads = 256;
-constexpr int kGatherRowsPerWarp = 8;
+constexpr int kGatherRowsPerWarp = 4;
 
 // A warp copies kGatherRowsPerWarp consecutive destination rows.  Lanes 0..7 each locate one
 // row's source entry (bisection over cu_seq_lens: batch_size + 1 ints, cache resident), all
