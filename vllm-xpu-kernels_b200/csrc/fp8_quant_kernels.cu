@@ -106,10 +106,16 @@ __global__ void __launch_bounds__(kQuantThreads) absmax_to_scale_kernel(const Qu
   pdl_prologue();
   float m = 0.0f;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kQuantThreads;
-  for (int64_t c = static_cast<int64_t>(blockIdx.x) * kQuantThreads + threadIdx.x; c < p.n_chunks; c += stride) {
-    Chunk<VEC * (int)sizeof(Tin)> in;
-    load_chunk(in, static_cast<const Tin*>(p.input) + c * VEC, p.wide_loads);
-    m = chunk_absmax<Tin, VEC>(in, m);
+  // four chunks per pass: four independent loads in flight per thread
+  for (int64_t c0 = static_cast<int64_t>(blockIdx.x) * kQuantThreads + threadIdx.x; c0 < p.n_chunks; c0 += 4 * stride) {
+    Chunk<VEC * (int)sizeof(Tin)> in[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (c0 + u * stride < p.n_chunks)
+        load_chunk(in[u], static_cast<const Tin*>(p.input) + (c0 + u * stride) * VEC, p.wide_loads);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (c0 + u * stride < p.n_chunks) m = chunk_absmax<Tin, VEC>(in[u], m);
   }
   for (int64_t i = p.n_chunks * VEC + static_cast<int64_t>(blockIdx.x) * kQuantThreads + threadIdx.x; i < p.num_elems;
        i += stride)
