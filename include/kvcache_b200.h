@@ -23,6 +23,11 @@
  *   - Tokens whose slot is negative are skipped (csrc/cache.cpp:49, :145).
  *     Slots >= num_blocks*block_size and duplicate slots are undefined
  *     behaviour, as in the reference; kvc_count_bad_slots() is the debug check.
+ *   - Environment (read once per process): KVC_PREFETCH_CTAS=<n> sets how many CTAs of
+ *     a scatter launch prefetch their inputs into L2 before waiting for the preceding
+ *     kernel (default: half of one resident wave; 0 disables);
+ *     KVC_TEST_MAX_ITEMS_PER_LAUNCH=<n> lowers the work-item limit at which
+ *     kvc_reshape_and_cache_flash splits a batch into several launches (test hook).
  *   - fp8 stores compute float(x) / scale in IEEE fp32 (correctly rounded),
  *     then round to nearest even onto the fp8 grid and saturate at the largest
  *     finite value (448 for e4m3, 57344 for e5m2); NaN becomes 0x7F.

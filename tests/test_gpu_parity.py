@@ -367,3 +367,33 @@ def test_host_entry_matches_device_entry(cuda_device):
         torch.cuda.synchronize()
         assert H.same_bytes(kc1, kc2) and H.same_bytes(vc1, vc2)
     cabi.release_staging()
+
+
+def test_very_large_batches_are_split_into_several_launches(cuda_device):
+    """Batches beyond 2^31 work items go out as several launches.  No test can hold such a batch, so a
+    child process lowers the per-launch limit (KVC_TEST_MAX_ITEMS_PER_LAUNCH) and checks a small one."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import sys, torch
+sys.path[:0] = [%r, %r]
+from oracle import torch_views
+from vllm_xpu_kernels import cabi
+torch.manual_seed(0)
+T, H, D, bs, nb = 1000, 4, 64, 16, 64
+key = torch.randn(T, H, D).to(torch.bfloat16); value = torch.randn(T, H, D).to(torch.bfloat16)
+slots = torch.randperm(nb * bs)[:T]; slots[::7] = -1
+kc = torch.zeros(nb, bs, H, D, dtype=torch.uint8); vc = torch.zeros_like(kc)
+dev = torch.device("cuda:0")
+dk, dv = kc.to(dev), vc.to(dev)
+s = torch.tensor(0.02, device=dev)
+cabi.reshape_and_cache_flash(key.to(dev), value.to(dev), dk, dv, slots.to(dev), "fp8", s, s)
+torch.cuda.synchronize()
+torch_views.run("flash", key, value, kc, vc, slots, "fp8", 0.02, 0.02)
+assert torch.equal(dk.cpu(), kc) and torch.equal(dv.cpu(), vc)
+print("split ok")
+''' % (H.GOLDEN_DIR.rsplit("/tests/", 1)[0], H.GOLDEN_DIR.rsplit("/tests/", 1)[0] + "/vllm-xpu-kernels_b200")
+    env = dict(os.environ, KVC_TEST_MAX_ITEMS_PER_LAUNCH="1500")  # 16 items per token -> 93 tokens per launch
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "split ok" in r.stdout, r.stdout + r.stderr

@@ -665,8 +665,15 @@ static int flash_impl(const void* key, const void* value, void* key_cache, void*
   p.div_items_per_token = FastDiv(p.items_per_token);
   p.div_chunks_per_row = FastDiv(p.chunks_per_row);
 
-  // Item indices are 31-bit: very large batches go out as several launches.
-  const int64_t max_tokens_per_launch = ((1ll << 31) - kFlashThreads) / items_per_token;
+  // Item indices are 31-bit: very large batches go out as several launches.  The limit can be
+  // lowered through KVC_TEST_MAX_ITEMS_PER_LAUNCH so that tests reach the splitting code.
+  static const int64_t item_limit = [] {
+    const char* e = getenv("KVC_TEST_MAX_ITEMS_PER_LAUNCH");
+    const int64_t v = e ? strtoll(e, nullptr, 10) : 0;
+    return (v > 0 && v < (1ll << 31) - kFlashThreads) ? v : (1ll << 31) - kFlashThreads;
+  }();
+  int64_t max_tokens_per_launch = item_limit / items_per_token;
+  if (max_tokens_per_launch < 1) max_tokens_per_launch = 1;
   for (int64_t t0 = 0; t0 < num_tokens; t0 += max_tokens_per_launch) {
     const int64_t nt = (num_tokens - t0 < max_tokens_per_launch) ? num_tokens - t0 : max_tokens_per_launch;
     p.key = static_cast<const char*>(key) + t0 * key_stride_t * es_in;
