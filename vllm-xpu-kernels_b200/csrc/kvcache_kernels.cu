@@ -348,56 +348,67 @@ struct MlaParams {
   int64_t num_tokens;
   int bs_shift;
   bool wide_loads, wide_stores;
+  bool linear_slots;       // block_stride == block_size * entry_stride: address = slot * entry_stride
   uint32_t prefetch_ctas;  // CTAs that may prefetch before the dependency wait
-  uint32_t n_items;        // ceil(T / 2) * chunks_per_token
+  uint32_t n_items;        // ceil(T / kMlaTokensPerThread) * chunks_per_token
   uint32_t chunks_per_token;
   uint32_t chunks_kv_c;    // chunks that come from kv_c; the rest come from k_pe
   FastDiv div_chunks_per_token;
 };
 
 constexpr int kMlaThreads = 256;
+constexpr int kMlaTokensPerThread = 2;
 
-// One thread moves the same VEC-element chunk of two consecutive tokens' concatenated rows,
-// so two independent loads are in flight per thread.  Chunks below chunks_kv_c read kv_c,
-// the others k_pe; VEC divides both widths (the host picks it), so a chunk never straddles.
+// One thread moves the same VEC-element chunk of kMlaTokensPerThread consecutive tokens'
+// concatenated rows, so that many independent loads are in flight per thread and the scale set-up
+// and index arithmetic are shared.  Chunks below chunks_kv_c read kv_c, the others k_pe; VEC
+// divides both widths (the host picks it), so a chunk never straddles.
 template <typename Tin, int KV, int VEC>
 __global__ void __launch_bounds__(kMlaThreads) mla_scatter_kernel(const MlaParams p) {
   constexpr int IN_B = VEC * (int)sizeof(Tin);
   constexpr int OUT_ES = (KV == KVC_KV_AUTO) ? (int)sizeof(Tin) : 1;
   constexpr int OUT_B = VEC * OUT_ES;
+  constexpr int N = kMlaTokensPerThread;
 
   const uint32_t item = blockIdx.x * kMlaThreads + threadIdx.x;
   if (item >= p.n_items) return;
-  const uint32_t pair = p.div_chunks_per_token.div(item);
-  const uint32_t chunk = item - pair * p.chunks_per_token;
-  const int64_t t0 = static_cast<int64_t>(pair) * 2;
+  const uint32_t group = p.div_chunks_per_token.div(item);
+  const uint32_t chunk = item - group * p.chunks_per_token;
+  const int64_t t0 = static_cast<int64_t>(group) * N;
   const bool from_pe = chunk >= p.chunks_kv_c;
   const Tin* base = static_cast<const Tin*>(from_pe ? p.k_pe : p.kv_c);
   const int64_t stride = from_pe ? p.k_pe_stride : p.kv_c_stride;
-  const int64_t col = static_cast<int64_t>(from_pe ? chunk - p.chunks_kv_c : chunk) * VEC;
+  const Tin* src = base + t0 * stride + static_cast<int64_t>(from_pe ? chunk - p.chunks_kv_c : chunk) * VEC;
   if (blockIdx.x < p.prefetch_ctas) {
-    if (slot_hint(p.slot_mapping + t0) >= 0) prefetch_l2(base + t0 * stride + col);
-    if (t0 + 1 < p.num_tokens && slot_hint(p.slot_mapping + t0 + 1) >= 0) prefetch_l2(base + (t0 + 1) * stride + col);
+#pragma unroll
+    for (int i = 0; i < N; ++i)
+      if (t0 + i < p.num_tokens && slot_hint(p.slot_mapping + t0 + i) >= 0) prefetch_l2(src + i * stride);
   }
   pdl_prologue();
 
-  int64_t slot[2];
-  slot[0] = __ldg(p.slot_mapping + t0);
-  slot[1] = (t0 + 1 < p.num_tokens) ? __ldg(p.slot_mapping + t0 + 1) : -1;
-
-  Chunk<IN_B> in[2];
+  int64_t slot[N];
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
-    if (slot[i] >= 0) load_chunk(in[i], base + (t0 + i) * stride + col, p.wide_loads);
+  for (int i = 0; i < N; ++i) slot[i] = (t0 + i < p.num_tokens) ? __ldg(p.slot_mapping + t0 + i) : -1;
+
+  Chunk<IN_B> in[N];
+#pragma unroll
+  for (int i = 0; i < N; ++i)
+    if (slot[i] >= 0) load_chunk(in[i], src + i * stride, p.wide_loads);
 
   ScaleCtx sc{};
   if constexpr (KV != KVC_KV_AUTO) sc = make_scale_ctx<Tin, KV>(p.scale);
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < N; ++i) {
     if (slot[i] < 0) continue;
-    int64_t blk, off;
-    split_slot(slot[i], p.block_size, p.bs_shift, blk, off);
-    const int64_t dst = blk * p.block_stride + off * p.entry_stride + static_cast<int64_t>(chunk) * VEC;
+    int64_t dst;
+    if (p.linear_slots) {
+      dst = slot[i] * p.entry_stride;
+    } else {
+      int64_t blk, off;
+      split_slot(slot[i], p.block_size, p.bs_shift, blk, off);
+      dst = blk * p.block_stride + off * p.entry_stride;
+    }
+    dst += static_cast<int64_t>(chunk) * VEC;
     Chunk<OUT_B> out;
     convert_chunk<Tin, KV, VEC>(in[i], out, sc);
     store_chunk(static_cast<char*>(p.kv_cache) + dst * OUT_ES, out, p.wide_stores);
@@ -797,7 +808,7 @@ static int mla_impl(const void* kv_c, const void* k_pe, void* kv_cache, const in
   for (int i = 0; i < 3 && wide_st; ++i) wide_st = ((out_strides[i] * es_out) % 32) == 0;
 
   const int64_t chunks = (kv_lora_rank + pe_dim) / vec;
-  const int64_t pairs = (num_tokens + 1) / 2;
+  const int64_t pairs = (num_tokens + kMlaTokensPerThread - 1) / kMlaTokensPerThread;  // token groups
   if (chunks >= (1ll << 30) || pairs * chunks >= (1ll << 31) - kMlaThreads)
     return fail(KVC_ERR_INVALID_ARG, "num_tokens * (kv_lora_rank + pe_dim) too large for one call");
 
@@ -816,6 +827,7 @@ static int mla_impl(const void* kv_c, const void* k_pe, void* kv_cache, const in
   p.bs_shift = pow2_shift(block_size);
   p.wide_loads = wide;
   p.wide_stores = wide_st;
+  p.linear_slots = (block_stride == block_size * entry_stride);
   p.prefetch_ctas = prefetch_cta_count();
   p.n_items = static_cast<uint32_t>(pairs * chunks);
   p.chunks_per_token = static_cast<uint32_t>(chunks);
