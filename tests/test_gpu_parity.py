@@ -397,3 +397,58 @@ print("split ok")
     env = dict(os.environ, KVC_TEST_MAX_ITEMS_PER_LAUNCH="1500")  # 16 items per token -> 93 tokens per launch
     r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "split ok" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("dtype,kv", [(torch.half, "auto"), (torch.bfloat16, "fp8"), (torch.bfloat16, "auto"),
+                                      (torch.float, "auto"), (torch.half, "fp8_e5m2")])
+@pytest.mark.parametrize("bs", [16, 32, 64, 8, 48])
+def test_paged_sequence_like_slots(dtype, kv, bs, cuda_device):
+    """Slot patterns a prefill produces -- whole aligned runs, runs that start mid-block, cross a block
+    boundary, contain padding or run backwards -- exercise the vector V stores and their fallbacks."""
+    dev = cuda_device
+    Hh, D, nb = 3, 64, 40
+    g = torch.Generator().manual_seed(bs)
+    blocks = torch.randperm(nb, generator=g).tolist()
+    slots = []
+    b = iter(blocks)
+    def run(block, start, n):
+        return [block * bs + start + i for i in range(n)]
+    slots += run(next(b), 0, bs)                       # a whole block
+    slots += run(next(b), 0, bs) + run(next(b), 0, bs)  # two whole blocks back to back
+    slots += run(next(b), bs // 2, bs - bs // 2)       # starts mid-block
+    slots += run(next(b), 0, bs // 2)                  # ends mid-block
+    hole = run(next(b), 0, bs)
+    hole[bs // 3] = -1                                 # padding inside a run
+    slots += hole
+    slots += list(reversed(run(next(b), 0, bs)))       # descending offsets
+    blk2 = next(b)
+    slots += [blk2 * bs + (i * 7) % bs for i in range(bs)] if bs % 7 else run(blk2, 0, bs)  # permuted offsets
+    slots += run(next(b), 0, 16 if bs >= 16 else bs)   # a run of 16 at offset 0
+    slots += run(next(b), 16, 16) if bs >= 32 else []  # a run of 16 at offset 16
+    slots += run(next(b), 8, 16) if bs >= 32 else []   # a run of 16 at offset 8 (not vector-aligned)
+    slots += [-1] * 5 + run(next(b), 0, bs)            # padding shifts the run against the warp's halves
+    T = len(slots)
+    slots = torch.tensor(slots, dtype=torch.long)
+    torch.manual_seed(bs + 1)
+    key = torch.randn(T, Hh, D).to(dtype)
+    value = torch.randn(T, Hh, D).to(dtype)
+    cdt = H.cache_torch_dtype(dtype, kv)
+    x = 16 // torch.empty((), dtype=cdt).element_size()
+    kc = H.fill_pattern_(torch.empty(nb, Hh, D // x, bs, x, dtype=cdt), 5)
+    vc = H.fill_pattern_(torch.empty(nb, Hh, D, bs, dtype=cdt), 6)
+    dkc, dvc = kc.to(dev), vc.to(dev)
+    fmax = 57344.0 if kv == "fp8_e5m2" else 448.0
+    ks = float(key.float().abs().amax() / fmax)
+    vs = float(value.float().abs().amax() / fmax)
+    H.oracle_call("paged", key, value, kc, vc, slots, kv, ks, vs)
+    run_cabi("paged", key.to(dev), value.to(dev), dkc, dvc, slots.to(dev), kv, dev_scale(ks, dev), dev_scale(vs, dev))
+    assert H.same_bytes(dkc.cpu(), kc), "key cache differs"
+    assert H.same_bytes(dvc.cpu(), vc), "value cache differs"
+    # a misaligned value cache base must fall back to element stores and still be right
+    buf = torch.zeros(vc.numel() * vc.element_size() + 64, dtype=torch.uint8, device=dev)
+    es = vc.element_size()
+    dvc2 = buf[16:16 + vc.numel() * es].view(cdt).view(vc.shape)
+    dvc2.copy_(H.fill_pattern_(torch.empty(nb, Hh, D, bs, dtype=cdt), 6).to(dev))
+    dkc2 = H.fill_pattern_(torch.empty(nb, Hh, D // x, bs, x, dtype=cdt), 5).to(dev)
+    run_cabi("paged", key.to(dev), value.to(dev), dkc2, dvc2, slots.to(dev), kv, dev_scale(ks, dev), dev_scale(vs, dev))
+    assert H.same_bytes(dvc2.cpu(), vc), "value cache (16-byte-offset base) differs"
