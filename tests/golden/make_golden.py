@@ -2,7 +2,7 @@
 
 Run where the reference checkout is available (it is NOT needed to run the tests):
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <path to a checkout of the reference project>
 
 What comes from the reference, imported as Python and executed on the CPU:
   * the cache factories ``create_kv_caches_with_random`` (paged layout) and
@@ -209,7 +209,7 @@ def make_tables() -> dict:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path to a checkout of the reference project")
     ns = ap.parse_args()
     ru = load_reference_utils(ns.reference)
 
