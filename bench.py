@@ -2,7 +2,7 @@
 """Benchmark of the KV-cache write path: reshape_and_cache_flash, bf16 -> fp8_e4m3.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
-                    [--workload C4|C2|C5-fp8|C5-bf16|C1] [--scaling weak|strong]
+                    [--workload C4|C2|C3|C5-fp8|C5-bf16|C1] [--scaling weak|strong]
 
 One step = one call of the op over one batch (the "C4" batch by default: 16384 tokens,
 8 KV heads x 128, cache of 65536 blocks x 64 slots, fp8_e4m3 store, slots in runs of 64).
@@ -46,7 +46,6 @@ import torch  # noqa: E402
 
 import workloads  # noqa: E402
 
-METRIC = "reshape_and_cache_flash_fp8_tokens_per_s"
 NBUF = 8            # distinct input sets rotated through, so inputs come from HBM, not L2
 GRAPH_STEPS = 64    # steps captured per CUDA graph
 
@@ -210,11 +209,10 @@ def make_batch_sets(name: str, rank: int, world: int, scaling: str, nbuf: int):
 # --------------------------------------------------------------------------------------------
 # CPU oracle timing (cpu_baseline leg and --impl reference)
 # --------------------------------------------------------------------------------------------
-def cpu_oracle_rate(w, budget_s: float, host_blocks: int = 4096, tokens: int | None = None):
-    """tokens/s of the CPU oracle on (a prefix of) batch ``w``.  The host cache keeps the
-    batch's block size and row shape but only ``host_blocks`` blocks, so that it fits in
-    ordinary host memory; the tokens' blocks are renumbered into it, runs of slots intact."""
-    import numpy as np
+def cpu_oracle_pass(w, tokens: int | None = None, host_blocks: int = 4096):
+    """(run, T, blocks, threads): ``run()`` is one pass of the CPU oracle over (a prefix of) batch ``w``.
+    The host cache keeps the batch's layout, block size and row shape but only ``host_blocks`` blocks, so
+    that it fits in ordinary host memory; the tokens' blocks are renumbered into it, runs of slots intact."""
     import oracle
     from oracle import torch_views as H  # numpy views of torch tensors
 
@@ -223,21 +221,36 @@ def cpu_oracle_rate(w, budget_s: float, host_blocks: int = 4096, tokens: int | N
     slots = w.slot_mapping[:T].clone()
     bs = w.block_size
     act = slots >= 0
-    blocks = torch.div(slots[act], bs, rounding_mode="floor")
-    uniq, inv = torch.unique(blocks, return_inverse=True)
-    if uniq.numel() > host_blocks:
-        host_blocks = int(uniq.numel())
+    uniq, inv = torch.unique(torch.div(slots[act], bs, rounding_mode="floor"), return_inverse=True)
+    host_blocks = max(host_blocks, int(uniq.numel()))
     slots[act] = inv * bs + slots[act] % bs
     cdt = torch.uint8 if w.kv_cache_dtype != "auto" else key.dtype
-    kc = torch.zeros(host_blocks, bs, w.num_heads, w.head_size, dtype=cdt)
-    vc = torch.zeros_like(kc)
+    if w.layout == "flash":
+        kc = torch.zeros(host_blocks, bs, w.num_heads, w.head_size, dtype=cdt)
+        vc = torch.zeros_like(kc)
+        fn = oracle.reshape_and_cache_flash
+    else:
+        x = 16 // torch.empty((), dtype=cdt).element_size()
+        kc = torch.zeros(host_blocks, w.num_heads, w.head_size // x, bs, x, dtype=cdt)
+        vc = torch.zeros(host_blocks, w.num_heads, w.head_size, bs, dtype=cdt)
+        fn = oracle.reshape_and_cache
     threads = host_threads()
     args = (H.as_np(key), H.as_np(value), H.as_np(kc), H.as_np(vc), slots.numpy(), w.kv_cache_dtype,
             float(w.k_scale), float(w.v_scale), H.ORC_IN[key.dtype])
-    oracle.reshape_and_cache_flash(*args, threads=threads)  # warm-up: page in, spin up the thread pool
+
+    def run() -> None:
+        fn(*args, threads=threads)
+
+    return run, T, host_blocks, threads
+
+
+def cpu_oracle_rate(w, budget_s: float, tokens: int | None = None):
+    """tokens/s of the CPU oracle on (a prefix of) batch ``w``, measured for about ``budget_s`` seconds."""
+    run, T, _, threads = cpu_oracle_pass(w, tokens)
+    run()  # warm-up: page in, spin up the thread pool
     n, t0 = 0, time.perf_counter()
     while True:
-        oracle.reshape_and_cache_flash(*args, threads=threads)
+        run()
         n += 1
         dt = time.perf_counter() - t0
         if dt >= budget_s and n >= 3:
@@ -250,36 +263,24 @@ def run_reference_arm(ns) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import oracle
-    from oracle import torch_views as H
     w = workloads.BY_NAME[ns.workload](variant=0)
     # size the per-step sample so that warmup + steps end within about two minutes
     rate0, threads, _, _, _ = cpu_oracle_rate(w, 2.0)
     per_step = int(max(64, min(w.num_tokens, rate0 * 100.0 / max(1, ns.steps + ns.warmup))))
-    per_step -= per_step % w.block_size or 0
+    per_step -= per_step % w.block_size
     per_step = max(w.block_size, per_step)
-    T = per_step
-    key, value = w.key[:T].contiguous(), w.value[:T].contiguous()
-    slots = w.slot_mapping[:T].clone()
-    bs = w.block_size
-    act = slots >= 0
-    uniq, inv = torch.unique(torch.div(slots[act], bs, rounding_mode="floor"), return_inverse=True)
-    slots[act] = inv * bs + slots[act] % bs
-    kc = torch.zeros(max(4096, int(uniq.numel())), bs, w.num_heads, w.head_size, dtype=torch.uint8)
-    vc = torch.zeros_like(kc)
-    args = (H.as_np(key), H.as_np(value), H.as_np(kc), H.as_np(vc), slots.numpy(), w.kv_cache_dtype,
-            float(w.k_scale), float(w.v_scale), H.ORC_IN[key.dtype])
+    run, T, blocks, threads = cpu_oracle_pass(w, per_step)
     for _ in range(ns.warmup):
-        oracle.reshape_and_cache_flash(*args, threads=threads)
+        run()
     t0 = time.perf_counter()
     for _ in range(ns.steps):
-        oracle.reshape_and_cache_flash(*args, threads=threads)
+        run()
     dt = time.perf_counter() - t0
     value_tps = T * ns.steps / dt
-    sample = (f"{T} of the batch's {w.num_tokens} tokens per step into a {kc.shape[0]}-block host cache, "
+    sample = (f"{T} of the batch's {w.num_tokens} tokens per step into a {blocks}-block host cache, "
               f"{ns.steps} steps, {threads} OpenMP threads")
     line = {
-        "impl": "reference", "metric": METRIC, "value": value_tps, "unit": "tokens/s", "n_gpus": ns.gpus,
+        "impl": "reference", "metric": metric_name(w), "value": value_tps, "unit": "tokens/s", "n_gpus": ns.gpus,
         "steps": ns.steps, "warmup": ns.warmup, "ms_per_step": dt / ns.steps * 1e3, "higher_is_better": True,
         "scaling": ns.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": describe_workload(w, ns.workload), "tokens_per_step": T},
@@ -290,8 +291,15 @@ def run_reference_arm(ns) -> None:
     print(json.dumps(line), flush=True)
 
 
+def metric_name(w) -> str:
+    """The headline metric for the fp8 flash workloads; the other layouts/modes name themselves."""
+    op = "reshape_and_cache_flash" if w.layout == "flash" else "reshape_and_cache"
+    return f"{op}_fp8_tokens_per_s" if w.kv_cache_dtype != "auto" else f"{op}_tokens_per_s"
+
+
 def describe_workload(w, name: str) -> str:
-    return (f"{name}: reshape_and_cache_flash {str(w.key.dtype).replace('torch.', '')}->{w.kv_cache_dtype}, "
+    op = "reshape_and_cache_flash" if w.layout == "flash" else "reshape_and_cache"
+    return (f"{name}: {op} {str(w.key.dtype).replace('torch.', '')}->{w.kv_cache_dtype}, "
             f"T={w.num_tokens} (active {w.num_active}), H={w.num_heads}, D={w.head_size}, "
             f"block_size={w.block_size}, num_blocks={w.num_blocks}")
 
@@ -311,13 +319,12 @@ def run_b200_arm(ns):
 
     sets = make_batch_sets(ns.workload, rank, world, ns.scaling, NBUF)
     w0 = sets[0]
-    if w0.layout != "flash":
-        raise SystemExit("bench.py times the flash-layout op; see benchmark/benchmark_reshape_and_cache.py for the paged one")
-    ksh, _ = w0.cache_shapes()
+    paged = w0.layout == "paged"
+    ksh, vsh = w0.cache_shapes()
     cdt = w0.cache_dtype
     # torch.zeros: the allocation is touched once so first-use effects stay out of the timed region
     key_cache = torch.zeros(ksh, dtype=torch.uint8 if cdt != w0.key.dtype else cdt, device=dev)
-    value_cache = torch.zeros_like(key_cache)
+    value_cache = torch.zeros(vsh, dtype=key_cache.dtype, device=dev)
     if cdt != w0.key.dtype:
         key_cache, value_cache = key_cache.view(cdt), value_cache.view(cdt)
     dsets = [(w.key.to(dev), w.value.to(dev), w.slot_mapping.to(dev), w.k_scale.to(dev), w.v_scale.to(dev)) for w in sets]
@@ -326,7 +333,10 @@ def run_b200_arm(ns):
 
     def step(i: int) -> None:
         k, v, s, ks, vs = dsets[i % NBUF]
-        cabi.reshape_and_cache_flash(k, v, key_cache, value_cache, s, kv, ks, vs)
+        if paged:
+            cabi.reshape_and_cache(k, v, key_cache, value_cache, s, kv, ks, vs)
+        else:
+            cabi.reshape_and_cache_flash(k, v, key_cache, value_cache, s, kv, ks, vs)
 
     # graphs: GRAPH_STEPS steps each, plus one for the remainder so that exactly K steps are timed
     def capture(n: int):
@@ -385,17 +395,32 @@ def run_b200_arm(ns):
     e2e_steps = max(1, min(ns.steps, 40))
     hsets = [(w.key.contiguous().pin_memory(), w.value.contiguous().pin_memory(), w.slot_mapping.pin_memory())
              for w in sets[:4]]
-    kflat = key_cache.view(torch.uint8).view(w0.num_blocks * w0.block_size, -1)
-    vflat = value_cache.view(torch.uint8).view(w0.num_blocks * w0.block_size, -1)
-    probes = [torch.empty(2, kflat.shape[1], dtype=torch.uint8).pin_memory() for _ in range(4)]
     last_slots = [int(w.slot_mapping[w.slot_mapping >= 0][-1]) for w in sets[:4]]
+    if paged:
+        # the paged op has no host-buffer entry point: copies go through torch, the call through the C ABI;
+        # the step's result read back is the cache block (K and V) the last token was written into
+        kflat = key_cache.view(torch.uint8).view(w0.num_blocks, -1)
+        vflat = value_cache.view(torch.uint8).view(w0.num_blocks, -1)
+        last_rows = [s // w0.block_size for s in last_slots]
+        e2e_api = "pinned host tensors -> .to(device) -> kvc_reshape_and_cache"
+    else:
+        kflat = key_cache.view(torch.uint8).view(w0.num_blocks * w0.block_size, -1)
+        vflat = value_cache.view(torch.uint8).view(w0.num_blocks * w0.block_size, -1)
+        last_rows = last_slots
+        e2e_api = "kvc_reshape_and_cache_flash_host (pinned host key/value/slot_mapping)"
+    probes = [(torch.empty(kflat.shape[1], dtype=torch.uint8).pin_memory(),
+               torch.empty(vflat.shape[1], dtype=torch.uint8).pin_memory()) for _ in range(4)]
 
     def e2e_step(i: int) -> None:
         j = i % 4
         hk, hv, hs = hsets[j]
-        cabi.reshape_and_cache_flash_host(hk, hv, key_cache, value_cache, hs, kv, dsets[j][3], dsets[j][4])
-        probes[j][0].copy_(kflat[last_slots[j]], non_blocking=True)  # the step's result: last token's K and V rows
-        probes[j][1].copy_(vflat[last_slots[j]], non_blocking=True)
+        if paged:
+            cabi.reshape_and_cache(hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True), key_cache, value_cache,
+                                   hs.to(dev, non_blocking=True), kv, dsets[j][3], dsets[j][4])
+        else:
+            cabi.reshape_and_cache_flash_host(hk, hv, key_cache, value_cache, hs, kv, dsets[j][3], dsets[j][4])
+        probes[j][0].copy_(kflat[last_rows[j]], non_blocking=True)  # the step's result, read back
+        probes[j][1].copy_(vflat[last_rows[j]], non_blocking=True)
 
     for i in range(4):
         e2e_step(i)
@@ -408,8 +433,9 @@ def run_b200_arm(ns):
     barrier(dist)
     e2e_value = tokens_all * e2e_steps / e2e_s
     h2d = sets[0].key.numel() * sets[0].key.element_size() * 2 + sets[0].num_tokens * 8
-    d2h = 2 * probes[0].shape[1]
-    cabi.release_staging()
+    d2h = probes[0][0].numel() + probes[0][1].numel()
+    if not paged:
+        cabi.release_staging()
 
     # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1)
     cpu = None
@@ -420,9 +446,11 @@ def run_b200_arm(ns):
 
     line = None
     if rank == 0:
-        head = "all 8 KV heads per rank" if ns.scaling == "weak" else f"{w0.num_heads} of 8 KV heads per rank"
+        total_heads = w0.num_heads * (world if ns.scaling == "strong" else 1)
+        head = (f"all {w0.num_heads} KV heads per rank" if ns.scaling == "weak"
+                else f"{w0.num_heads} of {total_heads} KV heads per rank")
         line = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": ns.steps,
+            "metric": metric_name(w0), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": ns.steps,
             "warmup": ns.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": ns.scaling,
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {
@@ -439,7 +467,7 @@ def run_b200_arm(ns):
                          "single_launch_us_eager": single_us},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "api": "kvc_reshape_and_cache_flash_host (pinned host key/value/slot_mapping)"},
+                    "steps": e2e_steps, "api": e2e_api},
             "clocks": clocks,
             "gpu_launches": ns.steps,
         }
@@ -463,7 +491,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=8192)
     ap.add_argument("--warmup", type=int, default=128)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
-    ap.add_argument("--workload", choices=[k for k in workloads.BY_NAME if k != "C3"], default="C4")
+    ap.add_argument("--workload", choices=list(workloads.BY_NAME), default="C4")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="time budget of the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
