@@ -158,10 +158,8 @@ def gather_cache(src_cache, dst, block_table, cu_seq_lens, batch_size: int, seq_
         _stream(stream)))
 
 
-def reshape_and_cache_flash_host(host_key, host_value, key_cache, value_cache, host_slot_mapping,
-                                 kv_cache_dtype: str, k_scale=None, v_scale=None, stream=None) -> None:
-    """``kvc_reshape_and_cache_flash_host``: key/value/slot_mapping are HOST tensors
-    ([T, H, D] with contiguous heads; pinned for asynchronous copies), caches and scales on the device."""
+def _host_entry_args(host_key, host_value, host_slot_mapping, kv_cache_dtype: str):
+    """Checks shared by the two host-buffer entry points; returns (kv code, num_heads, head_size)."""
     kv = parse_kv_cache_dtype(kv_cache_dtype)
     for t in (host_key, host_value, host_slot_mapping):
         if t.is_cuda:
@@ -169,6 +167,14 @@ def reshape_and_cache_flash_host(host_key, host_value, key_cache, value_cache, h
     H, D = host_key.shape[1], host_key.shape[2]
     if H > 1 and (host_key.stride(1) != D or host_value.stride(1) != D):
         raise RuntimeError("host key/value must have contiguous heads")
+    return kv, H, D
+
+
+def reshape_and_cache_flash_host(host_key, host_value, key_cache, value_cache, host_slot_mapping,
+                                 kv_cache_dtype: str, k_scale=None, v_scale=None, stream=None) -> None:
+    """``kvc_reshape_and_cache_flash_host``: key/value/slot_mapping are HOST tensors
+    ([T, H, D] with contiguous heads; pinned for asynchronous copies), caches and scales on the device."""
+    kv, H, D = _host_entry_args(host_key, host_value, host_slot_mapping, kv_cache_dtype)
     _check(lib().kvc_reshape_and_cache_flash_host(
         host_key.data_ptr(), host_value.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
         host_slot_mapping.data_ptr(), host_slot_mapping.shape[0], H, D, key_cache.shape[1],
@@ -187,13 +193,7 @@ def reshape_and_cache_flash_host_noalloc(host_key, host_value, key_cache, value_
     cudaMalloc (all free GPU memory already belongs to the serving framework's pool) or must not
     pay its synchronisation.  Batches that do not fit raise ``RuntimeError``; calls that overlap on
     the GPU race on the shared area; the first call per device should precede any stream capture."""
-    kv = parse_kv_cache_dtype(kv_cache_dtype)
-    for t in (host_key, host_value, host_slot_mapping):
-        if t.is_cuda:
-            raise RuntimeError("host entry point needs CPU tensors for key, value and slot_mapping")
-    H, D = host_key.shape[1], host_key.shape[2]
-    if H > 1 and (host_key.stride(1) != D or host_value.stride(1) != D):
-        raise RuntimeError("host key/value must have contiguous heads")
+    kv, H, D = _host_entry_args(host_key, host_value, host_slot_mapping, kv_cache_dtype)
     _check(lib().kvc_reshape_and_cache_flash_host_noalloc(
         host_key.data_ptr(), host_value.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
         host_slot_mapping.data_ptr(), host_slot_mapping.shape[0], H, D, key_cache.shape[1],
