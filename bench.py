@@ -258,6 +258,45 @@ def cpu_oracle_rate(w, budget_s: float, tokens: int | None = None):
     return T * n / dt, threads, T, n, dt
 
 
+def cpu_torch_loop_rate(w, budget_s: float, host_blocks: int = 4096):
+    """tokens/s of the reference's own CPU statement of the op: the per-token torch loop of its tests
+    (oracle/torch_reference.py), same bounded sample as ``cpu_oracle_pass``."""
+    from oracle import torch_reference
+
+    T = w.num_tokens
+    key, value = w.key.contiguous(), w.value.contiguous()
+    slots = w.slot_mapping.clone()
+    bs = w.block_size
+    act = slots >= 0
+    uniq, inv = torch.unique(torch.div(slots[act], bs, rounding_mode="floor"), return_inverse=True)
+    host_blocks = max(host_blocks, int(uniq.numel()))
+    slots[act] = inv * bs + slots[act] % bs
+    cdt = w.cache_dtype
+    raw = torch.uint8 if cdt != key.dtype else cdt
+    if w.layout == "flash":
+        kc = torch.zeros(host_blocks, bs, w.num_heads, w.head_size, dtype=raw)
+        vc = torch.zeros_like(kc)
+        fn = torch_reference.reshape_and_cache_flash
+    else:
+        x = 16 // torch.empty((), dtype=cdt).element_size()
+        kc = torch.zeros(host_blocks, w.num_heads, w.head_size // x, bs, x, dtype=raw)
+        vc = torch.zeros(host_blocks, w.num_heads, w.head_size, bs, dtype=raw)
+        fn = torch_reference.reshape_and_cache
+    if cdt != key.dtype:
+        kc, vc = kc.view(cdt), vc.view(cdt)
+    torch.set_num_threads(host_threads())
+    args = (key, value, kc, vc, slots, w.kv_cache_dtype, float(w.k_scale), float(w.v_scale))
+    fn(*args)
+    n, t0 = 0, time.perf_counter()
+    while True:
+        fn(*args)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= budget_s:
+            break
+    return T * n / dt, torch.get_num_threads(), n, dt
+
+
 def run_reference_arm(ns) -> None:
     """--impl reference: the CPU implementation of the path alone, same metric and config."""
     rank = int(os.environ.get("RANK", "0"))
@@ -443,6 +482,10 @@ def run_b200_arm(ns):
         rate, threads, T, n, dt = cpu_oracle_rate(workloads.BY_NAME[ns.workload](variant=0), ns.cpu_seconds)
         cpu = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
                "sample": f"{n} passes over {T} tokens of the batch into a 4096-block host cache, {dt:.1f} s"}
+        # also what the reference itself runs on a CPU: the per-token torch loop of its tests
+        trate, tthreads, tn, tdt = cpu_torch_loop_rate(workloads.BY_NAME[ns.workload](variant=0), 3.0)
+        cpu["torch_loop"] = {"value": trate, "unit": "tokens/s", "cores": tthreads,
+                             "sample": f"{tn} passes of the reference tests' per-token torch loop, {tdt:.1f} s"}
 
     line = None
     if rank == 0:

@@ -139,3 +139,28 @@ def test_three_instruction_division_is_exact_on_a_subsample():
     r = subprocess.run([exe, "16"], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "mismatches 0" in r.stdout
+
+
+@pytest.mark.parametrize("layout", ["flash", "paged"])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("kv", ["auto", "fp8", "fp8_e5m2"])
+def test_c_oracle_equals_the_torch_loops_of_the_reference_tests(layout, dtype, kv):
+    """Beyond the committed fixtures: the C oracle against the torch restatement of the reference's
+    expected-result loops on fresh random inputs (strided key/value, padding, several scales)."""
+    from oracle import torch_reference
+    torch.manual_seed(hash((layout, str(dtype), kv)) % 1000)
+    T, Hh, D, bs, nb = 97, 3, 32, 8, 20
+    qkv = (torch.randn(T, 3, Hh, D) * 2).to(dtype)
+    key, value = qkv[:, 1], qkv[:, 2]
+    slots = torch.randperm(nb * bs)[:T]
+    slots[::6] = -1
+    cdt = H.cache_torch_dtype(dtype, kv)
+    x = 16 // torch.empty((), dtype=cdt).element_size()
+    shapes = ((nb, bs, Hh, D), (nb, bs, Hh, D)) if layout == "flash" else ((nb, Hh, D // x, bs, x), (nb, Hh, D, bs))
+    for ks, vs in ((0.011, 0.013), (1.0, 0.5), (float(key.float().abs().max()) / 448, 3.0)):
+        a = [H.fill_pattern_(torch.empty(s, dtype=cdt), i) for i, s in enumerate(shapes)]
+        b = [t.clone() for t in a]
+        H.oracle_call(layout, key, value, a[0], a[1], slots, kv, ks, vs)
+        getattr(torch_reference, "reshape_and_cache_flash" if layout == "flash" else "reshape_and_cache")(
+            key, value, b[0], b[1], slots, kv, ks, vs)
+        assert H.same_bytes(a[0], b[0]) and H.same_bytes(a[1], b[1]), (ks, vs)
