@@ -28,6 +28,8 @@
  *     kernel (default: half of one resident wave; 0 disables);
  *     KVC_TEST_MAX_ITEMS_PER_LAUNCH=<n> lowers the work-item limit at which
  *     kvc_reshape_and_cache_flash splits a batch into several launches (test hook).
+ *     (The torch op layer additionally honours KVC_DEBUG_SLOTS=1: validate slot_mapping
+ *     with kvc_count_bad_slots before every scatter, synchronising; debugging only.)
  *   - fp8 stores compute float(x) / scale in IEEE fp32 (correctly rounded),
  *     then round to nearest even onto the fp8 grid and saturate at the largest
  *     finite value (448 for e4m3, 57344 for e5m2); NaN becomes 0x7F.

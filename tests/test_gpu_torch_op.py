@@ -134,3 +134,33 @@ def test_device_guard_on_second_gpu():
     ops.reshape_and_cache_flash(key, value, kc, vc, slots, "auto", ks, vs)
     torch.cuda.synchronize(dev)
     assert H.same_bytes(kc.reshape(-1, 8, 64)[slots], key.contiguous())
+
+
+def test_debug_slot_validation_is_opt_in(cuda_device):
+    """KVC_DEBUG_SLOTS=1 makes the torch layer count out-of-range slots on the device and raise BEFORE
+    the scatter is launched (nothing is ever written through a bad slot); off by default."""
+    import os
+    import subprocess
+    import sys
+    from tests.conftest import PKG_ROOT, REPO
+    code = r'''
+import sys, torch
+sys.path[:0] = [%r, %r]
+from vllm_xpu_kernels import ops
+dev = torch.device("cuda:0")
+key = torch.randn(8, 2, 64, device=dev).to(torch.bfloat16); value = torch.randn_like(key)
+kc = torch.zeros(4, 16, 2, 64, dtype=torch.bfloat16, device=dev); vc = torch.zeros_like(kc)
+one = torch.ones(1, device=dev)
+good = torch.tensor([0, 5, -1, 63, 17, 2, 9, 33], device=dev)
+ops.reshape_and_cache_flash(key, value, kc, vc, good, "auto", one, one)
+bad = good.clone(); bad[3] = 64; bad[6] = 1000
+try:
+    ops.reshape_and_cache_flash(key, value, kc, vc, bad, "auto", one, one)
+except RuntimeError as e:
+    assert "2 entries of slot_mapping are >= num_blocks * block_size = 64" in str(e), str(e)
+    print("rejected")
+torch.cuda.synchronize()
+''' % (REPO, PKG_ROOT)
+    env = dict(os.environ, KVC_DEBUG_SLOTS="1")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "rejected" in r.stdout, r.stdout + r.stderr

@@ -5,8 +5,11 @@
 // device and stream, and hands plain pointers to the CUDA library's C ABI.  There is no
 // CPU path: tensors that are not on a CUDA device are rejected.
 #include <ATen/core/Tensor.h>
+#include <ATen/ops/zeros.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
+
+#include <cstdlib>
 
 #include "dispatch_utils.h"
 #include "kvcache_b200.h"
@@ -66,6 +69,22 @@ CommonArgs check_common(const char* op, const at::Tensor& key, const at::Tensor&
 
 void check_rc(const char* op, int rc) { TORCH_CHECK(rc == KVC_OK, op, ": ", kvc_last_error()); }
 
+// Opt-in debugging (KVC_DEBUG_SLOTS=1): count slots >= num_slots on the device and fail before the
+// scatter is launched.  It allocates and synchronises, so it is off by default and must not be
+// used under CUDA-graph capture.  The reference performs no such check.
+void debug_check_slots(const char* op, const at::Tensor& slot_mapping, int64_t num_slots, cudaStream_t stream) {
+  static const bool enabled = [] {
+    const char* e = std::getenv("KVC_DEBUG_SLOTS");
+    return e != nullptr && e[0] != '\0' && e[0] != '0';
+  }();
+  if (!enabled || slot_mapping.size(0) == 0) return;
+  at::Tensor bad = at::zeros({1}, slot_mapping.options());
+  check_rc(op, kvc_count_bad_slots(slot_mapping.data_ptr<int64_t>(), slot_mapping.size(0), num_slots,
+                                   bad.data_ptr<int64_t>(), stream));
+  const int64_t n = bad.item<int64_t>();
+  TORCH_CHECK(n == 0, op, ": ", n, " entries of slot_mapping are >= num_blocks * block_size = ", num_slots);
+}
+
 }  // namespace
 
 void reshape_and_cache(at::Tensor& key, at::Tensor& value, at::Tensor& key_cache, at::Tensor& value_cache,
@@ -88,6 +107,7 @@ void reshape_and_cache(at::Tensor& key, at::Tensor& value, at::Tensor& key_cache
 
   const c10::cuda::CUDAGuard guard(key.device());
   const cudaStream_t stream = c10::cuda::getCurrentCUDAStream().stream();
+  debug_check_slots(op, slot_mapping, key_cache.size(0) * block_size, stream);
   check_rc(op, kvc_reshape_and_cache(key.data_ptr(), value.data_ptr(), key_cache.data_ptr(),
                                      value_cache.data_ptr(), slot_mapping.data_ptr<int64_t>(), a.num_tokens,
                                      a.num_heads, a.head_size, block_size, x, key.stride(0), key.stride(1),
@@ -116,6 +136,7 @@ void reshape_and_cache_flash(at::Tensor& key, at::Tensor& value, at::Tensor& key
 
   const c10::cuda::CUDAGuard guard(key.device());
   const cudaStream_t stream = c10::cuda::getCurrentCUDAStream().stream();
+  debug_check_slots(op, slot_mapping, key_cache.size(0) * key_cache.size(1), stream);
   check_rc(op, kvc_reshape_and_cache_flash(
                    key.data_ptr(), value.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
                    slot_mapping.data_ptr<int64_t>(), a.num_tokens, a.num_heads, a.head_size, key_cache.size(1),
@@ -157,6 +178,7 @@ void concat_and_cache_mla(at::Tensor& kv_c, at::Tensor& k_pe, at::Tensor& kv_cac
   }
   const c10::cuda::CUDAGuard guard(dev);
   const cudaStream_t stream = c10::cuda::getCurrentCUDAStream().stream();
+  debug_check_slots(op, slot_mapping, kv_cache.size(0) * kv_cache.size(1), stream);
   check_rc(op, kvc_concat_and_cache_mla(kv_c.data_ptr(), k_pe.data_ptr(), kv_cache.data_ptr(),
                                         slot_mapping.data_ptr<int64_t>(), num_tokens, kv_lora_rank, pe_dim,
                                         kv_cache.size(1), kv_c.stride(0), k_pe.stride(0), kv_cache.stride(0),
