@@ -73,3 +73,45 @@ def test_shard_heads_rejects_uneven_split():
     parts = [workloads.shard_heads(w, r, 4) for r in range(4)]
     assert torch.equal(torch.cat([p.key for p in parts], dim=1), w.key)
     assert all(p.slot_mapping is w.slot_mapping for p in parts)
+
+
+def _failing_worker(rank: int, world: int, port: int, out_dir: str) -> None:
+    """Rank 1 leaves between steps (no collective in flight); rank 0's next reduction must end with an
+    error within the process-group timeout instead of hanging."""
+    import datetime
+    import time
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if here not in sys.path:
+        sys.path.insert(0, here)
+    import bench
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    assert bench.max_over_ranks(dist, float(rank), device="cpu") == 1.0  # one healthy step first
+    if rank == 1:
+        os._exit(0)  # the rank disappears without a goodbye
+    time.sleep(1.0)
+    t0 = time.monotonic()
+    try:
+        bench.max_over_ranks(dist, 5.0, device="cpu")
+        outcome = "no error"
+    except Exception as e:  # noqa: BLE001  (gloo reports a closed connection or a timeout)
+        outcome = "detected: " + type(e).__name__
+    took = time.monotonic() - t0
+    with open(os.path.join(out_dir, "outcome"), "w") as f:
+        f.write(f"{outcome} after {took:.1f}s")
+    os._exit(0)  # skip the process-group teardown, which would wait for the missing rank
+
+
+def test_missing_rank_is_detected_not_waited_for(tmp_path):
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=60)
+    assert all(not p.is_alive() for p in procs), "a rank hung"
+    text = (tmp_path / "outcome").read_text()
+    assert text.startswith("detected"), text
+    assert float(text.rsplit("after ", 1)[1][:-1]) < 30.0
