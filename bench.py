@@ -194,14 +194,20 @@ def host_threads() -> int:
         return max(1, os.cpu_count() or 1)
 
 
-def make_batch_sets(name: str, rank: int, world: int, scaling: str, nbuf: int):
-    """nbuf independent batches of the named workload for this rank (CPU tensors)."""
+def make_batch_sets(name: str, rank: int, world: int, scaling: str, nbuf: int, tokens: int | None = None):
+    """nbuf independent batches of the named workload for this rank (CPU tensors).  ``tokens`` resizes
+    the C4 batch (size studies only; the named configuration is the default)."""
+    def make(variant: int):
+        if tokens is not None and name == "C4":
+            return workloads.c4(variant=variant, num_tokens=tokens)
+        return workloads.BY_NAME[name](variant=variant)
+
     sets = []
     for b in range(nbuf):
         if scaling == "strong":
-            w = workloads.shard_heads(workloads.BY_NAME[name](variant=b), rank, world)
+            w = workloads.shard_heads(make(b), rank, world)
         else:
-            w = workloads.BY_NAME[name](variant=b + 100 * rank)
+            w = make(b + 100 * rank)
         sets.append(w)
     return sets
 
@@ -356,7 +362,7 @@ def run_b200_arm(ns):
     torch.cuda.set_device(dev)
     cabi.lib()
 
-    sets = make_batch_sets(ns.workload, rank, world, ns.scaling, NBUF)
+    sets = make_batch_sets(ns.workload, rank, world, ns.scaling, NBUF, ns.tokens)
     w0 = sets[0]
     paged = w0.layout == "paged"
     ksh, vsh = w0.cache_shapes()
@@ -536,6 +542,7 @@ def main() -> None:
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--workload", choices=list(workloads.BY_NAME), default="C4")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--tokens", type=int, default=None, help="resize the C4 batch (size studies; default 16384)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="time budget of the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ns = ap.parse_args()
