@@ -250,6 +250,57 @@ KVC_API int kvc_dynamic_per_token_scaled_fp8_quant(void* out, const void* input,
                                                    void* stream);
 
 /*
+ * Rotary position embedding, in place.  Replaces rotary_embedding of the reference: host launcher
+ * csrc/pos_encoding_kernels.cpp:165-286, device code :9-162, prototype csrc/ops.h:33-39, schema
+ * csrc/torch_bindings.cpp:61-65.
+ *
+ *   positions      int64 [num_tokens]
+ *   query          [num_tokens, num_heads, head_size]; token stride query_stride_t, head stride
+ *                  query_stride_h (elements), last dim contiguous; a flat [num_tokens, heads * head_size]
+ *                  tensor is the case query_stride_h == head_size
+ *   key            the same with num_kv_heads, or NULL (then num_kv_heads is ignored)
+ *   cos_sin_cache  contiguous [max_position, rot_dim] of the tensors' type: row p holds rot_dim/2 cosines,
+ *                  then rot_dim/2 sines
+ *
+ * For every token t, head h and i < rot_dim/2, with c = cos_sin_cache[positions[t]][i] and
+ * s = cos_sin_cache[positions[t]][rot_dim/2 + i]:
+ *     x' = x*c - y*s,   y' = y*c + x*s
+ * where (x, y) = elements (i, rot_dim/2 + i) of the head when is_neox, else (2i, 2i+1); each product
+ * and the sum are rounded to the tensors' type (three roundings, no fused multiply-add), which is what
+ * the torch expression of the reference's tests/ops/rotary_embedding_op.py:11-30 computes.  Elements at
+ * and above rot_dim are not touched.  A token whose position is outside [0, max_position) is left
+ * unrotated (the reference would read outside the table).  The reference takes one head stride, from
+ * query, for both tensors (pos_encoding_kernels.cpp:209-211); here key has its own.
+ */
+KVC_API int kvc_rotary_embedding(const int64_t* positions, void* query, void* key, const void* cos_sin_cache,
+                                 int64_t num_tokens, int64_t num_heads, int64_t num_kv_heads, int64_t head_size,
+                                 int64_t rot_dim, int64_t max_position, int64_t query_stride_t,
+                                 int64_t query_stride_h, int64_t key_stride_t, int64_t key_stride_h, int is_neox,
+                                 int in_dtype, void* stream);
+
+/*
+ * No counterpart in the reference: kvc_rotary_embedding followed by kvc_reshape_and_cache_flash of the
+ * rotated key and the value, in one pass, so that the key rows are read from HBM once and there is one
+ * launch instead of two.  Results are bit-identical to the two calls in sequence.
+ *
+ *   tokens [0, num_slot_tokens) have a slot in slot_mapping (negative = skip); tokens from there to
+ *   num_tokens are rotated only.  value and the caches are as in kvc_reshape_and_cache_flash.
+ *   write_back_key == 0 leaves `key` as it was (un-rotated) and only the cache receives the rotated
+ *   rows: for callers whose attention reads keys from the cache alone.
+ *
+ * Needs 16-byte access everywhere (pointers, strides, rot_dim/2 or rot_dim, head_size - rot_dim in
+ * whole 16-byte vectors); otherwise KVC_ERR_UNSUPPORTED, and the two separate calls do the job.
+ */
+KVC_API int kvc_rotary_embedding_and_cache_flash(
+    const int64_t* positions, void* query, void* key, const void* value, const void* cos_sin_cache, void* key_cache,
+    void* value_cache, const int64_t* slot_mapping, int64_t num_tokens, int64_t num_slot_tokens, int64_t num_heads,
+    int64_t num_kv_heads, int64_t head_size, int64_t rot_dim, int64_t max_position, int64_t block_size,
+    int64_t query_stride_t, int64_t query_stride_h, int64_t key_stride_t, int64_t key_stride_h,
+    int64_t value_stride_t, int64_t value_stride_h, int64_t block_stride, int64_t page_stride, int64_t head_stride,
+    int is_neox, int write_back_key, int in_dtype, int kv_dtype, const float* k_scale, const float* v_scale,
+    void* stream);
+
+/*
  * Debug aid the reference lacks: counts entries of slot_mapping that are
  * >= num_slots (negative entries are legal padding and not counted) into
  * *bad_count, a DEVICE int64 the caller owns; the kernel overwrites it.

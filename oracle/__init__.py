@@ -63,6 +63,12 @@ def lib() -> ctypes.CDLL:
         L.orc_f32_to_e4m3.argtypes = [f32]
         L.orc_f32_to_e5m2.restype = ctypes.c_uint8
         L.orc_f32_to_e5m2.argtypes = [f32]
+        L.orc_rotary_embedding.restype = ci
+        L.orc_rotary_embedding.argtypes = [vp, vp, vp, vp] + [i64] * 9 + [ci, ci]
+        L.orc_f32_to_bf16.restype = ctypes.c_uint16
+        L.orc_f32_to_bf16.argtypes = [f32]
+        L.orc_f32_to_f16.restype = ctypes.c_uint16
+        L.orc_f32_to_f16.argtypes = [f32]
         L.orc_max_threads.restype = ci
         _lib = L
     return _lib
@@ -218,6 +224,43 @@ def per_token_fp8_quant(x: np.ndarray, in_dtype: str, fp8: str, scale_ub=None):
     lib().orc_per_token_fp8_quant(out.ctypes.data, scales.ctypes.data, x.ctypes.data, T, hidden, IN_DTYPES[in_dtype],
                                   KV_DTYPES[fp8], ctypes.cast(ub, ctypes.c_void_p) if ub is not None else None)
     return out, scales
+
+
+def rotary_embedding(positions, query, key, head_size: int, cos_sin_cache, is_neox: bool, in_dtype: str) -> None:
+    """In-place oracle for ``_C.rotary_embedding``.  ``query`` / ``key`` (or None) are numpy views shaped
+    ``[T, heads, head_size]`` (any token and head stride, contiguous last dim) or ``[T, heads * head_size]``;
+    ``positions`` int64 ``[T]``; ``cos_sin_cache`` contiguous ``[max_position, rot_dim]`` of the same type."""
+    positions = np.ascontiguousarray(positions, dtype=np.int64).reshape(-1)
+    T = positions.shape[0]
+
+    def geometry(a):
+        if a.ndim == 2:
+            if a.shape[1] % head_size or (a.shape[1] > 1 and _estrides(a)[1] != 1):
+                raise ValueError("flat query/key must be [T, heads * head_size] with a contiguous last dim")
+            return a.shape[1] // head_size, _estrides(a)[0], head_size
+        if a.ndim != 3 or a.shape[2] != head_size or _estrides(a)[2] != 1:
+            raise ValueError("query/key must be [T, heads, head_size] with a contiguous last dim")
+        return a.shape[1], _estrides(a)[0], _estrides(a)[1]
+
+    want = np.float32 if in_dtype == "f32" else np.uint16
+    for a in (query, key, cos_sin_cache):
+        if a is not None and a.dtype != want:
+            raise TypeError(f"{in_dtype} tensors must be {np.dtype(want)} arrays")
+    if query.shape[0] != T or (key is not None and key.shape[0] != T):
+        raise ValueError("query, key and positions must have the same number of tokens")
+    if not cos_sin_cache.flags.c_contiguous:
+        raise ValueError("cos_sin_cache must be contiguous")
+    hq, qs, qhs = geometry(query)
+    hk, ks, khs = geometry(key) if key is not None else (hq, 0, 0)
+    max_pos, rot_dim = cos_sin_cache.shape
+    if rot_dim % 2 or rot_dim > head_size:
+        raise ValueError("rot_dim must be even and at most head_size")
+    rc = lib().orc_rotary_embedding(
+        positions.ctypes.data, query.ctypes.data, None if key is None else key.ctypes.data,
+        cos_sin_cache.ctypes.data, T, hq, hk, rot_dim, max_pos, qs, ks, qhs, khs, int(bool(is_neox)),
+        IN_DTYPES[in_dtype])
+    if rc != 0:
+        raise IndexError("positions holds an entry outside [0, max_position)")
 
 
 def convert_table(in_dtype: str, kv_cache_dtype: str, scale: float) -> np.ndarray:

@@ -20,6 +20,9 @@
  *                                csrc/quantization/fp8/fp8_quant.cpp:15-45, :47-131,
  *                                fp8_quant.h:56-102; element rule quant_utils.h:80-91
  *                                (multiply by 1.0f/scale, clamp, cast)
+ *   orc_rotary_embedding         csrc/pos_encoding_kernels.cpp:9-37 (pair update), :40-88 (loops over
+ *                                heads), :174-232 (host sizes and strides); torch form
+ *                                tests/ops/rotary_embedding_op.py:11-30, :85-118
  *   element conversion           csrc/quantization/fp8/quant_utils.h:62-78
  *                                (auto: bit copy; fp8: float(src) / scale,
  *                                then cast)
@@ -42,7 +45,9 @@
  * conversion the reference calls, because the reference's own cache tests switch fp8 off
  * (tests/test_cache.py:37 there) -- there is no reference test vector for fp8 cache bytes.
  * The fp8 quantisation ops are pinned by the torch recipes of the reference's
- * tests/test_fp8_quant.py:20-75.
+ * tests/test_fp8_quant.py:20-75.  The rotary embedding is pinned by fixtures computed with the
+ * reference's RotaryEmbedding.forward_native (tests/ops/rotary_embedding_op.py); its own test
+ * (tests/test_rotary_embedding.py) checks the op's schema only, no values.
  *
  * The paged op divides by the scale like the flash op; the reference's paged
  * kernel multiplies (csrc/cache.cpp:70-79) in a branch its own tests disable.
@@ -329,6 +334,100 @@ void orc_per_token_fp8_quant(uint8_t* out, float* scales, const void* in, int64_
     const float inv = 1.0f / s;
     for (int64_t i = 0; i < hidden; ++i) out[t * hidden + i] = quant_elem(load_as_f32(in, t * hidden + i, in_dt), inv, kv);
   }
+}
+
+/* ------------------------------------------------------------------------------------------
+ * rotary position embedding, in place on query and (optionally) key
+ * ------------------------------------------------------------------------------------------ */
+static inline uint16_t f32_to_bf16_rne(float f) {
+  uint32_t u = f2u(f);
+  if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x0040u); /* quiet NaN */
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+static inline uint16_t f32_to_f16_rne(float f) {
+  const uint32_t u = f2u(f);
+  const uint16_t sign = (uint16_t)((u >> 16) & 0x8000u);
+  const uint32_t a = u & 0x7FFFFFFFu;
+  if (a > 0x7F800000u) return (uint16_t)(sign | 0x7E00u);
+  if (a >= 0x477FF000u) return (uint16_t)(sign | 0x7C00u); /* >= 65520 rounds to inf */
+  const int e = (int)(a >> 23);
+  if (e >= 113) { /* normal half */
+    uint32_t r = a >> 13;
+    const uint32_t rem = a & 0x1FFFu;
+    if (rem > 0x1000u || (rem == 0x1000u && (r & 1u))) r += 1u;
+    r -= (uint32_t)112 << 10;
+    return (uint16_t)(sign | r);
+  }
+  if (e < 102) return sign; /* below half of the smallest subnormal (2^-25) rounds to zero */
+  const uint32_t mant = (a & 0x7FFFFFu) | 0x800000u; /* value = mant * 2^(e-150); unit 2^-24 */
+  const int sh = 126 - e;                            /* mant >> sh = value / 2^-24 */
+  uint32_t q = mant >> sh;
+  const uint32_t rem = mant & ((1u << sh) - 1u);
+  const uint32_t half = 1u << (sh - 1);
+  if (rem > half || (rem == half && (q & 1u))) q += 1u;
+  return (uint16_t)(sign | q);
+}
+
+uint16_t orc_f32_to_bf16(float f) { return f32_to_bf16_rne(f); }
+uint16_t orc_f32_to_f16(float f) { return f32_to_f16_rne(f); }
+
+/* One arithmetic result rounded to the tensor's type, as a torch elementwise op on that dtype
+ * does (compute in fp32, round once to the 16-bit type). */
+static inline float round_to(float f, int dt) {
+  if (dt == ORC_F16) return orc_f16_to_f32(f32_to_f16_rne(f));
+  if (dt == ORC_BF16) return orc_bf16_to_f32(f32_to_bf16_rne(f));
+  return f;
+}
+static inline void store_from_f32(void* p, int64_t i, float f, int dt) {
+  if (dt == ORC_F32) ((float*)p)[i] = f;
+  else if (dt == ORC_F16) ((uint16_t*)p)[i] = f32_to_f16_rne(f);
+  else ((uint16_t*)p)[i] = f32_to_bf16_rne(f);
+}
+
+/* pos_encoding_kernels.cpp:9-37: x' = x*cos - y*sin, y' = y*cos + x*sin, every product and the
+ * sum each rounded to the tensor's type (three roundings per output, no fused multiply-add). */
+static void rope_heads(void* arr, int64_t heads, int64_t token_off, int64_t head_stride, const void* cs,
+                       int64_t cs_off, int64_t embed_dim, int is_neox, int dt) {
+  for (int64_t h = 0; h < heads; ++h) {
+    const int64_t base = token_off + h * head_stride;
+    for (int64_t r = 0; r < embed_dim; ++r) {
+      const int64_t xi = is_neox ? r : 2 * r;
+      const int64_t yi = is_neox ? embed_dim + r : 2 * r + 1;
+      const float c = load_as_f32(cs, cs_off + r, dt);
+      const float s = load_as_f32(cs, cs_off + embed_dim + r, dt);
+      const float x = load_as_f32(arr, base + xi, dt);
+      const float y = load_as_f32(arr, base + yi, dt);
+      const float xc = round_to(x * c, dt), ys = round_to(y * s, dt);
+      const float yc = round_to(y * c, dt), xs = round_to(x * s, dt);
+      store_from_f32(arr, base + xi, xc - ys, dt);
+      store_from_f32(arr, base + yi, yc + xs, dt);
+    }
+  }
+}
+
+/* Strides in elements.  `key` may be NULL.  Returns 1 if a position is outside [0, max_position). */
+int orc_rotary_embedding(const int64_t* positions, void* query, void* key, const void* cos_sin_cache,
+                         int64_t num_tokens, int64_t num_heads, int64_t num_kv_heads, int64_t rot_dim,
+                         int64_t max_position, int64_t query_stride, int64_t key_stride,
+                         int64_t query_head_stride, int64_t key_head_stride, int is_neox, int dt) {
+  const int64_t embed_dim = rot_dim / 2;
+  int bad = 0;
+#pragma omp parallel for schedule(static) reduction(| : bad)
+  for (int64_t t = 0; t < num_tokens; ++t) {
+    const int64_t pos = positions[t];
+    if (pos < 0 || pos >= max_position) {
+      bad |= 1;
+      continue;
+    }
+    rope_heads(query, num_heads, t * query_stride, query_head_stride, cos_sin_cache, pos * rot_dim, embed_dim,
+               is_neox, dt);
+    if (key)
+      rope_heads(key, num_kv_heads, t * key_stride, key_head_stride, cos_sin_cache, pos * rot_dim, embed_dim,
+                 is_neox, dt);
+  }
+  return bad;
 }
 
 int orc_max_threads(void) {

@@ -37,3 +37,20 @@ def run_gather(src_cache, dst, block_table, cu_seq_lens, batch_size: int, seq_st
     import oracle
     oracle.gather_cache(as_np(src_cache), as_np(dst), block_table.numpy(), cu_seq_lens.numpy(), batch_size,
                         None if seq_starts is None else seq_starts.numpy())
+
+
+def run_rope(positions, query, key, head_size: int, cos_sin_cache, is_neox: bool) -> None:
+    """In-place rotary embedding on CPU torch tensors: positions [T] or [B, S]; query/key
+    [.., heads, head_size] or [.., heads * head_size] (leading dims collapse to tokens)."""
+    import oracle
+
+    def tokens_first(t):
+        if t is None:
+            return None
+        lead = positions.dim()
+        return t.reshape(-1, *t.shape[lead:]) if lead > 1 else t
+
+    q, k = tokens_first(query), tokens_first(key)
+    assert q.data_ptr() == query.data_ptr() and (k is None or k.data_ptr() == key.data_ptr()), "reshape copied"
+    oracle.rotary_embedding(positions.reshape(-1).numpy(), as_np(q), None if k is None else as_np(k), head_size,
+                            as_np(cos_sin_cache), is_neox, ORC_IN[query.dtype])

@@ -10,6 +10,10 @@ What comes from the reference, imported as Python and executed on the CPU:
     views of one allocation) and ``seed_everything`` from its tests/utils.py;
   * PyTorch's own ``float -> float8`` cast, which is the conversion the reference
     kernels call (csrc/quantization/fp8/quant_utils.h:70-74 there).
+  * ``RotaryEmbedding`` from its tests/ops/rotary_embedding_op.py: the cos/sin table recipe and
+    ``forward_native``, the torch statement of the rotary embedding op (imported with empty
+    stand-ins for the compiled ``vllm_xpu_kernels._C*`` modules, which that file imports but
+    ``forward_native`` never calls).
 What is restated here because it only exists inline in GPU-only test functions:
   * the MLA and gather recipes and expectations (tests/test_cache.py:337-375, :423-477);
   * the input recipe (``qkv = randn(T, 3, H, D); _, key, value = qkv.unbind(1)``,
@@ -23,9 +27,12 @@ fp8 as uint8, so the files are readable without torch.
 from __future__ import annotations
 
 import argparse
+import importlib
 import importlib.util
 import os
 import random
+import sys
+import types
 
 import numpy as np
 import torch
@@ -40,6 +47,30 @@ def load_reference_utils(ref_root: str):
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     return mod
+
+
+def load_reference_rotary(ref_root: str):
+    """The reference's RotaryEmbedding class.  Its module imports the compiled extension modules at
+    import time; forward_native is pure torch, so empty stand-ins are enough."""
+    saved = {k: sys.modules.pop(k) for k in list(sys.modules) if k == "tests" or k.startswith("tests.")
+             or k == "vllm_xpu_kernels" or k.startswith("vllm_xpu_kernels.")}
+    try:
+        pkg = types.ModuleType("vllm_xpu_kernels")
+        pkg.__path__ = []
+        sys.modules["vllm_xpu_kernels"] = pkg
+        for sub in ("_C", "_moe_C", "_xpu_C"):
+            sys.modules["vllm_xpu_kernels." + sub] = types.ModuleType("vllm_xpu_kernels." + sub)
+        sys.path.insert(0, ref_root)
+        try:
+            mod = importlib.import_module("tests.ops.rotary_embedding_op")
+        finally:
+            sys.path.remove(ref_root)
+        return mod.RotaryEmbedding
+    finally:
+        for k in [k for k in sys.modules if k == "tests" or k.startswith("tests.") or k == "vllm_xpu_kernels"
+                  or k.startswith("vllm_xpu_kernels.")]:
+            del sys.modules[k]
+        sys.modules.update(saved)
 
 
 def bits(t: torch.Tensor) -> np.ndarray:
@@ -193,6 +224,37 @@ def make_quant_case(ru, dtype: str, fp8: str, T: int, hidden: int, seed: int, wi
     return d
 
 
+def make_rope_case(RotaryEmbedding, dtype: str, is_neox: bool, head_size: int, rot_dim: int, max_position: int,
+                   seq_len: int, num_heads: int, num_kv_heads: int, use_key: bool, head_pad: int, flat: bool,
+                   seed: int) -> dict:
+    """Inputs as in tests/test_rotary_embedding.py:52-87 of the reference (randint positions, randn
+    query/key cut out of a wider last dim when ``head_pad``, optionally flattened to
+    [.., heads * head_size]); expected = RotaryEmbedding.forward_native on the CPU with the table cast
+    to the tensors' type, which is what the op is handed (tests/test_rotary_embedding.py:21)."""
+    tdt = DT[dtype]
+    torch.manual_seed(seed)
+    rot = RotaryEmbedding(head_size, rot_dim, max_position, 10000, is_neox, torch.float32)
+    table = rot.cos_sin_cache.to(tdt)
+    rot.cos_sin_cache = table
+    positions = torch.randint(0, max_position, (seq_len,))
+    q_store = torch.randn(seq_len, num_heads, head_size + head_pad, dtype=tdt)
+    k_store = torch.randn(seq_len, num_kv_heads, head_size + head_pad, dtype=tdt)
+    query = q_store[..., :head_size]
+    key = k_store[..., :head_size] if use_key else None
+    if flat:
+        assert head_pad == 0
+        query = query.flatten(start_dim=-2)
+        key = key.flatten(start_dim=-2) if use_key else None
+    q_out, k_out = rot.forward_native(positions, query.clone(), key.clone() if use_key else None)
+    d = dict(op="rope", dtype=dtype, is_neox=np.bool_(is_neox), head_size=head_size, rot_dim=rot_dim, flat=np.bool_(flat),
+             head_pad=head_pad, positions=positions.numpy(), cos_sin_cache=bits(table), query_store=bits(q_store),
+             query_after=bits(q_out.reshape(seq_len, num_heads, head_size)))
+    if use_key:
+        d["key_store"] = bits(k_store)
+        d["key_after"] = bits(k_out.reshape(seq_len, num_kv_heads, head_size))
+    return d
+
+
 def make_tables() -> dict:
     """torch's e4m3 / e5m2 cast over every bf16 and fp16 bit pattern at a few scales."""
     out = {}
@@ -210,8 +272,13 @@ def make_tables() -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path to a checkout of the reference project")
+    ap.add_argument("--only", default=None, help="write only the fixtures whose name starts with this prefix")
     ns = ap.parse_args()
     ru = load_reference_utils(ns.reference)
+    RotaryEmbedding = load_reference_rotary(ns.reference)
+
+    def wanted(name: str) -> bool:
+        return ns.only is None or name.startswith(ns.only)
 
     cases = []
     # auto: the reference's own matrix (dtypes x head sizes x block sizes, tests/test_cache.py:14-19),
@@ -244,9 +311,9 @@ def main() -> None:
     for c in cases:
         name = "{layout}_{dtype}_{kv_cache_dtype}_T{T}_H{H}_D{D}_bs{bs}_nb{nb}_s{seed}_div{d}".format(
             d=int(c["scale_div"]), **c) + ("_skip" if c.get("n_skip") else "")
-        data = make_case(ru, **c)
-        np.savez_compressed(os.path.join(HERE, name + ".npz"), **data)
         names.append(name)
+        if wanted(name):
+            np.savez_compressed(os.path.join(HERE, name + ".npz"), **make_case(ru, **c))
     extra = []
     for dtype in ("half", "bfloat16", "float"):
         extra.append(("mla_%s_auto_T42_R512_P64_bs16_nb8" % dtype, make_mla_case(ru, dtype, "auto", 42, 512, 64, 16, 8, 0)))
@@ -263,10 +330,27 @@ def main() -> None:
                 extra.append(("quant_%s_%s_T%d_h%d" % (dtype, fp8, T, hidden),
                               make_quant_case(ru, dtype, fp8, T, hidden, qi, with_ub=bool(qi % 2))))
                 qi += 1
+    # rotary embedding: the reference test's matrix (tests/test_rotary_embedding.py:43-51: neox / gpt-j,
+    # head sizes 32 and 108 with rotary_dim 32, with and without key, padded heads, flat layout), shrunk to
+    # 11 tokens, in all three types, plus full rotation at head size 128 with grouped kv heads
+    ri = 100
+    for dtype in ("float", "half", "bfloat16"):
+        for is_neox in (True, False):
+            for head_size, rot_dim, hq, hk, use_key, pad, flat in (
+                    (32, 32, 7, 7, True, 0, False), (108, 32, 7, 7, True, 64, False), (108, 32, 7, 7, False, 0, True),
+                    (32, 32, 7, 7, True, 0, True), (128, 128, 8, 2, True, 0, False), (64, 48, 3, 1, True, 0, False)):
+                ri += 1
+                name = "rope_%s_%s_D%d_R%d_Hq%d_Hk%d%s%s%s" % (
+                    dtype, "neox" if is_neox else "gptj", head_size, rot_dim, hq, hk, "" if use_key else "_nokey",
+                    "_pad%d" % pad if pad else "", "_flat" if flat else "")
+                extra.append((name, lambda a=(dtype, is_neox, head_size, rot_dim, 257 if ri % 2 else 11, 11, hq, hk,
+                                               use_key, pad, flat, ri): make_rope_case(RotaryEmbedding, *a)))
     for name, data in extra:
-        np.savez_compressed(os.path.join(HERE, name + ".npz"), **data)
         names.append(name)
-    np.savez_compressed(os.path.join(HERE, "fp8_tables.npz"), **make_tables())
+        if wanted(name):
+            np.savez_compressed(os.path.join(HERE, name + ".npz"), **(data() if callable(data) else data))
+    if wanted("fp8_tables"):
+        np.savez_compressed(os.path.join(HERE, "fp8_tables.npz"), **make_tables())
     with open(os.path.join(HERE, "MANIFEST.txt"), "w") as f:
         f.write("# written by make_golden.py with torch %s\n" % torch.__version__)
         for n in names + ["fp8_tables"]:

@@ -20,7 +20,8 @@ def golden_files(kind: str = "kv") -> list[str]:
     """Fixture files of one kind: "kv" (flash_* and paged_*), "mla" or "gather"."""
     with open(os.path.join(GOLDEN_DIR, "MANIFEST.txt")) as f:
         names = [ln.strip() for ln in f if ln.strip() and not ln.startswith("#")]
-    prefixes = {"kv": ("flash_", "paged_"), "mla": ("mla_",), "gather": ("gather_",), "quant": ("quant_",)}[kind]
+    prefixes = {"kv": ("flash_", "paged_"), "mla": ("mla_",), "gather": ("gather_",), "quant": ("quant_",),
+                "rope": ("rope_",)}[kind]
     return [n for n in names if n.startswith(prefixes)]
 
 
@@ -50,6 +51,35 @@ class QuantCase:
         self.scales = torch.from_numpy(z["scales"])
         self.out_token = torch.from_numpy(z["out_token"])
         self.scale_ub = float(z["scale_ub"]) if "scale_ub" in z.files else None
+
+
+class RopeCase:
+    """A rotary-embedding fixture with the memory layout it was made with: query/key are
+    [..., :head_size] cuts of wider allocations when the heads are padded, or flattened to
+    [T, heads * head_size]."""
+
+    def __init__(self, fname: str):
+        z = np.load(os.path.join(GOLDEN_DIR, fname))
+        self.dtype = TORCH_DT[str(z["dtype"])]
+        self.is_neox = bool(z["is_neox"])
+        self.head_size = int(z["head_size"])
+        self.rot_dim = int(z["rot_dim"])
+        self.flat = bool(z["flat"])
+        self.positions = torch.from_numpy(z["positions"].astype(np.int64))
+        self.cos_sin_cache = from_bits(z["cos_sin_cache"], self.dtype)
+        self.query_store = from_bits(z["query_store"], self.dtype)
+        self.key_store = from_bits(z["key_store"], self.dtype) if "key_store" in z.files else None
+        self.query_after = from_bits(z["query_after"], self.dtype)
+        self.key_after = from_bits(z["key_after"], self.dtype) if "key_after" in z.files else None
+
+    def views(self, q_store: torch.Tensor, k_store):
+        """(query, key) views of the given allocations, as the op is handed them."""
+        q = q_store[..., :self.head_size]
+        k = None if k_store is None else k_store[..., :self.head_size]
+        if self.flat:
+            q = q.flatten(start_dim=-2)
+            k = None if k is None else k.flatten(start_dim=-2)
+        return q, k
 
 
 class GatherCase:

@@ -98,9 +98,34 @@ def test_torch_extension_registers_reference_schemas():
     }
     for name, sig in quant.items():  # csrc/torch_bindings.cpp:67-88 of the reference
         assert str(getattr(torch.ops._C, name).default._schema) == str(torch._C.parse_schema(f"_C::{name}{sig}"))
+    # csrc/torch_bindings.cpp:61-64 of the reference
+    rope = "(Tensor positions, Tensor! query, Tensor!? key, int head_size, Tensor cos_sin_cache, bool is_neox) -> ()"
+    assert str(torch.ops._C.rotary_embedding.default._schema) == str(
+        torch._C.parse_schema("_C::rotary_embedding" + rope))
     from vllm_xpu_kernels import ops as wrappers
-    for fn in ("reshape_and_cache", "reshape_and_cache_flash", "concat_and_cache_mla", "gather_cache"):
+    for fn in ("reshape_and_cache", "reshape_and_cache_flash", "concat_and_cache_mla", "gather_cache",
+               "rotary_embedding", "rotary_embedding_and_cache_flash"):
         assert callable(getattr(wrappers, fn))
+
+
+def test_rotary_entry_points_validate_without_touching_the_device():
+    L = cabi.lib()
+    p = ctypes.c_void_p(0x1000)
+    # empty batch / no heads: nothing to do
+    assert L.kvc_rotary_embedding(p, p, p, p, 0, 8, 2, 64, 64, 100, 512, 64, 128, 64, 1, 2, None) == 0
+    assert L.kvc_rotary_embedding(p, None, None, p, 4, 0, 0, 64, 64, 100, 0, 0, 0, 0, 1, 2, None) == 0
+    # odd rot_dim, rot_dim > head_size, bad type code, missing table
+    assert L.kvc_rotary_embedding(p, p, p, p, 4, 8, 2, 64, 63, 100, 512, 64, 128, 64, 1, 2, None) == 1
+    assert "rot_dim" in cabi.last_error()
+    assert L.kvc_rotary_embedding(p, p, p, p, 4, 8, 2, 64, 128, 100, 512, 64, 128, 64, 1, 2, None) == 1
+    assert L.kvc_rotary_embedding(p, p, p, p, 4, 8, 2, 64, 64, 100, 512, 64, 128, 64, 1, 7, None) == 2
+    assert L.kvc_rotary_embedding(p, p, p, None, 4, 8, 2, 64, 64, 100, 512, 64, 128, 64, 1, 2, None) == 1
+    # fused: rows of 36 halves cannot be moved in 16-byte pieces -> unsupported, with advice
+    args = [p] * 8 + [4, 4, 2, 2, 36, 12, 100, 16, 72, 36, 72, 36, 72, 36, 16 * 72, 72, 36, 1, 1, 1, 0, None, None, None]
+    assert L.kvc_rotary_embedding_and_cache_flash(*args) == 2
+    assert "kvc_reshape_and_cache_flash" in cabi.last_error()
+    args[9] = 5  # more slot tokens than tokens
+    assert L.kvc_rotary_embedding_and_cache_flash(*args) == 1
 
 
 def test_no_cpu_fallback():

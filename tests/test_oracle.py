@@ -56,6 +56,39 @@ def test_oracle_reproduces_reference_quant_recipes(fname):
     assert (got != c.out_token.numpy()).mean() <= 0.005
 
 
+@pytest.mark.parametrize("fname", H.golden_files("rope"))
+def test_oracle_reproduces_reference_rotary_fixture(fname):
+    """Expected values come from the reference's RotaryEmbedding.forward_native."""
+    c = H.RopeCase(fname)
+    q_store = c.query_store.clone()
+    k_store = None if c.key_store is None else c.key_store.clone()
+    q, k = c.views(q_store, k_store)
+    torch_views.run_rope(c.positions, q, k, c.head_size, c.cos_sin_cache, c.is_neox)
+    assert H.same_bytes(q_store[..., :c.head_size], c.query_after)
+    assert H.same_bytes(q_store[..., c.head_size:], c.query_store[..., c.head_size:])  # padding untouched
+    if k_store is not None:
+        assert H.same_bytes(k_store[..., :c.head_size], c.key_after)
+
+
+def test_rotary_oracle_rounding_helpers_match_torch():
+    """The oracle's float -> f16 / bf16 roundings against torch's casts, over a dense sweep."""
+    L = oracle.lib()
+    g = torch.Generator().manual_seed(11)
+    bits = torch.randint(-2**31, 2**31 - 1, (200000,), generator=g, dtype=torch.int64).to(torch.int32)
+    x = bits.view(torch.float32)
+    x = x[~torch.isnan(x)]
+    edge = torch.tensor([65504.0, 65519.9, 65520.0, 6.1e-5, 5.96e-8, 2.98e-8, 2.9802322e-8, 8.9e-8, 0.0, -0.0,
+                         float("inf"), -float("inf"), 3.3895314e38, 1e-40, 9.2e-41])
+    x = torch.cat([x, edge, -edge])
+    want_h = x.to(torch.float16).view(torch.int16).numpy().view(np.uint16)
+    want_b = x.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    xs = x.numpy()
+    step = max(1, len(xs) // 20000)
+    for i in list(range(0, len(xs), step)) + list(range(len(xs) - 2 * len(edge), len(xs))):
+        assert L.orc_f32_to_f16(float(xs[i])) == want_h[i], xs[i]
+        assert L.orc_f32_to_bf16(float(xs[i])) == want_b[i], xs[i]
+
+
 @pytest.mark.parametrize("in_dtype,tdt", [("bf16", torch.bfloat16), ("f16", torch.float16)])
 def test_conversion_tables_match_torch_cast(in_dtype, tdt):
     z = np.load(os.path.join(H.GOLDEN_DIR, "fp8_tables.npz"))

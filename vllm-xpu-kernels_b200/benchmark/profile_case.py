@@ -24,8 +24,15 @@ from vllm_xpu_kernels import cabi  # noqa: E402
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--layout", choices=["flash", "paged", "mla", "gather", "quant-static", "quant-dynamic", "quant-token"], default="flash",
-                    help="mla: concat_and_cache_mla (512 + 64 wide entries); gather: gather_cache of such entries")
+    ap.add_argument("--layout", choices=["flash", "paged", "mla", "gather", "quant-static", "quant-dynamic", "quant-token",
+                                         "rope", "rope-cache", "rope-then-cache"], default="flash",
+                    help="mla: concat_and_cache_mla (512 + 64 wide entries); gather: gather_cache of such entries; "
+                         "rope: rotary_embedding; rope-cache: the fused rotary_embedding_and_cache_flash; "
+                         "rope-then-cache: the two separate ops back to back (what the fused op replaces)")
+    ap.add_argument("--q-heads", type=int, default=64, help="query heads of the rope layouts (--heads are kv heads)")
+    ap.add_argument("--rot-dim", type=int, default=0, help="rotary dim of the rope layouts (0: head size)")
+    ap.add_argument("--gptj", action="store_true", help="interleaved pairs instead of the NeoX halves")
+    ap.add_argument("--no-write-back", action="store_true", help="rope-cache: leave key un-rotated")
     ap.add_argument("--kv", choices=["auto", "fp8", "fp8_e5m2"], default="fp8")
     ap.add_argument("--dtype", choices=["bfloat16", "half", "float"], default="bfloat16")
     ap.add_argument("--tokens", type=int, default=32768)
@@ -48,6 +55,9 @@ def main() -> None:
         return
     if ns.layout.startswith("quant"):
         run_quant(ns, dev)
+        return
+    if ns.layout.startswith("rope"):
+        run_rope(ns, dev)
         return
     dt = {"bfloat16": torch.bfloat16, "half": torch.float16, "float": torch.float32}[ns.dtype]
     T, H, D, bs = ns.tokens, ns.heads, ns.head_size, ns.block_size
@@ -180,6 +190,67 @@ def run_quant(ns, dev) -> None:
     best = min(times[1:]) if len(times) > 1 else times[0]
     print(f"layout={ns.layout} fp8={ns.kv} dtype={ns.dtype} T={T} hidden={hidden} algorithmic_bytes={alg} "
           f"launches={ns.launches} event_us={['%.1f' % t for t in times]} best_GBps={alg / best / 1e3:.0f}")
+
+
+def run_rope(ns, dev) -> None:
+    """Rotary embedding of a fused qkv projection output [T, (Hq + 2 Hkv) * D], alone, fused with the cache
+    write, or followed by the separate cache write."""
+    dt = {"bfloat16": torch.bfloat16, "half": torch.float16, "float": torch.float32}[ns.dtype]
+    T, hq, hk, D, bs = ns.tokens, ns.q_heads, ns.heads, ns.head_size, ns.block_size
+    R = ns.rot_dim or D
+    neox = not ns.gptj
+    es = torch.empty((), dtype=dt).element_size()
+    es_out = 1 if ns.kv != "auto" else es
+    max_pos = 8192
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, R, 2, dtype=torch.float) / R))
+    freqs = torch.einsum("i,j -> ij", torch.arange(max_pos, dtype=torch.float), inv_freq)
+    table = torch.cat((freqs.cos(), freqs.sin()), dim=-1).to(dt).to(dev)
+    nb = 2 * ((T + bs - 1) // bs)
+    cdt = dt if ns.kv == "auto" else torch.uint8
+    with_cache = ns.layout != "rope"
+    if with_cache:
+        kc = torch.zeros(nb, bs, hk, D, dtype=cdt, device=dev)
+        vc = torch.zeros(nb, bs, hk, D, dtype=cdt, device=dev)
+    sets = []
+    for b in range(ns.nbuf):
+        qkv = torch.randn(T, (hq + 2 * hk) * D, device=dev).to(dt)
+        q = qkv[:, :hq * D].view(T, hq, D)
+        k = qkv[:, hq * D:(hq + hk) * D].view(T, hk, D)
+        v = qkv[:, (hq + hk) * D:].view(T, hk, D)
+        positions = torch.arange(T, device=dev) % max_pos
+        perm = torch.randperm(nb, device=dev)[:(T + bs - 1) // bs]
+        slots = (perm[:, None] * bs + torch.arange(bs, device=dev)[None, :]).flatten()[:T].contiguous()
+        sets.append((positions, q, k, v, slots))
+    ks = torch.tensor(0.05, device=dev)
+    vs = torch.tensor(0.05, device=dev)
+    rope_bytes = 2 * T * (hq + hk) * R * es + T * R * es + 8 * T
+    if with_cache:
+        wb = 0 if (ns.layout == "rope-cache" and ns.no_write_back) else T * hk * R * es
+        alg = (2 * T * hq * R * es + T * R * es + 16 * T + T * hk * D * es + wb + T * hk * D * es_out
+               + T * hk * D * (es + es_out))
+    else:
+        alg = rope_bytes
+    evs = []
+    for i in range(ns.launches):
+        positions, q, k, v, slots = sets[i % ns.nbuf]
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        if ns.layout == "rope":
+            cabi.rotary_embedding(positions, q, k, D, table, neox)
+        elif ns.layout == "rope-cache":
+            cabi.rotary_embedding_and_cache_flash(positions, q, k, v, D, table, neox, kc, vc, slots, ns.kv, ks, vs,
+                                                  write_back_key=not ns.no_write_back)
+        else:
+            cabi.rotary_embedding(positions, q, k, D, table, neox)
+            cabi.reshape_and_cache_flash(k, v, kc, vc, slots, ns.kv, ks, vs)
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    times = [a.elapsed_time(b) * 1e3 for a, b in evs]
+    best = min(times[1:]) if len(times) > 1 else times[0]
+    print(f"layout={ns.layout} kv={ns.kv} dtype={ns.dtype} T={T} Hq={hq} Hkv={hk} D={D} rot_dim={R} "
+          f"style={'neox' if neox else 'gptj'} algorithmic_bytes={alg} launches={ns.launches} "
+          f"event_us={['%.1f' % t for t in times]} best_GBps={alg / best / 1e3:.0f}")
 
 
 if __name__ == "__main__":

@@ -24,8 +24,10 @@ INCLUDE = os.path.join(REPO, "include")
 CUDA_LIB = os.path.join(PKG, "libkvcache_b200.so")
 TORCH_EXT = os.path.join(PKG, "_C.abi3.so")
 
-CUDA_SOURCES = [os.path.join(CSRC, "kvcache_kernels.cu"), os.path.join(CSRC, "fp8_quant_kernels.cu")]
+CUDA_SOURCES = [os.path.join(CSRC, "kvcache_kernels.cu"), os.path.join(CSRC, "fp8_quant_kernels.cu"),
+                os.path.join(CSRC, "rope_kernels.cu")]
 EXT_SOURCES = [os.path.join(CSRC, "cache.cpp"), os.path.join(CSRC, "fp8_quant.cpp"),
+               os.path.join(CSRC, "pos_encoding.cpp"),
                os.path.join(CSRC, "torch_bindings.cpp")]
 HEADERS = [
     os.path.join(INCLUDE, "kvcache_b200.h"),
@@ -33,7 +35,7 @@ HEADERS = [
     os.path.join(CSRC, "dispatch_utils.h"),
     os.path.join(CSRC, "core", "registration.h"),
 ]
-CUDA_HEADERS = [HEADERS[0], os.path.join(CSRC, "kvc_common.cuh")]
+CUDA_HEADERS = [HEADERS[0], os.path.join(CSRC, "kvc_common.cuh"), os.path.join(CSRC, "kvc_convert.cuh")]
 
 
 def _stale(target: str, sources: list[str]) -> bool:
@@ -64,7 +66,7 @@ def build_cuda_lib(force: bool = False, verbose: bool = False) -> str:
     if force or _stale(CUDA_LIB, CUDA_SOURCES + CUDA_HEADERS):
         cmd = [
             _nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-            "-shared", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", INCLUDE, "-I", CSRC, "-o", CUDA_LIB,
+            "--threads", str(len(CUDA_SOURCES)), "-shared", "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", INCLUDE, "-I", CSRC, "-o", CUDA_LIB,
         ]
         if verbose:
             cmd += ["-Xptxas", "-v"]

@@ -127,6 +127,67 @@ __device__ __forceinline__ void load_chunk(Chunk<BYTES>& c, const void* gptr, bo
   }
 }
 
+// The same for memory that the running kernel also WRITES (an in-place op): a plain weak load,
+// because the non-coherent path is only defined for data that stays read-only during the kernel.
+// BYTES == 32 is one 256-bit access and needs a 32-byte aligned address; smaller sizes need
+// their own size as alignment.
+template <int BYTES>
+__device__ __forceinline__ void load_chunk_inplace(Chunk<BYTES>& c, const void* gptr) {
+  if constexpr (BYTES == 32) {
+    uint4 lo, hi;
+    asm volatile("ld.global.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+                 : "l"(gptr)
+                 : "memory");
+    reinterpret_cast<uint4*>(c.b)[0] = lo;
+    reinterpret_cast<uint4*>(c.b)[1] = hi;
+  } else if constexpr (BYTES == 16) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(gptr)
+                 : "memory");
+    *reinterpret_cast<uint4*>(c.b) = v;
+  } else if constexpr (BYTES == 8) {
+    uint2 v;
+    asm volatile("ld.global.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(gptr) : "memory");
+    *reinterpret_cast<uint2*>(c.b) = v;
+  } else if constexpr (BYTES == 4) {
+    uint32_t v;
+    asm volatile("ld.global.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(gptr) : "memory");
+    *reinterpret_cast<uint32_t*>(c.b) = v;
+  } else {
+    static_assert(BYTES == 2, "unsupported chunk size");
+    uint16_t v;
+    asm volatile("ld.global.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(gptr) : "memory");
+    *reinterpret_cast<uint16_t*>(c.b) = v;
+  }
+}
+
+// Read-only data that several threads of a CTA share (table rows): non-coherent path, L1 kept.
+template <int BYTES>
+__device__ __forceinline__ void load_chunk_shared_ro(Chunk<BYTES>& c, const void* gptr) {
+  if constexpr (BYTES == 32) {
+    uint4 lo, hi;
+    asm volatile("ld.global.nc.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+                 : "l"(gptr));
+    reinterpret_cast<uint4*>(c.b)[0] = lo;
+    reinterpret_cast<uint4*>(c.b)[1] = hi;
+  } else if constexpr (BYTES == 16) {
+    *reinterpret_cast<uint4*>(c.b) = __ldg(static_cast<const uint4*>(gptr));
+  } else if constexpr (BYTES == 8) {
+    *reinterpret_cast<uint2*>(c.b) = __ldg(static_cast<const uint2*>(gptr));
+  } else if constexpr (BYTES == 4) {
+    *reinterpret_cast<uint32_t*>(c.b) = __ldg(static_cast<const uint32_t*>(gptr));
+  } else if constexpr (BYTES == 2) {
+    *reinterpret_cast<uint16_t*>(c.b) = __ldg(static_cast<const uint16_t*>(gptr));
+  } else {
+    static_assert(BYTES == 1, "unsupported chunk size");
+    c.b[0] = __ldg(static_cast<const unsigned char*>(gptr));
+  }
+}
+
 // Stores PIECE bytes taken at byte offset `at` of the chunk; PIECE in {16,8,4,2,1}.
 template <int PIECE, int BYTES>
 __device__ __forceinline__ void store_piece(void* gptr, const Chunk<BYTES>& c, int at) {

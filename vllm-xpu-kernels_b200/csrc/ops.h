@@ -30,3 +30,16 @@ void static_scaled_fp8_quant(at::Tensor& out, at::Tensor const& input, at::Tenso
 void dynamic_scaled_fp8_quant(at::Tensor& out, at::Tensor const& input, at::Tensor& scale);
 void dynamic_per_token_scaled_fp8_quant(at::Tensor& out, at::Tensor const& input, at::Tensor& scales,
                                         std::optional<at::Tensor> const& scale_ub);
+
+// Rotary position embedding, in place (namespace `_C`; the reference's csrc/ops.h:33-39 and
+// pos_encoding_kernels.cpp:165-286).
+void rotary_embedding(at::Tensor& positions, at::Tensor& query, std::optional<at::Tensor> key, int64_t head_size,
+                      at::Tensor& cos_sin_cache, bool is_neox);
+
+// rotary_embedding followed by reshape_and_cache_flash(key, value, ...) in one pass (namespace
+// `_C_cache_ops`; the reference has no such op).
+void rotary_embedding_and_cache_flash(at::Tensor& positions, at::Tensor& query, at::Tensor& key, at::Tensor& value,
+                                      int64_t head_size, at::Tensor& cos_sin_cache, bool is_neox,
+                                      at::Tensor& key_cache, at::Tensor& value_cache, at::Tensor& slot_mapping,
+                                      const std::string& kv_cache_dtype, at::Tensor& k_scale, at::Tensor& v_scale,
+                                      bool write_back_key);

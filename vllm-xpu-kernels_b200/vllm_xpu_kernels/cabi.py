@@ -34,6 +34,8 @@ SYMBOLS = (
     "kvc_static_scaled_fp8_quant",
     "kvc_dynamic_scaled_fp8_quant",
     "kvc_dynamic_per_token_scaled_fp8_quant",
+    "kvc_rotary_embedding",
+    "kvc_rotary_embedding_and_cache_flash",
 )
 
 _lib = None
@@ -75,6 +77,10 @@ def lib() -> ctypes.CDLL:
         L.kvc_dynamic_per_token_scaled_fp8_quant.argtypes = [vp, vp, vp, vp, i64, i64, ci, ci, vp]
         L.kvc_count_bad_slots.restype = ci
         L.kvc_count_bad_slots.argtypes = [vp, i64, i64, vp, vp]
+        L.kvc_rotary_embedding.restype = ci
+        L.kvc_rotary_embedding.argtypes = [vp] * 4 + [i64] * 10 + [ci, ci, vp]
+        L.kvc_rotary_embedding_and_cache_flash.restype = ci
+        L.kvc_rotary_embedding_and_cache_flash.argtypes = [vp] * 8 + [i64] * 17 + [ci, ci, ci, ci, vp, vp, vp]
         _lib = L
     return _lib
 
@@ -236,3 +242,67 @@ def dynamic_per_token_scaled_fp8_quant(out, input, scales, scale_ub=None, stream
     _check(lib().kvc_dynamic_per_token_scaled_fp8_quant(
         out.data_ptr(), input.data_ptr(), scales.data_ptr(), 0 if scale_ub is None else scale_ub.data_ptr(), tokens,
         hidden, _in_dtype(input), FP8_CODE[out.dtype], _stream(stream)))
+
+
+def _rope_geometry(t, head_size: int, lead: int):
+    """(heads, token stride, head stride) of a query/key tensor whose first ``lead`` dims index
+    tokens: [.., heads, head_size] or [.., heads * head_size] (csrc/pos_encoding_kernels.cpp:196-211
+    of the reference).  With two leading dims the batch dim must be the seq dim's continuation."""
+    if t.stride(-1) != 1 and t.shape[-1] > 1:
+        raise RuntimeError("rotary_embedding: the last dim of query/key must be contiguous")
+    if lead == 2 and t.shape[0] > 1 and t.stride(0) != t.shape[1] * t.stride(1):
+        raise RuntimeError("rotary_embedding: [batch, seq, ...] tensors must be contiguous across batch and seq")
+    if t.dim() == lead + 2:
+        if t.shape[-1] != head_size:
+            raise RuntimeError("rotary_embedding: last dim of query/key must be head_size")
+        return t.shape[-2], t.stride(lead - 1), t.stride(-2)
+    if t.dim() != lead + 1 or t.shape[-1] % head_size:
+        raise RuntimeError("rotary_embedding: query/key must be [.., heads, head_size] or [.., heads * head_size]")
+    return t.shape[-1] // head_size, t.stride(lead - 1), head_size
+
+
+def _rope_args(positions, query, key, head_size: int, cos_sin_cache):
+    lead = positions.dim()
+    if lead not in (1, 2):
+        raise RuntimeError("positions must have shape [num_tokens] or [batch_size, seq_len]")
+    if not positions.is_contiguous() or positions.dtype != torch.int64:
+        raise RuntimeError("rotary_embedding: positions must be a contiguous int64 tensor")
+    for t in (query, key):
+        if t is not None and tuple(t.shape[:lead]) != tuple(positions.shape):
+            raise RuntimeError("query, key and positions must have the same number of tokens" if lead == 1 else
+                               "query, key and positions must have the same batch_size and seq_len")
+    if cos_sin_cache.dim() != 2 or not cos_sin_cache.is_contiguous() or cos_sin_cache.dtype != query.dtype:
+        raise RuntimeError("rotary_embedding: cos_sin_cache must be a contiguous [max_position, rot_dim] tensor of "
+                           "the query's dtype")
+    hq, qst, qsh = _rope_geometry(query, head_size, lead)
+    hk, kst, ksh = _rope_geometry(key, head_size, lead) if key is not None else (0, 0, 0)
+    return positions.numel(), hq, hk, qst, qsh, kst, ksh
+
+
+def rotary_embedding(positions, query, key, head_size: int, cos_sin_cache, is_neox: bool, stream=None) -> None:
+    """``kvc_rotary_embedding``: in place on query and key (key may be None)."""
+    T, hq, hk, qst, qsh, kst, ksh = _rope_args(positions, query, key, head_size, cos_sin_cache)
+    _check(lib().kvc_rotary_embedding(
+        positions.data_ptr(), query.data_ptr(), 0 if key is None else key.data_ptr(), cos_sin_cache.data_ptr(),
+        T, hq, hk, head_size, cos_sin_cache.shape[1], cos_sin_cache.shape[0], qst, qsh, kst, ksh,
+        int(bool(is_neox)), _in_dtype(query), _stream(stream)))
+
+
+def rotary_embedding_and_cache_flash(positions, query, key, value, head_size: int, cos_sin_cache, is_neox: bool,
+                                     key_cache, value_cache, slot_mapping, kv_cache_dtype: str, k_scale=None,
+                                     v_scale=None, write_back_key: bool = True, stream=None) -> None:
+    """``kvc_rotary_embedding_and_cache_flash``: rotary embedding of query and key in place, and the rotated key
+    and ``value`` [T, Hkv, head_size] into their cache slots (caches [num_blocks, block_size, Hkv, head_size])."""
+    T, hq, hk, qst, qsh, kst, ksh = _rope_args(positions, query, key, head_size, cos_sin_cache)
+    kv = parse_kv_cache_dtype(kv_cache_dtype)
+    if value.dim() != 3 or value.shape[0] != T or value.shape[1] != hk or value.shape[2] != head_size:
+        raise RuntimeError("rotary_embedding_and_cache_flash: value must be [num_tokens, num_kv_heads, head_size]")
+    if slot_mapping.shape[0] > T:
+        raise RuntimeError("rotary_embedding_and_cache_flash: slot_mapping is longer than positions")
+    _check(lib().kvc_rotary_embedding_and_cache_flash(
+        positions.data_ptr(), query.data_ptr(), key.data_ptr(), value.data_ptr(), cos_sin_cache.data_ptr(),
+        key_cache.data_ptr(), value_cache.data_ptr(), slot_mapping.data_ptr(), T, slot_mapping.shape[0], hq, hk,
+        head_size, cos_sin_cache.shape[1], cos_sin_cache.shape[0], key_cache.shape[1], qst, qsh, kst, ksh,
+        value.stride(0), value.stride(1), key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
+        int(bool(is_neox)), int(bool(write_back_key)), _in_dtype(query), kv, _scale_ptr(k_scale, kv),
+        _scale_ptr(v_scale, kv), _stream(stream)))
