@@ -46,6 +46,31 @@ def test_rope_golden(fname, face, cuda_device):
         assert H.same_bytes(k_store.cpu()[..., c.head_size:], c.key_store[..., c.head_size:])
 
 
+@pytest.mark.parametrize("max_position", [11, 4096])
+@pytest.mark.parametrize("is_neox_style", [True, False])
+@pytest.mark.parametrize("head_size", [32, 108])
+@pytest.mark.parametrize("seq_len", [11, 1024])
+@pytest.mark.parametrize("use_key", [True, False])
+@pytest.mark.parametrize("head_stride_is_contiguous", [True, False])
+def test_rotary_embedding_opcheck(max_position, is_neox_style, head_size, seq_len, use_key,
+                                  head_stride_is_contiguous, cuda_device):
+    """The reference's own test of this op (tests/test_rotary_embedding.py:43-87 there): schema, fake-tensor
+    and dispatch checks over its matrix of layouts, fp32, rotary_dim 32, 7 heads."""
+    rotary_dim, num_heads, batch_size = 32, 7, 1
+    table = cos_sin_table(max_position, rotary_dim, torch.float32).to(cuda_device)
+    positions = torch.randint(0, max_position, (batch_size, seq_len), device=cuda_device)
+    head_stride = head_size + (64 if head_stride_is_contiguous else 0)
+    query = torch.randn(batch_size, seq_len, num_heads, head_stride, dtype=torch.float32, device=cuda_device)
+    key = torch.randn_like(query) if use_key else None
+    query = query[..., :head_size]
+    key = key[..., :head_size] if use_key else None
+    H.opcheck(torch.ops._C.rotary_embedding, (positions, query, key, head_size, table, is_neox_style))
+    if head_stride_is_contiguous:
+        H.opcheck(torch.ops._C.rotary_embedding,
+                  (positions, query.flatten(start_dim=-2), key.flatten(start_dim=-2) if use_key else None, head_size,
+                   table, is_neox_style))
+
+
 # ------------------------------------------------------------------------------------ vs oracle
 SHAPES = [
     # T, Hq, Hkv, head_size, rot_dim, head_pad, token_pad   (pads in elements; odd pads force narrow accesses)
@@ -284,6 +309,71 @@ def test_fused_rope_cache_without_key_write_back(is_neox, cuda_device):
     assert H.same_bytes(got_q, cq)
     assert H.same_bytes(got_k, key_before)
     assert H.same_bytes(d_both.cpu(), both)
+
+
+def test_fused_rope_cache_torch_op(cuda_device):
+    """The torch face of the fused op: same bytes as the C ABI call, opcheck-clean, usable on a side stream
+    and from a device other than the current one's default tensors."""
+    dev = cuda_device
+    T, hq, hk, D, R, bs, nb = 64, 8, 2, 128, 128, 16, 8
+    table, positions, qkv, split, slots, both, k_scale, v_scale = _fused_case(
+        torch.float16, "fp8", True, T, hq, hk, D, R, bs, nb, 60, seed=4, device=dev)
+    ks = torch.tensor(k_scale, dtype=torch.float32, device=dev)
+    vs = torch.tensor(v_scale, dtype=torch.float32, device=dev)
+    d1, c1 = qkv.to(dev), both.to(dev)
+    d2, c2 = qkv.to(dev), both.to(dev)
+    q, k, v = split(d1)
+    cabi.rotary_embedding_and_cache_flash(positions.to(dev), q, k, v, D, table.to(dev), True, c1[:, 0], c1[:, 1],
+                                          slots.to(dev), "fp8", ks, vs)
+    q2, k2, v2 = split(d2)
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        ops.rotary_embedding_and_cache_flash(positions.to(dev), q2, k2, v2, D, table.to(dev), True, c2[:, 0], c2[:, 1],
+                                             slots.to(dev), "fp8", ks, vs)
+    side.synchronize()
+    torch.cuda.synchronize()
+    assert H.same_bytes(d1.cpu(), d2.cpu()) and H.same_bytes(c1.cpu(), c2.cpu())
+    d3, c3 = qkv.to(dev), both.to(dev)
+    q3, k3, v3 = split(d3)
+    H.opcheck(torch.ops._C_cache_ops.rotary_embedding_and_cache_flash,
+              (positions.to(dev), q3, k3, v3, D, table.to(dev), True, c3[:, 0], c3[:, 1], slots.to(dev), "fp8", ks, vs))
+    with pytest.raises(RuntimeError, match="value must be"):
+        ops.rotary_embedding_and_cache_flash(positions.to(dev), q3, k3, v3[:, :1], D, table.to(dev), True, c3[:, 0],
+                                             c3[:, 1], slots.to(dev), "fp8", ks, vs)
+    with pytest.raises(RuntimeError, match="Unsupported data type of kv cache"):
+        ops.rotary_embedding_and_cache_flash(positions.to(dev), q3, k3, v3, D, table.to(dev), True, c3[:, 0],
+                                             c3[:, 1], slots.to(dev), "int4", ks, vs)
+
+
+def test_rope_in_a_cuda_graph(cuda_device):
+    """Both ops only enqueue work and read their scalars on the device: capture and replay."""
+    dev = cuda_device
+    T, hq, hk, D, R, bs, nb = 48, 4, 2, 64, 64, 16, 6
+    table, positions, qkv, split, slots, both, k_scale, v_scale = _fused_case(
+        torch.bfloat16, "fp8", False, T, hq, hk, D, R, bs, nb, T, seed=6, device=dev)
+    ks = torch.tensor(k_scale, dtype=torch.float32, device=dev)
+    vs = torch.tensor(v_scale, dtype=torch.float32, device=dev)
+    d_qkv, d_both = qkv.to(dev), both.to(dev)
+    d_pos, d_tab, d_slots = positions.to(dev), table.to(dev), slots.to(dev)
+    q, k, v = split(d_qkv)
+    pristine = d_qkv.clone()
+    ops.rotary_embedding_and_cache_flash(d_pos, q, k, v, D, d_tab, False, d_both[:, 0], d_both[:, 1], d_slots, "fp8",
+                                         ks, vs)  # warm-up outside capture
+    torch.cuda.synchronize()
+    d_qkv.copy_(pristine)
+    d_both.copy_(both.to(dev))
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        ops.rotary_embedding_and_cache_flash(d_pos, q, k, v, D, d_tab, False, d_both[:, 0], d_both[:, 1], d_slots,
+                                             "fp8", ks, vs)
+    d_qkv.copy_(pristine)
+    g.replay()
+    torch.cuda.synchronize()
+    cq, ck, cv = split(qkv)
+    torch_views.run_rope(positions, cq, ck, D, table, False)
+    H.oracle_call("flash", ck, cv, both[:, 0], both[:, 1], slots, "fp8", k_scale, v_scale)
+    assert H.same_bytes(d_qkv.cpu(), qkv) and H.same_bytes(d_both.cpu(), both)
 
 
 def test_fused_rope_cache_refuses_layouts_without_16_byte_access(cuda_device):
