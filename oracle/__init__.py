@@ -69,6 +69,12 @@ def lib() -> ctypes.CDLL:
         L.orc_f32_to_bf16.argtypes = [f32]
         L.orc_f32_to_f16.restype = ctypes.c_uint16
         L.orc_f32_to_f16.argtypes = [f32]
+        L.orc_paged_decode_attention.restype = None
+        L.orc_paged_decode_attention.argtypes = [vp] * 7 + [f32, f32] + [i64] * 11 + [f32, ci, ci]
+        L.orc_e4m3_to_f32.restype = f32
+        L.orc_e4m3_to_f32.argtypes = [ctypes.c_uint8]
+        L.orc_e5m2_to_f32.restype = f32
+        L.orc_e5m2_to_f32.argtypes = [ctypes.c_uint8]
         L.orc_max_threads.restype = ci
         _lib = L
     return _lib
@@ -261,6 +267,44 @@ def rotary_embedding(positions, query, key, head_size: int, cos_sin_cache, is_ne
         IN_DTYPES[in_dtype])
     if rc != 0:
         raise IndexError("positions holds an entry outside [0, max_position)")
+
+
+def paged_decode_attention(query, key_cache, value_cache, block_table, seq_lens, scale: float, in_dtype: str,
+                           kv_cache_dtype: str = "auto", k_descale: float = 1.0, v_descale: float = 1.0,
+                           sink=None) -> np.ndarray:
+    """fp32 ``[num_seqs, num_heads, head_size]`` result of one-token-per-sequence attention over a paged
+    cache.  ``query`` [S, Hq, D] (contiguous last dim); caches [num_blocks, block_size, Hkv, D] views with the
+    same strides, of the query's type (uint16 bit patterns / float32) or uint8 fp8 bytes; ``block_table`` int32
+    [S, max_blocks]; ``seq_lens`` int32 [S]; ``sink`` [Hq] of the query's type or None."""
+    want = np.float32 if in_dtype == "f32" else np.uint16
+    kv = KV_DTYPES[kv_cache_dtype]
+    if query.dtype != want or (sink is not None and sink.dtype != want):
+        raise TypeError(f"{in_dtype} query/sink must be {np.dtype(want)} arrays")
+    if key_cache.dtype != (want if kv == 0 else np.uint8) or value_cache.dtype != key_cache.dtype:
+        raise TypeError("cache arrays do not fit kv_cache_dtype")
+    if key_cache.shape != value_cache.shape or key_cache.strides != value_cache.strides:
+        raise ValueError("key_cache and value_cache must have the same shape and strides")
+    S, hq, D = query.shape
+    nb, bs, hk, Dc = key_cache.shape
+    if Dc != D or hq % hk or _estrides(query)[2] != 1 or _estrides(key_cache)[3] != 1:
+        raise ValueError("shapes of query and caches do not fit")
+    block_table = np.ascontiguousarray(block_table, dtype=np.int32)
+    seq_lens = np.ascontiguousarray(seq_lens, dtype=np.int32)
+    if block_table.shape[0] != S or seq_lens.shape[0] != S:
+        raise ValueError("block_table / seq_lens do not fit the number of sequences")
+    if S and int(seq_lens.max(initial=0)) > block_table.shape[1] * bs:
+        raise ValueError("a sequence is longer than its block table")
+    if block_table.size and (block_table.min() < 0 or block_table.max() >= nb):
+        raise IndexError("block_table names a block outside the cache")
+    sink_c = None if sink is None else np.ascontiguousarray(sink)
+    out = np.empty((S, hq, D), dtype=np.float32)
+    qs, cs = _estrides(query), _estrides(key_cache)
+    lib().orc_paged_decode_attention(
+        out.ctypes.data, query.ctypes.data, key_cache.ctypes.data, value_cache.ctypes.data, block_table.ctypes.data,
+        seq_lens.ctypes.data, None if sink_c is None else sink_c.ctypes.data, float(k_descale), float(v_descale),
+        S, hq, hk, D, bs, block_table.shape[1], qs[0], qs[1], cs[0], cs[1], cs[2], float(scale),
+        IN_DTYPES[in_dtype], kv)
+    return out
 
 
 def convert_table(in_dtype: str, kv_cache_dtype: str, scale: float) -> np.ndarray:

@@ -23,6 +23,9 @@
  *   orc_rotary_embedding         csrc/pos_encoding_kernels.cpp:9-37 (pair update), :40-88 (loops over
  *                                heads), :174-232 (host sizes and strides); torch form
  *                                tests/ops/rotary_embedding_op.py:11-30, :85-118
+ *   orc_paged_decode_attention   tests/flash_attn/test_flash_attn_varlen_func.py:27-110 (ref_paged_attn with
+ *                                query_len 1, no window, not causal, optional sink column) and the decode
+ *                                branch of csrc/flash_attn/flash_api.cpp:124-165 (paged, max_seqlen_q == 1)
  *   element conversion           csrc/quantization/fp8/quant_utils.h:62-78
  *                                (auto: bit copy; fp8: float(src) / scale,
  *                                then cast)
@@ -54,6 +57,7 @@
  */
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #ifdef _OPENMP
@@ -428,6 +432,74 @@ int orc_rotary_embedding(const int64_t* positions, void* query, void* key, const
                  is_neox, dt);
   }
   return bad;
+}
+
+/* ------------------------------------------------------------------------------------------
+ * paged decode attention: one query token per sequence against that sequence's cached keys/values
+ * ------------------------------------------------------------------------------------------ */
+float orc_e4m3_to_f32(uint8_t b) {
+  const int e = (b >> 3) & 0xF, m = b & 7;
+  float v;
+  if (e == 0xF && m == 7) return u2f(0x7FC00000u); /* the only NaN code; e4m3fn has no infinity */
+  if (e == 0) v = (float)m * 0.001953125f;          /* m * 2^-9 */
+  else v = ldexpf(1.0f + (float)m / 8.0f, e - 7);
+  return (b & 0x80) ? -v : v;
+}
+float orc_e5m2_to_f32(uint8_t b) { return orc_f16_to_f32((uint16_t)b << 8); }
+
+static inline float cache_elem(const void* p, int64_t i, int q_dt, int kv) {
+  if (kv == ORC_KV_E4M3) return orc_e4m3_to_f32(((const uint8_t*)p)[i]);
+  if (kv == ORC_KV_E5M2) return orc_e5m2_to_f32(((const uint8_t*)p)[i]);
+  return load_as_f32(p, i, q_dt);
+}
+
+/* out[s][h][:] = softmax_j(scale * q[s][h] . K[s][j][h/g]) @ V[s][:][h/g], j < seq_lens[s], g = Hq / Hkv,
+ * K[s][j] = key_cache[block_table[s][j / bs]][j % bs] (times k_descale for an fp8 cache), V likewise.
+ * A sink adds one more logit sink[h] to the softmax denominator only.  Everything is accumulated in
+ * double and written as fp32: this is the ideal result, the kernels are held to a tolerance around it.
+ * Strides in elements.  Sequences of length 0 give zeros. */
+void orc_paged_decode_attention(float* out, const void* query, const void* key_cache, const void* value_cache,
+                                const int32_t* block_table, const int32_t* seq_lens, const void* sink,
+                                float k_descale, float v_descale, int64_t num_seqs, int64_t num_heads,
+                                int64_t num_kv_heads, int64_t head_size, int64_t block_size,
+                                int64_t block_table_stride, int64_t query_stride_t, int64_t query_stride_h,
+                                int64_t block_stride, int64_t page_stride, int64_t head_stride, float scale,
+                                int q_dt, int kv) {
+  const int64_t group = num_heads / num_kv_heads;
+#pragma omp parallel for collapse(2) schedule(dynamic)
+  for (int64_t s = 0; s < num_seqs; ++s) {
+    for (int64_t h = 0; h < num_heads; ++h) {
+      const int64_t n = seq_lens[s];
+      const int64_t kvh = h / group;
+      float* o = out + (s * num_heads + h) * head_size;
+      for (int64_t d = 0; d < head_size; ++d) o[d] = 0.0f;
+      if (n <= 0) continue;
+      double* logit = (double*)malloc((size_t)n * sizeof(double));
+      double* acc = (double*)calloc((size_t)head_size, sizeof(double));
+      double mx = sink ? (double)load_as_f32(sink, h, q_dt) : -INFINITY;
+      for (int64_t j = 0; j < n; ++j) {
+        const int64_t blk = block_table[s * block_table_stride + j / block_size];
+        const int64_t base = blk * block_stride + (j % block_size) * page_stride + kvh * head_stride;
+        double dot = 0.0;
+        for (int64_t d = 0; d < head_size; ++d)
+          dot += (double)load_as_f32(query, s * query_stride_t + h * query_stride_h + d, q_dt) *
+                 (double)cache_elem(key_cache, base + d, q_dt, kv);
+        logit[j] = dot * (double)scale * (double)k_descale;
+        if (logit[j] > mx) mx = logit[j];
+      }
+      double denom = sink ? exp((double)load_as_f32(sink, h, q_dt) - mx) : 0.0;
+      for (int64_t j = 0; j < n; ++j) {
+        const double p = exp(logit[j] - mx);
+        denom += p;
+        const int64_t blk = block_table[s * block_table_stride + j / block_size];
+        const int64_t base = blk * block_stride + (j % block_size) * page_stride + kvh * head_stride;
+        for (int64_t d = 0; d < head_size; ++d) acc[d] += p * (double)cache_elem(value_cache, base + d, q_dt, kv);
+      }
+      for (int64_t d = 0; d < head_size; ++d) o[d] = (float)(acc[d] / denom * (double)v_descale);
+      free(logit);
+      free(acc);
+    }
+  }
 }
 
 int orc_max_threads(void) {

@@ -54,3 +54,14 @@ def run_rope(positions, query, key, head_size: int, cos_sin_cache, is_neox: bool
     assert q.data_ptr() == query.data_ptr() and (k is None or k.data_ptr() == key.data_ptr()), "reshape copied"
     oracle.rotary_embedding(positions.reshape(-1).numpy(), as_np(q), None if k is None else as_np(k), head_size,
                             as_np(cos_sin_cache), is_neox, ORC_IN[query.dtype])
+
+
+def run_paged_decode_attention(query, key_cache, value_cache, block_table, seq_lens, scale: float,
+                               kv_cache_dtype: str = "auto", k_descale: float = 1.0, v_descale: float = 1.0,
+                               sink=None) -> torch.Tensor:
+    """fp32 [S, Hq, D] result of the oracle's decode attention on CPU torch tensors."""
+    import oracle
+    out = oracle.paged_decode_attention(
+        as_np(query), as_np(key_cache), as_np(value_cache), block_table.numpy(), seq_lens.numpy(), scale,
+        ORC_IN[query.dtype], kv_cache_dtype, k_descale, v_descale, None if sink is None else as_np(sink))
+    return torch.from_numpy(out)

@@ -73,6 +73,28 @@ def load_reference_rotary(ref_root: str):
         sys.modules.update(saved)
 
 
+def load_reference_paged_attn(ref_root: str):
+    """``ref_paged_attn`` from the reference's tests/flash_attn/test_flash_attn_varlen_func.py.  That file
+    imports the compiled attention interface at import time; the reference function is pure torch."""
+    names = ("vllm_xpu_kernels", "vllm_xpu_kernels.flash_attn_interface")
+    saved = {k: sys.modules.pop(k) for k in list(sys.modules) if k in names}
+    try:
+        pkg = types.ModuleType("vllm_xpu_kernels")
+        pkg.__path__ = []
+        iface = types.ModuleType("vllm_xpu_kernels.flash_attn_interface")
+        iface.flash_attn_varlen_func = None
+        sys.modules.update({names[0]: pkg, names[1]: iface})
+        spec = importlib.util.spec_from_file_location(
+            "reference_test_flash_attn", os.path.join(ref_root, "tests", "flash_attn", "test_flash_attn_varlen_func.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod.ref_paged_attn
+    finally:
+        for k in names:
+            sys.modules.pop(k, None)
+        sys.modules.update(saved)
+
+
 def bits(t: torch.Tensor) -> np.ndarray:
     """Raw storage of a (possibly strided) tensor as a contiguous numpy array."""
     t = t.contiguous()
@@ -255,6 +277,41 @@ def make_rope_case(RotaryEmbedding, dtype: str, is_neox: bool, head_size: int, r
     return d
 
 
+def make_decode_attn_case(ref_paged_attn, dtype: str, num_heads: int, num_kv_heads: int, head_size: int,
+                          kv_lens: list, block_size: int, num_blocks: int, with_sink: bool, kv_cache_dtype: str,
+                          descale: float, seed: int) -> dict:
+    """Inputs as in test_decode_with_paged_kv of the reference (tests/flash_attn/test_flash_attn_varlen_func.py:
+    274-372: one query token per sequence, randn query and caches, randint block tables, optional randn sink);
+    expected = its ref_paged_attn on the CPU.  For an fp8 cache the caches are first cast to fp8; the reference
+    function then sees their exact 16-bit images times a power-of-two descale."""
+    tdt = DT[dtype]
+    torch.manual_seed(seed)
+    num_seqs = len(kv_lens)
+    query = torch.randn(num_seqs, num_heads, head_size, dtype=tdt)
+    key_cache = torch.randn(num_blocks, block_size, num_kv_heads, head_size, dtype=tdt)
+    value_cache = torch.randn_like(key_cache)
+    max_blocks = (max(kv_lens) + block_size - 1) // block_size
+    block_tables = torch.randint(0, num_blocks, (num_seqs, max_blocks), dtype=torch.int32)
+    sink = torch.randn(num_heads, dtype=tdt) if with_sink else None
+    stored_k, stored_v = key_cache, value_cache
+    if kv_cache_dtype != "auto":
+        fdt = torch.float8_e5m2 if kv_cache_dtype == "fp8_e5m2" else torch.float8_e4m3fn
+        stored_k, stored_v = (key_cache / descale).to(fdt), (value_cache / descale).to(fdt)
+        key_cache, value_cache = (stored_k.to(tdt) * descale), (stored_v.to(tdt) * descale)
+        assert torch.equal(key_cache.float(), stored_k.float() * descale)  # the 16-bit image is exact
+    scale = head_size ** -0.5
+    expected = ref_paged_attn(query=query.clone(), key_cache=key_cache, value_cache=value_cache,
+                              query_lens=[1] * num_seqs, kv_lens=kv_lens, block_tables=block_tables, scale=scale,
+                              casual=False, is_paged=True, sink=sink, window_size_left=-1, window_size_right=-1)
+    d = dict(op="decode_attn", dtype=dtype, kv_cache_dtype=kv_cache_dtype, query=bits(query),
+             key_cache=bits(stored_k), value_cache=bits(stored_v), block_tables=block_tables.numpy(),
+             kv_lens=np.array(kv_lens, dtype=np.int32), scale=np.float32(scale), descale=np.float32(descale),
+             expected=bits(expected))
+    if with_sink:
+        d["sink"] = bits(sink)
+    return d
+
+
 def make_tables() -> dict:
     """torch's e4m3 / e5m2 cast over every bf16 and fp16 bit pattern at a few scales."""
     out = {}
@@ -276,6 +333,7 @@ def main() -> None:
     ns = ap.parse_args()
     ru = load_reference_utils(ns.reference)
     RotaryEmbedding = load_reference_rotary(ns.reference)
+    ref_paged_attn = load_reference_paged_attn(ns.reference)
 
     def wanted(name: str) -> bool:
         return ns.only is None or name.startswith(ns.only)
@@ -345,6 +403,24 @@ def main() -> None:
                     "_pad%d" % pad if pad else "", "_flat" if flat else "")
                 extra.append((name, lambda a=(dtype, is_neox, head_size, rot_dim, 257 if ri % 2 else 11, 11, hq, hk,
                                                use_key, pad, flat, ri): make_rope_case(RotaryEmbedding, *a)))
+    # paged decode attention: the head-count pairs, both types and the sink switch of the reference's decode
+    # test (tests/flash_attn/test_flash_attn_varlen_func.py:14-24, :274-288), with smaller caches and shorter
+    # sequences (one of them a single token, one crossing many blocks); fp8 caches on top
+    ai = 200
+    for dtype, hq, hk, D, lens, bs, nb, sink, kv, descale in (
+            ("bfloat16", 8, 2, 128, [300, 37, 129], 16, 24, False, "auto", 1.0),
+            ("half", 4, 4, 64, [1, 523, 64], 16, 16, True, "auto", 1.0),
+            ("bfloat16", 10, 2, 64, [65, 17, 250], 16, 16, True, "auto", 1.0),
+            ("half", 16, 1, 128, [200, 33], 32, 8, False, "auto", 1.0),
+            ("bfloat16", 16, 1, 192, [100], 64, 3, False, "auto", 1.0),
+            ("half", 8, 2, 256, [130, 5], 64, 4, True, "auto", 1.0),
+            ("bfloat16", 8, 2, 128, [300, 37, 129], 16, 24, False, "fp8", 0.5),
+            ("half", 4, 4, 64, [70, 523], 16, 16, True, "fp8", 2.0),
+            ("bfloat16", 10, 2, 128, [90, 260], 32, 10, True, "fp8_e5m2", 1.0)):
+        ai += 1
+        name = "decode_attn_%s_%s_Hq%d_Hk%d_D%d_bs%d%s" % (dtype, kv, hq, hk, D, bs, "_sink" if sink else "")
+        extra.append((name, lambda a=(dtype, hq, hk, D, lens, bs, nb, sink, kv, descale, ai):
+                      make_decode_attn_case(ref_paged_attn, *a)))
     for name, data in extra:
         names.append(name)
         if wanted(name):

@@ -21,7 +21,7 @@ def golden_files(kind: str = "kv") -> list[str]:
     with open(os.path.join(GOLDEN_DIR, "MANIFEST.txt")) as f:
         names = [ln.strip() for ln in f if ln.strip() and not ln.startswith("#")]
     prefixes = {"kv": ("flash_", "paged_"), "mla": ("mla_",), "gather": ("gather_",), "quant": ("quant_",),
-                "rope": ("rope_",)}[kind]
+                "rope": ("rope_",), "decode_attn": ("decode_attn_",)}[kind]
     return [n for n in names if n.startswith(prefixes)]
 
 
@@ -80,6 +80,29 @@ class RopeCase:
             q = q.flatten(start_dim=-2)
             k = None if k is None else k.flatten(start_dim=-2)
         return q, k
+
+
+class DecodeAttnCase:
+    """A paged decode-attention fixture: one query token per sequence, caches [nb, bs, Hkv, D]."""
+
+    def __init__(self, fname: str):
+        z = np.load(os.path.join(GOLDEN_DIR, fname))
+        self.dtype = TORCH_DT[str(z["dtype"])]
+        self.kv_cache_dtype = str(z["kv_cache_dtype"])
+        cdt = cache_torch_dtype(self.dtype, self.kv_cache_dtype)
+        self.query = from_bits(z["query"], self.dtype)
+        self.key_cache = from_bits(z["key_cache"], cdt)
+        self.value_cache = from_bits(z["value_cache"], cdt)
+        self.block_tables = torch.from_numpy(z["block_tables"].astype(np.int32))
+        self.kv_lens = torch.from_numpy(z["kv_lens"].astype(np.int32))
+        self.scale = float(z["scale"])
+        self.descale = float(z["descale"])
+        self.sink = from_bits(z["sink"], self.dtype) if "sink" in z.files else None
+        self.expected = from_bits(z["expected"], self.dtype)
+
+
+# The reference's own tolerance for this op (tests/flash_attn/test_flash_attn_varlen_func.py:265, :386).
+ATTN_ATOL = ATTN_RTOL = 1e-2
 
 
 class GatherCase:

@@ -70,6 +70,29 @@ def test_oracle_reproduces_reference_rotary_fixture(fname):
         assert H.same_bytes(k_store[..., :c.head_size], c.key_after)
 
 
+@pytest.mark.parametrize("fname", H.golden_files("decode_attn"))
+def test_oracle_reproduces_reference_decode_attention_fixture(fname):
+    """Expected values come from the reference's ref_paged_attn, which rounds the scaled query, the logits and
+    the probabilities to the 16-bit type; the oracle keeps everything in double.  Tolerance: the reference
+    test's own (atol = rtol = 1e-2)."""
+    c = H.DecodeAttnCase(fname)
+    got = torch_views.run_paged_decode_attention(c.query, c.key_cache, c.value_cache, c.block_tables, c.kv_lens,
+                                                 c.scale, c.kv_cache_dtype, c.descale, c.descale, c.sink)
+    torch.testing.assert_close(got, c.expected.float(), atol=H.ATTN_ATOL, rtol=H.ATTN_RTOL)
+
+
+def test_fp8_decoders_invert_the_encoders():
+    L = oracle.lib()
+    for b in range(256):
+        v4, v5 = L.orc_e4m3_to_f32(b), L.orc_e5m2_to_f32(b)
+        want4 = torch.tensor([b], dtype=torch.uint8).view(torch.float8_e4m3fn).float().item()
+        want5 = torch.tensor([b], dtype=torch.uint8).view(torch.float8_e5m2).float().item()
+        assert (v4 != v4 and want4 != want4) or v4 == want4, b
+        assert (v5 != v5 and want5 != want5) or v5 == want5, b
+        if v4 == v4:
+            assert L.orc_f32_to_e4m3(v4) == b
+
+
 def test_rotary_oracle_rounding_helpers_match_torch():
     """The oracle's float -> f16 / bf16 roundings against torch's casts, over a dense sweep."""
     L = oracle.lib()
