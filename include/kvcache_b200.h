@@ -301,6 +301,45 @@ KVC_API int kvc_rotary_embedding_and_cache_flash(
     void* stream);
 
 /*
+ * Paged decode attention: one query token per sequence against its cached keys and values.
+ * Replaces the decode branch of mha_varlen_fwd of the reference (csrc/flash_attn/flash_api.cpp:124-165:
+ * paged, max_seqlen_q == 1, no window; op schema :179-193), and extends it to caches stored as fp8,
+ * which the reference leaves unimplemented (vllm_xpu_kernels/flash_attn_interface.py:77-82).
+ *
+ *   out, query     [num_seqs, num_heads, head_size], fp16 or bf16 (q_dtype: KVC_IN_F16 / KVC_IN_BF16),
+ *                  strides in elements, last dim contiguous, rows 16-byte aligned
+ *   key_cache,     [num_blocks, block_size, num_kv_heads, head_size] views with common strides
+ *   value_cache    (block_stride, page_stride, head_stride, in elements), as written by
+ *                  kvc_reshape_and_cache_flash: kv_dtype KVC_KV_AUTO = the query's type, KVC_KV_FP8_* = bytes
+ *   block_table    int32 [num_seqs, block_table_stride]: block of tokens [i*block_size, (i+1)*block_size)
+ *   seq_lens       int32 [num_seqs]: cached tokens per sequence (0 gives a zero row)
+ *   sink           NULL, or [num_heads] of the query's type: an extra logit that only enters the softmax
+ *                  denominator (flash_api.cpp:27, "softmax_sink")
+ *   k_descale,     NULL (= 1), or device fp32 scalars: a stored key element k means k * k_descale, the
+ *   v_descale      inverse of the k_scale / v_scale division of the cache write; ignored for KVC_KV_AUTO
+ *   max_seq_len    host-side upper bound of seq_lens (the reference's max_seqlen_k); sizes the split
+ *   workspace      device scratch of kvc_paged_decode_workspace_bytes(...) bytes, 16-byte aligned; may be
+ *                  NULL when that function returns 0
+ *
+ *   out[s][h] = sum_j softmax_j(softmax_scale * q[s][h] . K[s][j][h / g]) * V[s][j][h / g],  g = num_heads /
+ *   num_kv_heads.  Products run on fp16/bf16 tensor-core tiles with fp32 accumulation; probabilities are
+ *   rounded to the 16-bit type before they meet V, as in the reference's torch statement
+ *   (tests/flash_attn/test_flash_attn_varlen_func.py:27-110).  Floating point: results agree with that
+ *   statement within its own tolerance, atol = rtol = 1e-2.  head_size 64, 128, 192 or 256.
+ */
+KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads,
+                                                 int64_t head_size, int64_t max_seq_len);
+KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void* key_cache, const void* value_cache,
+                                       const int32_t* block_table, const int32_t* seq_lens, const void* sink,
+                                       const float* k_descale, const float* v_descale, void* workspace,
+                                       int64_t workspace_bytes, int64_t num_seqs, int64_t num_heads,
+                                       int64_t num_kv_heads, int64_t head_size, int64_t block_size,
+                                       int64_t block_table_stride, int64_t max_seq_len, int64_t query_stride_t,
+                                       int64_t query_stride_h, int64_t out_stride_t, int64_t out_stride_h,
+                                       int64_t block_stride, int64_t page_stride, int64_t head_stride,
+                                       float softmax_scale, int q_dtype, int kv_dtype, void* stream);
+
+/*
  * Debug aid the reference lacks: counts entries of slot_mapping that are
  * >= num_slots (negative entries are legal padding and not counted) into
  * *bad_count, a DEVICE int64 the caller owns; the kernel overwrites it.

@@ -1,0 +1,217 @@
+"""GPU parity of the paged decode attention against the fixtures computed with the reference's
+``ref_paged_attn`` and against the CPU oracle.
+
+Floating point.  Tolerance: atol = rtol = 1e-2, the reference test's own for this op
+(tests/flash_attn/test_flash_attn_varlen_func.py:386 there), against both the fixtures (which carry the
+reference statement's 16-bit roundings) and the oracle (which keeps everything in double)."""
+import pytest
+import torch
+
+from oracle import torch_views
+from tests import helpers as H
+from vllm_xpu_kernels import cabi
+
+pytestmark = pytest.mark.gpu
+
+TOL = dict(atol=H.ATTN_ATOL, rtol=H.ATTN_RTOL)
+
+
+def dscalar(v, dev):
+    return torch.tensor(v, dtype=torch.float32, device=dev)
+
+
+def run_gpu(dev, query, key_cache, value_cache, block_tables, kv_lens, scale, kv="auto", k_descale=1.0, v_descale=1.0,
+            sink=None, max_seq_len=None, caches_on_device=None):
+    kc, vc = caches_on_device if caches_on_device is not None else (key_cache.to(dev), value_cache.to(dev))
+    out = cabi.paged_decode_attention(
+        query.to(dev), kc, vc, block_tables.to(dev), kv_lens.to(dev), scale,
+        int(kv_lens.max()) if max_seq_len is None else max_seq_len, kv,
+        dscalar(k_descale, dev) if kv != "auto" else None, dscalar(v_descale, dev) if kv != "auto" else None,
+        None if sink is None else sink.to(dev))
+    torch.cuda.synchronize()
+    return out.cpu()
+
+
+# ------------------------------------------------------------------------------------ fixtures
+@pytest.mark.parametrize("fname", H.golden_files("decode_attn"))
+def test_decode_attention_golden(fname, cuda_device):
+    c = H.DecodeAttnCase(fname)
+    got = run_gpu(cuda_device, c.query, c.key_cache, c.value_cache, c.block_tables, c.kv_lens, c.scale,
+                  c.kv_cache_dtype, c.descale, c.descale, c.sink)
+    assert got.dtype == c.dtype
+    torch.testing.assert_close(got.float(), c.expected.float(), **TOL)
+    want = torch_views.run_paged_decode_attention(c.query, c.key_cache, c.value_cache, c.block_tables, c.kv_lens,
+                                                  c.scale, c.kv_cache_dtype, c.descale, c.descale, c.sink)
+    torch.testing.assert_close(got.float(), want, **TOL)
+
+
+# ------------------------------------------------------------------------------------ the reference's decode matrix
+def make_case(dtype, hq, hk, D, kv_lens, bs, nb, sink, seed, kv="auto", descale=1.0):
+    torch.manual_seed(seed)
+    S = len(kv_lens)
+    query = torch.randn(S, hq, D).to(dtype)
+    key_cache = torch.randn(nb, bs, hk, D).to(dtype)
+    value_cache = torch.randn(nb, bs, hk, D).to(dtype)
+    max_blocks = (max(max(kv_lens), 1) + bs - 1) // bs
+    block_tables = torch.randint(0, nb, (S, max_blocks), dtype=torch.int32)
+    lens = torch.tensor(kv_lens, dtype=torch.int32)
+    sk = torch.randn(hq).to(dtype) if sink else None
+    if kv != "auto":
+        fdt = torch.float8_e5m2 if kv == "fp8_e5m2" else torch.float8_e4m3fn
+        key_cache = (key_cache.float() / descale).to(fdt)
+        value_cache = (value_cache.float() / descale).to(fdt)
+    return query, key_cache, value_cache, block_tables, lens, sk
+
+
+@pytest.mark.parametrize("seq_lens", [[1025], [523, 37, 2011], [13000], [523, 37, 2011, 5000]])
+@pytest.mark.parametrize("num_heads", [(4, 4), (8, 2), (10, 2), (16, 1)])
+@pytest.mark.parametrize("head_size", [64, 128, 192, 256])
+def test_decode_attention_reference_matrix(seq_lens, num_heads, head_size, cuda_device):
+    """Shapes of test_decode_with_paged_kv of the reference (tests/flash_attn/test_flash_attn_varlen_func.py:
+    274-288): block size 64, 2048 blocks; type and sink alternate over the matrix instead of multiplying it."""
+    hq, hk = num_heads
+    idx = len(seq_lens) + hq + head_size // 64
+    dtype = torch.bfloat16 if idx % 2 else torch.float16
+    sink = bool((idx // 2) % 2)
+    query, kc, vc, bt, lens, sk = make_case(dtype, hq, hk, head_size, seq_lens, 64, 2048, sink, seed=42)
+    scale = head_size ** -0.5
+    got = run_gpu(cuda_device, query, kc, vc, bt, lens, scale, sink=sk)
+    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, scale, sink=sk)
+    torch.testing.assert_close(got.float(), want, **TOL)
+
+
+def test_decode_attention_block_indices_beyond_32_bits(cuda_device):
+    """32768 blocks of 64 x 4 heads x 128 (the reference's large NUM_BLOCKS): byte offsets pass 2^32."""
+    dev = cuda_device
+    torch.manual_seed(1)
+    nb, bs, hk, hq, D = 32768, 64, 4, 8, 128
+    kc = torch.randn(nb, bs, hk, D, device=dev, dtype=torch.float16)
+    vc = torch.randn(nb, bs, hk, D, device=dev, dtype=torch.float16)
+    lens = torch.tensor([700, 64, 1], dtype=torch.int32)
+    bt = torch.randint(nb - 40, nb, (3, 11), dtype=torch.int32)
+    query = torch.randn(3, hq, D).to(torch.float16)
+    got = run_gpu(dev, query, None, None, bt, lens, D ** -0.5, caches_on_device=(kc, vc))
+    # the oracle sees a compact copy: the blocks the tables name, renumbered
+    used, inv = torch.unique(bt, return_inverse=True)
+    small_k, small_v = kc[used.to(dev).long()].cpu(), vc[used.to(dev).long()].cpu()
+    want = torch_views.run_paged_decode_attention(query, small_k, small_v, inv.to(torch.int32), lens, D ** -0.5)
+    torch.testing.assert_close(got.float(), want, **TOL)
+
+
+# ------------------------------------------------------------------------------------ fp8 caches
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("kv,descale", [("fp8", 0.03), ("fp8_e4m3", 1.0), ("fp8_e5m2", 0.002)])
+@pytest.mark.parametrize("geom", [(8, 2, 128, [300, 37, 1290], 16), (4, 4, 64, [65, 1], 64), (16, 1, 256, [777], 32),
+                                  (10, 2, 192, [130, 4000], 128)])
+def test_decode_attention_fp8_cache(dtype, kv, descale, geom, cuda_device):
+    hq, hk, D, lens, bs = geom
+    nb = 96
+    query, kc, vc, bt, lens_t, sk = make_case(dtype, hq, hk, D, lens, bs, nb, True, seed=7, kv=kv, descale=descale)
+    scale = D ** -0.5
+    got = run_gpu(cuda_device, query, kc.view(torch.uint8), vc.view(torch.uint8), bt, lens_t, scale, kv, descale,
+                  descale * 0.5, sk)
+    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens_t, scale, kv, descale, descale * 0.5, sk)
+    torch.testing.assert_close(got.float(), want, **TOL)
+
+
+# ------------------------------------------------------------------------------------ edges
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_decode_attention_edge_lengths_and_layouts(dtype, cuda_device):
+    """Lengths around the 64-token tile and the block size, an empty sequence, a block size that is not a power
+    of two, 32 query heads per kv head (two row tiles), caches that are the [:, 0] / [:, 1] views of one
+    allocation, and a query cut out of a wider projection output."""
+    dev = cuda_device
+    torch.manual_seed(3)
+    hq, hk, D, bs, nb = 32, 1, 128, 48, 40
+    lens = [0, 1, 47, 48, 49, 63, 64, 65, 127, 128, 129, 400]
+    S = len(lens)
+    both = torch.randn(nb, 2, bs, hk, D).to(dtype)
+    wide = torch.randn(S, hq * D + 256).to(dtype)
+    query = wide[:, 128:128 + hq * D].view(S, hq, D)
+    bt = torch.randint(0, nb, (S, 9), dtype=torch.int32)
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    sk = torch.randn(hq).to(dtype)
+    d_both = both.to(dev)
+    d_query = wide.to(dev)[:, 128:128 + hq * D].view(S, hq, D)
+    out = cabi.paged_decode_attention(d_query, d_both[:, 0], d_both[:, 1], bt.to(dev), lens_t.to(dev), 0.11, 400,
+                                      sink=sk.to(dev))
+    torch.cuda.synchronize()
+    want = torch_views.run_paged_decode_attention(query, both[:, 0], both[:, 1], bt, lens_t, 0.11, sink=sk)
+    torch.testing.assert_close(out.cpu().float(), want, **TOL)
+    assert torch.count_nonzero(out[0]) == 0  # the empty sequence
+    # no sink: an empty sequence still gives zeros, not NaN
+    out2 = cabi.paged_decode_attention(d_query, d_both[:, 0], d_both[:, 1], bt.to(dev), lens_t.to(dev), 0.11, 400)
+    want2 = torch_views.run_paged_decode_attention(query, both[:, 0], both[:, 1], bt, lens_t, 0.11)
+    torch.testing.assert_close(out2.cpu().float(), want2, **TOL)
+
+
+def test_decode_attention_split_count_does_not_change_the_result(cuda_device):
+    """max_seq_len only sizes the split: a larger bound gives more, shorter splits of the same sums."""
+    query, kc, vc, bt, lens, sk = make_case(torch.bfloat16, 8, 2, 128, [3000, 200], 64, 128, True, seed=11)
+    a = run_gpu(cuda_device, query, kc, vc, bt, lens, 0.09, sink=sk, max_seq_len=3000)
+    b = run_gpu(cuda_device, query, kc, vc, bt, lens, 0.09, sink=sk, max_seq_len=60000)
+    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, 0.09, sink=sk)
+    torch.testing.assert_close(a.float(), want, **TOL)
+    torch.testing.assert_close(b.float(), want, **TOL)
+    # many sequences: enough CTAs without splitting
+    query, kc, vc, bt, lens, sk = make_case(torch.float16, 8, 8, 64, [100 + 7 * i for i in range(300)], 16, 512, False,
+                                            seed=12)
+    c = run_gpu(cuda_device, query, kc, vc, bt, lens, 0.125)
+    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, 0.125)
+    torch.testing.assert_close(c.float(), want, **TOL)
+
+
+def test_write_fp8_cache_then_attend(cuda_device):
+    """The two halves together: reshape_and_cache_flash stores fp8 keys and values with k_scale / v_scale, the
+    decode attention reads them back with the same scales as descales.  Checked against the oracle's own
+    write followed by its attention, and against attention over the unquantised rows within fp8's error."""
+    dev = cuda_device
+    torch.manual_seed(5)
+    hq, hk, D, bs, nb = 8, 2, 128, 16, 64
+    lens = [333, 90]
+    S = len(lens)
+    bt = torch.randperm(nb)[:S * 21].view(S, 21).to(torch.int32)  # no block belongs to two sequences
+    keys = [torch.randn(n, hk, D).to(torch.bfloat16) for n in lens]
+    values = [torch.randn(n, hk, D).to(torch.bfloat16) for n in lens]
+    slots = torch.cat([bt[s, torch.arange(n) // bs].long() * bs + torch.arange(n) % bs for s, n in enumerate(lens)])
+    key, value = torch.cat(keys), torch.cat(values)
+    k_scale = float(key.float().abs().max() / 448)
+    v_scale = float(value.float().abs().max() / 448)
+    cache = torch.zeros(nb, 2, bs, hk, D, dtype=torch.uint8)
+    d_cache = cache.to(dev)
+    cabi.reshape_and_cache_flash(key.to(dev), value.to(dev), d_cache[:, 0], d_cache[:, 1], slots.to(dev), "fp8",
+                                 dscalar(k_scale, dev), dscalar(v_scale, dev))
+    query = torch.randn(S, hq, D).to(torch.bfloat16)
+    lens_t = torch.tensor(lens, dtype=torch.int32)
+    out = cabi.paged_decode_attention(query.to(dev), d_cache[:, 0], d_cache[:, 1], bt.to(dev), lens_t.to(dev),
+                                      D ** -0.5, max(lens), "fp8", dscalar(k_scale, dev), dscalar(v_scale, dev))
+    torch.cuda.synchronize()
+    H.oracle_call("flash", key, value, cache[:, 0], cache[:, 1], slots, "fp8", k_scale, v_scale)
+    assert H.same_bytes(d_cache.cpu(), cache)
+    want = torch_views.run_paged_decode_attention(query, cache[:, 0], cache[:, 1], bt, lens_t, D ** -0.5, "fp8",
+                                                  k_scale, v_scale)
+    torch.testing.assert_close(out.cpu().float(), want, **TOL)
+    # against the unquantised rows: fp8 storage costs a few percent
+    dense = torch.zeros(nb, 2, bs, hk, D, dtype=torch.bfloat16)
+    H.oracle_call("flash", key, value, dense[:, 0], dense[:, 1], slots, "auto", 1.0, 1.0)
+    ideal = torch_views.run_paged_decode_attention(query, dense[:, 0], dense[:, 1], bt, lens_t, D ** -0.5)
+    torch.testing.assert_close(out.cpu().float(), ideal, atol=0.15, rtol=0.15)
+
+
+def test_decode_attention_rejects_bad_arguments(cuda_device):
+    dev = cuda_device
+    q = torch.zeros(2, 8, 128, dtype=torch.float16, device=dev)
+    kc = torch.zeros(4, 16, 2, 128, dtype=torch.float16, device=dev)
+    bt = torch.zeros(2, 4, dtype=torch.int32, device=dev)
+    lens = torch.ones(2, dtype=torch.int32, device=dev)
+    with pytest.raises(RuntimeError, match="head_size"):
+        cabi.paged_decode_attention(q[..., :96].contiguous(), kc[..., :96].contiguous(), kc[..., :96].contiguous(), bt,
+                                    lens, 1.0, 1)
+    with pytest.raises(RuntimeError, match="multiple of num_kv_heads"):
+        cabi.paged_decode_attention(q[:, :7].contiguous(), kc, kc, bt, lens, 1.0, 1)
+    with pytest.raises(RuntimeError, match="fp16 or bf16"):
+        cabi.paged_decode_attention(q.float(), kc, kc, bt, lens, 1.0, 1)
+    with pytest.raises(RuntimeError, match="Unsupported data type of kv cache"):
+        cabi.paged_decode_attention(q, kc, kc, bt, lens, 1.0, 1, "int8")
+    out = cabi.paged_decode_attention(q[:0], kc, kc, bt[:0], lens[:0], 1.0, 0)  # no sequences: nothing to do
+    assert out.shape[0] == 0

@@ -25,7 +25,7 @@ CUDA_LIB = os.path.join(PKG, "libkvcache_b200.so")
 TORCH_EXT = os.path.join(PKG, "_C.abi3.so")
 
 CUDA_SOURCES = [os.path.join(CSRC, "kvcache_kernels.cu"), os.path.join(CSRC, "fp8_quant_kernels.cu"),
-                os.path.join(CSRC, "rope_kernels.cu")]
+                os.path.join(CSRC, "rope_kernels.cu"), os.path.join(CSRC, "paged_attention_kernels.cu")]
 EXT_SOURCES = [os.path.join(CSRC, "cache.cpp"), os.path.join(CSRC, "fp8_quant.cpp"),
                os.path.join(CSRC, "pos_encoding.cpp"),
                os.path.join(CSRC, "torch_bindings.cpp")]

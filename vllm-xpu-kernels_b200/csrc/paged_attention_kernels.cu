@@ -1,0 +1,700 @@
+// Paged decode attention for NVIDIA B200 (sm_100a): one query token per sequence against the keys
+// and values that the cache-write kernels of this library stored, in their 16-bit type or as fp8
+// bytes with per-tensor descales.  C ABI: kvc_paged_decode_attention.
+//
+//   out[s][h] = softmax_j( scale * q[s][h] . K[s][j][h / g] ) @ V[s][j][h / g],   j < seq_lens[s]
+//   K[s][j] = key_cache[block_table[s][j / block_size]][j % block_size]   (flash layout [nb, bs, Hkv, D])
+//
+// The work is a stream over the sequence's cache blocks (HBM-bound: every cached byte is read once and
+// meets 2 * g multiply-adds), so the kernel is organised around keeping loads in flight; the small
+// matrix products run on mma.sync tiles (16 query rows x 16 tokens) fed by ldmatrix from shared memory.
+// Long sequences are cut into splits that run as separate CTAs and are merged by a second kernel.
+//
+// The reference plugin's counterpart is the decode branch of mha_varlen_fwd,
+// csrc/flash_attn/flash_api.cpp:124-165 (paged, max_seqlen_q == 1, no window), which launches a
+// split-KV kernel plus a reduction; it reads 16-bit caches only (k_descale / v_descale raise
+// NotImplementedError in vllm_xpu_kernels/flash_attn_interface.py:77-82).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <mutex>
+
+#include "kvc_common.cuh"
+
+namespace kvc {
+
+namespace {
+
+constexpr int kAttnThreads = 128;       // 4 warps
+constexpr int kTileTokens = 64;         // tokens per pipeline stage; warp w owns tokens [16w, 16w + 16) for Q.K
+constexpr int kRows = 16;               // query rows per CTA (the heads of one kv group, padded)
+constexpr int kPRowBytes = kTileTokens * 2 + 16;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// ---------------------------------------------------------------------------------------------
+// small PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+// 16-byte asynchronous copy global -> shared; src_bytes == 0 writes zeros instead.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+// d += a (16x16, row) * b (16x8, col), fp32 accumulate.
+template <typename T16>
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (std::is_same_v<T16, __half>) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+
+template <typename T16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (std::is_same_v<T16, __half>) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  } else {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+}
+
+// Two fp8 bytes (low 16 bits of `v`) -> two fp16 (exact: every e4m3 / e5m2 value is an fp16 value).
+template <int KV>
+__device__ __forceinline__ uint32_t fp8x2_to_f16x2(uint32_t v) {
+  uint32_t r;
+  const uint16_t h = static_cast<uint16_t>(v);
+  if constexpr (KV == KVC_KV_FP8_E4M3) {
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(h));
+  } else {
+    asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(r) : "h"(h));
+  }
+  return r;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// parameters
+// ---------------------------------------------------------------------------------------------
+struct DecodeParams {
+  void* out;               // [S, Hq, D] of the query's type
+  const void* query;       // [S, Hq, D]
+  const void* key_cache;   // [nb, bs, Hkv, D]: 16-bit type of the query, or fp8 bytes
+  const void* value_cache;
+  const int32_t* block_table;  // [S, block_table_stride]
+  const int32_t* seq_lens;     // [S]
+  const void* sink;            // [Hq] of the query's type, or NULL
+  const float* k_descale;      // device scalars, or NULL for 1
+  const float* v_descale;
+  float* part_lse;  // [S, Hq, splits]   log2-domain log-sum-exp of each split (-inf: empty)
+  float* part_out;  // [S, Hq, splits, D] normalised partial results
+  int64_t query_stride_t, query_stride_h, out_stride_t, out_stride_h;  // elements
+  int64_t block_stride, page_stride, head_stride;                      // elements of the cache
+  int64_t block_table_stride;
+  int32_t num_heads, num_kv_heads, group, row_tiles;  // group = Hq / Hkv; row_tiles = ceil(group / 16)
+  int32_t block_size;
+  int32_t num_splits, tiles_per_split;
+  float softmax_scale;
+};
+
+// ---------------------------------------------------------------------------------------------
+// the decode kernel
+// ---------------------------------------------------------------------------------------------
+// TQ: type of query and output.  KV: KVC_KV_AUTO (cache holds TQ) or an fp8 code (cache holds bytes that
+// are widened to fp16 on their way into shared memory; the products then run in fp16).  D: head size.
+template <typename TQ, int KV, int D>
+struct DecodeCfg {
+  using T16 = std::conditional_t<KV == KVC_KV_AUTO, TQ, __half>;  // operand type of the matrix products
+  static constexpr int kRowBytes = D * 2 + 16;                     // shared-memory row of K, V and Q (16 B pad:
+                                                                    // eight consecutive rows hit distinct banks)
+  static constexpr int kTileBytes = kTileTokens * kRowBytes;       // one K or V tile
+  static constexpr int kStages = (KV != KVC_KV_AUTO) ? 2 : (D <= 128 ? 3 : 2);
+  static constexpr int kSmemQ = kRows * kRowBytes;
+  static constexpr int kSmemP = kRows * kPRowBytes;
+  static constexpr int kSmemRed = 2 * 4 * kRows * (int)sizeof(float);
+  static constexpr int kSmemBytes = kStages * 2 * kTileBytes + kSmemQ + kSmemP + kSmemRed;
+  static constexpr int kSliceCols = D / 4;  // output columns owned by a warp in P.V
+  static_assert(D % 64 == 0 && D <= 256, "head sizes 64, 128, 192, 256");
+};
+
+template <typename TQ, int KV, int D>
+__global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const DecodeParams p) {
+  using Cfg = DecodeCfg<TQ, KV, D>;
+  using T16 = typename Cfg::T16;
+  constexpr int RB = Cfg::kRowBytes;
+  constexpr int NST = Cfg::kStages;
+  constexpr int SL = Cfg::kSliceCols;
+
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* s_kv = smem;                                  // NST x (K tile, V tile)
+  unsigned char* s_q = s_kv + NST * 2 * Cfg::kTileBytes;       // [16][RB]
+  unsigned char* s_p = s_q + Cfg::kSmemQ;                      // [16][kPRowBytes]
+  float* s_max = reinterpret_cast<float*>(s_p + Cfg::kSmemP);  // [4 warps][16 rows]
+  float* s_sum = s_max + 4 * kRows;                            // [4 warps][16 rows]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;  // accumulator row (and row + 8) and column pair of this lane
+  const int seq = blockIdx.x;
+  const int kvh = blockIdx.y / p.row_tiles, row_tile = blockIdx.y - kvh * p.row_tiles;
+  const int split = blockIdx.z;
+  const int row0 = row_tile * kRows;                       // first group-local query row of this CTA
+  const int rows = min(kRows, p.group - row0);             // valid rows
+  const int head0 = kvh * p.group + row0;                  // first query head of this CTA
+
+  pdl_prologue();
+
+  const int n = p.seq_lens[seq];
+  const int total_tiles = (n + kTileTokens - 1) / kTileTokens;
+  const int tile_begin = split * p.tiles_per_split;
+  const int tile_end = min(tile_begin + p.tiles_per_split, total_tiles);
+
+  if (tile_begin >= tile_end) {  // nothing cached in this split's range
+    if (p.num_splits > 1) {
+      if (tid < rows) p.part_lse[(static_cast<int64_t>(seq) * p.num_heads + head0 + tid) * p.num_splits + split] = -INFINITY;
+    } else {
+      TQ* o = static_cast<TQ*>(p.out) + seq * p.out_stride_t;
+      for (int i = tid; i < rows * D; i += kAttnThreads) o[(head0 + i / D) * p.out_stride_h + i % D] = TQ(0.0f);
+    }
+    return;
+  }
+
+  // ---- query rows -> shared memory (as T16), rows beyond the group are zero -------------------
+  {
+    constexpr int kChunks = D / 8;  // 16-byte chunks (8 elements) per row
+    for (int c = tid; c < kRows * kChunks; c += kAttnThreads) {
+      const int r = c / kChunks, col = c - r * kChunks;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < rows) {
+        const TQ* src = static_cast<const TQ*>(p.query) + seq * p.query_stride_t + (head0 + r) * p.query_stride_h + col * 8;
+        v = *reinterpret_cast<const uint4*>(src);
+        if constexpr (!std::is_same_v<TQ, T16>) {  // bf16 query, fp16 products
+          uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xFFFF0000u);
+            w[i] = pack2<__half>(lo, hi);
+          }
+        }
+      }
+      *reinterpret_cast<uint4*>(s_q + r * RB + col * 16) = v;
+    }
+  }
+
+  // ---- producer: one tile of K and V rows into a stage ---------------------------------------
+  const int32_t* table = p.block_table + seq * p.block_table_stride;
+  const int64_t head_off = static_cast<int64_t>(kvh) * p.head_stride;
+  auto row_offset = [&](int token) -> int64_t {  // element offset of a cached token's row for this kv head
+    const int blk_idx = token / p.block_size;
+    const int64_t blk = table[blk_idx];
+    return blk * p.block_stride + static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride + head_off;
+  };
+
+  [[maybe_unused]] auto load_tile_async = [&](int tile, int stage) {  // 16-bit cache: cp.async
+    constexpr int kChunks = D / 8;
+    constexpr int kPerThread = kTileTokens * kChunks / kAttnThreads;
+    unsigned char* ks = s_kv + stage * 2 * Cfg::kTileBytes;
+    unsigned char* vs = ks + Cfg::kTileBytes;
+    const int tok0 = tile * kTileTokens;
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      const int c = i * kAttnThreads + tid;
+      const int r = c / kChunks, col = c - r * kChunks;
+      const int token = tok0 + r;
+      const bool valid = token < n;
+      const int64_t off = valid ? row_offset(token) + col * 8 : 0;
+      const uint32_t dst = r * RB + col * 16;
+      cp_async_16(smem_u32(ks + dst), static_cast<const T16*>(p.key_cache) + off, valid ? 16 : 0);
+      cp_async_16(smem_u32(vs + dst), static_cast<const T16*>(p.value_cache) + off, valid ? 16 : 0);
+    }
+  };
+
+  // fp8 cache: 16 bytes (16 elements) per chunk through registers, widened to fp16 when stored.
+  constexpr int kF8Chunks = D / 16;
+  constexpr int kF8PerThread = (KV != KVC_KV_AUTO) ? kTileTokens * kF8Chunks / kAttnThreads : 1;
+  [[maybe_unused]] uint4 stage_k[kF8PerThread], stage_v[kF8PerThread];
+  [[maybe_unused]] auto load_tile_regs = [&](int tile) {
+    const int tok0 = tile * kTileTokens;
+#pragma unroll
+    for (int i = 0; i < kF8PerThread; ++i) {
+      const int c = i * kAttnThreads + tid;
+      const int r = c / kF8Chunks, col = c - r * kF8Chunks;
+      const int token = tok0 + r;
+      stage_k[i] = make_uint4(0, 0, 0, 0);
+      stage_v[i] = make_uint4(0, 0, 0, 0);
+      if (token < n) {
+        const int64_t off = row_offset(token) + col * 16;
+        stage_k[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(p.key_cache) + off));
+        stage_v[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(p.value_cache) + off));
+      }
+    }
+  };
+  [[maybe_unused]] auto store_tile_regs = [&](int stage) {
+    unsigned char* ks = s_kv + stage * 2 * Cfg::kTileBytes;
+    unsigned char* vs = ks + Cfg::kTileBytes;
+#pragma unroll
+    for (int i = 0; i < kF8PerThread; ++i) {
+      const int c = i * kAttnThreads + tid;
+      const int r = c / kF8Chunks, col = c - r * kF8Chunks;
+      const uint32_t dst = r * RB + col * 32;
+      const uint32_t* kw = reinterpret_cast<const uint32_t*>(&stage_k[i]);
+      const uint32_t* vw = reinterpret_cast<const uint32_t*>(&stage_v[i]);
+      uint4 a, b;
+      a.x = fp8x2_to_f16x2<KV>(kw[0]); a.y = fp8x2_to_f16x2<KV>(kw[0] >> 16);
+      a.z = fp8x2_to_f16x2<KV>(kw[1]); a.w = fp8x2_to_f16x2<KV>(kw[1] >> 16);
+      b.x = fp8x2_to_f16x2<KV>(kw[2]); b.y = fp8x2_to_f16x2<KV>(kw[2] >> 16);
+      b.z = fp8x2_to_f16x2<KV>(kw[3]); b.w = fp8x2_to_f16x2<KV>(kw[3] >> 16);
+      *reinterpret_cast<uint4*>(ks + dst) = a;
+      *reinterpret_cast<uint4*>(ks + dst + 16) = b;
+      a.x = fp8x2_to_f16x2<KV>(vw[0]); a.y = fp8x2_to_f16x2<KV>(vw[0] >> 16);
+      a.z = fp8x2_to_f16x2<KV>(vw[1]); a.w = fp8x2_to_f16x2<KV>(vw[1] >> 16);
+      b.x = fp8x2_to_f16x2<KV>(vw[2]); b.y = fp8x2_to_f16x2<KV>(vw[2] >> 16);
+      b.z = fp8x2_to_f16x2<KV>(vw[3]); b.w = fp8x2_to_f16x2<KV>(vw[3] >> 16);
+      *reinterpret_cast<uint4*>(vs + dst) = a;
+      *reinterpret_cast<uint4*>(vs + dst + 16) = b;
+    }
+  };
+
+  // ---- running state ---------------------------------------------------------------------------
+  const float scale2 = p.softmax_scale * kLog2e * ((KV != KVC_KV_AUTO && p.k_descale) ? __ldg(p.k_descale) : 1.0f);
+  float m_run[2] = {-INFINITY, -INFINITY};  // running maximum (log2 domain) of rows g and g + 8
+  float l_run[2] = {0.f, 0.f};              // this thread's share of the running sum of rows g and g + 8
+  float o_acc[SL / 8][4];                   // rows g / g + 8, columns warp * SL + nt * 8 + 2t, +1
+#pragma unroll
+  for (int i = 0; i < SL / 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+
+  const uint32_t q_base = smem_u32(s_q);
+  const uint32_t p_base = smem_u32(s_p);
+  // ldmatrix lane addressing (see the fragment layouts of mma.m16n8k16):
+  //   A operand (Q, P):  row = lane % 16, k offset = (lane / 16) * 8
+  //   B operand from K rows (tokens x d, no transpose): token = lane % 8 + (lane / 16) * 8, d offset = ((lane / 8) % 2) * 8
+  //   B operand from V rows (tokens x d, transposed):   token = lane % 8 + ((lane / 8) % 2) * 8, d offset = (lane / 16) * 8
+  const uint32_t a_lane_off_q = (lane & 15) * RB + (lane >> 4) * 16;
+  const uint32_t a_lane_off_p = (lane & 15) * kPRowBytes + (lane >> 4) * 16;
+  const uint32_t k_lane_off = ((lane & 7) + (lane >> 4) * 8) * RB + ((lane >> 3) & 1) * 16;
+  const uint32_t v_lane_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * RB + (lane >> 4) * 16;
+
+  // ---- prologue of the pipeline ---------------------------------------------------------------
+  if constexpr (KV == KVC_KV_AUTO) {
+#pragma unroll
+    for (int i = 0; i < NST - 1; ++i) {
+      if (tile_begin + i < tile_end) load_tile_async(tile_begin + i, i);
+      cp_async_commit();
+    }
+  } else {
+    load_tile_regs(tile_begin);
+  }
+
+  for (int tile = tile_begin; tile < tile_end; ++tile) {
+    const int stage = (tile - tile_begin) % NST;
+    if constexpr (KV == KVC_KV_AUTO) {
+      cp_async_wait<NST - 2>();  // this tile has landed
+      __syncthreads();           // ... for every thread; and the stage computed last iteration is free
+      const int next = tile + NST - 1;
+      if (next < tile_end) load_tile_async(next, (next - tile_begin) % NST);
+      cp_async_commit();
+    } else {
+      store_tile_regs(stage);    // the other stage may still be read by slower warps; this one is free
+      if (tile + 1 < tile_end) load_tile_regs(tile + 1);
+      __syncthreads();
+    }
+    const uint32_t ks = smem_u32(s_kv + stage * 2 * Cfg::kTileBytes);
+    const uint32_t vs = ks + Cfg::kTileBytes;
+
+    // ---- S = Q K^T for this warp's 16 tokens -------------------------------------------------
+    float s_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    const uint32_t k_warp = ks + warp * 16 * RB + k_lane_off;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t a[4], b[4];
+      ldmatrix_x4(a, q_base + a_lane_off_q + kk * 32);
+      ldmatrix_x4(b, k_warp + kk * 32);
+      mma_16816<T16>(s_acc[0], a, b[0], b[1]);
+      mma_16816<T16>(s_acc[1], a, b[2], b[3]);
+    }
+
+    // ---- scale, mask the tail, row maxima -----------------------------------------------------
+    const int tok_base = tile * kTileTokens + warp * 16 + 2 * t;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int token = tok_base + nt * 8 + (e & 1);
+        const float v = token < n ? s_acc[nt][e] * scale2 : -INFINITY;
+        s_acc[nt][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xFFFFFFFFu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xFFFFFFFFu, mx[r], 2));
+    }
+    if (t == 0) {
+      s_max[warp * kRows + g] = mx[0];
+      s_max[warp * kRows + g + 8] = mx[1];
+    }
+    __syncthreads();
+    float m_new[2], alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + 8 * r;
+      const float tile_max = fmaxf(fmaxf(s_max[row], s_max[kRows + row]), fmaxf(s_max[2 * kRows + row], s_max[3 * kRows + row]));
+      m_new[r] = fmaxf(m_run[r], tile_max);
+      alpha[r] = (m_new[r] == -INFINITY) ? 1.0f : exp2f(m_run[r] - m_new[r]);
+      m_run[r] = m_new[r];
+      l_run[r] *= alpha[r];
+    }
+
+    // ---- P = exp2(S - m) to shared memory (T16), row sums -------------------------------------
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      float pv[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        pv[e] = (m_new[r] == -INFINITY) ? 0.f : exp2f(s_acc[nt][e] - m_new[r]);
+      }
+      const uint32_t lo = pack2<T16>(pv[0], pv[1]), hi = pack2<T16>(pv[2], pv[3]);
+      // the sums use the rounded probabilities, the values the products will see
+      float r0a, r0b, r1a, r1b;
+      if constexpr (std::is_same_v<T16, __half>) {
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+        r0a = f0.x; r0b = f0.y; r1a = f1.x; r1b = f1.y;
+      } else {
+        r0a = __uint_as_float(lo << 16); r0b = __uint_as_float(lo & 0xFFFF0000u);
+        r1a = __uint_as_float(hi << 16); r1b = __uint_as_float(hi & 0xFFFF0000u);
+      }
+      l_run[0] += r0a + r0b;
+      l_run[1] += r1a + r1b;
+      const int col = warp * 16 + nt * 8 + 2 * t;  // token column inside the tile
+      *reinterpret_cast<uint32_t*>(s_p + g * kPRowBytes + col * 2) = lo;
+      *reinterpret_cast<uint32_t*>(s_p + (g + 8) * kPRowBytes + col * 2) = hi;
+    }
+    __syncthreads();
+
+    // ---- O[:, slice of this warp] = alpha * O + P V --------------------------------------------
+#pragma unroll
+    for (int i = 0; i < SL / 8; ++i) {
+      o_acc[i][0] *= alpha[0];
+      o_acc[i][1] *= alpha[0];
+      o_acc[i][2] *= alpha[1];
+      o_acc[i][3] *= alpha[1];
+    }
+    const uint32_t v_warp = vs + v_lane_off + warp * SL * 2;
+#pragma unroll
+    for (int kk = 0; kk < kTileTokens / 16; ++kk) {
+      uint32_t a[4];
+      ldmatrix_x4(a, p_base + a_lane_off_p + kk * 32);
+#pragma unroll
+      for (int np = 0; np < SL / 16; ++np) {  // two 8-column tiles per ldmatrix
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, v_warp + kk * 16 * RB + np * 32);
+        mma_16816<T16>(o_acc[2 * np], a, b[0], b[1]);
+        mma_16816<T16>(o_acc[2 * np + 1], a, b[2], b[3]);
+      }
+    }
+  }
+  if constexpr (KV == KVC_KV_AUTO) cp_async_wait<0>();
+
+  // ---- row sums across the lanes of a row and the four warps ----------------------------------
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xFFFFFFFFu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xFFFFFFFFu, l_run[r], 2);
+  }
+  __syncthreads();  // s_max / s_sum of the last tile are no longer read
+  if (t == 0) {
+    s_sum[warp * kRows + g] = l_run[0];
+    s_sum[warp * kRows + g + 8] = l_run[1];
+  }
+  __syncthreads();
+  const float v_descale = (KV != KVC_KV_AUTO && p.v_descale) ? __ldg(p.v_descale) : 1.0f;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = g + 8 * r;
+    if (row >= rows) continue;
+    float l = s_sum[row] + s_sum[kRows + row] + s_sum[2 * kRows + row] + s_sum[3 * kRows + row];
+    float m = m_run[r];
+    const int head = head0 + row;
+    if (p.num_splits > 1) {
+      const int64_t slot = (static_cast<int64_t>(seq) * p.num_heads + head) * p.num_splits + split;
+      if (warp == 0 && t == 0) p.part_lse[slot] = m + log2f(l);
+      float* po = p.part_out + slot * D + warp * SL + 2 * t;
+      const float inv = 1.0f / l;
+#pragma unroll
+      for (int i = 0; i < SL / 8; ++i)
+        *reinterpret_cast<float2*>(po + i * 8) = make_float2(o_acc[i][2 * r] * inv, o_acc[i][2 * r + 1] * inv);
+    } else {
+      float rescale = 1.0f;
+      if (p.sink) {  // one more logit in the denominator
+        const float sk = static_cast<float>(static_cast<const TQ*>(p.sink)[head]) * kLog2e;
+        const float mf = fmaxf(m, sk);
+        rescale = exp2f(m - mf);
+        l = l * rescale + exp2f(sk - mf);
+      }
+      const float f = rescale / l * v_descale;
+      TQ* o = static_cast<TQ*>(p.out) + seq * p.out_stride_t + head * p.out_stride_h + warp * SL + 2 * t;
+#pragma unroll
+      for (int i = 0; i < SL / 8; ++i) {
+        const uint32_t w = pack2<TQ>(o_acc[i][2 * r] * f, o_acc[i][2 * r + 1] * f);
+        *reinterpret_cast<uint32_t*>(o + i * 8) = w;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// merge of the splits: out = sum_p w_p o_p / (sum_p w_p [+ sink]),  w_p = exp2(lse_p - max lse)
+// ---------------------------------------------------------------------------------------------
+template <typename TQ>
+__global__ void __launch_bounds__(128) paged_decode_merge_kernel(const DecodeParams p, int head_size) {
+  const int seq = blockIdx.x / p.num_heads, head = blockIdx.x - seq * p.num_heads;
+  pdl_prologue();
+  const int64_t base = (static_cast<int64_t>(seq) * p.num_heads + head) * p.num_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < p.num_splits; ++s) m = fmaxf(m, p.part_lse[base + s]);
+  float sk = -INFINITY;
+  if (p.sink) sk = static_cast<float>(static_cast<const TQ*>(p.sink)[head]) * kLog2e;
+  TQ* o = static_cast<TQ*>(p.out) + seq * p.out_stride_t + head * p.out_stride_h;
+  if (m == -INFINITY) {  // no cached token at all
+    for (int d = threadIdx.x; d < head_size; d += blockDim.x) o[d] = TQ(0.0f);
+    return;
+  }
+  const float mf = fmaxf(m, sk);
+  float denom = (sk == -INFINITY) ? 0.f : exp2f(sk - mf);
+  for (int s = 0; s < p.num_splits; ++s) {
+    const float lse = p.part_lse[base + s];
+    if (lse != -INFINITY) denom += exp2f(lse - mf);
+  }
+  const float v_descale = p.v_descale ? __ldg(p.v_descale) : 1.0f;
+  const float inv = v_descale / denom;
+  for (int d = threadIdx.x; d < head_size; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < p.num_splits; ++s) {
+      const float lse = p.part_lse[base + s];
+      if (lse != -INFINITY) acc += exp2f(lse - mf) * p.part_out[(base + s) * head_size + d];
+    }
+    o[d] = TQ(acc * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kMaxSplits = 128;
+
+int pick_splits(int64_t ctas_without_split, int64_t max_tiles) {
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int64_t target = static_cast<int64_t>(sms) * 4;  // a few CTAs per SM
+  int64_t s = (target + ctas_without_split - 1) / ctas_without_split;
+  if (s > max_tiles) s = max_tiles;
+  if (s > kMaxSplits) s = kMaxSplits;
+  if (s < 1) s = 1;
+  return static_cast<int>(s);
+}
+
+template <typename TQ, int KV, int D>
+cudaError_t launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  using Cfg = DecodeCfg<TQ, KV, D>;
+  static std::once_flag once[64];
+  static cudaError_t attr_err[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::call_once(once[dev], [&] {
+    attr_err[dev] = cudaFuncSetAttribute(paged_decode_kernel<TQ, KV, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+  });
+  if (attr_err[dev] != cudaSuccess) return attr_err[dev];
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kAttnThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, paged_decode_kernel<TQ, KV, D>, p);
+}
+
+template <typename TQ, int KV>
+cudaError_t launch_decode_d(int head_size, const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  switch (head_size) {
+    case 64: return launch_decode<TQ, KV, 64>(p, grid, st);
+    case 128: return launch_decode<TQ, KV, 128>(p, grid, st);
+    case 192: return launch_decode<TQ, KV, 192>(p, grid, st);
+    default: return launch_decode<TQ, KV, 256>(p, grid, st);
+  }
+}
+
+template <typename TQ>
+cudaError_t launch_decode_kv(int kv, int head_size, const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  switch (kv) {
+    case KVC_KV_AUTO: return launch_decode_d<TQ, KVC_KV_AUTO>(head_size, p, grid, st);
+    case KVC_KV_FP8_E4M3: return launch_decode_d<TQ, KVC_KV_FP8_E4M3>(head_size, p, grid, st);
+    default: return launch_decode_d<TQ, KVC_KV_FP8_E5M2>(head_size, p, grid, st);
+  }
+}
+
+struct DecodePlan {
+  int splits;
+  int tiles_per_split;
+  int64_t workspace_bytes;
+};
+
+DecodePlan plan_decode(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads, int64_t head_size,
+                       int64_t max_seq_len) {
+  DecodePlan pl{1, 1, 0};
+  const int64_t group = num_kv_heads > 0 ? num_heads / num_kv_heads : 1;
+  const int64_t row_tiles = (group + kRows - 1) / kRows;
+  int64_t max_tiles = (max_seq_len + kTileTokens - 1) / kTileTokens;
+  if (max_tiles < 1) max_tiles = 1;
+  const int64_t base = num_seqs * num_kv_heads * row_tiles;
+  pl.splits = base > 0 ? pick_splits(base, max_tiles) : 1;
+  pl.tiles_per_split = static_cast<int>((max_tiles + pl.splits - 1) / pl.splits);
+  pl.splits = static_cast<int>((max_tiles + pl.tiles_per_split - 1) / pl.tiles_per_split);  // drop empty tails
+  if (pl.splits > 1) pl.workspace_bytes = num_seqs * num_heads * pl.splits * (head_size + 1) * (int64_t)sizeof(float);
+  return pl;
+}
+
+}  // namespace
+}  // namespace kvc
+
+extern "C" {
+
+KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads,
+                                                 int64_t head_size, int64_t max_seq_len) {
+  if (num_seqs <= 0 || num_heads <= 0 || num_kv_heads <= 0 || head_size <= 0 || max_seq_len < 0) return 0;
+  return kvc::plan_decode(num_seqs, num_heads, num_kv_heads, head_size, max_seq_len).workspace_bytes;
+}
+
+KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void* key_cache, const void* value_cache,
+                                       const int32_t* block_table, const int32_t* seq_lens, const void* sink,
+                                       const float* k_descale, const float* v_descale, void* workspace,
+                                       int64_t workspace_bytes, int64_t num_seqs, int64_t num_heads,
+                                       int64_t num_kv_heads, int64_t head_size, int64_t block_size,
+                                       int64_t block_table_stride, int64_t max_seq_len, int64_t query_stride_t,
+                                       int64_t query_stride_h, int64_t out_stride_t, int64_t out_stride_h,
+                                       int64_t block_stride, int64_t page_stride, int64_t head_stride,
+                                       float softmax_scale, int q_dtype, int kv_dtype, void* stream) {
+  using namespace kvc;
+  if (q_dtype != KVC_IN_F16 && q_dtype != KVC_IN_BF16)
+    return fail(KVC_ERR_UNSUPPORTED, "paged_decode_attention: query must be fp16 or bf16");
+  if (kv_dtype != KVC_KV_AUTO && kv_dtype != KVC_KV_FP8_E4M3 && kv_dtype != KVC_KV_FP8_E5M2)
+    return fail(KVC_ERR_UNSUPPORTED, "Unsupported data type of kv cache: code " + std::to_string(kv_dtype));
+  if (num_seqs < 0 || num_heads <= 0 || num_kv_heads <= 0 || block_size <= 0 || max_seq_len < 0)
+    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: sizes must be positive");
+  if (num_heads % num_kv_heads)
+    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: num_heads must be a multiple of num_kv_heads");
+  if (head_size != 64 && head_size != 128 && head_size != 192 && head_size != 256)
+    return fail(KVC_ERR_UNSUPPORTED, "paged_decode_attention: head_size must be 64, 128, 192 or 256");
+  if (num_seqs == 0) return KVC_OK;
+  if (num_seqs > 0x7FFFFFFFll || num_heads > 65535 * 16 || block_size > 0x7FFFFFFFll || max_seq_len > 0x7FFFFFFFll)
+    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: sizes out of range");
+  if (!out || !query || !key_cache || !value_cache || !block_table || !seq_lens)
+    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: out, query, caches, block_table and seq_lens must be non-NULL");
+  const int ces = kv_dtype == KVC_KV_AUTO ? 2 : 1;
+  const bool ok_align = aligned(query, 16) && aligned(out, 4) && aligned(key_cache, 16) && aligned(value_cache, 16) &&
+                        (query_stride_t * 2) % 16 == 0 && (query_stride_h * 2) % 16 == 0 && (out_stride_t * 2) % 4 == 0 &&
+                        (out_stride_h * 2) % 4 == 0 && (block_stride * ces) % 16 == 0 && (page_stride * ces) % 16 == 0 &&
+                        (head_stride * ces) % 16 == 0 && aligned(block_table, 4) && aligned(seq_lens, 4);
+  if (!ok_align)
+    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: query and cache rows must be 16-byte aligned");
+
+  const DecodePlan pl = plan_decode(num_seqs, num_heads, num_kv_heads, head_size, max_seq_len);
+  if (pl.splits > 1 && (!workspace || workspace_bytes < pl.workspace_bytes || !aligned(workspace, 16)))
+    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: workspace missing, misaligned (16 bytes) or too small; ask "
+                                         "kvc_paged_decode_workspace_bytes ("
+                                         + std::to_string(pl.workspace_bytes) + " bytes)");
+
+  DecodeParams p{};
+  p.out = out;
+  p.query = query;
+  p.key_cache = key_cache;
+  p.value_cache = value_cache;
+  p.block_table = block_table;
+  p.seq_lens = seq_lens;
+  p.sink = sink;
+  p.k_descale = k_descale;
+  p.v_descale = v_descale;
+  p.query_stride_t = query_stride_t;
+  p.query_stride_h = query_stride_h;
+  p.out_stride_t = out_stride_t;
+  p.out_stride_h = out_stride_h;
+  p.block_stride = block_stride;
+  p.page_stride = page_stride;
+  p.head_stride = head_stride;
+  p.block_table_stride = block_table_stride;
+  p.num_heads = static_cast<int32_t>(num_heads);
+  p.num_kv_heads = static_cast<int32_t>(num_kv_heads);
+  p.group = static_cast<int32_t>(num_heads / num_kv_heads);
+  p.row_tiles = (p.group + kRows - 1) / kRows;
+  p.block_size = static_cast<int32_t>(block_size);
+  p.num_splits = pl.splits;
+  p.tiles_per_split = pl.tiles_per_split;
+  p.softmax_scale = softmax_scale;
+  if (pl.splits > 1) {
+    p.part_out = static_cast<float*>(workspace);  // first: its float2 stores need 8-byte alignment
+    p.part_lse = p.part_out + num_seqs * num_heads * pl.splits * head_size;
+  }
+  const int64_t grid_y = static_cast<int64_t>(p.num_kv_heads) * p.row_tiles;
+  if (grid_y > 65535) return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: too many kv heads");
+  const dim3 grid(static_cast<unsigned>(num_seqs), static_cast<unsigned>(grid_y), static_cast<unsigned>(pl.splits));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = (q_dtype == KVC_IN_F16) ? launch_decode_kv<__half>(kv_dtype, static_cast<int>(head_size), p, grid, st)
+                                           : launch_decode_kv<__nv_bfloat16>(kv_dtype, static_cast<int>(head_size), p, grid, st);
+  if (e != cudaSuccess)
+    return fail(KVC_ERR_CUDA, std::string("paged_decode_attention launch failed: ") + cudaGetErrorString(e));
+  if (pl.splits > 1) {
+    const dim3 mgrid(static_cast<unsigned>(num_seqs * num_heads));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = mgrid;
+    cfg.blockDim = dim3(128);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = (q_dtype == KVC_IN_F16)
+            ? cudaLaunchKernelEx(&cfg, paged_decode_merge_kernel<__half>, p, static_cast<int>(head_size))
+            : cudaLaunchKernelEx(&cfg, paged_decode_merge_kernel<__nv_bfloat16>, p, static_cast<int>(head_size));
+    if (e != cudaSuccess)
+      return fail(KVC_ERR_CUDA, std::string("paged_decode_attention merge launch failed: ") + cudaGetErrorString(e));
+  }
+  return KVC_OK;
+}
+
+}  // extern "C"

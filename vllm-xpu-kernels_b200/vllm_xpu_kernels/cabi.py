@@ -36,6 +36,8 @@ SYMBOLS = (
     "kvc_dynamic_per_token_scaled_fp8_quant",
     "kvc_rotary_embedding",
     "kvc_rotary_embedding_and_cache_flash",
+    "kvc_paged_decode_workspace_bytes",
+    "kvc_paged_decode_attention",
 )
 
 _lib = None
@@ -77,6 +79,10 @@ def lib() -> ctypes.CDLL:
         L.kvc_dynamic_per_token_scaled_fp8_quant.argtypes = [vp, vp, vp, vp, i64, i64, ci, ci, vp]
         L.kvc_count_bad_slots.restype = ci
         L.kvc_count_bad_slots.argtypes = [vp, i64, i64, vp, vp]
+        L.kvc_paged_decode_workspace_bytes.restype = i64
+        L.kvc_paged_decode_workspace_bytes.argtypes = [i64] * 5
+        L.kvc_paged_decode_attention.restype = ci
+        L.kvc_paged_decode_attention.argtypes = [vp] * 10 + [i64] * 15 + [ctypes.c_float, ci, ci, vp]
         L.kvc_rotary_embedding.restype = ci
         L.kvc_rotary_embedding.argtypes = [vp] * 4 + [i64] * 10 + [ci, ci, vp]
         L.kvc_rotary_embedding_and_cache_flash.restype = ci
@@ -306,3 +312,25 @@ def rotary_embedding_and_cache_flash(positions, query, key, value, head_size: in
         value.stride(0), value.stride(1), key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
         int(bool(is_neox)), int(bool(write_back_key)), _in_dtype(query), kv, _scale_ptr(k_scale, kv),
         _scale_ptr(v_scale, kv), _stream(stream)))
+
+
+def paged_decode_attention(query, key_cache, value_cache, block_table, seq_lens, softmax_scale: float,
+                           max_seq_len: int, kv_cache_dtype: str = "auto", k_descale=None, v_descale=None, sink=None,
+                           out=None, stream=None):
+    """``kvc_paged_decode_attention``: query [S, Hq, D] (fp16 / bf16), caches [num_blocks, block_size, Hkv, D]
+    (the query's type, or fp8 / uint8 bytes with ``kv_cache_dtype`` "fp8*"), block_table int32 [S, max_blocks],
+    seq_lens int32 [S]; ``k_descale`` / ``v_descale`` device fp32 scalars; ``sink`` [Hq].  Returns ``out``."""
+    kv = parse_kv_cache_dtype(kv_cache_dtype)
+    S, hq, D = query.shape
+    hk = key_cache.shape[2]
+    if out is None:
+        out = torch.empty_like(query)
+    nbytes = lib().kvc_paged_decode_workspace_bytes(S, hq, hk, D, max_seq_len)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=query.device)
+    _check(lib().kvc_paged_decode_attention(
+        out.data_ptr(), query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), block_table.data_ptr(),
+        seq_lens.data_ptr(), 0 if sink is None else sink.data_ptr(), _scale_ptr(k_descale, kv),
+        _scale_ptr(v_descale, kv), ws.data_ptr(), ws.numel(), S, hq, hk, D, key_cache.shape[1], block_table.stride(0),
+        max_seq_len, query.stride(0), query.stride(1), out.stride(0), out.stride(1), key_cache.stride(0),
+        key_cache.stride(1), key_cache.stride(2), float(softmax_scale), _in_dtype(query), kv, _stream(stream)))
+    return out
