@@ -25,10 +25,12 @@ from vllm_xpu_kernels import cabi  # noqa: E402
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--layout", choices=["flash", "paged", "mla", "gather", "quant-static", "quant-dynamic", "quant-token",
-                                         "rope", "rope-cache", "rope-then-cache"], default="flash",
+                                         "rope", "rope-cache", "rope-then-cache", "decode"], default="flash",
                     help="mla: concat_and_cache_mla (512 + 64 wide entries); gather: gather_cache of such entries; "
                          "rope: rotary_embedding; rope-cache: the fused rotary_embedding_and_cache_flash; "
                          "rope-then-cache: the two separate ops back to back (what the fused op replaces)")
+    ap.add_argument("--seqs", type=int, default=64, help="decode: sequences in the batch (one query token each)")
+    ap.add_argument("--seq-len", type=int, default=4096, help="decode: cached tokens per sequence")
     ap.add_argument("--q-heads", type=int, default=64, help="query heads of the rope layouts (--heads are kv heads)")
     ap.add_argument("--rot-dim", type=int, default=0, help="rotary dim of the rope layouts (0: head size)")
     ap.add_argument("--gptj", action="store_true", help="interleaved pairs instead of the NeoX halves")
@@ -58,6 +60,9 @@ def main() -> None:
         return
     if ns.layout.startswith("rope"):
         run_rope(ns, dev)
+        return
+    if ns.layout == "decode":
+        run_decode(ns, dev)
         return
     dt = {"bfloat16": torch.bfloat16, "half": torch.float16, "float": torch.float32}[ns.dtype]
     T, H, D, bs = ns.tokens, ns.heads, ns.head_size, ns.block_size
@@ -251,6 +256,41 @@ def run_rope(ns, dev) -> None:
     print(f"layout={ns.layout} kv={ns.kv} dtype={ns.dtype} T={T} Hq={hq} Hkv={hk} D={D} rot_dim={R} "
           f"style={'neox' if neox else 'gptj'} algorithmic_bytes={alg} launches={ns.launches} "
           f"event_us={['%.1f' % t for t in times]} best_GBps={alg / best / 1e3:.0f}")
+
+
+def run_decode(ns, dev) -> None:
+    """Paged decode attention: --seqs sequences of --seq-len cached tokens, --q-heads query heads over --heads kv
+    heads.  Every launch streams the whole cache (larger than L2 at the default size), so one buffer set is enough."""
+    dt = {"bfloat16": torch.bfloat16, "half": torch.float16}[ns.dtype]
+    S, L, hq, hk, D, bs = ns.seqs, ns.seq_len, ns.q_heads, ns.heads, ns.head_size, ns.block_size
+    blocks_per_seq = (L + bs - 1) // bs
+    nb = S * blocks_per_seq
+    es = 2 if ns.kv == "auto" else 1
+    if ns.kv == "auto":
+        kc = torch.randn(nb, bs, hk, D, device=dev).to(dt)
+        vc = torch.randn(nb, bs, hk, D, device=dev).to(dt)
+    else:
+        kc = torch.randint(0, 120, (nb, bs, hk, D), device=dev, dtype=torch.uint8)
+        vc = torch.randint(0, 120, (nb, bs, hk, D), device=dev, dtype=torch.uint8)
+    table = torch.randperm(nb, device=dev).view(S, blocks_per_seq).to(torch.int32)
+    lens = torch.full((S,), L, dtype=torch.int32, device=dev)
+    query = torch.randn(S, hq, D, device=dev).to(dt)
+    out = torch.empty_like(query)
+    ds = torch.tensor(0.05, device=dev)
+    alg = 2 * S * L * hk * D * es + 2 * S * hq * D * 2 + 4 * S * blocks_per_seq + 4 * S
+    evs = []
+    for i in range(ns.launches):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        cabi.paged_decode_attention(query, kc, vc, table, lens, D ** -0.5, L, ns.kv, ds, ds, out=out)
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    times = [a.elapsed_time(b) * 1e3 for a, b in evs]
+    best = min(times[1:]) if len(times) > 1 else times[0]
+    print(f"layout=decode kv={ns.kv} dtype={ns.dtype} seqs={S} seq_len={L} Hq={hq} Hkv={hk} D={D} bs={bs} "
+          f"algorithmic_bytes={alg} launches={ns.launches} event_us={['%.1f' % t for t in times]} "
+          f"best_GBps={alg / best / 1e3:.0f}")
 
 
 if __name__ == "__main__":

@@ -28,7 +28,6 @@ namespace {
 constexpr int kAttnThreads = 128;       // 4 warps
 constexpr int kTileTokens = 64;         // tokens per pipeline stage; warp w owns tokens [16w, 16w + 16) for Q.K
 constexpr int kRows = 16;               // query rows per CTA (the heads of one kv group, padded)
-constexpr int kPRowBytes = kTileTokens * 2 + 16;
 constexpr float kLog2e = 1.4426950408889634f;
 
 // ---------------------------------------------------------------------------------------------
@@ -126,18 +125,26 @@ struct DecodeParams {
 // ---------------------------------------------------------------------------------------------
 // TQ: type of query and output.  KV: KVC_KV_AUTO (cache holds TQ) or an fp8 code (cache holds bytes that
 // are widened to fp16 on their way into shared memory; the products then run in fp16).  D: head size.
+//
+// A CTA owns (sequence, kv head, up to 16 query heads of its group, one split of the sequence) and walks
+// the split in tiles of 64 tokens through a two-stage shared-memory ring.  Warp w owns tokens
+// [16w, 16w + 16) of every tile for BOTH products: it keeps its own running maximum, sum and a full
+// 16 x D accumulator, the probabilities go from the first product's accumulators straight into the second
+// product's A operand, and the four warps meet only at the pipeline barrier (one per tile) and in the
+// final merge of their partial results.
 template <typename TQ, int KV, int D>
 struct DecodeCfg {
   using T16 = std::conditional_t<KV == KVC_KV_AUTO, TQ, __half>;  // operand type of the matrix products
   static constexpr int kRowBytes = D * 2 + 16;                     // shared-memory row of K, V and Q (16 B pad:
                                                                     // eight consecutive rows hit distinct banks)
   static constexpr int kTileBytes = kTileTokens * kRowBytes;       // one K or V tile
-  static constexpr int kStages = (KV != KVC_KV_AUTO) ? 2 : (D <= 128 ? 3 : 2);
+  static constexpr int kStages = 2;
   static constexpr int kSmemQ = kRows * kRowBytes;
-  static constexpr int kSmemP = kRows * kPRowBytes;
-  static constexpr int kSmemRed = 2 * 4 * kRows * (int)sizeof(float);
-  static constexpr int kSmemBytes = kStages * 2 * kTileBytes + kSmemQ + kSmemP + kSmemRed;
-  static constexpr int kSliceCols = D / 4;  // output columns owned by a warp in P.V
+  static constexpr int kSmemOff = 2 * kTileTokens * (int)sizeof(int64_t);  // row offsets of two tiles
+  static constexpr int kSmemBytes = kStages * 2 * kTileBytes + kSmemQ + kSmemOff;
+  // the final merge reuses the ring: 4 warps x (16 x D fp32 + 32 floats of statistics)
+  static_assert(4 * (kRows * D + 2 * kRows) * (int)sizeof(float) <= kStages * 2 * kTileBytes, "merge buffer fits");
+  static constexpr bool kQInRegs = D <= 128;  // query fragments stay in registers (else re-read per tile)
   static_assert(D % 64 == 0 && D <= 256, "head sizes 64, 128, 192, 256");
 };
 
@@ -146,24 +153,21 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
   using Cfg = DecodeCfg<TQ, KV, D>;
   using T16 = typename Cfg::T16;
   constexpr int RB = Cfg::kRowBytes;
-  constexpr int NST = Cfg::kStages;
-  constexpr int SL = Cfg::kSliceCols;
+  constexpr int NT = D / 8;  // 8-column tiles of the output accumulator
 
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* s_kv = smem;                                  // NST x (K tile, V tile)
-  unsigned char* s_q = s_kv + NST * 2 * Cfg::kTileBytes;       // [16][RB]
-  unsigned char* s_p = s_q + Cfg::kSmemQ;                      // [16][kPRowBytes]
-  float* s_max = reinterpret_cast<float*>(s_p + Cfg::kSmemP);  // [4 warps][16 rows]
-  float* s_sum = s_max + 4 * kRows;                            // [4 warps][16 rows]
+  unsigned char* s_kv = smem;                                       // 2 stages x (K tile, V tile)
+  unsigned char* s_q = s_kv + Cfg::kStages * 2 * Cfg::kTileBytes;   // [16][RB]
+  int64_t* s_off = reinterpret_cast<int64_t*>(s_q + Cfg::kSmemQ);   // [2][64] element offsets, -1 = no such token
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;  // accumulator row (and row + 8) and column pair of this lane
   const int seq = blockIdx.x;
   const int kvh = blockIdx.y / p.row_tiles, row_tile = blockIdx.y - kvh * p.row_tiles;
   const int split = blockIdx.z;
-  const int row0 = row_tile * kRows;                       // first group-local query row of this CTA
-  const int rows = min(kRows, p.group - row0);             // valid rows
-  const int head0 = kvh * p.group + row0;                  // first query head of this CTA
+  const int row0 = row_tile * kRows;             // first group-local query row of this CTA
+  const int rows = min(kRows, p.group - row0);   // valid rows
+  const int head0 = kvh * p.group + row0;        // first query head of this CTA
 
   pdl_prologue();
 
@@ -204,139 +208,164 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
     }
   }
 
-  // ---- producer: one tile of K and V rows into a stage ---------------------------------------
+  // ---- producer ----------------------------------------------------------------------------------
+  // Row offsets (block-table lookup, one per token) are computed by the first 64 threads one tile ahead and
+  // handed over through shared memory; the copies themselves are fully coalesced: consecutive threads take
+  // consecutive 16-byte chunks of a row.
   const int32_t* table = p.block_table + seq * p.block_table_stride;
   const int64_t head_off = static_cast<int64_t>(kvh) * p.head_stride;
-  auto row_offset = [&](int token) -> int64_t {  // element offset of a cached token's row for this kv head
-    const int blk_idx = token / p.block_size;
-    const int64_t blk = table[blk_idx];
-    return blk * p.block_stride + static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride + head_off;
+  auto publish_offsets = [&](int tile) {  // by threads 0..63, into slot (tile - tile_begin) % 2
+    if (tid < kTileTokens) {
+      const int token = tile * kTileTokens + tid;
+      int64_t off = -1;
+      if (tile < tile_end && token < n) {
+        const int blk_idx = token / p.block_size;
+        off = static_cast<int64_t>(__ldg(table + blk_idx)) * p.block_stride +
+              static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride + head_off;
+      }
+      s_off[((tile - tile_begin) & 1) * kTileTokens + tid] = off;
+    }
   };
 
   [[maybe_unused]] auto load_tile_async = [&](int tile, int stage) {  // 16-bit cache: cp.async
-    constexpr int kChunks = D / 8;
-    constexpr int kPerThread = kTileTokens * kChunks / kAttnThreads;
+    constexpr int kChunks = D / 8;                               // 16-byte chunks per row
+    constexpr int kRowsPerPass = kAttnThreads / kChunks;         // rows covered by one instruction of the CTA
+    static_assert(kAttnThreads % kChunks == 0 || kChunks == 24, "chunk mapping");
+    const int64_t* offs = s_off + ((tile - tile_begin) & 1) * kTileTokens;
     unsigned char* ks = s_kv + stage * 2 * Cfg::kTileBytes;
-    unsigned char* vs = ks + Cfg::kTileBytes;
-    const int tok0 = tile * kTileTokens;
+    if constexpr (kAttnThreads % kChunks == 0) {
+      const int r0 = tid / kChunks, col = tid - r0 * kChunks;
 #pragma unroll
-    for (int i = 0; i < kPerThread; ++i) {
-      const int c = i * kAttnThreads + tid;
-      const int r = c / kChunks, col = c - r * kChunks;
-      const int token = tok0 + r;
-      const bool valid = token < n;
-      const int64_t off = valid ? row_offset(token) + col * 8 : 0;
-      const uint32_t dst = r * RB + col * 16;
-      cp_async_16(smem_u32(ks + dst), static_cast<const T16*>(p.key_cache) + off, valid ? 16 : 0);
-      cp_async_16(smem_u32(vs + dst), static_cast<const T16*>(p.value_cache) + off, valid ? 16 : 0);
+      for (int i = 0; i < kTileTokens / kRowsPerPass; ++i) {
+        const int r = r0 + i * kRowsPerPass;
+        const int64_t off = offs[r];
+        const int64_t src = (off < 0 ? 0 : off) + col * 8;
+        const uint32_t dst = smem_u32(ks + r * RB + col * 16);
+        cp_async_16(dst, static_cast<const T16*>(p.key_cache) + src, off < 0 ? 0 : 16);
+        cp_async_16(dst + Cfg::kTileBytes, static_cast<const T16*>(p.value_cache) + src, off < 0 ? 0 : 16);
+      }
+    } else {  // D = 192: 24 chunks per row
+      for (int c = tid; c < kTileTokens * kChunks; c += kAttnThreads) {
+        const int r = c / kChunks, col = c - r * kChunks;
+        const int64_t off = offs[r];
+        const int64_t src = (off < 0 ? 0 : off) + col * 8;
+        const uint32_t dst = smem_u32(ks + r * RB + col * 16);
+        cp_async_16(dst, static_cast<const T16*>(p.key_cache) + src, off < 0 ? 0 : 16);
+        cp_async_16(dst + Cfg::kTileBytes, static_cast<const T16*>(p.value_cache) + src, off < 0 ? 0 : 16);
+      }
     }
   };
 
   // fp8 cache: 16 bytes (16 elements) per chunk through registers, widened to fp16 when stored.
-  constexpr int kF8Chunks = D / 16;
+  constexpr int kF8Chunks = D / 16;                                            // chunks per row
   constexpr int kF8PerThread = (KV != KVC_KV_AUTO) ? kTileTokens * kF8Chunks / kAttnThreads : 1;
   [[maybe_unused]] uint4 stage_k[kF8PerThread], stage_v[kF8PerThread];
   [[maybe_unused]] auto load_tile_regs = [&](int tile) {
-    const int tok0 = tile * kTileTokens;
+    const int64_t* offs = s_off + ((tile - tile_begin) & 1) * kTileTokens;
 #pragma unroll
     for (int i = 0; i < kF8PerThread; ++i) {
       const int c = i * kAttnThreads + tid;
       const int r = c / kF8Chunks, col = c - r * kF8Chunks;
-      const int token = tok0 + r;
+      const int64_t off = offs[r];
       stage_k[i] = make_uint4(0, 0, 0, 0);
       stage_v[i] = make_uint4(0, 0, 0, 0);
-      if (token < n) {
-        const int64_t off = row_offset(token) + col * 16;
-        stage_k[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(p.key_cache) + off));
-        stage_v[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(p.value_cache) + off));
+      if (off >= 0) {
+        stage_k[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(p.key_cache) + off + col * 16));
+        stage_v[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(p.value_cache) + off + col * 16));
       }
     }
   };
+  [[maybe_unused]] auto widen = [](const uint4& v, uint4& a, uint4& b) {
+    a.x = fp8x2_to_f16x2<KV>(v.x); a.y = fp8x2_to_f16x2<KV>(v.x >> 16);
+    a.z = fp8x2_to_f16x2<KV>(v.y); a.w = fp8x2_to_f16x2<KV>(v.y >> 16);
+    b.x = fp8x2_to_f16x2<KV>(v.z); b.y = fp8x2_to_f16x2<KV>(v.z >> 16);
+    b.z = fp8x2_to_f16x2<KV>(v.w); b.w = fp8x2_to_f16x2<KV>(v.w >> 16);
+  };
   [[maybe_unused]] auto store_tile_regs = [&](int stage) {
     unsigned char* ks = s_kv + stage * 2 * Cfg::kTileBytes;
-    unsigned char* vs = ks + Cfg::kTileBytes;
 #pragma unroll
     for (int i = 0; i < kF8PerThread; ++i) {
       const int c = i * kAttnThreads + tid;
       const int r = c / kF8Chunks, col = c - r * kF8Chunks;
-      const uint32_t dst = r * RB + col * 32;
-      const uint32_t* kw = reinterpret_cast<const uint32_t*>(&stage_k[i]);
-      const uint32_t* vw = reinterpret_cast<const uint32_t*>(&stage_v[i]);
+      unsigned char* dst = ks + r * RB + col * 32;
       uint4 a, b;
-      a.x = fp8x2_to_f16x2<KV>(kw[0]); a.y = fp8x2_to_f16x2<KV>(kw[0] >> 16);
-      a.z = fp8x2_to_f16x2<KV>(kw[1]); a.w = fp8x2_to_f16x2<KV>(kw[1] >> 16);
-      b.x = fp8x2_to_f16x2<KV>(kw[2]); b.y = fp8x2_to_f16x2<KV>(kw[2] >> 16);
-      b.z = fp8x2_to_f16x2<KV>(kw[3]); b.w = fp8x2_to_f16x2<KV>(kw[3] >> 16);
-      *reinterpret_cast<uint4*>(ks + dst) = a;
-      *reinterpret_cast<uint4*>(ks + dst + 16) = b;
-      a.x = fp8x2_to_f16x2<KV>(vw[0]); a.y = fp8x2_to_f16x2<KV>(vw[0] >> 16);
-      a.z = fp8x2_to_f16x2<KV>(vw[1]); a.w = fp8x2_to_f16x2<KV>(vw[1] >> 16);
-      b.x = fp8x2_to_f16x2<KV>(vw[2]); b.y = fp8x2_to_f16x2<KV>(vw[2] >> 16);
-      b.z = fp8x2_to_f16x2<KV>(vw[3]); b.w = fp8x2_to_f16x2<KV>(vw[3] >> 16);
-      *reinterpret_cast<uint4*>(vs + dst) = a;
-      *reinterpret_cast<uint4*>(vs + dst + 16) = b;
+      widen(stage_k[i], a, b);
+      *reinterpret_cast<uint4*>(dst) = a;
+      *reinterpret_cast<uint4*>(dst + 16) = b;
+      widen(stage_v[i], a, b);
+      *reinterpret_cast<uint4*>(dst + Cfg::kTileBytes) = a;
+      *reinterpret_cast<uint4*>(dst + Cfg::kTileBytes + 16) = b;
     }
   };
 
-  // ---- running state ---------------------------------------------------------------------------
+  // ---- running state of this warp ----------------------------------------------------------------
   const float scale2 = p.softmax_scale * kLog2e * ((KV != KVC_KV_AUTO && p.k_descale) ? __ldg(p.k_descale) : 1.0f);
   float m_run[2] = {-INFINITY, -INFINITY};  // running maximum (log2 domain) of rows g and g + 8
-  float l_run[2] = {0.f, 0.f};              // this thread's share of the running sum of rows g and g + 8
-  float o_acc[SL / 8][4];                   // rows g / g + 8, columns warp * SL + nt * 8 + 2t, +1
+  float l_run[2] = {0.f, 0.f};              // this lane's share of the running sums of rows g and g + 8
+  float o_acc[NT][4];                       // rows g (c0, c1) / g + 8 (c2, c3), columns nt * 8 + 2t, + 1
 #pragma unroll
-  for (int i = 0; i < SL / 8; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+  for (int i = 0; i < NT; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
 
   const uint32_t q_base = smem_u32(s_q);
-  const uint32_t p_base = smem_u32(s_p);
-  // ldmatrix lane addressing (see the fragment layouts of mma.m16n8k16):
-  //   A operand (Q, P):  row = lane % 16, k offset = (lane / 16) * 8
+  // ldmatrix lane addressing (fragment layouts of mma.m16n8k16):
+  //   A operand (Q):  row = lane % 16, k offset = (lane / 16) * 8
   //   B operand from K rows (tokens x d, no transpose): token = lane % 8 + (lane / 16) * 8, d offset = ((lane / 8) % 2) * 8
   //   B operand from V rows (tokens x d, transposed):   token = lane % 8 + ((lane / 8) % 2) * 8, d offset = (lane / 16) * 8
   const uint32_t a_lane_off_q = (lane & 15) * RB + (lane >> 4) * 16;
-  const uint32_t a_lane_off_p = (lane & 15) * kPRowBytes + (lane >> 4) * 16;
-  const uint32_t k_lane_off = ((lane & 7) + (lane >> 4) * 8) * RB + ((lane >> 3) & 1) * 16;
-  const uint32_t v_lane_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * RB + (lane >> 4) * 16;
+  const uint32_t k_lane_off = (warp * 16 + (lane & 7) + (lane >> 4) * 8) * RB + ((lane >> 3) & 1) * 16;
+  const uint32_t v_lane_off = (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * RB + (lane >> 4) * 16;
 
-  // ---- prologue of the pipeline ---------------------------------------------------------------
+  // ---- prologue of the pipeline -------------------------------------------------------------------
+  publish_offsets(tile_begin);
+  publish_offsets(tile_begin + 1);
+  __syncthreads();  // offsets and query rows are visible
   if constexpr (KV == KVC_KV_AUTO) {
-#pragma unroll
-    for (int i = 0; i < NST - 1; ++i) {
-      if (tile_begin + i < tile_end) load_tile_async(tile_begin + i, i);
-      cp_async_commit();
-    }
+    load_tile_async(tile_begin, 0);
+    cp_async_commit();
   } else {
     load_tile_regs(tile_begin);
   }
+  [[maybe_unused]] uint32_t qf[Cfg::kQInRegs ? D / 16 : 1][4];
+  if constexpr (Cfg::kQInRegs) {
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) ldmatrix_x4(qf[kk], q_base + a_lane_off_q + kk * 32);
+  }
 
   for (int tile = tile_begin; tile < tile_end; ++tile) {
-    const int stage = (tile - tile_begin) % NST;
+    const int stage = (tile - tile_begin) & 1;
     if constexpr (KV == KVC_KV_AUTO) {
-      cp_async_wait<NST - 2>();  // this tile has landed
-      __syncthreads();           // ... for every thread; and the stage computed last iteration is free
-      const int next = tile + NST - 1;
-      if (next < tile_end) load_tile_async(next, (next - tile_begin) % NST);
+      cp_async_wait<0>();  // this tile has landed
+      __syncthreads();     // ... for every thread; the other stage and the older offset slot are free
+      if (tile + 1 < tile_end) load_tile_async(tile + 1, stage ^ 1);
       cp_async_commit();
+      publish_offsets(tile + 2);  // into the slot this tile's copies were issued from
     } else {
-      store_tile_regs(stage);    // the other stage may still be read by slower warps; this one is free
+      store_tile_regs(stage);  // the stage computed two tiles ago; everyone is past it (barrier of the last tile)
+      __syncthreads();         // this tile is in shared memory; offsets of tile + 1 are visible
       if (tile + 1 < tile_end) load_tile_regs(tile + 1);
-      __syncthreads();
+      publish_offsets(tile + 2);
     }
     const uint32_t ks = smem_u32(s_kv + stage * 2 * Cfg::kTileBytes);
     const uint32_t vs = ks + Cfg::kTileBytes;
 
-    // ---- S = Q K^T for this warp's 16 tokens -------------------------------------------------
+    // ---- S = Q K^T for this warp's 16 tokens ---------------------------------------------------
     float s_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    const uint32_t k_warp = ks + warp * 16 * RB + k_lane_off;
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
-      uint32_t a[4], b[4];
-      ldmatrix_x4(a, q_base + a_lane_off_q + kk * 32);
-      ldmatrix_x4(b, k_warp + kk * 32);
-      mma_16816<T16>(s_acc[0], a, b[0], b[1]);
-      mma_16816<T16>(s_acc[1], a, b[2], b[3]);
+      uint32_t b[4];
+      ldmatrix_x4(b, ks + k_lane_off + kk * 32);
+      if constexpr (Cfg::kQInRegs) {
+        mma_16816<T16>(s_acc[0], qf[kk], b[0], b[1]);
+        mma_16816<T16>(s_acc[1], qf[kk], b[2], b[3]);
+      } else {
+        uint32_t a[4];
+        ldmatrix_x4(a, q_base + a_lane_off_q + kk * 32);
+        mma_16816<T16>(s_acc[0], a, b[0], b[1]);
+        mma_16816<T16>(s_acc[1], a, b[2], b[3]);
+      }
     }
 
-    // ---- scale, mask the tail, row maxima -----------------------------------------------------
+    // ---- scale, mask the tail, running maximum of this warp's rows ------------------------------
     const int tok_base = tile * kTileTokens + warp * 16 + 2 * t;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -349,107 +378,109 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
     }
+    float alpha[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xFFFFFFFFu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xFFFFFFFFu, mx[r], 2));
-    }
-    if (t == 0) {
-      s_max[warp * kRows + g] = mx[0];
-      s_max[warp * kRows + g + 8] = mx[1];
-    }
-    __syncthreads();
-    float m_new[2], alpha[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      const int row = g + 8 * r;
-      const float tile_max = fmaxf(fmaxf(s_max[row], s_max[kRows + row]), fmaxf(s_max[2 * kRows + row], s_max[3 * kRows + row]));
-      m_new[r] = fmaxf(m_run[r], tile_max);
-      alpha[r] = (m_new[r] == -INFINITY) ? 1.0f : exp2f(m_run[r] - m_new[r]);
-      m_run[r] = m_new[r];
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      alpha[r] = (m_new == -INFINITY) ? 1.0f : exp2f(m_run[r] - m_new);
+      m_run[r] = m_new;
       l_run[r] *= alpha[r];
     }
 
-    // ---- P = exp2(S - m) to shared memory (T16), row sums -------------------------------------
+    // ---- P = exp2(S - m), rounded to T16: the A operand of the second product ---------------------
+    uint32_t pa[4];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       float pv[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1;
-        pv[e] = (m_new[r] == -INFINITY) ? 0.f : exp2f(s_acc[nt][e] - m_new[r]);
+        pv[e] = (m_run[r] == -INFINITY) ? 0.f : exp2f(s_acc[nt][e] - m_run[r]);
       }
       const uint32_t lo = pack2<T16>(pv[0], pv[1]), hi = pack2<T16>(pv[2], pv[3]);
-      // the sums use the rounded probabilities, the values the products will see
-      float r0a, r0b, r1a, r1b;
+      pa[2 * nt] = lo;       // row g,     tokens nt * 8 + 2t, + 1
+      pa[2 * nt + 1] = hi;   // row g + 8
+      // the sums use the rounded probabilities, the values the product will see
       if constexpr (std::is_same_v<T16, __half>) {
         const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&lo));
         const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&hi));
-        r0a = f0.x; r0b = f0.y; r1a = f1.x; r1b = f1.y;
+        l_run[0] += f0.x + f0.y;
+        l_run[1] += f1.x + f1.y;
       } else {
-        r0a = __uint_as_float(lo << 16); r0b = __uint_as_float(lo & 0xFFFF0000u);
-        r1a = __uint_as_float(hi << 16); r1b = __uint_as_float(hi & 0xFFFF0000u);
+        l_run[0] += __uint_as_float(lo << 16) + __uint_as_float(lo & 0xFFFF0000u);
+        l_run[1] += __uint_as_float(hi << 16) + __uint_as_float(hi & 0xFFFF0000u);
       }
-      l_run[0] += r0a + r0b;
-      l_run[1] += r1a + r1b;
-      const int col = warp * 16 + nt * 8 + 2 * t;  // token column inside the tile
-      *reinterpret_cast<uint32_t*>(s_p + g * kPRowBytes + col * 2) = lo;
-      *reinterpret_cast<uint32_t*>(s_p + (g + 8) * kPRowBytes + col * 2) = hi;
     }
-    __syncthreads();
 
-    // ---- O[:, slice of this warp] = alpha * O + P V --------------------------------------------
+    // ---- O = alpha * O + P V over this warp's 16 tokens -------------------------------------------
+    if (__any_sync(0xFFFFFFFFu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {  // the maximum rarely moves
 #pragma unroll
-    for (int i = 0; i < SL / 8; ++i) {
-      o_acc[i][0] *= alpha[0];
-      o_acc[i][1] *= alpha[0];
-      o_acc[i][2] *= alpha[1];
-      o_acc[i][3] *= alpha[1];
-    }
-    const uint32_t v_warp = vs + v_lane_off + warp * SL * 2;
-#pragma unroll
-    for (int kk = 0; kk < kTileTokens / 16; ++kk) {
-      uint32_t a[4];
-      ldmatrix_x4(a, p_base + a_lane_off_p + kk * 32);
-#pragma unroll
-      for (int np = 0; np < SL / 16; ++np) {  // two 8-column tiles per ldmatrix
-        uint32_t b[4];
-        ldmatrix_x4_trans(b, v_warp + kk * 16 * RB + np * 32);
-        mma_16816<T16>(o_acc[2 * np], a, b[0], b[1]);
-        mma_16816<T16>(o_acc[2 * np + 1], a, b[2], b[3]);
+      for (int i = 0; i < NT; ++i) {
+        o_acc[i][0] *= alpha[0];
+        o_acc[i][1] *= alpha[0];
+        o_acc[i][2] *= alpha[1];
+        o_acc[i][3] *= alpha[1];
       }
+    }
+#pragma unroll
+    for (int np = 0; np < D / 16; ++np) {  // two 8-column tiles per ldmatrix
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, vs + v_lane_off + np * 32);
+      mma_16816<T16>(o_acc[2 * np], pa, b[0], b[1]);
+      mma_16816<T16>(o_acc[2 * np + 1], pa, b[2], b[3]);
     }
   }
   if constexpr (KV == KVC_KV_AUTO) cp_async_wait<0>();
 
-  // ---- row sums across the lanes of a row and the four warps ----------------------------------
+  // ---- merge the four warps' partial results through shared memory ---------------------------------
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     l_run[r] += __shfl_xor_sync(0xFFFFFFFFu, l_run[r], 1);
     l_run[r] += __shfl_xor_sync(0xFFFFFFFFu, l_run[r], 2);
   }
-  __syncthreads();  // s_max / s_sum of the last tile are no longer read
+  __syncthreads();  // nobody reads the ring any more
+  float* s_o = reinterpret_cast<float*>(smem);           // [4 warps][16 rows][D]
+  float* s_m = s_o + 4 * kRows * D;                      // [4][16]
+  float* s_l = s_m + 4 * kRows;                          // [4][16]
   if (t == 0) {
-    s_sum[warp * kRows + g] = l_run[0];
-    s_sum[warp * kRows + g + 8] = l_run[1];
+    s_m[warp * kRows + g] = m_run[0];
+    s_m[warp * kRows + g + 8] = m_run[1];
+    s_l[warp * kRows + g] = l_run[0];
+    s_l[warp * kRows + g + 8] = l_run[1];
+  }
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    float* dst = s_o + (warp * kRows + g) * D + i * 8 + 2 * t;
+    *reinterpret_cast<float2*>(dst) = make_float2(o_acc[i][0], o_acc[i][1]);
+    *reinterpret_cast<float2*>(dst + 8 * D) = make_float2(o_acc[i][2], o_acc[i][3]);
   }
   __syncthreads();
+
   const float v_descale = (KV != KVC_KV_AUTO && p.v_descale) ? __ldg(p.v_descale) : 1.0f;
+  // thread -> (row, pair of columns): 16 rows x D / 2 pairs over 128 threads
+  for (int idx = tid; idx < rows * (D / 2); idx += kAttnThreads) {
+    const int row = idx / (D / 2), d = (idx - row * (D / 2)) * 2;
+    float m = -INFINITY;
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int row = g + 8 * r;
-    if (row >= rows) continue;
-    float l = s_sum[row] + s_sum[kRows + row] + s_sum[2 * kRows + row] + s_sum[3 * kRows + row];
-    float m = m_run[r];
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, s_m[w * kRows + row]);
+    float l = 0.f, ox = 0.f, oy = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = s_m[w * kRows + row];
+      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+      l += f * s_l[w * kRows + row];
+      const float2 o = *reinterpret_cast<const float2*>(s_o + (w * kRows + row) * D + d);
+      ox += f * o.x;
+      oy += f * o.y;
+    }
     const int head = head0 + row;
     if (p.num_splits > 1) {
       const int64_t slot = (static_cast<int64_t>(seq) * p.num_heads + head) * p.num_splits + split;
-      if (warp == 0 && t == 0) p.part_lse[slot] = m + log2f(l);
-      float* po = p.part_out + slot * D + warp * SL + 2 * t;
+      if (d == 0) p.part_lse[slot] = m + log2f(l);
       const float inv = 1.0f / l;
-#pragma unroll
-      for (int i = 0; i < SL / 8; ++i)
-        *reinterpret_cast<float2*>(po + i * 8) = make_float2(o_acc[i][2 * r] * inv, o_acc[i][2 * r + 1] * inv);
+      *reinterpret_cast<float2*>(p.part_out + slot * D + d) = make_float2(ox * inv, oy * inv);
     } else {
       float rescale = 1.0f;
       if (p.sink) {  // one more logit in the denominator
@@ -459,12 +490,8 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
         l = l * rescale + exp2f(sk - mf);
       }
       const float f = rescale / l * v_descale;
-      TQ* o = static_cast<TQ*>(p.out) + seq * p.out_stride_t + head * p.out_stride_h + warp * SL + 2 * t;
-#pragma unroll
-      for (int i = 0; i < SL / 8; ++i) {
-        const uint32_t w = pack2<TQ>(o_acc[i][2 * r] * f, o_acc[i][2 * r + 1] * f);
-        *reinterpret_cast<uint32_t*>(o + i * 8) = w;
-      }
+      TQ* o = static_cast<TQ*>(p.out) + seq * p.out_stride_t + head * p.out_stride_h + d;
+      *reinterpret_cast<uint32_t*>(o) = pack2<TQ>(ox * f, oy * f);
     }
   }
 }
