@@ -135,12 +135,15 @@ struct DecodeParams {
 template <typename TQ, int KV, int D>
 struct DecodeCfg {
   using T16 = std::conditional_t<KV == KVC_KV_AUTO, TQ, __half>;  // operand type of the matrix products
-  static constexpr int kRowBytes = D * 2 + 16;                     // shared-memory row of K, V and Q (16 B pad:
-                                                                    // eight consecutive rows hit distinct banks)
-  static constexpr int kTileBytes = kTileTokens * kRowBytes;       // one K or V tile
-  static constexpr int kStages = 2;
-  static constexpr int kSmemQ = kRows * kRowBytes;
-  static constexpr int kSmemOff = 2 * kTileTokens * (int)sizeof(int64_t);  // row offsets of two tiles
+  static constexpr int kCacheES = (KV == KVC_KV_AUTO) ? 2 : 1;    // bytes per cached element
+  static constexpr int kQRowBytes = D * 2 + 16;                   // shared-memory row of Q
+  static constexpr int kRowBytes = D * kCacheES + 16;             // shared-memory row of K and V (16 B pad:
+                                                                  // eight consecutive rows hit distinct banks)
+  static constexpr int kTileBytes = kTileTokens * kRowBytes;      // one K or V tile
+  // fp8 tiles are half the size: twice the stages, i.e. the same bytes in flight per CTA
+  static constexpr int kStages = (KV == KVC_KV_AUTO) ? 2 : (D <= 192 ? 4 : 3);
+  static constexpr int kSmemQ = kRows * kQRowBytes;
+  static constexpr int kSmemOff = kStages * kTileTokens * (int)sizeof(int64_t);  // row offsets, one slot per stage
   static constexpr int kSmemBytes = kStages * 2 * kTileBytes + kSmemQ + kSmemOff;
   // the final merge reuses the ring: 4 warps x (16 x D fp32 + 32 floats of statistics)
   static_assert(4 * (kRows * D + 2 * kRows) * (int)sizeof(float) <= kStages * 2 * kTileBytes, "merge buffer fits");
@@ -148,17 +151,28 @@ struct DecodeCfg {
   static_assert(D % 64 == 0 && D <= 256, "head sizes 64, 128, 192, 256");
 };
 
+// Within every group of 16 head dimensions the fp8 path works on a permuted order: an ldmatrix of fp8 rows
+// hands lane t the four CONSECUTIVE elements 4t .. 4t+3, which become the operand pairs (k = 2t, 2t+1) and
+// (k = 2t+8, 2t+9) of one mma step.  A dot product does not care about the order as long as Q uses the same
+// one, so the query's 32-bit words are stored in that order: word W (elements 2W, 2W+1) of a group goes to
+// position (W & 1) * 4 + (W >> 1).
+__device__ __forceinline__ int fp8_q_word_position(int w) { return (w & 1) * 4 + (w >> 1); }
+
 template <typename TQ, int KV, int D>
 __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const DecodeParams p) {
   using Cfg = DecodeCfg<TQ, KV, D>;
   using T16 = typename Cfg::T16;
+  constexpr bool kFp8 = KV != KVC_KV_AUTO;
+  constexpr int ES = Cfg::kCacheES;
+  constexpr int QRB = Cfg::kQRowBytes;
   constexpr int RB = Cfg::kRowBytes;
+  constexpr int NST = Cfg::kStages;
   constexpr int NT = D / 8;  // 8-column tiles of the output accumulator
 
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* s_kv = smem;                                       // 2 stages x (K tile, V tile)
-  unsigned char* s_q = s_kv + Cfg::kStages * 2 * Cfg::kTileBytes;   // [16][RB]
-  int64_t* s_off = reinterpret_cast<int64_t*>(s_q + Cfg::kSmemQ);   // [2][64] element offsets, -1 = no such token
+  unsigned char* s_kv = smem;                                       // NST stages x (K tile, V tile)
+  unsigned char* s_q = s_kv + NST * 2 * Cfg::kTileBytes;            // [16][QRB]
+  int64_t* s_off = reinterpret_cast<int64_t*>(s_q + Cfg::kSmemQ);   // [NST][64] element offsets, -1 = no such token
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;  // accumulator row (and row + 8) and column pair of this lane
@@ -204,17 +218,24 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
           }
         }
       }
-      *reinterpret_cast<uint4*>(s_q + r * RB + col * 16) = v;
+      if constexpr (kFp8) {
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+        uint32_t* group = reinterpret_cast<uint32_t*>(s_q + r * QRB + (col >> 1) * 32);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) group[fp8_q_word_position((col & 1) * 4 + i)] = w[i];
+      } else {
+        *reinterpret_cast<uint4*>(s_q + r * QRB + col * 16) = v;
+      }
     }
   }
 
   // ---- producer ----------------------------------------------------------------------------------
-  // Row offsets (block-table lookup, one per token) are computed by the first 64 threads one tile ahead and
-  // handed over through shared memory; the copies themselves are fully coalesced: consecutive threads take
-  // consecutive 16-byte chunks of a row.
+  // Row offsets (block-table lookup, one per token) are computed by the first 64 threads one tile ahead of
+  // the copy that needs them and handed over through shared memory; the copies themselves are fully
+  // coalesced: consecutive threads take consecutive 16-byte chunks of a row.
   const int32_t* table = p.block_table + seq * p.block_table_stride;
   const int64_t head_off = static_cast<int64_t>(kvh) * p.head_stride;
-  auto publish_offsets = [&](int tile) {  // by threads 0..63, into slot (tile - tile_begin) % 2
+  auto publish_offsets = [&](int tile) {  // by threads 0..63, into slot (tile - tile_begin) % NST
     if (tid < kTileTokens) {
       const int token = tile * kTileTokens + tid;
       int64_t off = -1;
@@ -223,145 +244,106 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
         off = static_cast<int64_t>(__ldg(table + blk_idx)) * p.block_stride +
               static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride + head_off;
       }
-      s_off[((tile - tile_begin) & 1) * kTileTokens + tid] = off;
+      s_off[((tile - tile_begin) % NST) * kTileTokens + tid] = off;
     }
   };
-
-  [[maybe_unused]] auto load_tile_async = [&](int tile, int stage) {  // 16-bit cache: cp.async
-    constexpr int kChunks = D / 8;                               // 16-byte chunks per row
-    constexpr int kRowsPerPass = kAttnThreads / kChunks;         // rows covered by one instruction of the CTA
-    static_assert(kAttnThreads % kChunks == 0 || kChunks == 24, "chunk mapping");
-    const int64_t* offs = s_off + ((tile - tile_begin) & 1) * kTileTokens;
-    unsigned char* ks = s_kv + stage * 2 * Cfg::kTileBytes;
+  auto load_tile = [&](int tile) {  // both tiles of `tile` into its stage; rows beyond the sequence become zeros
+    constexpr int kChunks = D * ES / 16;  // 16-byte chunks per row
+    const int slot = (tile - tile_begin) % NST;
+    const int64_t* offs = s_off + slot * kTileTokens;
+    unsigned char* ks = s_kv + slot * 2 * Cfg::kTileBytes;
+    const unsigned char* kc = static_cast<const unsigned char*>(p.key_cache);
+    const unsigned char* vc = static_cast<const unsigned char*>(p.value_cache);
+    auto copy_chunk = [&](int r, int col) {
+      const int64_t off = offs[r];
+      const int64_t src = (off < 0 ? 0 : off) * ES + col * 16;
+      const uint32_t dst = smem_u32(ks + r * RB + col * 16);
+      cp_async_16(dst, kc + src, off < 0 ? 0 : 16);
+      cp_async_16(dst + Cfg::kTileBytes, vc + src, off < 0 ? 0 : 16);
+    };
     if constexpr (kAttnThreads % kChunks == 0) {
+      constexpr int kRowsPerPass = kAttnThreads / kChunks;
       const int r0 = tid / kChunks, col = tid - r0 * kChunks;
 #pragma unroll
-      for (int i = 0; i < kTileTokens / kRowsPerPass; ++i) {
-        const int r = r0 + i * kRowsPerPass;
-        const int64_t off = offs[r];
-        const int64_t src = (off < 0 ? 0 : off) + col * 8;
-        const uint32_t dst = smem_u32(ks + r * RB + col * 16);
-        cp_async_16(dst, static_cast<const T16*>(p.key_cache) + src, off < 0 ? 0 : 16);
-        cp_async_16(dst + Cfg::kTileBytes, static_cast<const T16*>(p.value_cache) + src, off < 0 ? 0 : 16);
-      }
-    } else {  // D = 192: 24 chunks per row
-      for (int c = tid; c < kTileTokens * kChunks; c += kAttnThreads) {
-        const int r = c / kChunks, col = c - r * kChunks;
-        const int64_t off = offs[r];
-        const int64_t src = (off < 0 ? 0 : off) + col * 8;
-        const uint32_t dst = smem_u32(ks + r * RB + col * 16);
-        cp_async_16(dst, static_cast<const T16*>(p.key_cache) + src, off < 0 ? 0 : 16);
-        cp_async_16(dst + Cfg::kTileBytes, static_cast<const T16*>(p.value_cache) + src, off < 0 ? 0 : 16);
-      }
-    }
-  };
-
-  // fp8 cache: 16 bytes (16 elements) per chunk through registers, widened to fp16 when stored.
-  constexpr int kF8Chunks = D / 16;                                            // chunks per row
-  constexpr int kF8PerThread = (KV != KVC_KV_AUTO) ? kTileTokens * kF8Chunks / kAttnThreads : 1;
-  [[maybe_unused]] uint4 stage_k[kF8PerThread], stage_v[kF8PerThread];
-  [[maybe_unused]] auto load_tile_regs = [&](int tile) {
-    const int64_t* offs = s_off + ((tile - tile_begin) & 1) * kTileTokens;
-#pragma unroll
-    for (int i = 0; i < kF8PerThread; ++i) {
-      const int c = i * kAttnThreads + tid;
-      const int r = c / kF8Chunks, col = c - r * kF8Chunks;
-      const int64_t off = offs[r];
-      stage_k[i] = make_uint4(0, 0, 0, 0);
-      stage_v[i] = make_uint4(0, 0, 0, 0);
-      if (off >= 0) {
-        stage_k[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(p.key_cache) + off + col * 16));
-        stage_v[i] = __ldg(reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(p.value_cache) + off + col * 16));
-      }
-    }
-  };
-  [[maybe_unused]] auto widen = [](const uint4& v, uint4& a, uint4& b) {
-    a.x = fp8x2_to_f16x2<KV>(v.x); a.y = fp8x2_to_f16x2<KV>(v.x >> 16);
-    a.z = fp8x2_to_f16x2<KV>(v.y); a.w = fp8x2_to_f16x2<KV>(v.y >> 16);
-    b.x = fp8x2_to_f16x2<KV>(v.z); b.y = fp8x2_to_f16x2<KV>(v.z >> 16);
-    b.z = fp8x2_to_f16x2<KV>(v.w); b.w = fp8x2_to_f16x2<KV>(v.w >> 16);
-  };
-  [[maybe_unused]] auto store_tile_regs = [&](int stage) {
-    unsigned char* ks = s_kv + stage * 2 * Cfg::kTileBytes;
-#pragma unroll
-    for (int i = 0; i < kF8PerThread; ++i) {
-      const int c = i * kAttnThreads + tid;
-      const int r = c / kF8Chunks, col = c - r * kF8Chunks;
-      unsigned char* dst = ks + r * RB + col * 32;
-      uint4 a, b;
-      widen(stage_k[i], a, b);
-      *reinterpret_cast<uint4*>(dst) = a;
-      *reinterpret_cast<uint4*>(dst + 16) = b;
-      widen(stage_v[i], a, b);
-      *reinterpret_cast<uint4*>(dst + Cfg::kTileBytes) = a;
-      *reinterpret_cast<uint4*>(dst + Cfg::kTileBytes + 16) = b;
+      for (int i = 0; i < kTileTokens / kRowsPerPass; ++i) copy_chunk(r0 + i * kRowsPerPass, col);
+    } else {  // D = 192: 24 or 12 chunks per row
+      for (int c = tid; c < kTileTokens * kChunks; c += kAttnThreads) copy_chunk(c / kChunks, c % kChunks);
     }
   };
 
   // ---- running state of this warp ----------------------------------------------------------------
-  const float scale2 = p.softmax_scale * kLog2e * ((KV != KVC_KV_AUTO && p.k_descale) ? __ldg(p.k_descale) : 1.0f);
+  const float scale2 = p.softmax_scale * kLog2e * ((kFp8 && p.k_descale) ? __ldg(p.k_descale) : 1.0f);
   float m_run[2] = {-INFINITY, -INFINITY};  // running maximum (log2 domain) of rows g and g + 8
   float l_run[2] = {0.f, 0.f};              // this lane's share of the running sums of rows g and g + 8
-  float o_acc[NT][4];                       // rows g (c0, c1) / g + 8 (c2, c3), columns nt * 8 + 2t, + 1
+  // rows g (c0, c1) / g + 8 (c2, c3); columns of tile i: 16-bit cache  8i + 2t, + 1
+  //                                                      fp8 cache     16 (i / 2) + 4t + (i % 2), + 2
+  float o_acc[NT][4];
 #pragma unroll
   for (int i = 0; i < NT; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
 
   const uint32_t q_base = smem_u32(s_q);
-  // ldmatrix lane addressing (fragment layouts of mma.m16n8k16):
-  //   A operand (Q):  row = lane % 16, k offset = (lane / 16) * 8
-  //   B operand from K rows (tokens x d, no transpose): token = lane % 8 + (lane / 16) * 8, d offset = ((lane / 8) % 2) * 8
-  //   B operand from V rows (tokens x d, transposed):   token = lane % 8 + ((lane / 8) % 2) * 8, d offset = (lane / 16) * 8
-  const uint32_t a_lane_off_q = (lane & 15) * RB + (lane >> 4) * 16;
+  // ldmatrix lane addressing (fragment layouts of mma.m16n8k16; a "column step" is 16 bytes of a row):
+  //   A operand (Q):  row = lane % 16, column step = lane / 16
+  //   B operand from K rows (no transpose): token = lane % 8 + (lane / 16) * 8, column step = (lane / 8) % 2
+  //   B operand from V rows (transposed):   token = lane % 8 + ((lane / 8) % 2) * 8, column step = lane / 16
+  const uint32_t a_lane_off_q = (lane & 15) * QRB + (lane >> 4) * 16;
   const uint32_t k_lane_off = (warp * 16 + (lane & 7) + (lane >> 4) * 8) * RB + ((lane >> 3) & 1) * 16;
   const uint32_t v_lane_off = (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * RB + (lane >> 4) * 16;
 
   // ---- prologue of the pipeline -------------------------------------------------------------------
-  publish_offsets(tile_begin);
-  publish_offsets(tile_begin + 1);
+#pragma unroll
+  for (int i = 0; i < NST; ++i) publish_offsets(tile_begin + i);
   __syncthreads();  // offsets and query rows are visible
-  if constexpr (KV == KVC_KV_AUTO) {
-    load_tile_async(tile_begin, 0);
+#pragma unroll
+  for (int i = 0; i < NST - 1; ++i) {
+    if (tile_begin + i < tile_end) load_tile(tile_begin + i);
     cp_async_commit();
-  } else {
-    load_tile_regs(tile_begin);
   }
   [[maybe_unused]] uint32_t qf[Cfg::kQInRegs ? D / 16 : 1][4];
   if constexpr (Cfg::kQInRegs) {
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) ldmatrix_x4(qf[kk], q_base + a_lane_off_q + kk * 32);
   }
+  auto q_frag = [&](int kk, uint32_t (&a)[4]) {
+    if constexpr (Cfg::kQInRegs) {
+      a[0] = qf[kk][0]; a[1] = qf[kk][1]; a[2] = qf[kk][2]; a[3] = qf[kk][3];
+    } else {
+      ldmatrix_x4(a, q_base + a_lane_off_q + kk * 32);
+    }
+  };
 
   for (int tile = tile_begin; tile < tile_end; ++tile) {
-    const int stage = (tile - tile_begin) & 1;
-    if constexpr (KV == KVC_KV_AUTO) {
-      cp_async_wait<0>();  // this tile has landed
-      __syncthreads();     // ... for every thread; the other stage and the older offset slot are free
-      if (tile + 1 < tile_end) load_tile_async(tile + 1, stage ^ 1);
-      cp_async_commit();
-      publish_offsets(tile + 2);  // into the slot this tile's copies were issued from
-    } else {
-      store_tile_regs(stage);  // the stage computed two tiles ago; everyone is past it (barrier of the last tile)
-      __syncthreads();         // this tile is in shared memory; offsets of tile + 1 are visible
-      if (tile + 1 < tile_end) load_tile_regs(tile + 1);
-      publish_offsets(tile + 2);
-    }
-    const uint32_t ks = smem_u32(s_kv + stage * 2 * Cfg::kTileBytes);
+    const int slot = (tile - tile_begin) % NST;
+    cp_async_wait<NST - 2>();  // this tile has landed
+    __syncthreads();           // ... for every thread; the stage and offset slot of the previous tile are free
+    if (tile + NST - 1 < tile_end) load_tile(tile + NST - 1);
+    cp_async_commit();
+    publish_offsets(tile + NST);  // into the slot this tile's copies were issued from
+    const uint32_t ks = smem_u32(s_kv + slot * 2 * Cfg::kTileBytes);
     const uint32_t vs = ks + Cfg::kTileBytes;
 
     // ---- S = Q K^T for this warp's 16 tokens ---------------------------------------------------
     float s_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    if constexpr (!kFp8) {
 #pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk) {
-      uint32_t b[4];
-      ldmatrix_x4(b, ks + k_lane_off + kk * 32);
-      if constexpr (Cfg::kQInRegs) {
-        mma_16816<T16>(s_acc[0], qf[kk], b[0], b[1]);
-        mma_16816<T16>(s_acc[1], qf[kk], b[2], b[3]);
-      } else {
-        uint32_t a[4];
-        ldmatrix_x4(a, q_base + a_lane_off_q + kk * 32);
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a[4], b[4];
+        q_frag(kk, a);
+        ldmatrix_x4(b, ks + k_lane_off + kk * 32);
         mma_16816<T16>(s_acc[0], a, b[0], b[1]);
         mma_16816<T16>(s_acc[1], a, b[2], b[3]);
+      }
+    } else {
+#pragma unroll
+      for (int jj = 0; jj < D / 32; ++jj) {  // 32 head dimensions = two mma steps per ldmatrix
+        uint32_t a[4], b[4];
+        ldmatrix_x4(b, ks + k_lane_off + jj * 32);  // tokens 0-7: d-groups (2jj, 2jj+1); tokens 8-15: the same
+        q_frag(2 * jj, a);
+        mma_16816<T16>(s_acc[0], a, fp8x2_to_f16x2<KV>(b[0]), fp8x2_to_f16x2<KV>(b[0] >> 16));
+        mma_16816<T16>(s_acc[1], a, fp8x2_to_f16x2<KV>(b[2]), fp8x2_to_f16x2<KV>(b[2] >> 16));
+        q_frag(2 * jj + 1, a);
+        mma_16816<T16>(s_acc[0], a, fp8x2_to_f16x2<KV>(b[1]), fp8x2_to_f16x2<KV>(b[1] >> 16));
+        mma_16816<T16>(s_acc[1], a, fp8x2_to_f16x2<KV>(b[3]), fp8x2_to_f16x2<KV>(b[3] >> 16));
       }
     }
 
@@ -424,15 +406,33 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
         o_acc[i][3] *= alpha[1];
       }
     }
+    if constexpr (!kFp8) {
 #pragma unroll
-    for (int np = 0; np < D / 16; ++np) {  // two 8-column tiles per ldmatrix
-      uint32_t b[4];
-      ldmatrix_x4_trans(b, vs + v_lane_off + np * 32);
-      mma_16816<T16>(o_acc[2 * np], pa, b[0], b[1]);
-      mma_16816<T16>(o_acc[2 * np + 1], pa, b[2], b[3]);
+      for (int np = 0; np < D / 16; ++np) {  // two 8-column tiles per ldmatrix
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vs + v_lane_off + np * 32);
+        mma_16816<T16>(o_acc[2 * np], pa, b[0], b[1]);
+        mma_16816<T16>(o_acc[2 * np + 1], pa, b[2], b[3]);
+      }
+    } else {
+#pragma unroll
+      for (int jj = 0; jj < D / 32; ++jj) {  // 32 head dimensions = four 8-column tiles per ldmatrix
+        uint32_t b[4];
+        // transposed 16-bit units: b[i] = (V[2t][2g], V[2t][2g+1], V[2t+1][2g], V[2t+1][2g+1]) as bytes, for
+        // tokens 0-7 / 8-15 (i = 0 / 1) of dimensions 32jj .. +15, and the same (i = 2 / 3) of 32jj+16 .. +31
+        ldmatrix_x4_trans(b, vs + v_lane_off + jj * 32);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) b[i] = __byte_perm(b[i], 0, 0x3120);  // (even d: tokens 2t, 2t+1 | odd d: same)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          mma_16816<T16>(o_acc[4 * jj + 2 * h], pa, fp8x2_to_f16x2<KV>(b[2 * h]), fp8x2_to_f16x2<KV>(b[2 * h + 1]));
+          mma_16816<T16>(o_acc[4 * jj + 2 * h + 1], pa, fp8x2_to_f16x2<KV>(b[2 * h] >> 16),
+                         fp8x2_to_f16x2<KV>(b[2 * h + 1] >> 16));
+        }
+      }
     }
   }
-  if constexpr (KV == KVC_KV_AUTO) cp_async_wait<0>();
+  cp_async_wait<0>();
 
   // ---- merge the four warps' partial results through shared memory ---------------------------------
 #pragma unroll
@@ -452,13 +452,22 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
   }
 #pragma unroll
   for (int i = 0; i < NT; ++i) {
-    float* dst = s_o + (warp * kRows + g) * D + i * 8 + 2 * t;
-    *reinterpret_cast<float2*>(dst) = make_float2(o_acc[i][0], o_acc[i][1]);
-    *reinterpret_cast<float2*>(dst + 8 * D) = make_float2(o_acc[i][2], o_acc[i][3]);
+    float* dst = s_o + (warp * kRows + g) * D;
+    if constexpr (!kFp8) {
+      dst += i * 8 + 2 * t;
+      *reinterpret_cast<float2*>(dst) = make_float2(o_acc[i][0], o_acc[i][1]);
+      *reinterpret_cast<float2*>(dst + 8 * D) = make_float2(o_acc[i][2], o_acc[i][3]);
+    } else {
+      dst += 16 * (i >> 1) + 4 * t + (i & 1);
+      dst[0] = o_acc[i][0];
+      dst[2] = o_acc[i][1];
+      dst[8 * D] = o_acc[i][2];
+      dst[8 * D + 2] = o_acc[i][3];
+    }
   }
   __syncthreads();
 
-  const float v_descale = (KV != KVC_KV_AUTO && p.v_descale) ? __ldg(p.v_descale) : 1.0f;
+  const float v_descale = (kFp8 && p.v_descale) ? __ldg(p.v_descale) : 1.0f;
   // thread -> (row, pair of columns): 16 rows x D / 2 pairs over 128 threads
   for (int idx = tid; idx < rows * (D / 2); idx += kAttnThreads) {
     const int row = idx / (D / 2), d = (idx - row * (D / 2)) * 2;
