@@ -318,8 +318,9 @@ KVC_API int kvc_rotary_embedding_and_cache_flash(
  *   k_descale,     NULL (= 1), or device fp32 scalars: a stored key element k means k * k_descale, the
  *   v_descale      inverse of the k_scale / v_scale division of the cache write; ignored for KVC_KV_AUTO
  *   max_seq_len    host-side upper bound of seq_lens (the reference's max_seqlen_k); sizes the split
- *   workspace      device scratch of kvc_paged_decode_workspace_bytes(...) bytes, 16-byte aligned; may be
- *                  NULL when that function returns 0
+ *   workspace      device scratch of kvc_paged_decode_workspace_bytes(same sizes and types) bytes, 16-byte
+ *                  aligned; may be NULL when that function returns 0 (it needs a current CUDA device)
+ *   softmax_scale  positive; the descales are positive too
  *
  *   out[s][h] = sum_j softmax_j(softmax_scale * q[s][h] . K[s][j][h / g]) * V[s][j][h / g],  g = num_heads /
  *   num_kv_heads.  Products run on fp16/bf16 tensor-core tiles with fp32 accumulation; probabilities are
@@ -328,7 +329,7 @@ KVC_API int kvc_rotary_embedding_and_cache_flash(
  *   statement within its own tolerance, atol = rtol = 1e-2.  head_size 64, 128, 192 or 256.
  */
 KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads,
-                                                 int64_t head_size, int64_t max_seq_len);
+                                                 int64_t head_size, int64_t max_seq_len, int q_dtype, int kv_dtype);
 KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void* key_cache, const void* value_cache,
                                        const int32_t* block_table, const int32_t* seq_lens, const void* sink,
                                        const float* k_descale, const float* v_descale, void* workspace,

@@ -70,6 +70,13 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
   }
 }
 
+// 2^x, one MUFU instruction (2 ulp; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <typename T16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if constexpr (std::is_same_v<T16, __half>) {
@@ -140,8 +147,9 @@ struct DecodeCfg {
   static constexpr int kRowBytes = D * kCacheES + 16;             // shared-memory row of K and V (16 B pad:
                                                                   // eight consecutive rows hit distinct banks)
   static constexpr int kTileBytes = kTileTokens * kRowBytes;      // one K or V tile
-  // fp8 tiles are half the size: twice the stages, i.e. the same bytes in flight per CTA
-  static constexpr int kStages = (KV == KVC_KV_AUTO) ? 2 : (D <= 192 ? 4 : 3);
+  // Two stages: one tile is consumed while the next one lands.  More stages were slower: what the kernel
+  // needs most is resident warps (D = 128: 76 KB, three CTAs per SM for a 16-bit cache; 43 KB, four for fp8).
+  static constexpr int kStages = 2;
   static constexpr int kSmemQ = kRows * kQRowBytes;
   static constexpr int kSmemOff = kStages * kTileTokens * (int)sizeof(int64_t);  // row offsets, one slot per stage
   static constexpr int kSmemBytes = kStages * 2 * kTileBytes + kSmemQ + kSmemOff;
@@ -273,7 +281,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
 
   // ---- running state of this warp ----------------------------------------------------------------
   const float scale2 = p.softmax_scale * kLog2e * ((kFp8 && p.k_descale) ? __ldg(p.k_descale) : 1.0f);
-  float m_run[2] = {-INFINITY, -INFINITY};  // running maximum (log2 domain) of rows g and g + 8
+  float m_run[2] = {-INFINITY, -INFINITY};  // running maximum of the raw logits of rows g and g + 8
   float l_run[2] = {0.f, 0.f};              // this lane's share of the running sums of rows g and g + 8
   // rows g (c0, c1) / g + 8 (c2, c3); columns of tile i: 16-bit cache  8i + 2t, + 1
   //                                                      fp8 cache     16 (i / 2) + 4t + (i % 2), + 2
@@ -347,53 +355,40 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
       }
     }
 
-    // ---- scale, mask the tail, running maximum of this warp's rows ------------------------------
-    const int tok_base = tile * kTileTokens + warp * 16 + 2 * t;
-    float mx[2] = {-INFINITY, -INFINITY};
+    // ---- mask the tail, running maximum (of the raw logits: the scale is positive), P = 2^(scale (S - m)) --
+    if ((tile + 1) * kTileTokens > n) {  // only the last tile of a sequence has tokens to mask
+      const int tok_base = tile * kTileTokens + warp * 16 + 2 * t;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
+      for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int token = tok_base + nt * 8 + (e & 1);
-        const float v = token < n ? s_acc[nt][e] * scale2 : -INFINITY;
-        s_acc[nt][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        for (int e = 0; e < 4; ++e)
+          if (tok_base + nt * 8 + (e & 1) >= n) s_acc[nt][e] = -INFINITY;
       }
     }
-    float alpha[2];
+    float alpha[2], neg_ms[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xFFFFFFFFu, mx[r], 1));
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xFFFFFFFFu, mx[r], 2));
-      const float m_new = fmaxf(m_run[r], mx[r]);
-      alpha[r] = (m_new == -INFINITY) ? 1.0f : exp2f(m_run[r] - m_new);
+      float mx = fmaxf(fmaxf(s_acc[0][2 * r], s_acc[0][2 * r + 1]), fmaxf(s_acc[1][2 * r], s_acc[1][2 * r + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+      const float m_new = fmaxf(m_run[r], mx);
+      alpha[r] = (m_new == -INFINITY) ? 1.0f : fast_exp2((m_run[r] - m_new) * scale2);
+      neg_ms[r] = (m_new == -INFINITY) ? 0.f : -m_new * scale2;  // all masked so far: 2^(-inf) = 0 below
       m_run[r] = m_new;
       l_run[r] *= alpha[r];
     }
-
-    // ---- P = exp2(S - m), rounded to T16: the A operand of the second product ---------------------
+    // rounded to T16, the probabilities are the A operand of the second product; the running sums take them
+    // unrounded, as the reference statement normalises before it rounds
     uint32_t pa[4];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt) {
       float pv[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int r = e >> 1;
-        pv[e] = (m_run[r] == -INFINITY) ? 0.f : exp2f(s_acc[nt][e] - m_run[r]);
-      }
-      const uint32_t lo = pack2<T16>(pv[0], pv[1]), hi = pack2<T16>(pv[2], pv[3]);
-      pa[2 * nt] = lo;       // row g,     tokens nt * 8 + 2t, + 1
-      pa[2 * nt + 1] = hi;   // row g + 8
-      // the sums use the rounded probabilities, the values the product will see
-      if constexpr (std::is_same_v<T16, __half>) {
-        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&lo));
-        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&hi));
-        l_run[0] += f0.x + f0.y;
-        l_run[1] += f1.x + f1.y;
-      } else {
-        l_run[0] += __uint_as_float(lo << 16) + __uint_as_float(lo & 0xFFFF0000u);
-        l_run[1] += __uint_as_float(hi << 16) + __uint_as_float(hi & 0xFFFF0000u);
-      }
+      for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(fmaf(s_acc[nt][e], scale2, neg_ms[e >> 1]));
+      l_run[0] += pv[0] + pv[1];
+      l_run[1] += pv[2] + pv[3];
+      pa[2 * nt] = pack2<T16>(pv[0], pv[1]);      // row g,     tokens nt * 8 + 2t, + 1
+      pa[2 * nt + 1] = pack2<T16>(pv[2], pv[3]);  // row g + 8
     }
 
     // ---- O = alpha * O + P V over this warp's 16 tokens -------------------------------------------
@@ -444,9 +439,9 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
   float* s_o = reinterpret_cast<float*>(smem);           // [4 warps][16 rows][D]
   float* s_m = s_o + 4 * kRows * D;                      // [4][16]
   float* s_l = s_m + 4 * kRows;                          // [4][16]
-  if (t == 0) {
-    s_m[warp * kRows + g] = m_run[0];
-    s_m[warp * kRows + g + 8] = m_run[1];
+  if (t == 0) {  // maxima leave in the log2 domain (-inf stays -inf)
+    s_m[warp * kRows + g] = m_run[0] * scale2;
+    s_m[warp * kRows + g + 8] = m_run[1] * scale2;
     s_l[warp * kRows + g] = l_run[0];
     s_l[warp * kRows + g + 8] = l_run[1];
   }
@@ -478,7 +473,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float mw = s_m[w * kRows + row];
-      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - m);
+      const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - m);
       l += f * s_l[w * kRows + row];
       const float2 o = *reinterpret_cast<const float2*>(s_o + (w * kRows + row) * D + d);
       ox += f * o.x;
@@ -547,15 +542,71 @@ namespace {
 
 constexpr int kMaxSplits = 128;
 
-int pick_splits(int64_t ctas_without_split, int64_t max_tiles) {
+// How many CTAs of a kernel instance one SM holds (asked of the runtime once per instance and device).
+template <typename TQ, int KV, int D>
+int decode_ctas_per_sm() {
+  using Cfg = DecodeCfg<TQ, KV, D>;
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+  if (cached[dev] == 0) {
+    int n = 0;
+    cudaFuncSetAttribute(paged_decode_kernel<TQ, KV, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, paged_decode_kernel<TQ, KV, D>, kAttnThreads,
+                                                      Cfg::kSmemBytes) != cudaSuccess || n < 1)
+      n = 1;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+template <typename TQ, int KV>
+int decode_ctas_per_sm_d(int head_size) {
+  switch (head_size) {
+    case 64: return decode_ctas_per_sm<TQ, KV, 64>();
+    case 128: return decode_ctas_per_sm<TQ, KV, 128>();
+    case 192: return decode_ctas_per_sm<TQ, KV, 192>();
+    default: return decode_ctas_per_sm<TQ, KV, 256>();
+  }
+}
+
+int decode_slots(int q_dtype, int kv, int head_size) {  // CTAs the whole device holds at once
+  int per_sm;
+  if (q_dtype == KVC_IN_F16) {
+    per_sm = kv == KVC_KV_AUTO ? decode_ctas_per_sm_d<__half, KVC_KV_AUTO>(head_size)
+             : kv == KVC_KV_FP8_E4M3 ? decode_ctas_per_sm_d<__half, KVC_KV_FP8_E4M3>(head_size)
+                                     : decode_ctas_per_sm_d<__half, KVC_KV_FP8_E5M2>(head_size);
+  } else {
+    per_sm = kv == KVC_KV_AUTO ? decode_ctas_per_sm_d<__nv_bfloat16, KVC_KV_AUTO>(head_size)
+             : kv == KVC_KV_FP8_E4M3 ? decode_ctas_per_sm_d<__nv_bfloat16, KVC_KV_FP8_E4M3>(head_size)
+                                     : decode_ctas_per_sm_d<__nv_bfloat16, KVC_KV_FP8_E5M2>(head_size);
+  }
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int64_t target = static_cast<int64_t>(sms) * 4;  // a few CTAs per SM
-  int64_t s = (target + ctas_without_split - 1) / ctas_without_split;
-  if (s > max_tiles) s = max_tiles;
-  if (s > kMaxSplits) s = kMaxSplits;
-  if (s < 1) s = 1;
-  return static_cast<int>(s);
+  return sms * per_sm;
+}
+
+// Number of splits for sequences of `max_tiles` tiles when `base` CTAs exist without splitting and the device
+// holds `slots` CTAs at once.  All CTAs of a launch are equally long (tiles_per_split tiles plus a fixed
+// start-up cost of about two tiles), so the launch takes ceil(ctas / slots) rounds of that length; splitting
+// adds the merge launch and its traffic, about three tiles' worth.  Pick the count that minimises the sum,
+// the smaller one on ties.
+int pick_splits(int64_t base, int64_t max_tiles, int64_t slots) {
+  int best = 1;
+  int64_t best_cost = -1;
+  const int64_t limit = max_tiles < kMaxSplits ? max_tiles : kMaxSplits;
+  for (int64_t s = 1; s <= limit; ++s) {
+    const int64_t tps = (max_tiles + s - 1) / s;
+    const int64_t eff = (max_tiles + tps - 1) / tps;  // splits that are not empty
+    if (eff != s) continue;
+    const int64_t rounds = (base * s + slots - 1) / slots;
+    const int64_t cost = rounds * (tps + 2) + (s > 1 ? 3 : 0);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = static_cast<int>(s);
+    }
+  }
+  return best;
 }
 
 template <typename TQ, int KV, int D>
@@ -611,14 +662,14 @@ struct DecodePlan {
 };
 
 DecodePlan plan_decode(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads, int64_t head_size,
-                       int64_t max_seq_len) {
+                       int64_t max_seq_len, int q_dtype, int kv_dtype) {
   DecodePlan pl{1, 1, 0};
   const int64_t group = num_kv_heads > 0 ? num_heads / num_kv_heads : 1;
   const int64_t row_tiles = (group + kRows - 1) / kRows;
   int64_t max_tiles = (max_seq_len + kTileTokens - 1) / kTileTokens;
   if (max_tiles < 1) max_tiles = 1;
   const int64_t base = num_seqs * num_kv_heads * row_tiles;
-  pl.splits = base > 0 ? pick_splits(base, max_tiles) : 1;
+  pl.splits = base > 0 ? pick_splits(base, max_tiles, decode_slots(q_dtype, kv_dtype, static_cast<int>(head_size))) : 1;
   pl.tiles_per_split = static_cast<int>((max_tiles + pl.splits - 1) / pl.splits);
   pl.splits = static_cast<int>((max_tiles + pl.tiles_per_split - 1) / pl.tiles_per_split);  // drop empty tails
   if (pl.splits > 1) pl.workspace_bytes = num_seqs * num_heads * pl.splits * (head_size + 1) * (int64_t)sizeof(float);
@@ -631,9 +682,12 @@ DecodePlan plan_decode(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads
 extern "C" {
 
 KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads,
-                                                 int64_t head_size, int64_t max_seq_len) {
-  if (num_seqs <= 0 || num_heads <= 0 || num_kv_heads <= 0 || head_size <= 0 || max_seq_len < 0) return 0;
-  return kvc::plan_decode(num_seqs, num_heads, num_kv_heads, head_size, max_seq_len).workspace_bytes;
+                                                 int64_t head_size, int64_t max_seq_len, int q_dtype, int kv_dtype) {
+  if (num_seqs <= 0 || num_heads <= 0 || num_kv_heads <= 0 || max_seq_len < 0) return 0;
+  if (head_size != 64 && head_size != 128 && head_size != 192 && head_size != 256) return 0;
+  if (q_dtype != KVC_IN_F16 && q_dtype != KVC_IN_BF16) return 0;
+  if (kv_dtype != KVC_KV_AUTO && kv_dtype != KVC_KV_FP8_E4M3 && kv_dtype != KVC_KV_FP8_E5M2) return 0;
+  return kvc::plan_decode(num_seqs, num_heads, num_kv_heads, head_size, max_seq_len, q_dtype, kv_dtype).workspace_bytes;
 }
 
 KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void* key_cache, const void* value_cache,
@@ -654,6 +708,8 @@ KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void*
     return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: sizes must be positive");
   if (num_heads % num_kv_heads)
     return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: num_heads must be a multiple of num_kv_heads");
+  if (!(softmax_scale > 0.0f))
+    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: softmax_scale must be positive");
   if (head_size != 64 && head_size != 128 && head_size != 192 && head_size != 256)
     return fail(KVC_ERR_UNSUPPORTED, "paged_decode_attention: head_size must be 64, 128, 192 or 256");
   if (num_seqs == 0) return KVC_OK;
@@ -669,7 +725,7 @@ KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void*
   if (!ok_align)
     return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: query and cache rows must be 16-byte aligned");
 
-  const DecodePlan pl = plan_decode(num_seqs, num_heads, num_kv_heads, head_size, max_seq_len);
+  const DecodePlan pl = plan_decode(num_seqs, num_heads, num_kv_heads, head_size, max_seq_len, q_dtype, kv_dtype);
   if (pl.splits > 1 && (!workspace || workspace_bytes < pl.workspace_bytes || !aligned(workspace, 16)))
     return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: workspace missing, misaligned (16 bytes) or too small; ask "
                                          "kvc_paged_decode_workspace_bytes ("

@@ -80,7 +80,7 @@ def lib() -> ctypes.CDLL:
         L.kvc_count_bad_slots.restype = ci
         L.kvc_count_bad_slots.argtypes = [vp, i64, i64, vp, vp]
         L.kvc_paged_decode_workspace_bytes.restype = i64
-        L.kvc_paged_decode_workspace_bytes.argtypes = [i64] * 5
+        L.kvc_paged_decode_workspace_bytes.argtypes = [i64] * 5 + [ci, ci]
         L.kvc_paged_decode_attention.restype = ci
         L.kvc_paged_decode_attention.argtypes = [vp] * 10 + [i64] * 15 + [ctypes.c_float, ci, ci, vp]
         L.kvc_rotary_embedding.restype = ci
@@ -325,7 +325,7 @@ def paged_decode_attention(query, key_cache, value_cache, block_table, seq_lens,
     hk = key_cache.shape[2]
     if out is None:
         out = torch.empty_like(query)
-    nbytes = lib().kvc_paged_decode_workspace_bytes(S, hq, hk, D, max_seq_len)
+    nbytes = lib().kvc_paged_decode_workspace_bytes(S, hq, hk, D, max_seq_len, _in_dtype(query), kv)
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=query.device)
     _check(lib().kvc_paged_decode_attention(
         out.data_ptr(), query.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(), block_table.data_ptr(),
