@@ -102,6 +102,22 @@ def test_torch_extension_registers_reference_schemas():
     rope = "(Tensor positions, Tensor! query, Tensor!? key, int head_size, Tensor cos_sin_cache, bool is_neox) -> ()"
     assert str(torch.ops._C.rotary_embedding.default._schema) == str(
         torch._C.parse_schema("_C::rotary_embedding" + rope))
+    # csrc/flash_attn/flash_api.cpp:179-193 of the reference
+    fa = ("(Tensor q, Tensor k, Tensor v, Tensor!? out, Tensor cu_seqlens_q, Tensor cu_seqlens_k, Tensor? seqused_k, "
+          "Tensor? leftpad_k, Tensor? block_table, Tensor? alibi_slopes, int max_seqlen_q, int max_seqlen_k, "
+          "float p_dropout, float softmax_scale, Tensor? softmax_sink, bool zero_tensors, bool is_causal, "
+          "int window_size_left, int window_size_right, float softcap, bool return_softmax, Generator? gen) -> Tensor[]")
+    assert str(torch.ops._vllm_fa2_C.varlen_fwd.default._schema) == str(
+        torch._C.parse_schema("_vllm_fa2_C::varlen_fwd" + fa))
+    from vllm_xpu_kernels import flash_attn_interface
+    import inspect
+    params = list(inspect.signature(flash_attn_interface.flash_attn_varlen_func).parameters)
+    # vllm_xpu_kernels/flash_attn_interface.py:24-53 of the reference, in order
+    assert params[:27] == ["q", "k", "v", "max_seqlen_q", "cu_seqlens_q", "max_seqlen_k", "cu_seqlens_k", "seqused_k",
+                           "q_v", "dropout_p", "softmax_scale", "causal", "window_size", "softcap", "alibi_slopes",
+                           "deterministic", "return_attn_probs", "block_table", "return_softmax_lse", "out",
+                           "scheduler_metadata", "q_descale", "k_descale", "v_descale", "num_splits", "fa_version",
+                           "s_aux"]
     from vllm_xpu_kernels import ops as wrappers
     for fn in ("reshape_and_cache", "reshape_and_cache_flash", "concat_and_cache_mla", "gather_cache",
                "rotary_embedding", "rotary_embedding_and_cache_flash"):
@@ -126,6 +142,26 @@ def test_rotary_entry_points_validate_without_touching_the_device():
     assert "kvc_reshape_and_cache_flash" in cabi.last_error()
     args[9] = 5  # more slot tokens than tokens
     assert L.kvc_rotary_embedding_and_cache_flash(*args) == 1
+
+
+def test_decode_attention_entry_point_validates_without_touching_the_device():
+    L = cabi.lib()
+    p = ctypes.c_void_p(0x1000)
+    f = ctypes.c_float
+    # workspace_bytes, num_seqs (0: every call returns before it would launch), num_heads, num_kv_heads, head_size,
+    # block_size, block_table_stride, max_seq_len, 4 query/out strides, 3 cache strides, scale, q_dtype, kv_dtype
+    base = [p] * 10 + [0, 0, 8, 2, 128, 16, 8, 100, 1024, 128, 1024, 128, 4096, 256, 128, f(0.1), 1, 0, None]
+    assert L.kvc_paged_decode_attention(*base) == 0  # no sequences
+    bad = list(base); bad[14] = 96      # head size 96
+    assert L.kvc_paged_decode_attention(*bad) == 2 and "head_size" in cabi.last_error()
+    bad = list(base); bad[12] = 7       # 7 query heads over 2 kv heads
+    assert L.kvc_paged_decode_attention(*bad) == 1
+    bad = list(base); bad[25] = f(0.0)  # scale must be positive
+    assert L.kvc_paged_decode_attention(*bad) == 1 and "softmax_scale" in cabi.last_error()
+    bad = list(base); bad[26] = 0       # fp32 query
+    assert L.kvc_paged_decode_attention(*bad) == 2
+    assert L.kvc_paged_decode_workspace_bytes(0, 8, 2, 128, 100, 1, 0) == 0
+    assert L.kvc_paged_decode_workspace_bytes(4, 8, 2, 96, 100, 1, 0) == 0
 
 
 def test_no_cpu_fallback():

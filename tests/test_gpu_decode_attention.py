@@ -10,6 +10,7 @@ import torch
 from oracle import torch_views
 from tests import helpers as H
 from vllm_xpu_kernels import cabi
+from vllm_xpu_kernels.flash_attn_interface import flash_attn_varlen_func
 
 pytestmark = pytest.mark.gpu
 
@@ -215,3 +216,82 @@ def test_decode_attention_rejects_bad_arguments(cuda_device):
         cabi.paged_decode_attention(q, kc, kc, bt, lens, 1.0, 1, "int8")
     out = cabi.paged_decode_attention(q[:0], kc, kc, bt[:0], lens[:0], 1.0, 0)  # no sequences: nothing to do
     assert out.shape[0] == 0
+
+
+# ------------------------------------------------------------------------------------ the reference-facing call
+@pytest.mark.parametrize("fname", H.golden_files("decode_attn"))
+def test_flash_attn_varlen_func_on_the_fixtures(fname, cuda_device):
+    """The call of the reference's test (tests/flash_attn/test_flash_attn_varlen_func.py:355-366 there), through
+    this package's flash_attn_varlen_func; fp8 fixtures add the descales."""
+    dev = cuda_device
+    c = H.DecodeAttnCase(fname)
+    S = c.query.shape[0]
+    cu_q = torch.arange(S + 1, dtype=torch.int32, device=dev)
+    kw = {}
+    if c.kv_cache_dtype != "auto":
+        kw = dict(k_descale=dscalar(c.descale, dev).expand(S, c.key_cache.shape[2]),
+                  v_descale=dscalar(c.descale, dev).expand(S, c.key_cache.shape[2]))
+    out = flash_attn_varlen_func(c.query.to(dev), c.key_cache.to(dev), c.value_cache.to(dev), 1, cu_q,
+                                 int(c.kv_lens.max()), seqused_k=c.kv_lens.to(dev), softmax_scale=c.scale,
+                                 causal=False, block_table=c.block_tables.to(dev), window_size=(-1, -1),
+                                 s_aux=None if c.sink is None else c.sink.to(dev), **kw)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.cpu().float(), c.expected.float(), **TOL)
+
+
+def test_attention_ops_pass_opcheck_and_refuse_what_is_not_built(cuda_device):
+    dev = cuda_device
+    query, kc, vc, bt, lens, sk = make_case(torch.float16, 8, 2, 64, [70, 200, 5], 16, 32, True, seed=21)
+    q, kc, vc, bt, lens, sk = (x.to(dev) for x in (query, kc, vc, bt, lens, sk))
+    cu_q = torch.arange(4, dtype=torch.int32, device=dev)
+    args = (q, kc, vc, None, cu_q, torch.empty_like(cu_q), lens, None, bt, None, 1, 200, 0.0, 0.125, sk, False, False,
+            -1, -1, 0.0, False, None)
+    # the reference's schema pairs a mutable optional `out` with a Tensor[] return, which torch's AOT
+    # functionalisation refuses for any custom op; the other three checks apply
+    H.opcheck(torch.ops._vllm_fa2_C.varlen_fwd, args,
+              test_utils=("test_schema", "test_autograd_registration", "test_faketensor"))
+    k8 = (kc.float() / 0.05).to(torch.float8_e4m3fn)
+    v8 = (vc.float() / 0.05).to(torch.float8_e4m3fn)
+    out = torch.empty_like(q)
+    H.opcheck(torch.ops._vllm_fa2_C.paged_decode_attention,
+              (q, k8, v8, out, lens, bt, 200, 0.125, sk, "fp8", dscalar(0.05, dev), dscalar(0.05, dev)))
+    torch.ops._vllm_fa2_C.paged_decode_attention(q, k8, v8, out, lens, bt, 200, 0.125, sk, "fp8", dscalar(0.05, dev),
+                                                 dscalar(0.05, dev))  # opcheck works on copies
+    want = torch_views.run_paged_decode_attention(query, k8.cpu(), v8.cpu(), bt.cpu(), lens.cpu(), 0.125, "fp8", 0.05,
+                                                  0.05, sk.cpu())
+    torch.testing.assert_close(out.cpu().float(), want, **TOL)
+    # uint8 view of the same cache, named explicitly
+    out2 = flash_attn_varlen_func(q, k8.view(torch.uint8), v8.view(torch.uint8), 1, cu_q, 200, seqused_k=lens,
+                                  softmax_scale=0.125, block_table=bt, s_aux=sk, k_descale=dscalar(0.05, dev),
+                                  v_descale=dscalar(0.05, dev), kv_cache_dtype="fp8_e4m3")
+    assert H.same_bytes(out2.cpu(), out.cpu())
+    # what the reference routes to its chunked-prefill kernel is refused, loudly
+    with pytest.raises(RuntimeError, match="only the paged decode case"):
+        flash_attn_varlen_func(q, kc, vc, 2, cu_q, 200, seqused_k=lens, softmax_scale=0.125, block_table=bt)
+    with pytest.raises(RuntimeError, match="only the paged decode case"):
+        flash_attn_varlen_func(q, kc, vc, 1, cu_q, 200, seqused_k=lens, softmax_scale=0.125, block_table=bt,
+                               window_size=[127, -1])
+    with pytest.raises(RuntimeError, match="page_table must have dtype torch.int32"):
+        flash_attn_varlen_func(q, kc, vc, 1, cu_q, 200, seqused_k=lens, softmax_scale=0.125, block_table=bt.long())
+    with pytest.raises(RuntimeError, match="only supports fp16 and bf16"):
+        flash_attn_varlen_func(q.float(), kc.float(), vc.float(), 1, cu_q, 200, seqused_k=lens, softmax_scale=0.125,
+                               block_table=bt)
+
+
+def test_decode_attention_in_a_cuda_graph(cuda_device):
+    dev = cuda_device
+    query, kc, vc, bt, lens, sk = make_case(torch.bfloat16, 8, 2, 128, [900, 40], 16, 64, False, seed=23)
+    q, kc, vc, bt, lens = (x.to(dev) for x in (query, kc, vc, bt, lens))
+    cu_q = torch.arange(3, dtype=torch.int32, device=dev)
+    call = lambda: flash_attn_varlen_func(q, kc, vc, 1, cu_q, 900, seqused_k=lens, softmax_scale=0.09, block_table=bt)
+    eager = call()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        captured = call()
+    captured.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert H.same_bytes(captured.cpu(), eager.cpu())
+    want = torch_views.run_paged_decode_attention(query, kc.cpu(), vc.cpu(), bt.cpu(), lens.cpu(), 0.09)
+    torch.testing.assert_close(captured.cpu().float(), want, **TOL)

@@ -27,7 +27,7 @@ TORCH_EXT = os.path.join(PKG, "_C.abi3.so")
 CUDA_SOURCES = [os.path.join(CSRC, "kvcache_kernels.cu"), os.path.join(CSRC, "fp8_quant_kernels.cu"),
                 os.path.join(CSRC, "rope_kernels.cu"), os.path.join(CSRC, "paged_attention_kernels.cu")]
 EXT_SOURCES = [os.path.join(CSRC, "cache.cpp"), os.path.join(CSRC, "fp8_quant.cpp"),
-               os.path.join(CSRC, "pos_encoding.cpp"),
+               os.path.join(CSRC, "pos_encoding.cpp"), os.path.join(CSRC, "flash_api.cpp"),
                os.path.join(CSRC, "torch_bindings.cpp")]
 HEADERS = [
     os.path.join(INCLUDE, "kvcache_b200.h"),
