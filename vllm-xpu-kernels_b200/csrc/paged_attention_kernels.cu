@@ -123,6 +123,7 @@ struct DecodeParams {
   int64_t block_table_stride;
   int32_t num_heads, num_kv_heads, group, row_tiles;  // group = Hq / Hkv; row_tiles = ceil(group / 16)
   int32_t block_size;
+  int32_t bs_shift;  // log2(block_size), or -1
   int32_t num_splits, tiles_per_split;
   float softmax_scale;
 };
@@ -248,26 +249,33 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
       const int token = tile * kTileTokens + tid;
       int64_t off = -1;
       if (tile < tile_end && token < n) {
-        const int blk_idx = token / p.block_size;
+        const int blk_idx = p.bs_shift >= 0 ? (token >> p.bs_shift) : token / p.block_size;
         off = static_cast<int64_t>(__ldg(table + blk_idx)) * p.block_stride +
               static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride + head_off;
       }
       s_off[((tile - tile_begin) % NST) * kTileTokens + tid] = off;
     }
   };
+  const unsigned char* kc_base = static_cast<const unsigned char*>(p.key_cache);
+  const int64_t v_minus_k = static_cast<const unsigned char*>(p.value_cache) - kc_base;
   auto load_tile = [&](int tile) {  // both tiles of `tile` into its stage; rows beyond the sequence become zeros
     constexpr int kChunks = D * ES / 16;  // 16-byte chunks per row
     const int slot = (tile - tile_begin) % NST;
     const int64_t* offs = s_off + slot * kTileTokens;
     unsigned char* ks = s_kv + slot * 2 * Cfg::kTileBytes;
-    const unsigned char* kc = static_cast<const unsigned char*>(p.key_cache);
-    const unsigned char* vc = static_cast<const unsigned char*>(p.value_cache);
+    const bool full = (tile + 1) * kTileTokens <= n;  // every row of the tile exists: no per-row checks
     auto copy_chunk = [&](int r, int col) {
       const int64_t off = offs[r];
-      const int64_t src = (off < 0 ? 0 : off) * ES + col * 16;
       const uint32_t dst = smem_u32(ks + r * RB + col * 16);
-      cp_async_16(dst, kc + src, off < 0 ? 0 : 16);
-      cp_async_16(dst + Cfg::kTileBytes, vc + src, off < 0 ? 0 : 16);
+      if (full) {
+        const unsigned char* src = kc_base + off * ES + col * 16;
+        cp_async_16(dst, src, 16);
+        cp_async_16(dst + Cfg::kTileBytes, src + v_minus_k, 16);
+      } else {
+        const unsigned char* src = kc_base + (off < 0 ? 0 : off) * ES + col * 16;
+        cp_async_16(dst, src, off < 0 ? 0 : 16);
+        cp_async_16(dst + Cfg::kTileBytes, src + v_minus_k, off < 0 ? 0 : 16);
+      }
     };
     if constexpr (kAttnThreads % kChunks == 0) {
       constexpr int kRowsPerPass = kAttnThreads / kChunks;
@@ -754,6 +762,7 @@ KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void*
   p.group = static_cast<int32_t>(num_heads / num_kv_heads);
   p.row_tiles = (p.group + kRows - 1) / kRows;
   p.block_size = static_cast<int32_t>(block_size);
+  p.bs_shift = pow2_shift(block_size);
   p.num_splits = pl.splits;
   p.tiles_per_split = pl.tiles_per_split;
   p.softmax_scale = softmax_scale;
