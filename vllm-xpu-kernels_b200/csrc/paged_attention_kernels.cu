@@ -148,8 +148,9 @@ struct DecodeCfg {
   static constexpr int kRowBytes = D * kCacheES + 16;             // shared-memory row of K and V (16 B pad:
                                                                   // eight consecutive rows hit distinct banks)
   static constexpr int kTileBytes = kTileTokens * kRowBytes;      // one K or V tile
-  // Two stages: one tile is consumed while the next one lands.  More stages were slower: what the kernel
-  // needs most is resident warps (D = 128: 76 KB, three CTAs per SM for a 16-bit cache; 43 KB, four for fp8).
+  // Two stages: one tile is consumed while the next one lands.  More stages were slower (fp8, D = 128: 110 us
+  // with two stages and four CTAs per SM, 129 us with three stages and three CTAs, 185 us with four and two):
+  // resident warps count for more than bytes in flight per CTA.
   static constexpr int kStages = 2;
   static constexpr int kSmemQ = kRows * kQRowBytes;
   static constexpr int kSmemOff = kStages * kTileTokens * (int)sizeof(int64_t);  // row offsets, one slot per stage
@@ -289,7 +290,8 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
 
   // ---- running state of this warp ----------------------------------------------------------------
   const float scale2 = p.softmax_scale * kLog2e * ((kFp8 && p.k_descale) ? __ldg(p.k_descale) : 1.0f);
-  float m_run[2] = {-INFINITY, -INFINITY};  // running maximum of the raw logits of rows g and g + 8
+  const float lazy_margin = 8.0f / scale2;  // raw-logit distance that is worth a factor 2^8
+  float m_run[2] = {-INFINITY, -INFINITY};  // reference point (a lagging maximum) of the raw logits of rows g, g + 8
   float l_run[2] = {0.f, 0.f};              // this lane's share of the running sums of rows g and g + 8
   // rows g (c0, c1) / g + 8 (c2, c3); columns of tile i: 16-bit cache  8i + 2t, + 1
   //                                                      fp8 cache     16 (i / 2) + 4t + (i % 2), + 2
@@ -373,16 +375,19 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
           if (tok_base + nt * 8 + (e & 1) >= n) s_acc[nt][e] = -INFINITY;
       }
     }
+    // The reference point of the exponentials follows the maximum lazily: it moves only when a logit exceeds it
+    // by more than 2^8 after scaling (probabilities then reach at most 256, harmless in fp16 / bf16 / fp32), so
+    // that the accumulator is rescaled a few times per sequence instead of in most tiles.
     float alpha[2], neg_ms[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       float mx = fmaxf(fmaxf(s_acc[0][2 * r], s_acc[0][2 * r + 1]), fmaxf(s_acc[1][2 * r], s_acc[1][2 * r + 1]));
       mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
-      const float m_new = fmaxf(m_run[r], mx);
-      alpha[r] = (m_new == -INFINITY) ? 1.0f : fast_exp2((m_run[r] - m_new) * scale2);
-      neg_ms[r] = (m_new == -INFINITY) ? 0.f : -m_new * scale2;  // all masked so far: 2^(-inf) = 0 below
-      m_run[r] = m_new;
+      const bool move = mx > m_run[r] + lazy_margin;  // also the first finite maximum (m_run = -inf)
+      alpha[r] = move ? fast_exp2((m_run[r] - mx) * scale2) : 1.0f;
+      m_run[r] = move ? mx : m_run[r];
+      neg_ms[r] = (m_run[r] == -INFINITY) ? 0.f : -m_run[r] * scale2;  // all masked so far: 2^(-inf) = 0 below
       l_run[r] *= alpha[r];
     }
     // rounded to T16, the probabilities are the A operand of the second product; the running sums take them
