@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* s_kv = smem;                                       // NST stages x (K tile, V tile)
   unsigned char* s_q = s_kv + NST * 2 * Cfg::kTileBytes;            // [16][QRB]
-  int64_t* s_off = reinterpret_cast<int64_t*>(s_q + Cfg::kSmemQ);   // [NST][64] element offsets, -1 = no such token
+  int64_t* s_off = reinterpret_cast<int64_t*>(s_q + Cfg::kSmemQ);   // [NST][64] byte offsets of the tokens' rows
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;  // accumulator row (and row + 8) and column pair of this lane
@@ -248,35 +248,29 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
   auto publish_offsets = [&](int tile) {  // by threads 0..63, into slot (tile - tile_begin) % NST
     if (tid < kTileTokens) {
       const int token = tile * kTileTokens + tid;
-      int64_t off = -1;
+      int64_t off = 0;  // rows beyond the sequence are copied with size 0 from a valid address
       if (tile < tile_end && token < n) {
         const int blk_idx = p.bs_shift >= 0 ? (token >> p.bs_shift) : token / p.block_size;
-        off = static_cast<int64_t>(__ldg(table + blk_idx)) * p.block_stride +
-              static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride + head_off;
+        off = (static_cast<int64_t>(__ldg(table + blk_idx)) * p.block_stride +
+               static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride + head_off) * ES;
       }
       s_off[((tile - tile_begin) % NST) * kTileTokens + tid] = off;
     }
   };
-  const unsigned char* kc_base = static_cast<const unsigned char*>(p.key_cache);
-  const int64_t v_minus_k = static_cast<const unsigned char*>(p.value_cache) - kc_base;
+  const int64_t v_minus_k =
+      static_cast<const unsigned char*>(p.value_cache) - static_cast<const unsigned char*>(p.key_cache);
   auto load_tile = [&](int tile) {  // both tiles of `tile` into its stage; rows beyond the sequence become zeros
     constexpr int kChunks = D * ES / 16;  // 16-byte chunks per row
     const int slot = (tile - tile_begin) % NST;
     const int64_t* offs = s_off + slot * kTileTokens;
     unsigned char* ks = s_kv + slot * 2 * Cfg::kTileBytes;
-    const bool full = (tile + 1) * kTileTokens <= n;  // every row of the tile exists: no per-row checks
+    const int rows_left = n - tile * kTileTokens;  // rows of this tile that exist (may exceed 64)
     auto copy_chunk = [&](int r, int col) {
-      const int64_t off = offs[r];
+      const unsigned char* src = static_cast<const unsigned char*>(p.key_cache) + col * 16 + offs[r];
       const uint32_t dst = smem_u32(ks + r * RB + col * 16);
-      if (full) {
-        const unsigned char* src = kc_base + off * ES + col * 16;
-        cp_async_16(dst, src, 16);
-        cp_async_16(dst + Cfg::kTileBytes, src + v_minus_k, 16);
-      } else {
-        const unsigned char* src = kc_base + (off < 0 ? 0 : off) * ES + col * 16;
-        cp_async_16(dst, src, off < 0 ? 0 : 16);
-        cp_async_16(dst + Cfg::kTileBytes, src + v_minus_k, off < 0 ? 0 : 16);
-      }
+      const int nbytes = r < rows_left ? 16 : 0;
+      cp_async_16(dst, src, nbytes);
+      cp_async_16(dst + Cfg::kTileBytes, src + v_minus_k, nbytes);
     };
     if constexpr (kAttnThreads % kChunks == 0) {
       constexpr int kRowsPerPass = kAttnThreads / kChunks;
