@@ -26,7 +26,6 @@ namespace kvc {
 namespace {
 
 constexpr int kAttnThreads = 128;       // 4 warps
-constexpr int kTileTokens = 64;         // tokens per pipeline stage; warp w owns tokens [16w, 16w + 16) for Q.K
 constexpr int kRows = 16;               // query rows per CTA (the heads of one kv group, padded)
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -135,8 +134,8 @@ struct DecodeParams {
 // are widened to fp16 on their way into shared memory; the products then run in fp16).  D: head size.
 //
 // A CTA owns (sequence, kv head, up to 16 query heads of its group, one split of the sequence) and walks
-// the split in tiles of 64 tokens through a two-stage shared-memory ring.  Warp w owns tokens
-// [16w, 16w + 16) of every tile for BOTH products: it keeps its own running maximum, sum and a full
+// the split in tiles of 64 (or 128) tokens through a two-stage shared-memory ring.  Warp w owns tokens
+// [16w, 16w + 16) of every 64 tokens for BOTH products: it keeps its own running maximum, sum and a full
 // 16 x D accumulator, the probabilities go from the first product's accumulators straight into the second
 // product's A operand, and the four warps meet only at the pipeline barrier (one per tile) and in the
 // final merge of their partial results.
@@ -147,17 +146,25 @@ struct DecodeCfg {
   static constexpr int kQRowBytes = D * 2 + 16;                   // shared-memory row of Q
   static constexpr int kRowBytes = D * kCacheES + 16;             // shared-memory row of K and V (16 B pad:
                                                                   // eight consecutive rows hit distinct banks)
-  static constexpr int kTileBytes = kTileTokens * kRowBytes;      // one K or V tile
+  // Tokens per tile: 64, or 128 where a row is at most 128 bytes (fp8 with D <= 128, 16-bit with D = 64).  With
+  // 128 a warp owns two groups of 16 tokens per tile, whose first products are independent instruction streams,
+  // and a CTA keeps twice the bytes in flight at the shared-memory footprint of the 64-token 16-bit case.
+  static constexpr int kTile = (D * kCacheES <= 128) ? 128 : 64;
+  static constexpr int kGroups = kTile / 64;                      // 16-token groups per warp and tile
+  static constexpr int kTileBytes = kTile * kRowBytes;            // one K or V tile
   // Two stages: one tile is consumed while the next one lands.  More stages were slower (fp8, D = 128: 110 us
   // with two stages and four CTAs per SM, 129 us with three stages and three CTAs, 185 us with four and two):
   // resident warps count for more than bytes in flight per CTA.
   static constexpr int kStages = 2;
-  static constexpr int kSmemQ = kRows * kQRowBytes;
-  static constexpr int kSmemOff = kStages * kTileTokens * (int)sizeof(int64_t);  // row offsets, one slot per stage
+  static constexpr bool kQInRegs = D <= 128;  // query fragments stay in registers (else re-read per tile)
+  // The query rows pass through shared memory once on their way into registers; they borrow the second
+  // stage of the ring, which is not written before every thread has fetched its fragments.
+  static constexpr int kSmemQ = kQInRegs ? 0 : kRows * kQRowBytes;
+  static_assert(kRows * kQRowBytes <= 2 * kTileBytes, "query rows fit in a stage");
+  static constexpr int kSmemOff = kStages * kTile * (int)sizeof(int64_t);  // row offsets, one slot per stage
   static constexpr int kSmemBytes = kStages * 2 * kTileBytes + kSmemQ + kSmemOff;
   // the final merge reuses the ring: 4 warps x (16 x D fp32 + 32 floats of statistics)
   static_assert(4 * (kRows * D + 2 * kRows) * (int)sizeof(float) <= kStages * 2 * kTileBytes, "merge buffer fits");
-  static constexpr bool kQInRegs = D <= 128;  // query fragments stay in registers (else re-read per tile)
   static_assert(D % 64 == 0 && D <= 256, "head sizes 64, 128, 192, 256");
 };
 
@@ -177,12 +184,15 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
   constexpr int QRB = Cfg::kQRowBytes;
   constexpr int RB = Cfg::kRowBytes;
   constexpr int NST = Cfg::kStages;
+  constexpr int TN = Cfg::kTile;
+  constexpr int NG = Cfg::kGroups;
   constexpr int NT = D / 8;  // 8-column tiles of the output accumulator
 
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* s_kv = smem;                                       // NST stages x (K tile, V tile)
-  unsigned char* s_q = s_kv + NST * 2 * Cfg::kTileBytes;            // [16][QRB]
-  int64_t* s_off = reinterpret_cast<int64_t*>(s_q + Cfg::kSmemQ);   // [NST][64] byte offsets of the tokens' rows
+  unsigned char* s_q = Cfg::kQInRegs ? s_kv + 2 * Cfg::kTileBytes   // [16][QRB]: borrowed from stage 1, or own
+                                     : s_kv + NST * 2 * Cfg::kTileBytes;
+  int64_t* s_off = reinterpret_cast<int64_t*>(s_kv + NST * 2 * Cfg::kTileBytes + Cfg::kSmemQ);   // [NST][TN] byte offsets of the tokens' rows
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;  // accumulator row (and row + 8) and column pair of this lane
@@ -196,7 +206,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
   pdl_prologue();
 
   const int n = p.seq_lens[seq];
-  const int total_tiles = (n + kTileTokens - 1) / kTileTokens;
+  const int total_tiles = (n + TN - 1) / TN;
   const int tile_begin = split * p.tiles_per_split;
   const int tile_end = min(tile_begin + p.tiles_per_split, total_tiles);
 
@@ -246,15 +256,15 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
   const int32_t* table = p.block_table + seq * p.block_table_stride;
   const int64_t head_off = static_cast<int64_t>(kvh) * p.head_stride;
   auto publish_offsets = [&](int tile) {  // by threads 0..63, into slot (tile - tile_begin) % NST
-    if (tid < kTileTokens) {
-      const int token = tile * kTileTokens + tid;
+    if (tid < TN) {
+      const int token = tile * TN + tid;
       int64_t off = 0;  // rows beyond the sequence are copied with size 0 from a valid address
       if (tile < tile_end && token < n) {
         const int blk_idx = p.bs_shift >= 0 ? (token >> p.bs_shift) : token / p.block_size;
         off = (static_cast<int64_t>(__ldg(table + blk_idx)) * p.block_stride +
                static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride + head_off) * ES;
       }
-      s_off[((tile - tile_begin) % NST) * kTileTokens + tid] = off;
+      s_off[((tile - tile_begin) % NST) * TN + tid] = off;
     }
   };
   const int64_t v_minus_k =
@@ -262,9 +272,9 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
   auto load_tile = [&](int tile) {  // both tiles of `tile` into its stage; rows beyond the sequence become zeros
     constexpr int kChunks = D * ES / 16;  // 16-byte chunks per row
     const int slot = (tile - tile_begin) % NST;
-    const int64_t* offs = s_off + slot * kTileTokens;
+    const int64_t* offs = s_off + slot * TN;
     unsigned char* ks = s_kv + slot * 2 * Cfg::kTileBytes;
-    const int rows_left = n - tile * kTileTokens;  // rows of this tile that exist (may exceed 64)
+    const int rows_left = n - tile * TN;  // rows of this tile that exist (may exceed the tile)
     auto copy_chunk = [&](int r, int col) {
       const unsigned char* src = static_cast<const unsigned char*>(p.key_cache) + col * 16 + offs[r];
       const uint32_t dst = smem_u32(ks + r * RB + col * 16);
@@ -276,9 +286,9 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
       constexpr int kRowsPerPass = kAttnThreads / kChunks;
       const int r0 = tid / kChunks, col = tid - r0 * kChunks;
 #pragma unroll
-      for (int i = 0; i < kTileTokens / kRowsPerPass; ++i) copy_chunk(r0 + i * kRowsPerPass, col);
+      for (int i = 0; i < TN / kRowsPerPass; ++i) copy_chunk(r0 + i * kRowsPerPass, col);
     } else {  // D = 192: 24 or 12 chunks per row
-      for (int c = tid; c < kTileTokens * kChunks; c += kAttnThreads) copy_chunk(c / kChunks, c % kChunks);
+      for (int c = tid; c < TN * kChunks; c += kAttnThreads) copy_chunk(c / kChunks, c % kChunks);
     }
   };
 
@@ -334,39 +344,55 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
     const uint32_t ks = smem_u32(s_kv + slot * 2 * Cfg::kTileBytes);
     const uint32_t vs = ks + Cfg::kTileBytes;
 
-    // ---- S = Q K^T for this warp's 16 tokens ---------------------------------------------------
-    float s_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    // ---- S = Q K^T for this warp's groups of 16 tokens (group gi: rows 64 gi + 16 warp ..) -------
+    float s_acc[NG][2][4];
+#pragma unroll
+    for (int gi = 0; gi < NG; ++gi)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) s_acc[gi][nt][0] = s_acc[gi][nt][1] = s_acc[gi][nt][2] = s_acc[gi][nt][3] = 0.f;
     if constexpr (!kFp8) {
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
-        uint32_t a[4], b[4];
+        uint32_t a[4];
         q_frag(kk, a);
-        ldmatrix_x4(b, ks + k_lane_off + kk * 32);
-        mma_16816<T16>(s_acc[0], a, b[0], b[1]);
-        mma_16816<T16>(s_acc[1], a, b[2], b[3]);
+#pragma unroll
+        for (int gi = 0; gi < NG; ++gi) {
+          uint32_t b[4];
+          ldmatrix_x4(b, ks + k_lane_off + gi * 64 * RB + kk * 32);
+          mma_16816<T16>(s_acc[gi][0], a, b[0], b[1]);
+          mma_16816<T16>(s_acc[gi][1], a, b[2], b[3]);
+        }
       }
     } else {
 #pragma unroll
       for (int jj = 0; jj < D / 32; ++jj) {  // 32 head dimensions = two mma steps per ldmatrix
-        uint32_t a[4], b[4];
-        ldmatrix_x4(b, ks + k_lane_off + jj * 32);  // tokens 0-7: d-groups (2jj, 2jj+1); tokens 8-15: the same
-        q_frag(2 * jj, a);
-        mma_16816<T16>(s_acc[0], a, fp8x2_to_f16x2<KV>(b[0]), fp8x2_to_f16x2<KV>(b[0] >> 16));
-        mma_16816<T16>(s_acc[1], a, fp8x2_to_f16x2<KV>(b[2]), fp8x2_to_f16x2<KV>(b[2] >> 16));
-        q_frag(2 * jj + 1, a);
-        mma_16816<T16>(s_acc[0], a, fp8x2_to_f16x2<KV>(b[1]), fp8x2_to_f16x2<KV>(b[1] >> 16));
-        mma_16816<T16>(s_acc[1], a, fp8x2_to_f16x2<KV>(b[3]), fp8x2_to_f16x2<KV>(b[3] >> 16));
+        uint32_t a0[4], a1[4];
+        q_frag(2 * jj, a0);
+        q_frag(2 * jj + 1, a1);
+#pragma unroll
+        for (int gi = 0; gi < NG; ++gi) {
+          uint32_t b[4];
+          // tokens 0-7: d-groups (2jj, 2jj+1); tokens 8-15: the same
+          ldmatrix_x4(b, ks + k_lane_off + gi * 64 * RB + jj * 32);
+          mma_16816<T16>(s_acc[gi][0], a0, fp8x2_to_f16x2<KV>(b[0]), fp8x2_to_f16x2<KV>(b[0] >> 16));
+          mma_16816<T16>(s_acc[gi][1], a0, fp8x2_to_f16x2<KV>(b[2]), fp8x2_to_f16x2<KV>(b[2] >> 16));
+          mma_16816<T16>(s_acc[gi][0], a1, fp8x2_to_f16x2<KV>(b[1]), fp8x2_to_f16x2<KV>(b[1] >> 16));
+          mma_16816<T16>(s_acc[gi][1], a1, fp8x2_to_f16x2<KV>(b[3]), fp8x2_to_f16x2<KV>(b[3] >> 16));
+        }
       }
     }
 
     // ---- mask the tail, running maximum (of the raw logits: the scale is positive), P = 2^(scale (S - m)) --
-    if ((tile + 1) * kTileTokens > n) {  // only the last tile of a sequence has tokens to mask
-      const int tok_base = tile * kTileTokens + warp * 16 + 2 * t;
+    if ((tile + 1) * TN > n) {  // only the last tile of a sequence has tokens to mask
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
+      for (int gi = 0; gi < NG; ++gi) {
+        const int tok_base = tile * TN + gi * 64 + warp * 16 + 2 * t;
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-          if (tok_base + nt * 8 + (e & 1) >= n) s_acc[nt][e] = -INFINITY;
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (tok_base + nt * 8 + (e & 1) >= n) s_acc[gi][nt][e] = -INFINITY;
+        }
       }
     }
     // The reference point of the exponentials follows the maximum lazily: it moves only when a logit exceeds it
@@ -375,7 +401,11 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
     float alpha[2], neg_ms[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      float mx = fmaxf(fmaxf(s_acc[0][2 * r], s_acc[0][2 * r + 1]), fmaxf(s_acc[1][2 * r], s_acc[1][2 * r + 1]));
+      float mx = -INFINITY;
+#pragma unroll
+      for (int gi = 0; gi < NG; ++gi)
+        mx = fmaxf(mx, fmaxf(fmaxf(s_acc[gi][0][2 * r], s_acc[gi][0][2 * r + 1]),
+                             fmaxf(s_acc[gi][1][2 * r], s_acc[gi][1][2 * r + 1])));
       mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
       const bool move = mx > m_run[r] + lazy_margin;  // also the first finite maximum (m_run = -inf)
@@ -386,20 +416,23 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
     }
     // rounded to T16, the probabilities are the A operand of the second product; the running sums take them
     // unrounded, as the reference statement normalises before it rounds
-    uint32_t pa[4];
+    uint32_t pa[NG][4];
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      float pv[4];
+    for (int gi = 0; gi < NG; ++gi) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(fmaf(s_acc[nt][e], scale2, neg_ms[e >> 1]));
-      l_run[0] += pv[0] + pv[1];
-      l_run[1] += pv[2] + pv[3];
-      pa[2 * nt] = pack2<T16>(pv[0], pv[1]);      // row g,     tokens nt * 8 + 2t, + 1
-      pa[2 * nt + 1] = pack2<T16>(pv[2], pv[3]);  // row g + 8
+      for (int nt = 0; nt < 2; ++nt) {
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(fmaf(s_acc[gi][nt][e], scale2, neg_ms[e >> 1]));
+        l_run[0] += pv[0] + pv[1];
+        l_run[1] += pv[2] + pv[3];
+        pa[gi][2 * nt] = pack2<T16>(pv[0], pv[1]);      // row g,     tokens nt * 8 + 2t, + 1 of the group
+        pa[gi][2 * nt + 1] = pack2<T16>(pv[2], pv[3]);  // row g + 8
+      }
     }
 
-    // ---- O = alpha * O + P V over this warp's 16 tokens -------------------------------------------
-    if (__any_sync(0xFFFFFFFFu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {  // the maximum rarely moves
+    // ---- O = alpha * O + P V over this warp's tokens ----------------------------------------------
+    if (__any_sync(0xFFFFFFFFu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {  // rare, see above
 #pragma unroll
       for (int i = 0; i < NT; ++i) {
         o_acc[i][0] *= alpha[0];
@@ -411,25 +444,32 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
     if constexpr (!kFp8) {
 #pragma unroll
       for (int np = 0; np < D / 16; ++np) {  // two 8-column tiles per ldmatrix
-        uint32_t b[4];
-        ldmatrix_x4_trans(b, vs + v_lane_off + np * 32);
-        mma_16816<T16>(o_acc[2 * np], pa, b[0], b[1]);
-        mma_16816<T16>(o_acc[2 * np + 1], pa, b[2], b[3]);
+#pragma unroll
+        for (int gi = 0; gi < NG; ++gi) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, vs + v_lane_off + gi * 64 * RB + np * 32);
+          mma_16816<T16>(o_acc[2 * np], pa[gi], b[0], b[1]);
+          mma_16816<T16>(o_acc[2 * np + 1], pa[gi], b[2], b[3]);
+        }
       }
     } else {
 #pragma unroll
       for (int jj = 0; jj < D / 32; ++jj) {  // 32 head dimensions = four 8-column tiles per ldmatrix
-        uint32_t b[4];
-        // transposed 16-bit units: b[i] = (V[2t][2g], V[2t][2g+1], V[2t+1][2g], V[2t+1][2g+1]) as bytes, for
-        // tokens 0-7 / 8-15 (i = 0 / 1) of dimensions 32jj .. +15, and the same (i = 2 / 3) of 32jj+16 .. +31
-        ldmatrix_x4_trans(b, vs + v_lane_off + jj * 32);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) b[i] = __byte_perm(b[i], 0, 0x3120);  // (even d: tokens 2t, 2t+1 | odd d: same)
+        for (int gi = 0; gi < NG; ++gi) {
+          uint32_t b[4];
+          // transposed 16-bit units: b[i] = (V[2t][2g], V[2t][2g+1], V[2t+1][2g], V[2t+1][2g+1]) as bytes, for
+          // tokens 0-7 / 8-15 (i = 0 / 1) of dimensions 32jj .. +15, and the same (i = 2 / 3) of 32jj+16 .. +31
+          ldmatrix_x4_trans(b, vs + v_lane_off + gi * 64 * RB + jj * 32);
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          mma_16816<T16>(o_acc[4 * jj + 2 * h], pa, fp8x2_to_f16x2<KV>(b[2 * h]), fp8x2_to_f16x2<KV>(b[2 * h + 1]));
-          mma_16816<T16>(o_acc[4 * jj + 2 * h + 1], pa, fp8x2_to_f16x2<KV>(b[2 * h] >> 16),
-                         fp8x2_to_f16x2<KV>(b[2 * h + 1] >> 16));
+          for (int i = 0; i < 4; ++i) b[i] = __byte_perm(b[i], 0, 0x3120);  // (even d: tokens 2t, 2t+1 | odd d: same)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            mma_16816<T16>(o_acc[4 * jj + 2 * h], pa[gi], fp8x2_to_f16x2<KV>(b[2 * h]),
+                           fp8x2_to_f16x2<KV>(b[2 * h + 1]));
+            mma_16816<T16>(o_acc[4 * jj + 2 * h + 1], pa[gi], fp8x2_to_f16x2<KV>(b[2 * h] >> 16),
+                           fp8x2_to_f16x2<KV>(b[2 * h + 1] >> 16));
+          }
         }
       }
     }
@@ -668,12 +708,18 @@ struct DecodePlan {
   int64_t workspace_bytes;
 };
 
+// Tokens per tile of the kernel instance for this head size and cache type (DecodeCfg::kTile).
+int decode_tile_tokens(int64_t head_size, int kv_dtype) {
+  return head_size * (kv_dtype == KVC_KV_AUTO ? 2 : 1) <= 128 ? 128 : 64;
+}
+
 DecodePlan plan_decode(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads, int64_t head_size,
                        int64_t max_seq_len, int q_dtype, int kv_dtype) {
   DecodePlan pl{1, 1, 0};
+  const int tile_tokens = decode_tile_tokens(head_size, kv_dtype);
   const int64_t group = num_kv_heads > 0 ? num_heads / num_kv_heads : 1;
   const int64_t row_tiles = (group + kRows - 1) / kRows;
-  int64_t max_tiles = (max_seq_len + kTileTokens - 1) / kTileTokens;
+  int64_t max_tiles = (max_seq_len + tile_tokens - 1) / tile_tokens;
   if (max_tiles < 1) max_tiles = 1;
   const int64_t base = num_seqs * num_kv_heads * row_tiles;
   pl.splits = base > 0 ? pick_splits(base, max_tiles, decode_slots(q_dtype, kv_dtype, static_cast<int>(head_size))) : 1;
