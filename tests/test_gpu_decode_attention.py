@@ -162,6 +162,20 @@ def test_decode_attention_split_count_does_not_change_the_result(cuda_device):
     torch.testing.assert_close(c.float(), want, **TOL)
 
 
+def test_decode_attention_head_shards_concatenate(cuda_device):
+    """Tensor parallelism: a rank that holds kv heads [k0, k1) and their query heads computes exactly its slice of
+    the output; no exchange.  (Tolerance, not bits: the split count depends on how many heads a launch has.)"""
+    query, kc, vc, bt, lens, sk = make_case(torch.bfloat16, 16, 4, 128, [1500, 64, 700], 16, 128, True, seed=31)
+    whole = run_gpu(cuda_device, query, kc, vc, bt, lens, 0.09, sink=sk)
+    for world in (2, 4):
+        parts = []
+        for rank in range(world):
+            k0, k1 = rank * 4 // world, (rank + 1) * 4 // world
+            parts.append(run_gpu(cuda_device, query[:, k0 * 4:k1 * 4], kc[:, :, k0:k1], vc[:, :, k0:k1], bt, lens, 0.09,
+                                 sink=sk[k0 * 4:k1 * 4].contiguous(), max_seq_len=1500))
+        torch.testing.assert_close(torch.cat(parts, dim=1).float(), whole.float(), **TOL)
+
+
 def test_write_fp8_cache_then_attend(cuda_device):
     """The two halves together: reshape_and_cache_flash stores fp8 keys and values with k_scale / v_scale, the
     decode attention reads them back with the same scales as descales.  Checked against the oracle's own

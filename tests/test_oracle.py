@@ -81,6 +81,29 @@ def test_oracle_reproduces_reference_decode_attention_fixture(fname):
     torch.testing.assert_close(got, c.expected.float(), atol=H.ATTN_ATOL, rtol=H.ATTN_RTOL)
 
 
+def test_decode_attention_shards_by_kv_head():
+    """Tensor parallelism over kv heads: each rank holds its kv heads' cache slice and the query heads of those
+    groups; concatenating the ranks' outputs along the head axis gives the unsharded result (nothing is exchanged)."""
+    torch.manual_seed(4)
+    S, hq, hk, D, bs, nb = 3, 16, 4, 64, 16, 12
+    query = torch.randn(S, hq, D).to(torch.bfloat16)
+    kc = torch.randn(nb, bs, hk, D).to(torch.bfloat16)
+    vc = torch.randn(nb, bs, hk, D).to(torch.bfloat16)
+    bt = torch.randint(0, nb, (S, 6), dtype=torch.int32)
+    lens = torch.tensor([90, 1, 33], dtype=torch.int32)
+    sink = torch.randn(hq).to(torch.bfloat16)
+    whole = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, 0.125, sink=sink)
+    for world in (2, 4):
+        g = hq // hk
+        parts = []
+        for rank in range(world):
+            k0, k1 = rank * hk // world, (rank + 1) * hk // world
+            parts.append(torch_views.run_paged_decode_attention(
+                query[:, k0 * g:k1 * g], kc[:, :, k0:k1], vc[:, :, k0:k1], bt, lens, 0.125,
+                sink=sink[k0 * g:k1 * g].contiguous()))
+        assert torch.equal(torch.cat(parts, dim=1), whole)
+
+
 def test_fp8_decoders_invert_the_encoders():
     L = oracle.lib()
     for b in range(256):

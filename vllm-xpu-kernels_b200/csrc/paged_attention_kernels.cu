@@ -139,17 +139,19 @@ struct DecodeParams {
 // 16 x D accumulator, the probabilities go from the first product's accumulators straight into the second
 // product's A operand, and the four warps meet only at the pipeline barrier (one per tile) and in the
 // final merge of their partial results.
-template <typename TQ, int KV, int D>
+template <typename TQ, int KV, int D, bool WIDE>
 struct DecodeCfg {
   using T16 = std::conditional_t<KV == KVC_KV_AUTO, TQ, __half>;  // operand type of the matrix products
   static constexpr int kCacheES = (KV == KVC_KV_AUTO) ? 2 : 1;    // bytes per cached element
   static constexpr int kQRowBytes = D * 2 + 16;                   // shared-memory row of Q
   static constexpr int kRowBytes = D * kCacheES + 16;             // shared-memory row of K and V (16 B pad:
                                                                   // eight consecutive rows hit distinct banks)
-  // Tokens per tile: 64, or 128 where a row is at most 128 bytes (fp8 with D <= 128, 16-bit with D = 64).  With
-  // 128 a warp owns two groups of 16 tokens per tile, whose first products are independent instruction streams,
-  // and a CTA keeps twice the bytes in flight at the shared-memory footprint of the 64-token 16-bit case.
-  static constexpr int kTile = (D * kCacheES <= 128) ? 128 : 64;
+  // Tokens per tile: 64, or (WIDE) 128 where a row is at most 128 bytes (fp8 with D <= 128, 16-bit with D = 64).
+  // With 128 a warp owns two groups of 16 tokens per tile, whose first products are independent instruction
+  // streams, and a CTA keeps twice the bytes in flight, at the price of fewer CTAs per SM; the host picks the
+  // variant per launch.
+  static_assert(!WIDE || D * kCacheES <= 128, "wide tiles only for rows of at most 128 bytes");
+  static constexpr int kTile = WIDE ? 128 : 64;
   static constexpr int kGroups = kTile / 64;                      // 16-token groups per warp and tile
   static constexpr int kTileBytes = kTile * kRowBytes;            // one K or V tile
   // Two stages: one tile is consumed while the next one lands.  More stages were slower (fp8, D = 128: 110 us
@@ -175,9 +177,9 @@ struct DecodeCfg {
 // position (W & 1) * 4 + (W >> 1).
 __device__ __forceinline__ int fp8_q_word_position(int w) { return (w & 1) * 4 + (w >> 1); }
 
-template <typename TQ, int KV, int D>
+template <typename TQ, int KV, int D, bool WIDE>
 __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const DecodeParams p) {
-  using Cfg = DecodeCfg<TQ, KV, D>;
+  using Cfg = DecodeCfg<TQ, KV, D, WIDE>;
   using T16 = typename Cfg::T16;
   constexpr bool kFp8 = KV != KVC_KV_AUTO;
   constexpr int ES = Cfg::kCacheES;
@@ -590,16 +592,17 @@ namespace {
 constexpr int kMaxSplits = 128;
 
 // How many CTAs of a kernel instance one SM holds (asked of the runtime once per instance and device).
-template <typename TQ, int KV, int D>
+template <typename TQ, int KV, int D, bool WIDE>
 int decode_ctas_per_sm() {
-  using Cfg = DecodeCfg<TQ, KV, D>;
+  using Cfg = DecodeCfg<TQ, KV, D, WIDE>;
   static int cached[64] = {0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
   if (cached[dev] == 0) {
     int n = 0;
-    cudaFuncSetAttribute(paged_decode_kernel<TQ, KV, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, paged_decode_kernel<TQ, KV, D>, kAttnThreads,
+    cudaFuncSetAttribute(paged_decode_kernel<TQ, KV, D, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         Cfg::kSmemBytes);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, paged_decode_kernel<TQ, KV, D, WIDE>, kAttnThreads,
                                                       Cfg::kSmemBytes) != cudaSuccess || n < 1)
       n = 1;
     cached[dev] = n;
@@ -607,26 +610,35 @@ int decode_ctas_per_sm() {
   return cached[dev];
 }
 
+// Wide tiles exist where a cached row is at most 128 bytes.
+constexpr bool wide_exists(int kv, int d) { return d * (kv == KVC_KV_AUTO ? 2 : 1) <= 128; }
+
 template <typename TQ, int KV>
-int decode_ctas_per_sm_d(int head_size) {
+int decode_ctas_per_sm_d(int head_size, bool wide) {
   switch (head_size) {
-    case 64: return decode_ctas_per_sm<TQ, KV, 64>();
-    case 128: return decode_ctas_per_sm<TQ, KV, 128>();
-    case 192: return decode_ctas_per_sm<TQ, KV, 192>();
-    default: return decode_ctas_per_sm<TQ, KV, 256>();
+    case 64:
+      if (wide) return decode_ctas_per_sm<TQ, KV, 64, true>();
+      return decode_ctas_per_sm<TQ, KV, 64, false>();
+    case 128:
+      if constexpr (wide_exists(KV, 128)) {
+        if (wide) return decode_ctas_per_sm<TQ, KV, 128, true>();
+      }
+      return decode_ctas_per_sm<TQ, KV, 128, false>();
+    case 192: return decode_ctas_per_sm<TQ, KV, 192, false>();
+    default: return decode_ctas_per_sm<TQ, KV, 256, false>();
   }
 }
 
-int decode_slots(int q_dtype, int kv, int head_size) {  // CTAs the whole device holds at once
+int decode_slots(int q_dtype, int kv, int head_size, bool wide) {  // CTAs the whole device holds at once
   int per_sm;
   if (q_dtype == KVC_IN_F16) {
-    per_sm = kv == KVC_KV_AUTO ? decode_ctas_per_sm_d<__half, KVC_KV_AUTO>(head_size)
-             : kv == KVC_KV_FP8_E4M3 ? decode_ctas_per_sm_d<__half, KVC_KV_FP8_E4M3>(head_size)
-                                     : decode_ctas_per_sm_d<__half, KVC_KV_FP8_E5M2>(head_size);
+    per_sm = kv == KVC_KV_AUTO ? decode_ctas_per_sm_d<__half, KVC_KV_AUTO>(head_size, wide)
+             : kv == KVC_KV_FP8_E4M3 ? decode_ctas_per_sm_d<__half, KVC_KV_FP8_E4M3>(head_size, wide)
+                                     : decode_ctas_per_sm_d<__half, KVC_KV_FP8_E5M2>(head_size, wide);
   } else {
-    per_sm = kv == KVC_KV_AUTO ? decode_ctas_per_sm_d<__nv_bfloat16, KVC_KV_AUTO>(head_size)
-             : kv == KVC_KV_FP8_E4M3 ? decode_ctas_per_sm_d<__nv_bfloat16, KVC_KV_FP8_E4M3>(head_size)
-                                     : decode_ctas_per_sm_d<__nv_bfloat16, KVC_KV_FP8_E5M2>(head_size);
+    per_sm = kv == KVC_KV_AUTO ? decode_ctas_per_sm_d<__nv_bfloat16, KVC_KV_AUTO>(head_size, wide)
+             : kv == KVC_KV_FP8_E4M3 ? decode_ctas_per_sm_d<__nv_bfloat16, KVC_KV_FP8_E4M3>(head_size, wide)
+                                     : decode_ctas_per_sm_d<__nv_bfloat16, KVC_KV_FP8_E5M2>(head_size, wide);
   }
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -638,7 +650,7 @@ int decode_slots(int q_dtype, int kv, int head_size) {  // CTAs the whole device
 // start-up cost of about two tiles), so the launch takes ceil(ctas / slots) rounds of that length; splitting
 // adds the merge launch and its traffic, about three tiles' worth.  Pick the count that minimises the sum,
 // the smaller one on ties.
-int pick_splits(int64_t base, int64_t max_tiles, int64_t slots) {
+int pick_splits(int64_t base, int64_t max_tiles, int64_t slots, int64_t* cost_out) {
   int best = 1;
   int64_t best_cost = -1;
   const int64_t limit = max_tiles < kMaxSplits ? max_tiles : kMaxSplits;
@@ -653,12 +665,13 @@ int pick_splits(int64_t base, int64_t max_tiles, int64_t slots) {
       best = static_cast<int>(s);
     }
   }
+  *cost_out = best_cost;
   return best;
 }
 
-template <typename TQ, int KV, int D>
+template <typename TQ, int KV, int D, bool WIDE>
 cudaError_t launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
-  using Cfg = DecodeCfg<TQ, KV, D>;
+  using Cfg = DecodeCfg<TQ, KV, D, WIDE>;
   static std::once_flag once[64];
   static cudaError_t attr_err[64];
   int dev = 0;
@@ -666,8 +679,8 @@ cudaError_t launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   std::call_once(once[dev], [&] {
-    attr_err[dev] = cudaFuncSetAttribute(paged_decode_kernel<TQ, KV, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kSmemBytes);
+    attr_err[dev] = cudaFuncSetAttribute(paged_decode_kernel<TQ, KV, D, WIDE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   });
   if (attr_err[dev] != cudaSuccess) return attr_err[dev];
   cudaLaunchConfig_t cfg = {};
@@ -680,51 +693,66 @@ cudaError_t launch_decode(const DecodeParams& p, dim3 grid, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, paged_decode_kernel<TQ, KV, D>, p);
+  return cudaLaunchKernelEx(&cfg, paged_decode_kernel<TQ, KV, D, WIDE>, p);
 }
 
 template <typename TQ, int KV>
-cudaError_t launch_decode_d(int head_size, const DecodeParams& p, dim3 grid, cudaStream_t st) {
+cudaError_t launch_decode_d(int head_size, bool wide, const DecodeParams& p, dim3 grid, cudaStream_t st) {
   switch (head_size) {
-    case 64: return launch_decode<TQ, KV, 64>(p, grid, st);
-    case 128: return launch_decode<TQ, KV, 128>(p, grid, st);
-    case 192: return launch_decode<TQ, KV, 192>(p, grid, st);
-    default: return launch_decode<TQ, KV, 256>(p, grid, st);
+    case 64:
+      if (wide) return launch_decode<TQ, KV, 64, true>(p, grid, st);
+      return launch_decode<TQ, KV, 64, false>(p, grid, st);
+    case 128:
+      if constexpr (wide_exists(KV, 128)) {
+        if (wide) return launch_decode<TQ, KV, 128, true>(p, grid, st);
+      }
+      return launch_decode<TQ, KV, 128, false>(p, grid, st);
+    case 192: return launch_decode<TQ, KV, 192, false>(p, grid, st);
+    default: return launch_decode<TQ, KV, 256, false>(p, grid, st);
   }
 }
 
 template <typename TQ>
-cudaError_t launch_decode_kv(int kv, int head_size, const DecodeParams& p, dim3 grid, cudaStream_t st) {
+cudaError_t launch_decode_kv(int kv, int head_size, bool wide, const DecodeParams& p, dim3 grid, cudaStream_t st) {
   switch (kv) {
-    case KVC_KV_AUTO: return launch_decode_d<TQ, KVC_KV_AUTO>(head_size, p, grid, st);
-    case KVC_KV_FP8_E4M3: return launch_decode_d<TQ, KVC_KV_FP8_E4M3>(head_size, p, grid, st);
-    default: return launch_decode_d<TQ, KVC_KV_FP8_E5M2>(head_size, p, grid, st);
+    case KVC_KV_AUTO: return launch_decode_d<TQ, KVC_KV_AUTO>(head_size, wide, p, grid, st);
+    case KVC_KV_FP8_E4M3: return launch_decode_d<TQ, KVC_KV_FP8_E4M3>(head_size, wide, p, grid, st);
+    default: return launch_decode_d<TQ, KVC_KV_FP8_E5M2>(head_size, wide, p, grid, st);
   }
 }
 
 struct DecodePlan {
   int splits;
   int tiles_per_split;
+  bool wide;  // 128-token tiles
   int64_t workspace_bytes;
 };
 
-// Tokens per tile of the kernel instance for this head size and cache type (DecodeCfg::kTile).
-int decode_tile_tokens(int64_t head_size, int kv_dtype) {
-  return head_size * (kv_dtype == KVC_KV_AUTO ? 2 : 1) <= 128 ? 128 : 64;
-}
-
 DecodePlan plan_decode(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads, int64_t head_size,
                        int64_t max_seq_len, int q_dtype, int kv_dtype) {
-  DecodePlan pl{1, 1, 0};
-  const int tile_tokens = decode_tile_tokens(head_size, kv_dtype);
+  DecodePlan pl{1, 1, false, 0};
   const int64_t group = num_kv_heads > 0 ? num_heads / num_kv_heads : 1;
   const int64_t row_tiles = (group + kRows - 1) / kRows;
-  int64_t max_tiles = (max_seq_len + tile_tokens - 1) / tile_tokens;
-  if (max_tiles < 1) max_tiles = 1;
   const int64_t base = num_seqs * num_kv_heads * row_tiles;
-  pl.splits = base > 0 ? pick_splits(base, max_tiles, decode_slots(q_dtype, kv_dtype, static_cast<int>(head_size))) : 1;
-  pl.tiles_per_split = static_cast<int>((max_tiles + pl.splits - 1) / pl.splits);
-  pl.splits = static_cast<int>((max_tiles + pl.tiles_per_split - 1) / pl.tiles_per_split);  // drop empty tails
+  if (base <= 0) return pl;
+  // both tile sizes where both exist: the cheaper plan wins.  A 128-token tile costs about 1.5 64-token tiles
+  // of a CTA's time (measured on batches with many rounds: fewer barriers and more overlap per token).
+  int64_t best_cost = -1;
+  for (int wide = 0; wide <= (wide_exists(kv_dtype, static_cast<int>(head_size)) ? 1 : 0); ++wide) {
+    const int tile_tokens = wide ? 128 : 64;
+    int64_t max_tiles = (max_seq_len + tile_tokens - 1) / tile_tokens;
+    if (max_tiles < 1) max_tiles = 1;
+    int64_t cost = 0;
+    const int s = pick_splits(base, max_tiles, decode_slots(q_dtype, kv_dtype, static_cast<int>(head_size), wide != 0),
+                              &cost);
+    cost = wide ? (cost * 3 + 1) / 2 : cost;
+    if (best_cost < 0 || cost <= best_cost) {  // ties go to the wide tile: fewer barriers per token
+      best_cost = cost;
+      pl.wide = wide != 0;
+      pl.tiles_per_split = static_cast<int>((max_tiles + s - 1) / s);
+      pl.splits = static_cast<int>((max_tiles + pl.tiles_per_split - 1) / pl.tiles_per_split);  // drop empty tails
+    }
+  }
   if (pl.splits > 1) pl.workspace_bytes = num_seqs * num_heads * pl.splits * (head_size + 1) * (int64_t)sizeof(float);
   return pl;
 }
@@ -819,8 +847,9 @@ KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void*
   if (grid_y > 65535) return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: too many kv heads");
   const dim3 grid(static_cast<unsigned>(num_seqs), static_cast<unsigned>(grid_y), static_cast<unsigned>(pl.splits));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e = (q_dtype == KVC_IN_F16) ? launch_decode_kv<__half>(kv_dtype, static_cast<int>(head_size), p, grid, st)
-                                           : launch_decode_kv<__nv_bfloat16>(kv_dtype, static_cast<int>(head_size), p, grid, st);
+  cudaError_t e = (q_dtype == KVC_IN_F16)
+                      ? launch_decode_kv<__half>(kv_dtype, static_cast<int>(head_size), pl.wide, p, grid, st)
+                      : launch_decode_kv<__nv_bfloat16>(kv_dtype, static_cast<int>(head_size), pl.wide, p, grid, st);
   if (e != cudaSuccess)
     return fail(KVC_ERR_CUDA, std::string("paged_decode_attention launch failed: ") + cudaGetErrorString(e));
   if (pl.splits > 1) {
