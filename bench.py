@@ -2,7 +2,7 @@
 """Benchmark of the KV-cache write path: reshape_and_cache_flash, bf16 -> fp8_e4m3.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
-                    [--workload C4|C2|C3|C5-fp8|C5-bf16|C1] [--scaling weak|strong]
+                    [--workload C4|C2|C3|C5-fp8|C5-bf16|C1|<op>] [--scaling weak|strong]
 
 One step = one call of the op over one batch (the "C4" batch by default: 16384 tokens,
 8 KV heads x 128, cache of 65536 blocks x 64 slots, fp8_e4m3 store, slots in runs of 64).
@@ -25,6 +25,11 @@ Under torchrun every rank runs the same per-rank batch on its own GPU and cache 
 on the data path; NCCL only carries the barrier and the max-over-ranks of the times.
 
 --impl reference times the CPU oracle alone (rank 0 only), in the same units.
+
+The ops around the cache write have workloads of their own, measured and reported the same way
+(--workload mla-fp8 | gather | quant-static | quant-token | rope | rope-cache-fp8 | decode-bf16 |
+decode-fp8; sizes in benchmark/op_workloads.py).  Their e2e figure moves the step's inputs from pinned
+host memory through torch copies, calls the C ABI and reads the step's result back.
 """
 from __future__ import annotations
 
@@ -44,6 +49,7 @@ for _p in (REPO, PKG_ROOT, os.path.join(PKG_ROOT, "benchmark")):
 
 import torch  # noqa: E402
 
+import op_workloads  # noqa: E402
 import workloads  # noqa: E402
 
 NBUF = 8            # distinct input sets rotated through, so inputs come from HBM, not L2
@@ -525,6 +531,130 @@ def run_b200_arm(ns):
     return line
 
 
+# --------------------------------------------------------------------------------------------
+# the ops around the cache write (MLA, gather, fp8 quantisation, rotary embedding, decode attention)
+# --------------------------------------------------------------------------------------------
+def run_op_reference_arm(ns) -> None:
+    """--impl reference for an op workload: the CPU oracle alone, a bounded sample per step."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    w = op_workloads.BY_NAME[ns.workload]()
+    rate0, _, _, _, _ = op_workloads.cpu_rate(w, 1.0)
+    per_step = int(max(64, min(w.units_per_step, rate0 * 100.0 / max(1, ns.steps + ns.warmup))))
+    run, n, threads = w.cpu_run(per_step)
+    for _ in range(ns.warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(ns.steps):
+        run()
+    dt = time.perf_counter() - t0
+    value = n * ns.steps / dt
+    sample = f"{n} of the step's {w.units_per_step} tokens per step, {ns.steps} steps, {threads} thread(s)"
+    print(json.dumps({
+        "impl": "reference", "metric": w.metric, "value": value, "unit": "tokens/s", "n_gpus": ns.gpus,
+        "steps": ns.steps, "warmup": ns.warmup, "ms_per_step": dt / ns.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": w.arithmetic, "data": "synthetic",
+        "config": {"workload": f"{w.name}: {w.describe}", "tokens_per_step": n},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+def run_op_arm(ns):
+    """One of the ops around the cache write, measured like the cache write itself: CUDA graphs of
+    GRAPH_STEPS steps over rotating inputs, device events, max over ranks; every rank runs the same work."""
+    from vllm_xpu_kernels import cabi  # raises if the CUDA library is not built
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU oracle")
+    dist, rank, world, local = dist_setup(ns.gpus)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    cabi.lib()
+    w = op_workloads.BY_NAME[ns.workload]()
+    nbuf = 2
+    step, e2e_step, h2d, d2h = w.make_steps(dev, nbuf)
+
+    def capture(n: int):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(n):
+                step(i)
+        return g
+
+    for i in range(max(3, nbuf)):
+        step(i)
+    torch.cuda.synchronize()
+    steps, warmup = ns.steps, ns.warmup
+    g_full = capture(GRAPH_STEPS) if steps >= GRAPH_STEPS or warmup >= GRAPH_STEPS else None
+    g_rem = capture(steps % GRAPH_STEPS) if steps % GRAPH_STEPS else None
+    g_wrem = capture(warmup % GRAPH_STEPS) if warmup % GRAPH_STEPS else None
+    sampler = ClockSampler(local)
+    for _ in range(warmup // GRAPH_STEPS):
+        g_full.replay()
+    if g_wrem is not None:
+        g_wrem.replay()
+    barrier(dist)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps // GRAPH_STEPS):
+        g_full.replay()
+    if g_rem is not None:
+        g_rem.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    barrier(dist)
+    ms_per_step = max_over_ranks(dist, e0.elapsed_time(e1)) / steps
+    value = w.units_per_step * world / (ms_per_step * 1e-3)
+    achieved = w.algorithmic_bytes / (e0.elapsed_time(e1) / steps * 1e-3) / 1e9
+    peak, peak_src = measured_peaks()
+
+    e2e_steps = max(1, min(steps, 20))
+    for i in range(2):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    barrier(dist)
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    e2e_s = max_over_ranks(dist, time.perf_counter() - t0)
+    barrier(dist)
+
+    cpu = None
+    if rank == 0 and world == 1 and not ns.no_cpu_baseline:
+        rate, threads, n, passes, dt = op_workloads.cpu_rate(w, min(ns.cpu_seconds, 10.0))
+        cpu = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
+               "sample": f"{passes} passes of the CPU oracle over {n} of the step's {w.units_per_step} tokens, {dt:.1f} s"}
+    line = None
+    if rank == 0:
+        line = {
+            "metric": w.metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": w.arithmetic, "data": "synthetic",
+            "config": {"workload": f"{w.name}: {w.describe}", "sharding": "every rank runs the whole step on its own data",
+                       "l2": f"inputs rotate over {nbuf} sets; one step moves {w.algorithmic_bytes / 1e6:.0f} MB "
+                             f"(L2 is 126 MB)",
+                       "timing": f"CUDA graphs of {GRAPH_STEPS} steps, events on the launching stream"},
+            "hbm_gbs": achieved * world,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": w.algorithmic_bytes,
+                         "frac_of_nominal_8000": achieved / 8000.0},
+            "cpu_baseline": cpu,
+            "e2e": {"value": w.units_per_step * world * e2e_steps / e2e_s, "unit": "tokens/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "api": "pinned host tensors -> .to(device) -> C ABI call -> result read back"},
+            "clocks": clocks,
+            "gpu_launches": steps * w.launches_per_step,
+        }
+    if dist is not None:
+        dist.destroy_process_group()
+    return line
+
+
 # DRAM bytes per launch from the ncu capture summarised in
 # profiles/flash_scatter_bf16_fp8.md.  The capture ran the same kernel on 32768 tokens (the
 # full-size workload holds too much memory for a multi-pass capture); traffic grows in
@@ -540,7 +670,9 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=8192)
     ap.add_argument("--warmup", type=int, default=128)
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
-    ap.add_argument("--workload", choices=list(workloads.BY_NAME), default="C4")
+    ap.add_argument("--workload", choices=list(workloads.BY_NAME) + list(op_workloads.BY_NAME), default="C4",
+                    help="C1..C5: the cache-write configurations (C4 is the headline); the others are the ops "
+                         "around the write, measured the same way")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
     ap.add_argument("--tokens", type=int, default=None, help="resize the C4 batch (size studies; default 16384)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="time budget of the cpu_baseline leg")
@@ -548,11 +680,12 @@ def main() -> None:
     ns = ap.parse_args()
     if ns.steps < 1 or ns.warmup < 0:
         raise SystemExit("--steps must be >= 1 and --warmup >= 0")
+    is_op = ns.workload in op_workloads.BY_NAME
     if ns.impl == "reference":
-        run_reference_arm(ns)
+        (run_op_reference_arm if is_op else run_reference_arm)(ns)
     else:
         with LibraryChatterToStderr():
-            line = run_b200_arm(ns)
+            line = (run_op_arm if is_op else run_b200_arm)(ns)
         if line is not None:
             print(json.dumps(line), flush=True)
 

@@ -23,6 +23,19 @@ def test_reference_arm_prints_one_json_line():
     assert d["steps"] == 2 and d["warmup"] == 1 and d["gpu_launches"] == 0
 
 
+def test_reference_arm_of_the_op_workloads():
+    """The ops around the cache write have the same reference arm (CPU oracle, bounded sample per step)."""
+    for workload, metric in (("rope", "rotary_embedding_tokens_per_s"), ("gather", "gather_cache_tokens_per_s")):
+        r = subprocess.run([sys.executable, os.path.join(REPO, "bench.py"), "--impl", "reference", "--steps", "2",
+                            "--warmup", "1", "--workload", workload], capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr
+        lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
+        assert len(lines) == 1
+        d = json.loads(lines[0])
+        assert d["impl"] == "reference" and d["metric"] == metric and d["value"] > 0 and d["gpu_launches"] == 0
+        assert d["cpu_baseline"]["value"] == d["value"] and d["e2e"]["h2d_bytes_per_step"] == 0
+
+
 def test_non_zero_ranks_of_the_reference_arm_do_nothing():
     env = dict(os.environ, RANK="1", WORLD_SIZE="2")
     r = subprocess.run([sys.executable, os.path.join(REPO, "bench.py"), "--impl", "reference", "--gpus", "2",
