@@ -71,6 +71,8 @@ def lib() -> ctypes.CDLL:
         L.orc_f32_to_f16.argtypes = [f32]
         L.orc_paged_decode_attention.restype = None
         L.orc_paged_decode_attention.argtypes = [vp] * 7 + [f32, f32] + [i64] * 11 + [f32, ci, ci]
+        L.orc_paged_attention.restype = None
+        L.orc_paged_attention.argtypes = [vp] * 8 + [f32, f32] + [i64] * 11 + [f32, ci, ci, ci]
         L.orc_e4m3_to_f32.restype = f32
         L.orc_e4m3_to_f32.argtypes = [ctypes.c_uint8]
         L.orc_e5m2_to_f32.restype = f32
@@ -271,11 +273,12 @@ def rotary_embedding(positions, query, key, head_size: int, cos_sin_cache, is_ne
 
 def paged_decode_attention(query, key_cache, value_cache, block_table, seq_lens, scale: float, in_dtype: str,
                            kv_cache_dtype: str = "auto", k_descale: float = 1.0, v_descale: float = 1.0,
-                           sink=None) -> np.ndarray:
-    """fp32 ``[num_seqs, num_heads, head_size]`` result of one-token-per-sequence attention over a paged
-    cache.  ``query`` [S, Hq, D] (contiguous last dim); caches [num_blocks, block_size, Hkv, D] views with the
-    same strides, of the query's type (uint16 bit patterns / float32) or uint8 fp8 bytes; ``block_table`` int32
-    [S, max_blocks]; ``seq_lens`` int32 [S]; ``sink`` [Hq] of the query's type or None."""
+                           sink=None, cu_seqlens_q=None, causal: bool = False) -> np.ndarray:
+    """fp32 ``[tokens, num_heads, head_size]`` result of attention over a paged cache.  ``query`` [tokens, Hq, D]
+    (contiguous last dim): one token per sequence, or with ``cu_seqlens_q`` (int32 [S + 1]) the last q_len_s
+    positions of each sequence, optionally under a causal mask; caches [num_blocks, block_size, Hkv, D] views
+    with the same strides, of the query's type (uint16 bit patterns / float32) or uint8 fp8 bytes;
+    ``block_table`` int32 [S, max_blocks]; ``seq_lens`` int32 [S]; ``sink`` [Hq] of the query's type or None."""
     want = np.float32 if in_dtype == "f32" else np.uint16
     kv = KV_DTYPES[kv_cache_dtype]
     if query.dtype != want or (sink is not None and sink.dtype != want):
@@ -284,7 +287,13 @@ def paged_decode_attention(query, key_cache, value_cache, block_table, seq_lens,
         raise TypeError("cache arrays do not fit kv_cache_dtype")
     if key_cache.shape != value_cache.shape or key_cache.strides != value_cache.strides:
         raise ValueError("key_cache and value_cache must have the same shape and strides")
-    S, hq, D = query.shape
+    T, hq, D = query.shape
+    cu = None
+    if cu_seqlens_q is not None:
+        cu = np.ascontiguousarray(cu_seqlens_q, dtype=np.int32)
+        if cu.ndim != 1 or cu[0] != 0 or cu[-1] != T or np.any(np.diff(cu) < 0):
+            raise ValueError("cu_seqlens_q must run from 0 to the number of query tokens")
+    S = T if cu is None else cu.shape[0] - 1
     nb, bs, hk, Dc = key_cache.shape
     if Dc != D or hq % hk or _estrides(query)[2] != 1 or _estrides(key_cache)[3] != 1:
         raise ValueError("shapes of query and caches do not fit")
@@ -297,13 +306,13 @@ def paged_decode_attention(query, key_cache, value_cache, block_table, seq_lens,
     if block_table.size and (block_table.min() < 0 or block_table.max() >= nb):
         raise IndexError("block_table names a block outside the cache")
     sink_c = None if sink is None else np.ascontiguousarray(sink)
-    out = np.empty((S, hq, D), dtype=np.float32)
+    out = np.empty((T, hq, D), dtype=np.float32)
     qs, cs = _estrides(query), _estrides(key_cache)
-    lib().orc_paged_decode_attention(
+    lib().orc_paged_attention(
         out.ctypes.data, query.ctypes.data, key_cache.ctypes.data, value_cache.ctypes.data, block_table.ctypes.data,
-        seq_lens.ctypes.data, None if sink_c is None else sink_c.ctypes.data, float(k_descale), float(v_descale),
-        S, hq, hk, D, bs, block_table.shape[1], qs[0], qs[1], cs[0], cs[1], cs[2], float(scale),
-        IN_DTYPES[in_dtype], kv)
+        seq_lens.ctypes.data, None if cu is None else cu.ctypes.data, None if sink_c is None else sink_c.ctypes.data,
+        float(k_descale), float(v_descale), S, hq, hk, D, bs, block_table.shape[1], qs[0], qs[1], cs[0], cs[1], cs[2],
+        float(scale), int(bool(causal)), IN_DTYPES[in_dtype], kv)
     return out
 
 

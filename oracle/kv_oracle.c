@@ -23,9 +23,9 @@
  *   orc_rotary_embedding         csrc/pos_encoding_kernels.cpp:9-37 (pair update), :40-88 (loops over
  *                                heads), :174-232 (host sizes and strides); torch form
  *                                tests/ops/rotary_embedding_op.py:11-30, :85-118
- *   orc_paged_decode_attention   tests/flash_attn/test_flash_attn_varlen_func.py:27-110 (ref_paged_attn with
- *                                query_len 1, no window, not causal, optional sink column) and the decode
- *                                branch of csrc/flash_attn/flash_api.cpp:124-165 (paged, max_seqlen_q == 1)
+ *   orc_paged_attention,         tests/flash_attn/test_flash_attn_varlen_func.py:27-110 (ref_paged_attn: paged,
+ *   orc_paged_decode_attention   optional causal mask and sink column, no window) and mha_varlen_fwd,
+ *                                csrc/flash_attn/flash_api.cpp:10-176 (decode branch :124-165)
  *   element conversion           csrc/quantization/fp8/quant_utils.h:62-78
  *                                (auto: bit copy; fp8: float(src) / scale,
  *                                then cast)
@@ -453,11 +453,66 @@ static inline float cache_elem(const void* p, int64_t i, int q_dt, int kv) {
   return load_as_f32(p, i, q_dt);
 }
 
-/* out[s][h][:] = softmax_j(scale * q[s][h] . K[s][j][h/g]) @ V[s][:][h/g], j < seq_lens[s], g = Hq / Hkv,
- * K[s][j] = key_cache[block_table[s][j / bs]][j % bs] (times k_descale for an fp8 cache), V likewise.
+/* Query token t of sequence s (tokens cu_seqlens_q[s] .. cu_seqlens_q[s+1]; cu_seqlens_q == NULL means one
+ * token per sequence, token s) and head h:
+ *   out[t][h][:] = softmax_j(scale * q[t][h] . K[s][j][h/g]) @ V[s][:][h/g],  j < limit, g = Hq / Hkv,
+ *   limit = seq_lens[s], or with `causal` seq_lens[s] - q_len_s + i + 1 for the i-th query token of the sequence
+ *   (the query tokens are the LAST q_len_s positions of the sequence, tests/flash_attn/
+ *   test_flash_attn_varlen_func.py:79-80 of the reference),
+ *   K[s][j] = key_cache[block_table[s][j / bs]][j % bs] (times k_descale for an fp8 cache), V likewise.
  * A sink adds one more logit sink[h] to the softmax denominator only.  Everything is accumulated in
  * double and written as fp32: this is the ideal result, the kernels are held to a tolerance around it.
- * Strides in elements.  Sequences of length 0 give zeros. */
+ * Strides in elements.  Rows with nothing to attend to give zeros. */
+void orc_paged_attention(float* out, const void* query, const void* key_cache, const void* value_cache,
+                         const int32_t* block_table, const int32_t* seq_lens, const int32_t* cu_seqlens_q,
+                         const void* sink, float k_descale, float v_descale, int64_t num_seqs, int64_t num_heads,
+                         int64_t num_kv_heads, int64_t head_size, int64_t block_size, int64_t block_table_stride,
+                         int64_t query_stride_t, int64_t query_stride_h, int64_t block_stride, int64_t page_stride,
+                         int64_t head_stride, float scale, int causal, int q_dt, int kv) {
+  const int64_t group = num_heads / num_kv_heads;
+#pragma omp parallel for collapse(2) schedule(dynamic)
+  for (int64_t s = 0; s < num_seqs; ++s) {
+    for (int64_t h = 0; h < num_heads; ++h) {
+      const int64_t t0 = cu_seqlens_q ? cu_seqlens_q[s] : s;
+      const int64_t q_len = cu_seqlens_q ? cu_seqlens_q[s + 1] - cu_seqlens_q[s] : 1;
+      const int64_t kvh = h / group;
+      for (int64_t i = 0; i < q_len; ++i) {
+        const int64_t t = t0 + i;
+        int64_t n = seq_lens[s];
+        if (causal) n = n - q_len + i + 1;
+        float* o = out + (t * num_heads + h) * head_size;
+        for (int64_t d = 0; d < head_size; ++d) o[d] = 0.0f;
+        if (n <= 0) continue;
+        double* logit = (double*)malloc((size_t)n * sizeof(double));
+        double* acc = (double*)calloc((size_t)head_size, sizeof(double));
+        double mx = sink ? (double)load_as_f32(sink, h, q_dt) : -INFINITY;
+        for (int64_t j = 0; j < n; ++j) {
+          const int64_t blk = block_table[s * block_table_stride + j / block_size];
+          const int64_t base = blk * block_stride + (j % block_size) * page_stride + kvh * head_stride;
+          double dot = 0.0;
+          for (int64_t d = 0; d < head_size; ++d)
+            dot += (double)load_as_f32(query, t * query_stride_t + h * query_stride_h + d, q_dt) *
+                   (double)cache_elem(key_cache, base + d, q_dt, kv);
+          logit[j] = dot * (double)scale * (double)k_descale;
+          if (logit[j] > mx) mx = logit[j];
+        }
+        double denom = sink ? exp((double)load_as_f32(sink, h, q_dt) - mx) : 0.0;
+        for (int64_t j = 0; j < n; ++j) {
+          const double p = exp(logit[j] - mx);
+          denom += p;
+          const int64_t blk = block_table[s * block_table_stride + j / block_size];
+          const int64_t base = blk * block_stride + (j % block_size) * page_stride + kvh * head_stride;
+          for (int64_t d = 0; d < head_size; ++d) acc[d] += p * (double)cache_elem(value_cache, base + d, q_dt, kv);
+        }
+        for (int64_t d = 0; d < head_size; ++d) o[d] = (float)(acc[d] / denom * (double)v_descale);
+        free(logit);
+        free(acc);
+      }
+    }
+  }
+}
+
+/* One query token per sequence: the decode case. */
 void orc_paged_decode_attention(float* out, const void* query, const void* key_cache, const void* value_cache,
                                 const int32_t* block_table, const int32_t* seq_lens, const void* sink,
                                 float k_descale, float v_descale, int64_t num_seqs, int64_t num_heads,
@@ -465,41 +520,9 @@ void orc_paged_decode_attention(float* out, const void* query, const void* key_c
                                 int64_t block_table_stride, int64_t query_stride_t, int64_t query_stride_h,
                                 int64_t block_stride, int64_t page_stride, int64_t head_stride, float scale,
                                 int q_dt, int kv) {
-  const int64_t group = num_heads / num_kv_heads;
-#pragma omp parallel for collapse(2) schedule(dynamic)
-  for (int64_t s = 0; s < num_seqs; ++s) {
-    for (int64_t h = 0; h < num_heads; ++h) {
-      const int64_t n = seq_lens[s];
-      const int64_t kvh = h / group;
-      float* o = out + (s * num_heads + h) * head_size;
-      for (int64_t d = 0; d < head_size; ++d) o[d] = 0.0f;
-      if (n <= 0) continue;
-      double* logit = (double*)malloc((size_t)n * sizeof(double));
-      double* acc = (double*)calloc((size_t)head_size, sizeof(double));
-      double mx = sink ? (double)load_as_f32(sink, h, q_dt) : -INFINITY;
-      for (int64_t j = 0; j < n; ++j) {
-        const int64_t blk = block_table[s * block_table_stride + j / block_size];
-        const int64_t base = blk * block_stride + (j % block_size) * page_stride + kvh * head_stride;
-        double dot = 0.0;
-        for (int64_t d = 0; d < head_size; ++d)
-          dot += (double)load_as_f32(query, s * query_stride_t + h * query_stride_h + d, q_dt) *
-                 (double)cache_elem(key_cache, base + d, q_dt, kv);
-        logit[j] = dot * (double)scale * (double)k_descale;
-        if (logit[j] > mx) mx = logit[j];
-      }
-      double denom = sink ? exp((double)load_as_f32(sink, h, q_dt) - mx) : 0.0;
-      for (int64_t j = 0; j < n; ++j) {
-        const double p = exp(logit[j] - mx);
-        denom += p;
-        const int64_t blk = block_table[s * block_table_stride + j / block_size];
-        const int64_t base = blk * block_stride + (j % block_size) * page_stride + kvh * head_stride;
-        for (int64_t d = 0; d < head_size; ++d) acc[d] += p * (double)cache_elem(value_cache, base + d, q_dt, kv);
-      }
-      for (int64_t d = 0; d < head_size; ++d) o[d] = (float)(acc[d] / denom * (double)v_descale);
-      free(logit);
-      free(acc);
-    }
-  }
+  orc_paged_attention(out, query, key_cache, value_cache, block_table, seq_lens, NULL, sink, k_descale, v_descale,
+                      num_seqs, num_heads, num_kv_heads, head_size, block_size, block_table_stride, query_stride_t,
+                      query_stride_h, block_stride, page_stride, head_stride, scale, 0, q_dt, kv);
 }
 
 int orc_max_threads(void) {

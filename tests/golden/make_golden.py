@@ -279,7 +279,7 @@ def make_rope_case(RotaryEmbedding, dtype: str, is_neox: bool, head_size: int, r
 
 def make_decode_attn_case(ref_paged_attn, dtype: str, num_heads: int, num_kv_heads: int, head_size: int,
                           kv_lens: list, block_size: int, num_blocks: int, with_sink: bool, kv_cache_dtype: str,
-                          descale: float, seed: int) -> dict:
+                          descale: float, seed: int, query_lens: list | None = None, causal: bool = False) -> dict:
     """Inputs as in test_decode_with_paged_kv of the reference (tests/flash_attn/test_flash_attn_varlen_func.py:
     274-372: one query token per sequence, randn query and caches, randint block tables, optional randn sink);
     expected = its ref_paged_attn on the CPU.  For an fp8 cache the caches are first cast to fp8; the reference
@@ -287,7 +287,8 @@ def make_decode_attn_case(ref_paged_attn, dtype: str, num_heads: int, num_kv_hea
     tdt = DT[dtype]
     torch.manual_seed(seed)
     num_seqs = len(kv_lens)
-    query = torch.randn(num_seqs, num_heads, head_size, dtype=tdt)
+    query_lens = query_lens or [1] * num_seqs
+    query = torch.randn(sum(query_lens), num_heads, head_size, dtype=tdt)
     key_cache = torch.randn(num_blocks, block_size, num_kv_heads, head_size, dtype=tdt)
     value_cache = torch.randn_like(key_cache)
     max_blocks = (max(kv_lens) + block_size - 1) // block_size
@@ -301,12 +302,12 @@ def make_decode_attn_case(ref_paged_attn, dtype: str, num_heads: int, num_kv_hea
         assert torch.equal(key_cache.float(), stored_k.float() * descale)  # the 16-bit image is exact
     scale = head_size ** -0.5
     expected = ref_paged_attn(query=query.clone(), key_cache=key_cache, value_cache=value_cache,
-                              query_lens=[1] * num_seqs, kv_lens=kv_lens, block_tables=block_tables, scale=scale,
-                              casual=False, is_paged=True, sink=sink, window_size_left=-1, window_size_right=-1)
+                              query_lens=query_lens, kv_lens=kv_lens, block_tables=block_tables, scale=scale,
+                              casual=causal, is_paged=True, sink=sink, window_size_left=-1, window_size_right=-1)
     d = dict(op="decode_attn", dtype=dtype, kv_cache_dtype=kv_cache_dtype, query=bits(query),
              key_cache=bits(stored_k), value_cache=bits(stored_v), block_tables=block_tables.numpy(),
-             kv_lens=np.array(kv_lens, dtype=np.int32), scale=np.float32(scale), descale=np.float32(descale),
-             expected=bits(expected))
+             kv_lens=np.array(kv_lens, dtype=np.int32), query_lens=np.array(query_lens, dtype=np.int32),
+             causal=np.bool_(causal), scale=np.float32(scale), descale=np.float32(descale), expected=bits(expected))
     if with_sink:
         d["sink"] = bits(sink)
     return d
@@ -421,6 +422,20 @@ def main() -> None:
         name = "decode_attn_%s_%s_Hq%d_Hk%d_D%d_bs%d%s" % (dtype, kv, hq, hk, D, bs, "_sink" if sink else "")
         extra.append((name, lambda a=(dtype, hq, hk, D, lens, bs, nb, sink, kv, descale, ai):
                       make_decode_attn_case(ref_paged_attn, *a)))
+    # variable query lengths: the sequence list of the reference's test_varlen_with_paged_kv
+    # (tests/flash_attn/test_flash_attn_varlen_func.py:121: (1, 1328), (5, 18), (129, 463)), shortened, with and
+    # without the causal mask and the sink, plus an fp8 cache
+    for dtype, hq, hk, D, lens, bs, nb, sink, kv, descale, causal in (
+            ("bfloat16", 8, 2, 128, [(1, 328), (5, 18), (129, 263)], 16, 24, False, "auto", 1.0, True),
+            ("half", 4, 4, 64, [(1, 328), (5, 18), (129, 263)], 16, 24, True, "auto", 1.0, True),
+            ("bfloat16", 10, 2, 64, [(7, 7), (33, 200), (1, 1)], 16, 16, True, "auto", 1.0, False),
+            ("half", 16, 1, 128, [(40, 100), (3, 64)], 32, 8, False, "auto", 1.0, True),
+            ("bfloat16", 8, 2, 128, [(1, 328), (5, 18), (129, 263)], 16, 24, True, "fp8", 0.5, True)):
+        ai += 1
+        name = "varlen_attn_%s_%s_Hq%d_Hk%d_D%d_bs%d%s%s" % (dtype, kv, hq, hk, D, bs, "_sink" if sink else "",
+                                                         "_causal" if causal else "")
+        extra.append((name, lambda a=(dtype, hq, hk, D, [k for _, k in lens], bs, nb, sink, kv, descale, ai,
+                                       [q for q, _ in lens], causal): make_decode_attn_case(ref_paged_attn, *a)))
     for name, data in extra:
         names.append(name)
         if wanted(name):

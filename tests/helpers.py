@@ -21,7 +21,8 @@ def golden_files(kind: str = "kv") -> list[str]:
     with open(os.path.join(GOLDEN_DIR, "MANIFEST.txt")) as f:
         names = [ln.strip() for ln in f if ln.strip() and not ln.startswith("#")]
     prefixes = {"kv": ("flash_", "paged_"), "mla": ("mla_",), "gather": ("gather_",), "quant": ("quant_",),
-                "rope": ("rope_",), "decode_attn": ("decode_attn_",)}[kind]
+                "rope": ("rope_",), "decode_attn": ("decode_attn_",),
+                "varlen_attn": ("varlen_attn_",)}[kind]
     return [n for n in names if n.startswith(prefixes)]
 
 
@@ -83,7 +84,8 @@ class RopeCase:
 
 
 class DecodeAttnCase:
-    """A paged decode-attention fixture: one query token per sequence, caches [nb, bs, Hkv, D]."""
+    """A paged attention fixture: query tokens (one per sequence in the decode fixtures, query_lens otherwise),
+    caches [nb, bs, Hkv, D]."""
 
     def __init__(self, fname: str):
         z = np.load(os.path.join(GOLDEN_DIR, fname))
@@ -99,6 +101,10 @@ class DecodeAttnCase:
         self.descale = float(z["descale"])
         self.sink = from_bits(z["sink"], self.dtype) if "sink" in z.files else None
         self.expected = from_bits(z["expected"], self.dtype)
+        self.query_lens = torch.from_numpy(z["query_lens"].astype(np.int32))
+        self.causal = bool(z["causal"])
+        self.cu_seqlens_q = torch.cat([torch.zeros(1, dtype=torch.int32),
+                                       torch.cumsum(self.query_lens, 0).to(torch.int32)])
 
 
 # The reference's own tolerance for this op (tests/flash_attn/test_flash_attn_varlen_func.py:265, :386).
