@@ -330,6 +330,37 @@ KVC_API int kvc_rotary_embedding_and_cache_flash(
  */
 KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads,
                                                  int64_t head_size, int64_t max_seq_len, int q_dtype, int kv_dtype);
+
+/*
+ * The same over several query tokens per sequence (a chunk of a prefill, speculative tokens): the paged case of
+ * mha_varlen_fwd with max_seqlen_q > 1 and no window (csrc/flash_attn/flash_api.cpp:105-123 routes it to the
+ * reference's chunked-prefill kernel).
+ *
+ *   query, out     [total_q, num_heads, head_size]; sequence s owns tokens cu_seqlens_q[s] .. cu_seqlens_q[s+1]
+ *   cu_seqlens_q   int32 [num_seqs + 1] on the device; NULL means one token per sequence (the decode call above)
+ *   max_seqlen_q   host-side upper bound of the query lengths (sizes the grid)
+ *   causal         the query tokens are the last q_len positions of their sequence; with causal != 0 the i-th
+ *                  of them sees the first seq_lens[s] - q_len + i + 1 cached tokens, else all seq_lens[s]
+ *                  (tests/flash_attn/test_flash_attn_varlen_func.py:79-80, :99-100 of the reference).  A row that
+ *                  sees no token gives zeros.
+ *
+ * Built on the decode kernel: 16 (token, head) rows of one kv head per CTA, each CTA streaming the cached
+ * tokens its rows may see.  That is the right shape for short query runs; a long prefill re-reads the keys and
+ * values (from L2) once per 16 rows and runs far below a tensor-core-bound prefill kernel, which this library
+ * does not have.  At most 65535 sequences per call.
+ */
+KVC_API int64_t kvc_paged_attention_workspace_bytes(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q,
+                                                    int64_t num_heads, int64_t num_kv_heads, int64_t head_size,
+                                                    int64_t max_seq_len, int q_dtype, int kv_dtype);
+KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_cache, const void* value_cache,
+                                const int32_t* block_table, const int32_t* seq_lens, const int32_t* cu_seqlens_q,
+                                const void* sink, const float* k_descale, const float* v_descale, void* workspace,
+                                int64_t workspace_bytes, int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q,
+                                int64_t num_heads, int64_t num_kv_heads, int64_t head_size, int64_t block_size,
+                                int64_t block_table_stride, int64_t max_seq_len, int64_t query_stride_t,
+                                int64_t query_stride_h, int64_t out_stride_t, int64_t out_stride_h,
+                                int64_t block_stride, int64_t page_stride, int64_t head_stride, float softmax_scale,
+                                int causal, int q_dtype, int kv_dtype, void* stream);
 KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void* key_cache, const void* value_cache,
                                        const int32_t* block_table, const int32_t* seq_lens, const void* sink,
                                        const float* k_descale, const float* v_descale, void* workspace,

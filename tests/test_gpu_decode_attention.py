@@ -279,10 +279,13 @@ def test_attention_ops_pass_opcheck_and_refuse_what_is_not_built(cuda_device):
                                   softmax_scale=0.125, block_table=bt, s_aux=sk, k_descale=dscalar(0.05, dev),
                                   v_descale=dscalar(0.05, dev), kv_cache_dtype="fp8_e4m3")
     assert H.same_bytes(out2.cpu(), out.cpu())
-    # what the reference routes to its chunked-prefill kernel is refused, loudly
-    with pytest.raises(RuntimeError, match="only the paged decode case"):
-        flash_attn_varlen_func(q, kc, vc, 2, cu_q, 200, seqused_k=lens, softmax_scale=0.125, block_table=bt)
-    with pytest.raises(RuntimeError, match="only the paged decode case"):
+    # a larger bound on the query length changes nothing for one-token sequences
+    out3 = flash_attn_varlen_func(q, kc, vc, 2, cu_q, 200, seqused_k=lens, softmax_scale=0.125, block_table=bt,
+                                  causal=True)
+    out4 = flash_attn_varlen_func(q, kc, vc, 1, cu_q, 200, seqused_k=lens, softmax_scale=0.125, block_table=bt)
+    torch.testing.assert_close(out3.float(), out4.float(), **TOL)
+    # local attention is refused, loudly
+    with pytest.raises(RuntimeError, match="without a sliding window"):
         flash_attn_varlen_func(q, kc, vc, 1, cu_q, 200, seqused_k=lens, softmax_scale=0.125, block_table=bt,
                                window_size=[127, -1])
     with pytest.raises(RuntimeError, match="page_table must have dtype torch.int32"):
@@ -309,3 +312,96 @@ def test_decode_attention_in_a_cuda_graph(cuda_device):
     assert H.same_bytes(captured.cpu(), eager.cpu())
     want = torch_views.run_paged_decode_attention(query, kc.cpu(), vc.cpu(), bt.cpu(), lens.cpu(), 0.09)
     torch.testing.assert_close(captured.cpu().float(), want, **TOL)
+
+
+# ------------------------------------------------------------------------------------ several query tokens per sequence
+def cu_of(lens):
+    return torch.cat([torch.zeros(1, dtype=torch.int32), torch.cumsum(torch.tensor(lens), 0).to(torch.int32)])
+
+
+@pytest.mark.parametrize("fname", H.golden_files("varlen_attn"))
+@pytest.mark.parametrize("face", ["cabi", "interface"])
+def test_varlen_attention_golden(fname, face, cuda_device):
+    """Fixtures from the reference's ref_paged_attn with query lengths (1, 5, 129), (7, 33, 1), (40, 3)."""
+    dev = cuda_device
+    c = H.DecodeAttnCase(fname)
+    S = c.kv_lens.shape[0]
+    ds = dscalar(c.descale, dev)
+    if face == "cabi":
+        out = cabi.paged_attention(c.query.to(dev), c.key_cache.to(dev), c.value_cache.to(dev), c.block_tables.to(dev),
+                                   c.kv_lens.to(dev), c.cu_seqlens_q.to(dev), int(c.query_lens.max()), c.scale,
+                                   int(c.kv_lens.max()), c.causal, c.kv_cache_dtype, ds, ds,
+                                   None if c.sink is None else c.sink.to(dev))
+    else:
+        kw = dict(k_descale=ds.expand(S, c.key_cache.shape[2]), v_descale=ds.expand(S, c.key_cache.shape[2])) \
+            if c.kv_cache_dtype != "auto" else {}
+        out = flash_attn_varlen_func(c.query.to(dev), c.key_cache.to(dev), c.value_cache.to(dev),
+                                     int(c.query_lens.max()), c.cu_seqlens_q.to(dev), int(c.kv_lens.max()),
+                                     seqused_k=c.kv_lens.to(dev), softmax_scale=c.scale, causal=c.causal,
+                                     block_table=c.block_tables.to(dev), window_size=(-1, -1),
+                                     s_aux=None if c.sink is None else c.sink.to(dev), **kw)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.cpu().float(), c.expected.float(), **TOL)
+
+
+@pytest.mark.parametrize("num_heads", [(4, 4), (8, 2), (10, 2), (16, 1)])
+@pytest.mark.parametrize("head_size", [64, 128, 192, 256])
+@pytest.mark.parametrize("causal", [False, True])
+def test_varlen_attention_reference_matrix(num_heads, head_size, causal, cuda_device):
+    """The sequence list of the reference's test_varlen_with_paged_kv: (1, 1328), (5, 18), (129, 463), block size
+    64, over its head pairs and head sizes, with and without the causal mask; type and sink alternate."""
+    dev = cuda_device
+    hq, hk = num_heads
+    q_lens, kv_lens = [1, 5, 129], [1328, 18, 463]
+    idx = hq + head_size // 64 + int(causal)
+    dtype = torch.bfloat16 if idx % 2 else torch.float16
+    torch.manual_seed(42)
+    query = torch.randn(sum(q_lens), hq, head_size).to(dtype)
+    _, kc, vc, bt, lens, sk = make_case(dtype, hq, hk, head_size, kv_lens, 64, 2048, bool((idx // 2) % 2), seed=43)
+    cu = cu_of(q_lens)
+    scale = head_size ** -0.5
+    out = cabi.paged_attention(query.to(dev), kc.to(dev), vc.to(dev), bt.to(dev), lens.to(dev), cu.to(dev), 129, scale,
+                               1328, causal, sink=None if sk is None else sk.to(dev))
+    torch.cuda.synchronize()
+    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, scale, sink=sk, cu_seqlens_q=cu,
+                                                  causal=causal)
+    torch.testing.assert_close(out.cpu().float(), want, **TOL)
+
+
+@pytest.mark.parametrize("kv,descale", [("auto", 1.0), ("fp8", 0.04), ("fp8_e5m2", 0.002)])
+def test_varlen_attention_mixed_batch_and_edges(kv, descale, cuda_device):
+    """A batch as a serving step sees it: decodes, a prefill chunk that starts mid-sequence, a whole short
+    prompt, a query run longer than its cached sequence (its first tokens see nothing: zeros), an empty
+    sequence; 5 query heads per kv head, so rows of different tokens share a 16-row tile."""
+    dev = cuda_device
+    hq, hk, D, bs, nb = 10, 2, 128, 16, 200
+    q_lens = [1, 300, 40, 1, 9, 0, 1]
+    kv_lens = [700, 1000, 40, 1, 5, 0, 64]
+    dtype = torch.bfloat16
+    torch.manual_seed(50)
+    query = torch.randn(sum(q_lens), hq, D).to(dtype)
+    _, kc, vc, bt, lens, sk = make_case(dtype, hq, hk, D, kv_lens, bs, nb, True, seed=51, kv=kv, descale=descale)
+    cu = cu_of(q_lens)
+    kcd, vcd = (kc.view(torch.uint8), vc.view(torch.uint8)) if kv != "auto" else (kc, vc)
+    out = cabi.paged_attention(query.to(dev), kcd.to(dev), vcd.to(dev), bt.to(dev), lens.to(dev), cu.to(dev), 300, 0.09,
+                               1000, True, kv, dscalar(descale, dev), dscalar(descale, dev), sk.to(dev))
+    torch.cuda.synchronize()
+    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, 0.09, kv, descale, descale, sk, cu, True)
+    torch.testing.assert_close(out.cpu().float(), want, **TOL)
+    first_of_run5 = int(cu[4])
+    assert torch.count_nonzero(out[first_of_run5:first_of_run5 + 4]) == 0  # 9 queries over 5 tokens: 4 see nothing
+
+
+def test_varlen_attention_long_chunk(cuda_device):
+    """A 1024-token chunk over 3072 cached tokens (slow path of a long prefill, still exact)."""
+    dev = cuda_device
+    hq, hk, D = 8, 1, 128
+    torch.manual_seed(60)
+    query = torch.randn(1024, hq, D).to(torch.float16)
+    _, kc, vc, bt, lens, _ = make_case(torch.float16, hq, hk, D, [3072], 64, 64, False, seed=61)
+    cu = cu_of([1024])
+    out = cabi.paged_attention(query.to(dev), kc.to(dev), vc.to(dev), bt.to(dev), lens.to(dev), cu.to(dev), 1024,
+                               D ** -0.5, 3072, True)
+    torch.cuda.synchronize()
+    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, D ** -0.5, cu_seqlens_q=cu, causal=True)
+    torch.testing.assert_close(out.cpu().float(), want, **TOL)

@@ -1,8 +1,8 @@
 // Torch-facing launcher of the paged decode attention, registered under `_vllm_fa2_C` like the
 // reference's attention op.  Counterpart in the reference: mha_varlen_fwd, csrc/flash_attn/flash_api.cpp:10-176
-// (decode branch :124-165) and its schema :179-193.  Only that decode branch is built here: one query
-// token per sequence, paged keys/values, no sliding window.  The other branch of the reference (chunked
-// prefill) raises an error instead of computing anything.
+// (decode branch :124-165) and its schema :179-193.  The paged case without a sliding window is built: the
+// decode branch (one query token per sequence) and, on the same kernel, several query tokens per sequence
+// with the causal mask.  The non-paged and local-attention cases raise an error instead of computing anything.
 #include <ATen/core/Tensor.h>
 #include <ATen/ops/empty.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -20,7 +20,8 @@ namespace {
 void paged_decode_impl(const char* op, const at::Tensor& q, const at::Tensor& k_cache, const at::Tensor& v_cache,
                        at::Tensor& out, const at::Tensor& seqused_k, const at::Tensor& block_table,
                        int64_t max_seqlen_k, double softmax_scale, const std::optional<at::Tensor>& sink, int kv,
-                       const std::optional<at::Tensor>& k_descale, const std::optional<at::Tensor>& v_descale) {
+                       const std::optional<at::Tensor>& k_descale, const std::optional<at::Tensor>& v_descale,
+                       const std::optional<at::Tensor>& cu_seqlens_q, int64_t max_seqlen_q, bool causal) {
   TORCH_CHECK(q.is_cuda(), op, ": query must be a CUDA tensor (this build has no CPU path)");
   const auto dev = q.device();
   const auto qt = q.scalar_type();
@@ -38,9 +39,19 @@ void paged_decode_impl(const char* op, const at::Tensor& q, const at::Tensor& k_
               kv == KVC_KV_AUTO ? "query and key must have the same dtype" : "cache dtype does not fit kv_cache_dtype");
   TORCH_CHECK(block_table.scalar_type() == at::kInt, "page_table must have dtype torch.int32");
   TORCH_CHECK(block_table.dim() == 2 && block_table.stride(-1) == 1, "page_table must have contiguous last dimension");
-  TORCH_CHECK(seqused_k.scalar_type() == at::kInt && seqused_k.is_contiguous() && seqused_k.numel() == q.size(0), op,
+  const int64_t num_seqs = seqused_k.numel();
+  TORCH_CHECK(seqused_k.scalar_type() == at::kInt && seqused_k.is_contiguous() && seqused_k.dim() == 1, op,
               ": seqused_k must be a contiguous int32 vector with one entry per sequence");
-  TORCH_CHECK(block_table.size(0) == q.size(0), op, ": block_table must have one row per sequence");
+  TORCH_CHECK(block_table.size(0) == num_seqs, op, ": block_table must have one row per sequence");
+  const int32_t* cu_q = nullptr;
+  if (cu_seqlens_q.has_value()) {
+    TORCH_CHECK(cu_seqlens_q->device() == dev && cu_seqlens_q->scalar_type() == at::kInt &&
+                    cu_seqlens_q->is_contiguous() && cu_seqlens_q->numel() == num_seqs + 1,
+                "cu_seqlens_q must have dtype torch.int32 and one entry per sequence plus one");
+    cu_q = cu_seqlens_q->data_ptr<int32_t>();
+  } else {
+    TORCH_CHECK(q.size(0) == num_seqs && max_seqlen_q == 1, op, ": without cu_seqlens_q every sequence has one query token");
+  }
   TORCH_CHECK(out.scalar_type() == qt && out.sizes() == q.sizes() && out.stride(-1) == 1, op,
               ": out must have query's shape and dtype");
   const void* sink_ptr = nullptr;
@@ -62,16 +73,17 @@ void paged_decode_impl(const char* op, const at::Tensor& q, const at::Tensor& k_
   }
   const int in = vllm::kvc_in_dtype_of(qt);
   const c10::cuda::CUDAGuard guard(dev);
-  const int64_t ws_bytes =
-      kvc_paged_decode_workspace_bytes(q.size(0), q.size(1), k_cache.size(2), q.size(2), max_seqlen_k, in, kv);
+  const int64_t ws_bytes = kvc_paged_attention_workspace_bytes(num_seqs, q.size(0), max_seqlen_q, q.size(1),
+                                                               k_cache.size(2), q.size(2), max_seqlen_k, in, kv);
   at::Tensor ws;
   if (ws_bytes > 0) ws = at::empty({ws_bytes}, q.options().dtype(at::kByte));
-  const int rc = kvc_paged_decode_attention(
+  const int rc = kvc_paged_attention(
       out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr<int32_t>(),
-      seqused_k.data_ptr<int32_t>(), sink_ptr, kd, vd, ws_bytes > 0 ? ws.data_ptr() : nullptr, ws_bytes, q.size(0),
-      q.size(1), k_cache.size(2), q.size(2), k_cache.size(1), block_table.stride(0), max_seqlen_k, q.stride(0),
-      q.stride(1), out.stride(0), out.stride(1), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2),
-      static_cast<float>(softmax_scale), in, kv, c10::cuda::getCurrentCUDAStream().stream());
+      seqused_k.data_ptr<int32_t>(), cu_q, sink_ptr, kd, vd, ws_bytes > 0 ? ws.data_ptr() : nullptr, ws_bytes, num_seqs,
+      q.size(0), max_seqlen_q, q.size(1), k_cache.size(2), q.size(2), k_cache.size(1), block_table.stride(0),
+      max_seqlen_k, q.stride(0), q.stride(1), out.stride(0), out.stride(1), k_cache.stride(0), k_cache.stride(1),
+      k_cache.stride(2), static_cast<float>(softmax_scale), causal ? 1 : 0, in, kv,
+      c10::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == KVC_OK, op, ": ", kvc_last_error());
 }
 
@@ -88,21 +100,18 @@ std::vector<at::Tensor> mha_varlen_fwd(const at::Tensor& q, const at::Tensor& k,
   constexpr const char* op = "varlen_fwd";
   (void)cu_seqlens_k;
   (void)zero_tensors;
-  (void)is_causal;  // a single query token sees every cached token either way
   (void)gen_;
   const bool is_local = window_size_left != -1 || window_size_right != -1;
-  TORCH_CHECK(block_table_.has_value() && seqused_k.has_value() && max_seqlen_q == 1 && !is_local, op,
-              ": only the paged decode case is built (block_table and seqused_k given, max_seqlen_q == 1, no "
-              "sliding window); the chunked-prefill case of the reference is not");
+  TORCH_CHECK(block_table_.has_value() && seqused_k.has_value() && !is_local, op,
+              ": only the paged case without a sliding window is built (block_table and seqused_k given); the "
+              "non-paged and the local-attention cases of the reference are not");
   TORCH_CHECK(!alibi_slopes_.has_value() && !leftpad_k_.has_value() && softcap == 0.0 && p_dropout == 0.0 &&
                   !return_softmax,
               op, ": alibi_slopes, leftpad_k, softcap, dropout and return_softmax are not supported");
   TORCH_CHECK(cu_seqlens_q.scalar_type() == at::kInt, "cu_seqlens_q must have dtype torch.int32");
-  TORCH_CHECK(cu_seqlens_q.numel() == q.size(0) + 1, op,
-              ": with max_seqlen_q == 1 every sequence has exactly one query token");
   at::Tensor out = out_.has_value() ? *out_ : at::empty(q.sizes(), q.options());
   paged_decode_impl(op, q, k, v, out, *seqused_k, *block_table_, max_seqlen_k, softmax_scale, softmax_sink_,
-                    KVC_KV_AUTO, std::nullopt, std::nullopt);
+                    KVC_KV_AUTO, std::nullopt, std::nullopt, cu_seqlens_q, max_seqlen_q, is_causal);
   return {out, at::empty({0}, q.options().dtype(at::kFloat))};
 }
 
@@ -128,9 +137,11 @@ void paged_decode_attention(const at::Tensor& q, const at::Tensor& k_cache, cons
                             const at::Tensor& seqused_k, const at::Tensor& block_table, int64_t max_seqlen_k,
                             double softmax_scale, std::optional<at::Tensor> softmax_sink,
                             const std::string& kv_cache_dtype, std::optional<at::Tensor> k_descale,
-                            std::optional<at::Tensor> v_descale) {
+                            std::optional<at::Tensor> v_descale, std::optional<at::Tensor> cu_seqlens_q,
+                            int64_t max_seqlen_q, bool is_causal) {
   paged_decode_impl("paged_decode_attention", q, k_cache, v_cache, out, seqused_k, block_table, max_seqlen_k,
-                    softmax_scale, softmax_sink, vllm::kvc_kv_dtype_of(kv_cache_dtype), k_descale, v_descale);
+                    softmax_scale, softmax_sink, vllm::kvc_kv_dtype_of(kv_cache_dtype), k_descale, v_descale,
+                    cu_seqlens_q, max_seqlen_q, is_causal);
 }
 
 }  // namespace
@@ -149,7 +160,8 @@ KVC_TORCH_LIBRARY(_vllm_fa2_C, m) {
   m.def(
       "paged_decode_attention(Tensor q, Tensor k_cache, Tensor v_cache, Tensor! out, Tensor seqused_k, "
       "Tensor block_table, int max_seqlen_k, float softmax_scale, Tensor? softmax_sink, str kv_cache_dtype, "
-      "Tensor? k_descale, Tensor? v_descale) -> ()");
+      "Tensor? k_descale, Tensor? v_descale, Tensor? cu_seqlens_q=None, int max_seqlen_q=1, bool is_causal=False) "
+      "-> ()");
 }
 
 KVC_TORCH_LIBRARY_IMPL(_vllm_fa2_C, Meta, m) { m.impl("varlen_fwd", &mha_varlen_fwd_meta); }

@@ -112,6 +112,7 @@ struct DecodeParams {
   const void* value_cache;
   const int32_t* block_table;  // [S, block_table_stride]
   const int32_t* seq_lens;     // [S]
+  const int32_t* cu_seqlens_q; // [S + 1] first query token of each sequence, or NULL: one token per sequence
   const void* sink;            // [Hq] of the query's type, or NULL
   const float* k_descale;      // device scalars, or NULL for 1
   const float* v_descale;
@@ -120,10 +121,13 @@ struct DecodeParams {
   int64_t query_stride_t, query_stride_h, out_stride_t, out_stride_h;  // elements
   int64_t block_stride, page_stride, head_stride;                      // elements of the cache
   int64_t block_table_stride;
-  int32_t num_heads, num_kv_heads, group, row_tiles;  // group = Hq / Hkv; row_tiles = ceil(group / 16)
+  // group = Hq / Hkv; a (sequence, kv head) has q_len * group query rows, token-major: row R is token R / group,
+  // head R % group of the group; row_tiles = ceil(max_seqlen_q * group / 16)
+  int32_t num_heads, num_kv_heads, group, row_tiles;
   int32_t block_size;
   int32_t bs_shift;  // log2(block_size), or -1
   int32_t num_splits, tiles_per_split;
+  int32_t causal;  // query token i of q_len sees the first seq_len - q_len + i + 1 cached tokens
   float softmax_scale;
 };
 
@@ -168,6 +172,9 @@ struct DecodeCfg {
   // the final merge reuses the ring: 4 warps x (16 x D fp32 + 32 floats of statistics)
   static_assert(4 * (kRows * D + 2 * kRows) * (int)sizeof(float) <= kStages * 2 * kTileBytes, "merge buffer fits");
   static_assert(D % 64 == 0 && D <= 256, "head sizes 64, 128, 192, 256");
+  // CTAs per SM the register allocation has to leave room for: the 64-token fp8 instance of D = 128 lives on
+  // four (43 KB of shared memory each); it measured 107 us with four and 123 us with three on the 64 x 4096 batch.
+  static constexpr int kMinCtasPerSm = (KV != KVC_KV_AUTO && D == 128 && !WIDE) ? 4 : 1;
 };
 
 // Within every group of 16 head dimensions the fp8 path works on a permuted order: an ldmatrix of fp8 rows
@@ -178,7 +185,8 @@ struct DecodeCfg {
 __device__ __forceinline__ int fp8_q_word_position(int w) { return (w & 1) * 4 + (w >> 1); }
 
 template <typename TQ, int KV, int D, bool WIDE>
-__global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kAttnThreads, DecodeCfg<TQ, KV, D, WIDE>::kMinCtasPerSm)
+paged_decode_kernel(const DecodeParams p) {
   using Cfg = DecodeCfg<TQ, KV, D, WIDE>;
   using T16 = typename Cfg::T16;
   constexpr bool kFp8 = KV != KVC_KV_AUTO;
@@ -198,26 +206,40 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;  // accumulator row (and row + 8) and column pair of this lane
-  const int seq = blockIdx.x;
-  const int kvh = blockIdx.y / p.row_tiles, row_tile = blockIdx.y - kvh * p.row_tiles;
+  const int seq = blockIdx.y;
+  const int kvh = blockIdx.x / p.row_tiles, row_tile = blockIdx.x - kvh * p.row_tiles;
   const int split = blockIdx.z;
-  const int row0 = row_tile * kRows;             // first group-local query row of this CTA
-  const int rows = min(kRows, p.group - row0);   // valid rows
-  const int head0 = kvh * p.group + row0;        // first query head of this CTA
+  const int row0 = row_tile * kRows;  // first query row of this CTA within its (sequence, kv head)
 
   pdl_prologue();
 
+  const int q_start = p.cu_seqlens_q ? p.cu_seqlens_q[seq] : seq;
+  const int q_len = p.cu_seqlens_q ? p.cu_seqlens_q[seq + 1] - q_start : 1;
+  const int seq_rows = q_len * p.group;
+  if (row0 >= seq_rows) return;                   // this sequence has fewer query rows than the longest one
+  const int rows = min(kRows, seq_rows - row0);   // valid rows
+  // row r of the CTA: query token (row0 + r) / group of the sequence, head kvh * group + (row0 + r) % group
+  auto row_token = [&](int r) { return (row0 + r) / p.group; };
+  auto row_head = [&](int r) { return kvh * p.group + (row0 + r) % p.group; };
+
   const int n = p.seq_lens[seq];
-  const int total_tiles = (n + TN - 1) / TN;
+  // cached tokens row r may see; the CTA walks up to the largest limit among its rows (the last row's)
+  auto row_limit = [&](int r) { return p.causal ? max(0, min(n, n - q_len + row_token(r) + 1)) : n; };
+  const int n_item = row_limit(rows - 1);
+  const int lim_min = row_limit(0);
+  const int total_tiles = (n_item + TN - 1) / TN;
   const int tile_begin = split * p.tiles_per_split;
   const int tile_end = min(tile_begin + p.tiles_per_split, total_tiles);
 
-  if (tile_begin >= tile_end) {  // nothing cached in this split's range
-    if (p.num_splits > 1) {
-      if (tid < rows) p.part_lse[(static_cast<int64_t>(seq) * p.num_heads + head0 + tid) * p.num_splits + split] = -INFINITY;
-    } else {
-      TQ* o = static_cast<TQ*>(p.out) + seq * p.out_stride_t;
-      for (int i = tid; i < rows * D; i += kAttnThreads) o[(head0 + i / D) * p.out_stride_h + i % D] = TQ(0.0f);
+  if (tile_begin >= tile_end) {  // nothing to attend to in this split's range
+    for (int i = tid; i < rows * (p.num_splits > 1 ? 1 : D); i += kAttnThreads) {
+      const int r = p.num_splits > 1 ? i : i / D;
+      const int64_t tok = q_start + row_token(r);
+      if (p.num_splits > 1) {
+        p.part_lse[(tok * p.num_heads + row_head(r)) * p.num_splits + split] = -INFINITY;
+      } else {
+        static_cast<TQ*>(p.out)[tok * p.out_stride_t + row_head(r) * p.out_stride_h + i % D] = TQ(0.0f);
+      }
     }
     return;
   }
@@ -229,7 +251,8 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
       const int r = c / kChunks, col = c - r * kChunks;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (r < rows) {
-        const TQ* src = static_cast<const TQ*>(p.query) + seq * p.query_stride_t + (head0 + r) * p.query_stride_h + col * 8;
+        const TQ* src = static_cast<const TQ*>(p.query) + static_cast<int64_t>(q_start + row_token(r)) * p.query_stride_t +
+                        row_head(r) * p.query_stride_h + col * 8;
         v = *reinterpret_cast<const uint4*>(src);
         if constexpr (!std::is_same_v<TQ, T16>) {  // bf16 query, fp16 products
           uint32_t* w = reinterpret_cast<uint32_t*>(&v);
@@ -297,6 +320,8 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
   // ---- running state of this warp ----------------------------------------------------------------
   const float scale2 = p.softmax_scale * kLog2e * ((kFp8 && p.k_descale) ? __ldg(p.k_descale) : 1.0f);
   const float lazy_margin = 8.0f / scale2;  // raw-logit distance that is worth a factor 2^8
+  // cached tokens visible to this lane's rows g and g + 8 (padding rows: the CTA's limit; they are never stored)
+  const int lim[2] = {g < rows ? row_limit(g) : n_item, g + 8 < rows ? row_limit(g + 8) : n_item};
   float m_run[2] = {-INFINITY, -INFINITY};  // reference point (a lagging maximum) of the raw logits of rows g, g + 8
   float l_run[2] = {0.f, 0.f};              // this lane's share of the running sums of rows g and g + 8
   // rows g (c0, c1) / g + 8 (c2, c3); columns of tile i: 16-bit cache  8i + 2t, + 1
@@ -385,7 +410,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
     }
 
     // ---- mask the tail, running maximum (of the raw logits: the scale is positive), P = 2^(scale (S - m)) --
-    if ((tile + 1) * TN > n) {  // only the last tile of a sequence has tokens to mask
+    if ((tile + 1) * TN > lim_min) {  // only the tiles that reach past some row's limit have tokens to mask
 #pragma unroll
       for (int gi = 0; gi < NG; ++gi) {
         const int tok_base = tile * TN + gi * 64 + warp * 16 + 2 * t;
@@ -393,7 +418,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
         for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            if (tok_base + nt * 8 + (e & 1) >= n) s_acc[gi][nt][e] = -INFINITY;
+            if (tok_base + nt * 8 + (e & 1) >= lim[e >> 1]) s_acc[gi][nt][e] = -INFINITY;
         }
       }
     }
@@ -528,22 +553,23 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
       ox += f * o.x;
       oy += f * o.y;
     }
-    const int head = head0 + row;
+    const int head = row_head(row);
+    const int64_t tok = q_start + row_token(row);
     if (p.num_splits > 1) {
-      const int64_t slot = (static_cast<int64_t>(seq) * p.num_heads + head) * p.num_splits + split;
-      if (d == 0) p.part_lse[slot] = m + log2f(l);
-      const float inv = 1.0f / l;
+      const int64_t slot = (tok * p.num_heads + head) * p.num_splits + split;
+      if (d == 0) p.part_lse[slot] = (l > 0.f) ? m + log2f(l) : -INFINITY;
+      const float inv = (l > 0.f) ? 1.0f / l : 0.f;
       *reinterpret_cast<float2*>(p.part_out + slot * D + d) = make_float2(ox * inv, oy * inv);
     } else {
       float rescale = 1.0f;
       if (p.sink) {  // one more logit in the denominator
         const float sk = static_cast<float>(static_cast<const TQ*>(p.sink)[head]) * kLog2e;
         const float mf = fmaxf(m, sk);
-        rescale = exp2f(m - mf);
+        rescale = (m == -INFINITY) ? 0.f : exp2f(m - mf);
         l = l * rescale + exp2f(sk - mf);
       }
-      const float f = rescale / l * v_descale;
-      TQ* o = static_cast<TQ*>(p.out) + seq * p.out_stride_t + head * p.out_stride_h + d;
+      const float f = (l > 0.f) ? rescale / l * v_descale : 0.f;  // a row that sees no token gives zeros
+      TQ* o = static_cast<TQ*>(p.out) + tok * p.out_stride_t + head * p.out_stride_h + d;
       *reinterpret_cast<uint32_t*>(o) = pack2<TQ>(ox * f, oy * f);
     }
   }
@@ -554,7 +580,7 @@ __global__ void __launch_bounds__(kAttnThreads) paged_decode_kernel(const Decode
 // ---------------------------------------------------------------------------------------------
 template <typename TQ>
 __global__ void __launch_bounds__(128) paged_decode_merge_kernel(const DecodeParams p, int head_size) {
-  const int seq = blockIdx.x / p.num_heads, head = blockIdx.x - seq * p.num_heads;
+  const int seq = blockIdx.x / p.num_heads, head = blockIdx.x - seq * p.num_heads;  // "seq": a query token
   pdl_prologue();
   const int64_t base = (static_cast<int64_t>(seq) * p.num_heads + head) * p.num_splits;
   float m = -INFINITY;
@@ -725,15 +751,19 @@ struct DecodePlan {
   int splits;
   int tiles_per_split;
   bool wide;  // 128-token tiles
+  int64_t row_tiles;  // 16-row tiles of the longest sequence's query rows
   int64_t workspace_bytes;
 };
 
-DecodePlan plan_decode(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads, int64_t head_size,
-                       int64_t max_seq_len, int q_dtype, int kv_dtype) {
-  DecodePlan pl{1, 1, false, 0};
+DecodePlan plan_decode(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q, int64_t num_heads,
+                       int64_t num_kv_heads, int64_t head_size, int64_t max_seq_len, int q_dtype, int kv_dtype) {
+  DecodePlan pl{1, 1, false, 1, 0};
   const int64_t group = num_kv_heads > 0 ? num_heads / num_kv_heads : 1;
-  const int64_t row_tiles = (group + kRows - 1) / kRows;
-  const int64_t base = num_seqs * num_kv_heads * row_tiles;
+  pl.row_tiles = (max_seqlen_q * group + kRows - 1) / kRows;
+  // CTAs that do work without splitting: per kv head, ceil(q_len * group / 16) for every sequence (tiles do not
+  // span sequences); exact for one token per sequence, else bounded through the total number of query rows
+  const int64_t base = max_seqlen_q == 1 ? num_seqs * num_kv_heads * pl.row_tiles
+                                         : num_kv_heads * (total_q * group / kRows + num_seqs);
   if (base <= 0) return pl;
   // both tile sizes where both exist: the cheaper plan wins.  A 128-token tile costs about 1.5 64-token tiles
   // of a CTA's time (measured on batches with many rounds: fewer barriers and more overlap per token).
@@ -753,7 +783,7 @@ DecodePlan plan_decode(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads
       pl.splits = static_cast<int>((max_tiles + pl.tiles_per_split - 1) / pl.tiles_per_split);  // drop empty tails
     }
   }
-  if (pl.splits > 1) pl.workspace_bytes = num_seqs * num_heads * pl.splits * (head_size + 1) * (int64_t)sizeof(float);
+  if (pl.splits > 1) pl.workspace_bytes = total_q * num_heads * pl.splits * (head_size + 1) * (int64_t)sizeof(float);
   return pl;
 }
 
@@ -762,55 +792,71 @@ DecodePlan plan_decode(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads
 
 extern "C" {
 
-KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads,
-                                                 int64_t head_size, int64_t max_seq_len, int q_dtype, int kv_dtype) {
-  if (num_seqs <= 0 || num_heads <= 0 || num_kv_heads <= 0 || max_seq_len < 0) return 0;
+KVC_API int64_t kvc_paged_attention_workspace_bytes(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q,
+                                                    int64_t num_heads, int64_t num_kv_heads, int64_t head_size,
+                                                    int64_t max_seq_len, int q_dtype, int kv_dtype) {
+  if (num_seqs <= 0 || total_q <= 0 || max_seqlen_q <= 0 || num_heads <= 0 || num_kv_heads <= 0 || max_seq_len < 0)
+    return 0;
   if (head_size != 64 && head_size != 128 && head_size != 192 && head_size != 256) return 0;
   if (q_dtype != KVC_IN_F16 && q_dtype != KVC_IN_BF16) return 0;
   if (kv_dtype != KVC_KV_AUTO && kv_dtype != KVC_KV_FP8_E4M3 && kv_dtype != KVC_KV_FP8_E5M2) return 0;
-  return kvc::plan_decode(num_seqs, num_heads, num_kv_heads, head_size, max_seq_len, q_dtype, kv_dtype).workspace_bytes;
+  return kvc::plan_decode(num_seqs, total_q, max_seqlen_q, num_heads, num_kv_heads, head_size, max_seq_len, q_dtype,
+                          kv_dtype)
+      .workspace_bytes;
 }
 
-KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void* key_cache, const void* value_cache,
-                                       const int32_t* block_table, const int32_t* seq_lens, const void* sink,
-                                       const float* k_descale, const float* v_descale, void* workspace,
-                                       int64_t workspace_bytes, int64_t num_seqs, int64_t num_heads,
-                                       int64_t num_kv_heads, int64_t head_size, int64_t block_size,
-                                       int64_t block_table_stride, int64_t max_seq_len, int64_t query_stride_t,
-                                       int64_t query_stride_h, int64_t out_stride_t, int64_t out_stride_h,
-                                       int64_t block_stride, int64_t page_stride, int64_t head_stride,
-                                       float softmax_scale, int q_dtype, int kv_dtype, void* stream) {
+KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_heads, int64_t num_kv_heads,
+                                                 int64_t head_size, int64_t max_seq_len, int q_dtype, int kv_dtype) {
+  return kvc_paged_attention_workspace_bytes(num_seqs, num_seqs, 1, num_heads, num_kv_heads, head_size, max_seq_len,
+                                             q_dtype, kv_dtype);
+}
+
+KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_cache, const void* value_cache,
+                                const int32_t* block_table, const int32_t* seq_lens, const int32_t* cu_seqlens_q,
+                                const void* sink, const float* k_descale, const float* v_descale, void* workspace,
+                                int64_t workspace_bytes, int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q,
+                                int64_t num_heads, int64_t num_kv_heads, int64_t head_size, int64_t block_size,
+                                int64_t block_table_stride, int64_t max_seq_len, int64_t query_stride_t,
+                                int64_t query_stride_h, int64_t out_stride_t, int64_t out_stride_h,
+                                int64_t block_stride, int64_t page_stride, int64_t head_stride, float softmax_scale,
+                                int causal, int q_dtype, int kv_dtype, void* stream) {
   using namespace kvc;
   if (q_dtype != KVC_IN_F16 && q_dtype != KVC_IN_BF16)
-    return fail(KVC_ERR_UNSUPPORTED, "paged_decode_attention: query must be fp16 or bf16");
+    return fail(KVC_ERR_UNSUPPORTED, "paged_attention: query must be fp16 or bf16");
   if (kv_dtype != KVC_KV_AUTO && kv_dtype != KVC_KV_FP8_E4M3 && kv_dtype != KVC_KV_FP8_E5M2)
     return fail(KVC_ERR_UNSUPPORTED, "Unsupported data type of kv cache: code " + std::to_string(kv_dtype));
-  if (num_seqs < 0 || num_heads <= 0 || num_kv_heads <= 0 || block_size <= 0 || max_seq_len < 0)
-    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: sizes must be positive");
+  if (num_seqs < 0 || total_q < 0 || max_seqlen_q < 0 || num_heads <= 0 || num_kv_heads <= 0 || block_size <= 0 ||
+      max_seq_len < 0)
+    return fail(KVC_ERR_INVALID_ARG, "paged_attention: sizes must be positive");
   if (num_heads % num_kv_heads)
-    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: num_heads must be a multiple of num_kv_heads");
-  if (!(softmax_scale > 0.0f))
-    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: softmax_scale must be positive");
+    return fail(KVC_ERR_INVALID_ARG, "paged_attention: num_heads must be a multiple of num_kv_heads");
+  if (!(softmax_scale > 0.0f)) return fail(KVC_ERR_INVALID_ARG, "paged_attention: softmax_scale must be positive");
   if (head_size != 64 && head_size != 128 && head_size != 192 && head_size != 256)
-    return fail(KVC_ERR_UNSUPPORTED, "paged_decode_attention: head_size must be 64, 128, 192 or 256");
-  if (num_seqs == 0) return KVC_OK;
-  if (num_seqs > 0x7FFFFFFFll || num_heads > 65535 * 16 || block_size > 0x7FFFFFFFll || max_seq_len > 0x7FFFFFFFll)
-    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: sizes out of range");
+    return fail(KVC_ERR_UNSUPPORTED, "paged_attention: head_size must be 64, 128, 192 or 256");
+  if (num_seqs == 0 || total_q == 0 || max_seqlen_q == 0) return KVC_OK;
+  if (!cu_seqlens_q && (total_q != num_seqs || max_seqlen_q != 1))
+    return fail(KVC_ERR_INVALID_ARG, "paged_attention: without cu_seqlens_q every sequence has one query token");
+  if (num_seqs > 65535)
+    return fail(KVC_ERR_INVALID_ARG, "paged_attention: at most 65535 sequences per call");
+  if (total_q > 0x7FFFFFFFll || max_seqlen_q > total_q || num_heads > 65535 * 16 || block_size > 0x7FFFFFFFll ||
+      max_seq_len > 0x7FFFFFFFll)
+    return fail(KVC_ERR_INVALID_ARG, "paged_attention: sizes out of range");
   if (!out || !query || !key_cache || !value_cache || !block_table || !seq_lens)
-    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: out, query, caches, block_table and seq_lens must be non-NULL");
+    return fail(KVC_ERR_INVALID_ARG, "paged_attention: out, query, caches, block_table and seq_lens must be non-NULL");
   const int ces = kv_dtype == KVC_KV_AUTO ? 2 : 1;
   const bool ok_align = aligned(query, 16) && aligned(out, 4) && aligned(key_cache, 16) && aligned(value_cache, 16) &&
                         (query_stride_t * 2) % 16 == 0 && (query_stride_h * 2) % 16 == 0 && (out_stride_t * 2) % 4 == 0 &&
                         (out_stride_h * 2) % 4 == 0 && (block_stride * ces) % 16 == 0 && (page_stride * ces) % 16 == 0 &&
-                        (head_stride * ces) % 16 == 0 && aligned(block_table, 4) && aligned(seq_lens, 4);
-  if (!ok_align)
-    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: query and cache rows must be 16-byte aligned");
+                        (head_stride * ces) % 16 == 0 && aligned(block_table, 4) && aligned(seq_lens, 4) &&
+                        aligned(cu_seqlens_q, 4);
+  if (!ok_align) return fail(KVC_ERR_INVALID_ARG, "paged_attention: query and cache rows must be 16-byte aligned");
 
-  const DecodePlan pl = plan_decode(num_seqs, num_heads, num_kv_heads, head_size, max_seq_len, q_dtype, kv_dtype);
+  const DecodePlan pl = plan_decode(num_seqs, total_q, max_seqlen_q, num_heads, num_kv_heads, head_size, max_seq_len,
+                                    q_dtype, kv_dtype);
   if (pl.splits > 1 && (!workspace || workspace_bytes < pl.workspace_bytes || !aligned(workspace, 16)))
-    return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: workspace missing, misaligned (16 bytes) or too small; ask "
-                                         "kvc_paged_decode_workspace_bytes ("
-                                         + std::to_string(pl.workspace_bytes) + " bytes)");
+    return fail(KVC_ERR_INVALID_ARG, "paged_attention: workspace missing, misaligned (16 bytes) or too small; ask "
+                                     "kvc_paged_attention_workspace_bytes (" + std::to_string(pl.workspace_bytes) +
+                                     " bytes)");
 
   DecodeParams p{};
   p.out = out;
@@ -819,6 +865,7 @@ KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void*
   p.value_cache = value_cache;
   p.block_table = block_table;
   p.seq_lens = seq_lens;
+  p.cu_seqlens_q = cu_seqlens_q;
   p.sink = sink;
   p.k_descale = k_descale;
   p.v_descale = v_descale;
@@ -833,27 +880,28 @@ KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void*
   p.num_heads = static_cast<int32_t>(num_heads);
   p.num_kv_heads = static_cast<int32_t>(num_kv_heads);
   p.group = static_cast<int32_t>(num_heads / num_kv_heads);
-  p.row_tiles = (p.group + kRows - 1) / kRows;
+  p.row_tiles = static_cast<int32_t>(pl.row_tiles);
   p.block_size = static_cast<int32_t>(block_size);
   p.bs_shift = pow2_shift(block_size);
   p.num_splits = pl.splits;
   p.tiles_per_split = pl.tiles_per_split;
+  p.causal = causal ? 1 : 0;
   p.softmax_scale = softmax_scale;
   if (pl.splits > 1) {
     p.part_out = static_cast<float*>(workspace);  // first: its float2 stores need 8-byte alignment
-    p.part_lse = p.part_out + num_seqs * num_heads * pl.splits * head_size;
+    p.part_lse = p.part_out + total_q * num_heads * pl.splits * head_size;
   }
-  const int64_t grid_y = static_cast<int64_t>(p.num_kv_heads) * p.row_tiles;
-  if (grid_y > 65535) return fail(KVC_ERR_INVALID_ARG, "paged_decode_attention: too many kv heads");
-  const dim3 grid(static_cast<unsigned>(num_seqs), static_cast<unsigned>(grid_y), static_cast<unsigned>(pl.splits));
+  const int64_t grid_x = static_cast<int64_t>(p.num_kv_heads) * p.row_tiles;
+  if (grid_x > 0x7FFFFFFFll) return fail(KVC_ERR_INVALID_ARG, "paged_attention: too many query rows per sequence");
+  const dim3 grid(static_cast<unsigned>(grid_x), static_cast<unsigned>(num_seqs), static_cast<unsigned>(pl.splits));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = (q_dtype == KVC_IN_F16)
                       ? launch_decode_kv<__half>(kv_dtype, static_cast<int>(head_size), pl.wide, p, grid, st)
                       : launch_decode_kv<__nv_bfloat16>(kv_dtype, static_cast<int>(head_size), pl.wide, p, grid, st);
   if (e != cudaSuccess)
-    return fail(KVC_ERR_CUDA, std::string("paged_decode_attention launch failed: ") + cudaGetErrorString(e));
+    return fail(KVC_ERR_CUDA, std::string("paged_attention launch failed: ") + cudaGetErrorString(e));
   if (pl.splits > 1) {
-    const dim3 mgrid(static_cast<unsigned>(num_seqs * num_heads));
+    const dim3 mgrid(static_cast<unsigned>(total_q * num_heads));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = mgrid;
     cfg.blockDim = dim3(128);
@@ -867,9 +915,25 @@ KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void*
             ? cudaLaunchKernelEx(&cfg, paged_decode_merge_kernel<__half>, p, static_cast<int>(head_size))
             : cudaLaunchKernelEx(&cfg, paged_decode_merge_kernel<__nv_bfloat16>, p, static_cast<int>(head_size));
     if (e != cudaSuccess)
-      return fail(KVC_ERR_CUDA, std::string("paged_decode_attention merge launch failed: ") + cudaGetErrorString(e));
+      return fail(KVC_ERR_CUDA, std::string("paged_attention merge launch failed: ") + cudaGetErrorString(e));
   }
   return KVC_OK;
+}
+
+KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void* key_cache, const void* value_cache,
+                                       const int32_t* block_table, const int32_t* seq_lens, const void* sink,
+                                       const float* k_descale, const float* v_descale, void* workspace,
+                                       int64_t workspace_bytes, int64_t num_seqs, int64_t num_heads,
+                                       int64_t num_kv_heads, int64_t head_size, int64_t block_size,
+                                       int64_t block_table_stride, int64_t max_seq_len, int64_t query_stride_t,
+                                       int64_t query_stride_h, int64_t out_stride_t, int64_t out_stride_h,
+                                       int64_t block_stride, int64_t page_stride, int64_t head_stride,
+                                       float softmax_scale, int q_dtype, int kv_dtype, void* stream) {
+  return kvc_paged_attention(out, query, key_cache, value_cache, block_table, seq_lens, nullptr, sink, k_descale,
+                             v_descale, workspace, workspace_bytes, num_seqs, num_seqs, num_seqs > 0 ? 1 : 0, num_heads,
+                             num_kv_heads, head_size, block_size, block_table_stride, max_seq_len, query_stride_t,
+                             query_stride_h, out_stride_t, out_stride_h, block_stride, page_stride, head_stride,
+                             softmax_scale, 0, q_dtype, kv_dtype, stream);
 }
 
 }  // extern "C"
