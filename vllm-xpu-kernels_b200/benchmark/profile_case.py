@@ -25,7 +25,7 @@ from vllm_xpu_kernels import cabi  # noqa: E402
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--layout", choices=["flash", "paged", "mla", "gather", "quant-static", "quant-dynamic", "quant-token",
-                                         "rope", "rope-cache", "rope-then-cache", "decode"], default="flash",
+                                         "rope", "rope-cache", "rope-then-cache", "decode", "prefill"], default="flash",
                     help="mla: concat_and_cache_mla (512 + 64 wide entries); gather: gather_cache of such entries; "
                          "rope: rotary_embedding; rope-cache: the fused rotary_embedding_and_cache_flash; "
                          "rope-then-cache: the two separate ops back to back (what the fused op replaces)")
@@ -63,6 +63,9 @@ def main() -> None:
         return
     if ns.layout == "decode":
         run_decode(ns, dev)
+        return
+    if ns.layout == "prefill":
+        run_prefill(ns, dev)
         return
     dt = {"bfloat16": torch.bfloat16, "half": torch.float16, "float": torch.float32}[ns.dtype]
     T, H, D, bs = ns.tokens, ns.heads, ns.head_size, ns.block_size
@@ -291,6 +294,41 @@ def run_decode(ns, dev) -> None:
     print(f"layout=decode kv={ns.kv} dtype={ns.dtype} seqs={S} seq_len={L} Hq={hq} Hkv={hk} D={D} bs={bs} "
           f"algorithmic_bytes={alg} launches={ns.launches} event_us={['%.1f' % t for t in times]} "
           f"best_GBps={alg / best / 1e3:.0f}")
+
+
+def run_prefill(ns, dev) -> None:
+    """Causal attention of whole prompts over their own paged keys/values: --seqs prompts of --seq-len tokens
+    (query length = cached length).  Compute-bound: reports TFLOP/s of the 4 * L^2 / 2 * Hq * D useful flops."""
+    dt = {"bfloat16": torch.bfloat16, "half": torch.float16}[ns.dtype]
+    S, L, hq, hk, D, bs = ns.seqs, ns.seq_len, ns.q_heads, ns.heads, ns.head_size, ns.block_size
+    blocks_per_seq = (L + bs - 1) // bs
+    nb = S * blocks_per_seq
+    if ns.kv == "auto":
+        kc = torch.randn(nb, bs, hk, D, device=dev).to(dt)
+        vc = torch.randn(nb, bs, hk, D, device=dev).to(dt)
+    else:
+        kc = torch.randint(0, 120, (nb, bs, hk, D), device=dev, dtype=torch.uint8)
+        vc = torch.randint(0, 120, (nb, bs, hk, D), device=dev, dtype=torch.uint8)
+    table = torch.randperm(nb, device=dev).view(S, blocks_per_seq).to(torch.int32)
+    lens = torch.full((S,), L, dtype=torch.int32, device=dev)
+    cu = (torch.arange(S + 1, device=dev, dtype=torch.int32) * L)
+    query = torch.randn(S * L, hq, D, device=dev).to(dt)
+    out = torch.empty_like(query)
+    ds = torch.tensor(0.05, device=dev)
+    flops = 4.0 * S * (L * (L + 1) / 2) * hq * D
+    evs = []
+    for i in range(ns.launches):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        cabi.paged_attention(query, kc, vc, table, lens, cu, L, D ** -0.5, L, True, ns.kv, ds, ds, out=out)
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    times = [a.elapsed_time(b) * 1e3 for a, b in evs]
+    best = min(times[1:]) if len(times) > 1 else times[0]
+    print(f"layout=prefill kv={ns.kv} dtype={ns.dtype} seqs={S} seq_len={L} Hq={hq} Hkv={hk} D={D} bs={bs} "
+          f"useful_flops={flops:.3e} launches={ns.launches} event_us={['%.1f' % t for t in times]} "
+          f"best_TFLOPs={flops / best / 1e6:.1f}")
 
 
 if __name__ == "__main__":

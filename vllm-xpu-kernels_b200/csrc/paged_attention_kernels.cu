@@ -128,6 +128,7 @@ struct DecodeParams {
   int32_t bs_shift;  // log2(block_size), or -1
   int32_t num_splits, tiles_per_split;
   int32_t causal;  // query token i of q_len sees the first seq_len - q_len + i + 1 cached tokens
+  int32_t many_rows_elsewhere;  // sequences with more than 16 rows per kv head are handled by paged_prefill_kernel
   float softmax_scale;
 };
 
@@ -174,7 +175,8 @@ struct DecodeCfg {
   static_assert(D % 64 == 0 && D <= 256, "head sizes 64, 128, 192, 256");
   // CTAs per SM the register allocation has to leave room for: the 64-token fp8 instance of D = 128 lives on
   // four (43 KB of shared memory each); it measured 107 us with four and 123 us with three on the 64 x 4096 batch.
-  static constexpr int kMinCtasPerSm = (KV != KVC_KV_AUTO && D == 128 && !WIDE) ? 4 : 1;
+  // The other D = 128 instances hold three by shared memory (75-76 KB) and must not lose one to registers.
+  static constexpr int kMinCtasPerSm = D != 128 ? 1 : (KV != KVC_KV_AUTO && !WIDE) ? 4 : 3;
 };
 
 // Within every group of 16 head dimensions the fp8 path works on a permuted order: an ldmatrix of fp8 rows
@@ -217,6 +219,7 @@ paged_decode_kernel(const DecodeParams p) {
   const int q_len = p.cu_seqlens_q ? p.cu_seqlens_q[seq + 1] - q_start : 1;
   const int seq_rows = q_len * p.group;
   if (row0 >= seq_rows) return;                   // this sequence has fewer query rows than the longest one
+  if (p.many_rows_elsewhere && seq_rows > kRows) return;  // the many-rows kernel's
   const int rows = min(kRows, seq_rows - row0);   // valid rows
   // row r of the CTA: query token (row0 + r) / group of the sequence, head kvh * group + (row0 + r) % group
   auto row_token = [&](int r) { return (row0 + r) / p.group; };
@@ -576,6 +579,358 @@ paged_decode_kernel(const DecodeParams p) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// the many-rows kernel: sequences with more than 16 query rows per kv head (prefill chunks)
+// ---------------------------------------------------------------------------------------------
+// Same stream over the cached tokens, other division of labour: a CTA owns 64 query rows (token-major
+// (token, head) pairs of one kv head) and every warp 16 of them against ALL tokens of a tile, so a tile of
+// keys and values serves 64 rows instead of 16 and nothing is merged across warps.  Sequences with at most
+// 16 rows per kv head are left to paged_decode_kernel (its launch skips the others).
+constexpr int kPrefillRows = 64;
+
+template <typename TQ, int KV, int D>
+struct PrefillCfg {
+  using T16 = std::conditional_t<KV == KVC_KV_AUTO, TQ, __half>;
+  static constexpr int kCacheES = (KV == KVC_KV_AUTO) ? 2 : 1;
+  static constexpr int kQRowBytes = D * 2 + 16;
+  static constexpr int kRowBytes = D * kCacheES + 16;
+  static constexpr int kTile = 64;
+  static constexpr int kTileBytes = kTile * kRowBytes;
+  static constexpr int kStages = 2;
+  // the query rows pass through the second stage on their way into registers (D <= 128) or stay behind the ring
+  static constexpr bool kQInRegs = D <= 128;
+  static constexpr int kSmemQ = kQInRegs ? 0 : kPrefillRows * kQRowBytes;
+  static_assert(kPrefillRows * kQRowBytes <= 2 * kTileBytes || !kQInRegs, "query rows fit in a stage");
+  static constexpr int kSmemOff = kStages * kTile * (int)sizeof(int64_t);
+  static constexpr int kSmemBytes = kStages * 2 * kTileBytes + kSmemQ + kSmemOff;
+};
+
+template <typename TQ, int KV, int D>
+__global__ void __launch_bounds__(kAttnThreads) paged_prefill_kernel(const DecodeParams p) {
+  using Cfg = PrefillCfg<TQ, KV, D>;
+  using T16 = typename Cfg::T16;
+  constexpr bool kFp8 = KV != KVC_KV_AUTO;
+  constexpr int ES = Cfg::kCacheES;
+  constexpr int QRB = Cfg::kQRowBytes;
+  constexpr int RB = Cfg::kRowBytes;
+  constexpr int NST = Cfg::kStages;
+  constexpr int TN = Cfg::kTile;
+  constexpr int NG = TN / 16;  // 16-token groups of a tile, all of them this warp's
+  constexpr int NT = D / 8;
+
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* s_kv = smem;
+  unsigned char* s_q = Cfg::kQInRegs ? s_kv + 2 * Cfg::kTileBytes : s_kv + NST * 2 * Cfg::kTileBytes;
+  int64_t* s_off = reinterpret_cast<int64_t*>(s_kv + NST * 2 * Cfg::kTileBytes + Cfg::kSmemQ);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int seq = blockIdx.y;
+  const int kvh = blockIdx.x / p.row_tiles, row_tile = blockIdx.x - kvh * p.row_tiles;
+  const int row0 = row_tile * kPrefillRows;
+
+  pdl_prologue();
+
+  const int q_start = p.cu_seqlens_q ? p.cu_seqlens_q[seq] : seq;  // NULL: one query token per sequence
+  const int q_len = p.cu_seqlens_q ? p.cu_seqlens_q[seq + 1] - q_start : 1;
+  const int seq_rows = q_len * p.group;
+  if (seq_rows <= kRows || row0 >= seq_rows) return;  // few rows: the decode kernel's; or past this sequence's rows
+  const int rows = min(kPrefillRows, seq_rows - row0);
+  auto row_token = [&](int r) { return (row0 + r) / p.group; };
+  auto row_head = [&](int r) { return kvh * p.group + (row0 + r) % p.group; };
+  const int n = p.seq_lens[seq];
+  auto row_limit = [&](int r) { return p.causal ? max(0, min(n, n - q_len + row_token(r) + 1)) : n; };
+  const int n_item = row_limit(rows - 1);
+  const int lim_min = row_limit(0);
+  const int tile_end = (n_item + TN - 1) / TN;
+  constexpr int tile_begin = 0;
+
+  // this lane's rows: 16 warp + g and + 8
+  const int my_row[2] = {warp * 16 + g, warp * 16 + g + 8};
+  const bool warp_has_rows = warp * 16 < rows;
+
+  if (tile_end <= 0) {  // no row sees any token
+    for (int i = tid; i < rows * D; i += kAttnThreads) {
+      const int r = i / D;
+      static_cast<TQ*>(p.out)[static_cast<int64_t>(q_start + row_token(r)) * p.out_stride_t +
+                              row_head(r) * p.out_stride_h + i % D] = TQ(0.0f);
+    }
+    return;
+  }
+
+  // ---- query rows -> shared memory (as T16; fp8 path: permuted inside groups of 16) ----------------
+  {
+    constexpr int kChunks = D / 8;
+    for (int c = tid; c < kPrefillRows * kChunks; c += kAttnThreads) {
+      const int r = c / kChunks, col = c - r * kChunks;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (r < rows) {
+        const TQ* src = static_cast<const TQ*>(p.query) + static_cast<int64_t>(q_start + row_token(r)) * p.query_stride_t +
+                        row_head(r) * p.query_stride_h + col * 8;
+        v = *reinterpret_cast<const uint4*>(src);
+        if constexpr (!std::is_same_v<TQ, T16>) {
+          uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xFFFF0000u);
+            w[i] = pack2<__half>(lo, hi);
+          }
+        }
+      }
+      if constexpr (kFp8) {
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(&v);
+        uint32_t* group = reinterpret_cast<uint32_t*>(s_q + r * QRB + (col >> 1) * 32);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) group[fp8_q_word_position((col & 1) * 4 + i)] = w[i];
+      } else {
+        *reinterpret_cast<uint4*>(s_q + r * QRB + col * 16) = v;
+      }
+    }
+  }
+
+  // ---- producer (as in the decode kernel) -----------------------------------------------------------
+  const int32_t* table = p.block_table + seq * p.block_table_stride;
+  const int64_t head_off = static_cast<int64_t>(kvh) * p.head_stride;
+  auto publish_offsets = [&](int tile) {
+    if (tid < TN) {
+      const int token = tile * TN + tid;
+      int64_t off = 0;
+      if (tile < tile_end && token < n) {
+        const int blk_idx = p.bs_shift >= 0 ? (token >> p.bs_shift) : token / p.block_size;
+        off = (static_cast<int64_t>(__ldg(table + blk_idx)) * p.block_stride +
+               static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride + head_off) * ES;
+      }
+      s_off[((tile - tile_begin) % NST) * TN + tid] = off;
+    }
+  };
+  const int64_t v_minus_k =
+      static_cast<const unsigned char*>(p.value_cache) - static_cast<const unsigned char*>(p.key_cache);
+  auto load_tile = [&](int tile) {
+    constexpr int kChunks = D * ES / 16;
+    const int slot = (tile - tile_begin) % NST;
+    const int64_t* offs = s_off + slot * TN;
+    unsigned char* ks = s_kv + slot * 2 * Cfg::kTileBytes;
+    const int rows_left = n - tile * TN;
+    auto copy_chunk = [&](int r, int col) {
+      const unsigned char* src = static_cast<const unsigned char*>(p.key_cache) + col * 16 + offs[r];
+      const uint32_t dst = smem_u32(ks + r * RB + col * 16);
+      const int nbytes = r < rows_left ? 16 : 0;
+      cp_async_16(dst, src, nbytes);
+      cp_async_16(dst + Cfg::kTileBytes, src + v_minus_k, nbytes);
+    };
+    if constexpr (kAttnThreads % kChunks == 0) {
+      constexpr int kRowsPerPass = kAttnThreads / kChunks;
+      const int r0 = tid / kChunks, col = tid - r0 * kChunks;
+#pragma unroll
+      for (int i = 0; i < TN / kRowsPerPass; ++i) copy_chunk(r0 + i * kRowsPerPass, col);
+    } else {
+      for (int c = tid; c < TN * kChunks; c += kAttnThreads) copy_chunk(c / kChunks, c % kChunks);
+    }
+  };
+
+  // ---- state of this warp's 16 rows ------------------------------------------------------------------
+  const float scale2 = p.softmax_scale * kLog2e * ((kFp8 && p.k_descale) ? __ldg(p.k_descale) : 1.0f);
+  const float lazy_margin = 8.0f / scale2;
+  const int lim[2] = {my_row[0] < rows ? row_limit(my_row[0]) : 0, my_row[1] < rows ? row_limit(my_row[1]) : 0};
+  // the warp stops computing where its last valid row's limit ends (it keeps helping with the copies)
+  const int warp_limit = warp_has_rows ? row_limit(min(rows, warp * 16 + 16) - 1) : 0;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  float o_acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+
+  const uint32_t q_base = smem_u32(s_q);
+  const uint32_t a_lane_off_q = (warp * 16 + (lane & 15)) * QRB + (lane >> 4) * 16;
+  const uint32_t k_lane_off = ((lane & 7) + (lane >> 4) * 8) * RB + ((lane >> 3) & 1) * 16;
+  const uint32_t v_lane_off = ((lane & 7) + ((lane >> 3) & 1) * 8) * RB + (lane >> 4) * 16;
+
+#pragma unroll
+  for (int i = 0; i < NST; ++i) publish_offsets(tile_begin + i);
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < NST - 1; ++i) {
+    if (tile_begin + i < tile_end) load_tile(tile_begin + i);
+    cp_async_commit();
+  }
+  [[maybe_unused]] uint32_t qf[Cfg::kQInRegs ? D / 16 : 1][4];
+  if constexpr (Cfg::kQInRegs) {
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) ldmatrix_x4(qf[kk], q_base + a_lane_off_q + kk * 32);
+  }
+  auto q_frag = [&](int kk, uint32_t (&a)[4]) {
+    if constexpr (Cfg::kQInRegs) {
+      a[0] = qf[kk][0]; a[1] = qf[kk][1]; a[2] = qf[kk][2]; a[3] = qf[kk][3];
+    } else {
+      ldmatrix_x4(a, q_base + a_lane_off_q + kk * 32);
+    }
+  };
+
+  for (int tile = tile_begin; tile < tile_end; ++tile) {
+    const int slot = (tile - tile_begin) % NST;
+    cp_async_wait<NST - 2>();
+    __syncthreads();
+    if (tile + NST - 1 < tile_end) load_tile(tile + NST - 1);
+    cp_async_commit();
+    publish_offsets(tile + NST);
+    if (tile * TN >= warp_limit) continue;  // nothing left for this warp's rows (warp-uniform)
+    const uint32_t ks = smem_u32(s_kv + slot * 2 * Cfg::kTileBytes);
+    const uint32_t vs = ks + Cfg::kTileBytes;
+
+    float s_acc[NG][2][4];
+#pragma unroll
+    for (int gi = 0; gi < NG; ++gi)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) s_acc[gi][nt][0] = s_acc[gi][nt][1] = s_acc[gi][nt][2] = s_acc[gi][nt][3] = 0.f;
+    if constexpr (!kFp8) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        uint32_t a[4];
+        q_frag(kk, a);
+#pragma unroll
+        for (int gi = 0; gi < NG; ++gi) {
+          uint32_t b[4];
+          ldmatrix_x4(b, ks + k_lane_off + gi * 16 * RB + kk * 32);
+          mma_16816<T16>(s_acc[gi][0], a, b[0], b[1]);
+          mma_16816<T16>(s_acc[gi][1], a, b[2], b[3]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int jj = 0; jj < D / 32; ++jj) {
+        uint32_t a0[4], a1[4];
+        q_frag(2 * jj, a0);
+        q_frag(2 * jj + 1, a1);
+#pragma unroll
+        for (int gi = 0; gi < NG; ++gi) {
+          uint32_t b[4];
+          ldmatrix_x4(b, ks + k_lane_off + gi * 16 * RB + jj * 32);
+          mma_16816<T16>(s_acc[gi][0], a0, fp8x2_to_f16x2<KV>(b[0]), fp8x2_to_f16x2<KV>(b[0] >> 16));
+          mma_16816<T16>(s_acc[gi][1], a0, fp8x2_to_f16x2<KV>(b[2]), fp8x2_to_f16x2<KV>(b[2] >> 16));
+          mma_16816<T16>(s_acc[gi][0], a1, fp8x2_to_f16x2<KV>(b[1]), fp8x2_to_f16x2<KV>(b[1] >> 16));
+          mma_16816<T16>(s_acc[gi][1], a1, fp8x2_to_f16x2<KV>(b[3]), fp8x2_to_f16x2<KV>(b[3] >> 16));
+        }
+      }
+    }
+
+    if ((tile + 1) * TN > lim_min) {  // some row of the CTA has tokens to mask in this tile
+#pragma unroll
+      for (int gi = 0; gi < NG; ++gi) {
+        const int tok_base = tile * TN + gi * 16 + 2 * t;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (tok_base + nt * 8 + (e & 1) >= lim[e >> 1]) s_acc[gi][nt][e] = -INFINITY;
+        }
+      }
+    }
+    float alpha[2], neg_ms[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int gi = 0; gi < NG; ++gi)
+        mx = fmaxf(mx, fmaxf(fmaxf(s_acc[gi][0][2 * r], s_acc[gi][0][2 * r + 1]),
+                             fmaxf(s_acc[gi][1][2 * r], s_acc[gi][1][2 * r + 1])));
+      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+      const bool move = mx > m_run[r] + lazy_margin;
+      alpha[r] = move ? fast_exp2((m_run[r] - mx) * scale2) : 1.0f;
+      m_run[r] = move ? mx : m_run[r];
+      neg_ms[r] = (m_run[r] == -INFINITY) ? 0.f : -m_run[r] * scale2;
+      l_run[r] *= alpha[r];
+    }
+    uint32_t pa[NG][4];
+#pragma unroll
+    for (int gi = 0; gi < NG; ++gi) {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pv[e] = fast_exp2(fmaf(s_acc[gi][nt][e], scale2, neg_ms[e >> 1]));
+        l_run[0] += pv[0] + pv[1];
+        l_run[1] += pv[2] + pv[3];
+        pa[gi][2 * nt] = pack2<T16>(pv[0], pv[1]);
+        pa[gi][2 * nt + 1] = pack2<T16>(pv[2], pv[3]);
+      }
+    }
+    if (__any_sync(0xFFFFFFFFu, alpha[0] != 1.0f || alpha[1] != 1.0f)) {
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        o_acc[i][0] *= alpha[0];
+        o_acc[i][1] *= alpha[0];
+        o_acc[i][2] *= alpha[1];
+        o_acc[i][3] *= alpha[1];
+      }
+    }
+    if constexpr (!kFp8) {
+#pragma unroll
+      for (int np = 0; np < D / 16; ++np) {
+#pragma unroll
+        for (int gi = 0; gi < NG; ++gi) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, vs + v_lane_off + gi * 16 * RB + np * 32);
+          mma_16816<T16>(o_acc[2 * np], pa[gi], b[0], b[1]);
+          mma_16816<T16>(o_acc[2 * np + 1], pa[gi], b[2], b[3]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int jj = 0; jj < D / 32; ++jj) {
+#pragma unroll
+        for (int gi = 0; gi < NG; ++gi) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, vs + v_lane_off + gi * 16 * RB + jj * 32);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) b[i] = __byte_perm(b[i], 0, 0x3120);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            mma_16816<T16>(o_acc[4 * jj + 2 * h], pa[gi], fp8x2_to_f16x2<KV>(b[2 * h]),
+                           fp8x2_to_f16x2<KV>(b[2 * h + 1]));
+            mma_16816<T16>(o_acc[4 * jj + 2 * h + 1], pa[gi], fp8x2_to_f16x2<KV>(b[2 * h] >> 16),
+                           fp8x2_to_f16x2<KV>(b[2 * h + 1] >> 16));
+          }
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  // ---- every lane finishes its own two rows ---------------------------------------------------------
+  const float v_descale = (kFp8 && p.v_descale) ? __ldg(p.v_descale) : 1.0f;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = l_run[r];
+    l += __shfl_xor_sync(0xFFFFFFFFu, l, 1);
+    l += __shfl_xor_sync(0xFFFFFFFFu, l, 2);
+    if (my_row[r] >= rows) continue;
+    const int head = row_head(my_row[r]);
+    const float m = m_run[r] * scale2;  // log2 domain; -inf if the row saw nothing
+    float rescale = 1.0f;
+    if (p.sink) {
+      const float sk = static_cast<float>(static_cast<const TQ*>(p.sink)[head]) * kLog2e;
+      const float mf = fmaxf(m, sk);
+      rescale = (m == -INFINITY) ? 0.f : exp2f(m - mf);
+      l = l * rescale + exp2f(sk - mf);
+    }
+    const float f = (l > 0.f) ? rescale / l * v_descale : 0.f;
+    TQ* o = static_cast<TQ*>(p.out) + static_cast<int64_t>(q_start + row_token(my_row[r])) * p.out_stride_t +
+            head * p.out_stride_h;
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      const float x = o_acc[i][2 * r] * f, y = o_acc[i][2 * r + 1] * f;
+      if constexpr (!kFp8) {
+        *reinterpret_cast<uint32_t*>(o + i * 8 + 2 * t) = pack2<TQ>(x, y);
+      } else {  // columns 16 (i / 2) + 4t + (i % 2) and + 2
+        TQ* dst = o + 16 * (i >> 1) + 4 * t + (i & 1);
+        dst[0] = TQ(x);
+        dst[2] = TQ(y);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // merge of the splits: out = sum_p w_p o_p / (sum_p w_p [+ sink]),  w_p = exp2(lse_p - max lse)
 // ---------------------------------------------------------------------------------------------
 template <typename TQ>
@@ -747,6 +1102,52 @@ cudaError_t launch_decode_kv(int kv, int head_size, bool wide, const DecodeParam
   }
 }
 
+template <typename TQ, int KV, int D>
+cudaError_t launch_prefill(const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  using Cfg = PrefillCfg<TQ, KV, D>;
+  static std::once_flag once[64];
+  static cudaError_t attr_err[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::call_once(once[dev], [&] {
+    attr_err[dev] = cudaFuncSetAttribute(paged_prefill_kernel<TQ, KV, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+  });
+  if (attr_err[dev] != cudaSuccess) return attr_err[dev];
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kAttnThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, paged_prefill_kernel<TQ, KV, D>, p);
+}
+
+template <typename TQ, int KV>
+cudaError_t launch_prefill_d(int head_size, const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  switch (head_size) {
+    case 64: return launch_prefill<TQ, KV, 64>(p, grid, st);
+    case 128: return launch_prefill<TQ, KV, 128>(p, grid, st);
+    case 192: return launch_prefill<TQ, KV, 192>(p, grid, st);
+    default: return launch_prefill<TQ, KV, 256>(p, grid, st);
+  }
+}
+
+template <typename TQ>
+cudaError_t launch_prefill_kv(int kv, int head_size, const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  switch (kv) {
+    case KVC_KV_AUTO: return launch_prefill_d<TQ, KVC_KV_AUTO>(head_size, p, grid, st);
+    case KVC_KV_FP8_E4M3: return launch_prefill_d<TQ, KVC_KV_FP8_E4M3>(head_size, p, grid, st);
+    default: return launch_prefill_d<TQ, KVC_KV_FP8_E5M2>(head_size, p, grid, st);
+  }
+}
+
 struct DecodePlan {
   int splits;
   int tiles_per_split;
@@ -760,6 +1161,13 @@ DecodePlan plan_decode(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q, 
   DecodePlan pl{1, 1, false, 1, 0};
   const int64_t group = num_kv_heads > 0 ? num_heads / num_kv_heads : 1;
   pl.row_tiles = (max_seqlen_q * group + kRows - 1) / kRows;
+  if (max_seqlen_q * group > kRows) {
+    // some sequence may have more than 16 query rows per kv head: those go to the many-rows kernel, the others
+    // to the decode kernel with one row tile and no split (the merge would not know which tokens have partials)
+    pl.row_tiles = 1;
+    pl.tiles_per_split = static_cast<int>((max_seq_len + 63) / 64 > 0 ? (max_seq_len + 63) / 64 : 1);
+    return pl;
+  }
   // CTAs that do work without splitting: per kv head, ceil(q_len * group / 16) for every sequence (tiles do not
   // span sequences); exact for one token per sequence, else bounded through the total number of query rows
   const int64_t base = max_seqlen_q == 1 ? num_seqs * num_kv_heads * pl.row_tiles
@@ -886,6 +1294,7 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
   p.num_splits = pl.splits;
   p.tiles_per_split = pl.tiles_per_split;
   p.causal = causal ? 1 : 0;
+  p.many_rows_elsewhere = (max_seqlen_q * p.group > kRows) ? 1 : 0;
   p.softmax_scale = softmax_scale;
   if (pl.splits > 1) {
     p.part_out = static_cast<float*>(workspace);  // first: its float2 stores need 8-byte alignment
@@ -900,6 +1309,17 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
                       : launch_decode_kv<__nv_bfloat16>(kv_dtype, static_cast<int>(head_size), pl.wide, p, grid, st);
   if (e != cudaSuccess)
     return fail(KVC_ERR_CUDA, std::string("paged_attention launch failed: ") + cudaGetErrorString(e));
+  if (max_seqlen_q * p.group > kRows) {  // sequences with more than 16 query rows per kv head
+    DecodeParams pp = p;
+    pp.row_tiles = static_cast<int32_t>((max_seqlen_q * p.group + kPrefillRows - 1) / kPrefillRows);
+    const int64_t px = static_cast<int64_t>(pp.num_kv_heads) * pp.row_tiles;
+    if (px > 0x7FFFFFFFll) return fail(KVC_ERR_INVALID_ARG, "paged_attention: too many query rows per sequence");
+    const dim3 pgrid(static_cast<unsigned>(px), static_cast<unsigned>(num_seqs), 1);
+    e = (q_dtype == KVC_IN_F16) ? launch_prefill_kv<__half>(kv_dtype, static_cast<int>(head_size), pp, pgrid, st)
+                                : launch_prefill_kv<__nv_bfloat16>(kv_dtype, static_cast<int>(head_size), pp, pgrid, st);
+    if (e != cudaSuccess)
+      return fail(KVC_ERR_CUDA, std::string("paged_attention many-rows launch failed: ") + cudaGetErrorString(e));
+  }
   if (pl.splits > 1) {
     const dim3 mgrid(static_cast<unsigned>(total_q * num_heads));
     cudaLaunchConfig_t cfg = {};
