@@ -26,6 +26,7 @@ class OpWorkload:
     make_steps: Callable           # (device, nbuf) -> (step(i), e2e_step(i), h2d_bytes, d2h_bytes)
     cpu_run: Callable              # (units) -> (run(), units_done, threads)
     arithmetic: str = "f32"
+    flops: float = 0.0             # > 0: the step is compute-bound; useful floating-point operations of one step
 
 
 def _rope_table(max_pos: int, rot_dim: int, dtype: torch.dtype) -> torch.Tensor:
@@ -315,6 +316,74 @@ def decode(kv: str) -> OpWorkload:
         S * L, 2 * S * L * hk * D * es + 2 * S * hq * D * 2 + 4 * S * blocks_per_seq + 4 * S, 2, make_steps, cpu_run)
 
 
+# ---------------------------------------------------------------------------------------------- prefill attention
+def prefill(kv: str) -> OpWorkload:
+    """Causal attention of whole prompts over their own paged keys/values (query length = cached length): the
+    many-rows path of paged attention.  Compute-bound, unlike everything else here."""
+    S, L, hq, hk, D, bs = 4, 2048, 64, 8, 128, 64
+    es = 2 if kv == "auto" else 1
+    blocks_per_seq = L // bs
+
+    def build(device, n_seq):
+        nb = n_seq * blocks_per_seq
+        if kv == "auto":
+            kc = torch.randn(nb, bs, hk, D, device=device).to(torch.bfloat16)
+            vc = torch.randn(nb, bs, hk, D, device=device).to(torch.bfloat16)
+        else:
+            kc = torch.randint(0, 120, (nb, bs, hk, D), device=device, dtype=torch.uint8)
+            vc = torch.randint(0, 120, (nb, bs, hk, D), device=device, dtype=torch.uint8)
+        table = torch.randperm(nb, device=device).view(n_seq, blocks_per_seq).to(torch.int32)
+        lens = torch.full((n_seq,), L, dtype=torch.int32, device=device)
+        cu = torch.arange(n_seq + 1, device=device, dtype=torch.int32) * L
+        return kc, vc, table, lens, cu
+
+    def make_steps(dev, nbuf):
+        from vllm_xpu_kernels import cabi
+        torch.manual_seed(15)
+        kc, vc, table, lens, cu = build(dev, S)
+        queries = [torch.randn(S * L, hq, D, device=dev).to(torch.bfloat16) for _ in range(nbuf)]
+        out = torch.empty(S * L, hq, D, dtype=torch.bfloat16, device=dev)
+        ds = torch.tensor(0.05, device=dev)
+        host = [q.cpu().pin_memory() for q in queries[:2]]
+        out_host = torch.empty(S * L, hq, D, dtype=torch.bfloat16).pin_memory()
+
+        def step(i):
+            cabi.paged_attention(queries[i % nbuf], kc, vc, table, lens, cu, L, D ** -0.5, L, True, kv, ds, ds, out=out)
+
+        def e2e_step(i):
+            cabi.paged_attention(host[i % 2].to(dev, non_blocking=True), kc, vc, table, lens, cu, L, D ** -0.5, L, True,
+                                 kv, ds, ds, out=out)
+            out_host.copy_(out, non_blocking=True)
+
+        return step, e2e_step, S * L * hq * D * 2, S * L * hq * D * 2
+
+    def cpu_run(units):
+        from oracle import torch_views
+        torch.manual_seed(15)
+        # the oracle is quadratic in the prompt length: a short prompt of the same head geometry
+        n = max(16, min(256, units))
+        nb = (n + bs - 1) // bs
+        kc = torch.randn(nb, bs, hk, D).to(torch.bfloat16)
+        vc = torch.randn(nb, bs, hk, D).to(torch.bfloat16)
+        if kv != "auto":
+            kc, vc = kc.to(torch.float8_e4m3fn), vc.to(torch.float8_e4m3fn)
+        table = torch.arange(nb, dtype=torch.int32)[None, :]
+        lens = torch.tensor([n], dtype=torch.int32)
+        cu = torch.tensor([0, n], dtype=torch.int32)
+        q = torch.randn(n, hq, D).to(torch.bfloat16)
+        name = "auto" if kv == "auto" else "fp8"
+        return (lambda: torch_views.run_paged_decode_attention(q, kc, vc, table, lens, D ** -0.5, name, 0.05, 0.05,
+                                                               cu_seqlens_q=cu, causal=True)), n, _oracle_threads()
+
+    tag = "bf16" if kv == "auto" else "fp8"
+    return OpWorkload(
+        f"prefill-{tag}", f"paged_attention_prefill_{tag}_cache_tokens_per_s",
+        f"causal paged attention of {S} whole prompts of {L} tokens, {hq} q / {hk} kv heads x {D}, cache "
+        f"{'bfloat16' if kv == 'auto' else 'fp8_e4m3'}, block_size={bs} (CPU oracle: a {256}-token prompt)",
+        S * L, 2 * S * L * hk * D * es + 2 * S * L * hq * D * 2, 1, make_steps, cpu_run,
+        flops=4.0 * S * (L * (L + 1) / 2) * hq * D)
+
+
 BY_NAME: dict[str, Callable[[], OpWorkload]] = {
     "mla-fp8": lambda: mla("fp8"),
     "gather": gather,
@@ -324,6 +393,8 @@ BY_NAME: dict[str, Callable[[], OpWorkload]] = {
     "rope-cache-fp8": lambda: rope(True),
     "decode-bf16": lambda: decode("auto"),
     "decode-fp8": lambda: decode("fp8"),
+    "prefill-bf16": lambda: prefill("auto"),
+    "prefill-fp8": lambda: prefill("fp8"),
 }
 
 

@@ -605,7 +605,7 @@ struct PrefillCfg {
 };
 
 template <typename TQ, int KV, int D>
-__global__ void __launch_bounds__(kAttnThreads) paged_prefill_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kAttnThreads, (D <= 128 ? 3 : 1)) paged_prefill_kernel(const DecodeParams p) {
   using Cfg = PrefillCfg<TQ, KV, D>;
   using T16 = typename Cfg::T16;
   constexpr bool kFp8 = KV != KVC_KV_AUTO;
@@ -625,7 +625,10 @@ __global__ void __launch_bounds__(kAttnThreads) paged_prefill_kernel(const Decod
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int seq = blockIdx.y;
-  const int kvh = blockIdx.x / p.row_tiles, row_tile = blockIdx.x - kvh * p.row_tiles;
+  // the longest rows first: under the causal mask the last row tiles of a sequence see the most tokens, and
+  // CTAs are handed out in index order
+  const int row_tile = p.row_tiles - 1 - static_cast<int>(blockIdx.x / p.num_kv_heads);
+  const int kvh = blockIdx.x % p.num_kv_heads;
   const int row0 = row_tile * kPrefillRows;
 
   pdl_prologue();
