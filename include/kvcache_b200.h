@@ -344,10 +344,10 @@ KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_h
  *                  (tests/flash_attn/test_flash_attn_varlen_func.py:79-80, :99-100 of the reference).  A row that
  *                  sees no token gives zeros.
  *
- * Built on the decode kernel: 16 (token, head) rows of one kv head per CTA, each CTA streaming the cached
- * tokens its rows may see.  That is the right shape for short query runs; a long prefill re-reads the keys and
- * values (from L2) once per 16 rows and runs far below a tensor-core-bound prefill kernel, which this library
- * does not have.  At most 65535 sequences per call.
+ * Sequences with at most 16 (token, head) rows per kv head run on the decode kernel, the others on a second
+ * kernel launched beside it in which a CTA owns 64 rows (mma.sync tiles, about 0.16-0.19 of the chip's dense
+ * bf16 GEMM rate on long prompts; a tcgen05 flash-attention kernel is not part of this library).  In such a
+ * mixed call the decode part is not split over the sequence.  At most 65535 sequences per call.
  */
 KVC_API int64_t kvc_paged_attention_workspace_bytes(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q,
                                                     int64_t num_heads, int64_t num_kv_heads, int64_t head_size,

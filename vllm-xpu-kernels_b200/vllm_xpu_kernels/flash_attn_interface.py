@@ -1,7 +1,8 @@
 """``flash_attn_varlen_func`` with the reference's signature (vllm_xpu_kernels/flash_attn_interface.py:24-125
 there), for the case this library builds: paged keys/values (``block_table`` and ``seqused_k`` given), no
 sliding window -- decode (one query token per sequence) at HBM speed, and several query tokens per sequence
-with the causal mask on the same kernel (fine for short runs, slow for long prefills).  On top of the reference,
+with the causal mask (short runs on the decode kernel, long ones on an mma.sync kernel at a fraction of the
+chip's GEMM rate).  On top of the reference,
 the cache may hold fp8 bytes: pass ``k_descale`` / ``v_descale`` (the inverse of the k_scale / v_scale the
 cache was written with), which the reference's interface names but rejects."""
 from typing import Optional
