@@ -73,6 +73,8 @@ def lib() -> ctypes.CDLL:
         L.orc_paged_decode_attention.argtypes = [vp] * 7 + [f32, f32] + [i64] * 11 + [f32, ci, ci]
         L.orc_paged_attention.restype = None
         L.orc_paged_attention.argtypes = [vp] * 8 + [f32, f32] + [i64] * 11 + [f32, ci, ci, ci]
+        L.orc_paged_attention_window.restype = None
+        L.orc_paged_attention_window.argtypes = [vp] * 8 + [f32, f32] + [i64] * 11 + [f32, ci, i64, i64, ci, ci]
         L.orc_e4m3_to_f32.restype = f32
         L.orc_e4m3_to_f32.argtypes = [ctypes.c_uint8]
         L.orc_e5m2_to_f32.restype = f32
@@ -273,12 +275,13 @@ def rotary_embedding(positions, query, key, head_size: int, cos_sin_cache, is_ne
 
 def paged_decode_attention(query, key_cache, value_cache, block_table, seq_lens, scale: float, in_dtype: str,
                            kv_cache_dtype: str = "auto", k_descale: float = 1.0, v_descale: float = 1.0,
-                           sink=None, cu_seqlens_q=None, causal: bool = False) -> np.ndarray:
+                           sink=None, cu_seqlens_q=None, causal: bool = False, window=(-1, -1)) -> np.ndarray:
     """fp32 ``[tokens, num_heads, head_size]`` result of attention over a paged cache.  ``query`` [tokens, Hq, D]
     (contiguous last dim): one token per sequence, or with ``cu_seqlens_q`` (int32 [S + 1]) the last q_len_s
     positions of each sequence, optionally under a causal mask; caches [num_blocks, block_size, Hkv, D] views
     with the same strides, of the query's type (uint16 bit patterns / float32) or uint8 fp8 bytes;
-    ``block_table`` int32 [S, max_blocks]; ``seq_lens`` int32 [S]; ``sink`` [Hq] of the query's type or None."""
+    ``block_table`` int32 [S, max_blocks]; ``seq_lens`` int32 [S]; ``sink`` [Hq] of the query's type or None;
+    ``window`` = (left, right) limits attention to positions [pos - left, pos + right], a negative side is open."""
     want = np.float32 if in_dtype == "f32" else np.uint16
     kv = KV_DTYPES[kv_cache_dtype]
     if query.dtype != want or (sink is not None and sink.dtype != want):
@@ -308,11 +311,11 @@ def paged_decode_attention(query, key_cache, value_cache, block_table, seq_lens,
     sink_c = None if sink is None else np.ascontiguousarray(sink)
     out = np.empty((T, hq, D), dtype=np.float32)
     qs, cs = _estrides(query), _estrides(key_cache)
-    lib().orc_paged_attention(
+    lib().orc_paged_attention_window(
         out.ctypes.data, query.ctypes.data, key_cache.ctypes.data, value_cache.ctypes.data, block_table.ctypes.data,
         seq_lens.ctypes.data, None if cu is None else cu.ctypes.data, None if sink_c is None else sink_c.ctypes.data,
         float(k_descale), float(v_descale), S, hq, hk, D, bs, block_table.shape[1], qs[0], qs[1], cs[0], cs[1], cs[2],
-        float(scale), int(bool(causal)), IN_DTYPES[in_dtype], kv)
+        float(scale), int(bool(causal)), int(window[0]), int(window[1]), IN_DTYPES[in_dtype], kv)
     return out
 
 

@@ -463,12 +463,13 @@ static inline float cache_elem(const void* p, int64_t i, int q_dt, int kv) {
  * A sink adds one more logit sink[h] to the softmax denominator only.  Everything is accumulated in
  * double and written as fp32: this is the ideal result, the kernels are held to a tolerance around it.
  * Strides in elements.  Rows with nothing to attend to give zeros. */
-void orc_paged_attention(float* out, const void* query, const void* key_cache, const void* value_cache,
-                         const int32_t* block_table, const int32_t* seq_lens, const int32_t* cu_seqlens_q,
-                         const void* sink, float k_descale, float v_descale, int64_t num_seqs, int64_t num_heads,
-                         int64_t num_kv_heads, int64_t head_size, int64_t block_size, int64_t block_table_stride,
-                         int64_t query_stride_t, int64_t query_stride_h, int64_t block_stride, int64_t page_stride,
-                         int64_t head_stride, float scale, int causal, int q_dt, int kv) {
+void orc_paged_attention_window(float* out, const void* query, const void* key_cache, const void* value_cache,
+                                const int32_t* block_table, const int32_t* seq_lens, const int32_t* cu_seqlens_q,
+                                const void* sink, float k_descale, float v_descale, int64_t num_seqs,
+                                int64_t num_heads, int64_t num_kv_heads, int64_t head_size, int64_t block_size,
+                                int64_t block_table_stride, int64_t query_stride_t, int64_t query_stride_h,
+                                int64_t block_stride, int64_t page_stride, int64_t head_stride, float scale,
+                                int causal, int64_t window_left, int64_t window_right, int q_dt, int kv) {
   const int64_t group = num_heads / num_kv_heads;
 #pragma omp parallel for collapse(2) schedule(dynamic)
   for (int64_t s = 0; s < num_seqs; ++s) {
@@ -478,15 +479,22 @@ void orc_paged_attention(float* out, const void* query, const void* key_cache, c
       const int64_t kvh = h / group;
       for (int64_t i = 0; i < q_len; ++i) {
         const int64_t t = t0 + i;
-        int64_t n = seq_lens[s];
-        if (causal) n = n - q_len + i + 1;
+        /* the query token sits at position pos of its sequence and sees cached tokens lo <= j < n:
+         * all of them; under the causal mask those up to pos; with a sliding window (a negative side is
+         * open) those within [pos - left, pos + right] (tests/flash_attn/test_flash_attn_varlen_func.py:81-95) */
+        const int64_t len = seq_lens[s];
+        const int64_t pos = len - q_len + i;
+        int64_t n = len, lo = 0;
+        if (causal && pos + 1 < n) n = pos + 1;
+        if (window_right >= 0 && pos + window_right + 1 < n) n = pos + window_right + 1;
+        if (window_left >= 0 && pos - window_left > lo) lo = pos - window_left;
         float* o = out + (t * num_heads + h) * head_size;
         for (int64_t d = 0; d < head_size; ++d) o[d] = 0.0f;
-        if (n <= 0) continue;
+        if (n <= lo) continue;
         double* logit = (double*)malloc((size_t)n * sizeof(double));
         double* acc = (double*)calloc((size_t)head_size, sizeof(double));
         double mx = sink ? (double)load_as_f32(sink, h, q_dt) : -INFINITY;
-        for (int64_t j = 0; j < n; ++j) {
+        for (int64_t j = lo; j < n; ++j) {
           const int64_t blk = block_table[s * block_table_stride + j / block_size];
           const int64_t base = blk * block_stride + (j % block_size) * page_stride + kvh * head_stride;
           double dot = 0.0;
@@ -497,7 +505,7 @@ void orc_paged_attention(float* out, const void* query, const void* key_cache, c
           if (logit[j] > mx) mx = logit[j];
         }
         double denom = sink ? exp((double)load_as_f32(sink, h, q_dt) - mx) : 0.0;
-        for (int64_t j = 0; j < n; ++j) {
+        for (int64_t j = lo; j < n; ++j) {
           const double p = exp(logit[j] - mx);
           denom += p;
           const int64_t blk = block_table[s * block_table_stride + j / block_size];
@@ -510,6 +518,19 @@ void orc_paged_attention(float* out, const void* query, const void* key_cache, c
       }
     }
   }
+}
+
+/* No sliding window. */
+void orc_paged_attention(float* out, const void* query, const void* key_cache, const void* value_cache,
+                         const int32_t* block_table, const int32_t* seq_lens, const int32_t* cu_seqlens_q,
+                         const void* sink, float k_descale, float v_descale, int64_t num_seqs, int64_t num_heads,
+                         int64_t num_kv_heads, int64_t head_size, int64_t block_size, int64_t block_table_stride,
+                         int64_t query_stride_t, int64_t query_stride_h, int64_t block_stride, int64_t page_stride,
+                         int64_t head_stride, float scale, int causal, int q_dt, int kv) {
+  orc_paged_attention_window(out, query, key_cache, value_cache, block_table, seq_lens, cu_seqlens_q, sink, k_descale,
+                             v_descale, num_seqs, num_heads, num_kv_heads, head_size, block_size, block_table_stride,
+                             query_stride_t, query_stride_h, block_stride, page_stride, head_stride, scale, causal, -1,
+                             -1, q_dt, kv);
 }
 
 /* One query token per sequence: the decode case. */

@@ -58,12 +58,12 @@ def run_rope(positions, query, key, head_size: int, cos_sin_cache, is_neox: bool
 
 def run_paged_decode_attention(query, key_cache, value_cache, block_table, seq_lens, scale: float,
                                kv_cache_dtype: str = "auto", k_descale: float = 1.0, v_descale: float = 1.0,
-                               sink=None, cu_seqlens_q=None, causal: bool = False) -> torch.Tensor:
+                               sink=None, cu_seqlens_q=None, causal: bool = False, window=(-1, -1)) -> torch.Tensor:
     """fp32 [tokens, Hq, D] result of the oracle's paged attention on CPU torch tensors (one query token per
     sequence unless ``cu_seqlens_q`` says otherwise)."""
     import oracle
     out = oracle.paged_decode_attention(
         as_np(query), as_np(key_cache), as_np(value_cache), block_table.numpy(), seq_lens.numpy(), scale,
         ORC_IN[query.dtype], kv_cache_dtype, k_descale, v_descale, None if sink is None else as_np(sink),
-        None if cu_seqlens_q is None else cu_seqlens_q.numpy(), causal)
+        None if cu_seqlens_q is None else cu_seqlens_q.numpy(), causal, window)
     return torch.from_numpy(out)

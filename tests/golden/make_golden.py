@@ -279,7 +279,8 @@ def make_rope_case(RotaryEmbedding, dtype: str, is_neox: bool, head_size: int, r
 
 def make_decode_attn_case(ref_paged_attn, dtype: str, num_heads: int, num_kv_heads: int, head_size: int,
                           kv_lens: list, block_size: int, num_blocks: int, with_sink: bool, kv_cache_dtype: str,
-                          descale: float, seed: int, query_lens: list | None = None, causal: bool = False) -> dict:
+                          descale: float, seed: int, query_lens: list | None = None, causal: bool = False,
+                          window: tuple = (-1, -1), paged: bool = True) -> dict:
     """Inputs as in test_decode_with_paged_kv of the reference (tests/flash_attn/test_flash_attn_varlen_func.py:
     274-372: one query token per sequence, randn query and caches, randint block tables, optional randn sink);
     expected = its ref_paged_attn on the CPU.  For an fp8 cache the caches are first cast to fp8; the reference
@@ -289,7 +290,10 @@ def make_decode_attn_case(ref_paged_attn, dtype: str, num_heads: int, num_kv_hea
     num_seqs = len(kv_lens)
     query_lens = query_lens or [1] * num_seqs
     query = torch.randn(sum(query_lens), num_heads, head_size, dtype=tdt)
-    key_cache = torch.randn(num_blocks, block_size, num_kv_heads, head_size, dtype=tdt)
+    if paged:
+        key_cache = torch.randn(num_blocks, block_size, num_kv_heads, head_size, dtype=tdt)
+    else:  # keys/values of all sequences back to back: [sum(kv_lens), heads, head_size]
+        key_cache = torch.randn(sum(kv_lens), num_kv_heads, head_size, dtype=tdt)
     value_cache = torch.randn_like(key_cache)
     max_blocks = (max(kv_lens) + block_size - 1) // block_size
     block_tables = torch.randint(0, num_blocks, (num_seqs, max_blocks), dtype=torch.int32)
@@ -303,11 +307,13 @@ def make_decode_attn_case(ref_paged_attn, dtype: str, num_heads: int, num_kv_hea
     scale = head_size ** -0.5
     expected = ref_paged_attn(query=query.clone(), key_cache=key_cache, value_cache=value_cache,
                               query_lens=query_lens, kv_lens=kv_lens, block_tables=block_tables, scale=scale,
-                              casual=causal, is_paged=True, sink=sink, window_size_left=-1, window_size_right=-1)
+                              casual=causal, is_paged=paged, sink=sink, window_size_left=window[0],
+                              window_size_right=window[1])
     d = dict(op="decode_attn", dtype=dtype, kv_cache_dtype=kv_cache_dtype, query=bits(query),
              key_cache=bits(stored_k), value_cache=bits(stored_v), block_tables=block_tables.numpy(),
              kv_lens=np.array(kv_lens, dtype=np.int32), query_lens=np.array(query_lens, dtype=np.int32),
-             causal=np.bool_(causal), scale=np.float32(scale), descale=np.float32(descale), expected=bits(expected))
+             causal=np.bool_(causal), window=np.array(window, dtype=np.int64), paged=np.bool_(paged),
+             scale=np.float32(scale), descale=np.float32(descale), expected=bits(expected))
     if with_sink:
         d["sink"] = bits(sink)
     return d
@@ -436,6 +442,22 @@ def main() -> None:
                                                          "_causal" if causal else "")
         extra.append((name, lambda a=(dtype, hq, hk, D, [k for _, k in lens], bs, nb, sink, kv, descale, ai,
                                        [q for q, _ in lens], causal): make_decode_attn_case(ref_paged_attn, *a)))
+    # sliding windows (the reference's SLIDING_WINDOWS, tests/flash_attn/test_flash_attn_varlen_func.py:20) and the
+    # non-paged form (keys/values of all sequences back to back, as many kv heads as query heads, :183-187)
+    for dtype, hq, hk, D, lens, bs, nb, sink, causal, window, paged in (
+            ("bfloat16", 8, 2, 128, [(1, 328), (5, 18), (129, 263)], 16, 24, False, False, (-1, 127), True),
+            ("half", 8, 2, 64, [(1, 328), (5, 18), (129, 263)], 16, 24, True, True, (127, -1), True),
+            ("bfloat16", 4, 4, 64, [(1, 328), (5, 18), (129, 263)], 16, 24, False, True, (127, 127), True),
+            ("half", 10, 2, 128, [(1, 700), (40, 300)], 32, 24, True, False, (63, 0), True),
+            ("bfloat16", 4, 4, 64, [(1, 328), (5, 18), (129, 263)], 16, 24, False, True, (-1, -1), False),
+            ("half", 4, 4, 128, [(129, 263), (1, 40)], 16, 24, True, False, (-1, -1), False)):
+        ai += 1
+        name = "window_attn_%s_Hq%d_Hk%d_D%d%s%s_w%s_%s%s" % (
+            dtype, hq, hk, D, "_sink" if sink else "", "_causal" if causal else "",
+            str(window[0]).replace("-", "m"), str(window[1]).replace("-", "m"), "" if paged else "_dense")
+        extra.append((name, lambda a=(dtype, hq, hk, D, [k for _, k in lens], bs, nb, sink, "auto", 1.0, ai,
+                                       [q for q, _ in lens], causal, window, paged):
+                      make_decode_attn_case(ref_paged_attn, *a)))
     for name, data in extra:
         names.append(name)
         if wanted(name):

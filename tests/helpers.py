@@ -22,7 +22,7 @@ def golden_files(kind: str = "kv") -> list[str]:
         names = [ln.strip() for ln in f if ln.strip() and not ln.startswith("#")]
     prefixes = {"kv": ("flash_", "paged_"), "mla": ("mla_",), "gather": ("gather_",), "quant": ("quant_",),
                 "rope": ("rope_",), "decode_attn": ("decode_attn_",),
-                "varlen_attn": ("varlen_attn_",)}[kind]
+                "varlen_attn": ("varlen_attn_",), "window_attn": ("window_attn_",)}[kind]
     return [n for n in names if n.startswith(prefixes)]
 
 
@@ -105,6 +105,18 @@ class DecodeAttnCase:
         self.causal = bool(z["causal"])
         self.cu_seqlens_q = torch.cat([torch.zeros(1, dtype=torch.int32),
                                        torch.cumsum(self.query_lens, 0).to(torch.int32)])
+        self.window = tuple(int(x) for x in z["window"]) if "window" in z.files else (-1, -1)
+        self.paged = bool(z["paged"]) if "paged" in z.files else True
+        if not self.paged:
+            # keys/values of all sequences back to back [total_k, H, D]: the same thing as a cache of one-token
+            # blocks with the identity table block_tables[s][j] = cu_seqlens_k[s] + j
+            self.cu_seqlens_k = torch.cat([torch.zeros(1, dtype=torch.int32),
+                                           torch.cumsum(self.kv_lens, 0).to(torch.int32)])
+            self.dense_key, self.dense_value = self.key_cache, self.value_cache
+            self.key_cache, self.value_cache = self.key_cache[:, None], self.value_cache[:, None]
+            j = torch.arange(int(self.kv_lens.max()), dtype=torch.int32)[None, :]
+            self.block_tables = torch.minimum(self.cu_seqlens_k[:-1, None] + j,
+                                              torch.tensor(self.key_cache.shape[0] - 1, dtype=torch.int32))
 
 
 # The reference's own tolerance for this op (tests/flash_attn/test_flash_attn_varlen_func.py:265, :386).

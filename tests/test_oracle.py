@@ -91,6 +91,16 @@ def test_oracle_reproduces_reference_varlen_attention_fixture(fname):
     torch.testing.assert_close(got, c.expected.float(), atol=H.ATTN_ATOL, rtol=H.ATTN_RTOL)
 
 
+@pytest.mark.parametrize("fname", H.golden_files("window_attn"))
+def test_oracle_reproduces_reference_window_and_dense_attention_fixture(fname):
+    """Sliding windows (one side open, both closed, with and without the causal mask) and the non-paged form."""
+    c = H.DecodeAttnCase(fname)
+    got = torch_views.run_paged_decode_attention(c.query, c.key_cache, c.value_cache, c.block_tables, c.kv_lens,
+                                                 c.scale, c.kv_cache_dtype, c.descale, c.descale, c.sink,
+                                                 c.cu_seqlens_q, c.causal, c.window)
+    torch.testing.assert_close(got, c.expected.float(), atol=H.ATTN_ATOL, rtol=H.ATTN_RTOL)
+
+
 def test_decode_attention_shards_by_kv_head():
     """Tensor parallelism over kv heads: each rank holds its kv heads' cache slice and the query heads of those
     groups; concatenating the ranks' outputs along the head axis gives the unsharded result (nothing is exchanged)."""
