@@ -332,9 +332,10 @@ KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_h
                                                  int64_t head_size, int64_t max_seq_len, int q_dtype, int kv_dtype);
 
 /*
- * The same over several query tokens per sequence (a chunk of a prefill, speculative tokens): the paged case of
- * mha_varlen_fwd with max_seqlen_q > 1 and no window (csrc/flash_attn/flash_api.cpp:105-123 routes it to the
- * reference's chunked-prefill kernel).
+ * The same over several query tokens per sequence (a chunk of a prefill, speculative tokens) and with sliding
+ * windows: what mha_varlen_fwd routes to the reference's chunked-prefill kernel (csrc/flash_attn/
+ * flash_api.cpp:105-123: max_seqlen_q > 1 or local attention).  Its non-paged form is the case block_size = 1
+ * with block_table[s][j] = cu_seqlens_k[s] + j.
  *
  *   query, out     [total_q, num_heads, head_size]; sequence s owns tokens cu_seqlens_q[s] .. cu_seqlens_q[s+1]
  *   cu_seqlens_q   int32 [num_seqs + 1] on the device; NULL means one token per sequence (the decode call above)
@@ -343,6 +344,8 @@ KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_h
  *                  of them sees the first seq_lens[s] - q_len + i + 1 cached tokens, else all seq_lens[s]
  *                  (tests/flash_attn/test_flash_attn_varlen_func.py:79-80, :99-100 of the reference).  A row that
  *                  sees no token gives zeros.
+ *   window_left,   sliding window: the query token at position pos sees cached positions pos - window_left ..
+ *   window_right   pos + window_right; -1 leaves a side open (test_flash_attn_varlen_func.py:81-95)
  *
  * Sequences with at most 16 (token, head) rows per kv head run on the decode kernel, the others on a second
  * kernel launched beside it in which a CTA owns 64 rows (mma.sync tiles, about 0.16-0.19 of the chip's dense
@@ -360,7 +363,8 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
                                 int64_t block_table_stride, int64_t max_seq_len, int64_t query_stride_t,
                                 int64_t query_stride_h, int64_t out_stride_t, int64_t out_stride_h,
                                 int64_t block_stride, int64_t page_stride, int64_t head_stride, float softmax_scale,
-                                int causal, int q_dtype, int kv_dtype, void* stream);
+                                int causal, int64_t window_left, int64_t window_right, int q_dtype, int kv_dtype,
+                                void* stream);
 KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void* key_cache, const void* value_cache,
                                        const int32_t* block_table, const int32_t* seq_lens, const void* sink,
                                        const float* k_descale, const float* v_descale, void* workspace,

@@ -284,10 +284,10 @@ def test_attention_ops_pass_opcheck_and_refuse_what_is_not_built(cuda_device):
                                   causal=True)
     out4 = flash_attn_varlen_func(q, kc, vc, 1, cu_q, 200, seqused_k=lens, softmax_scale=0.125, block_table=bt)
     torch.testing.assert_close(out3.float(), out4.float(), **TOL)
-    # local attention is refused, loudly
-    with pytest.raises(RuntimeError, match="without a sliding window"):
+    # what is not built is refused, loudly
+    with pytest.raises(RuntimeError, match="softcap"):
         flash_attn_varlen_func(q, kc, vc, 1, cu_q, 200, seqused_k=lens, softmax_scale=0.125, block_table=bt,
-                               window_size=[127, -1])
+                               softcap=30.0)
     with pytest.raises(RuntimeError, match="page_table must have dtype torch.int32"):
         flash_attn_varlen_func(q, kc, vc, 1, cu_q, 200, seqused_k=lens, softmax_scale=0.125, block_table=bt.long())
     with pytest.raises(RuntimeError, match="only supports fp16 and bf16"):
@@ -405,3 +405,71 @@ def test_varlen_attention_long_chunk(cuda_device):
     torch.cuda.synchronize()
     want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, D ** -0.5, cu_seqlens_q=cu, causal=True)
     torch.testing.assert_close(out.cpu().float(), want, **TOL)
+
+
+# ------------------------------------------------------------------------------------ sliding windows, non-paged form
+@pytest.mark.parametrize("fname", H.golden_files("window_attn"))
+@pytest.mark.parametrize("face", ["cabi", "interface"])
+def test_window_and_dense_attention_golden(fname, face, cuda_device):
+    """Fixtures from the reference's ref_paged_attn: windows (-1, 127), (127, -1), (127, 127), (63, 0) and the
+    non-paged form, which the C ABI takes as a cache of one-token blocks and the interface as cu_seqlens_k."""
+    dev = cuda_device
+    c = H.DecodeAttnCase(fname)
+    sink = None if c.sink is None else c.sink.to(dev)
+    if face == "cabi":
+        out = cabi.paged_attention(c.query.to(dev), c.key_cache.to(dev), c.value_cache.to(dev), c.block_tables.to(dev),
+                                   c.kv_lens.to(dev), c.cu_seqlens_q.to(dev), int(c.query_lens.max()), c.scale,
+                                   int(c.kv_lens.max()), c.causal, sink=sink, window=c.window)
+    elif c.paged:
+        out = flash_attn_varlen_func(c.query.to(dev), c.key_cache.to(dev), c.value_cache.to(dev),
+                                     int(c.query_lens.max()), c.cu_seqlens_q.to(dev), int(c.kv_lens.max()),
+                                     seqused_k=c.kv_lens.to(dev), softmax_scale=c.scale, causal=c.causal,
+                                     block_table=c.block_tables.to(dev), window_size=list(c.window), s_aux=sink)
+    else:
+        out = flash_attn_varlen_func(c.query.to(dev), c.dense_key.to(dev), c.dense_value.to(dev),
+                                     int(c.query_lens.max()), c.cu_seqlens_q.to(dev), int(c.kv_lens.max()),
+                                     cu_seqlens_k=c.cu_seqlens_k.to(dev), softmax_scale=c.scale, causal=c.causal,
+                                     block_table=None, window_size=list(c.window), s_aux=sink)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.cpu().float(), c.expected.float(), **TOL)
+
+
+@pytest.mark.parametrize("window", [(-1, 127), (127, -1), (127, 127), (0, 0), (1000, 3)])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("kv", ["auto", "fp8"])
+def test_window_attention_vs_oracle(window, causal, kv, cuda_device):
+    """The reference's SLIDING_WINDOWS over its sequence list plus long decodes (the window then starts far into
+    the sequence: whole tiles and splits are skipped), 16-bit and fp8 caches."""
+    dev = cuda_device
+    hq, hk, D, bs, nb = 8, 2, 128, 64, 256
+    q_lens, kv_lens = [1, 5, 129, 1, 1], [1328, 18, 463, 9000, 130]
+    torch.manual_seed(70)
+    query = torch.randn(sum(q_lens), hq, D).to(torch.bfloat16)
+    ds = 0.04 if kv != "auto" else 1.0  # descales only exist for fp8 caches
+    _, kc, vc, bt, lens, sk = make_case(torch.bfloat16, hq, hk, D, kv_lens, bs, nb, True, seed=71, kv=kv, descale=ds)
+    cu = cu_of(q_lens)
+    kcd, vcd = (kc.view(torch.uint8), vc.view(torch.uint8)) if kv != "auto" else (kc, vc)
+    out = cabi.paged_attention(query.to(dev), kcd.to(dev), vcd.to(dev), bt.to(dev), lens.to(dev), cu.to(dev), 129, 0.09,
+                               9000, causal, kv, dscalar(ds, dev), dscalar(ds, dev), sk.to(dev), window=window)
+    torch.cuda.synchronize()
+    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, 0.09, kv, ds, ds, sk, cu, causal, window)
+    torch.testing.assert_close(out.cpu().float(), want, **TOL)
+
+
+def test_window_decode_with_splits(cuda_device):
+    """Pure decode (no cu_seqlens_q through the decode entry's kernel path) with a left window on long sequences:
+    the split covers the window, not the sequence."""
+    dev = cuda_device
+    hq, hk, D, bs, nb = 16, 2, 128, 16, 1200
+    kv_lens = [16000, 5000, 300, 40]
+    torch.manual_seed(72)
+    query = torch.randn(4, hq, D).to(torch.float16)
+    _, kc, vc, bt, lens, _ = make_case(torch.float16, hq, hk, D, kv_lens, bs, nb, False, seed=73)
+    cu = cu_of([1, 1, 1, 1])
+    for window in [(2047, -1), (4095, 0), (511, 511)]:
+        out = cabi.paged_attention(query.to(dev), kc.to(dev), vc.to(dev), bt.to(dev), lens.to(dev), cu.to(dev), 1, 0.09,
+                                   16000, True, window=window)
+        torch.cuda.synchronize()
+        want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, 0.09, cu_seqlens_q=cu, causal=True,
+                                                      window=window)
+        torch.testing.assert_close(out.cpu().float(), want, **TOL)

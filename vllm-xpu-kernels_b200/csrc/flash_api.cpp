@@ -1,10 +1,10 @@
 // Torch-facing launcher of the paged decode attention, registered under `_vllm_fa2_C` like the
 // reference's attention op.  Counterpart in the reference: mha_varlen_fwd, csrc/flash_attn/flash_api.cpp:10-176
-// (decode branch :124-165) and its schema :179-193.  The paged case without a sliding window is built: the
-// decode branch (one query token per sequence) and, on the same kernel, several query tokens per sequence
-// with the causal mask.  The non-paged and local-attention cases raise an error instead of computing anything.
+// (decode branch :124-165) and its schema :179-193.  Both branches are served: one query token per sequence
+// (decode) and several, with the causal mask and sliding windows; the non-paged form runs as a cache of
+// one-token blocks.  alibi, softcap, dropout and the softmax output are refused.
 #include <ATen/core/Tensor.h>
-#include <ATen/ops/empty.h>
+#include <ATen/ATen.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
@@ -21,7 +21,8 @@ void paged_decode_impl(const char* op, const at::Tensor& q, const at::Tensor& k_
                        at::Tensor& out, const at::Tensor& seqused_k, const at::Tensor& block_table,
                        int64_t max_seqlen_k, double softmax_scale, const std::optional<at::Tensor>& sink, int kv,
                        const std::optional<at::Tensor>& k_descale, const std::optional<at::Tensor>& v_descale,
-                       const std::optional<at::Tensor>& cu_seqlens_q, int64_t max_seqlen_q, bool causal) {
+                       const std::optional<at::Tensor>& cu_seqlens_q, int64_t max_seqlen_q, bool causal,
+                       int64_t window_left, int64_t window_right) {
   TORCH_CHECK(q.is_cuda(), op, ": query must be a CUDA tensor (this build has no CPU path)");
   const auto dev = q.device();
   const auto qt = q.scalar_type();
@@ -82,7 +83,7 @@ void paged_decode_impl(const char* op, const at::Tensor& q, const at::Tensor& k_
       seqused_k.data_ptr<int32_t>(), cu_q, sink_ptr, kd, vd, ws_bytes > 0 ? ws.data_ptr() : nullptr, ws_bytes, num_seqs,
       q.size(0), max_seqlen_q, q.size(1), k_cache.size(2), q.size(2), k_cache.size(1), block_table.stride(0),
       max_seqlen_k, q.stride(0), q.stride(1), out.stride(0), out.stride(1), k_cache.stride(0), k_cache.stride(1),
-      k_cache.stride(2), static_cast<float>(softmax_scale), causal ? 1 : 0, in, kv,
+      k_cache.stride(2), static_cast<float>(softmax_scale), causal ? 1 : 0, window_left, window_right, in, kv,
       c10::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == KVC_OK, op, ": ", kvc_last_error());
 }
@@ -98,20 +99,40 @@ std::vector<at::Tensor> mha_varlen_fwd(const at::Tensor& q, const at::Tensor& k,
                                        int64_t window_size_left, int64_t window_size_right, double softcap,
                                        bool return_softmax, std::optional<at::Generator> gen_) {
   constexpr const char* op = "varlen_fwd";
-  (void)cu_seqlens_k;
   (void)zero_tensors;
   (void)gen_;
-  const bool is_local = window_size_left != -1 || window_size_right != -1;
-  TORCH_CHECK(block_table_.has_value() && seqused_k.has_value() && !is_local, op,
-              ": only the paged case without a sliding window is built (block_table and seqused_k given); the "
-              "non-paged and the local-attention cases of the reference are not");
   TORCH_CHECK(!alibi_slopes_.has_value() && !leftpad_k_.has_value() && softcap == 0.0 && p_dropout == 0.0 &&
                   !return_softmax,
               op, ": alibi_slopes, leftpad_k, softcap, dropout and return_softmax are not supported");
   TORCH_CHECK(cu_seqlens_q.scalar_type() == at::kInt, "cu_seqlens_q must have dtype torch.int32");
+  // as in the reference's statement, a window exists only if one side is positive; a negative side is open
+  // (tests/flash_attn/test_flash_attn_varlen_func.py:81-85 there)
+  const bool is_local = window_size_left > 0 || window_size_right > 0;
+  const int64_t wl = is_local && window_size_left >= 0 ? window_size_left : -1;
+  const int64_t wr = is_local && window_size_right >= 0 ? window_size_right : -1;
   at::Tensor out = out_.has_value() ? *out_ : at::empty(q.sizes(), q.options());
-  paged_decode_impl(op, q, k, v, out, *seqused_k, *block_table_, max_seqlen_k, softmax_scale, softmax_sink_,
-                    KVC_KV_AUTO, std::nullopt, std::nullopt, cu_seqlens_q, max_seqlen_q, is_causal);
+  if (block_table_.has_value()) {
+    TORCH_CHECK(seqused_k.has_value(), op, ": seqused_k is needed with a block_table");
+    paged_decode_impl(op, q, k, v, out, *seqused_k, *block_table_, max_seqlen_k, softmax_scale, softmax_sink_,
+                      KVC_KV_AUTO, std::nullopt, std::nullopt, cu_seqlens_q, max_seqlen_q, is_causal, wl, wr);
+  } else {
+    // Non-paged form: k, v are [total_k, heads, head_size], sequence s owning rows cu_seqlens_k[s] ..
+    // cu_seqlens_k[s+1].  That is a cache of one-token blocks with the table block_table[s][j] = cu_seqlens_k[s] + j.
+    TORCH_CHECK(k.dim() == 3 && v.dim() == 3, op, ": without a block_table key and value are [total_k, heads, head_size]");
+    TORCH_CHECK(cu_seqlens_k.scalar_type() == at::kInt && cu_seqlens_k.is_contiguous() &&
+                    cu_seqlens_k.numel() == cu_seqlens_q.numel() && cu_seqlens_k.device() == q.device(),
+                "cu_seqlens_k must have dtype torch.int32");
+    const int64_t num_seqs = cu_seqlens_k.numel() - 1;
+    const int64_t total_k = k.size(0);
+    at::Tensor starts = cu_seqlens_k.slice(0, 0, num_seqs);
+    at::Tensor lens = cu_seqlens_k.slice(0, 1, num_seqs + 1) - starts;
+    at::Tensor table = (starts.unsqueeze(1) + at::arange(std::max<int64_t>(max_seqlen_k, 1), starts.options()).unsqueeze(0))
+                           .clamp_max(std::max<int64_t>(total_k - 1, 0))
+                           .contiguous();
+    at::Tensor k4 = k.unsqueeze(1), v4 = v.unsqueeze(1);
+    paged_decode_impl(op, q, k4, v4, out, lens.contiguous(), table, max_seqlen_k, softmax_scale, softmax_sink_,
+                      KVC_KV_AUTO, std::nullopt, std::nullopt, cu_seqlens_q, max_seqlen_q, is_causal, wl, wr);
+  }
   return {out, at::empty({0}, q.options().dtype(at::kFloat))};
 }
 
@@ -138,10 +159,13 @@ void paged_decode_attention(const at::Tensor& q, const at::Tensor& k_cache, cons
                             double softmax_scale, std::optional<at::Tensor> softmax_sink,
                             const std::string& kv_cache_dtype, std::optional<at::Tensor> k_descale,
                             std::optional<at::Tensor> v_descale, std::optional<at::Tensor> cu_seqlens_q,
-                            int64_t max_seqlen_q, bool is_causal) {
+                            int64_t max_seqlen_q, bool is_causal, int64_t window_size_left,
+                            int64_t window_size_right) {
+  const bool is_local = window_size_left > 0 || window_size_right > 0;
   paged_decode_impl("paged_decode_attention", q, k_cache, v_cache, out, seqused_k, block_table, max_seqlen_k,
                     softmax_scale, softmax_sink, vllm::kvc_kv_dtype_of(kv_cache_dtype), k_descale, v_descale,
-                    cu_seqlens_q, max_seqlen_q, is_causal);
+                    cu_seqlens_q, max_seqlen_q, is_causal, is_local && window_size_left >= 0 ? window_size_left : -1,
+                    is_local && window_size_right >= 0 ? window_size_right : -1);
 }
 
 }  // namespace
@@ -160,8 +184,8 @@ KVC_TORCH_LIBRARY(_vllm_fa2_C, m) {
   m.def(
       "paged_decode_attention(Tensor q, Tensor k_cache, Tensor v_cache, Tensor! out, Tensor seqused_k, "
       "Tensor block_table, int max_seqlen_k, float softmax_scale, Tensor? softmax_sink, str kv_cache_dtype, "
-      "Tensor? k_descale, Tensor? v_descale, Tensor? cu_seqlens_q=None, int max_seqlen_q=1, bool is_causal=False) "
-      "-> ()");
+      "Tensor? k_descale, Tensor? v_descale, Tensor? cu_seqlens_q=None, int max_seqlen_q=1, bool is_causal=False, "
+      "int window_size_left=-1, int window_size_right=-1) -> ()");
 }
 
 KVC_TORCH_LIBRARY_IMPL(_vllm_fa2_C, Meta, m) { m.impl("varlen_fwd", &mha_varlen_fwd_meta); }

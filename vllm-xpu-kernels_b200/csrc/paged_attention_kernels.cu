@@ -129,6 +129,8 @@ struct DecodeParams {
   int32_t num_splits, tiles_per_split;
   int32_t causal;  // query token i of q_len sees the first seq_len - q_len + i + 1 cached tokens
   int32_t many_rows_elsewhere;  // sequences with more than 16 rows per kv head are handled by paged_prefill_kernel
+  // sliding window: the query token at position pos sees cached positions [pos - left, pos + right]; -1 = open
+  int32_t window_left, window_right;
   float softmax_scale;
 };
 
@@ -226,12 +228,23 @@ paged_decode_kernel(const DecodeParams p) {
   auto row_head = [&](int r) { return kvh * p.group + (row0 + r) % p.group; };
 
   const int n = p.seq_lens[seq];
-  // cached tokens row r may see; the CTA walks up to the largest limit among its rows (the last row's)
-  auto row_limit = [&](int r) { return p.causal ? max(0, min(n, n - q_len + row_token(r) + 1)) : n; };
+  // Cached tokens row r may see: [row_lo(r), row_limit(r)).  The query token of the row sits at position
+  // pos = n - q_len + token; the causal mask ends its view at pos, a window at pos + right, and a window starts
+  // it at pos - left.  Both ends grow with the token, so the CTA walks from its first row's start to its last
+  // row's end.
+  auto row_limit = [&](int r) {
+    const int pos = n - q_len + row_token(r);
+    int hi = n;
+    if (p.causal) hi = min(hi, pos + 1);
+    if (p.window_right >= 0) hi = min(hi, pos + p.window_right + 1);
+    return max(0, hi);
+  };
+  auto row_lo = [&](int r) { return p.window_left >= 0 ? max(0, n - q_len + row_token(r) - p.window_left) : 0; };
   const int n_item = row_limit(rows - 1);
   const int lim_min = row_limit(0);
+  const int lo_max = row_lo(rows - 1);
   const int total_tiles = (n_item + TN - 1) / TN;
-  const int tile_begin = split * p.tiles_per_split;
+  const int tile_begin = row_lo(0) / TN + split * p.tiles_per_split;
   const int tile_end = min(tile_begin + p.tiles_per_split, total_tiles);
 
   if (tile_begin >= tile_end) {  // nothing to attend to in this split's range
@@ -325,6 +338,7 @@ paged_decode_kernel(const DecodeParams p) {
   const float lazy_margin = 8.0f / scale2;  // raw-logit distance that is worth a factor 2^8
   // cached tokens visible to this lane's rows g and g + 8 (padding rows: the CTA's limit; they are never stored)
   const int lim[2] = {g < rows ? row_limit(g) : n_item, g + 8 < rows ? row_limit(g + 8) : n_item};
+  const int lo[2] = {g < rows ? row_lo(g) : 0, g + 8 < rows ? row_lo(g + 8) : 0};
   float m_run[2] = {-INFINITY, -INFINITY};  // reference point (a lagging maximum) of the raw logits of rows g, g + 8
   float l_run[2] = {0.f, 0.f};              // this lane's share of the running sums of rows g and g + 8
   // rows g (c0, c1) / g + 8 (c2, c3); columns of tile i: 16-bit cache  8i + 2t, + 1
@@ -413,15 +427,17 @@ paged_decode_kernel(const DecodeParams p) {
     }
 
     // ---- mask the tail, running maximum (of the raw logits: the scale is positive), P = 2^(scale (S - m)) --
-    if ((tile + 1) * TN > lim_min) {  // only the tiles that reach past some row's limit have tokens to mask
+    if ((tile + 1) * TN > lim_min || tile * TN < lo_max) {  // only tiles that cross some row's ends need masking
 #pragma unroll
       for (int gi = 0; gi < NG; ++gi) {
         const int tok_base = tile * TN + gi * 64 + warp * 16 + 2 * t;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (tok_base + nt * 8 + (e & 1) >= lim[e >> 1]) s_acc[gi][nt][e] = -INFINITY;
+          for (int e = 0; e < 4; ++e) {
+            const int token = tok_base + nt * 8 + (e & 1);
+            if (token >= lim[e >> 1] || token < lo[e >> 1]) s_acc[gi][nt][e] = -INFINITY;
+          }
         }
       }
     }
@@ -641,17 +657,25 @@ __global__ void __launch_bounds__(kAttnThreads, (D <= 128 ? 3 : 1)) paged_prefil
   auto row_token = [&](int r) { return (row0 + r) / p.group; };
   auto row_head = [&](int r) { return kvh * p.group + (row0 + r) % p.group; };
   const int n = p.seq_lens[seq];
-  auto row_limit = [&](int r) { return p.causal ? max(0, min(n, n - q_len + row_token(r) + 1)) : n; };
+  auto row_limit = [&](int r) {  // cached tokens row r may see: [row_lo(r), row_limit(r)), as in the decode kernel
+    const int pos = n - q_len + row_token(r);
+    int hi = n;
+    if (p.causal) hi = min(hi, pos + 1);
+    if (p.window_right >= 0) hi = min(hi, pos + p.window_right + 1);
+    return max(0, hi);
+  };
+  auto row_lo = [&](int r) { return p.window_left >= 0 ? max(0, n - q_len + row_token(r) - p.window_left) : 0; };
   const int n_item = row_limit(rows - 1);
   const int lim_min = row_limit(0);
+  const int lo_max = row_lo(rows - 1);
   const int tile_end = (n_item + TN - 1) / TN;
-  constexpr int tile_begin = 0;
+  const int tile_begin = row_lo(0) / TN;
 
   // this lane's rows: 16 warp + g and + 8
   const int my_row[2] = {warp * 16 + g, warp * 16 + g + 8};
   const bool warp_has_rows = warp * 16 < rows;
 
-  if (tile_end <= 0) {  // no row sees any token
+  if (tile_end <= tile_begin) {  // no row sees any token
     for (int i = tid; i < rows * D; i += kAttnThreads) {
       const int r = i / D;
       static_cast<TQ*>(p.out)[static_cast<int64_t>(q_start + row_token(r)) * p.out_stride_t +
@@ -734,8 +758,11 @@ __global__ void __launch_bounds__(kAttnThreads, (D <= 128 ? 3 : 1)) paged_prefil
   const float scale2 = p.softmax_scale * kLog2e * ((kFp8 && p.k_descale) ? __ldg(p.k_descale) : 1.0f);
   const float lazy_margin = 8.0f / scale2;
   const int lim[2] = {my_row[0] < rows ? row_limit(my_row[0]) : 0, my_row[1] < rows ? row_limit(my_row[1]) : 0};
-  // the warp stops computing where its last valid row's limit ends (it keeps helping with the copies)
+  const int lo[2] = {my_row[0] < rows ? row_lo(my_row[0]) : 0, my_row[1] < rows ? row_lo(my_row[1]) : 0};
+  // the warp computes only between its first row's start and its last valid row's end (it keeps helping with
+  // the copies outside that range)
   const int warp_limit = warp_has_rows ? row_limit(min(rows, warp * 16 + 16) - 1) : 0;
+  const int warp_lo = warp_has_rows ? row_lo(warp * 16) : 0;
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.f, 0.f};
   float o_acc[NT][4];
@@ -775,7 +802,7 @@ __global__ void __launch_bounds__(kAttnThreads, (D <= 128 ? 3 : 1)) paged_prefil
     if (tile + NST - 1 < tile_end) load_tile(tile + NST - 1);
     cp_async_commit();
     publish_offsets(tile + NST);
-    if (tile * TN >= warp_limit) continue;  // nothing left for this warp's rows (warp-uniform)
+    if (tile * TN >= warp_limit || (tile + 1) * TN <= warp_lo) continue;  // nothing here for this warp's rows
     const uint32_t ks = smem_u32(s_kv + slot * 2 * Cfg::kTileBytes);
     const uint32_t vs = ks + Cfg::kTileBytes;
 
@@ -815,15 +842,17 @@ __global__ void __launch_bounds__(kAttnThreads, (D <= 128 ? 3 : 1)) paged_prefil
       }
     }
 
-    if ((tile + 1) * TN > lim_min) {  // some row of the CTA has tokens to mask in this tile
+    if ((tile + 1) * TN > lim_min || tile * TN < lo_max) {  // some row of the CTA has tokens to mask in this tile
 #pragma unroll
       for (int gi = 0; gi < NG; ++gi) {
         const int tok_base = tile * TN + gi * 16 + 2 * t;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            if (tok_base + nt * 8 + (e & 1) >= lim[e >> 1]) s_acc[gi][nt][e] = -INFINITY;
+          for (int e = 0; e < 4; ++e) {
+            const int token = tok_base + nt * 8 + (e & 1);
+            if (token >= lim[e >> 1] || token < lo[e >> 1]) s_acc[gi][nt][e] = -INFINITY;
+          }
         }
       }
     }
@@ -1230,8 +1259,11 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
                                 int64_t block_table_stride, int64_t max_seq_len, int64_t query_stride_t,
                                 int64_t query_stride_h, int64_t out_stride_t, int64_t out_stride_h,
                                 int64_t block_stride, int64_t page_stride, int64_t head_stride, float softmax_scale,
-                                int causal, int q_dtype, int kv_dtype, void* stream) {
+                                int causal, int64_t window_left, int64_t window_right, int q_dtype, int kv_dtype,
+                                void* stream) {
   using namespace kvc;
+  if (window_left < -1 || window_right < -1 || window_left > 0x7FFFFFFFll || window_right > 0x7FFFFFFFll)
+    return fail(KVC_ERR_INVALID_ARG, "paged_attention: a window side is -1 (open) or a non-negative number of tokens");
   if (q_dtype != KVC_IN_F16 && q_dtype != KVC_IN_BF16)
     return fail(KVC_ERR_UNSUPPORTED, "paged_attention: query must be fp16 or bf16");
   if (kv_dtype != KVC_KV_AUTO && kv_dtype != KVC_KV_FP8_E4M3 && kv_dtype != KVC_KV_FP8_E5M2)
@@ -1262,7 +1294,13 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
                         aligned(cu_seqlens_q, 4);
   if (!ok_align) return fail(KVC_ERR_INVALID_ARG, "paged_attention: query and cache rows must be 16-byte aligned");
 
-  const DecodePlan pl = plan_decode(num_seqs, total_q, max_seqlen_q, num_heads, num_kv_heads, head_size, max_seq_len,
+  // what a query token can see at most: a closed window bounds it whatever the sequence length
+  int64_t visible = max_seq_len;
+  if (window_left >= 0 && (causal || window_right >= 0)) {
+    const int64_t w = window_left + 1 + (causal ? 0 : window_right) + 127;  // + tile alignment slack
+    if (w < visible) visible = w;
+  }
+  const DecodePlan pl = plan_decode(num_seqs, total_q, max_seqlen_q, num_heads, num_kv_heads, head_size, visible,
                                     q_dtype, kv_dtype);
   if (pl.splits > 1 && (!workspace || workspace_bytes < pl.workspace_bytes || !aligned(workspace, 16)))
     return fail(KVC_ERR_INVALID_ARG, "paged_attention: workspace missing, misaligned (16 bytes) or too small; ask "
@@ -1298,6 +1336,8 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
   p.tiles_per_split = pl.tiles_per_split;
   p.causal = causal ? 1 : 0;
   p.many_rows_elsewhere = (max_seqlen_q * p.group > kRows) ? 1 : 0;
+  p.window_left = static_cast<int32_t>(window_left);
+  p.window_right = static_cast<int32_t>(window_right);
   p.softmax_scale = softmax_scale;
   if (pl.splits > 1) {
     p.part_out = static_cast<float*>(workspace);  // first: its float2 stores need 8-byte alignment
@@ -1356,7 +1396,7 @@ KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void*
                              v_descale, workspace, workspace_bytes, num_seqs, num_seqs, num_seqs > 0 ? 1 : 0, num_heads,
                              num_kv_heads, head_size, block_size, block_table_stride, max_seq_len, query_stride_t,
                              query_stride_h, out_stride_t, out_stride_h, block_stride, page_stride, head_stride,
-                             softmax_scale, 0, q_dtype, kv_dtype, stream);
+                             softmax_scale, 0, -1, -1, q_dtype, kv_dtype, stream);
 }
 
 }  // extern "C"

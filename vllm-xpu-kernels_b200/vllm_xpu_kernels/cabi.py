@@ -88,7 +88,7 @@ def lib() -> ctypes.CDLL:
         L.kvc_paged_attention_workspace_bytes.restype = i64
         L.kvc_paged_attention_workspace_bytes.argtypes = [i64] * 7 + [ci, ci]
         L.kvc_paged_attention.restype = ci
-        L.kvc_paged_attention.argtypes = [vp] * 11 + [i64] * 17 + [ctypes.c_float, ci, ci, ci, vp]
+        L.kvc_paged_attention.argtypes = [vp] * 11 + [i64] * 17 + [ctypes.c_float, ci, i64, i64, ci, ci, vp]
         L.kvc_rotary_embedding.restype = ci
         L.kvc_rotary_embedding.argtypes = [vp] * 4 + [i64] * 10 + [ci, ci, vp]
         L.kvc_rotary_embedding_and_cache_flash.restype = ci
@@ -344,10 +344,11 @@ def paged_decode_attention(query, key_cache, value_cache, block_table, seq_lens,
 
 def paged_attention(query, key_cache, value_cache, block_table, seq_lens, cu_seqlens_q, max_seqlen_q: int,
                     softmax_scale: float, max_seq_len: int, causal: bool = True, kv_cache_dtype: str = "auto",
-                    k_descale=None, v_descale=None, sink=None, out=None, stream=None):
+                    k_descale=None, v_descale=None, sink=None, out=None, stream=None, window=(-1, -1)):
     """``kvc_paged_attention``: like ``paged_decode_attention`` with several query tokens per sequence: query
     [total_q, Hq, D], ``cu_seqlens_q`` int32 [S + 1] on the device, the query tokens being the last positions of
-    their sequences (``causal``: token i of q_len sees seq_len - q_len + i + 1 cached tokens).  Returns ``out``."""
+    their sequences (``causal``: token i of q_len sees seq_len - q_len + i + 1 cached tokens); ``window`` =
+    (left, right) keeps positions [pos - left, pos + right], -1 = open.  Returns ``out``."""
     kv = parse_kv_cache_dtype(kv_cache_dtype)
     T, hq, D = query.shape
     S = seq_lens.shape[0]
@@ -362,5 +363,5 @@ def paged_attention(query, key_cache, value_cache, block_table, seq_lens, cu_seq
         _scale_ptr(v_descale, kv), ws.data_ptr(), ws.numel(), S, T, max_seqlen_q, hq, hk, D, key_cache.shape[1],
         block_table.stride(0), max_seq_len, query.stride(0), query.stride(1), out.stride(0), out.stride(1),
         key_cache.stride(0), key_cache.stride(1), key_cache.stride(2), float(softmax_scale), int(bool(causal)),
-        _in_dtype(query), kv, _stream(stream)))
+        int(window[0]), int(window[1]), _in_dtype(query), kv, _stream(stream)))
     return out

@@ -1,8 +1,8 @@
 """``flash_attn_varlen_func`` with the reference's signature (vllm_xpu_kernels/flash_attn_interface.py:24-125
-there), for the case this library builds: paged keys/values (``block_table`` and ``seqused_k`` given), no
-sliding window -- decode (one query token per sequence) at HBM speed, and several query tokens per sequence
-with the causal mask (short runs on the decode kernel, long ones on an mma.sync kernel at a fraction of the
-chip's GEMM rate).  On top of the reference,
+there): paged keys/values (``block_table`` + ``seqused_k``) or the non-paged form (``cu_seqlens_k``), causal
+mask, sliding windows, sink -- decode (one query token per sequence) at HBM speed, several query tokens per
+sequence on the same kernel (short runs) or an mma.sync kernel at a fraction of the chip's GEMM rate (long
+ones).  softcap, alibi, dropout and returning the softmax are not supported.  On top of the reference,
 the cache may hold fp8 bytes: pass ``k_descale`` / ``v_descale`` (the inverse of the k_scale / v_scale the
 cache was written with), which the reference's interface names but rejects."""
 from typing import Optional
@@ -79,14 +79,15 @@ def flash_attn_varlen_func(
     if fp8_cache or k_descale is not None or v_descale is not None:
         if not fp8_cache:
             raise NotImplementedError("k_descale / v_descale need an fp8 (or uint8) cache")
-        if block_table is None or real_window_size != (-1, -1) or softcap or dropout_p or alibi_slopes is not None:
-            raise NotImplementedError("fp8 caches: only the paged case without a sliding window is built")
+        if block_table is None or softcap or dropout_p or alibi_slopes is not None:
+            raise NotImplementedError("fp8 caches: only the paged form is built (no softcap, dropout, alibi)")
         if out is None:
             out = torch.empty_like(q)
         name = kv_cache_dtype or _FP8_NAMES[k.dtype]
         torch.ops._vllm_fa2_C.paged_decode_attention(q, k, v, out, seqused_k, block_table, max_seqlen_k,
                                                      float(softmax_scale), s_aux, name, k_descale, v_descale,
-                                                     cu_seqlens_q, max_seqlen_q, causal)
+                                                     cu_seqlens_q, max_seqlen_q, causal, real_window_size[0],
+                                                     real_window_size[1])
         return out
 
     dummy_cu_seqlens_k = torch.empty_like(cu_seqlens_q)
