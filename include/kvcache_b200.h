@@ -348,9 +348,16 @@ KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_h
  *   window_right   pos + window_right; -1 leaves a side open (test_flash_attn_varlen_func.py:81-95)
  *
  * Sequences with at most 16 (token, head) rows per kv head run on the decode kernel, the others on a second
- * kernel launched beside it in which a CTA owns 64 rows (mma.sync tiles, about 0.16-0.19 of the chip's dense
- * bf16 GEMM rate on long prompts; a tcgen05 flash-attention kernel is not part of this library).  In such a
- * mixed call the decode part is not split over the sequence.  At most 65535 sequences per call.
+ * kernel launched beside it.  With a 16-bit cache, head size 128 and some sequence of more than 64 rows per kv
+ * head that second kernel runs on the tcgen05 tensor cores: a CTA owns 128 rows, both products are
+ * tcgen05.mma with operands in 128-byte-swizzled shared memory and accumulators in tensor memory, two CTAs per
+ * SM.  Otherwise (fp8 caches, other head sizes, short runs) it is the mma.sync kernel in which a CTA owns 64
+ * rows.  In such a mixed call the decode part is not split over the sequence.  At most 65535 sequences per call.
+ *
+ * kvc_paged_attention_device_status waits for the device's earlier work and reads the tcgen05 kernel's status
+ * word: 0 = fine; 1 = a bounded wait on an mbarrier gave up (results of that call are then undefined; the
+ * kernel still ran to its end and freed its tensor memory); 2 = its shared-memory window was not 1024-byte
+ * aligned (nothing was computed).  The word is sticky for the life of the process.
  */
 KVC_API int64_t kvc_paged_attention_workspace_bytes(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q,
                                                     int64_t num_heads, int64_t num_kv_heads, int64_t head_size,
@@ -365,6 +372,7 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
                                 int64_t block_stride, int64_t page_stride, int64_t head_stride, float softmax_scale,
                                 int causal, int64_t window_left, int64_t window_right, int q_dtype, int kv_dtype,
                                 void* stream);
+KVC_API int kvc_paged_attention_device_status(int* status);
 KVC_API int kvc_paged_decode_attention(void* out, const void* query, const void* key_cache, const void* value_cache,
                                        const int32_t* block_table, const int32_t* seq_lens, const void* sink,
                                        const float* k_descale, const float* v_descale, void* workspace,

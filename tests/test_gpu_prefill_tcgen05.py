@@ -1,0 +1,141 @@
+"""GPU parity of the many-rows attention kernel that runs on the tcgen05 tensor cores (16-bit cache, head size
+128, some sequence with more than 64 query rows per kv head) against the CPU oracle, and against the mma.sync
+kernel it replaces for those calls.
+
+Floating point.  Tolerance: atol = rtol = 1e-2, the reference test's own for this op
+(tests/flash_attn/test_flash_attn_varlen_func.py:386 there).  After every case the kernel's status word must
+be 0: no bounded wait gave up."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from oracle import torch_views
+from tests import helpers as H
+from tests.test_gpu_decode_attention import cu_of, make_case
+from vllm_xpu_kernels import cabi
+from vllm_xpu_kernels.flash_attn_interface import flash_attn_varlen_func
+
+pytestmark = pytest.mark.gpu
+
+TOL = dict(atol=H.ATTN_ATOL, rtol=H.ATTN_RTOL)
+
+
+def run_case(dev, dtype, hq, hk, q_lens, kv_lens, bs, causal, sink, seed, window=(-1, -1), scale=None, out=None):
+    D = 128
+    nb = max(64, sum((n + bs - 1) // bs for n in kv_lens) + 8)
+    torch.manual_seed(seed)
+    query = torch.randn(sum(q_lens), hq, D).to(dtype)
+    _, kc, vc, bt, lens, sk = make_case(dtype, hq, hk, D, kv_lens, bs, nb, sink, seed=seed + 1)
+    cu = cu_of(q_lens)
+    scale = D ** -0.5 if scale is None else scale
+    got = cabi.paged_attention(query.to(dev), kc.to(dev), vc.to(dev), bt.to(dev), lens.to(dev), cu.to(dev), max(q_lens),
+                               scale, max(kv_lens), causal, sink=None if sk is None else sk.to(dev), window=window,
+                               out=out)
+    assert cabi.paged_attention_device_status() == 0
+    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, scale, sink=sk, cu_seqlens_q=cu,
+                                                  causal=causal, window=window)
+    torch.testing.assert_close(got.cpu().float(), want, **TOL)
+    return got
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("heads", [(4, 4), (8, 2), (6, 2), (16, 1)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_prefill_heads_and_types(dtype, heads, causal, cuda_device):
+    """Group sizes 1, 4, 3 (rows of a token do not divide a tile) and 16; ragged query and cache lengths, a
+    sequence that is pure decode, one whose rows fill less than a tile, one that spans several row tiles."""
+    hq, hk = heads
+    run_case(cuda_device, dtype, hq, hk, q_lens=[200, 1, 70, 513], kv_lens=[777, 300, 70, 1500], bs=64, causal=causal,
+             sink=(hq == 8), seed=100 + hq)
+
+
+@pytest.mark.parametrize("bs", [16, 48, 128])
+def test_prefill_block_sizes(bs, cuda_device):
+    """Blocks shorter and longer than a 64-token tile, and a block size that is no power of two."""
+    run_case(cuda_device, torch.bfloat16, 8, 2, q_lens=[333, 129], kv_lens=[1000, 129], bs=bs, causal=True, sink=False,
+             seed=200 + bs)
+
+
+@pytest.mark.parametrize("window", [(-1, 127), (127, -1), (127, 127), (0, 0), (1000, 3)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_prefill_windows(window, causal, cuda_device):
+    """Sliding windows: rows of a tile start and end at different cached tokens, whole tiles are skipped."""
+    run_case(cuda_device, torch.float16, 8, 2, q_lens=[400, 90], kv_lens=[2000, 500], bs=32, causal=causal, sink=True,
+             seed=300, window=window, scale=0.09)
+
+
+def test_prefill_query_run_longer_than_the_cache_and_large_scores(cuda_device):
+    """More query tokens than cached ones (the first rows see nothing: zeros) and a softmax scale that makes
+    the running maximum move often, so that the accumulator is rescaled in tensor memory."""
+    got = run_case(cuda_device, torch.bfloat16, 4, 1, q_lens=[300], kv_lens=[200], bs=16, causal=True, sink=False,
+                   seed=400, scale=1.5)
+    assert torch.count_nonzero(got[:100]) == 0
+
+
+def test_prefill_output_rows_that_are_not_16_byte_aligned(cuda_device):
+    """The output may be a view whose rows start on 4-byte boundaries only (the narrow store path)."""
+    dev = cuda_device
+    hq, D, T = 8, 128, 150
+    buf = torch.zeros(T, hq, D + 2, dtype=torch.bfloat16, device=dev)
+    out = buf[:, :, 2:]
+    got = run_case(dev, torch.bfloat16, hq, 2, q_lens=[T], kv_lens=[640], bs=64, causal=True, sink=False, seed=500,
+                   out=out)
+    assert got.data_ptr() == out.data_ptr()
+    assert torch.count_nonzero(buf[:, :, :2]) == 0
+
+
+def test_prefill_long_prompt_multi_tile(cuda_device):
+    """A 2048-token prompt from an empty cache, 8 query heads per kv head: 128 row tiles x 32 token tiles."""
+    run_case(cuda_device, torch.bfloat16, 8, 1, q_lens=[2048], kv_lens=[2048], bs=64, causal=True, sink=False, seed=600)
+
+
+def test_prefill_non_paged_form(cuda_device):
+    """The interface's dense form (cu_seqlens_k, no block table) reaches the same kernel as a cache of
+    one-token blocks."""
+    dev = cuda_device
+    hq, hk, D = 8, 2, 128
+    lens = [257, 130]
+    torch.manual_seed(700)
+    q = torch.randn(sum(lens), hq, D).to(torch.float16)
+    k = torch.randn(sum(lens), hk, D).to(torch.float16)
+    v = torch.randn(sum(lens), hk, D).to(torch.float16)
+    cu = cu_of(lens)
+    out = flash_attn_varlen_func(q.to(dev), k.to(dev), v.to(dev), max(lens), cu.to(dev), max(lens),
+                                 cu_seqlens_k=cu.to(dev), softmax_scale=D ** -0.5, causal=True, block_table=None)
+    assert cabi.paged_attention_device_status() == 0
+    bt = torch.stack([torch.arange(int(cu[i]), int(cu[i]) + max(lens), dtype=torch.int32) for i in range(2)])
+    bt = bt.clamp(max=sum(lens) - 1)
+    want = torch_views.run_paged_decode_attention(q, k.unsqueeze(1), v.unsqueeze(1), bt,
+                                                  torch.tensor(lens, dtype=torch.int32), D ** -0.5, cu_seqlens_q=cu,
+                                                  causal=True)
+    torch.testing.assert_close(out.cpu().float(), want, **TOL)
+
+
+def test_prefill_agrees_with_the_mma_sync_kernel(cuda_device):
+    """The same call in a child process with KVC_PREFILL_LEGACY=1 (the switch is read once per process)."""
+    dev = cuda_device
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import sys, torch\n"
+        "sys.path[:0] = [%r, %r]\n"
+        "from tests.test_gpu_decode_attention import cu_of, make_case\n"
+        "from vllm_xpu_kernels import cabi\n"
+        "torch.manual_seed(800)\n"
+        "q = torch.randn(700, 8, 128).to(torch.bfloat16)\n"
+        "_, kc, vc, bt, lens, sk = make_case(torch.bfloat16, 8, 2, 128, [900, 400], 64, 64, True, seed=801)\n"
+        "cu = cu_of([500, 200]); dev = 'cuda:0'\n"
+        "out = cabi.paged_attention(q.to(dev), kc.to(dev), vc.to(dev), bt.to(dev), lens.to(dev), cu.to(dev), 500, 0.09,"
+        " 900, True, sink=sk.to(dev))\n"
+        "torch.save(out.cpu(), sys.argv[1])\n") % (repo, os.path.join(repo, "vllm-xpu-kernels_b200"))
+    import tempfile
+    outs = []
+    for legacy in ("0", "1"):
+        with tempfile.NamedTemporaryFile(suffix=".pt") as f:
+            env = dict(os.environ, KVC_PREFILL_LEGACY=legacy)
+            subprocess.run([sys.executable, "-c", code, f.name], check=True, env=env, timeout=300, cwd=repo)
+            outs.append(torch.load(f.name))
+    assert dev is not None
+    torch.testing.assert_close(outs[0].float(), outs[1].float(), **TOL)

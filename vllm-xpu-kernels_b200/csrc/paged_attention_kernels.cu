@@ -962,6 +962,13 @@ __global__ void __launch_bounds__(kAttnThreads, (D <= 128 ? 3 : 1)) paged_prefil
   }
 }
 
+}  // namespace kvc
+
+// the many-rows kernel on tcgen05 (16-bit cache, head size 128)
+#include "paged_prefill_umma.cuh"
+
+namespace kvc {
+
 // ---------------------------------------------------------------------------------------------
 // merge of the splits: out = sum_p w_p o_p / (sum_p w_p [+ sink]),  w_p = exp2(lse_p - max lse)
 // ---------------------------------------------------------------------------------------------
@@ -1180,6 +1187,47 @@ cudaError_t launch_prefill_kv(int kv, int head_size, const DecodeParams& p, dim3
   }
 }
 
+// The tcgen05 kernel serves calls whose cache holds the query's 16-bit type with head size 128, once some
+// sequence has more than 64 query rows per kv head (below that its 128-row tiles would be mostly padding).
+// KVC_PREFILL_LEGACY=1 keeps every call on the mma.sync kernel (for comparisons).
+inline bool prefill_umma_enabled() {
+  static const bool off = [] {
+    const char* e = getenv("KVC_PREFILL_LEGACY");
+    return e && e[0] == '1';
+  }();
+  return !off;
+}
+inline bool prefill_uses_umma(int kv_dtype, int64_t head_size, int64_t max_rows_per_kv_head) {
+  return prefill_umma_enabled() && kv_dtype == KVC_KV_AUTO && head_size == 128 && max_rows_per_kv_head > kPrefillRows;
+}
+
+template <typename TQ>
+cudaError_t launch_prefill_umma(const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  using Cfg = UmmaPrefillCfg<TQ, 128>;
+  static std::once_flag once[64];
+  static cudaError_t attr_err[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  std::call_once(once[dev], [&] {
+    attr_err[dev] = cudaFuncSetAttribute(paged_prefill_umma_kernel<TQ, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+  });
+  if (attr_err[dev] != cudaSuccess) return attr_err[dev];
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, paged_prefill_umma_kernel<TQ, 128>, p);
+}
+
 struct DecodePlan {
   int splits;
   int tiles_per_split;
@@ -1354,12 +1402,18 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
     return fail(KVC_ERR_CUDA, std::string("paged_attention launch failed: ") + cudaGetErrorString(e));
   if (max_seqlen_q * p.group > kRows) {  // sequences with more than 16 query rows per kv head
     DecodeParams pp = p;
-    pp.row_tiles = static_cast<int32_t>((max_seqlen_q * p.group + kPrefillRows - 1) / kPrefillRows);
+    const bool use_umma = prefill_uses_umma(kv_dtype, head_size, max_seqlen_q * p.group);
+    const int64_t tile_rows = use_umma ? kUmmaRows : kPrefillRows;
+    pp.row_tiles = static_cast<int32_t>((max_seqlen_q * p.group + tile_rows - 1) / tile_rows);
     const int64_t px = static_cast<int64_t>(pp.num_kv_heads) * pp.row_tiles;
     if (px > 0x7FFFFFFFll) return fail(KVC_ERR_INVALID_ARG, "paged_attention: too many query rows per sequence");
     const dim3 pgrid(static_cast<unsigned>(px), static_cast<unsigned>(num_seqs), 1);
-    e = (q_dtype == KVC_IN_F16) ? launch_prefill_kv<__half>(kv_dtype, static_cast<int>(head_size), pp, pgrid, st)
-                                : launch_prefill_kv<__nv_bfloat16>(kv_dtype, static_cast<int>(head_size), pp, pgrid, st);
+    if (use_umma)
+      e = (q_dtype == KVC_IN_F16) ? launch_prefill_umma<__half>(pp, pgrid, st)
+                                  : launch_prefill_umma<__nv_bfloat16>(pp, pgrid, st);
+    else
+      e = (q_dtype == KVC_IN_F16) ? launch_prefill_kv<__half>(kv_dtype, static_cast<int>(head_size), pp, pgrid, st)
+                                  : launch_prefill_kv<__nv_bfloat16>(kv_dtype, static_cast<int>(head_size), pp, pgrid, st);
     if (e != cudaSuccess)
       return fail(KVC_ERR_CUDA, std::string("paged_attention many-rows launch failed: ") + cudaGetErrorString(e));
   }
@@ -1380,6 +1434,17 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
     if (e != cudaSuccess)
       return fail(KVC_ERR_CUDA, std::string("paged_attention merge launch failed: ") + cudaGetErrorString(e));
   }
+  return KVC_OK;
+}
+
+KVC_API int kvc_paged_attention_device_status(int* status) {
+  using namespace kvc;
+  if (!status) return fail(KVC_ERR_INVALID_ARG, "paged_attention_device_status: status must be non-NULL");
+  int v = 0;
+  const cudaError_t e = cudaMemcpyFromSymbol(&v, g_umma_status, sizeof(int));  // waits for the device's earlier work
+  if (e != cudaSuccess)
+    return fail(KVC_ERR_CUDA, std::string("paged_attention_device_status: ") + cudaGetErrorString(e));
+  *status = v;
   return KVC_OK;
 }
 

@@ -1,0 +1,324 @@
+// The many-rows attention kernel on the fifth-generation tensor cores (tcgen05, accumulators in tensor
+// memory).  Included by paged_attention_kernels.cu after DecodeParams and the cp.async helpers.
+//
+// Division of labour: a CTA of 128 threads owns 128 query rows (token-major (token, head) pairs of one kv
+// head) and walks the cached tokens in tiles of 64.  Per tile
+//   1. all threads copy the next tile's K and V rows into the other stage (cp.async, 128-byte swizzle),
+//   2. thread 0 issues S = Q K^T   (M = 128, N = 64, K = 16, D / 16 instructions, operands from shared memory,
+//      S in tensor-memory columns [0, 64)),
+//   3. thread r reads row r of S (tensor-memory lane r), applies mask and online softmax with no shuffle at
+//      all, and writes row r of P as 16-bit values into shared memory,
+//   4. thread 0 issues O += P V    (M = 128, N = D, K = 16, 4 instructions; O in columns [128, 128 + D)).
+// Steps 2-4 of one CTA are a dependency chain, so two CTAs share an SM (shared memory is sized for exactly
+// two, and each allocates 256 of the 512 tensor-memory columns): one CTA's softmax runs under the other's
+// matrix products.  O is rescaled in tensor memory only when a row's reference maximum moves (rare, see the
+// lazy rule of the other kernels).
+//
+// Every wait on an mbarrier is bounded; a wait that gives up sets the CTA's abort word, the CTA runs to its
+// end, frees its tensor memory and raises g_umma_status.
+#pragma once
+
+#include "umma_sm100.cuh"
+
+namespace kvc {
+namespace {
+
+constexpr int kUmmaRows = 128;
+constexpr uint32_t kUmmaTmemCols = 256;
+constexpr uint32_t kUmmaColS = 0;
+constexpr uint32_t kUmmaColO = 128;
+
+// 0 = fine; 1 = an mbarrier wait gave up; 2 = shared memory window not 1024-byte aligned
+__device__ int g_umma_status = 0;
+
+template <typename TQ, int D>
+struct UmmaPrefillCfg {
+  static_assert(D == 128, "head size 128");
+  static constexpr int kTile = 64;
+  static constexpr int kHalves = D / 64;                     // 128-byte-wide operand tiles per row
+  static constexpr int kQHalfBytes = kUmmaRows * 128;        // 16 KB
+  static constexpr int kQBytes = kQHalfBytes * kHalves;      // 32 KB
+  static constexpr int kKVHalfBytes = kTile * 128;           // 8 KB
+  static constexpr int kKVBytes = kKVHalfBytes * kHalves;    // one K or V tile: 16 KB
+  static constexpr int kPBytes = kUmmaRows * 128;            // 128 rows x 64 probabilities: 16 KB
+  static constexpr int kStages = 2;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffKV = kOffQ + kQBytes;             // [stage][K, V]
+  static constexpr int kOffP = kOffKV + kStages * 2 * kKVBytes;
+  static constexpr int kOffBar = kOffP + kPBytes;            // two mbarriers, tensor-memory slot, abort word
+  static constexpr int kSmemBytes = kOffBar + 64;
+  // two CTAs per SM: 2 x (bytes + 1 KB the system keeps per CTA) within the SM's 228 KB
+  static_assert(2 * (kSmemBytes + 1024) <= 233472, "two CTAs per SM");
+  // and never three, which could ask for more tensor memory than an SM has
+  static_assert(3 * (kSmemBytes + 1024) > 233472, "at most two CTAs per SM");
+};
+
+template <typename TQ, int D>
+__global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const DecodeParams p) {
+  using Cfg = UmmaPrefillCfg<TQ, D>;
+  using namespace umma;
+  constexpr int TN = Cfg::kTile;
+  constexpr int KVB = Cfg::kKVBytes;
+
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* s_q = smem + Cfg::kOffQ;
+  unsigned char* s_kv = smem + Cfg::kOffKV;
+  unsigned char* s_p = smem + Cfg::kOffP;
+  uint64_t* bar_s = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
+  uint64_t* bar_o = bar_s + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_s + 2);
+  volatile uint32_t* abort_word = tmem_slot + 1;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int seq = blockIdx.y;
+  const int row_tile = p.row_tiles - 1 - static_cast<int>(blockIdx.x / p.num_kv_heads);  // heaviest first
+  const int kvh = blockIdx.x % p.num_kv_heads;
+  const int row0 = row_tile * kUmmaRows;
+
+  pdl_prologue();
+
+  const int q_start = p.cu_seqlens_q ? p.cu_seqlens_q[seq] : seq;
+  const int q_len = p.cu_seqlens_q ? p.cu_seqlens_q[seq + 1] - q_start : 1;
+  const int seq_rows = q_len * p.group;
+  if (seq_rows <= kRows || row0 >= seq_rows) return;  // the decode kernel's sequence, or no rows here
+  const int rows = min(kUmmaRows, seq_rows - row0);
+  auto row_token = [&](int r) { return (row0 + r) / p.group; };
+  auto row_head = [&](int r) { return kvh * p.group + (row0 + r) % p.group; };
+  const int n = p.seq_lens[seq];
+  auto row_limit = [&](int r) {
+    const int pos = n - q_len + row_token(r);
+    int hi = n;
+    if (p.causal) hi = min(hi, pos + 1);
+    if (p.window_right >= 0) hi = min(hi, pos + p.window_right + 1);
+    return max(0, hi);
+  };
+  auto row_lo = [&](int r) { return p.window_left >= 0 ? max(0, n - q_len + row_token(r) - p.window_left) : 0; };
+  const int n_item = row_limit(rows - 1);
+  const int lim_min = row_limit(0);
+  const int lo_max = row_lo(rows - 1);
+  const int tile_end = (n_item + TN - 1) / TN;
+  const int tile_begin = row_lo(0) / TN;
+
+  if (tile_end <= tile_begin) {  // no row sees any token
+    for (int i = tid; i < rows * D; i += 128) {
+      const int r = i / D;
+      static_cast<TQ*>(p.out)[static_cast<int64_t>(q_start + row_token(r)) * p.out_stride_t +
+                              row_head(r) * p.out_stride_h + i % D] = TQ(0.0f);
+    }
+    return;
+  }
+  if (smem_addr(smem) & 1023u) {  // the operand tiles' swizzle assumes 1024-byte alignment
+    if (tid == 0) atomicMax(&g_umma_status, 2);
+    return;
+  }
+
+  // ---- barriers and tensor memory ----------------------------------------------------------------------
+  if (tid == 0) {
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    *abort_word = 0;
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(tmem_slot, kUmmaTmemCols);
+
+  // ---- query rows -> shared memory (zero rows past the end) --------------------------------------------
+  for (int c = tid; c < kUmmaRows * (D / 8); c += 128) {
+    const int r = c / (D / 8), col = c % (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < rows) {
+      const TQ* src = static_cast<const TQ*>(p.query) + static_cast<int64_t>(q_start + row_token(r)) * p.query_stride_t +
+                      row_head(r) * p.query_stride_h + col * 8;
+      v = *reinterpret_cast<const uint4*>(src);
+    }
+    *reinterpret_cast<uint4*>(s_q + (col >> 3) * Cfg::kQHalfBytes + swizzled_offset(r, col & 7)) = v;
+  }
+
+  // ---- producer: thread t copies chunk t % 16 of rows t / 16 + 8 i ---------------------------------------
+  const int32_t* table = p.block_table + seq * p.block_table_stride;
+  const int64_t head_off = static_cast<int64_t>(kvh) * p.head_stride;
+  const int64_t v_minus_k =
+      static_cast<const unsigned char*>(p.value_cache) - static_cast<const unsigned char*>(p.key_cache);
+  auto load_tile = [&](int tile, int stage) {
+    constexpr int kChunks = D / 8;  // 16-byte chunks per row
+    constexpr int kRowsPerPass = 128 / kChunks;
+    const int r0 = tid / kChunks, col = tid % kChunks;
+    const int rows_left = n - tile * TN;
+    unsigned char* ks = s_kv + stage * 2 * KVB;
+#pragma unroll
+    for (int i = 0; i < TN / kRowsPerPass; ++i) {
+      const int r = r0 + i * kRowsPerPass;
+      const int token = tile * TN + r;
+      const bool valid = r < rows_left;
+      int64_t off = 0;
+      if (valid) {
+        const int blk_idx = p.bs_shift >= 0 ? (token >> p.bs_shift) : token / p.block_size;
+        off = (static_cast<int64_t>(__ldg(table + blk_idx)) * p.block_stride +
+               static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride + head_off) * 2;
+      }
+      const unsigned char* src = static_cast<const unsigned char*>(p.key_cache) + off + col * 16;
+      const uint32_t dst = smem_addr(ks + (col >> 3) * Cfg::kKVHalfBytes) + swizzled_offset(r, col & 7);
+      cp_async_16(dst, src, valid ? 16 : 0);
+      cp_async_16(dst + KVB, src + v_minus_k, valid ? 16 : 0);
+    }
+  };
+
+  // ---- this thread's row ----------------------------------------------------------------------------------
+  const float scale2 = p.softmax_scale * kLog2e;
+  const float lazy_margin = 8.0f / scale2;
+  const int lim = tid < rows ? row_limit(tid) : 0;
+  const int lo = tid < rows ? row_lo(tid) : 0;
+  float m_run = -INFINITY, l_run = 0.f;
+
+  load_tile(tile_begin, 0);
+  cp_async_commit();
+
+  fence_smem_to_async_proxy();  // the query rows
+  fence_before_thread_sync();
+  __syncthreads();
+  fence_after_thread_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  constexpr uint32_t kIdescQK = instr_desc_f16<TQ>(kUmmaRows, TN, false, false);
+  constexpr uint32_t kIdescPV = instr_desc_f16<TQ>(kUmmaRows, D, false, true);
+
+  uint32_t it = 0;
+  for (int tile = tile_begin; tile < tile_end; ++tile, ++it) {
+    const int stage = it & 1;
+    // the other stage and P were last read by the previous tile's second product
+    if (it > 0) mbar_wait_bounded(bar_o, (it - 1) & 1, abort_word);
+    if (tile + 1 < tile_end) load_tile(tile + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    fence_smem_to_async_proxy();
+    __syncthreads();
+    const uint32_t ks = smem_addr(s_kv + stage * 2 * KVB);
+    const uint32_t vs = ks + KVB;
+    if (tid == 0) {
+      fence_after_thread_sync();
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint64_t da = smem_desc_sw128(smem_addr(s_q) + (kk >> 2) * Cfg::kQHalfBytes + (kk & 3) * 32, 16, 1024);
+        const uint64_t db = smem_desc_sw128(ks + (kk >> 2) * Cfg::kKVHalfBytes + (kk & 3) * 32, 16, 1024);
+        mma_f16_ss(tmem + kUmmaColS, da, db, kIdescQK, kk > 0 ? 1u : 0u);
+      }
+      mma_commit(bar_s);
+    }
+    mbar_wait_bounded(bar_s, it & 1, abort_word);
+    fence_after_thread_sync();
+
+    // ---- softmax of this thread's row ----------------------------------------------------------------
+    uint32_t sa[32], sb[32];
+    tmem_ld_32x32(tmem + lane_base + kUmmaColS, sa);
+    tmem_ld_32x32(tmem + lane_base + kUmmaColS + 32, sb);
+    tmem_ld_wait();
+    float s[64];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      s[i] = __uint_as_float(sa[i]);
+      s[32 + i] = __uint_as_float(sb[i]);
+    }
+    if ((tile + 1) * TN > lim_min || tile * TN < lo_max) {  // some row of the CTA has tokens to mask here
+      const int tok0 = tile * TN;
+#pragma unroll
+      for (int i = 0; i < 64; ++i)
+        if (tok0 + i >= lim || tok0 + i < lo) s[i] = -INFINITY;
+    }
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) mx = fmaxf(mx, s[i]);
+    const bool move = mx > m_run + lazy_margin;
+    const float alpha = move ? fast_exp2((m_run - mx) * scale2) : 1.0f;
+    m_run = move ? mx : m_run;
+    const float neg_ms = (m_run == -INFINITY) ? 0.f : -m_run * scale2;
+    l_run *= alpha;
+    float l_add[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float p0 = fast_exp2(fmaf(s[c * 8 + 2 * j], scale2, neg_ms));
+        const float p1 = fast_exp2(fmaf(s[c * 8 + 2 * j + 1], scale2, neg_ms));
+        l_add[j] += p0 + p1;
+        w[j] = pack2<TQ>(p0, p1);
+      }
+      *reinterpret_cast<uint4*>(s_p + swizzled_offset(tid, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    l_run += (l_add[0] + l_add[1]) + (l_add[2] + l_add[3]);
+    if (it > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // rare: a reference maximum of the warp moved
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32(tmem + lane_base + kUmmaColO + c * 32, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+        tmem_st_32x32(tmem + lane_base + kUmmaColO + c * 32, o);
+      }
+      tmem_st_wait();
+    }
+    fence_smem_to_async_proxy();  // P
+    fence_before_thread_sync();
+    __syncthreads();
+    if (tid == 0) {
+      fence_after_thread_sync();
+#pragma unroll
+      for (int kk = 0; kk < TN / 16; ++kk) {
+        const uint64_t da = smem_desc_sw128(smem_addr(s_p) + kk * 32, 16, 1024);
+        const uint64_t db = smem_desc_sw128(vs + kk * 16 * 128, Cfg::kKVHalfBytes, 1024);
+        mma_f16_ss(tmem + kUmmaColO, da, db, kIdescPV, (it > 0 || kk > 0) ? 1u : 0u);
+      }
+      mma_commit(bar_o);
+    }
+  }
+  cp_async_wait<0>();
+  const bool finished = mbar_wait_bounded(bar_o, (it - 1) & 1, abort_word);
+  fence_after_thread_sync();
+  if (!finished && (tid & 31) == 0) atomicMax(&g_umma_status, 1);
+
+  // ---- every thread finishes its own row ------------------------------------------------------------------
+  {
+    const bool live = tid < rows;
+    const int head = live ? row_head(tid) : 0;
+    float l = l_run;
+    const float m = m_run * scale2;  // log2 domain; -inf if the row saw nothing
+    float rescale = 1.0f;
+    if (p.sink && live) {
+      const float sk = static_cast<float>(static_cast<const TQ*>(p.sink)[head]) * kLog2e;
+      const float mf = fmaxf(m, sk);
+      rescale = (m == -INFINITY) ? 0.f : exp2f(m - mf);
+      l = l * rescale + exp2f(sk - mf);
+    }
+    const float f = (l > 0.f) ? rescale / l : 0.f;
+    TQ* o = static_cast<TQ*>(p.out) + (live ? static_cast<int64_t>(q_start + row_token(tid)) * p.out_stride_t +
+                                                  static_cast<int64_t>(head) * p.out_stride_h
+                                            : 0);
+    const bool vec16 = ((reinterpret_cast<uintptr_t>(p.out) | static_cast<uintptr_t>(p.out_stride_t * 2) |
+                         static_cast<uintptr_t>(p.out_stride_h * 2)) & 15u) == 0;
+#pragma unroll 1
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t acc[32];
+      tmem_ld_32x32(tmem + lane_base + kUmmaColO + c * 32, acc);
+      tmem_ld_wait();
+      if (!live) continue;
+      uint32_t w[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        w[i] = pack2<TQ>(__uint_as_float(acc[2 * i]) * f, __uint_as_float(acc[2 * i + 1]) * f);
+      if (vec16) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          *reinterpret_cast<uint4*>(o + c * 32 + i * 8) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) *reinterpret_cast<uint32_t*>(o + c * 32 + 2 * i) = w[i];
+      }
+    }
+  }
+  fence_before_thread_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kUmmaTmemCols);
+}
+
+}  // namespace
+}  // namespace kvc

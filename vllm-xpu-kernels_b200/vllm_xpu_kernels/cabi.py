@@ -40,6 +40,7 @@ SYMBOLS = (
     "kvc_paged_decode_attention",
     "kvc_paged_attention_workspace_bytes",
     "kvc_paged_attention",
+    "kvc_paged_attention_device_status",
 )
 
 _lib = None
@@ -89,6 +90,8 @@ def lib() -> ctypes.CDLL:
         L.kvc_paged_attention_workspace_bytes.argtypes = [i64] * 7 + [ci, ci]
         L.kvc_paged_attention.restype = ci
         L.kvc_paged_attention.argtypes = [vp] * 11 + [i64] * 17 + [ctypes.c_float, ci, i64, i64, ci, ci, vp]
+        L.kvc_paged_attention_device_status.restype = ci
+        L.kvc_paged_attention_device_status.argtypes = [ctypes.POINTER(ci)]
         L.kvc_rotary_embedding.restype = ci
         L.kvc_rotary_embedding.argtypes = [vp] * 4 + [i64] * 10 + [ci, ci, vp]
         L.kvc_rotary_embedding_and_cache_flash.restype = ci
@@ -365,3 +368,11 @@ def paged_attention(query, key_cache, value_cache, block_table, seq_lens, cu_seq
         key_cache.stride(0), key_cache.stride(1), key_cache.stride(2), float(softmax_scale), int(bool(causal)),
         int(window[0]), int(window[1]), _in_dtype(query), kv, _stream(stream)))
     return out
+
+
+def paged_attention_device_status() -> int:
+    """``kvc_paged_attention_device_status``: waits for the device and returns the status word of the tcgen05
+    many-rows kernel (0 = fine, 1 = a bounded wait inside a kernel gave up, 2 = shared memory misaligned)."""
+    v = ctypes.c_int(0)
+    _check(lib().kvc_paged_attention_device_status(ctypes.byref(v)))
+    return int(v.value)
