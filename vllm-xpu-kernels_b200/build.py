@@ -35,7 +35,7 @@ HEADERS = [
     os.path.join(CSRC, "dispatch_utils.h"),
     os.path.join(CSRC, "core", "registration.h"),
 ]
-CUDA_HEADERS = [HEADERS[0], os.path.join(CSRC, "kvc_common.cuh"), os.path.join(CSRC, "kvc_convert.cuh")]
+CUDA_HEADERS = [HEADERS[0]] + [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC)) if f.endswith(".cuh")]
 
 
 def _stale(target: str, sources: list[str]) -> bool:

@@ -17,6 +17,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdio>
 #include <mutex>
 
 #include "kvc_common.cuh"
@@ -132,6 +133,7 @@ struct DecodeParams {
   // sliding window: the query token at position pos sees cached positions [pos - left, pos + right]; -1 = open
   int32_t window_left, window_right;
   float softmax_scale;
+  int32_t debug_flags;  // KVC_UMMA_DEBUG: bit 0 = spin on the barrier instead of parking
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -1213,6 +1215,16 @@ cudaError_t launch_prefill_umma(const DecodeParams& p, dim3 grid, cudaStream_t s
   std::call_once(once[dev], [&] {
     attr_err[dev] = cudaFuncSetAttribute(paged_prefill_umma_kernel<TQ, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
+    // two CTAs per SM need the whole shared-memory carve-out
+    if (attr_err[dev] == cudaSuccess)
+      attr_err[dev] = cudaFuncSetAttribute(paged_prefill_umma_kernel<TQ, 128>,
+                                           cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (getenv("KVC_DEBUG_OCCUPANCY")) {
+      int ctas = -1;
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, paged_prefill_umma_kernel<TQ, 128>, 128, Cfg::kSmemBytes);
+      fprintf(stderr, "kvc: paged_prefill_umma_kernel: %d CTAs per SM (%d bytes of shared memory each)\n", ctas,
+              Cfg::kSmemBytes);
+    }
   });
   if (attr_err[dev] != cudaSuccess) return attr_err[dev];
   cudaLaunchConfig_t cfg = {};
@@ -1402,6 +1414,8 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
     return fail(KVC_ERR_CUDA, std::string("paged_attention launch failed: ") + cudaGetErrorString(e));
   if (max_seqlen_q * p.group > kRows) {  // sequences with more than 16 query rows per kv head
     DecodeParams pp = p;
+    static const int dbg = [] { const char* e = getenv("KVC_UMMA_DEBUG"); return e ? atoi(e) : 0; }();
+    pp.debug_flags = dbg;
     const bool use_umma = prefill_uses_umma(kv_dtype, head_size, max_seqlen_q * p.group);
     const int64_t tile_rows = use_umma ? kUmmaRows : kPrefillRows;
     pp.row_tiles = static_cast<int32_t>((max_seqlen_q * p.group + tile_rows - 1) / tile_rows);

@@ -2,17 +2,17 @@
 // memory).  Included by paged_attention_kernels.cu after DecodeParams and the cp.async helpers.
 //
 // Division of labour: a CTA of 128 threads owns 128 query rows (token-major (token, head) pairs of one kv
-// head) and walks the cached tokens in tiles of 64.  Per tile
-//   1. all threads copy the next tile's K and V rows into the other stage (cp.async, 128-byte swizzle),
-//   2. thread 0 issues S = Q K^T   (M = 128, N = 64, K = 16, D / 16 instructions, operands from shared memory,
-//      S in tensor-memory columns [0, 64)),
-//   3. thread r reads row r of S (tensor-memory lane r), applies mask and online softmax with no shuffle at
+// head) and walks the cached tokens in tiles of 64.  Per tile i
+//   1. all threads wait for S(i) = Q K(i)^T in tensor-memory columns [0, 64) and start the copies of K(i+2) and
+//      V(i+1) into the slots that the finished products have released (cp.async, 128-byte swizzle),
+//   2. thread r reads row r of S (tensor-memory lane r), applies mask and online softmax with no shuffle at
 //      all, and writes row r of P as 16-bit values into shared memory,
-//   4. thread 0 issues O += P V    (M = 128, N = D, K = 16, 4 instructions; O in columns [128, 128 + D)).
-// Steps 2-4 of one CTA are a dependency chain, so two CTAs share an SM (shared memory is sized for exactly
-// two, and each allocates 256 of the 512 tensor-memory columns): one CTA's softmax runs under the other's
-// matrix products.  O is rescaled in tensor memory only when a row's reference maximum moves (rare, see the
-// lazy rule of the other kernels).
+//   3. thread 0 issues O += P V(i)  (M = 128, N = D, K = 16, 4 instructions; O in columns [128, 128 + D)) and
+//      right behind it S = Q K(i+1)^T (M = 128, N = 64, K = 16, D / 16 instructions), one commit for both.
+// One barrier wait and one __syncthreads per tile.  The steps of one CTA are a dependency chain, so two CTAs
+// share an SM (shared memory is sized for exactly two, and each allocates 256 of the 512 tensor-memory
+// columns): one CTA's softmax runs under the other's matrix products.  O is rescaled in tensor memory only
+// when a row's reference maximum moves (rare, see the lazy rule of the other kernels).
 //
 // Every wait on an mbarrier is bounded; a wait that gives up sets the CTA's abort word, the CTA runs to its
 // end, frees its tensor memory and raises g_umma_status.
@@ -31,6 +31,12 @@ constexpr uint32_t kUmmaColO = 128;
 // 0 = fine; 1 = an mbarrier wait gave up; 2 = shared memory window not 1024-byte aligned
 __device__ int g_umma_status = 0;
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 template <typename TQ, int D>
 struct UmmaPrefillCfg {
   static_assert(D == 128, "head size 128");
@@ -45,7 +51,7 @@ struct UmmaPrefillCfg {
   static constexpr int kOffQ = 0;
   static constexpr int kOffKV = kOffQ + kQBytes;             // [stage][K, V]
   static constexpr int kOffP = kOffKV + kStages * 2 * kKVBytes;
-  static constexpr int kOffBar = kOffP + kPBytes;            // two mbarriers, tensor-memory slot, abort word
+  static constexpr int kOffBar = kOffP + kPBytes;            // the mbarrier, tensor-memory slot, abort word
   static constexpr int kSmemBytes = kOffBar + 64;
   // two CTAs per SM: 2 x (bytes + 1 KB the system keeps per CTA) within the SM's 228 KB
   static_assert(2 * (kSmemBytes + 1024) <= 233472, "two CTAs per SM");
@@ -64,9 +70,8 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
   unsigned char* s_q = smem + Cfg::kOffQ;
   unsigned char* s_kv = smem + Cfg::kOffKV;
   unsigned char* s_p = smem + Cfg::kOffP;
-  uint64_t* bar_s = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
-  uint64_t* bar_o = bar_s + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_s + 2);
+  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -114,8 +119,7 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
 
   // ---- barriers and tensor memory ----------------------------------------------------------------------
   if (tid == 0) {
-    mbar_init(bar_s, 1);
-    mbar_init(bar_o, 1);
+    mbar_init(bar, 1);
     *abort_word = 0;
     mbar_init_fence();
   }
@@ -133,34 +137,51 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
     *reinterpret_cast<uint4*>(s_q + (col >> 3) * Cfg::kQHalfBytes + swizzled_offset(r, col & 7)) = v;
   }
 
-  // ---- producer: thread t copies chunk t % 16 of rows t / 16 + 8 i ---------------------------------------
+  // ---- producer: thread t copies chunk t % 16 of rows t / 16 + 8 i of a K or a V tile ----------------------
   const int32_t* table = p.block_table + seq * p.block_table_stride;
   const int64_t head_off = static_cast<int64_t>(kvh) * p.head_stride;
-  const int64_t v_minus_k =
-      static_cast<const unsigned char*>(p.value_cache) - static_cast<const unsigned char*>(p.key_cache);
-  auto load_tile = [&](int tile, int stage) {
-    constexpr int kChunks = D / 8;  // 16-byte chunks per row
-    constexpr int kRowsPerPass = 128 / kChunks;
-    const int r0 = tid / kChunks, col = tid % kChunks;
+  // The thread's chunk of row r0 + 8 i sits 1024 i bytes after its chunk of row r0 (the swizzle repeats every
+  // 8 rows).  With power-of-two blocks of at least 64 tokens a tile lies inside one block: one table lookup per
+  // tile and a constant pointer step per row; other block sizes look every row up.
+  constexpr int kChunks = D / 8;  // 16-byte chunks per row
+  constexpr int kRowsPerPass = 128 / kChunks;
+  const int ld_r0 = tid / kChunks, ld_col = tid % kChunks;
+  const uint32_t ld_dst = (ld_col >> 3) * Cfg::kKVHalfBytes + swizzled_offset(ld_r0, ld_col & 7);
+  const bool tile_in_block = p.bs_shift >= 6;
+  const int64_t row_step_bytes = p.page_stride * 2 * kRowsPerPass;
+  auto load_rows = [&](int tile, const void* cache, unsigned char* dst_tile) {
     const int rows_left = n - tile * TN;
-    unsigned char* ks = s_kv + stage * 2 * KVB;
+    const uint32_t dst0 = smem_addr(dst_tile) + ld_dst;
+    if (tile_in_block) {
+      const int token0 = tile * TN;
+      const int64_t blk = __ldg(table + (token0 >> p.bs_shift));
+      const unsigned char* src =
+          static_cast<const unsigned char*>(cache) +
+          (blk * p.block_stride + static_cast<int64_t>((token0 & (p.block_size - 1)) + ld_r0) * p.page_stride + head_off) * 2 +
+          ld_col * 16;
 #pragma unroll
-    for (int i = 0; i < TN / kRowsPerPass; ++i) {
-      const int r = r0 + i * kRowsPerPass;
-      const int token = tile * TN + r;
-      const bool valid = r < rows_left;
-      int64_t off = 0;
-      if (valid) {
-        const int blk_idx = p.bs_shift >= 0 ? (token >> p.bs_shift) : token / p.block_size;
-        off = (static_cast<int64_t>(__ldg(table + blk_idx)) * p.block_stride +
-               static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride + head_off) * 2;
+      for (int i = 0; i < TN / kRowsPerPass; ++i) {
+        cp_async_16(dst0 + i * 1024, src, ld_r0 + i * kRowsPerPass < rows_left ? 16 : 0);
+        src += row_step_bytes;
       }
-      const unsigned char* src = static_cast<const unsigned char*>(p.key_cache) + off + col * 16;
-      const uint32_t dst = smem_addr(ks + (col >> 3) * Cfg::kKVHalfBytes) + swizzled_offset(r, col & 7);
-      cp_async_16(dst, src, valid ? 16 : 0);
-      cp_async_16(dst + KVB, src + v_minus_k, valid ? 16 : 0);
+    } else {
+#pragma unroll
+      for (int i = 0; i < TN / kRowsPerPass; ++i) {
+        const int r = ld_r0 + i * kRowsPerPass;
+        const int token = tile * TN + r;
+        const bool valid = r < rows_left;
+        int64_t off = 0;
+        if (valid) {
+          const int blk_idx = p.bs_shift >= 0 ? (token >> p.bs_shift) : token / p.block_size;
+          off = (static_cast<int64_t>(__ldg(table + blk_idx)) * p.block_stride +
+                 static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride + head_off) * 2;
+        }
+        cp_async_16(dst0 + i * 1024, static_cast<const unsigned char*>(cache) + off + ld_col * 16, valid ? 16 : 0);
+      }
     }
   };
+  auto k_slot = [&](int i) { return s_kv + (i & 1) * 2 * KVB; };
+  auto v_slot = [&](int i) { return s_kv + (i & 1) * 2 * KVB + KVB; };
 
   // ---- this thread's row ----------------------------------------------------------------------------------
   const float scale2 = p.softmax_scale * kLog2e;
@@ -169,10 +190,16 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
   const int lo = tid < rows ? row_lo(tid) : 0;
   float m_run = -INFINITY, l_run = 0.f;
 
-  load_tile(tile_begin, 0);
+  // Tile i of this CTA (token tile tile_begin + i) lives in K slot i & 1 and V slot i & 1.  Copy groups in
+  // commit order: {K(0)}, {K(1), V(0)}, then one group per iteration i: {K(i+2), V(i+1)}.
+  const int nt = tile_end - tile_begin;
+  load_rows(tile_begin, p.key_cache, k_slot(0));
   cp_async_commit();
-
-  fence_smem_to_async_proxy();  // the query rows
+  if (nt > 1) load_rows(tile_begin + 1, p.key_cache, k_slot(1));
+  load_rows(tile_begin, p.value_cache, v_slot(0));
+  cp_async_commit();
+  cp_async_wait<1>();           // K(0)
+  fence_smem_to_async_proxy();  // and the query rows
   fence_before_thread_sync();
   __syncthreads();
   fence_after_thread_sync();
@@ -180,71 +207,81 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
   constexpr uint32_t kIdescQK = instr_desc_f16<TQ>(kUmmaRows, TN, false, false);
   constexpr uint32_t kIdescPV = instr_desc_f16<TQ>(kUmmaRows, D, false, true);
-
-  uint32_t it = 0;
-  for (int tile = tile_begin; tile < tile_end; ++tile, ++it) {
-    const int stage = it & 1;
-    // the other stage and P were last read by the previous tile's second product
-    if (it > 0) mbar_wait_bounded(bar_o, (it - 1) & 1, abort_word);
-    if (tile + 1 < tile_end) load_tile(tile + 1, stage ^ 1);
-    cp_async_commit();
-    cp_async_wait<1>();
-    fence_smem_to_async_proxy();
-    __syncthreads();
-    const uint32_t ks = smem_addr(s_kv + stage * 2 * KVB);
-    const uint32_t vs = ks + KVB;
-    if (tid == 0) {
-      fence_after_thread_sync();
+  auto issue_qk = [&](int i) {  // S = Q K(i)^T
+    const uint32_t ks = smem_addr(k_slot(i));
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        const uint64_t da = smem_desc_sw128(smem_addr(s_q) + (kk >> 2) * Cfg::kQHalfBytes + (kk & 3) * 32, 16, 1024);
-        const uint64_t db = smem_desc_sw128(ks + (kk >> 2) * Cfg::kKVHalfBytes + (kk & 3) * 32, 16, 1024);
-        mma_f16_ss(tmem + kUmmaColS, da, db, kIdescQK, kk > 0 ? 1u : 0u);
-      }
-      mma_commit(bar_s);
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const uint64_t da = smem_desc_sw128(smem_addr(s_q) + (kk >> 2) * Cfg::kQHalfBytes + (kk & 3) * 32, 16, 1024);
+      const uint64_t db = smem_desc_sw128(ks + (kk >> 2) * Cfg::kKVHalfBytes + (kk & 3) * 32, 16, 1024);
+      mma_f16_ss(tmem + kUmmaColS, da, db, kIdescQK, kk > 0 ? 1u : 0u);
     }
-    mbar_wait_bounded(bar_s, it & 1, abort_word);
+  };
+  auto issue_pv = [&](int i) {  // O (+)= P V(i)
+    const uint32_t vs = smem_addr(v_slot(i));
+#pragma unroll
+    for (int kk = 0; kk < TN / 16; ++kk) {
+      const uint64_t da = smem_desc_sw128(smem_addr(s_p) + kk * 32, 16, 1024);
+      const uint64_t db = smem_desc_sw128(vs + kk * 16 * 128, Cfg::kKVHalfBytes, 1024);
+      mma_f16_ss(tmem + kUmmaColO, da, db, kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
+    }
+  };
+  // Phases of the one mbarrier: phase 0 = Q K(0)^T; phase i + 1 = {P V(i), Q K(i+1)^T}.
+  if (tid == 0) {
+    issue_qk(0);
+    mma_commit(bar);
+  }
+
+  for (int it = 0; it < nt; ++it) {
+    const int tile = tile_begin + it;
+    mbar_wait_bounded(bar, it & 1, abort_word, p.debug_flags & 1);  // S(it) is there; P, K slot it & 1 and V slot (it + 1) & 1 are free
     fence_after_thread_sync();
+    if (it + 2 < nt) load_rows(tile + 2, p.key_cache, k_slot(it));
+    if (it + 1 < nt) load_rows(tile + 1, p.value_cache, v_slot(it + 1));
+    cp_async_commit();
 
     // ---- softmax of this thread's row ----------------------------------------------------------------
     uint32_t sa[32], sb[32];
     tmem_ld_32x32(tmem + lane_base + kUmmaColS, sa);
     tmem_ld_32x32(tmem + lane_base + kUmmaColS + 32, sb);
     tmem_ld_wait();
-    float s[64];
+    float2 s2[32];  // the row's 64 scores as pairs, for the packed fp32 instructions
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      s[i] = __uint_as_float(sa[i]);
-      s[32 + i] = __uint_as_float(sb[i]);
+    for (int i = 0; i < 16; ++i) {
+      s2[i] = make_float2(__uint_as_float(sa[2 * i]), __uint_as_float(sa[2 * i + 1]));
+      s2[16 + i] = make_float2(__uint_as_float(sb[2 * i]), __uint_as_float(sb[2 * i + 1]));
     }
     if ((tile + 1) * TN > lim_min || tile * TN < lo_max) {  // some row of the CTA has tokens to mask here
       const int tok0 = tile * TN;
 #pragma unroll
-      for (int i = 0; i < 64; ++i)
-        if (tok0 + i >= lim || tok0 + i < lo) s[i] = -INFINITY;
+      for (int i = 0; i < 32; ++i) {
+        if (tok0 + 2 * i >= lim || tok0 + 2 * i < lo) s2[i].x = -INFINITY;
+        if (tok0 + 2 * i + 1 >= lim || tok0 + 2 * i + 1 < lo) s2[i].y = -INFINITY;
+      }
     }
-    float mx = -INFINITY;
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-    for (int i = 0; i < 64; ++i) mx = fmaxf(mx, s[i]);
+    for (int i = 0; i < 32; ++i) mx4[i & 3] = max3(mx4[i & 3], s2[i].x, s2[i].y);
+    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     const bool move = mx > m_run + lazy_margin;
     const float alpha = move ? fast_exp2((m_run - mx) * scale2) : 1.0f;
     m_run = move ? mx : m_run;
     const float neg_ms = (m_run == -INFINITY) ? 0.f : -m_run * scale2;
     l_run *= alpha;
-    float l_add[4] = {0.f, 0.f, 0.f, 0.f};
+    const float2 sc2 = make_float2(scale2, scale2), nm2 = make_float2(neg_ms, neg_ms);
+    float2 l_add[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       uint32_t w[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float p0 = fast_exp2(fmaf(s[c * 8 + 2 * j], scale2, neg_ms));
-        const float p1 = fast_exp2(fmaf(s[c * 8 + 2 * j + 1], scale2, neg_ms));
-        l_add[j] += p0 + p1;
-        w[j] = pack2<TQ>(p0, p1);
+        const float2 e = __ffma2_rn(s2[c * 4 + j], sc2, nm2);
+        const float2 pr = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+        l_add[j & 1] = __fadd2_rn(l_add[j & 1], pr);
+        w[j] = pack2<TQ>(pr.x, pr.y);
       }
       *reinterpret_cast<uint4*>(s_p + swizzled_offset(tid, c)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    l_run += (l_add[0] + l_add[1]) + (l_add[2] + l_add[3]);
+    l_run += (l_add[0].x + l_add[0].y) + (l_add[1].x + l_add[1].y);
     if (it > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // rare: a reference maximum of the warp moved
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
@@ -257,22 +294,19 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
       }
       tmem_st_wait();
     }
-    fence_smem_to_async_proxy();  // P
+    cp_async_wait<1>();           // all but this iteration's group: V(it) and K(it + 1) have landed
+    fence_smem_to_async_proxy();  // they and P
     fence_before_thread_sync();
     __syncthreads();
     if (tid == 0) {
       fence_after_thread_sync();
-#pragma unroll
-      for (int kk = 0; kk < TN / 16; ++kk) {
-        const uint64_t da = smem_desc_sw128(smem_addr(s_p) + kk * 32, 16, 1024);
-        const uint64_t db = smem_desc_sw128(vs + kk * 16 * 128, Cfg::kKVHalfBytes, 1024);
-        mma_f16_ss(tmem + kUmmaColO, da, db, kIdescPV, (it > 0 || kk > 0) ? 1u : 0u);
-      }
-      mma_commit(bar_o);
+      issue_pv(it);
+      if (it + 1 < nt) issue_qk(it + 1);
+      mma_commit(bar);
     }
   }
   cp_async_wait<0>();
-  const bool finished = mbar_wait_bounded(bar_o, (it - 1) & 1, abort_word);
+  const bool finished = mbar_wait_bounded(bar, nt & 1, abort_word, p.debug_flags & 1);
   fence_after_thread_sync();
   if (!finished && (tid & 31) == 0) atomicMax(&g_umma_status, 1);
 

@@ -126,6 +126,28 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
 }
 __device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+// One bounded try: the hardware parks the thread until the phase with the given parity completes or a time
+// limit of about `hint_ns` passes, whichever is first.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(smem_addr(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return done != 0;
+}
+// Waits until the phase with the given parity has completed, for at most kMaxTries tries of about 20 us each
+// (tens of milliseconds in all; a tile of work takes microseconds).  Returns false when it gave up or when
+// *abort is already set, and sets *abort (a shared-memory word of the CTA) so that every later wait of the CTA
+// returns at once: the kernel then runs to its end on whatever it finds, frees its tensor memory and reports
+// through its status word.
+constexpr uint32_t kMaxTries = 2048;
+constexpr uint32_t kTryNs = 20000;
 __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
@@ -139,16 +161,18 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
-// Polls until the phase with the given parity has completed, at most kMaxPolls times (tens of milliseconds;
-// a tile of work takes microseconds).  Returns false when it gave up or when *abort is already set, and sets
-// *abort (a shared-memory word of the CTA) so that every later wait of the CTA returns at once: the kernel
-// then runs to its end on whatever it finds, frees its tensor memory and reports through its status word.
-constexpr uint32_t kMaxPolls = 1u << 20;
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile uint32_t* abort) {
-  for (uint32_t i = 0; i < kMaxPolls; ++i) {
-    if (mbar_test(bar, parity)) return true;
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile uint32_t* abort,
+                                                  bool spin = false) {
+  if (spin) {
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+      if (mbar_test(bar, parity)) return true;
+    }
+    *abort = 1u;
+    return false;
+  }
+  for (uint32_t i = 0; i < kMaxTries; ++i) {
+    if (mbar_try_wait(bar, parity, kTryNs)) return true;
     if (*abort) return false;
-    if (i > 64) __nanosleep(32);
   }
   *abort = 1u;
   return false;
