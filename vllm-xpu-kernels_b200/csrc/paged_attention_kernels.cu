@@ -1221,7 +1221,7 @@ cudaError_t launch_prefill_umma(const DecodeParams& p, dim3 grid, cudaStream_t s
                                            cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (getenv("KVC_DEBUG_OCCUPANCY")) {
       int ctas = -1;
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, paged_prefill_umma_kernel<TQ, 128>, 128, Cfg::kSmemBytes);
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, paged_prefill_umma_kernel<TQ, 128>, kUmmaThreads, Cfg::kSmemBytes);
       fprintf(stderr, "kvc: paged_prefill_umma_kernel: %d CTAs per SM (%d bytes of shared memory each)\n", ctas,
               Cfg::kSmemBytes);
     }
@@ -1229,7 +1229,7 @@ cudaError_t launch_prefill_umma(const DecodeParams& p, dim3 grid, cudaStream_t s
   if (attr_err[dev] != cudaSuccess) return attr_err[dev];
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(128);
+  cfg.blockDim = dim3(kUmmaThreads);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];

@@ -1,14 +1,19 @@
 // The many-rows attention kernel on the fifth-generation tensor cores (tcgen05, accumulators in tensor
 // memory).  Included by paged_attention_kernels.cu after DecodeParams and the cp.async helpers.
 //
-// Division of labour: a CTA of 128 threads owns 128 query rows (token-major (token, head) pairs of one kv
-// head) and walks the cached tokens in tiles of 64.  Per tile i
-//   1. all threads wait for S(i) = Q K(i)^T in tensor-memory columns [0, 64) and start the copies of K(i+2) and
+// Division of labour: a CTA of 256 threads owns 128 query rows (token-major (token, head) pairs of one kv
+// head) and walks the cached tokens in tiles of 64.  Row r belongs to thread r of each of the two warpgroups
+// (tensor-memory lane r is readable by warps r / 32 and r / 32 + 4); the first warpgroup works on columns
+// [0, 32) of a tile's scores and columns [0, D / 2) of the accumulator, the second on the other halves.  Per
+// tile i
+//   1. all threads wait for S(i) = Q K(i)^T in tensor-memory columns [0, 64) or [64, 128) and start the copies of K(i+2) and
 //      V(i+1) into the slots that the finished products have released (cp.async, 128-byte swizzle),
-//   2. thread r reads row r of S (tensor-memory lane r), applies mask and online softmax with no shuffle at
-//      all, and writes row r of P as 16-bit values into shared memory,
+//   2. the two threads of row r read their halves of row r of S, apply the mask, agree on the row's maximum
+//      through one float of shared memory and two named barriers, and write their halves of row r of P as
+//      16-bit values into shared memory (no shuffle at all),
 //   3. thread 0 issues O += P V(i)  (M = 128, N = D, K = 16, 4 instructions; O in columns [128, 128 + D)) and
-//      right behind it S = Q K(i+1)^T (M = 128, N = 64, K = 16, D / 16 instructions), one commit for both.
+//      commits.  S(i+1) = Q K(i+1)^T (M = 128, N = 64, K = 16, D / 16 instructions) was issued in step 1, into
+//      the other of two score buffers, and runs under the softmax of tile i; the commit covers both.
 // One barrier wait and one __syncthreads per tile.  The steps of one CTA are a dependency chain, so two CTAs
 // share an SM (shared memory is sized for exactly two, and each allocates 256 of the 512 tensor-memory
 // columns): one CTA's softmax runs under the other's matrix products.  O is rescaled in tensor memory only
@@ -24,12 +29,21 @@ namespace kvc {
 namespace {
 
 constexpr int kUmmaRows = 128;
+constexpr int kUmmaThreads = 256;  // two warpgroups: both own all 128 rows, each one half of a tile's 64 columns
 constexpr uint32_t kUmmaTmemCols = 256;
 constexpr uint32_t kUmmaColS = 0;
 constexpr uint32_t kUmmaColO = 128;
 
 // 0 = fine; 1 = an mbarrier wait gave up; 2 = shared memory window not 1024-byte aligned
 __device__ int g_umma_status = 0;
+
+// named barriers of the CTA (0 is __syncthreads): arrive does not wait, sync does; `threads` take part in all
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void named_bar_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
@@ -52,7 +66,8 @@ struct UmmaPrefillCfg {
   static constexpr int kOffKV = kOffQ + kQBytes;             // [stage][K, V]
   static constexpr int kOffP = kOffKV + kStages * 2 * kKVBytes;
   static constexpr int kOffBar = kOffP + kPBytes;            // the mbarrier, tensor-memory slot, abort word
-  static constexpr int kSmemBytes = kOffBar + 64;
+  static constexpr int kOffXch = kOffBar + 16;               // one float per row: the warpgroups' exchange
+  static constexpr int kSmemBytes = kOffXch + kUmmaRows * 4;
   // two CTAs per SM: 2 x (bytes + 1 KB the system keeps per CTA) within the SM's 228 KB
   static_assert(2 * (kSmemBytes + 1024) <= 233472, "two CTAs per SM");
   // and never three, which could ask for more tensor memory than an SM has
@@ -60,7 +75,7 @@ struct UmmaPrefillCfg {
 };
 
 template <typename TQ, int D>
-__global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(const DecodeParams p) {
   using Cfg = UmmaPrefillCfg<TQ, D>;
   using namespace umma;
   constexpr int TN = Cfg::kTile;
@@ -73,8 +88,11 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
   uint64_t* bar = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
   volatile uint32_t* abort_word = tmem_slot + 1;
+  volatile float* xch = reinterpret_cast<volatile float*>(smem + Cfg::kOffXch);
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int wg = warp >> 2;               // warpgroup: which 32 of a tile's 64 columns (and which half of O)
+  const int row = tid & (kUmmaRows - 1);  // tensor-memory lane = query row; warps w and w + 4 share their lanes
   const int seq = blockIdx.y;
   const int row_tile = p.row_tiles - 1 - static_cast<int>(blockIdx.x / p.num_kv_heads);  // heaviest first
   const int kvh = blockIdx.x % p.num_kv_heads;
@@ -105,7 +123,7 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
   const int tile_begin = row_lo(0) / TN;
 
   if (tile_end <= tile_begin) {  // no row sees any token
-    for (int i = tid; i < rows * D; i += 128) {
+    for (int i = tid; i < rows * D; i += kUmmaThreads) {
       const int r = i / D;
       static_cast<TQ*>(p.out)[static_cast<int64_t>(q_start + row_token(r)) * p.out_stride_t +
                               row_head(r) * p.out_stride_h + i % D] = TQ(0.0f);
@@ -126,7 +144,7 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
   if (warp == 0) tmem_alloc(tmem_slot, kUmmaTmemCols);
 
   // ---- query rows -> shared memory (zero rows past the end) --------------------------------------------
-  for (int c = tid; c < kUmmaRows * (D / 8); c += 128) {
+  for (int c = tid; c < kUmmaRows * (D / 8); c += kUmmaThreads) {
     const int r = c / (D / 8), col = c % (D / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < rows) {
@@ -140,11 +158,11 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
   // ---- producer: thread t copies chunk t % 16 of rows t / 16 + 8 i of a K or a V tile ----------------------
   const int32_t* table = p.block_table + seq * p.block_table_stride;
   const int64_t head_off = static_cast<int64_t>(kvh) * p.head_stride;
-  // The thread's chunk of row r0 + 8 i sits 1024 i bytes after its chunk of row r0 (the swizzle repeats every
+  // The thread's chunk of row r0 + 16 i sits 2048 i bytes after its chunk of row r0 (the swizzle repeats every
   // 8 rows).  With power-of-two blocks of at least 64 tokens a tile lies inside one block: one table lookup per
   // tile and a constant pointer step per row; other block sizes look every row up.
   constexpr int kChunks = D / 8;  // 16-byte chunks per row
-  constexpr int kRowsPerPass = 128 / kChunks;
+  constexpr int kRowsPerPass = kUmmaThreads / kChunks;
   const int ld_r0 = tid / kChunks, ld_col = tid % kChunks;
   const uint32_t ld_dst = (ld_col >> 3) * Cfg::kKVHalfBytes + swizzled_offset(ld_r0, ld_col & 7);
   const bool tile_in_block = p.bs_shift >= 6;
@@ -161,7 +179,7 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
           ld_col * 16;
 #pragma unroll
       for (int i = 0; i < TN / kRowsPerPass; ++i) {
-        cp_async_16(dst0 + i * 1024, src, ld_r0 + i * kRowsPerPass < rows_left ? 16 : 0);
+        cp_async_16(dst0 + i * (kRowsPerPass * 128), src, ld_r0 + i * kRowsPerPass < rows_left ? 16 : 0);
         src += row_step_bytes;
       }
     } else {
@@ -176,7 +194,7 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
           off = (static_cast<int64_t>(__ldg(table + blk_idx)) * p.block_stride +
                  static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride + head_off) * 2;
         }
-        cp_async_16(dst0 + i * 1024, static_cast<const unsigned char*>(cache) + off + ld_col * 16, valid ? 16 : 0);
+        cp_async_16(dst0 + i * (kRowsPerPass * 128), static_cast<const unsigned char*>(cache) + off + ld_col * 16, valid ? 16 : 0);
       }
     }
   };
@@ -186,46 +204,61 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
   // ---- this thread's row ----------------------------------------------------------------------------------
   const float scale2 = p.softmax_scale * kLog2e;
   const float lazy_margin = 8.0f / scale2;
-  const int lim = tid < rows ? row_limit(tid) : 0;
-  const int lo = tid < rows ? row_lo(tid) : 0;
-  float m_run = -INFINITY, l_run = 0.f;
+  const int lim = row < rows ? row_limit(row) : 0;
+  const int lo = row < rows ? row_lo(row) : 0;
+  float m_run = -INFINITY, l_run = 0.f;  // the reference maximum is kept by both warpgroups, the sum is partial
 
   // Tile i of this CTA (token tile tile_begin + i) lives in K slot i & 1 and V slot i & 1.  Copy groups in
-  // commit order: {K(0)}, {K(1), V(0)}, then one group per iteration i: {K(i+2), V(i+1)}.
+  // commit order: {K(0), K(1)}, {V(0)}, then two groups per iteration i: {K(i+2)}, {V(i+1)}.  Waiting for all but
+  // the newest group at the end of iteration i therefore covers K(i+2), which the next iteration's first act
+  // consumes, and V(i); V(i+1) has another iteration to land.
   const int nt = tile_end - tile_begin;
   load_rows(tile_begin, p.key_cache, k_slot(0));
-  cp_async_commit();
   if (nt > 1) load_rows(tile_begin + 1, p.key_cache, k_slot(1));
+  cp_async_commit();
   load_rows(tile_begin, p.value_cache, v_slot(0));
   cp_async_commit();
-  cp_async_wait<1>();           // K(0)
+  cp_async_wait<1>();           // K(0), K(1)
   fence_smem_to_async_proxy();  // and the query rows
   fence_before_thread_sync();
   __syncthreads();
   fence_after_thread_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
   constexpr uint32_t kIdescQK = instr_desc_f16<TQ>(kUmmaRows, TN, false, false);
   constexpr uint32_t kIdescPV = instr_desc_f16<TQ>(kUmmaRows, D, false, true);
-  auto issue_qk = [&](int i) {  // S = Q K(i)^T
-    const uint32_t ks = smem_addr(k_slot(i));
+  // Descriptors: the upper word is constant per operand role, the lower one is (address >> 4) plus the leading
+  // byte offset; shared-memory addresses are below 2^18, so stepping an operand is an add on the lower word.
+  constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
+  constexpr uint32_t kLboK = (16u >> 4) << 16;                          // K-major operands: unused, 16 by convention
+  constexpr uint32_t kLboV = (static_cast<uint32_t>(Cfg::kKVHalfBytes) >> 4) << 16;  // V: distance of the D halves
+  auto make_desc = [](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
+  const uint32_t q_lo = (smem_addr(s_q) >> 4) | kLboK;
+  const uint32_t p_lo = (smem_addr(s_p) >> 4) | kLboK;
+  const uint32_t k_lo0 = (smem_addr(s_kv) >> 4) | kLboK;
+  const uint32_t v_lo0 = (smem_addr(s_kv + KVB) >> 4) | kLboV;
+  auto issue_qk = [&](int i) {  // S(i) = Q K(i)^T into the score buffer i & 1
+    const uint32_t k_lo = k_lo0 + (i & 1) * ((2 * KVB) >> 4);
+    const uint32_t s_col = tmem + kUmmaColS + (i & 1) * TN;
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
-      const uint64_t da = smem_desc_sw128(smem_addr(s_q) + (kk >> 2) * Cfg::kQHalfBytes + (kk & 3) * 32, 16, 1024);
-      const uint64_t db = smem_desc_sw128(ks + (kk >> 2) * Cfg::kKVHalfBytes + (kk & 3) * 32, 16, 1024);
-      mma_f16_ss(tmem + kUmmaColS, da, db, kIdescQK, kk > 0 ? 1u : 0u);
+      const uint64_t da = make_desc(q_lo + (((kk >> 2) * Cfg::kQHalfBytes + (kk & 3) * 32) >> 4));
+      const uint64_t db = make_desc(k_lo + (((kk >> 2) * Cfg::kKVHalfBytes + (kk & 3) * 32) >> 4));
+      mma_f16_ss(s_col, da, db, kIdescQK, kk > 0 ? 1u : 0u);
     }
   };
   auto issue_pv = [&](int i) {  // O (+)= P V(i)
-    const uint32_t vs = smem_addr(v_slot(i));
+    const uint32_t v_lo = v_lo0 + (i & 1) * ((2 * KVB) >> 4);
 #pragma unroll
     for (int kk = 0; kk < TN / 16; ++kk) {
-      const uint64_t da = smem_desc_sw128(smem_addr(s_p) + kk * 32, 16, 1024);
-      const uint64_t db = smem_desc_sw128(vs + kk * 16 * 128, Cfg::kKVHalfBytes, 1024);
+      const uint64_t da = make_desc(p_lo + ((kk * 32) >> 4));
+      const uint64_t db = make_desc(v_lo + ((kk * 16 * 128) >> 4));
       mma_f16_ss(tmem + kUmmaColO, da, db, kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
     }
   };
-  // Phases of the one mbarrier: phase 0 = Q K(0)^T; phase i + 1 = {P V(i), Q K(i+1)^T}.
+  // Phases of the one mbarrier: phase 0 = Q K(0)^T; phase i + 1 = {Q K(i+1)^T, issued when iteration i starts and
+  // running under its softmax, and P V(i), issued when the softmax is done}.  The scores alternate between two
+  // buffers of 64 tensor-memory columns.
   if (tid == 0) {
     issue_qk(0);
     mma_commit(bar);
@@ -235,33 +268,43 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
     const int tile = tile_begin + it;
     mbar_wait_bounded(bar, it & 1, abort_word, p.debug_flags & 1);  // S(it) is there; P, K slot it & 1 and V slot (it + 1) & 1 are free
     fence_after_thread_sync();
+    if (tid == 0 && it + 1 < nt) issue_qk(it + 1);  // K(it + 1) landed before the previous iteration's barrier
     if (it + 2 < nt) load_rows(tile + 2, p.key_cache, k_slot(it));
+    cp_async_commit();
     if (it + 1 < nt) load_rows(tile + 1, p.value_cache, v_slot(it + 1));
     cp_async_commit();
 
-    // ---- softmax of this thread's row ----------------------------------------------------------------
-    uint32_t sa[32], sb[32];
-    tmem_ld_32x32(tmem + lane_base + kUmmaColS, sa);
-    tmem_ld_32x32(tmem + lane_base + kUmmaColS + 32, sb);
+    // ---- softmax of this thread's half row: columns [32 wg, 32 wg + 32) of the tile ---------------------------
+    uint32_t sa[32];
+    tmem_ld_32x32(tmem + lane_base + kUmmaColS + (it & 1) * TN + wg * 32, sa);
     tmem_ld_wait();
-    float2 s2[32];  // the row's 64 scores as pairs, for the packed fp32 instructions
+    float2 s2[16];  // the scores as pairs, for the packed fp32 instructions
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      s2[i] = make_float2(__uint_as_float(sa[2 * i]), __uint_as_float(sa[2 * i + 1]));
-      s2[16 + i] = make_float2(__uint_as_float(sb[2 * i]), __uint_as_float(sb[2 * i + 1]));
-    }
+    for (int i = 0; i < 16; ++i) s2[i] = make_float2(__uint_as_float(sa[2 * i]), __uint_as_float(sa[2 * i + 1]));
     if ((tile + 1) * TN > lim_min || tile * TN < lo_max) {  // some row of the CTA has tokens to mask here
-      const int tok0 = tile * TN;
+      const int tok0 = tile * TN + wg * 32;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
+      for (int i = 0; i < 16; ++i) {
         if (tok0 + 2 * i >= lim || tok0 + 2 * i < lo) s2[i].x = -INFINITY;
         if (tok0 + 2 * i + 1 >= lim || tok0 + 2 * i + 1 < lo) s2[i].y = -INFINITY;
       }
     }
     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-    for (int i = 0; i < 32; ++i) mx4[i & 3] = max3(mx4[i & 3], s2[i].x, s2[i].y);
-    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+    for (int i = 0; i < 16; ++i) mx4[i & 3] = max3(mx4[i & 3], s2[i].x, s2[i].y);
+    float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+    // the row's maximum over both halves: the second warpgroup hands its half over, the first one answers
+    if (wg == 1) {
+      xch[row] = mx;
+      named_bar_arrive(1, kUmmaThreads);
+      named_bar_sync(2, kUmmaThreads);
+      mx = xch[row];
+    } else {
+      named_bar_sync(1, kUmmaThreads);
+      mx = fmaxf(mx, xch[row]);
+      xch[row] = mx;
+      named_bar_arrive(2, kUmmaThreads);
+    }
     const bool move = mx > m_run + lazy_margin;
     const float alpha = move ? fast_exp2((m_run - mx) * scale2) : 1.0f;
     m_run = move ? mx : m_run;
@@ -270,7 +313,7 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
     const float2 sc2 = make_float2(scale2, scale2), nm2 = make_float2(neg_ms, neg_ms);
     float2 l_add[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < 4; ++c) {
       uint32_t w[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -279,29 +322,29 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
         l_add[j & 1] = __fadd2_rn(l_add[j & 1], pr);
         w[j] = pack2<TQ>(pr.x, pr.y);
       }
-      *reinterpret_cast<uint4*>(s_p + swizzled_offset(tid, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(s_p + swizzled_offset(row, wg * 4 + c)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
     l_run += (l_add[0].x + l_add[0].y) + (l_add[1].x + l_add[1].y);
     if (it > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // rare: a reference maximum of the warp moved
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {  // this warpgroup's half of the accumulator's columns
         uint32_t o[32];
-        tmem_ld_32x32(tmem + lane_base + kUmmaColO + c * 32, o);
+        const uint32_t col = kUmmaColO + wg * (D / 2) + c * 32;
+        tmem_ld_32x32(tmem + lane_base + col, o);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-        tmem_st_32x32(tmem + lane_base + kUmmaColO + c * 32, o);
+        tmem_st_32x32(tmem + lane_base + col, o);
       }
       tmem_st_wait();
     }
-    cp_async_wait<1>();           // all but this iteration's group: V(it) and K(it + 1) have landed
+    cp_async_wait<1>();           // all but this iteration's V group: V(it) and K(it + 2) have landed
     fence_smem_to_async_proxy();  // they and P
     fence_before_thread_sync();
     __syncthreads();
     if (tid == 0) {
       fence_after_thread_sync();
       issue_pv(it);
-      if (it + 1 < nt) issue_qk(it + 1);
       mma_commit(bar);
     }
   }
@@ -310,11 +353,19 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
   fence_after_thread_sync();
   if (!finished && (tid & 31) == 0) atomicMax(&g_umma_status, 1);
 
-  // ---- every thread finishes its own row ------------------------------------------------------------------
+  // ---- the two threads of a row add up their sums, then each finishes its half of the row ---------------------
   {
-    const bool live = tid < rows;
-    const int head = live ? row_head(tid) : 0;
+    if (wg == 1) xch[row] = l_run;
+    __syncthreads();
     float l = l_run;
+    if (wg == 0) {
+      l += xch[row];
+      xch[row] = l;
+    }
+    __syncthreads();
+    if (wg == 1) l = xch[row];
+    const bool live = row < rows;
+    const int head = live ? row_head(row) : 0;
     const float m = m_run * scale2;  // log2 domain; -inf if the row saw nothing
     float rescale = 1.0f;
     if (p.sink && live) {
@@ -324,15 +375,15 @@ __global__ void __launch_bounds__(128, 2) paged_prefill_umma_kernel(const Decode
       l = l * rescale + exp2f(sk - mf);
     }
     const float f = (l > 0.f) ? rescale / l : 0.f;
-    TQ* o = static_cast<TQ*>(p.out) + (live ? static_cast<int64_t>(q_start + row_token(tid)) * p.out_stride_t +
-                                                  static_cast<int64_t>(head) * p.out_stride_h
+    TQ* o = static_cast<TQ*>(p.out) + (live ? static_cast<int64_t>(q_start + row_token(row)) * p.out_stride_t +
+                                                  static_cast<int64_t>(head) * p.out_stride_h + wg * (D / 2)
                                             : 0);
     const bool vec16 = ((reinterpret_cast<uintptr_t>(p.out) | static_cast<uintptr_t>(p.out_stride_t * 2) |
                          static_cast<uintptr_t>(p.out_stride_h * 2)) & 15u) == 0;
 #pragma unroll 1
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = 0; c < D / 64; ++c) {
       uint32_t acc[32];
-      tmem_ld_32x32(tmem + lane_base + kUmmaColO + c * 32, acc);
+      tmem_ld_32x32(tmem + lane_base + kUmmaColO + wg * (D / 2) + c * 32, acc);
       tmem_ld_wait();
       if (!live) continue;
       uint32_t w[16];
