@@ -60,13 +60,11 @@ struct UmmaPrefillCfg {
   static constexpr int kQBytes = kQHalfBytes * kHalves;      // 32 KB
   static constexpr int kKVHalfBytes = kTile * 128;           // 8 KB
   static constexpr int kKVBytes = kKVHalfBytes * kHalves;    // one K or V tile: 16 KB
-  static constexpr int kPBytes = kUmmaRows * 128;            // 128 rows x 64 probabilities: 16 KB
   static constexpr int kStages = 2;
   static constexpr int kOffQ = 0;
   static constexpr int kOffKV = kOffQ + kQBytes;             // [stage][K, V]
-  static constexpr int kOffP = kOffKV + kStages * 2 * kKVBytes;
-  static constexpr int kOffBar = kOffP + kPBytes;            // the mbarrier, tensor-memory slot, abort word
-  static constexpr int kOffXch = kOffBar + 16;               // one float per row: the warpgroups' exchange
+  static constexpr int kOffBar = kOffKV + kStages * 2 * kKVBytes;  // two mbarriers, tensor-memory slot, abort word
+  static constexpr int kOffXch = kOffBar + 32;               // one float per row: the warpgroups' exchange
   static constexpr int kSmemBytes = kOffXch + kUmmaRows * 4;
   // two CTAs per SM: 2 x (bytes + 1 KB the system keeps per CTA) within the SM's 228 KB
   static_assert(2 * (kSmemBytes + 1024) <= 233472, "two CTAs per SM");
@@ -84,9 +82,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* s_q = smem + Cfg::kOffQ;
   unsigned char* s_kv = smem + Cfg::kOffKV;
-  unsigned char* s_p = smem + Cfg::kOffP;
-  uint64_t* bar = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+  uint64_t* bar_s = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);  // phase j: S(j) = Q K(j)^T is complete
+  uint64_t* bar_o = bar_s + 1;                                         // phase j: O += P(j) V(j) is complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_s + 2);
   volatile uint32_t* abort_word = tmem_slot + 1;
   volatile float* xch = reinterpret_cast<volatile float*>(smem + Cfg::kOffXch);
 
@@ -137,7 +135,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
 
   // ---- barriers and tensor memory ----------------------------------------------------------------------
   if (tid == 0) {
-    mbar_init(bar, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
     *abort_word = 0;
     mbar_init_fence();
   }
@@ -234,7 +233,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   constexpr uint32_t kLboV = (static_cast<uint32_t>(Cfg::kKVHalfBytes) >> 4) << 16;  // V: distance of the D halves
   auto make_desc = [](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
   const uint32_t q_lo = (smem_addr(s_q) >> 4) | kLboK;
-  const uint32_t p_lo = (smem_addr(s_p) >> 4) | kLboK;
   const uint32_t k_lo0 = (smem_addr(s_kv) >> 4) | kLboK;
   const uint32_t v_lo0 = (smem_addr(s_kv + KVB) >> 4) | kLboV;
   auto issue_qk = [&](int i) {  // S(i) = Q K(i)^T into the score buffer i & 1
@@ -247,31 +245,28 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
       mma_f16_ss(s_col, da, db, kIdescQK, kk > 0 ? 1u : 0u);
     }
   };
-  auto issue_pv = [&](int i) {  // O (+)= P V(i)
+  auto issue_pv = [&](int i) {  // O (+)= P(i) V(i), P from the first 32 columns of score buffer i & 1
     const uint32_t v_lo = v_lo0 + (i & 1) * ((2 * KVB) >> 4);
+    const uint32_t p_col = tmem + kUmmaColS + (i & 1) * TN;
 #pragma unroll
     for (int kk = 0; kk < TN / 16; ++kk) {
-      const uint64_t da = make_desc(p_lo + ((kk * 32) >> 4));
       const uint64_t db = make_desc(v_lo + ((kk * 16 * 128) >> 4));
-      mma_f16_ss(tmem + kUmmaColO, da, db, kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
+      mma_f16_ts(tmem + kUmmaColO, p_col + kk * 8, db, kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
     }
   };
-  // Phases of the one mbarrier: phase 0 = Q K(0)^T; phase i + 1 = {Q K(i+1)^T, issued when iteration i starts and
-  // running under its softmax, and P V(i), issued when the softmax is done}.  The scores alternate between two
-  // buffers of 64 tensor-memory columns.
+  // The tensor pipe executes this thread's instructions in issue order: Q K(0)^T, then per iteration i
+  // Q K(i+1)^T (issued when the iteration starts) and P(i) V(i) (issued when its softmax is done).  Each
+  // product is followed by a commit to its own mbarrier.
   if (tid == 0) {
     issue_qk(0);
-    mma_commit(bar);
+    mma_commit(bar_s);
   }
 
   for (int it = 0; it < nt; ++it) {
     const int tile = tile_begin + it;
-    mbar_wait_bounded(bar, it & 1, abort_word, p.debug_flags & 1);  // S(it) is there; P, K slot it & 1 and V slot (it + 1) & 1 are free
+    mbar_wait_bounded(bar_s, it & 1, abort_word, p.debug_flags & 1);  // S(it) is there, K slot it & 1 is free
     fence_after_thread_sync();
-    if (tid == 0 && it + 1 < nt) issue_qk(it + 1);  // K(it + 1) landed before the previous iteration's barrier
     if (it + 2 < nt) load_rows(tile + 2, p.key_cache, k_slot(it));
-    cp_async_commit();
-    if (it + 1 < nt) load_rows(tile + 1, p.value_cache, v_slot(it + 1));
     cp_async_commit();
 
     // ---- softmax of this thread's half row: columns [32 wg, 32 wg + 32) of the tile ---------------------------
@@ -304,6 +299,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
       mx = fmaxf(mx, xch[row]);
       xch[row] = mx;
       named_bar_arrive(2, kUmmaThreads);
+      // Every thread has passed its wait for S(it) by now (it took part in barrier 1), so the barrier of the
+      // scores may move on by a phase: the next tile's first product goes out and runs under this softmax.
+      // K(it + 1) landed before the previous iteration's __syncthreads.
+      if (tid == 0 && it + 1 < nt) {
+        issue_qk(it + 1);
+        mma_commit(bar_s);
+      }
     }
     const bool move = mx > m_run + lazy_margin;
     const float alpha = move ? fast_exp2((m_run - mx) * scale2) : 1.0f;
@@ -312,19 +314,23 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
     l_run *= alpha;
     const float2 sc2 = make_float2(scale2, scale2), nm2 = make_float2(neg_ms, neg_ms);
     float2 l_add[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+    uint32_t w[16];  // this thread's 32 probabilities, two 16-bit values per word
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t w[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 e = __ffma2_rn(s2[c * 4 + j], sc2, nm2);
-        const float2 pr = make_float2(fast_exp2(e.x), fast_exp2(e.y));
-        l_add[j & 1] = __fadd2_rn(l_add[j & 1], pr);
-        w[j] = pack2<TQ>(pr.x, pr.y);
-      }
-      *reinterpret_cast<uint4*>(s_p + swizzled_offset(row, wg * 4 + c)) = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int j = 0; j < 16; ++j) {
+      const float2 e = __ffma2_rn(s2[j], sc2, nm2);
+      const float2 pr = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+      l_add[j & 1] = __fadd2_rn(l_add[j & 1], pr);
+      w[j] = pack2<TQ>(pr.x, pr.y);
     }
     l_run += (l_add[0].x + l_add[0].y) + (l_add[1].x + l_add[1].y);
+    // The previous tile's second product has had this softmax to finish: O is up to date for a rescale and
+    // V slot (it + 1) & 1 is free.
+    if (it > 0) {
+      mbar_wait_bounded(bar_o, (it - 1) & 1, abort_word, p.debug_flags & 1);
+      fence_after_thread_sync();
+    }
+    if (it + 1 < nt) load_rows(tile + 1, p.value_cache, v_slot(it + 1));
+    cp_async_commit();
     if (it > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // rare: a reference maximum of the warp moved
 #pragma unroll 1
       for (int c = 0; c < D / 64; ++c) {  // this warpgroup's half of the accumulator's columns
@@ -336,20 +342,22 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
         for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
         tmem_st_32x32(tmem + lane_base + col, o);
       }
-      tmem_st_wait();
     }
+    // P(it) takes the place of S(it): both warpgroups have read their halves (the exchange above orders that)
+    tmem_st_32x16(tmem + lane_base + kUmmaColS + (it & 1) * TN + wg * 16, w);
+    tmem_st_wait();
     cp_async_wait<1>();           // all but this iteration's V group: V(it) and K(it + 2) have landed
-    fence_smem_to_async_proxy();  // they and P
+    fence_smem_to_async_proxy();
     fence_before_thread_sync();
     __syncthreads();
     if (tid == 0) {
       fence_after_thread_sync();
       issue_pv(it);
-      mma_commit(bar);
+      mma_commit(bar_o);
     }
   }
   cp_async_wait<0>();
-  const bool finished = mbar_wait_bounded(bar, nt & 1, abort_word, p.debug_flags & 1);
+  const bool finished = mbar_wait_bounded(bar_o, (nt - 1) & 1, abort_word, p.debug_flags & 1);
   fence_after_thread_sync();
   if (!finished && (tid & 31) == 0) atomicMax(&g_umma_status, 1);
 
