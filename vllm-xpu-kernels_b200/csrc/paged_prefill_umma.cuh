@@ -29,7 +29,8 @@ namespace kvc {
 namespace {
 
 constexpr int kUmmaRows = 128;
-constexpr int kUmmaThreads = 256;  // two warpgroups: both own all 128 rows, each one half of a tile's 64 columns
+constexpr int kUmmaSoftmaxThreads = 256;  // two warpgroups: both own all 128 rows, each one half of a tile's 64 columns
+constexpr int kUmmaThreads = kUmmaSoftmaxThreads + 32;  // and one warp that issues the matrix products
 constexpr uint32_t kUmmaTmemCols = 256;
 constexpr uint32_t kUmmaColS = 0;
 constexpr uint32_t kUmmaColO = 128;
@@ -63,8 +64,8 @@ struct UmmaPrefillCfg {
   static constexpr int kStages = 2;
   static constexpr int kOffQ = 0;
   static constexpr int kOffKV = kOffQ + kQBytes;             // [stage][K, V]
-  static constexpr int kOffBar = kOffKV + kStages * 2 * kKVBytes;  // two mbarriers, tensor-memory slot, abort word
-  static constexpr int kOffXch = kOffBar + 32;               // one float per row: the warpgroups' exchange
+  static constexpr int kOffBar = kOffKV + kStages * 2 * kKVBytes;  // four mbarriers, tensor-memory slot, abort word
+  static constexpr int kOffXch = kOffBar + 48;               // one float per row: the warpgroups' exchange
   static constexpr int kSmemBytes = kOffXch + kUmmaRows * 4;
   // two CTAs per SM: 2 x (bytes + 1 KB the system keeps per CTA) within the SM's 228 KB
   static_assert(2 * (kSmemBytes + 1024) <= 233472, "two CTAs per SM");
@@ -82,9 +83,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* s_q = smem + Cfg::kOffQ;
   unsigned char* s_kv = smem + Cfg::kOffKV;
-  uint64_t* bar_s = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);  // phase j: S(j) = Q K(j)^T is complete
-  uint64_t* bar_o = bar_s + 1;                                         // phase j: O += P(j) V(j) is complete
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_s + 2);
+  uint64_t* bar_s = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);  // [2], one per score buffer: S(j) is complete
+  uint64_t* bar_o = bar_s + 2;                                         // phase j: O += P(j) V(j) is complete
+  uint64_t* bar_ready = bar_s + 3;  // phase j: all 256 softmax threads are done with tile j (P stored, copies landed)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_s + 4);
   volatile uint32_t* abort_word = tmem_slot + 1;
   volatile float* xch = reinterpret_cast<volatile float*>(smem + Cfg::kOffXch);
 
@@ -136,7 +138,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   // ---- barriers and tensor memory ----------------------------------------------------------------------
   if (tid == 0) {
     mbar_init(bar_s, 1);
+    mbar_init(bar_s + 1, 1);
     mbar_init(bar_o, 1);
+    mbar_init(bar_ready, kUmmaSoftmaxThreads);
     *abort_word = 0;
     mbar_init_fence();
   }
@@ -161,7 +165,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   // 8 rows).  With power-of-two blocks of at least 64 tokens a tile lies inside one block: one table lookup per
   // tile and a constant pointer step per row; other block sizes look every row up.
   constexpr int kChunks = D / 8;  // 16-byte chunks per row
-  constexpr int kRowsPerPass = kUmmaThreads / kChunks;
+  constexpr int kRowsPerPass = kUmmaSoftmaxThreads / kChunks;
   const int ld_r0 = tid / kChunks, ld_col = tid % kChunks;
   const uint32_t ld_dst = (ld_col >> 3) * Cfg::kKVHalfBytes + swizzled_offset(ld_r0, ld_col & 7);
   const bool tile_in_block = p.bs_shift >= 6;
@@ -212,11 +216,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   // the newest group at the end of iteration i therefore covers K(i+2), which the next iteration's first act
   // consumes, and V(i); V(i+1) has another iteration to land.
   const int nt = tile_end - tile_begin;
-  load_rows(tile_begin, p.key_cache, k_slot(0));
-  if (nt > 1) load_rows(tile_begin + 1, p.key_cache, k_slot(1));
-  cp_async_commit();
-  load_rows(tile_begin, p.value_cache, v_slot(0));
-  cp_async_commit();
+  const bool softmax_thread = tid < kUmmaSoftmaxThreads;
+  if (softmax_thread) {
+    load_rows(tile_begin, p.key_cache, k_slot(0));
+    if (nt > 1) load_rows(tile_begin + 1, p.key_cache, k_slot(1));
+    cp_async_commit();
+    load_rows(tile_begin, p.value_cache, v_slot(0));
+    cp_async_commit();
+  }
   cp_async_wait<1>();           // K(0), K(1)
   fence_smem_to_async_proxy();  // and the query rows
   fence_before_thread_sync();
@@ -254,17 +261,37 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
       mma_f16_ts(tmem + kUmmaColO, p_col + kk * 8, db, kIdescPV, (i > 0 || kk > 0) ? 1u : 0u);
     }
   };
-  // The tensor pipe executes this thread's instructions in issue order: Q K(0)^T, then per iteration i
-  // Q K(i+1)^T (issued when the iteration starts) and P(i) V(i) (issued when its softmax is done).  Each
-  // product is followed by a commit to its own mbarrier.
-  if (tid == 0) {
-    issue_qk(0);
-    mma_commit(bar_s);
+  // ---- the issuing warp -------------------------------------------------------------------------------------
+  // The tensor pipe executes one thread's instructions in issue order: Q K(0)^T, Q K(1)^T, then per tile j, once
+  // the softmax threads have reported it ready, P(j) V(j) and Q K(j+2)^T (into the score buffer whose P(j) the
+  // product just before it reads).  S(j) is therefore complete about two softmaxes before it is needed, and the
+  // softmax threads wait for the tensor pipe only where they depend on it.  A barrier of the scores serves every
+  // second tile, so it cannot run two phases ahead of a thread that still waits on it.
+  if (!softmax_thread) {
+    if (tid == kUmmaSoftmaxThreads) {
+      issue_qk(0);
+      mma_commit(bar_s);
+      if (nt > 1) {
+        issue_qk(1);
+        mma_commit(bar_s + 1);
+      }
+      for (int j = 0; j < nt; ++j) {
+        mbar_wait_bounded(bar_ready, j & 1, abort_word, p.debug_flags & 1);
+        fence_after_thread_sync();
+        issue_pv(j);
+        mma_commit(bar_o);
+        if (j + 2 < nt) {
+          issue_qk(j + 2);
+          mma_commit(bar_s + (j & 1));
+        }
+      }
+    }
+    __syncwarp();
   }
 
-  for (int it = 0; it < nt; ++it) {
+  for (int it = 0; softmax_thread && it < nt; ++it) {
     const int tile = tile_begin + it;
-    mbar_wait_bounded(bar_s, it & 1, abort_word, p.debug_flags & 1);  // S(it) is there, K slot it & 1 is free
+    mbar_wait_bounded(bar_s + (it & 1), (it >> 1) & 1, abort_word, p.debug_flags & 1);  // S(it) is there, K slot it & 1 is free
     fence_after_thread_sync();
     if (it + 2 < nt) load_rows(tile + 2, p.key_cache, k_slot(it));
     cp_async_commit();
@@ -291,21 +318,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
     // the row's maximum over both halves: the second warpgroup hands its half over, the first one answers
     if (wg == 1) {
       xch[row] = mx;
-      named_bar_arrive(1, kUmmaThreads);
-      named_bar_sync(2, kUmmaThreads);
+      named_bar_arrive(1, kUmmaSoftmaxThreads);
+      named_bar_sync(2, kUmmaSoftmaxThreads);
       mx = xch[row];
     } else {
-      named_bar_sync(1, kUmmaThreads);
+      named_bar_sync(1, kUmmaSoftmaxThreads);
       mx = fmaxf(mx, xch[row]);
       xch[row] = mx;
-      named_bar_arrive(2, kUmmaThreads);
-      // Every thread has passed its wait for S(it) by now (it took part in barrier 1), so the barrier of the
-      // scores may move on by a phase: the next tile's first product goes out and runs under this softmax.
-      // K(it + 1) landed before the previous iteration's __syncthreads.
-      if (tid == 0 && it + 1 < nt) {
-        issue_qk(it + 1);
-        mma_commit(bar_s);
-      }
+      named_bar_arrive(2, kUmmaSoftmaxThreads);
     }
     const bool move = mx > m_run + lazy_margin;
     const float alpha = move ? fast_exp2((m_run - mx) * scale2) : 1.0f;
@@ -349,30 +369,27 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
     cp_async_wait<1>();           // all but this iteration's V group: V(it) and K(it + 2) have landed
     fence_smem_to_async_proxy();
     fence_before_thread_sync();
-    __syncthreads();
-    if (tid == 0) {
-      fence_after_thread_sync();
-      issue_pv(it);
-      mma_commit(bar_o);
-    }
+    mbar_arrive(bar_ready);
   }
-  cp_async_wait<0>();
-  const bool finished = mbar_wait_bounded(bar_o, (nt - 1) & 1, abort_word, p.debug_flags & 1);
-  fence_after_thread_sync();
-  if (!finished && (tid & 31) == 0) atomicMax(&g_umma_status, 1);
+  if (softmax_thread) {
+    cp_async_wait<0>();
+    const bool finished = mbar_wait_bounded(bar_o, (nt - 1) & 1, abort_word, p.debug_flags & 1);
+    fence_after_thread_sync();
+    if (!finished && (tid & 31) == 0) atomicMax(&g_umma_status, 1);
+  }
 
   // ---- the two threads of a row add up their sums, then each finishes its half of the row ---------------------
   {
-    if (wg == 1) xch[row] = l_run;
+    if (softmax_thread && wg == 1) xch[row] = l_run;
     __syncthreads();
     float l = l_run;
-    if (wg == 0) {
+    if (softmax_thread && wg == 0) {
       l += xch[row];
       xch[row] = l;
     }
     __syncthreads();
-    if (wg == 1) l = xch[row];
-    const bool live = row < rows;
+    if (softmax_thread && wg == 1) l = xch[row];
+    const bool live = softmax_thread && row < rows;
     const int head = live ? row_head(row) : 0;
     const float m = m_run * scale2;  // log2 domain; -inf if the row saw nothing
     float rescale = 1.0f;
@@ -389,7 +406,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
     const bool vec16 = ((reinterpret_cast<uintptr_t>(p.out) | static_cast<uintptr_t>(p.out_stride_t * 2) |
                          static_cast<uintptr_t>(p.out_stride_h * 2)) & 15u) == 0;
 #pragma unroll 1
-    for (int c = 0; c < D / 64; ++c) {
+    for (int c = 0; softmax_thread && c < D / 64; ++c) {
       uint32_t acc[32];
       tmem_ld_32x32(tmem + lane_base + kUmmaColO + wg * (D / 2) + c * 32, acc);
       tmem_ld_wait();
