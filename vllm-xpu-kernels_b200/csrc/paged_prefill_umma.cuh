@@ -9,7 +9,7 @@
 //   1. all threads wait for S(i) = Q K(i)^T in tensor-memory columns [0, 64) or [64, 128) and start the copies of K(i+2) and
 //      V(i+1) into the slots that the finished products have released (cp.async, 128-byte swizzle),
 //   2. the two threads of row r read their halves of row r of S, apply the mask, agree on the row's maximum
-//      through one float of shared memory and two named barriers, and write their halves of row r of P as
+//      through two floats of shared memory and one named barrier, and write their halves of row r of P as
 //      16-bit values into shared memory (no shuffle at all),
 //   3. thread 0 issues O += P V(i)  (M = 128, N = D, K = 16, 4 instructions; O in columns [128, 128 + D)) and
 //      commits.  S(i+1) = Q K(i+1)^T (M = 128, N = 64, K = 16, D / 16 instructions) was issued in step 1, into
@@ -38,12 +38,9 @@ constexpr uint32_t kUmmaColO = 128;
 // 0 = fine; 1 = an mbarrier wait gave up; 2 = shared memory window not 1024-byte aligned
 __device__ int g_umma_status = 0;
 
-// named barriers of the CTA (0 is __syncthreads): arrive does not wait, sync does; `threads` take part in all
+// a named barrier of the CTA (0 is __syncthreads) over `threads` threads
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-__device__ __forceinline__ void named_bar_arrive(int id, int threads) {
-  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -65,8 +62,8 @@ struct UmmaPrefillCfg {
   static constexpr int kOffQ = 0;
   static constexpr int kOffKV = kOffQ + kQBytes;             // [stage][K, V]
   static constexpr int kOffBar = kOffKV + kStages * 2 * kKVBytes;  // four mbarriers, tensor-memory slot, abort word
-  static constexpr int kOffXch = kOffBar + 48;               // one float per row: the warpgroups' exchange
-  static constexpr int kSmemBytes = kOffXch + kUmmaRows * 4;
+  static constexpr int kOffXch = kOffBar + 48;               // the warpgroups' exchange: [tile parity][warpgroup][row]
+  static constexpr int kSmemBytes = kOffXch + 4 * kUmmaRows * 4;
   // two CTAs per SM: 2 x (bytes + 1 KB the system keeps per CTA) within the SM's 228 KB
   static_assert(2 * (kSmemBytes + 1024) <= 233472, "two CTAs per SM");
   // and never three, which could ask for more tensor memory than an SM has
@@ -315,17 +312,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
 #pragma unroll
     for (int i = 0; i < 16; ++i) mx4[i & 3] = max3(mx4[i & 3], s2[i].x, s2[i].y);
     float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-    // the row's maximum over both halves: the second warpgroup hands its half over, the first one answers
-    if (wg == 1) {
-      xch[row] = mx;
-      named_bar_arrive(1, kUmmaSoftmaxThreads);
-      named_bar_sync(2, kUmmaSoftmaxThreads);
-      mx = xch[row];
-    } else {
+    // The row's maximum over both halves: each thread publishes its half's maximum and reads the other's after
+    // one named barrier.  The slots alternate with the tile's parity: a thread that runs ahead writes the other
+    // slot, and cannot reach this slot again before its partner has passed the next tile's barrier.
+    {
+      volatile float* slot = xch + (it & 1) * 2 * kUmmaRows;
+      slot[wg * kUmmaRows + row] = mx;
       named_bar_sync(1, kUmmaSoftmaxThreads);
-      mx = fmaxf(mx, xch[row]);
-      xch[row] = mx;
-      named_bar_arrive(2, kUmmaSoftmaxThreads);
+      mx = fmaxf(mx, slot[(wg ^ 1) * kUmmaRows + row]);
     }
     const bool move = mx > m_run + lazy_margin;
     const float alpha = move ? fast_exp2((m_run - mx) * scale2) : 1.0f;
