@@ -133,7 +133,6 @@ struct DecodeParams {
   // sliding window: the query token at position pos sees cached positions [pos - left, pos + right]; -1 = open
   int32_t window_left, window_right;
   float softmax_scale;
-  int32_t debug_flags;  // KVC_UMMA_DEBUG: bit 0 = spin on the barrier instead of parking
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -1414,8 +1413,6 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
     return fail(KVC_ERR_CUDA, std::string("paged_attention launch failed: ") + cudaGetErrorString(e));
   if (max_seqlen_q * p.group > kRows) {  // sequences with more than 16 query rows per kv head
     DecodeParams pp = p;
-    static const int dbg = [] { const char* e = getenv("KVC_UMMA_DEBUG"); return e ? atoi(e) : 0; }();
-    pp.debug_flags = dbg;
     const bool use_umma = prefill_uses_umma(kv_dtype, head_size, max_seqlen_q * p.group);
     const int64_t tile_rows = use_umma ? kUmmaRows : kPrefillRows;
     pp.row_tiles = static_cast<int32_t>((max_seqlen_q * p.group + tile_rows - 1) / tile_rows);

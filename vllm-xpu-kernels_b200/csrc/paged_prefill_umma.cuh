@@ -167,15 +167,19 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   const uint32_t ld_dst = (ld_col >> 3) * Cfg::kKVHalfBytes + swizzled_offset(ld_r0, ld_col & 7);
   const bool tile_in_block = p.bs_shift >= 6;
   const int64_t row_step_bytes = p.page_stride * 2 * kRowsPerPass;
-  auto load_rows = [&](int tile, const void* cache, unsigned char* dst_tile) {
+  // The table entry of a tile is fetched two iterations before the copy that needs it, so that its latency
+  // stays out of the softmax threads' critical path.
+  auto tile_blk = [&](int tile) -> int32_t {
+    return (tile_in_block && tile < tile_end) ? __ldg(table + ((tile * TN) >> p.bs_shift)) : 0;
+  };
+  auto load_rows = [&](int tile, const void* cache, unsigned char* dst_tile, int32_t blk) {
     const int rows_left = n - tile * TN;
     const uint32_t dst0 = smem_addr(dst_tile) + ld_dst;
     if (tile_in_block) {
       const int token0 = tile * TN;
-      const int64_t blk = __ldg(table + (token0 >> p.bs_shift));
       const unsigned char* src =
           static_cast<const unsigned char*>(cache) +
-          (blk * p.block_stride + static_cast<int64_t>((token0 & (p.block_size - 1)) + ld_r0) * p.page_stride + head_off) * 2 +
+          (static_cast<int64_t>(blk) * p.block_stride + static_cast<int64_t>((token0 & (p.block_size - 1)) + ld_r0) * p.page_stride + head_off) * 2 +
           ld_col * 16;
 #pragma unroll
       for (int i = 0; i < TN / kRowsPerPass; ++i) {
@@ -214,11 +218,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   // consumes, and V(i); V(i+1) has another iteration to land.
   const int nt = tile_end - tile_begin;
   const bool softmax_thread = tid < kUmmaSoftmaxThreads;
+  int32_t blk_v = 0, blk_k = 0;  // table entries of tiles it + 1 (next V copy) and it + 2 (next K copy)
   if (softmax_thread) {
-    load_rows(tile_begin, p.key_cache, k_slot(0));
-    if (nt > 1) load_rows(tile_begin + 1, p.key_cache, k_slot(1));
+    const int32_t b0 = tile_blk(tile_begin);
+    blk_v = tile_blk(tile_begin + 1);
+    blk_k = tile_blk(tile_begin + 2);
+    load_rows(tile_begin, p.key_cache, k_slot(0), b0);
+    if (nt > 1) load_rows(tile_begin + 1, p.key_cache, k_slot(1), blk_v);
     cp_async_commit();
-    load_rows(tile_begin, p.value_cache, v_slot(0));
+    load_rows(tile_begin, p.value_cache, v_slot(0), b0);
     cp_async_commit();
   }
   cp_async_wait<1>();           // K(0), K(1)
@@ -273,7 +281,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
         mma_commit(bar_s + 1);
       }
       for (int j = 0; j < nt; ++j) {
-        mbar_wait_bounded(bar_ready, j & 1, abort_word, p.debug_flags & 1);
+        mbar_wait_bounded(bar_ready, j & 1, abort_word);
         fence_after_thread_sync();
         issue_pv(j);
         mma_commit(bar_o);
@@ -288,9 +296,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
 
   for (int it = 0; softmax_thread && it < nt; ++it) {
     const int tile = tile_begin + it;
-    mbar_wait_bounded(bar_s + (it & 1), (it >> 1) & 1, abort_word, p.debug_flags & 1);  // S(it) is there, K slot it & 1 is free
+    mbar_wait_bounded(bar_s + (it & 1), (it >> 1) & 1, abort_word);  // S(it) is there, K slot it & 1 is free
     fence_after_thread_sync();
-    if (it + 2 < nt) load_rows(tile + 2, p.key_cache, k_slot(it));
+    const int32_t blk_next = tile_blk(tile + 3);
+    if (it + 2 < nt) load_rows(tile + 2, p.key_cache, k_slot(it), blk_k);
     cp_async_commit();
 
     // ---- softmax of this thread's half row: columns [32 wg, 32 wg + 32) of the tile ---------------------------
@@ -340,11 +349,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
     // The previous tile's second product has had this softmax to finish: O is up to date for a rescale and
     // V slot (it + 1) & 1 is free.
     if (it > 0) {
-      mbar_wait_bounded(bar_o, (it - 1) & 1, abort_word, p.debug_flags & 1);
+      mbar_wait_bounded(bar_o, (it - 1) & 1, abort_word);
       fence_after_thread_sync();
     }
-    if (it + 1 < nt) load_rows(tile + 1, p.value_cache, v_slot(it + 1));
+    if (it + 1 < nt) load_rows(tile + 1, p.value_cache, v_slot(it + 1), blk_v);
     cp_async_commit();
+    blk_v = blk_k;
+    blk_k = blk_next;
     if (it > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // rare: a reference maximum of the warp moved
 #pragma unroll 1
       for (int c = 0; c < D / 64; ++c) {  // this warpgroup's half of the accumulator's columns
@@ -367,7 +378,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   }
   if (softmax_thread) {
     cp_async_wait<0>();
-    const bool finished = mbar_wait_bounded(bar_o, (nt - 1) & 1, abort_word, p.debug_flags & 1);
+    const bool finished = mbar_wait_bounded(bar_o, (nt - 1) & 1, abort_word);
     fence_after_thread_sync();
     if (!finished && (tid & 31) == 0) atomicMax(&g_umma_status, 1);
   }

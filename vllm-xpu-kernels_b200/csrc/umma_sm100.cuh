@@ -172,28 +172,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, ui
 // through its status word.
 constexpr uint32_t kMaxTries = 2048;
 constexpr uint32_t kTryNs = 20000;
-__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(done)
-      : "r"(smem_addr(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile uint32_t* abort,
-                                                  bool spin = false) {
-  if (spin) {
-    for (uint32_t i = 0; i < (1u << 22); ++i) {
-      if (mbar_test(bar, parity)) return true;
-    }
-    *abort = 1u;
-    return false;
-  }
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile uint32_t* abort) {
   for (uint32_t i = 0; i < kMaxTries; ++i) {
     if (mbar_try_wait(bar, parity, kTryNs)) return true;
     if (*abort) return false;
