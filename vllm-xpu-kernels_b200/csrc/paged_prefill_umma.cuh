@@ -102,8 +102,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   const int seq_rows = q_len * p.group;
   if (seq_rows <= kRows || row0 >= seq_rows) return;  // the decode kernel's sequence, or no rows here
   const int rows = min(kUmmaRows, seq_rows - row0);
-  auto row_token = [&](int r) { return (row0 + r) / p.group; };
-  auto row_head = [&](int r) { return kvh * p.group + (row0 + r) % p.group; };
+  // rows are token-major: row R of the kv head is token R / group, head R % group of the group (a shift and a
+  // mask for the usual power-of-two groups)
+  const int g_shift = (p.group & (p.group - 1)) == 0 ? __ffs(p.group) - 1 : -1;
+  auto row_token = [&](int r) { return g_shift >= 0 ? (row0 + r) >> g_shift : (row0 + r) / p.group; };
+  auto row_head = [&](int r) {
+    return kvh * p.group + (g_shift >= 0 ? (row0 + r) & (p.group - 1) : (row0 + r) % p.group);
+  };
   const int n = p.seq_lens[seq];
   auto row_limit = [&](int r) {
     const int pos = n - q_len + row_token(r);
