@@ -1,5 +1,5 @@
-"""GPU parity of the many-rows attention kernel that runs on the tcgen05 tensor cores (16-bit cache, head size
-128, some sequence with more than 64 query rows per kv head) against the CPU oracle, and against the mma.sync
+"""GPU parity of the many-rows attention kernel that runs on the tcgen05 tensor cores (head size 128, some
+sequence with more than 64 query rows per kv head; 16-bit and fp8 caches) against the CPU oracle, and against the mma.sync
 kernel it replaces for those calls.
 
 Floating point.  Tolerance: atol = rtol = 1e-2, the reference test's own for this op
@@ -23,22 +23,35 @@ pytestmark = pytest.mark.gpu
 TOL = dict(atol=H.ATTN_ATOL, rtol=H.ATTN_RTOL)
 
 
-def run_case(dev, dtype, hq, hk, q_lens, kv_lens, bs, causal, sink, seed, window=(-1, -1), scale=None, out=None):
+def run_case(dev, dtype, hq, hk, q_lens, kv_lens, bs, causal, sink, seed, window=(-1, -1), scale=None, out=None,
+             kv="auto", descale=1.0):
     D = 128
     nb = max(64, sum((n + bs - 1) // bs for n in kv_lens) + 8)
     torch.manual_seed(seed)
     query = torch.randn(sum(q_lens), hq, D).to(dtype)
-    _, kc, vc, bt, lens, sk = make_case(dtype, hq, hk, D, kv_lens, bs, nb, sink, seed=seed + 1)
+    _, kc, vc, bt, lens, sk = make_case(dtype, hq, hk, D, kv_lens, bs, nb, sink, seed=seed + 1, kv=kv, descale=descale)
     cu = cu_of(q_lens)
     scale = D ** -0.5 if scale is None else scale
-    got = cabi.paged_attention(query.to(dev), kc.to(dev), vc.to(dev), bt.to(dev), lens.to(dev), cu.to(dev), max(q_lens),
-                               scale, max(kv_lens), causal, sink=None if sk is None else sk.to(dev), window=window,
-                               out=out)
+    kcd, vcd = (kc.view(torch.uint8), vc.view(torch.uint8)) if kv != "auto" else (kc, vc)
+    ds = torch.tensor(descale, dtype=torch.float32, device=dev) if kv != "auto" else None
+    got = cabi.paged_attention(query.to(dev), kcd.to(dev), vcd.to(dev), bt.to(dev), lens.to(dev), cu.to(dev),
+                               max(q_lens), scale, max(kv_lens), causal, kv, ds, ds,
+                               sink=None if sk is None else sk.to(dev), window=window, out=out)
     assert cabi.paged_attention_device_status() == 0
-    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, scale, sink=sk, cu_seqlens_q=cu,
-                                                  causal=causal, window=window)
+    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, scale, kv, descale, descale, sink=sk,
+                                                  cu_seqlens_q=cu, causal=causal, window=window)
     torch.testing.assert_close(got.cpu().float(), want, **TOL)
     return got
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("kv,descale", [("fp8", 0.04), ("fp8_e5m2", 0.002)])
+@pytest.mark.parametrize("bs", [16, 64, 48])
+def test_prefill_fp8_caches(dtype, kv, descale, bs, cuda_device):
+    """fp8 caches are widened to fp16 on their way into shared memory (exact) and the products run in fp16, for
+    bf16 queries too; k_descale folds into the softmax scale, v_descale into the output."""
+    run_case(cuda_device, dtype, 8, 2, q_lens=[300, 1, 70, 140], kv_lens=[777, 300, 70, 1100], bs=bs, causal=True,
+             sink=(bs == 64), seed=900 + bs, kv=kv, descale=descale)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])

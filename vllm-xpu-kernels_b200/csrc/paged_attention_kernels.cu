@@ -1199,12 +1199,13 @@ inline bool prefill_umma_enabled() {
   return !off;
 }
 inline bool prefill_uses_umma(int kv_dtype, int64_t head_size, int64_t max_rows_per_kv_head) {
-  return prefill_umma_enabled() && kv_dtype == KVC_KV_AUTO && head_size == 128 && max_rows_per_kv_head > kPrefillRows;
+  (void)kv_dtype;  // 16-bit and fp8 caches alike
+  return prefill_umma_enabled() && head_size == 128 && max_rows_per_kv_head > kPrefillRows;
 }
 
-template <typename TQ>
+template <typename TQ, int KV>
 cudaError_t launch_prefill_umma(const DecodeParams& p, dim3 grid, cudaStream_t st) {
-  using Cfg = UmmaPrefillCfg<TQ, 128>;
+  using Cfg = UmmaPrefillCfg<TQ, KV, 128>;
   static std::once_flag once[64];
   static cudaError_t attr_err[64];
   int dev = 0;
@@ -1212,15 +1213,15 @@ cudaError_t launch_prefill_umma(const DecodeParams& p, dim3 grid, cudaStream_t s
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   std::call_once(once[dev], [&] {
-    attr_err[dev] = cudaFuncSetAttribute(paged_prefill_umma_kernel<TQ, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err[dev] = cudaFuncSetAttribute(paged_prefill_umma_kernel<TQ, KV, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
     // two CTAs per SM need the whole shared-memory carve-out
     if (attr_err[dev] == cudaSuccess)
-      attr_err[dev] = cudaFuncSetAttribute(paged_prefill_umma_kernel<TQ, 128>,
+      attr_err[dev] = cudaFuncSetAttribute(paged_prefill_umma_kernel<TQ, KV, 128>,
                                            cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (getenv("KVC_DEBUG_OCCUPANCY")) {
       int ctas = -1;
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, paged_prefill_umma_kernel<TQ, 128>, kUmmaThreads, Cfg::kSmemBytes);
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, paged_prefill_umma_kernel<TQ, KV, 128>, kUmmaThreads, Cfg::kSmemBytes);
       fprintf(stderr, "kvc: paged_prefill_umma_kernel: %d CTAs per SM (%d bytes of shared memory each)\n", ctas,
               Cfg::kSmemBytes);
     }
@@ -1236,7 +1237,16 @@ cudaError_t launch_prefill_umma(const DecodeParams& p, dim3 grid, cudaStream_t s
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, paged_prefill_umma_kernel<TQ, 128>, p);
+  return cudaLaunchKernelEx(&cfg, paged_prefill_umma_kernel<TQ, KV, 128>, p);
+}
+
+template <typename TQ>
+cudaError_t launch_prefill_umma_kv(int kv, const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  switch (kv) {
+    case KVC_KV_AUTO: return launch_prefill_umma<TQ, KVC_KV_AUTO>(p, grid, st);
+    case KVC_KV_FP8_E4M3: return launch_prefill_umma<TQ, KVC_KV_FP8_E4M3>(p, grid, st);
+    default: return launch_prefill_umma<TQ, KVC_KV_FP8_E5M2>(p, grid, st);
+  }
 }
 
 struct DecodePlan {
@@ -1420,8 +1430,8 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
     if (px > 0x7FFFFFFFll) return fail(KVC_ERR_INVALID_ARG, "paged_attention: too many query rows per sequence");
     const dim3 pgrid(static_cast<unsigned>(px), static_cast<unsigned>(num_seqs), 1);
     if (use_umma)
-      e = (q_dtype == KVC_IN_F16) ? launch_prefill_umma<__half>(pp, pgrid, st)
-                                  : launch_prefill_umma<__nv_bfloat16>(pp, pgrid, st);
+      e = (q_dtype == KVC_IN_F16) ? launch_prefill_umma_kv<__half>(kv_dtype, pp, pgrid, st)
+                                  : launch_prefill_umma_kv<__nv_bfloat16>(kv_dtype, pp, pgrid, st);
     else
       e = (q_dtype == KVC_IN_F16) ? launch_prefill_kv<__half>(kv_dtype, static_cast<int>(head_size), pp, pgrid, st)
                                   : launch_prefill_kv<__nv_bfloat16>(kv_dtype, static_cast<int>(head_size), pp, pgrid, st);

@@ -49,8 +49,9 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return r;
 }
 
-template <typename TQ, int D>
+template <typename TQ, int KV, int D>
 struct UmmaPrefillCfg {
+  using T16 = std::conditional_t<KV == KVC_KV_AUTO, TQ, __half>;  // operand type of the matrix products
   static_assert(D == 128, "head size 128");
   static constexpr int kTile = 64;
   static constexpr int kHalves = D / 64;                     // 128-byte-wide operand tiles per row
@@ -70,9 +71,11 @@ struct UmmaPrefillCfg {
   static_assert(3 * (kSmemBytes + 1024) > 233472, "at most two CTAs per SM");
 };
 
-template <typename TQ, int D>
+template <typename TQ, int KV, int D>
 __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(const DecodeParams p) {
-  using Cfg = UmmaPrefillCfg<TQ, D>;
+  using Cfg = UmmaPrefillCfg<TQ, KV, D>;
+  using T16 = typename Cfg::T16;
+  constexpr bool kFp8 = KV != KVC_KV_AUTO;
   using namespace umma;
   constexpr int TN = Cfg::kTile;
   constexpr int KVB = Cfg::kKVBytes;
@@ -156,6 +159,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
       const TQ* src = static_cast<const TQ*>(p.query) + static_cast<int64_t>(q_start + row_token(r)) * p.query_stride_t +
                       row_head(r) * p.query_stride_h + col * 8;
       v = *reinterpret_cast<const uint4*>(src);
+      if constexpr (!std::is_same_v<TQ, T16>) {  // bf16 query over an fp8 cache: the products run in fp16
+        uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xFFFF0000u);
+          w[i] = pack2<__half>(lo, hi);
+        }
+      }
     }
     *reinterpret_cast<uint4*>(s_q + (col >> 3) * Cfg::kQHalfBytes + swizzled_offset(r, col & 7)) = v;
   }
@@ -207,11 +218,51 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
       }
     }
   };
+  // fp8 caches: a row is 128 bytes; thread t fetches 32 of them (quarter t % 4 of row t / 4), widens them to
+  // fp16 (exact) and stores the 64 bytes as four chunks of the same swizzled 16-bit layout.  The fetch is split
+  // from the store so that the loads are in flight while the thread does other work.
+  struct Fp8Quarter {
+    uint4 a, b;
+  };
+  auto fetch_fp8 = [&](int tile, const void* cache, int32_t blk) {
+    Fp8Quarter q;
+    q.a = q.b = make_uint4(0, 0, 0, 0);
+    const int r = tid >> 2, token = tile * TN + r;
+    if (token < n) {
+      int64_t off;
+      if (tile_in_block) {
+        off = static_cast<int64_t>(blk) * p.block_stride + static_cast<int64_t>(token & (p.block_size - 1)) * p.page_stride;
+      } else {
+        const int blk_idx = p.bs_shift >= 0 ? (token >> p.bs_shift) : token / p.block_size;
+        off = static_cast<int64_t>(__ldg(table + blk_idx)) * p.block_stride +
+              static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride;
+      }
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(cache) + off + head_off +
+                                                        (tid & 3) * 32);
+      q.a = __ldg(src);
+      q.b = __ldg(src + 1);
+    }
+    return q;
+  };
+  auto store_fp8 = [&](const Fp8Quarter& q, unsigned char* dst_tile) {
+    const int r = tid >> 2, qu = tid & 3;  // fp16 chunks 4 qu .. 4 qu + 3 of the row: half qu / 2
+    unsigned char* dst = dst_tile + (qu >> 1) * Cfg::kKVHalfBytes;
+    const uint32_t src[8] = {q.a.x, q.a.y, q.a.z, q.a.w, q.b.x, q.b.y, q.b.z, q.b.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      uint4 o;
+      o.x = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2 * k]);
+      o.y = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2 * k] >> 16);
+      o.z = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2 * k + 1]);
+      o.w = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2 * k + 1] >> 16);
+      *reinterpret_cast<uint4*>(dst + swizzled_offset(r, (qu & 1) * 4 + k)) = o;
+    }
+  };
   auto k_slot = [&](int i) { return s_kv + (i & 1) * 2 * KVB; };
   auto v_slot = [&](int i) { return s_kv + (i & 1) * 2 * KVB + KVB; };
 
   // ---- this thread's row ----------------------------------------------------------------------------------
-  const float scale2 = p.softmax_scale * kLog2e;
+  const float scale2 = p.softmax_scale * kLog2e * ((kFp8 && p.k_descale) ? __ldg(p.k_descale) : 1.0f);
   const float lazy_margin = 8.0f / scale2;
   const int lim = row < rows ? row_limit(row) : 0;
   const int lo = row < rows ? row_lo(row) : 0;
@@ -228,11 +279,20 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
     const int32_t b0 = tile_blk(tile_begin);
     blk_v = tile_blk(tile_begin + 1);
     blk_k = tile_blk(tile_begin + 2);
-    load_rows(tile_begin, p.key_cache, k_slot(0), b0);
-    if (nt > 1) load_rows(tile_begin + 1, p.key_cache, k_slot(1), blk_v);
-    cp_async_commit();
-    load_rows(tile_begin, p.value_cache, v_slot(0), b0);
-    cp_async_commit();
+    if constexpr (kFp8) {
+      const Fp8Quarter k0 = fetch_fp8(tile_begin, p.key_cache, b0);
+      const Fp8Quarter k1 = fetch_fp8(tile_begin + 1, p.key_cache, blk_v);  // zeros past the sequence's end
+      const Fp8Quarter v0 = fetch_fp8(tile_begin, p.value_cache, b0);
+      store_fp8(k0, k_slot(0));
+      store_fp8(k1, k_slot(1));
+      store_fp8(v0, v_slot(0));
+    } else {
+      load_rows(tile_begin, p.key_cache, k_slot(0), b0);
+      if (nt > 1) load_rows(tile_begin + 1, p.key_cache, k_slot(1), blk_v);
+      cp_async_commit();
+      load_rows(tile_begin, p.value_cache, v_slot(0), b0);
+      cp_async_commit();
+    }
   }
   cp_async_wait<1>();           // K(0), K(1)
   fence_smem_to_async_proxy();  // and the query rows
@@ -241,8 +301,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   fence_after_thread_sync();
   const uint32_t tmem = *tmem_slot;
   const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-  constexpr uint32_t kIdescQK = instr_desc_f16<TQ>(kUmmaRows, TN, false, false);
-  constexpr uint32_t kIdescPV = instr_desc_f16<TQ>(kUmmaRows, D, false, true);
+  constexpr uint32_t kIdescQK = instr_desc_f16<T16>(kUmmaRows, TN, false, false);
+  constexpr uint32_t kIdescPV = instr_desc_f16<T16>(kUmmaRows, D, false, true);
   // Descriptors: the upper word is constant per operand role, the lower one is (address >> 4) plus the leading
   // byte offset; shared-memory addresses are below 2^18, so stepping an operand is an add on the lower word.
   constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
@@ -304,8 +364,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
     mbar_wait_bounded(bar_s + (it & 1), (it >> 1) & 1, abort_word);  // S(it) is there, K slot it & 1 is free
     fence_after_thread_sync();
     const int32_t blk_next = tile_blk(tile + 3);
-    if (it + 2 < nt) load_rows(tile + 2, p.key_cache, k_slot(it), blk_k);
-    cp_async_commit();
+    if constexpr (!kFp8) {
+      if (it + 2 < nt) load_rows(tile + 2, p.key_cache, k_slot(it), blk_k);
+      cp_async_commit();
+    }
 
     // ---- softmax of this thread's half row: columns [32 wg, 32 wg + 32) of the tile ---------------------------
     uint32_t sa[32];
@@ -348,7 +410,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
       const float2 e = __ffma2_rn(s2[j], sc2, nm2);
       const float2 pr = make_float2(fast_exp2(e.x), fast_exp2(e.y));
       l_add[j & 1] = __fadd2_rn(l_add[j & 1], pr);
-      w[j] = pack2<TQ>(pr.x, pr.y);
+      w[j] = pack2<T16>(pr.x, pr.y);
     }
     l_run += (l_add[0].x + l_add[0].y) + (l_add[1].x + l_add[1].y);
     // The previous tile's second product has had this softmax to finish: O is up to date for a rescale and
@@ -357,8 +419,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
       mbar_wait_bounded(bar_o, (it - 1) & 1, abort_word);
       fence_after_thread_sync();
     }
-    if (it + 1 < nt) load_rows(tile + 1, p.value_cache, v_slot(it + 1), blk_v);
-    cp_async_commit();
+    [[maybe_unused]] Fp8Quarter fk, fv;
+    if constexpr (kFp8) {  // in flight while P is stored (and O rescaled)
+      if (it + 2 < nt) fk = fetch_fp8(tile + 2, p.key_cache, blk_k);
+      if (it + 1 < nt) fv = fetch_fp8(tile + 1, p.value_cache, blk_v);
+    } else {
+      if (it + 1 < nt) load_rows(tile + 1, p.value_cache, v_slot(it + 1), blk_v);
+      cp_async_commit();
+    }
     blk_v = blk_k;
     blk_k = blk_next;
     if (it > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // rare: a reference maximum of the warp moved
@@ -376,6 +444,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
     // P(it) takes the place of S(it): both warpgroups have read their halves (the exchange above orders that)
     tmem_st_32x16(tmem + lane_base + kUmmaColS + (it & 1) * TN + wg * 16, w);
     tmem_st_wait();
+    if constexpr (kFp8) {  // K slot it & 1 is free since S(it), V slot (it + 1) & 1 since the wait on bar_o above
+      if (it + 2 < nt) store_fp8(fk, k_slot(it));
+      if (it + 1 < nt) store_fp8(fv, v_slot(it + 1));
+    }
     cp_async_wait<1>();           // all but this iteration's V group: V(it) and K(it + 2) have landed
     fence_smem_to_async_proxy();
     fence_before_thread_sync();
@@ -409,7 +481,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
       rescale = (m == -INFINITY) ? 0.f : exp2f(m - mf);
       l = l * rescale + exp2f(sk - mf);
     }
-    const float f = (l > 0.f) ? rescale / l : 0.f;
+    const float f = (l > 0.f) ? rescale / l * ((kFp8 && p.v_descale) ? __ldg(p.v_descale) : 1.0f) : 0.f;
     TQ* o = static_cast<TQ*>(p.out) + (live ? static_cast<int64_t>(q_start + row_token(row)) * p.out_stride_t +
                                                   static_cast<int64_t>(head) * p.out_stride_h + wg * (D / 2)
                                             : 0);
