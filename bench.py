@@ -625,8 +625,8 @@ def run_op_arm(ns):
         tpeak, tsrc = measured_tensor_peak()
         roofline = {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak,
                     "traffic": None, "peak_source": tsrc, "useful_flops_per_launch": w.flops,
-                    "note": ("tcgen05.mma, accumulators and probabilities in tensor memory" if w.name == "prefill-bf16"
-                             else "mma.sync tiles (fp8 caches are widened in registers), not tcgen05")}
+                    "note": "tcgen05.mma, accumulators and probabilities in tensor memory" +
+                            ("" if w.name == "prefill-bf16" else "; fp8 rows widened to fp16 on their way into shared memory")}
     else:
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                     "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": w.algorithmic_bytes,

@@ -348,11 +348,11 @@ KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_h
  *   window_right   pos + window_right; -1 leaves a side open (test_flash_attn_varlen_func.py:81-95)
  *
  * Sequences with at most 16 (token, head) rows per kv head run on the decode kernel, the others on a second
- * kernel launched beside it.  With a 16-bit cache, head size 128 and some sequence of more than 64 rows per kv
- * head that second kernel runs on the tcgen05 tensor cores: a CTA owns 128 rows, both products are
- * tcgen05.mma with operands in 128-byte-swizzled shared memory and accumulators in tensor memory, two CTAs per
- * SM.  Otherwise (fp8 caches, other head sizes, short runs) it is the mma.sync kernel in which a CTA owns 64
- * rows.  In such a mixed call the decode part is not split over the sequence.  At most 65535 sequences per call.
+ * kernel launched beside it.  With head size 128 and some sequence of more than 64 rows per kv head that
+ * second kernel runs on the tcgen05 tensor cores: a CTA owns 128 rows, both products are tcgen05.mma with keys
+ * and values in 128-byte-swizzled shared memory (fp8 caches widened to fp16 on the way in), scores,
+ * probabilities and accumulators in tensor memory, two CTAs per SM.  Otherwise (other head sizes, short runs)
+ * it is the mma.sync kernel in which a CTA owns 64 rows.  In such a mixed call the decode part is not split over the sequence.  At most 65535 sequences per call.
  *
  * kvc_paged_attention_device_status waits for the device's earlier work and reads the tcgen05 kernel's status
  * word: 0 = fine; 1 = a bounded wait on an mbarrier gave up (results of that call are then undefined; the

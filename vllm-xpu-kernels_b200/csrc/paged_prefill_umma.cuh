@@ -1,23 +1,27 @@
 // The many-rows attention kernel on the fifth-generation tensor cores (tcgen05, accumulators in tensor
 // memory).  Included by paged_attention_kernels.cu after DecodeParams and the cp.async helpers.
 //
-// Division of labour: a CTA of 256 threads owns 128 query rows (token-major (token, head) pairs of one kv
-// head) and walks the cached tokens in tiles of 64.  Row r belongs to thread r of each of the two warpgroups
-// (tensor-memory lane r is readable by warps r / 32 and r / 32 + 4); the first warpgroup works on columns
-// [0, 32) of a tile's scores and columns [0, D / 2) of the accumulator, the second on the other halves.  Per
-// tile i
-//   1. all threads wait for S(i) = Q K(i)^T in tensor-memory columns [0, 64) or [64, 128) and start the copies of K(i+2) and
-//      V(i+1) into the slots that the finished products have released (cp.async, 128-byte swizzle),
+// Division of labour: a CTA of 288 threads owns 128 query rows (token-major (token, head) pairs of one kv
+// head) and walks the cached tokens in tiles of 64.  Eight warps do the softmax: row r belongs to thread r of
+// each of two warpgroups (tensor-memory lane r is readable by warps r / 32 and r / 32 + 4); the first warpgroup
+// works on columns [0, 32) of a tile's scores and columns [0, D / 2) of the accumulator, the second on the other
+// halves.  The ninth warp issues the matrix products.  Per tile i
+//   1. the softmax threads wait for S(i) = Q K(i)^T in tensor-memory columns [0, 64) or [64, 128) (it was issued
+//      two tiles earlier and is there), and start the copy of K(i+2) into the slot S(i) has released (cp.async
+//      with the 128-byte swizzle applied to the destination; fp8 caches: registers, widened to fp16),
 //   2. the two threads of row r read their halves of row r of S, apply the mask, agree on the row's maximum
-//      through two floats of shared memory and one named barrier, and write their halves of row r of P as
-//      16-bit values into shared memory (no shuffle at all),
-//   3. thread 0 issues O += P V(i)  (M = 128, N = D, K = 16, 4 instructions; O in columns [128, 128 + D)) and
-//      commits.  S(i+1) = Q K(i+1)^T (M = 128, N = 64, K = 16, D / 16 instructions) was issued in step 1, into
-//      the other of two score buffers, and runs under the softmax of tile i; the commit covers both.
-// One barrier wait and one __syncthreads per tile.  The steps of one CTA are a dependency chain, so two CTAs
-// share an SM (shared memory is sized for exactly two, and each allocates 256 of the 512 tensor-memory
-// columns): one CTA's softmax runs under the other's matrix products.  O is rescaled in tensor memory only
-// when a row's reference maximum moves (rare, see the lazy rule of the other kernels).
+//      through two floats of shared memory and one named barrier, and compute their 32 probabilities (no
+//      shuffle at all),
+//   3. they wait for O += P(i-1) V(i-1) (long done), start the copy of V(i+1) into the slot it has released,
+//      rescale O in tensor memory if the row's reference maximum moved (rare, the lazy rule of the other
+//      kernels), store P(i) as 16-bit pairs over the scores they just read, and arrive on the `ready` mbarrier,
+//   4. the issuing thread, on `ready`, issues O += P(i) V(i) (M = 128, N = D, K = 16, 4 instructions, A from
+//      tensor memory, V as an MN-major B operand from shared memory; O in columns [128, 128 + D)) and
+//      S(i+2) = Q K(i+2)^T (M = 128, N = 64, K = 16, D / 16 instructions, both operands from shared memory), each
+//      followed by a commit to its mbarrier.  The tensor pipe runs one thread's instructions in order, which is
+//      what lets P(i) and S(i+2) share columns.
+// Two CTAs share an SM (shared memory is sized for exactly two, and each allocates 256 of the 512 tensor-memory
+// columns, so an allocation never waits).
 //
 // Every wait on an mbarrier is bounded; a wait that gives up sets the CTA's abort word, the CTA runs to its
 // end, frees its tensor memory and raises g_umma_status.
