@@ -626,7 +626,7 @@ def run_op_arm(ns):
         roofline = {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak,
                     "traffic": None, "peak_source": tsrc, "useful_flops_per_launch": w.flops,
                     "note": "tcgen05.mma, accumulators and probabilities in tensor memory" +
-                            ("" if w.name == "prefill-bf16" else "; fp8 rows widened to fp16 on their way into shared memory")}
+                            ("; fp8 rows widened to fp16 on their way into shared memory" if "fp8" in w.name else "")}
     else:
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                     "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": w.algorithmic_bytes,

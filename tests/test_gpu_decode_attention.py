@@ -393,7 +393,7 @@ def test_varlen_attention_mixed_batch_and_edges(kv, descale, cuda_device):
 
 
 def test_varlen_attention_long_chunk(cuda_device):
-    """A 1024-token chunk over 3072 cached tokens (slow path of a long prefill, still exact)."""
+    """A 1024-token chunk over 3072 cached tokens: 64 row tiles x up to 48 token tiles on the many-rows kernel."""
     dev = cuda_device
     hq, hk, D = 8, 1, 128
     torch.manual_seed(60)

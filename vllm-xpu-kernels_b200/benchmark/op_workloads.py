@@ -317,10 +317,10 @@ def decode(kv: str) -> OpWorkload:
 
 
 # ---------------------------------------------------------------------------------------------- prefill attention
-def prefill(kv: str) -> OpWorkload:
-    """Causal attention of whole prompts over their own paged keys/values (query length = cached length): the
-    many-rows path of paged attention.  Compute-bound, unlike everything else here."""
-    S, L, hq, hk, D, bs = 4, 2048, 64, 8, 128, 64
+def prefill(kv: str, S: int = 4, L: int = 2048) -> OpWorkload:
+    """Causal attention of S whole prompts of L tokens over their own paged keys/values (query length = cached
+    length): the many-rows path of paged attention.  Compute-bound, unlike everything else here."""
+    hq, hk, D, bs = 64, 8, 128, 64
     es = 2 if kv == "auto" else 1
     blocks_per_seq = L // bs
 
@@ -377,7 +377,8 @@ def prefill(kv: str) -> OpWorkload:
 
     tag = "bf16" if kv == "auto" else "fp8"
     return OpWorkload(
-        f"prefill-{tag}", f"paged_attention_prefill_{tag}_cache_tokens_per_s",
+        f"prefill-{tag}" + ("" if (S, L) == (4, 2048) else f"-{L // 1024}k"),
+        f"paged_attention_prefill_{tag}_cache_tokens_per_s",
         f"causal paged attention of {S} whole prompts of {L} tokens, {hq} q / {hk} kv heads x {D}, cache "
         f"{'bfloat16' if kv == 'auto' else 'fp8_e4m3'}, block_size={bs} (CPU oracle: a {256}-token prompt)",
         S * L, 2 * S * L * hk * D * es + 2 * S * L * hq * D * 2, 1, make_steps, cpu_run,
@@ -395,6 +396,8 @@ BY_NAME: dict[str, Callable[[], OpWorkload]] = {
     "decode-fp8": lambda: decode("fp8"),
     "prefill-bf16": lambda: prefill("auto"),
     "prefill-fp8": lambda: prefill("fp8"),
+    "prefill-bf16-8k": lambda: prefill("auto", 1, 8192),
+    "prefill-fp8-8k": lambda: prefill("fp8", 1, 8192),
 }
 
 
