@@ -155,26 +155,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   }
   if (warp == 0) tmem_alloc(tmem_slot, kUmmaTmemCols);
 
-  // ---- query rows -> shared memory (zero rows past the end) --------------------------------------------
-  for (int c = tid; c < kUmmaRows * (D / 8); c += kUmmaThreads) {
-    const int r = c / (D / 8), col = c % (D / 8);
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r < rows) {
-      const TQ* src = static_cast<const TQ*>(p.query) + static_cast<int64_t>(q_start + row_token(r)) * p.query_stride_t +
-                      row_head(r) * p.query_stride_h + col * 8;
-      v = *reinterpret_cast<const uint4*>(src);
-      if constexpr (!std::is_same_v<TQ, T16>) {  // bf16 query over an fp8 cache: the products run in fp16
-        uint32_t* w = reinterpret_cast<uint32_t*>(&v);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xFFFF0000u);
-          w[i] = pack2<__half>(lo, hi);
-        }
-      }
-    }
-    *reinterpret_cast<uint4*>(s_q + (col >> 3) * Cfg::kQHalfBytes + swizzled_offset(r, col & 7)) = v;
-  }
-
   // ---- producer: thread t copies chunk t % 16 of rows t / 16 + 8 i of a K or a V tile ----------------------
   const int32_t* table = p.block_table + seq * p.block_table_stride;
   const int64_t head_off = static_cast<int64_t>(kvh) * p.head_stride;
@@ -298,6 +278,26 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
       cp_async_commit();
     }
   }
+  // ---- query rows -> shared memory (zero rows past the end), while the first copies are in flight -----------
+  for (int c = tid; c < kUmmaRows * (D / 8); c += kUmmaThreads) {
+    const int r = c / (D / 8), col = c % (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < rows) {
+      const TQ* src = static_cast<const TQ*>(p.query) + static_cast<int64_t>(q_start + row_token(r)) * p.query_stride_t +
+                      row_head(r) * p.query_stride_h + col * 8;
+      v = *reinterpret_cast<const uint4*>(src);
+      if constexpr (!std::is_same_v<TQ, T16>) {  // bf16 query over an fp8 cache: the products run in fp16
+        uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xFFFF0000u);
+          w[i] = pack2<__half>(lo, hi);
+        }
+      }
+    }
+    *reinterpret_cast<uint4*>(s_q + (col >> 3) * Cfg::kQHalfBytes + swizzled_offset(r, col & 7)) = v;
+  }
+
   cp_async_wait<1>();           // K(0), K(1)
   fence_smem_to_async_proxy();  // and the query rows
   fence_before_thread_sync();
