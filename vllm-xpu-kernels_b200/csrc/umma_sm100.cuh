@@ -1,6 +1,6 @@
 // Fifth-generation tensor core (tcgen05) plumbing for sm_100a: tensor-memory allocation, shared-memory
 // matrix descriptors, the instruction descriptor of kind::f16, MMA issue and commit, tensor-memory loads
-// and stores, and mbarrier waits that give up after a bounded number of polls.
+// and stores, and mbarrier waits that give up after a bounded time.
 //
 // Shared-memory operand layout used throughout (the "128-byte swizzle" canonical layout): a tile is a
 // stack of rows of 128 bytes (64 sixteen-bit elements); eight rows form a 1024-byte atom; inside an atom
@@ -165,12 +165,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, ui
       : "memory");
   return done != 0;
 }
-// Waits until the phase with the given parity has completed, for at most kMaxTries tries of about 20 us each
-// (tens of milliseconds in all; a tile of work takes microseconds).  Returns false when it gave up or when
-// *abort is already set, and sets *abort (a shared-memory word of the CTA) so that every later wait of the CTA
-// returns at once: the kernel then runs to its end on whatever it finds, frees its tensor memory and reports
-// through its status word.
-constexpr uint32_t kMaxTries = 2048;
+// Waits until the phase with the given parity has completed, for at most kMaxTries tries of about 20 us each:
+// half a second in all, where a tile of work takes microseconds, so that a context that is switched out for a
+// while on a shared GPU does not trip it.  Returns false when it gave up or when *abort is already set, and sets
+// *abort (a shared-memory word of the CTA) so that every later wait of the CTA returns at once: the kernel then
+// runs to its end on whatever it finds, frees its tensor memory and reports through its status word.
+constexpr uint32_t kMaxTries = 25000;
 constexpr uint32_t kTryNs = 20000;
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile uint32_t* abort) {
   for (uint32_t i = 0; i < kMaxTries; ++i) {
