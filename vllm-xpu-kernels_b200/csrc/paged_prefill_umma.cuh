@@ -202,18 +202,20 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
       }
     }
   };
-  // fp8 caches: a row is 128 bytes; thread t fetches 32 of them (quarter t % 4 of row t / 4), widens them to
-  // fp16 (exact) and stores the 64 bytes as four chunks of the same swizzled 16-bit layout.  The fetch is split
-  // from the store so that the loads are in flight while the thread does other work.
+  // fp8 caches: a row is 128 bytes.  Thread t copies 32 of them (quarter t % 4 of row t / 4) with cp.async into
+  // the upper half of the tile's slot, where raw row r occupies the 128 bytes that row r of the second D half
+  // will occupy; later the same thread reads its 32 bytes back, widens them to fp16 (exact) and stores the 64
+  // bytes as four chunks of the swizzled 16-bit layout.  The only bytes a store can overwrite before they are
+  // read are those of the same row, which the same warp reads: a __syncwarp between the reads and the stores
+  // is all the ordering the conversion needs.
   struct Fp8Quarter {
     uint4 a, b;
   };
-  auto fetch_fp8 = [&](int tile, const void* cache, int32_t blk) {
-    Fp8Quarter q;
-    q.a = q.b = make_uint4(0, 0, 0, 0);
+  auto issue_raw_fp8 = [&](int tile, const void* cache, int32_t blk, unsigned char* dst_tile) {
     const int r = tid >> 2, token = tile * TN + r;
-    if (token < n) {
-      int64_t off;
+    const bool valid = token < n;
+    int64_t off = 0;
+    if (valid) {
       if (tile_in_block) {
         off = static_cast<int64_t>(blk) * p.block_stride + static_cast<int64_t>(token & (p.block_size - 1)) * p.page_stride;
       } else {
@@ -221,11 +223,17 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
         off = static_cast<int64_t>(__ldg(table + blk_idx)) * p.block_stride +
               static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride;
       }
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(cache) + off + head_off +
-                                                        (tid & 3) * 32);
-      q.a = __ldg(src);
-      q.b = __ldg(src + 1);
     }
+    const unsigned char* src = static_cast<const unsigned char*>(cache) + off + head_off + (tid & 3) * 32;
+    const uint32_t dst = smem_addr(dst_tile + Cfg::kKVHalfBytes) + r * 128 + (tid & 3) * 32;
+    cp_async_16(dst, src, valid ? 16 : 0);
+    cp_async_16(dst + 16, src + 16, valid ? 16 : 0);
+  };
+  auto read_raw_fp8 = [&](const unsigned char* dst_tile) {
+    const uint4* raw = reinterpret_cast<const uint4*>(dst_tile + Cfg::kKVHalfBytes + (tid >> 2) * 128 + (tid & 3) * 32);
+    Fp8Quarter q;
+    q.a = raw[0];
+    q.b = raw[1];
     return q;
   };
   auto store_fp8 = [&](const Fp8Quarter& q, unsigned char* dst_tile) {
@@ -264,9 +272,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
     blk_v = tile_blk(tile_begin + 1);
     blk_k = tile_blk(tile_begin + 2);
     if constexpr (kFp8) {
-      const Fp8Quarter k0 = fetch_fp8(tile_begin, p.key_cache, b0);
-      const Fp8Quarter k1 = fetch_fp8(tile_begin + 1, p.key_cache, blk_v);  // zeros past the sequence's end
-      const Fp8Quarter v0 = fetch_fp8(tile_begin, p.value_cache, b0);
+      issue_raw_fp8(tile_begin, p.key_cache, b0, k_slot(0));
+      issue_raw_fp8(tile_begin + 1, p.key_cache, blk_v, k_slot(1));  // zeros past the sequence's end
+      issue_raw_fp8(tile_begin, p.value_cache, b0, v_slot(0));
+      cp_async_commit();
+      cp_async_wait<0>();
+      const Fp8Quarter k0 = read_raw_fp8(k_slot(0)), k1 = read_raw_fp8(k_slot(1)), v0 = read_raw_fp8(v_slot(0));
+      __syncwarp();
       store_fp8(k0, k_slot(0));
       store_fp8(k1, k_slot(1));
       store_fp8(v0, v_slot(0));
@@ -368,10 +380,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
     mbar_wait_bounded(bar_s + (it & 1), (it >> 1) & 1, abort_word);  // S(it) is there, K slot it & 1 is free
     fence_after_thread_sync();
     const int32_t blk_next = tile_blk(tile + 3);
-    if constexpr (!kFp8) {
-      if (it + 2 < nt) load_rows(tile + 2, p.key_cache, k_slot(it), blk_k);
-      cp_async_commit();
+    if (it + 2 < nt) {
+      if constexpr (kFp8) {
+        issue_raw_fp8(tile + 2, p.key_cache, blk_k, k_slot(it));
+      } else {
+        load_rows(tile + 2, p.key_cache, k_slot(it), blk_k);
+      }
     }
+    cp_async_commit();
 
     // ---- softmax of this thread's half row: columns [32 wg, 32 wg + 32) of the tile ---------------------------
     uint32_t sa[32];
@@ -423,14 +439,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
       mbar_wait_bounded(bar_o, (it - 1) & 1, abort_word);
       fence_after_thread_sync();
     }
-    [[maybe_unused]] Fp8Quarter fk, fv;
-    if constexpr (kFp8) {  // in flight while P is stored (and O rescaled)
-      if (it + 2 < nt) fk = fetch_fp8(tile + 2, p.key_cache, blk_k);
-      if (it + 1 < nt) fv = fetch_fp8(tile + 1, p.value_cache, blk_v);
-    } else {
-      if (it + 1 < nt) load_rows(tile + 1, p.value_cache, v_slot(it + 1), blk_v);
-      cp_async_commit();
+    if (it + 1 < nt) {
+      if constexpr (kFp8) {
+        issue_raw_fp8(tile + 1, p.value_cache, blk_v, v_slot(it + 1));
+      } else {
+        load_rows(tile + 1, p.value_cache, v_slot(it + 1), blk_v);
+      }
     }
+    cp_async_commit();
     blk_v = blk_k;
     blk_k = blk_next;
     if (it > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // rare: a reference maximum of the warp moved
@@ -448,11 +464,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
     // P(it) takes the place of S(it): both warpgroups have read their halves (the exchange above orders that)
     tmem_st_32x16(tmem + lane_base + kUmmaColS + (it & 1) * TN + wg * 16, w);
     tmem_st_wait();
-    if constexpr (kFp8) {  // K slot it & 1 is free since S(it), V slot (it + 1) & 1 since the wait on bar_o above
-      if (it + 2 < nt) store_fp8(fk, k_slot(it));
-      if (it + 1 < nt) store_fp8(fv, v_slot(it + 1));
-    }
     cp_async_wait<1>();           // all but this iteration's V group: V(it) and K(it + 2) have landed
+    if constexpr (kFp8) {         // as raw bytes: widen K(it + 2) and V(it) in place (V(0) was done up front)
+      Fp8Quarter fk, fv;
+      if (it + 2 < nt) fk = read_raw_fp8(k_slot(it));
+      if (it > 0) fv = read_raw_fp8(v_slot(it));
+      __syncwarp();
+      if (it + 2 < nt) store_fp8(fk, k_slot(it));
+      if (it > 0) store_fp8(fv, v_slot(it));
+    }
     fence_smem_to_async_proxy();
     fence_before_thread_sync();
     mbar_arrive(bar_ready);
