@@ -22,6 +22,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <type_traits>
 
 namespace kvc {
 namespace umma {
@@ -56,6 +57,11 @@ __host__ __device__ constexpr uint32_t instr_desc_f16(int m, int n, bool a_mn_ma
   return (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
+
+// the encodings the kernels here run with (checked on a B200 against a CPU product of the same operands)
+static_assert(instr_desc_f16<__nv_bfloat16>(128, 64, false, false) == 0x08100490u, "S = Q K^T, bf16, M 128, N 64");
+static_assert(instr_desc_f16<__nv_bfloat16>(128, 128, false, true) == 0x08210490u, "O += P V, bf16, V MN-major");
+static_assert(instr_desc_f16<__half>(128, 128, false, true) == 0x08210010u, "O += P V, fp16, V MN-major");
 
 // ---- tensor memory ---------------------------------------------------------------------------------
 // Whole-warp calls.  `columns` is a power of two >= 32; the address of the allocation lands in *slot
