@@ -34,6 +34,7 @@ host memory through torch copies, calls the C ABI and reads the step's result ba
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import os
 import statistics
@@ -209,20 +210,32 @@ def host_threads() -> int:
         return max(1, os.cpu_count() or 1)
 
 
-def make_batch_sets(name: str, rank: int, world: int, scaling: str, nbuf: int, tokens: int | None = None):
-    """nbuf independent batches of the named workload for this rank (CPU tensors).  ``tokens`` resizes
-    the C4 batch (size studies only; the named configuration is the default)."""
+def make_batch_sets(name: str, rank: int, world: int, scaling: str, nbuf: int | None, tokens: int | None = None):
+    """Independent batches of the named workload for this rank (CPU tensors).  ``tokens`` resizes the C4
+    batch (size studies only; the named configuration is the default).
+
+    Replicated job: ``nbuf`` batches.  Head-sharded job: ``nbuf * world`` sets, so that a rank's rotating
+    inputs stay as large as the whole batch's (several times L2) although each set is ``world`` times
+    smaller: set j is the slice of batch ``j % nbuf`` that holds heads of rank ``(rank + j // nbuf) %
+    world`` -- the rank's own heads for the first ``nbuf`` sets, other ranks' rows of the same batch (same
+    shape, same slots, same scales) as further distinct inputs after that."""
     def make(variant: int):
         if tokens is not None and name == "C4":
             return workloads.c4(variant=variant, num_tokens=tokens)
         return workloads.BY_NAME[name](variant=variant)
 
+    if nbuf is None:  # enough sets for about 512 MB of inputs, between NBUF and 64
+        first = make(0)
+        per_set = first.key.numel() * first.key.element_size() * 2
+        nbuf = max(NBUF, min(64, -(-(512 << 20) // per_set)))
+    if scaling != "strong":
+        return [make(b + 100 * rank) for b in range(nbuf)]
+    batches = [make(b) for b in range(nbuf)]
     sets = []
-    for b in range(nbuf):
-        if scaling == "strong":
-            w = workloads.shard_heads(make(b), rank, world)
-        else:
-            w = make(b + 100 * rank)
+    for j in range(nbuf * world):
+        w = workloads.shard_heads(batches[j % nbuf], (rank + j // nbuf) % world, world)
+        if world > 1:  # a rank holds its heads only, packed
+            w = dataclasses.replace(w, key=w.key.contiguous(), value=w.value.contiguous())
         sets.append(w)
     return sets
 
@@ -367,6 +380,173 @@ def describe_workload(w, name: str) -> str:
 # --------------------------------------------------------------------------------------------
 # the B200 arm
 # --------------------------------------------------------------------------------------------
+def to_device_same_layout(t: torch.Tensor, dev, moved: dict) -> torch.Tensor:
+    """``t`` on the device with the strides it has on the host.  A view (C5's key and value are slices
+    of one fused qkv tensor) moves with the tensor it is a view of, once, so that the kernel meets the
+    same row stride and the same neighbours in memory as the configuration describes; ``Tensor.to``
+    alone would hand back a packed copy."""
+    base = t._base
+    if base is None or t.is_contiguous():
+        return t.to(dev)
+    if id(base) not in moved:
+        moved[id(base)] = base.to(dev)
+    return moved[id(base)].as_strided(t.shape, t.stride(), t.storage_offset())
+
+
+class DeviceCase:
+    """One cache-write workload resident on one GPU: its rotating input sets, the two caches, ``step(i)``."""
+
+    def __init__(self, cabi, name: str, rank: int, world: int, scaling: str, dev, tokens: int | None = None,
+                 nbuf: int | None = NBUF):
+        self.cabi, self.name, self.dev = cabi, name, dev
+        self.sets = make_batch_sets(name, rank, world, scaling, nbuf, tokens)
+        w0 = self.w0 = self.sets[0]
+        self.paged = w0.layout == "paged"
+        ksh, vsh = w0.cache_shapes()
+        cdt = w0.cache_dtype
+        # torch.zeros: the allocation is touched once so first-use effects stay out of the timed region
+        self.key_cache = torch.zeros(ksh, dtype=torch.uint8 if cdt != w0.key.dtype else cdt, device=dev)
+        self.value_cache = torch.zeros(vsh, dtype=self.key_cache.dtype, device=dev)
+        if cdt != w0.key.dtype:
+            self.key_cache, self.value_cache = self.key_cache.view(cdt), self.value_cache.view(cdt)
+        self.dsets = []
+        for w in self.sets:
+            moved: dict = {}
+            self.dsets.append((to_device_same_layout(w.key, dev, moved), to_device_same_layout(w.value, dev, moved),
+                               w.slot_mapping.to(dev), w.k_scale.to(dev), w.v_scale.to(dev)))
+        self.in_bytes = sum(w.key.numel() * w.key.element_size() * 2 for w in self.sets)
+        self.kv = w0.kv_cache_dtype
+
+    def step(self, i: int) -> None:
+        k, v, s, ks, vs = self.dsets[i % len(self.dsets)]
+        if self.paged:
+            self.cabi.reshape_and_cache(k, v, self.key_cache, self.value_cache, s, self.kv, ks, vs)
+        else:
+            self.cabi.reshape_and_cache_flash(k, v, self.key_cache, self.value_cache, s, self.kv, ks, vs)
+
+    def rows_written(self, blk: torch.Tensor, off: torch.Tensor, key_cache, value_cache):
+        """The cache rows at (block, offset) as [n, H*D] byte tensors, for either layout."""
+        if self.paged:
+            k = key_cache[blk, :, :, off]          # [n, H, D/x, x]
+            v = value_cache[blk, :, :, off]        # [n, H, D]
+        else:
+            k, v = key_cache[blk, off], value_cache[blk, off]
+        n = blk.numel()
+        return k.contiguous().view(torch.uint8).reshape(n, -1), v.contiguous().view(torch.uint8).reshape(n, -1)
+
+    def parity_rows(self, nrows: int = 64, which: int = 0) -> tuple[int, int]:
+        """(rows compared, rows that differ): runs input set ``which`` once more, reads ``nrows`` of the
+        cache rows it wrote and compares them byte for byte with what the CPU oracle writes for the same
+        tokens (into a small host cache: token i of the sample goes to slot i)."""
+        import oracle
+        from oracle import torch_views as H
+
+        w = self.sets[which]
+        self.step(which)
+        torch.cuda.synchronize()
+        act = torch.nonzero(w.slot_mapping >= 0).flatten()
+        if act.numel() == 0:
+            return 0, 0
+        g = torch.Generator().manual_seed(1234 + which)
+        idx = act[torch.randperm(act.numel(), generator=g)[:nrows]].sort().values
+        n, bs = int(idx.numel()), w.block_size
+        key, value = w.key[idx].contiguous(), w.value[idx].contiguous()
+        raw = torch.uint8 if w.cache_dtype != key.dtype else key.dtype
+        hb = (n + bs - 1) // bs
+        if self.paged:
+            x = 16 // torch.empty((), dtype=w.cache_dtype).element_size()
+            hk = torch.zeros(hb, w.num_heads, w.head_size // x, bs, x, dtype=raw)
+            hv = torch.zeros(hb, w.num_heads, w.head_size, bs, dtype=raw)
+            fn = oracle.reshape_and_cache
+        else:
+            hk = torch.zeros(hb, bs, w.num_heads, w.head_size, dtype=raw)
+            hv = torch.zeros_like(hk)
+            fn = oracle.reshape_and_cache_flash
+        hs = torch.arange(n, dtype=torch.long)
+        fn(H.as_np(key), H.as_np(value), H.as_np(hk), H.as_np(hv), hs.numpy(), w.kv_cache_dtype,
+           float(w.k_scale), float(w.v_scale), H.ORC_IN[key.dtype], threads=1)
+        ek, ev = self.rows_written(hs // bs, hs % bs, hk, hv)
+        slots = w.slot_mapping[idx].to(self.dev)
+        dk, dv = self.rows_written(slots // bs, slots % bs, self.key_cache, self.value_cache)
+        bad = (dk.cpu() != ek).any(dim=1) | (dv.cpu() != ev).any(dim=1)
+        return n, int(bad.sum())
+
+
+def time_passes(step, steps: int, warmup: int, dist, local: int, min_region_s: float, nsets: int = NBUF) -> dict:
+    """Times ``repeats`` passes of exactly ``steps`` steps each, back to back between one pair of CUDA
+    events on the launching stream.  A pass is replayed from CUDA graphs (one graph when ``steps`` is at
+    most GRAPH_STEPS); ``repeats`` is the smallest count that makes the timed region at least
+    ``min_region_s`` long, found from two untimed passes and agreed over the ranks.  An event after
+    every pass gives the spread between passes.  Successive graph replays continue the rotation over the
+    ``nsets`` input sets where the previous one stopped (a graph is captured per starting set)."""
+    def capture(n: int, start: int = 0):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(n):
+                step(start + i)
+        return g
+
+    for i in range(nsets):  # eager warm-up before capture (module load, first touch)
+        step(i)
+    torch.cuda.synchronize()
+    g_full = capture(GRAPH_STEPS) if steps >= GRAPH_STEPS or warmup >= GRAPH_STEPS else None
+    rem = steps % GRAPH_STEPS
+    # a short pass does not reach every input set: successive passes start where the last one stopped
+    n_rem = 0 if not rem else (1 if steps >= GRAPH_STEPS else max(1, min(8, -(-nsets // rem))))
+    g_rem = [capture(rem, k * rem) for k in range(n_rem)]
+    g_wrem = capture(warmup % GRAPH_STEPS) if warmup % GRAPH_STEPS else None
+    passes_done = [0]
+
+    def one_pass() -> None:
+        for _ in range(steps // GRAPH_STEPS):
+            g_full.replay()
+        if g_rem:
+            g_rem[passes_done[0] % len(g_rem)].replay()
+        passes_done[0] += 1
+
+    for _ in range(warmup // GRAPH_STEPS):
+        g_full.replay()
+    if g_wrem is not None:
+        g_wrem.replay()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    one_pass()
+    c0.record()
+    one_pass()
+    one_pass()
+    c1.record()
+    torch.cuda.synchronize()
+    est_pass_ms = max(max_over_ranks(dist, c0.elapsed_time(c1) / 2), 1e-4)
+    repeats = max(1, min(100_000, int(min_region_s * 1e3 / est_pass_ms + 0.999)))
+
+    sampler = ClockSampler(local)
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(repeats + 1)]
+    barrier(dist)
+    sampler.start()
+    events[0].record()
+    for r in range(repeats):
+        one_pass()
+        events[r + 1].record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    barrier(dist)
+    own_ms = events[0].elapsed_time(events[repeats])
+    per_pass = sorted(events[r].elapsed_time(events[r + 1]) / steps * 1e3 for r in range(repeats))
+    return {
+        "own_ms_per_step": own_ms / (repeats * steps),
+        "ms_per_step": max_over_ranks(dist, own_ms) / (repeats * steps),
+        "repeats": repeats, "launches": repeats * steps, "region_ms": own_ms, "clocks": clocks,
+        "pass_us_per_step": {"min": per_pass[0], "median": per_pass[len(per_pass) // 2], "max": per_pass[-1]},
+        "graphs": (f"a pass is one CUDA graph of {steps} launches ({len(g_rem)} such graph(s), each starting at the next input sets, "
+                   f"taken in turn)" if steps < GRAPH_STEPS else f"CUDA graphs of {GRAPH_STEPS} launches"),
+    }
+
+
+def timing_note(t: dict, steps: int) -> str:
+    return (f"{t['graphs']}, a pass of {steps} steps replayed {t['repeats']} times back to back between one pair "
+            f"of CUDA events on the launching stream ({t['region_ms']:.0f} ms), after the warm-up steps and three "
+            f"untimed passes; ms_per_step = region / (repeats * steps)")
+
+
 def run_b200_arm(ns):
     from vllm_xpu_kernels import cabi  # raises if the CUDA library is not built
 
@@ -376,82 +556,38 @@ def run_b200_arm(ns):
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     cabi.lib()
+    peak, peak_src = measured_peaks()
+    # --shard-of G on one GPU: this GPU runs the part rank 0 of G ranks would run
+    shard_rank, shard_world = (rank, world) if ns.shard_of is None else (0, ns.shard_of)
 
-    sets = make_batch_sets(ns.workload, rank, world, ns.scaling, NBUF, ns.tokens)
-    w0 = sets[0]
-    paged = w0.layout == "paged"
-    ksh, vsh = w0.cache_shapes()
-    cdt = w0.cache_dtype
-    # torch.zeros: the allocation is touched once so first-use effects stay out of the timed region
-    key_cache = torch.zeros(ksh, dtype=torch.uint8 if cdt != w0.key.dtype else cdt, device=dev)
-    value_cache = torch.zeros(vsh, dtype=key_cache.dtype, device=dev)
-    if cdt != w0.key.dtype:
-        key_cache, value_cache = key_cache.view(cdt), value_cache.view(cdt)
-    dsets = [(w.key.to(dev), w.value.to(dev), w.slot_mapping.to(dev), w.k_scale.to(dev), w.v_scale.to(dev)) for w in sets]
-    in_bytes = sum(k.numel() * k.element_size() * 2 for k, _, _, _, _ in dsets)
-    kv = w0.kv_cache_dtype
-
-    def step(i: int) -> None:
-        k, v, s, ks, vs = dsets[i % NBUF]
-        if paged:
-            cabi.reshape_and_cache(k, v, key_cache, value_cache, s, kv, ks, vs)
-        else:
-            cabi.reshape_and_cache_flash(k, v, key_cache, value_cache, s, kv, ks, vs)
-
-    # graphs: GRAPH_STEPS steps each, plus one for the remainder so that exactly K steps are timed
-    def capture(n: int):
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            for i in range(n):
-                step(i)
-        return g
-
-    for i in range(NBUF):  # eager warm-up before capture (module load, first-touch)
-        step(i)
-    torch.cuda.synchronize()
-    g_full = capture(GRAPH_STEPS) if ns.steps >= GRAPH_STEPS or ns.warmup >= GRAPH_STEPS else None
-    rem = ns.steps % GRAPH_STEPS
-    g_rem = capture(rem) if rem else None
-    wrem = ns.warmup % GRAPH_STEPS
-    g_wrem = capture(wrem) if wrem else None
-
-    sampler = ClockSampler(local)
-    for _ in range(ns.warmup // GRAPH_STEPS):
-        g_full.replay()
-    if g_wrem is not None:
-        g_wrem.replay()
-    barrier(dist)
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(ns.steps // GRAPH_STEPS):
-        g_full.replay()
-    if g_rem is not None:
-        g_rem.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    clocks = sampler.stop()
-    barrier(dist)
-    total_ms = max_over_ranks(dist, e0.elapsed_time(e1))
-    ms_per_step = total_ms / ns.steps
+    case = DeviceCase(cabi, ns.workload, shard_rank, shard_world, ns.scaling, dev, ns.tokens)
+    sets, w0, paged, in_bytes = case.sets, case.w0, case.paged, case.in_bytes
+    t = time_passes(case.step, ns.steps, ns.warmup, dist, local, ns.min_region_ms * 1e-3, len(case.dsets))
+    ms_per_step = t["ms_per_step"]
     tokens_all = sum_over_ranks(dist, float(w0.num_tokens)) if ns.scaling == "weak" else float(w0.num_tokens)
     value = tokens_all / (ms_per_step * 1e-3)
     bytes_launch = w0.algorithmic_bytes()
-    achieved = bytes_launch / (e0.elapsed_time(e1) / ns.steps * 1e-3) / 1e9  # this rank's own kernel
-    peak, peak_src = measured_peaks()
+    achieved = bytes_launch / (t["own_ms_per_step"] * 1e-3) / 1e9  # this rank's own kernel
+    hbm_all = sum_over_ranks(dist, float(bytes_launch)) / (ms_per_step * 1e-3) / 1e9
 
     # single launches bracketed by their own events (eager), for the launch-latency picture
     singles = []
     for i in range(min(200, max(8, ns.steps))):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        step(i)
+        case.step(i)
         b.record()
         singles.append((a, b))
     torch.cuda.synchronize()
     single_us = statistics.median(a.elapsed_time(b) for a, b in singles) * 1e3
 
+    # ---------------------------------------------------------------- every rank checks bytes it wrote
+    rows, bad = case.parity_rows(64, which=rank % NBUF)  # one of the rank's own-head sets
+    parity = {"rows": int(sum_over_ranks(dist, float(rows))), "mismatches": int(sum_over_ranks(dist, float(bad))),
+              "how": "64 cache rows per rank written by one more call, byte for byte against the CPU oracle"}
+
     # ---------------------------------------------------------------- end to end, host buffers
+    key_cache, value_cache, dsets, kv = case.key_cache, case.value_cache, case.dsets, case.kv
     e2e_steps = max(1, min(ns.steps, 40))
     hsets = [(w.key.contiguous().pin_memory(), w.value.contiguous().pin_memory(), w.slot_mapping.pin_memory())
              for w in sets[:4]]
@@ -496,6 +632,43 @@ def run_b200_arm(ns):
     d2h = probes[0][0].numel() + probes[0][1].numel()
     if not paged:
         cabi.release_staging()
+    launches = t["launches"]
+
+    # ---------------------------------------------------------------- N > 1: the replicated job as well
+    weak = None
+    if world > 1 and ns.scaling == "strong" and not ns.no_also:
+        del case, key_cache, value_cache, dsets, kflat, vflat
+        torch.cuda.empty_cache()
+        wcase = DeviceCase(cabi, ns.workload, rank, world, "weak", dev, ns.tokens)
+        wt = time_passes(wcase.step, ns.steps, ns.warmup, dist, local, ns.min_region_ms * 1e-3 / 2)
+        wtokens = sum_over_ranks(dist, float(wcase.w0.num_tokens))
+        weak = {"value": wtokens / (wt["ms_per_step"] * 1e-3), "unit": "tokens/s", "ms_per_step": wt["ms_per_step"],
+                "repeats": wt["repeats"],
+                "what": f"every rank writes the whole batch ({wcase.w0.num_heads} KV heads) into a cache of its own"}
+        launches += wt["launches"]
+        del wcase
+
+    # ---------------------------------------------------------------- N = 1: the metric's other configurations
+    also = None
+    if world == 1 and ns.workload == "C4" and ns.shard_of is None and ns.tokens is None and not ns.no_also:
+        del case, key_cache, value_cache, dsets, kflat, vflat
+        torch.cuda.empty_cache()
+        also = {}
+        for name in ("C2", "C5-fp8", "C5-bf16", "C3", "C1"):
+            c = DeviceCase(cabi, name, 0, 1, "weak", dev, nbuf=None)
+            ct = time_passes(c.step, ns.steps, ns.warmup, None, local, 0.05, len(c.dsets))
+            nbytes = c.w0.algorithmic_bytes()
+            gbs = nbytes / (ct["ms_per_step"] * 1e-3) / 1e9
+            rws, bd = c.parity_rows(64)
+            also[name] = {"us_per_step": ct["ms_per_step"] * 1e3, "gbs": gbs, "frac": gbs / peak,
+                          "tokens_per_s": c.w0.num_tokens / (ct["ms_per_step"] * 1e-3),
+                          "algorithmic_bytes_per_launch": nbytes, "repeats": ct["repeats"],
+                          "parity_check": {"rows": rws, "mismatches": bd},
+                          "input_sets": len(c.dsets), "input_mb": round(c.in_bytes / 1e6),
+                          "workload": describe_workload(c.w0, name)}
+            launches += ct["launches"]
+            del c
+            torch.cuda.empty_cache()
 
     # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1)
     cpu = None
@@ -510,7 +683,7 @@ def run_b200_arm(ns):
 
     line = None
     if rank == 0:
-        total_heads = w0.num_heads * (world if ns.scaling == "strong" else 1)
+        total_heads = w0.num_heads * (shard_world if ns.scaling == "strong" else 1)
         head = (f"all {w0.num_heads} KV heads per rank" if ns.scaling == "weak"
                 else f"{w0.num_heads} of {total_heads} KV heads per rank")
         line = {
@@ -520,21 +693,31 @@ def run_b200_arm(ns):
             "config": {
                 "workload": describe_workload(sets[0], ns.workload),
                 "sharding": f"by KV head, no collective; {head}",
-                "l2": f"inputs rotate over {NBUF} batch sets ({in_bytes / 1e6:.0f} MB per rank, L2 is 126 MB); "
+                "l2": f"inputs rotate over {len(sets)} input sets ({in_bytes / 1e6:.0f} MB per rank, L2 is 126 MB); "
                       f"each set writes its own cache blocks",
-                "timing": f"CUDA graphs of {GRAPH_STEPS} launches, events on the launching stream",
+                "timing": timing_note(t, ns.steps),
             },
-            "hbm_gbs": achieved * (world if ns.scaling == "weak" else 1),
+            "repeats": t["repeats"],
+            "pass_us_per_step": t["pass_us_per_step"],
+            "hbm_gbs": hbm_all,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(ns.workload), "peak_source": peak_src,
+                         "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(ns.workload) if shard_world == 1 and ns.tokens is None else None,
+                         "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": bytes_launch, "frac_of_nominal_8000": achieved / 8000.0,
                          "single_launch_us_eager": single_us},
+            "parity_check": parity,
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "api": e2e_api},
-            "clocks": clocks,
-            "gpu_launches": ns.steps,
+            "clocks": t["clocks"],
+            "gpu_launches": launches,
         }
+        if weak is not None:
+            line["weak"] = weak
+        if also is not None:
+            line["also"] = also
+        if ns.shard_of is not None:
+            line["config"]["sharding"] += f" (one GPU running the share of rank 0 of {ns.shard_of})"
     if dist is not None:
         dist.destroy_process_group()
     return line
@@ -585,43 +768,16 @@ def run_op_arm(ns):
     nbuf = 2
     step, e2e_step, h2d, d2h = w.make_steps(dev, nbuf)
 
-    def capture(n: int):
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            for i in range(n):
-                step(i)
-        return g
-
-    for i in range(max(3, nbuf)):
-        step(i)
-    torch.cuda.synchronize()
     steps, warmup = ns.steps, ns.warmup
-    g_full = capture(GRAPH_STEPS) if steps >= GRAPH_STEPS or warmup >= GRAPH_STEPS else None
-    g_rem = capture(steps % GRAPH_STEPS) if steps % GRAPH_STEPS else None
-    g_wrem = capture(warmup % GRAPH_STEPS) if warmup % GRAPH_STEPS else None
-    sampler = ClockSampler(local)
-    for _ in range(warmup // GRAPH_STEPS):
-        g_full.replay()
-    if g_wrem is not None:
-        g_wrem.replay()
-    barrier(dist)
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps // GRAPH_STEPS):
-        g_full.replay()
-    if g_rem is not None:
-        g_rem.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    clocks = sampler.stop()
-    barrier(dist)
-    ms_per_step = max_over_ranks(dist, e0.elapsed_time(e1)) / steps
+    t = time_passes(step, steps, warmup, dist, local, ns.min_region_ms * 1e-3)
+    clocks = t["clocks"]
+    ms_per_step = t["ms_per_step"]
+    own_s = t["own_ms_per_step"] * 1e-3
     value = w.units_per_step * world / (ms_per_step * 1e-3)
-    achieved = w.algorithmic_bytes / (e0.elapsed_time(e1) / steps * 1e-3) / 1e9
+    achieved = w.algorithmic_bytes / own_s / 1e9
     peak, peak_src = measured_peaks()
     if w.flops > 0:  # compute-bound step: useful flops against the measured dense bf16 GEMM rate
-        tf = w.flops / (e0.elapsed_time(e1) / steps * 1e-3) / 1e12
+        tf = w.flops / own_s / 1e12
         tpeak, tsrc = measured_tensor_peak()
         roofline = {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak,
                     "traffic": None, "peak_source": tsrc, "useful_flops_per_launch": w.flops,
@@ -658,7 +814,9 @@ def run_op_arm(ns):
             "config": {"workload": f"{w.name}: {w.describe}", "sharding": "every rank runs the whole step on its own data",
                        "l2": f"inputs rotate over {nbuf} sets; one step moves {w.algorithmic_bytes / 1e6:.0f} MB "
                              f"(L2 is 126 MB)",
-                       "timing": f"CUDA graphs of {GRAPH_STEPS} steps, events on the launching stream"},
+                       "timing": timing_note(t, steps)},
+            "repeats": t["repeats"],
+            "pass_us_per_step": t["pass_us_per_step"],
             "hbm_gbs": achieved * world,
             "roofline": roofline,
             "cpu_baseline": cpu,
@@ -666,19 +824,19 @@ def run_op_arm(ns):
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "api": "pinned host tensors -> .to(device) -> C ABI call -> result read back"},
             "clocks": clocks,
-            "gpu_launches": steps * w.launches_per_step,
+            "gpu_launches": t["launches"] * w.launches_per_step,
         }
     if dist is not None:
         dist.destroy_process_group()
     return line
 
 
-# DRAM bytes per launch from the ncu capture summarised in
-# profiles/flash_scatter_bf16_fp8.md.  The capture ran the same kernel on 32768 tokens (the
-# full-size workload holds too much memory for a multi-pass capture); traffic grows in
-# proportion to the tokens, so a 16384-token launch is half of it: dram__bytes_read.sum
-# 134 504 704 / 2, plus the 33 554 432 bytes written, all of which reach DRAM once (the capture
-# window itself saw 47 % of them leave L2 before the kernel ended, the rest are written back later).
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the C4 kernel, from an ncu
+# capture of the same kernel on 32768 tokens: the full-size workload holds too much memory for a
+# multi-pass capture, and traffic grows in proportion to the tokens, so a 16384-token launch is half
+# of it: 134 504 704 / 2 bytes read, plus the 33 554 432 bytes written, all of which reach DRAM once
+# (the capture window itself saw 47 % of them leave L2 before the kernel ended, the rest are written
+# back later).
 TRAFFIC_BYTES_PER_LAUNCH: dict[str, int | None] = {"C4": 67_252_352 + 33_554_432}
 
 
@@ -691,7 +849,15 @@ def main() -> None:
     ap.add_argument("--workload", choices=list(workloads.BY_NAME) + list(op_workloads.BY_NAME), default="C4",
                     help="C1..C5: the cache-write configurations (C4 is the headline); the others are the ops "
                          "around the write, measured the same way")
-    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="strong",
+                    help="strong (default): the batch's KV heads are divided over the ranks, each rank owning its "
+                         "heads' cache slice; weak: every rank writes the whole batch into a cache of its own")
+    ap.add_argument("--shard-of", type=int, default=None, metavar="G",
+                    help="one GPU only: run the share that rank 0 of G ranks would run (sizing studies)")
+    ap.add_argument("--min-region-ms", type=float, default=120.0,
+                    help="the pass of --steps steps is repeated until the timed region is at least this long")
+    ap.add_argument("--no-also", action="store_true",
+                    help="skip the secondary measurements (other configurations at N = 1, replicated job at N > 1)")
     ap.add_argument("--tokens", type=int, default=None, help="resize the C4 batch (size studies; default 16384)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, help="time budget of the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")

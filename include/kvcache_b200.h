@@ -195,7 +195,15 @@ KVC_API int kvc_reshape_and_cache_flash_host(const void* host_key, const void* h
  * imply.  For them the device staging of key, value and slot_mapping is a fixed
  * area of KVC_NOALLOC_STAGING_BYTES inside the library's own device image:
  * every GPU that loads the library holds that much until the process exits,
- * whether or not this entry point is ever called.
+ * whether or not this entry point is ever called.  "Loads" is meant literally:
+ * under the CUDA runtime's default lazy loading the library's device image
+ * reaches a GPU with the first kernel launch or symbol lookup of the library on
+ * that GPU, and it is that moment that reserves the area.  A process that is
+ * going to hand all free memory to a pool must therefore make its first call of
+ * this entry point on each device (or any other call of this library on that
+ * device) BEFORE it sizes the pool; if the very first use came afterwards, the
+ * load itself could fail for lack of memory and the call would return
+ * KVC_ERR_CUDA.  From then on no call changes the amount of free memory.
  *
  * Limit: 2 * round256(num_tokens*num_heads*head_size*elem_size)
  *        + round256(8*num_tokens) must not exceed KVC_NOALLOC_STAGING_BYTES
@@ -357,8 +365,27 @@ KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_h
  * kvc_paged_attention_device_status waits for the device's earlier work and reads the tcgen05 kernel's status
  * word: 0 = fine; 1 = a bounded wait on an mbarrier gave up (results of that call are then undefined; the
  * kernel still ran to its end and freed its tensor memory); 2 = its shared-memory window was not 1024-byte
- * aligned (nothing was computed).  The word is sticky for the life of the process.
+ * aligned (nothing was computed).  The word stays raised until kvc_paged_attention_clear_device_status
+ * (which also waits for the device's earlier work) puts it back to 0.
+ *
+ * kvc_paged_attention_plan tells the launch shape kvc_paged_attention will use for the same arguments (any of
+ * the four outputs may be NULL): sequence splits, tiles per split, tokens per tile, and the workspace that shape
+ * needs.  It knows the window; its workspace figure is never above kvc_paged_attention_workspace_bytes', which
+ * does not, because a windowed call never uses more splits than the same call without the window would.
+ *
+ * kvc_selftest_bounded_wait_gives_up runs the give-up path of the kernel's bounded waits on purpose: one CTA
+ * allocates tensor memory, waits on an mbarrier that nothing arrives on for `tries` tries of about 20 us each
+ * (1..5000), gives up, frees its tensor memory and raises the status word to 1.  No counterpart in the reference
+ * (its kernels have no bounded waits); it exists so that the path a stuck product or copy would take is one that
+ * has run.
  */
+KVC_API int kvc_paged_attention_plan(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q, int64_t num_heads,
+                                     int64_t num_kv_heads, int64_t head_size, int64_t max_seq_len, int causal,
+                                     int64_t window_left, int64_t window_right, int q_dtype, int kv_dtype,
+                                     int32_t* splits, int32_t* tiles_per_split, int32_t* tile_tokens,
+                                     int64_t* workspace_bytes);
+KVC_API int kvc_paged_attention_clear_device_status(void);
+KVC_API int kvc_selftest_bounded_wait_gives_up(int64_t tries, void* stream);
 KVC_API int64_t kvc_paged_attention_workspace_bytes(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q,
                                                     int64_t num_heads, int64_t num_kv_heads, int64_t head_size,
                                                     int64_t max_seq_len, int q_dtype, int kv_dtype);

@@ -473,3 +473,77 @@ def test_window_decode_with_splits(cuda_device):
         want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, 0.09, cu_seqlens_q=cu, causal=True,
                                                       window=window)
         torch.testing.assert_close(out.cpu().float(), want, **TOL)
+
+
+def test_windowed_multi_token_decode_over_a_tile_period(cuda_device):
+    """Four query tokens per sequence behind a closed left window, one sequence for every length of more than a
+    128-token period: a CTA's rows then span window + 4 tokens, which for some lengths touch one tile more than
+    the window alone does.  Every row must still see its newest tokens (the plan has to provide that tile); the
+    shape is one the planner runs on 128-token tiles."""
+    dev = cuda_device
+    hq, hk, D, bs, nb = 4, 1, 128, 64, 512
+    # a batch size for which the planner takes 128-token tiles on this device (its cost model counts the CTAs
+    # the device holds at once); every candidate covers more than a full 128-token period of lengths
+    for count in (141, 180, 240, 320, 480):
+        kv_lens = list(range(1150, 1150 + count))
+        plan = cabi.paged_attention_plan(count, 4 * count, 4, hq, hk, D, max(kv_lens), True, (1023, -1),
+                                         torch.bfloat16, "fp8")
+        if plan["tile_tokens"] == 128:
+            break
+    q_lens = [4] * len(kv_lens)
+    assert plan["tile_tokens"] == 128, plan
+    need = (1024 + 3 + 254) // 128  # tiles that window + 4 tokens can touch
+    assert plan["splits"] * plan["tiles_per_split"] >= need, plan
+    torch.manual_seed(80)
+    query = torch.randn(sum(q_lens), hq, D).to(torch.bfloat16)
+    _, kc, vc, bt, lens, _ = make_case(torch.bfloat16, hq, hk, D, kv_lens, bs, nb, False, seed=81, kv="fp8", descale=0.05)
+    cu = cu_of(q_lens)
+    out = cabi.paged_attention(query.to(dev), kc.view(torch.uint8).to(dev), vc.view(torch.uint8).to(dev), bt.to(dev),
+                               lens.to(dev), cu.to(dev), 4, 0.09, max(kv_lens), True, "fp8", dscalar(0.05, dev),
+                               dscalar(0.05, dev), window=(1023, -1))
+    torch.cuda.synchronize()
+    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, 0.09, "fp8", 0.05, 0.05, None, cu, True,
+                                                  (1023, -1))
+    torch.testing.assert_close(out.cpu().float(), want, **TOL)
+
+
+@pytest.mark.parametrize("slots_window", [(4096, -1), (1024, -1), (63, 0)])
+def test_windowed_decode_needs_no_more_workspace_than_the_size_query(slots_window, cuda_device):
+    """A windowed split decode with exactly the workspace kvc_paged_attention_workspace_bytes reports (which
+    knows no window) must be accepted and right, whatever the window does to the planner's choice."""
+    dev = cuda_device
+    hq, hk, D, bs, nb = 64, 8, 128, 64, 256
+    kv_lens = [8192]
+    torch.manual_seed(82)
+    query, kc, vc, bt, lens, _ = make_case(torch.bfloat16, hq, hk, D, kv_lens, bs, nb, False, seed=83)
+    cu = cu_of([1])
+    out = cabi.paged_attention(query.to(dev), kc.to(dev), vc.to(dev), bt.to(dev), lens.to(dev), cu.to(dev), 1, 0.09,
+                               8192, True, window=slots_window)
+    torch.cuda.synchronize()
+    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, 0.09, cu_seqlens_q=cu, causal=True,
+                                                  window=slots_window)
+    torch.testing.assert_close(out.cpu().float(), want, **TOL)
+    p = cabi.paged_attention_plan(1, 1, 1, hq, hk, D, 8192, True, slots_window)
+    ws = cabi.lib().kvc_paged_attention_workspace_bytes(1, 1, 1, hq, hk, D, 8192, cabi.IN_DTYPE[torch.bfloat16], 0)
+    assert p["workspace_bytes"] <= ws
+
+
+@pytest.mark.parametrize("window", [(0, 0), (-1, 0), (0, -1), (5, 0)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_torch_op_window_rule_is_the_reference_ops(window, causal, cuda_device):
+    """Through flash_attn_varlen_func a window side is open only when it is -1 (csrc/flash_attn/flash_api.cpp:94
+    of the reference): (0, 0) keeps the diagonal, (-1, 0) is a causal band without the causal flag."""
+    dev = cuda_device
+    hq, hk, D, bs, nb = 8, 2, 128, 16, 64
+    q_lens, kv_lens = [5, 1, 33], [40, 7, 33]
+    torch.manual_seed(84)
+    query = torch.randn(sum(q_lens), hq, D).to(torch.float16)
+    _, kc, vc, bt, lens, _ = make_case(torch.float16, hq, hk, D, kv_lens, bs, nb, False, seed=85)
+    cu = cu_of(q_lens)
+    out = flash_attn_varlen_func(query.to(dev), kc.to(dev), vc.to(dev), max(q_lens), cu.to(dev), max(kv_lens),
+                                 seqused_k=lens.to(dev), softmax_scale=0.09, causal=causal, block_table=bt.to(dev),
+                                 window_size=list(window))
+    torch.cuda.synchronize()
+    want = torch_views.run_paged_decode_attention(query, kc, vc, bt, lens, 0.09, cu_seqlens_q=cu, causal=causal,
+                                                  window=window)
+    torch.testing.assert_close(out.cpu().float(), want, **TOL)

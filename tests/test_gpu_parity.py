@@ -452,3 +452,70 @@ def test_paged_sequence_like_slots(dtype, kv, bs, cuda_device):
     dkc2 = H.fill_pattern_(torch.empty(nb, Hh, D // x, bs, x, dtype=cdt), 5).to(dev)
     run_cabi("paged", key.to(dev), value.to(dev), dkc2, dvc2, slots.to(dev), kv, dev_scale(ks, dev), dev_scale(vs, dev))
     assert H.same_bytes(dvc2.cpu(), vc), "value cache (16-byte-offset base) differs"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,kv", [(torch.half, "auto"), (torch.bfloat16, "fp8"), (torch.float, "auto"),
+                                      (torch.float, "fp8"), (torch.half, "fp8_e5m2")])
+@pytest.mark.parametrize("D", [128, 40, 20, 6])
+def test_paged_runs_and_scattered_slots_in_one_batch(dtype, kv, D, cuda_device):
+    """Groups of 32 tokens that hold runs, groups with scattered slots, groups that are half and half, padding
+    and a ragged tail in one call: each warp picks the order of its V stores from its own 32 slots (lane =
+    token for runs, lane = head dimension for scattered slots), and both orders must give the oracle's bytes
+    for every vector width the head size allows."""
+    if kv != "auto" and D % 2:
+        pytest.skip("fp8 caches pack two elements")
+    dev = cuda_device
+    Hh, bs, nb = 3, 16, 96
+    g = torch.Generator().manual_seed(D)
+    free = torch.randperm(nb * bs, generator=g).tolist()
+    blocks = torch.randperm(nb, generator=g).tolist()
+    slots: list[int] = []
+    used: set[int] = set()
+
+    def run(n):
+        b = blocks.pop()
+        out = [b * bs + i for i in range(n)]
+        used.update(out)
+        return out
+
+    def scattered(n):
+        out = []
+        while len(out) < n:
+            s = free.pop()
+            if s // bs in blocks:  # blocks still unassigned to a run
+                blocks.remove(s // bs)
+            if s not in used:
+                used.add(s)
+                out.append(s)
+        return out
+
+    slots += run(16) + run(16)            # a warp of runs
+    slots += scattered(32)                # a warp of scattered slots
+    slots += run(16) + scattered(16)      # 15 adjacent pairs: scattered order
+    slots += run(16) + run(8) + scattered(8)   # 22 adjacent pairs: run order
+    mixed = scattered(32)
+    for i in (0, 5, 6, 31):
+        mixed[i] = -1                     # padding among scattered slots
+    slots += mixed
+    slots += [-1] * 32                    # a warp with nothing to do
+    slots += scattered(11)                # ragged tail
+    T = len(slots)
+    slots_t = torch.tensor(slots, dtype=torch.long)
+    torch.manual_seed(D + 3)
+    key = torch.randn(T, Hh, D).to(dtype)
+    value = torch.randn(T, Hh, D).to(dtype)
+    cdt = H.cache_torch_dtype(dtype, kv)
+    x = 16 // torch.empty((), dtype=cdt).element_size()
+    if D % x:
+        x = 2 if D % 2 == 0 else 1
+    kc = H.fill_pattern_(torch.empty(nb, Hh, D // x, bs, x, dtype=cdt), 5)
+    vc = H.fill_pattern_(torch.empty(nb, Hh, D, bs, dtype=cdt), 6)
+    dkc, dvc = kc.to(dev), vc.to(dev)
+    fmax = 57344.0 if kv == "fp8_e5m2" else 448.0
+    ks = float(key.float().abs().amax() / fmax)
+    vs = float(value.float().abs().amax() / fmax)
+    H.oracle_call("paged", key, value, kc, vc, slots_t, kv, ks, vs)
+    run_cabi("paged", key.to(dev), value.to(dev), dkc, dvc, slots_t.to(dev), kv, dev_scale(ks, dev), dev_scale(vs, dev))
+    assert H.same_bytes(dkc.cpu(), kc), "key cache differs"
+    assert H.same_bytes(dvc.cpu(), vc), "value cache differs"

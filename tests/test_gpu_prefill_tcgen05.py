@@ -152,3 +152,24 @@ def test_prefill_agrees_with_the_mma_sync_kernel(cuda_device):
             outs.append(torch.load(f.name))
     assert dev is not None
     torch.testing.assert_close(outs[0].float(), outs[1].float(), **TOL)
+
+
+def test_a_bounded_wait_that_runs_out(cuda_device):
+    """The give-up path of the kernel's bounded mbarrier waits, run on purpose by the library's self-test kernel:
+    one CTA allocates tensor memory, waits about a millisecond for an arrival that never comes, gives up, frees
+    its tensor memory and raises the status word.  The context stays usable: the word reads 1, clears to 0, and a
+    normal call right after is correct."""
+    import time
+    dev = cuda_device
+    assert cabi.paged_attention_device_status() == 0
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    cabi.selftest_bounded_wait_gives_up(50)
+    assert cabi.paged_attention_device_status() == 1   # waits for the kernel
+    waited = time.perf_counter() - t0
+    assert waited < 5.0, f"the bounded wait took {waited:.3f} s"
+    cabi.paged_attention_clear_device_status()
+    assert cabi.paged_attention_device_status() == 0
+    # tensor memory was given back and nothing is stuck: a full-size call right behind it
+    run_case(dev, torch.bfloat16, 8, 2, q_lens=[300, 140], kv_lens=[777, 1100], bs=64, causal=True, sink=False, seed=31)
+    assert cabi.paged_attention_device_status() == 0

@@ -6,11 +6,13 @@ memory, or sit on a path where cudaMalloc's synchronisation is not acceptable; f
 area inside the library instead of allocating.  This file is named to be collected last, so a
 failure here cannot hide the result of any other test; it passes alone in a fresh process and
 after the rest of the suite.  Results are compared bit for bit, the tolerance every test of
-this integer/byte path uses, on two calls in a row that share the staging area.
+this integer/byte path uses, on two calls in a row that share the staging area, with the
+library's other entry points and with the CPU oracle.
 """
 import pytest
 import torch
 
+from tests import helpers as H_
 from vllm_xpu_kernels import cabi
 
 pytestmark = pytest.mark.gpu
@@ -56,6 +58,15 @@ def test_noalloc_entry_matches_allocating_entry_twice_in_a_row(kv, cuda_device):
         cabi.reshape_and_cache_flash(key.to(dev), value.to(dev), kc_dev, vc_dev, slots.to(dev), kv, ks, vs)
     torch.cuda.synchronize()
     assert _same(kc_new, kc_dev) and _same(vc_new, vc_dev)
+    # and against the CPU oracle directly, both batches into one host cache
+    cache_dt = torch.float8_e4m3fn if kv == "fp8" else torch.bfloat16
+    kc_cpu = torch.zeros(nb, bs, H, D, dtype=cdt).view(cache_dt)
+    vc_cpu = torch.zeros(nb, bs, H, D, dtype=cdt).view(cache_dt)
+    for T, seed, skip in ((4000, 1, 0), (777, 2, 5)):
+        key, value, slots = _batch(T, H, D, nb, bs, seed, skip)
+        H_.oracle_call("flash", key, value, kc_cpu, vc_cpu, slots, kv, float(ks), float(vs))
+    assert _same(kc_new.cpu(), kc_cpu), "key cache differs from the oracle's"
+    assert _same(vc_new.cpu(), vc_cpu), "value cache differs from the oracle's"
     cabi.release_staging()
 
 

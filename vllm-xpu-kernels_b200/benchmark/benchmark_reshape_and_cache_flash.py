@@ -14,11 +14,9 @@ from tabulate import tabulate
 from _common import DTYPES, cache_dtype, common_parser, make_inputs, ops, time_op
 
 
-@torch.inference_mode()
-def run_benchmark(num_tokens: int, num_heads: int, head_size: int, block_size: int, num_blocks: int,
-                  dtype: torch.dtype, kv_cache_dtype: str, num_iters: int, flush_l2: bool = True,
-                  device: str = "cuda") -> tuple[float, float]:
-    """(median, min) latency in seconds for one num_tokens."""
+def make_case(num_tokens: int, num_heads: int, head_size: int, block_size: int, num_blocks: int,
+              dtype: torch.dtype, kv_cache_dtype: str, device: str = "cuda"):
+    """(call, tensors): the inputs of one sweep point and the op call the sweep times."""
     key, value, slots, k_scale, v_scale = make_inputs(num_tokens, num_heads, head_size, block_size, num_blocks,
                                                       dtype, kv_cache_dtype, device)
     cdt = cache_dtype(dtype, kv_cache_dtype)
@@ -31,6 +29,15 @@ def run_benchmark(num_tokens: int, num_heads: int, head_size: int, block_size: i
     def call():
         ops.reshape_and_cache_flash(key, value, key_cache, value_cache, slots, kv_cache_dtype, k_scale, v_scale)
 
+    return call, (key, value, key_cache, value_cache, slots, k_scale, v_scale)
+
+
+@torch.inference_mode()
+def run_benchmark(num_tokens: int, num_heads: int, head_size: int, block_size: int, num_blocks: int,
+                  dtype: torch.dtype, kv_cache_dtype: str, num_iters: int, flush_l2: bool = True,
+                  device: str = "cuda") -> tuple[float, float]:
+    """(median, min) latency in seconds for one num_tokens."""
+    call, _ = make_case(num_tokens, num_heads, head_size, block_size, num_blocks, dtype, kv_cache_dtype, device)
     return time_op(call, num_iters, flush_l2=flush_l2)
 
 

@@ -105,11 +105,11 @@ std::vector<at::Tensor> mha_varlen_fwd(const at::Tensor& q, const at::Tensor& k,
                   !return_softmax,
               op, ": alibi_slopes, leftpad_k, softcap, dropout and return_softmax are not supported");
   TORCH_CHECK(cu_seqlens_q.scalar_type() == at::kInt, "cu_seqlens_q must have dtype torch.int32");
-  // as in the reference's statement, a window exists only if one side is positive; a negative side is open
-  // (tests/flash_attn/test_flash_attn_varlen_func.py:81-85 there)
-  const bool is_local = window_size_left > 0 || window_size_right > 0;
-  const int64_t wl = is_local && window_size_left >= 0 ? window_size_left : -1;
-  const int64_t wr = is_local && window_size_right >= 0 ? window_size_right : -1;
+  // The reference op's rule (csrc/flash_attn/flash_api.cpp:94 and csrc/xpu/attn/xe_2/fmha_xe2.cpp:99-106 there): a
+  // side is open only when it is -1, every other pair is a window -- (0, 0) is the diagonal, (-1, 0) a causal
+  // band -- and under the causal mask the right side counts as 0, which the kernels' min() of both ends gives.
+  TORCH_CHECK(window_size_left >= -1 && window_size_right >= -1, op, ": a window side is -1 (open) or >= 0");
+  const int64_t wl = window_size_left, wr = window_size_right;
   at::Tensor out = out_.has_value() ? *out_ : at::empty(q.sizes(), q.options());
   if (block_table_.has_value()) {
     TORCH_CHECK(seqused_k.has_value(), op, ": seqused_k is needed with a block_table");
@@ -161,11 +161,11 @@ void paged_decode_attention(const at::Tensor& q, const at::Tensor& k_cache, cons
                             std::optional<at::Tensor> v_descale, std::optional<at::Tensor> cu_seqlens_q,
                             int64_t max_seqlen_q, bool is_causal, int64_t window_size_left,
                             int64_t window_size_right) {
-  const bool is_local = window_size_left > 0 || window_size_right > 0;
+  TORCH_CHECK(window_size_left >= -1 && window_size_right >= -1,
+              "paged_decode_attention: a window side is -1 (open) or >= 0");
   paged_decode_impl("paged_decode_attention", q, k_cache, v_cache, out, seqused_k, block_table, max_seqlen_k,
                     softmax_scale, softmax_sink, vllm::kvc_kv_dtype_of(kv_cache_dtype), k_descale, v_descale,
-                    cu_seqlens_q, max_seqlen_q, is_causal, is_local && window_size_left >= 0 ? window_size_left : -1,
-                    is_local && window_size_right >= 0 ? window_size_right : -1);
+                    cu_seqlens_q, max_seqlen_q, is_causal, window_size_left, window_size_right);
 }
 
 }  // namespace

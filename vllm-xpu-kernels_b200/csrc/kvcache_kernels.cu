@@ -148,11 +148,20 @@ constexpr int kPagedThreads = 256;
 // Lane = token.  A warp owns 32 consecutive tokens x one head x VEC consecutive d, so that
 // every store instruction walks the token axis: when consecutive tokens occupy consecutive
 // offsets of one block (a sequence being prefilled) the 32 lanes write one contiguous run
-// (32 x-chunks of K, 32 elements of one V row) and whole sectors leave the SM; with random
-// slots each lane's piece lands in its own sector, which the layout makes unavoidable.
+// (32 x-chunks of K, 32 elements of one V row) and whole sectors leave the SM.
 // The 8 warps of a CTA take adjacent d-chunks of the same rows, so the CTA reads whole rows.
+//
+// With scattered slots (decode batches, random placement) no two tokens share a sector and the
+// lane = token order is the worst one for V: each of a lane's VEC stores goes to a line of its own,
+// 32 lines per instruction.  A warp that finds fewer than half of its tokens adjacent to their
+// successor therefore writes V in the transposed order: an instruction covers 32 / VEC tokens x VEC
+// consecutive d, i.e. per token one run of VEC sectors (bs elements apart in the cache, VEC * 32
+// bytes for 16-bit caches with 16-slot blocks), four sectors to a line.  The elements are fetched in
+// that order as well (a half-warp reads one 32-byte piece of a row), so no exchange between lanes is
+// needed beyond the owner lane's destination offset.  K is written by the owner lane either way:
+// its x-element groups are separate lines in both orders.
 template <typename Tin, int KV, int VEC>
-__global__ void __launch_bounds__(kPagedThreads) paged_scatter_kernel(const PagedParams p) {
+__global__ void __launch_bounds__(kPagedThreads, 4) paged_scatter_kernel(const PagedParams p) {
   constexpr int ES = (int)sizeof(Tin);
   constexpr int IN_B = VEC * ES;
   constexpr int OUT_ES = (KV == KVC_KV_AUTO) ? ES : 1;
@@ -165,66 +174,110 @@ __global__ void __launch_bounds__(kPagedThreads) paged_scatter_kernel(const Page
   const uint32_t chunk = warp - th * p.chunks_per_row;
   const uint32_t tg = p.div_heads.div(th);
   const uint32_t head = th - tg * static_cast<uint32_t>(p.num_heads);
-  const int64_t tok = static_cast<int64_t>(tg) * 32 + lane;
-  if (tok >= p.num_tokens) return;
+  const int64_t tok0 = static_cast<int64_t>(tg) * 32;
+  const int64_t tok = tok0 + lane;
+  const bool in_range = tok < p.num_tokens;
   const int d0 = static_cast<int>(chunk) * VEC;
   const Tin* ksrc = static_cast<const Tin*>(p.key) + tok * p.key_stride_t + head * p.key_stride_h + d0;
   const Tin* vsrc = static_cast<const Tin*>(p.value) + tok * p.value_stride_t + head * p.value_stride_h + d0;
-  if (blockIdx.x < p.prefetch_ctas && slot_hint(p.slot_mapping + tok) >= 0) {
+  if (blockIdx.x < p.prefetch_ctas && in_range && slot_hint(p.slot_mapping + tok) >= 0) {
     prefetch_l2(ksrc);
     prefetch_l2(vsrc);
   }
   pdl_prologue();
 
-  const int64_t slot = __ldg(p.slot_mapping + tok);
-  if (slot < 0) return;
+  const int64_t slot = in_range ? __ldg(p.slot_mapping + tok) : -1;
+  bool transposed = false;
+  if constexpr (VEC > 1) {
+    const int64_t next = __shfl_down_sync(0xffffffffu, slot, 1);
+    const bool adjacent = slot >= 0 && lane < 31u && next == slot + 1;
+    transposed = __popc(__ballot_sync(0xffffffffu, adjacent)) < 16;
+  }
+  const bool active = slot >= 0;
 
-  Chunk<IN_B> kin, vin;
-  load_chunk(kin, ksrc, p.wide_loads);
-  load_chunk(vin, vsrc, p.wide_loads);
-
-  int64_t blk, off;
-  split_slot(slot, p.block_size, p.bs_shift, blk, off);
+  int64_t blk = 0, off = 0;
+  if (active) split_slot(slot, p.block_size, p.bs_shift, blk, off);
+  const int64_t bh = blk * p.num_heads + head;
+  const int64_t bs = p.block_size;
+  const int x = p.x;
+  char* kc = static_cast<char*>(p.key_cache);
+  char* vc = static_cast<char*>(p.value_cache);
+  // K: element d lives at ((bh * (D/x) + d/x) * bs + off) * x + d%x.
+  const int64_t kbase = bh * (p.head_size / x);
+  // V: element d lives at (bh * D + d) * bs + off.
+  const int64_t vbase = active ? (bh * p.head_size + d0) * bs + off : -1;
 
   ScaleCtx ks{}, vs{};
   if constexpr (KV != KVC_KV_AUTO) {
     ks = make_scale_ctx<Tin, KV>(p.k_scale);
     vs = make_scale_ctx<Tin, KV>(p.v_scale);
   }
+
+  auto k_write = [&](const Chunk<OUT_B>& kout) {
+    auto k_store = [&](auto piece_tag) {
+      constexpr int PIECE = decltype(piece_tag)::value;  // bytes per store
+      constexpr int PE = PIECE / OUT_ES;                 // elements per store
+      if constexpr (PE >= 1 && PIECE <= OUT_B) {
+#pragma unroll
+        for (int j = 0; j < VEC; j += PE) {
+          const int d = d0 + j;
+          const int64_t idx = ((kbase + d / x) * bs + off) * x + d % x;
+          store_piece<PIECE>(kc + idx * OUT_ES, kout, j * OUT_ES);
+        }
+      }
+    };
+    switch (p.piece_bytes) {
+      case 16: k_store(std::integral_constant<int, 16>{}); break;
+      case 8: k_store(std::integral_constant<int, 8>{}); break;
+      case 4: k_store(std::integral_constant<int, 4>{}); break;
+      case 2: k_store(std::integral_constant<int, 2>{}); break;
+      default: k_store(std::integral_constant<int, 1>{}); break;
+    }
+  };
+
+  if constexpr (VEC > 1) {
+    if (transposed) {
+      constexpr int TPI = 32 / VEC;         // tokens per instruction
+      constexpr int G = VEC < 4 ? VEC : 4;  // loads in flight per lane
+      const uint32_t sub = lane / VEC, e = lane % VEC;
+      const Tin* vrow = static_cast<const Tin*>(p.value) + head * p.value_stride_h + d0 + e;
+#pragma unroll
+      for (int i0 = 0; i0 < VEC; i0 += G) {
+        Chunk<ES> raw[G];
+        int64_t dst[G];
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+          const uint32_t owner = (i0 + i) * TPI + sub;
+          dst[i] = __shfl_sync(0xffffffffu, vbase, owner);
+          if (dst[i] >= 0) load_chunk(raw[i], vrow + (tok0 + owner) * p.value_stride_t, false);
+        }
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+          if (dst[i] >= 0) {
+            Chunk<OUT_ES> o;
+            convert_chunk<Tin, KV, 1>(raw[i], o, vs);
+            store_piece<OUT_ES>(vc + (dst[i] + static_cast<int64_t>(e) * bs) * OUT_ES, o, 0);
+          }
+        }
+      }
+      if (!active) return;
+      Chunk<IN_B> kin;
+      load_chunk(kin, ksrc, p.wide_loads);
+      Chunk<OUT_B> kout;
+      convert_chunk<Tin, KV, VEC>(kin, kout, ks);
+      k_write(kout);
+      return;
+    }
+  }
+  if (!active) return;
+
+  Chunk<IN_B> kin, vin;
+  load_chunk(kin, ksrc, p.wide_loads);
+  load_chunk(vin, vsrc, p.wide_loads);
   Chunk<OUT_B> kout, vout;
   convert_chunk<Tin, KV, VEC>(kin, kout, ks);
   convert_chunk<Tin, KV, VEC>(vin, vout, vs);
-
-  const int64_t bh = blk * p.num_heads + head;
-  const int64_t bs = p.block_size;
-  const int x = p.x;
-
-  // K: element d lives at ((bh * (D/x) + d/x) * bs + off) * x + d%x.
-  char* kc = static_cast<char*>(p.key_cache);
-  const int64_t kbase = bh * (p.head_size / x);
-  auto k_store = [&](auto piece_tag) {
-    constexpr int PIECE = decltype(piece_tag)::value;  // bytes per store
-    constexpr int PE = PIECE / OUT_ES;                 // elements per store
-    if constexpr (PE >= 1 && PIECE <= OUT_B) {
-#pragma unroll
-      for (int j = 0; j < VEC; j += PE) {
-        const int d = d0 + j;
-        const int64_t idx = ((kbase + d / x) * bs + off) * x + d % x;
-        store_piece<PIECE>(kc + idx * OUT_ES, kout, j * OUT_ES);
-      }
-    }
-  };
-  switch (p.piece_bytes) {
-    case 16: k_store(std::integral_constant<int, 16>{}); break;
-    case 8: k_store(std::integral_constant<int, 8>{}); break;
-    case 4: k_store(std::integral_constant<int, 4>{}); break;
-    case 2: k_store(std::integral_constant<int, 2>{}); break;
-    default: k_store(std::integral_constant<int, 1>{}); break;
-  }
-
-  // V: element d lives at (bh * D + d) * bs + off.
-  char* vc = static_cast<char*>(p.value_cache);
-  const int64_t vbase = (bh * p.head_size + d0) * bs + off;
+  k_write(kout);
 #pragma unroll
   for (int j = 0; j < VEC; ++j) store_piece<OUT_ES>(vc + (vbase + j * bs) * OUT_ES, vout, j * OUT_ES);
 }
@@ -565,7 +618,6 @@ static int flash_impl(const void* key, const void* value, void* key_cache, void*
   p.linear_slots = (block_stride == block_size * page_stride);
   p.wide_loads = wide;
   p.wide_stores = wide_st;
-  p.prefetch_ctas = prefetch_cta_count();
   p.items_per_token = static_cast<uint32_t>(items_per_token);
   p.chunks_per_row = static_cast<uint32_t>(chunks_per_row);
   p.div_items_per_token = FastDiv(p.items_per_token);
@@ -587,6 +639,7 @@ static int flash_impl(const void* key, const void* value, void* key_cache, void*
     p.slot_mapping = slot_mapping + t0;
     p.n_items = static_cast<uint32_t>(nt * items_per_token);
     const dim3 grid(static_cast<unsigned>((p.n_items + kFlashThreads - 1) / kFlashThreads));
+    p.prefetch_ctas = prefetch_cta_count(grid.x);
     const cudaError_t e = KVC_DISPATCH(in_dtype, kv_dtype, launch_flash_vec, vec, rows == 1, p, grid, st);
     if (e != cudaSuccess)
       return fail(KVC_ERR_CUDA, std::string("reshape_and_cache_flash launch failed: ") + cudaGetErrorString(e));
@@ -643,7 +696,6 @@ static int paged_impl(const void* key, const void* value, void* key_cache, void*
   p.block_size = block_size;
   p.bs_shift = pow2_shift(block_size);
   p.wide_loads = wide;
-  p.prefetch_ctas = prefetch_cta_count();
   p.num_heads = static_cast<int32_t>(num_heads);
   p.head_size = static_cast<int32_t>(head_size);
   p.x = static_cast<int32_t>(x);
@@ -654,6 +706,7 @@ static int paged_impl(const void* key, const void* value, void* key_cache, void*
   p.div_heads = FastDiv(static_cast<uint32_t>(num_heads));
   constexpr int wpb = kPagedThreads / 32;
   const dim3 grid(static_cast<unsigned>((n_warps + wpb - 1) / wpb));
+  p.prefetch_ctas = prefetch_cta_count(grid.x);
   const cudaError_t e = KVC_DISPATCH(in_dtype, kv_dtype, launch_paged_vec, vec, p, grid, st);
   if (e != cudaSuccess)
     return fail(KVC_ERR_CUDA, std::string("reshape_and_cache launch failed: ") + cudaGetErrorString(e));
@@ -723,12 +776,12 @@ static int mla_impl(const void* kv_c, const void* k_pe, void* kv_cache, const in
   p.wide_loads = wide;
   p.wide_stores = wide_st;
   p.linear_slots = (block_stride == block_size * entry_stride);
-  p.prefetch_ctas = prefetch_cta_count();
   p.n_items = static_cast<uint32_t>(pairs * chunks);
   p.chunks_per_token = static_cast<uint32_t>(chunks);
   p.chunks_kv_c = static_cast<uint32_t>(kv_lora_rank / vec);
   p.div_chunks_per_token = FastDiv(p.chunks_per_token);
   const dim3 grid((p.n_items + kMlaThreads - 1) / kMlaThreads);
+  p.prefetch_ctas = prefetch_cta_count(grid.x);
   const cudaError_t e = KVC_DISPATCH(in_dtype, kv_dtype, launch_mla_vec, vec, p, grid, st);
   if (e != cudaSuccess)
     return fail(KVC_ERR_CUDA, std::string("concat_and_cache_mla launch failed: ") + cudaGetErrorString(e));

@@ -1051,6 +1051,13 @@ int decode_ctas_per_sm_d(int head_size, bool wide) {
 }
 
 int decode_slots(int q_dtype, int kv, int head_size, bool wide) {  // CTAs the whole device holds at once
+  // KVC_TEST_DECODE_SLOTS fixes the count, so that the planner can be exercised for a given device size
+  // on a machine without one
+  static const long forced = [] {
+    const char* e = getenv("KVC_TEST_DECODE_SLOTS");
+    return e ? strtol(e, nullptr, 10) : 0L;
+  }();
+  if (forced > 0) return static_cast<int>(forced);
   int per_sm;
   if (q_dtype == KVC_IN_F16) {
     per_sm = kv == KVC_KV_AUTO ? decode_ctas_per_sm_d<__half, KVC_KV_AUTO>(head_size, wide)
@@ -1071,10 +1078,10 @@ int decode_slots(int q_dtype, int kv, int head_size, bool wide) {  // CTAs the w
 // start-up cost of about two tiles), so the launch takes ceil(ctas / slots) rounds of that length; splitting
 // adds the merge launch and its traffic, about three tiles' worth.  Pick the count that minimises the sum,
 // the smaller one on ties.
-int pick_splits(int64_t base, int64_t max_tiles, int64_t slots, int64_t* cost_out) {
+int pick_splits(int64_t base, int64_t max_tiles, int64_t slots, int64_t max_splits, int64_t* cost_out) {
   int best = 1;
   int64_t best_cost = -1;
-  const int64_t limit = max_tiles < kMaxSplits ? max_tiles : kMaxSplits;
+  const int64_t limit = max_tiles < max_splits ? max_tiles : max_splits;
   for (int64_t s = 1; s <= limit; ++s) {
     const int64_t tps = (max_tiles + s - 1) / s;
     const int64_t eff = (max_tiles + tps - 1) / tps;  // splits that are not empty
@@ -1258,7 +1265,8 @@ struct DecodePlan {
 };
 
 DecodePlan plan_decode(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q, int64_t num_heads,
-                       int64_t num_kv_heads, int64_t head_size, int64_t max_seq_len, int q_dtype, int kv_dtype) {
+                       int64_t num_kv_heads, int64_t head_size, int64_t max_seq_len, int q_dtype, int kv_dtype,
+                       int64_t max_splits = kMaxSplits) {
   DecodePlan pl{1, 1, false, 1, 0};
   const int64_t group = num_kv_heads > 0 ? num_heads / num_kv_heads : 1;
   pl.row_tiles = (max_seqlen_q * group + kRows - 1) / kRows;
@@ -1283,7 +1291,7 @@ DecodePlan plan_decode(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q, 
     if (max_tiles < 1) max_tiles = 1;
     int64_t cost = 0;
     const int s = pick_splits(base, max_tiles, decode_slots(q_dtype, kv_dtype, static_cast<int>(head_size), wide != 0),
-                              &cost);
+                              max_splits, &cost);
     cost = wide ? (cost * 3 + 1) / 2 : cost;
     if (best_cost < 0 || cost <= best_cost) {  // ties go to the wide tile: fewer barriers per token
       best_cost = cost;
@@ -1296,10 +1304,57 @@ DecodePlan plan_decode(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q, 
   return pl;
 }
 
+// The launch shape of kvc_paged_attention.  A closed window bounds what a query token can see whatever the
+// sequence length, so the splits then cover the window, not the sequence.  A CTA of the decode kernel walks from
+// its first row's start to its last row's end: window + 1 tokens plus one per further query token it holds (at
+// most kRows), which touch at most floor((length - 2) / tile) + 2 tiles; the planner divides a token count by
+// the tile size rounding up, so the count it gets carries 127 tokens of slack for the larger tile.
+// The workspace is sized by kvc_paged_attention_workspace_bytes, which knows no window: the windowed plan never
+// uses more splits than the plan for the whole sequence, and so never needs more workspace than that query
+// reported (the cost model is not monotone in the tile count, the cap is what guarantees it).
+DecodePlan plan_attention(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q, int64_t num_heads,
+                          int64_t num_kv_heads, int64_t head_size, int64_t max_seq_len, int causal,
+                          int64_t window_left, int64_t window_right, int q_dtype, int kv_dtype) {
+  const DecodePlan whole = plan_decode(num_seqs, total_q, max_seqlen_q, num_heads, num_kv_heads, head_size,
+                                       max_seq_len, q_dtype, kv_dtype);
+  if (!(window_left >= 0 && (causal || window_right >= 0))) return whole;
+  const int64_t spread = (max_seqlen_q < kRows ? max_seqlen_q : kRows) - 1;
+  const int64_t w = window_left + 1 + (causal ? 0 : window_right) + spread + 127;
+  if (w >= max_seq_len) return whole;
+  DecodePlan pl = plan_decode(num_seqs, total_q, max_seqlen_q, num_heads, num_kv_heads, head_size, w, q_dtype, kv_dtype);
+  if (pl.splits > whole.splits)
+    pl = plan_decode(num_seqs, total_q, max_seqlen_q, num_heads, num_kv_heads, head_size, w, q_dtype, kv_dtype,
+                     whole.splits);
+  return pl;
+}
+
 }  // namespace
 }  // namespace kvc
 
 extern "C" {
+
+KVC_API int kvc_paged_attention_plan(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q, int64_t num_heads,
+                                     int64_t num_kv_heads, int64_t head_size, int64_t max_seq_len, int causal,
+                                     int64_t window_left, int64_t window_right, int q_dtype, int kv_dtype,
+                                     int32_t* splits, int32_t* tiles_per_split, int32_t* tile_tokens,
+                                     int64_t* workspace_bytes) {
+  using namespace kvc;
+  if (num_seqs <= 0 || total_q <= 0 || max_seqlen_q <= 0 || num_heads <= 0 || num_kv_heads <= 0 || max_seq_len < 0 ||
+      window_left < -1 || window_right < -1)
+    return fail(KVC_ERR_INVALID_ARG, "paged_attention_plan: sizes must be positive, window sides -1 or >= 0");
+  if (head_size != 64 && head_size != 128 && head_size != 192 && head_size != 256)
+    return fail(KVC_ERR_UNSUPPORTED, "paged_attention_plan: head_size must be 64, 128, 192 or 256");
+  if ((q_dtype != KVC_IN_F16 && q_dtype != KVC_IN_BF16) ||
+      (kv_dtype != KVC_KV_AUTO && kv_dtype != KVC_KV_FP8_E4M3 && kv_dtype != KVC_KV_FP8_E5M2))
+    return fail(KVC_ERR_UNSUPPORTED, "paged_attention_plan: unsupported query or cache type");
+  const DecodePlan pl = plan_attention(num_seqs, total_q, max_seqlen_q, num_heads, num_kv_heads, head_size, max_seq_len,
+                                       causal, window_left, window_right, q_dtype, kv_dtype);
+  if (splits) *splits = pl.splits;
+  if (tiles_per_split) *tiles_per_split = pl.tiles_per_split;
+  if (tile_tokens) *tile_tokens = pl.wide ? 128 : 64;
+  if (workspace_bytes) *workspace_bytes = pl.workspace_bytes;
+  return KVC_OK;
+}
 
 KVC_API int64_t kvc_paged_attention_workspace_bytes(int64_t num_seqs, int64_t total_q, int64_t max_seqlen_q,
                                                     int64_t num_heads, int64_t num_kv_heads, int64_t head_size,
@@ -1363,14 +1418,8 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
                         aligned(cu_seqlens_q, 4);
   if (!ok_align) return fail(KVC_ERR_INVALID_ARG, "paged_attention: query and cache rows must be 16-byte aligned");
 
-  // what a query token can see at most: a closed window bounds it whatever the sequence length
-  int64_t visible = max_seq_len;
-  if (window_left >= 0 && (causal || window_right >= 0)) {
-    const int64_t w = window_left + 1 + (causal ? 0 : window_right) + 127;  // + tile alignment slack
-    if (w < visible) visible = w;
-  }
-  const DecodePlan pl = plan_decode(num_seqs, total_q, max_seqlen_q, num_heads, num_kv_heads, head_size, visible,
-                                    q_dtype, kv_dtype);
+  const DecodePlan pl = plan_attention(num_seqs, total_q, max_seqlen_q, num_heads, num_kv_heads, head_size, max_seq_len,
+                                       causal, window_left, window_right, q_dtype, kv_dtype);
   if (pl.splits > 1 && (!workspace || workspace_bytes < pl.workspace_bytes || !aligned(workspace, 16)))
     return fail(KVC_ERR_INVALID_ARG, "paged_attention: workspace missing, misaligned (16 bytes) or too small; ask "
                                      "kvc_paged_attention_workspace_bytes (" + std::to_string(pl.workspace_bytes) +
@@ -1466,6 +1515,26 @@ KVC_API int kvc_paged_attention_device_status(int* status) {
   if (e != cudaSuccess)
     return fail(KVC_ERR_CUDA, std::string("paged_attention_device_status: ") + cudaGetErrorString(e));
   *status = v;
+  return KVC_OK;
+}
+
+KVC_API int kvc_paged_attention_clear_device_status(void) {
+  using namespace kvc;
+  const int zero = 0;
+  const cudaError_t e = cudaMemcpyToSymbol(g_umma_status, &zero, sizeof(int));  // waits for the device's earlier work
+  if (e != cudaSuccess)
+    return fail(KVC_ERR_CUDA, std::string("paged_attention_clear_device_status: ") + cudaGetErrorString(e));
+  return KVC_OK;
+}
+
+KVC_API int kvc_selftest_bounded_wait_gives_up(int64_t tries, void* stream) {
+  using namespace kvc;
+  if (tries < 1 || tries > 5000)
+    return fail(KVC_ERR_INVALID_ARG, "selftest_bounded_wait_gives_up: tries must be within 1..5000 (about 20 us each)");
+  umma_wait_gives_up_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<uint32_t>(tries));
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(KVC_ERR_CUDA, std::string("selftest_bounded_wait_gives_up launch failed: ") + cudaGetErrorString(e));
   return KVC_OK;
 }
 

@@ -536,5 +536,32 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   if (warp == 0) tmem_dealloc(tmem, kUmmaTmemCols);
 }
 
+// The give-up path of the bounded waits, run on purpose: one CTA allocates tensor memory, waits on an mbarrier
+// that receives no arrival with a limit of `tries` tries (about 20 us each), gives up, frees its tensor
+// memory and raises the status word, exactly as a CTA of the kernel above does when a product or a copy never
+// reports.  Nothing faults and nothing spins without a limit.
+__global__ void __launch_bounds__(128) umma_wait_gives_up_kernel(uint32_t tries) {
+  using namespace umma;
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ uint32_t abort_word;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    mbar_init(&bar, 1);
+    abort_word = 0;
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(&tmem_slot, 32);
+  fence_before_thread_sync();
+  __syncthreads();
+  fence_after_thread_sync();
+  const uint32_t tmem = tmem_slot;
+  const bool completed = mbar_wait_bounded(&bar, 0, &abort_word, tries);
+  if (!completed && (tid & 31) == 0) atomicMax(&g_umma_status, 1);
+  fence_before_thread_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 32);
+}
+
 }  // namespace
 }  // namespace kvc

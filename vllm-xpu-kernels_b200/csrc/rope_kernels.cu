@@ -422,7 +422,6 @@ void fill_rope_params(RopeParams& p, const void* cos_sin_cache, const RopeGeomet
   p.rot_dim = static_cast<int32_t>(g.rot_dim);
   p.embed_dim = static_cast<int32_t>(g.rot_dim / 2);
   p.num_q_heads = static_cast<uint32_t>(g.num_heads);
-  p.prefetch_ctas = prefetch_cta_count();
 }
 
 int64_t launch_item_limit() {
@@ -505,6 +504,7 @@ static int rope_impl(const int64_t* positions, void* query, void* key, const voi
     p.key = key ? static_cast<char*>(key) + t0 * g.key_stride_t * es : nullptr;
     p.n_items = static_cast<uint32_t>(nt * items_per_token);
     const dim3 grid((p.n_items + kRopeThreads - 1) / kRopeThreads);
+    p.prefetch_ctas = prefetch_cta_count(grid.x);
     cudaError_t e;
     if (g.in_dtype == KVC_IN_F32) e = launch_rope_style<float>(g.is_neox, vb, p, grid, st);
     else if (g.in_dtype == KVC_IN_F16) e = launch_rope_style<__half>(g.is_neox, vb, p, grid, st);
@@ -605,6 +605,7 @@ static int rope_cache_impl(const int64_t* positions, void* query, void* key, con
     q.num_slot_tokens = num_slot_tokens - t0;  // may be <= 0: no slots in this launch
     q.r.n_items = static_cast<uint32_t>(nt * items_per_token);
     const dim3 grid((q.r.n_items + kRopeThreads - 1) / kRopeThreads);
+    q.r.prefetch_ctas = prefetch_cta_count(grid.x);
     cudaError_t e;
     if (g.in_dtype == KVC_IN_F32) e = launch_rope_cache_kv<float>(kv_dtype, g.is_neox, vb, q, grid, st);
     else if (g.in_dtype == KVC_IN_F16) e = launch_rope_cache_kv<__half>(kv_dtype, g.is_neox, vb, q, grid, st);

@@ -178,8 +178,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, ui
 // runs to its end on whatever it finds, frees its tensor memory and reports through its status word.
 constexpr uint32_t kMaxTries = 25000;
 constexpr uint32_t kTryNs = 20000;
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile uint32_t* abort) {
-  for (uint32_t i = 0; i < kMaxTries; ++i) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile uint32_t* abort,
+                                                  uint32_t max_tries = kMaxTries) {
+  for (uint32_t i = 0; i < max_tries; ++i) {
     if (mbar_try_wait(bar, parity, kTryNs)) return true;
     if (*abort) return false;
   }

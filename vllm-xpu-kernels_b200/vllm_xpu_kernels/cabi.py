@@ -9,6 +9,7 @@ failing call raises ``RuntimeError`` with the library's message.
 from __future__ import annotations
 
 import ctypes
+import functools
 import os
 
 import torch
@@ -41,6 +42,9 @@ SYMBOLS = (
     "kvc_paged_attention_workspace_bytes",
     "kvc_paged_attention",
     "kvc_paged_attention_device_status",
+    "kvc_paged_attention_plan",
+    "kvc_paged_attention_clear_device_status",
+    "kvc_selftest_bounded_wait_gives_up",
 )
 
 _lib = None
@@ -92,6 +96,13 @@ def lib() -> ctypes.CDLL:
         L.kvc_paged_attention.argtypes = [vp] * 11 + [i64] * 17 + [ctypes.c_float, ci, i64, i64, ci, ci, vp]
         L.kvc_paged_attention_device_status.restype = ci
         L.kvc_paged_attention_device_status.argtypes = [ctypes.POINTER(ci)]
+        L.kvc_paged_attention_plan.restype = ci
+        L.kvc_paged_attention_plan.argtypes = ([i64] * 7 + [ci, i64, i64, ci, ci] + [ctypes.POINTER(ctypes.c_int32)] * 3 +
+                                               [ctypes.POINTER(i64)])
+        L.kvc_paged_attention_clear_device_status.restype = ci
+        L.kvc_paged_attention_clear_device_status.argtypes = []
+        L.kvc_selftest_bounded_wait_gives_up.restype = ci
+        L.kvc_selftest_bounded_wait_gives_up.argtypes = [i64, vp]
         L.kvc_rotary_embedding.restype = ci
         L.kvc_rotary_embedding.argtypes = [vp] * 4 + [i64] * 10 + [ci, ci, vp]
         L.kvc_rotary_embedding_and_cache_flash.restype = ci
@@ -128,12 +139,30 @@ def _stream(stream) -> int:
     return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
 
 
+def _on_tensors_device(fn):
+    """Runs ``fn`` with the device of its first CUDA tensor argument current, as the torch ops do under their
+    device guard: the default stream argument is then that device's current stream, and the entry points that
+    keep per-device state (host staging) pick the right device.  Pointers of one device handed to a launch on
+    another would fault or, with peer access on, silently cross the link."""
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        for a in list(args) + list(kwargs.values()):
+            if isinstance(a, torch.Tensor) and a.is_cuda:
+                if a.device.index != torch.cuda.current_device():
+                    with torch.cuda.device(a.device):
+                        return fn(*args, **kwargs)
+                break
+        return fn(*args, **kwargs)
+    return wrapper
+
+
 def _scale_ptr(s, kv: int) -> int:
     if kv == 0 or s is None:
         return 0
     return s.data_ptr()
 
 
+@_on_tensors_device
 def reshape_and_cache_flash(key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype: str,
                             k_scale=None, v_scale=None, stream=None) -> None:
     """``kvc_reshape_and_cache_flash`` on device tensors (caches [num_blocks, block_size, H, D])."""
@@ -146,6 +175,7 @@ def reshape_and_cache_flash(key, value, key_cache, value_cache, slot_mapping, kv
         _in_dtype(key), kv, _scale_ptr(k_scale, kv), _scale_ptr(v_scale, kv), _stream(stream)))
 
 
+@_on_tensors_device
 def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype: str,
                       k_scale=None, v_scale=None, stream=None) -> None:
     """``kvc_reshape_and_cache`` on device tensors (K [nb,H,D/x,bs,x], V [nb,H,D,bs], contiguous)."""
@@ -158,6 +188,7 @@ def reshape_and_cache(key, value, key_cache, value_cache, slot_mapping, kv_cache
         _in_dtype(key), kv, _scale_ptr(k_scale, kv), _scale_ptr(v_scale, kv), _stream(stream)))
 
 
+@_on_tensors_device
 def concat_and_cache_mla(kv_c, k_pe, kv_cache, slot_mapping, kv_cache_dtype: str, scale=None, stream=None) -> None:
     """``kvc_concat_and_cache_mla`` on device tensors (kv_cache [num_blocks, block_size, R + P])."""
     kv = parse_kv_cache_dtype(kv_cache_dtype)
@@ -167,6 +198,7 @@ def concat_and_cache_mla(kv_c, k_pe, kv_cache, slot_mapping, kv_cache_dtype: str
         kv_cache.stride(0), kv_cache.stride(1), _in_dtype(kv_c), kv, _scale_ptr(scale, kv), _stream(stream)))
 
 
+@_on_tensors_device
 def gather_cache(src_cache, dst, block_table, cu_seq_lens, batch_size: int, seq_starts=None, stream=None) -> None:
     """``kvc_gather_cache`` on device tensors (src_cache [num_blocks, block_size, entry], dst [rows, entry])."""
     entry = 1
@@ -191,6 +223,7 @@ def _host_entry_args(host_key, host_value, host_slot_mapping, kv_cache_dtype: st
     return kv, H, D
 
 
+@_on_tensors_device
 def reshape_and_cache_flash_host(host_key, host_value, key_cache, value_cache, host_slot_mapping,
                                  kv_cache_dtype: str, k_scale=None, v_scale=None, stream=None) -> None:
     """``kvc_reshape_and_cache_flash_host``: key/value/slot_mapping are HOST tensors
@@ -207,6 +240,7 @@ def reshape_and_cache_flash_host(host_key, host_value, key_cache, value_cache, h
 NOALLOC_STAGING_BYTES = 16 * 1024 * 1024  # KVC_NOALLOC_STAGING_BYTES in include/kvcache_b200.h
 
 
+@_on_tensors_device
 def reshape_and_cache_flash_host_noalloc(host_key, host_value, key_cache, value_cache, host_slot_mapping,
                                          kv_cache_dtype: str, k_scale=None, v_scale=None, stream=None) -> None:
     """``kvc_reshape_and_cache_flash_host_noalloc``: like ``reshape_and_cache_flash_host`` but the
@@ -227,6 +261,7 @@ def release_staging() -> None:
     _check(lib().kvc_release_staging())
 
 
+@_on_tensors_device
 def count_bad_slots(slot_mapping, num_slots: int, stream=None) -> int:
     """Number of slots >= num_slots (debug aid; synchronises to read the answer)."""
     out = torch.zeros(1, dtype=torch.int64, device=slot_mapping.device)
@@ -238,18 +273,21 @@ def count_bad_slots(slot_mapping, num_slots: int, stream=None) -> int:
 FP8_CODE = {torch.float8_e4m3fn: 1, torch.float8_e5m2: 2}
 
 
+@_on_tensors_device
 def static_scaled_fp8_quant(out, input, scale, stream=None) -> None:
     """``kvc_static_scaled_fp8_quant``: out (fp8) <- clamp(input * (1/scale)); all contiguous, on the device."""
     _check(lib().kvc_static_scaled_fp8_quant(out.data_ptr(), input.data_ptr(), scale.data_ptr(), input.numel(),
                                              _in_dtype(input), FP8_CODE[out.dtype], _stream(stream)))
 
 
+@_on_tensors_device
 def dynamic_scaled_fp8_quant(out, input, scale, stream=None) -> None:
     """``kvc_dynamic_scaled_fp8_quant``: scale (zero-initialised by the caller) <- absmax / fp8_max, then as static."""
     _check(lib().kvc_dynamic_scaled_fp8_quant(out.data_ptr(), input.data_ptr(), scale.data_ptr(), input.numel(),
                                               _in_dtype(input), FP8_CODE[out.dtype], _stream(stream)))
 
 
+@_on_tensors_device
 def dynamic_per_token_scaled_fp8_quant(out, input, scales, scale_ub=None, stream=None) -> None:
     """``kvc_dynamic_per_token_scaled_fp8_quant`` for input [..., hidden]: one scale per row."""
     hidden = input.shape[-1]
@@ -294,6 +332,7 @@ def _rope_args(positions, query, key, head_size: int, cos_sin_cache):
     return positions.numel(), hq, hk, qst, qsh, kst, ksh
 
 
+@_on_tensors_device
 def rotary_embedding(positions, query, key, head_size: int, cos_sin_cache, is_neox: bool, stream=None) -> None:
     """``kvc_rotary_embedding``: in place on query and key (key may be None)."""
     T, hq, hk, qst, qsh, kst, ksh = _rope_args(positions, query, key, head_size, cos_sin_cache)
@@ -303,6 +342,7 @@ def rotary_embedding(positions, query, key, head_size: int, cos_sin_cache, is_ne
         int(bool(is_neox)), _in_dtype(query), _stream(stream)))
 
 
+@_on_tensors_device
 def rotary_embedding_and_cache_flash(positions, query, key, value, head_size: int, cos_sin_cache, is_neox: bool,
                                      key_cache, value_cache, slot_mapping, kv_cache_dtype: str, k_scale=None,
                                      v_scale=None, write_back_key: bool = True, stream=None) -> None:
@@ -323,6 +363,7 @@ def rotary_embedding_and_cache_flash(positions, query, key, value, head_size: in
         _scale_ptr(v_scale, kv), _stream(stream)))
 
 
+@_on_tensors_device
 def paged_decode_attention(query, key_cache, value_cache, block_table, seq_lens, softmax_scale: float,
                            max_seq_len: int, kv_cache_dtype: str = "auto", k_descale=None, v_descale=None, sink=None,
                            out=None, stream=None):
@@ -345,6 +386,7 @@ def paged_decode_attention(query, key_cache, value_cache, block_table, seq_lens,
     return out
 
 
+@_on_tensors_device
 def paged_attention(query, key_cache, value_cache, block_table, seq_lens, cu_seqlens_q, max_seqlen_q: int,
                     softmax_scale: float, max_seq_len: int, causal: bool = True, kv_cache_dtype: str = "auto",
                     k_descale=None, v_descale=None, sink=None, out=None, stream=None, window=(-1, -1)):
@@ -376,3 +418,29 @@ def paged_attention_device_status() -> int:
     v = ctypes.c_int(0)
     _check(lib().kvc_paged_attention_device_status(ctypes.byref(v)))
     return int(v.value)
+
+
+def paged_attention_clear_device_status() -> None:
+    """``kvc_paged_attention_clear_device_status``: waits for the device and puts the status word back to 0."""
+    _check(lib().kvc_paged_attention_clear_device_status())
+
+
+def paged_attention_plan(num_seqs: int, total_q: int, max_seqlen_q: int, num_heads: int, num_kv_heads: int,
+                         head_size: int, max_seq_len: int, causal: bool = True, window=(-1, -1),
+                         q_dtype: torch.dtype = torch.bfloat16, kv_cache_dtype: str = "auto") -> dict:
+    """``kvc_paged_attention_plan``: the launch shape ``paged_attention`` uses for these arguments."""
+    i32 = ctypes.c_int32
+    splits, tps, tile = i32(0), i32(0), i32(0)
+    ws = ctypes.c_int64(0)
+    _check(lib().kvc_paged_attention_plan(num_seqs, total_q, max_seqlen_q, num_heads, num_kv_heads, head_size,
+                                          max_seq_len, int(bool(causal)), int(window[0]), int(window[1]),
+                                          IN_DTYPE[q_dtype], parse_kv_cache_dtype(kv_cache_dtype), ctypes.byref(splits),
+                                          ctypes.byref(tps), ctypes.byref(tile), ctypes.byref(ws)))
+    return {"splits": splits.value, "tiles_per_split": tps.value, "tile_tokens": tile.value,
+            "workspace_bytes": ws.value}
+
+
+def selftest_bounded_wait_gives_up(tries: int = 50, stream=None) -> None:
+    """``kvc_selftest_bounded_wait_gives_up``: launches the one-CTA kernel whose bounded wait runs out (about
+    20 us per try); afterwards ``paged_attention_device_status()`` is 1 until it is cleared."""
+    _check(lib().kvc_selftest_bounded_wait_gives_up(int(tries), _stream(stream)))

@@ -1,8 +1,9 @@
 """``flash_attn_varlen_func`` with the reference's signature (vllm_xpu_kernels/flash_attn_interface.py:24-125
 there): paged keys/values (``block_table`` + ``seqused_k``) or the non-paged form (``cu_seqlens_k``), causal
-mask, sliding windows, sink -- decode (one query token per sequence) at HBM speed, several query tokens per
-sequence on the same kernel (short runs) or an mma.sync kernel at a fraction of the chip's GEMM rate (long
-ones).  softcap, alibi, dropout and returning the softmax are not supported.  On top of the reference,
+mask, sliding windows, sink -- decode (one query token per sequence) at HBM speed; several query tokens per
+sequence on the same kernel (runs of at most 16 rows per kv head), on a tcgen05 kernel with scores and
+accumulators in tensor memory (head size 128, longer runs) or on an mma.sync kernel (other head sizes).
+softcap, alibi, dropout and returning the softmax are not supported.  On top of the reference,
 the cache may hold fp8 bytes: pass ``k_descale`` / ``v_descale`` (the inverse of the k_scale / v_scale the
 cache was written with), which the reference's interface names but rejects."""
 from typing import Optional
