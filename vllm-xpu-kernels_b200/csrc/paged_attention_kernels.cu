@@ -967,6 +967,7 @@ __global__ void __launch_bounds__(kAttnThreads, (D <= 128 ? 3 : 1)) paged_prefil
 
 // the many-rows kernel on tcgen05 (16-bit cache, head size 128)
 #include "paged_prefill_umma.cuh"
+#include "paged_prefill_pair_umma.cuh"
 
 namespace kvc {
 
@@ -1256,6 +1257,120 @@ cudaError_t launch_prefill_umma_kv(int kv, const DecodeParams& p, dim3 grid, cud
   }
 }
 
+// ---- the paired-tile tcgen05 kernel (16-bit caches, head size 128, power-of-two blocks of at least 8 tokens) ----
+// KVC_PREFILL_PAIR=0 keeps such calls on the one-tile tcgen05 kernel (for comparisons).
+inline bool prefill_pair_enabled() {
+  static const bool off = [] {
+    const char* e = getenv("KVC_PREFILL_PAIR");
+    return e && e[0] == '0';
+  }();
+  return !off;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled of the driver, looked up through the runtime (the library links no driver stub)
+inline EncodeTiledFn tensor_map_encoder() {
+  static const EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+inline bool prefill_uses_pair(int kv_dtype, int64_t head_size, int64_t max_rows_per_kv_head, int64_t block_size) {
+  return prefill_pair_enabled() && prefill_uses_umma(kv_dtype, head_size, max_rows_per_kv_head) &&
+         kv_dtype == KVC_KV_AUTO && head_size == 128 && pow2_shift(block_size) >= 3 && tensor_map_encoder() != nullptr;
+}
+
+// A tensor map over a paged cache [block][token in block][kv head][d] of 16-bit elements (any strides that are
+// multiples of 16 bytes): the box is min(block_size, 128) tokens x one head x 64 elements, stored with the
+// 128-byte swizzle.  The block dimension is given its largest legal extent: block numbers come from the block
+// table, and the map itself knows no allocation size.
+inline bool make_cache_tensor_map(CUtensorMap* map, const void* cache, int q_dtype, const DecodeParams& p) {
+  const cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(p.num_kv_heads), static_cast<cuuint64_t>(p.block_size),
+                              1ull << 31};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(p.head_stride) * 2, static_cast<cuuint64_t>(p.page_stride) * 2,
+                                 static_cast<cuuint64_t>(p.block_stride) * 2};
+  const cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(p.block_size < kPairTile ? p.block_size : kPairTile), 1};
+  const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+  const CUresult r = tensor_map_encoder()(
+      map, q_dtype == KVC_IN_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+      const_cast<void*>(cache), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// A tensor map over the query or the output [token][head][d]: the box is one row tile in its token-major row
+// order, 128 / group tokens x group heads x 64 elements.  Tokens past the tensor's end read as zeros and are not
+// written.
+inline bool make_query_tensor_map(CUtensorMap* map, const void* base, int64_t stride_t, int64_t stride_h, int q_dtype,
+                                  const DecodeParams& p, int64_t total_q) {
+  const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(p.num_heads), static_cast<cuuint64_t>(total_q)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(stride_h) * 2, static_cast<cuuint64_t>(stride_t) * 2};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(p.group), static_cast<cuuint32_t>(kPairRows / p.group)};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = tensor_map_encoder()(
+      map, q_dtype == KVC_IN_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+      const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <typename TQ>
+cudaError_t launch_prefill_pair(const DecodeParams& p, int q_dtype, int64_t total_q, int64_t num_seqs, cudaStream_t st) {
+  static std::once_flag once[64];
+  static cudaError_t attr_err[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  static int sm_count[64];
+  std::call_once(once[dev], [&] {
+    attr_err[dev] = cudaFuncSetAttribute(paged_prefill_pair_kernel<TQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         PairCfg::kSmemBytes);
+    if (attr_err[dev] == cudaSuccess)
+      attr_err[dev] = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+  });
+  if (attr_err[dev] != cudaSuccess) return attr_err[dev];
+  // One CTA per SM walks the work items (pairs of row tiles of a sequence and kv head, heaviest first) with a
+  // stride of the grid: tensor memory is allocated once per CTA and the items' fixed costs are paid back to back
+  // instead of once per CTA launch.
+  const int64_t items = static_cast<int64_t>(p.row_tiles) * p.num_kv_heads * num_seqs;
+  if (items <= 0 || items > 0x7FFFFFFFll) return cudaErrorInvalidValue;
+  const dim3 grid(static_cast<unsigned>(items < sm_count[dev] ? items : sm_count[dev]));
+  CUtensorMap map_k, map_v, map_q, map_o;
+  if (!make_cache_tensor_map(&map_k, p.key_cache, q_dtype, p) || !make_cache_tensor_map(&map_v, p.value_cache, q_dtype, p))
+    return cudaErrorInvalidValue;
+  // the query rows come by TMA where a row tile is a box: power-of-two groups of at most 128 heads
+  int q_by_tma = ((p.group & (p.group - 1)) == 0 && p.group <= kPairRows) ? 1 : 0;
+  int o_by_tma = q_by_tma && aligned(p.out, 16) && (p.out_stride_t * 2) % 16 == 0 && (p.out_stride_h * 2) % 16 == 0;
+  if (q_by_tma && !make_query_tensor_map(&map_q, p.query, p.query_stride_t, p.query_stride_h, q_dtype, p, total_q))
+    q_by_tma = 0;
+  if (o_by_tma && !make_query_tensor_map(&map_o, p.out, p.out_stride_t, p.out_stride_h, q_dtype, p, total_q))
+    o_by_tma = 0;
+  if (!q_by_tma) map_q = map_k;  // not read
+  if (!o_by_tma) map_o = map_k;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kPairThreads);
+  cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, paged_prefill_pair_kernel<TQ>, p, map_k, map_v, map_q, map_o, q_by_tma, o_by_tma,
+                            static_cast<int>(num_seqs), static_cast<int>(items));
+}
+
 struct DecodePlan {
   int splits;
   int tiles_per_split;
@@ -1473,12 +1588,20 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
   if (max_seqlen_q * p.group > kRows) {  // sequences with more than 16 query rows per kv head
     DecodeParams pp = p;
     const bool use_umma = prefill_uses_umma(kv_dtype, head_size, max_seqlen_q * p.group);
-    const int64_t tile_rows = use_umma ? kUmmaRows : kPrefillRows;
+    const bool use_pair = use_umma && prefill_uses_pair(kv_dtype, head_size, max_seqlen_q * p.group, block_size);
+    const int64_t tile_rows = use_pair ? 2 * kPairRows : use_umma ? kUmmaRows : kPrefillRows;
     pp.row_tiles = static_cast<int32_t>((max_seqlen_q * p.group + tile_rows - 1) / tile_rows);
     const int64_t px = static_cast<int64_t>(pp.num_kv_heads) * pp.row_tiles;
     if (px > 0x7FFFFFFFll) return fail(KVC_ERR_INVALID_ARG, "paged_attention: too many query rows per sequence");
     const dim3 pgrid(static_cast<unsigned>(px), static_cast<unsigned>(num_seqs), 1);
-    if (use_umma)
+    static const bool debug_dispatch = getenv("KVC_DEBUG_DISPATCH") != nullptr;
+    if (debug_dispatch)
+      fprintf(stderr, "kvc: many-rows attention on the %s kernel, grid %u x %u\n",
+              use_pair ? "paired-tile tcgen05" : use_umma ? "one-tile tcgen05" : "mma.sync", pgrid.x, pgrid.y);
+    if (use_pair)
+      e = (q_dtype == KVC_IN_F16) ? launch_prefill_pair<__half>(pp, q_dtype, total_q, num_seqs, st)
+                                  : launch_prefill_pair<__nv_bfloat16>(pp, q_dtype, total_q, num_seqs, st);
+    else if (use_umma)
       e = (q_dtype == KVC_IN_F16) ? launch_prefill_umma_kv<__half>(kv_dtype, pp, pgrid, st)
                                   : launch_prefill_umma_kv<__nv_bfloat16>(kv_dtype, pp, pgrid, st);
     else

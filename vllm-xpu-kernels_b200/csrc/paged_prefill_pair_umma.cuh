@@ -1,0 +1,664 @@
+// The many-rows attention kernel for 16-bit caches, head size 128, on the fifth-generation tensor cores.
+// One CTA per SM walks work items -- a pair of row tiles of 128 query rows each (token-major (token, head) pairs
+// of one kv head of one sequence) that share every key/value tile -- in tiles of 128 cached tokens, and is
+// specialised by warp:
+//
+//   warps 0-3   softmax of row tile A: thread r owns row r -- all 128 scores of a tile, the row's running
+//   warps 4-7   maximum and sum, its accumulator row (same for row tile B).  No value ever crosses threads.
+//   warp 8      issues the matrix products (tcgen05.mma, M = 128, N = 128, K = 16, fp32 accumulation in
+//               tensor memory): S = Q K^T with both operands in shared memory, O += P V with P read from tensor
+//               memory and V as an MN-major operand.
+//   warp 9      brings query, key and value tiles in with TMA tile copies (cp.async.bulk.tensor, 128-byte
+//               swizzle, no multicast, this GPU's memory only).  Keys and values come straight from the paged
+//               cache: a tensor map over [block][token in block][kv head][d] makes a cache block's rows one box,
+//               the block table gives the block coordinate, one lane issues one box.
+//   warps 10-11 idle (they complete the third warpgroup, whose registers go to the softmax threads).
+//
+// Tensor memory (512 columns, all of the SM's): O_A | O_B | X | P_A | P_B with 128, 128, 128, 64, 64 columns.
+// X holds the scores of whichever row tile's turn it is: a softmax thread moves its row of X into registers
+// at once (128 of the 224 registers it owns) and reports X free, so the issuing warp computes the other row
+// tile's scores, and then this row tile's NEXT scores, while this softmax is still running.  A row tile's chain
+// of dependent steps is thus its softmax alone; the tensor pipe alternates
+//
+//   S_A(j+1)  PV_A(j)  S_B(j+1)  PV_B(j)  S_A(j+2)  PV_A(j+1) ...
+//
+// each product batch (8 instructions) gated by one arrival of the softmax threads: X read (for an S batch) or P
+// stored (for a PV batch).  The probabilities have columns of their own, which PV(j) has finished reading before
+// the softmax of tile j + 1 stores into them (the wait for "O += P(j) V(j) complete" that a rescaling of O
+// needs anyway).
+//
+// A softmax thread costs about 3.5 instructions per score (one tcgen05.ld of 32 columns per 32 scores, packed
+// fp32 arithmetic, 3-input max, one ex2 per score, 16-bit packing); every fixed per-tile cost is spread over 128
+// scores per thread.
+//
+// Work items are numbered heaviest first and dealt to the CTAs in a serpentine; a CTA allocates tensor memory
+// once and re-arms its barriers per item.  Where the group size is a power of two a row tile is one box of the
+// query tensor and of the output tensor [token][head][d]: queries arrive by TMA, and a full row tile of results
+// leaves by TMA from the (then idle) query buffer; other group sizes and cut-off tiles take ordinary loads and
+// stores.
+//
+// Rows past a sequence's end inside the last tile: their keys may be anything (the scores are masked before
+// use), their values are zeroed in shared memory by the issuing warp before the product that reads them, so
+// that a probability of exactly zero cannot meet a NaN.
+//
+// Every wait on an mbarrier is bounded; a wait that gives up sets the CTA's abort word, the CTA runs to its
+// end, waits (bounded) for its copies in flight, frees its tensor memory and raises g_umma_status.
+#pragma once
+
+#include <cuda.h>
+
+#include "paged_prefill_umma.cuh"
+
+namespace kvc {
+namespace {
+
+constexpr int kPairRows = 128;     // rows of one row tile
+constexpr int kPairTile = 128;     // cached tokens per tile
+constexpr int kPairThreads = 384;  // three warpgroups: softmax A, softmax B, and {issuing warp, copy warp, two idle warps}
+// Registers: 384 threads leave 168 per thread; the third warpgroup gives most of its share to the softmax
+// threads, which hold a row's 128 scores at once (setmaxnreg, per warpgroup: 2 x 128 x 224 + 128 x 56 = 64512).
+constexpr int kPairSoftmaxRegs = 224;
+constexpr int kPairOtherRegs = 56;
+constexpr uint32_t kPairTmemCols = 512;
+constexpr uint32_t kColO = 0;    // O_A, O_B: 128 columns each
+constexpr uint32_t kColX = 256;  // the scores of the row tile whose turn it is: 128 columns
+constexpr uint32_t kColP = 384;  // P_A, P_B: 64 columns each (two 16-bit probabilities per column)
+
+struct PairCfg {
+  static constexpr int D = 128;
+  static constexpr int kHalfBytes = 128 * 128;       // 128 rows x 64 sixteen-bit elements: 16 KB
+  static constexpr int kTileBytes = 2 * kHalfBytes;  // a Q row tile, a K tile or a V tile: 32 KB
+  static constexpr int kOffQ = 0;                    // [row tile]
+  static constexpr int kOffK = 2 * kTileBytes;       // [stage]
+  static constexpr int kOffV = 4 * kTileBytes;       // [stage]
+  static constexpr int kOffBar = 6 * kTileBytes;     // 16 mbarriers, tensor-memory slot, abort word
+  static constexpr int kBarriers = 16;
+  static constexpr int kSmemBytes = kOffBar + kBarriers * 8 + 16;  // + tensor-memory slot and abort word
+  static_assert(kSmemBytes + 1024 <= 232448, "fits one SM");
+  static_assert(2 * (kSmemBytes + 1024) > 233472, "one CTA per SM: it allocates all of the SM's tensor memory");
+};
+
+// one box of a tiled 4-d tensor map -> shared memory of this CTA; completion is counted in bytes on `bar`
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(umma::smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(umma::smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// one box of shared memory -> a tiled 3-d tensor map (rows outside the tensor are not written); asynchronous,
+// tracked by the issuing thread's bulk group
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit_and_wait_read() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(umma::smem_addr(bar)), "r"(bytes) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void warpgroup_take_registers() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void warpgroup_give_registers() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// explicit shared-space accesses (a generic pointer would go through the slower generic path)
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+// A wait that ignores the abort word (used only to let copies in flight land before the CTA ends): at most
+// `tries` tries of about 20 us.
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, uint32_t tries) {
+  for (uint32_t i = 0; i < tries; ++i)
+    if (umma::mbar_try_wait(bar, parity, umma::kTryNs)) return true;
+  return false;
+}
+
+// The item a CTA takes in round `round`: items are numbered heaviest first and the CTAs walk them in a
+// serpentine -- forwards in even rounds, backwards in odd ones -- so that the CTA that got the heaviest item of
+// one round gets the lightest of the next and all CTAs end up with nearly the same amount of work.
+__device__ __forceinline__ int pair_item_of(int round, int num_items) {
+  const int g = static_cast<int>(gridDim.x), c = static_cast<int>(blockIdx.x);
+  (void)num_items;
+  return round * g + ((round & 1) ? g - 1 - c : c);
+}
+
+// What one work item is: the pair of row tiles `pair` of (sequence, kv head), its rows and the range of
+// key/value tiles it walks.
+struct PairItem {
+  int seq, kvh, row0;     // row0: first row of row tile A within the (sequence, kv head)
+  int q_start, q_len, n;  // first query token, query tokens and cached tokens of the sequence
+  int rows_all;           // rows of both tiles: A is full before B has any
+  int tile_begin, nt;     // first tile and number of tiles
+  bool has_b;
+};
+
+template <typename TQ>
+__global__ void __launch_bounds__(kPairThreads, 1)
+    paged_prefill_pair_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tmap_k,
+                              const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_q,
+                              const __grid_constant__ CUtensorMap tmap_o, const int q_by_tma, const int o_by_tma,
+                              const int num_seqs, const int num_items) {
+  using Cfg = PairCfg;
+  using namespace umma;
+  constexpr int D = Cfg::D, TN = kPairTile;
+
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* s_q = smem + Cfg::kOffQ;
+  unsigned char* s_k = smem + Cfg::kOffK;
+  unsigned char* s_v = smem + Cfg::kOffV;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
+  uint64_t* bar_s = bars;          // [row tile]  S(j) of the row tile is complete
+  uint64_t* bar_ready = bars + 2;  // [row tile]  its 128 softmax threads have stored P(j)
+  uint64_t* bar_o = bars + 4;      // [row tile]  O += P(j) V(j) is complete
+  uint64_t* bar_kfull = bars + 6;  // [stage]     the K tile has landed
+  uint64_t* bar_vfull = bars + 8;
+  uint64_t* bar_kfree = bars + 10;  // [stage]    every product that reads the K tile is complete
+  uint64_t* bar_vfree = bars + 12;
+  uint64_t* bar_xfree = bars + 14;  // the score columns have been read into registers (128 arrivals per use)
+  uint64_t* bar_qfull = bars + 15;  // the query rows have landed (when they come by TMA)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kBarriers);
+  volatile uint32_t* abort_word = tmem_slot + 1;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 9 * 32) {  // the tensor maps are kernel parameters: fetching them does not depend on the predecessor
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_k)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_v)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_q)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_o)) : "memory");
+  }
+  pdl_prologue();
+
+  if (smem_addr(smem) & 1023u) {  // the operand tiles' swizzle assumes 1024-byte alignment
+    if (tid == 0) atomicMax(&g_umma_status, 2);
+    return;
+  }
+  if (tid == 0) *abort_word = 0;
+  if (warp == 0) tmem_alloc(tmem_slot, kPairTmemCols);
+  fence_before_thread_sync();
+  __syncthreads();
+  fence_after_thread_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  // rows are token-major: row R of the kv head is token R / group, head R % group of the group
+  const int g_shift = (p.group & (p.group - 1)) == 0 ? __ffs(p.group) - 1 : -1;
+  auto row_token = [&](int R) {
+    if (g_shift >= 0) return R >> g_shift;
+    return R / p.group;
+  };
+  auto row_head = [&](const PairItem& w, int R) {
+    if (g_shift >= 0) return w.kvh * p.group + (R & (p.group - 1));
+    return w.kvh * p.group + R % p.group;
+  };
+  auto row_limit = [&](const PairItem& w, int R) {
+    const int pos = w.n - w.q_len + row_token(R);
+    int hi = w.n;
+    if (p.causal) hi = min(hi, pos + 1);
+    if (p.window_right >= 0) hi = min(hi, pos + p.window_right + 1);
+    return max(0, hi);
+  };
+  auto row_lo = [&](const PairItem& w, int R) {
+    return p.window_left >= 0 ? max(0, w.n - w.q_len + row_token(R) - p.window_left) : 0;
+  };
+
+  // ---- one work item's set-up, run by all threads: what it covers, results of rows that see nothing, and the
+  // barriers, which start every item in phase 0 (the previous item ended with a barrier of the whole CTA, all of
+  // its products, copies and arrivals complete).  Returns false when the item has no work for the matrix
+  // products.  Items are numbered heaviest first: the last pair of row tiles of every sequence and kv head, then
+  // the pair before it, and so on.
+  auto setup = [&](int item, PairItem& w) -> bool {
+    const int per_pair = num_seqs * p.num_kv_heads;
+    const int pair = p.row_tiles - 1 - item / per_pair;
+    const int rem = item - (item / per_pair) * per_pair;
+    w.seq = rem / p.num_kv_heads;
+    w.kvh = rem - w.seq * p.num_kv_heads;
+    w.row0 = pair * 2 * kPairRows;
+    w.q_start = p.cu_seqlens_q ? p.cu_seqlens_q[w.seq] : w.seq;
+    w.q_len = p.cu_seqlens_q ? p.cu_seqlens_q[w.seq + 1] - w.q_start : 1;
+    const int seq_rows = w.q_len * p.group;
+    if (seq_rows <= kRows || w.row0 >= seq_rows) return false;  // the decode kernel's sequence, or no rows here
+    w.rows_all = min(2 * kPairRows, seq_rows - w.row0);
+    w.has_b = w.rows_all > kPairRows;
+    w.n = p.seq_lens[w.seq];
+    // both ends grow with the row: the CTA walks from its first row's start to its last row's end
+    const int tile_end = (row_limit(w, w.row0 + w.rows_all - 1) + TN - 1) / TN;
+    w.tile_begin = row_lo(w, w.row0) / TN;
+    w.nt = tile_end - w.tile_begin;
+    if (w.nt <= 0) {  // no row sees any token
+      for (int i = tid; i < w.rows_all * D; i += kPairThreads) {
+        const int R = w.row0 + i / D;
+        static_cast<TQ*>(p.out)[static_cast<int64_t>(w.q_start + row_token(R)) * p.out_stride_t +
+                                row_head(w, R) * p.out_stride_h + i % D] = TQ(0.0f);
+      }
+      return false;
+    }
+    if (tid == 0) {
+      mbar_init(bar_s, 1);
+      mbar_init(bar_s + 1, 1);
+      mbar_init(bar_ready, kPairRows);
+      mbar_init(bar_ready + 1, kPairRows);
+      mbar_init(bar_o, 1);
+      mbar_init(bar_o + 1, 1);
+      for (int i = 0; i < 8; ++i) mbar_init(bar_kfull + i, 1);  // kfull, vfull, kfree, vfree
+      mbar_init(bar_xfree, kPairRows);
+      mbar_init(bar_qfull, 1);
+      mbar_init_fence();
+    }
+    __syncthreads();
+    return true;
+  };
+  // ---- and its end: every role is done with shared memory, tensor memory and the barriers
+  auto finish = [&]() {
+    fence_before_thread_sync();
+    __syncthreads();
+    fence_after_thread_sync();
+    if (tid == 0) {
+      for (int i = 0; i < Cfg::kBarriers; ++i) mbar_inval(bars + i);
+    }
+  };
+
+  if (warp >= 8) {
+    warpgroup_give_registers<kPairOtherRegs>();
+    PairItem w;
+    for (int round = 0; round * static_cast<int>(gridDim.x) < num_items; ++round) {
+      const int item = pair_item_of(round, num_items);
+      if (item >= num_items || !setup(item, w)) continue;
+      if (!q_by_tma && warp == 8) named_bar_sync(1, 9 * 32);  // the softmax warps have gathered the query rows
+      if (warp == 9) {
+        // ====================================================================================== copy warp
+        if (q_by_tma) {
+          // A row tile is a box of the query tensor [token][head][d] -- 128 / group tokens x group heads x 64
+          // elements, rows in exactly the token-major order of the tile (rows past the tensor's end arrive as
+          // zeros, rows of a following sequence are computed and never stored).
+          const int tokens_per_tile = kPairRows >> g_shift;  // 128 / group
+          if (lane == 0) mbar_arrive_expect_tx(bar_qfull, 2u * Cfg::kTileBytes);
+          __syncwarp();
+          if (lane < 4)  // row tile lane / 2, half lane % 2
+            tma_load_3d(smem_addr(s_q) + (lane >> 1) * Cfg::kTileBytes + (lane & 1) * Cfg::kHalfBytes, &tmap_q,
+                        bar_qfull, (lane & 1) * 64, w.kvh * p.group,
+                        w.q_start + (w.row0 >> g_shift) + (lane >> 1) * tokens_per_tile);
+        }
+        // A tile is 128 tokens: one box of 128 rows when a cache block holds at least 128 tokens, else 128 / bs
+        // boxes of bs rows; every box exists twice, once per 64-element half of the head dimension.  Lane l
+        // issues box l / 2, half l % 2.  Blocks that start at or beyond the sequence's end are not fetched.
+        const int32_t* table = p.block_table + w.seq * p.block_table_stride;
+        const int box_rows = min(p.block_size, TN);
+        const int ops = (TN / box_rows) * 2;
+        const uint32_t box_bytes = static_cast<uint32_t>(box_rows) * 128u;
+        const int b = lane >> 1, half = lane & 1;
+        auto load_tile = [&](int tile, const CUtensorMap* map, unsigned char* slot, uint64_t* full) {
+          const int token0 = tile * TN + b * box_rows;
+          const bool valid = lane < ops && token0 < w.n;
+          const unsigned mask = __ballot_sync(0xFFFFFFFFu, valid);
+          if (lane == 0) mbar_arrive_expect_tx(full, static_cast<uint32_t>(__popc(mask)) * box_bytes);
+          __syncwarp();
+          if (valid) {
+            const int32_t blk = __ldg(table + (token0 >> p.bs_shift));
+            tma_load_4d(smem_addr(slot) + half * Cfg::kHalfBytes + b * box_bytes, map, full, half * 64, w.kvh,
+                        token0 & (p.block_size - 1), blk);
+          }
+        };
+        for (int j = 0; j < w.nt; ++j) {
+          const int s = j & 1;
+          const uint32_t prev_use = static_cast<uint32_t>((j >> 1) - 1) & 1u;
+          if (j >= 2) mbar_wait_bounded(bar_kfree + s, prev_use, abort_word);
+          load_tile(w.tile_begin + j, &tmap_k, s_k + s * Cfg::kTileBytes, bar_kfull + s);
+          if (j >= 2) mbar_wait_bounded(bar_vfree + s, prev_use, abort_word);
+          load_tile(w.tile_begin + j, &tmap_v, s_v + s * Cfg::kTileBytes, bar_vfull + s);
+        }
+        if (*abort_word) {  // something gave up: let the copies that are still in flight land before going on
+          if (q_by_tma) mbar_wait_limited(bar_qfull, 0, 1000);
+          for (int j = max(0, w.nt - 2); j < w.nt; ++j) {
+            mbar_wait_limited(bar_kfull + (j & 1), (j >> 1) & 1, 1000);
+            mbar_wait_limited(bar_vfull + (j & 1), (j >> 1) & 1, 1000);
+          }
+        }
+      } else if (warp == 8) {
+        // ====================================================================================== issuing warp
+        constexpr uint32_t kIdescQK = instr_desc_f16<TQ>(kPairRows, TN, false, false);
+        constexpr uint32_t kIdescPV = instr_desc_f16<TQ>(kPairRows, D, false, true);
+        constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
+        constexpr uint32_t kLboK = (16u >> 4) << 16;                          // K-major operands: unused
+        constexpr uint32_t kLboV = (static_cast<uint32_t>(Cfg::kHalfBytes) >> 4) << 16;  // V: distance of the D halves
+        auto make_desc = [](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
+        const uint32_t q_lo = (smem_addr(s_q) >> 4) | kLboK;
+        const uint32_t k_lo0 = (smem_addr(s_k) >> 4) | kLboK;
+        const uint32_t v_lo0 = (smem_addr(s_v) >> 4) | kLboV;
+        auto issue_qk = [&](int g, int j) {  // X = Q_g K(j)^T
+          const uint32_t qa = q_lo + g * (Cfg::kTileBytes >> 4);
+          const uint32_t kb = k_lo0 + (j & 1) * (Cfg::kTileBytes >> 4);
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t step = ((kk >> 2) * Cfg::kHalfBytes + (kk & 3) * 32) >> 4;
+            mma_f16_ss(tmem + kColX, make_desc(qa + step), make_desc(kb + step), kIdescQK, kk > 0 ? 1u : 0u);
+          }
+        };
+        auto issue_pv = [&](int g, int j) {  // O_g (+)= P_g(j) V(j): P_g is 64 columns of two 16-bit values
+          const uint32_t vb = v_lo0 + (j & 1) * (Cfg::kTileBytes >> 4);
+#pragma unroll
+          for (int kk = 0; kk < TN / 16; ++kk)
+            mma_f16_ts(tmem + kColO + g * 128, tmem + kColP + g * 64 + kk * 8, make_desc(vb + ((kk * 16 * 128) >> 4)),
+                       kIdescPV, (j > 0 || kk > 0) ? 1u : 0u);
+        };
+        // Uses of the score columns X are numbered in issue order: with both row tiles use 2j is S_A(j) and use
+        // 2j + 1 is S_B(j); a use may be issued once the threads of the use before it have read their scores
+        // (phase use - 1 of bar_xfree).  S_g(j + 1) is thereby computed while the softmax of S_g(j) is still
+        // running, and a row tile's chain of dependent steps is its softmax alone.
+        const int groups = w.has_b ? 2 : 1;
+        auto wait_x = [&](int use) { mbar_wait_bounded(bar_xfree, static_cast<uint32_t>(use - 1) & 1u, abort_word); };
+        if (q_by_tma) mbar_wait_bounded(bar_qfull, 0, abort_word);
+        mbar_wait_bounded(bar_kfull, 0, abort_word);
+        fence_after_thread_sync();
+        if (lane == 0) {
+          issue_qk(0, 0);
+          mma_commit(bar_s);
+          if (!w.has_b) mma_commit(bar_kfree);
+        }
+        __syncwarp();
+        if (w.has_b) {
+          wait_x(1);
+          fence_after_thread_sync();
+          if (lane == 0) {
+            issue_qk(1, 0);
+            mma_commit(bar_s + 1);
+            mma_commit(bar_kfree);
+          }
+          __syncwarp();
+        }
+        for (int j = 0; j < w.nt; ++j) {
+          const int s = j & 1;
+          for (int g = 0; g < groups; ++g) {
+            // S_g(j + 1): as soon as the other row tile (or, alone, this one) has taken its scores out of X
+            if (j + 1 < w.nt) {
+              if (g == 0) mbar_wait_bounded(bar_kfull + ((j + 1) & 1), ((j + 1) >> 1) & 1, abort_word);
+              wait_x(groups * (j + 1) + g);
+              fence_after_thread_sync();
+              if (lane == 0) {
+                issue_qk(g, j + 1);
+                mma_commit(bar_s + g);
+                if (g == groups - 1) mma_commit(bar_kfree + ((j + 1) & 1));
+              }
+              __syncwarp();
+            }
+            // O_g += P_g(j) V(j)
+            if (g == 0) {
+              mbar_wait_bounded(bar_vfull + s, (j >> 1) & 1, abort_word);
+              const int valid_rows = w.n - (w.tile_begin + j) * TN;  // rows of the tile that hold tokens of the sequence
+              if (valid_rows < TN) {
+                unsigned char* v = s_v + s * Cfg::kTileBytes;
+                const int first = max(valid_rows, 0);
+                for (int i = lane; i < (TN - first) * 16; i += 32) {  // 8 chunks per row and half
+                  const int r = first + (i >> 4), c = i & 15;
+                  *reinterpret_cast<uint4*>(v + (c >> 3) * Cfg::kHalfBytes + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+                }
+                fence_smem_to_async_proxy();
+                __syncwarp();
+              }
+            }
+            mbar_wait_bounded(bar_ready + g, j & 1, abort_word);
+            fence_after_thread_sync();
+            if (lane == 0) {
+              issue_pv(g, j);
+              mma_commit(bar_o + g);
+              if (g == groups - 1) mma_commit(bar_vfree + s);
+            }
+            __syncwarp();
+          }
+        }
+      }
+      finish();
+    }
+  } else {
+    warpgroup_take_registers<kPairSoftmaxRegs>();
+    PairItem w;
+    for (int round = 0; round * static_cast<int>(gridDim.x) < num_items; ++round) {
+      const int item = pair_item_of(round, num_items);
+      if (item >= num_items || !setup(item, w)) continue;
+      if (!q_by_tma) {
+        // Odd group sizes: the softmax warps gather the query rows of both row tiles (zero rows past the end).
+        // All of a thread's loads are issued before its first store, so that the rows are fetched at memory
+        // latency once, not once per 16-byte piece.
+        constexpr int kQThreads = 256, kPerThread = 2 * kPairRows * (D / 8) / kQThreads;  // 16 pieces of 16 bytes
+        uint4 piece[kPerThread];
+#pragma unroll
+        for (int i = 0; i < kPerThread; ++i) {
+          const int c = tid + i * kQThreads;
+          const int r = c / (D / 8), col = c % (D / 8);  // r: row of the pair, 0..255
+          piece[i] = make_uint4(0, 0, 0, 0);
+          if (r < w.rows_all) {
+            const int R = w.row0 + r;
+            piece[i] = *reinterpret_cast<const uint4*>(static_cast<const TQ*>(p.query) +
+                                                       static_cast<int64_t>(w.q_start + row_token(R)) * p.query_stride_t +
+                                                       row_head(w, R) * p.query_stride_h + col * 8);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < kPerThread; ++i) {
+          const int c = tid + i * kQThreads;
+          const int r = c / (D / 8), col = c % (D / 8);
+          *reinterpret_cast<uint4*>(s_q + (r >> 7) * Cfg::kTileBytes + (col >> 3) * Cfg::kHalfBytes +
+                                    swizzled_offset(r & 127, col & 7)) = piece[i];
+        }
+        fence_smem_to_async_proxy();
+        named_bar_sync(1, 9 * 32);  // with the issuing warp, which reads Q through the async proxy after this
+      }
+      if (warp < 4 || w.has_b) {
+        // ====================================================================================== softmax warps
+        const int g = warp >> 2;  // row tile
+        const int r = tid & 127;  // row of the tile = tensor-memory lane
+        const int rows_g = g == 0 ? min(w.rows_all, kPairRows) : w.rows_all - kPairRows;
+        const int Rg0 = w.row0 + g * kPairRows;
+        const bool live = r < rows_g;
+        const int lim = live ? row_limit(w, Rg0 + r) : 0;
+        const int lo = live ? row_lo(w, Rg0 + r) : 0;
+        const int lim_min = row_limit(w, Rg0);
+        const int lo_max = row_lo(w, Rg0 + rows_g - 1);
+        const float scale2 = p.softmax_scale * kLog2e;
+        const float lazy_margin = 8.0f / scale2;
+        const uint32_t t_lanes = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);  // this warp's 32 lanes
+        const uint32_t t_x = t_lanes + kColX, t_p = t_lanes + kColP + g * 64, t_o = t_lanes + kColO + g * 128;
+        float m_run = -INFINITY, l_run = 0.f;
+
+        for (int it = 0; it < w.nt; ++it) {
+          const int tile = w.tile_begin + it;
+          mbar_wait_bounded(bar_s + g, it & 1, abort_word);
+          fence_after_thread_sync();
+          uint32_t sa[4][32];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_x + c * 32, sa[c]);
+          tmem_ld_wait();
+          fence_before_thread_sync();
+          mbar_arrive(bar_xfree);  // the scores are in registers: the other row tile's next product may have X
+          if ((tile + 1) * TN > lim_min || tile * TN < lo_max) {  // some row of the tile has tokens to mask here
+            const int tok0 = tile * TN;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (tok0 + c * 32 + i >= lim || tok0 + c * 32 + i < lo) sa[c][i] = 0xFF800000u;  // -inf
+          }
+          float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; i += 2)
+              mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sa[c][i]), __uint_as_float(sa[c][i + 1]));
+          const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+          // the reference point of the exponentials follows the maximum lazily: it moves only when a score exceeds
+          // it by more than 2^8 after scaling, so probabilities stay below 256 and O is rescaled a few times per row
+          const bool move = mx > m_run + lazy_margin;
+          const float alpha = move ? fast_exp2((m_run - mx) * scale2) : 1.0f;
+          m_run = move ? mx : m_run;
+          const float neg_ms = (m_run == -INFINITY) ? 0.f : -m_run * scale2;
+          l_run *= alpha;
+          if (it > 0) {  // O += P(it - 1) V(it - 1) is complete: O is at rest and P's columns may be overwritten
+            mbar_wait_bounded(bar_o + g, (it - 1) & 1, abort_word);
+            fence_after_thread_sync();
+          }
+          if (it > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // rare: a reference maximum of the warp moved
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld_32x32(t_o + c * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st_32x32(t_o + c * 32, o);
+            }
+          }
+          // 64 scores become 32 words of two 16-bit probabilities, stored as soon as they are complete
+          const float2 sc2 = make_float2(scale2, scale2), nm2 = make_float2(neg_ms, neg_ms);
+          float2 l_add[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t wd[32];
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const int c = 2 * h + cc;
+                const float2 e = __ffma2_rn(make_float2(__uint_as_float(sa[c][i]), __uint_as_float(sa[c][i + 1])), sc2, nm2);
+                const float2 pr = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+                l_add[(i >> 1) & 3] = __fadd2_rn(l_add[(i >> 1) & 3], pr);
+                wd[cc * 16 + (i >> 1)] = pack2<TQ>(pr.x, pr.y);
+              }
+            tmem_st_32x32(t_p + h * 32, wd);
+          }
+          l_run += ((l_add[0].x + l_add[0].y) + (l_add[1].x + l_add[1].y)) +
+                   ((l_add[2].x + l_add[2].y) + (l_add[3].x + l_add[3].y));
+          tmem_st_wait();
+          fence_before_thread_sync();
+          mbar_arrive(bar_ready + g);
+        }
+        const bool finished = mbar_wait_bounded(bar_o + g, (w.nt - 1) & 1, abort_word);
+        fence_after_thread_sync();
+        if (!finished && lane == 0) atomicMax(&g_umma_status, 1);
+
+        // ---- the row's result -------------------------------------------------------------------------------
+        const int R = Rg0 + r;
+        const int head = live ? row_head(w, R) : 0;
+        const float m = m_run * scale2;  // log2 domain; -inf if the row saw nothing
+        float l = l_run, rescale = 1.0f;
+        if (p.sink && live) {
+          const float sk = static_cast<float>(static_cast<const TQ*>(p.sink)[head]) * kLog2e;
+          const float mf = fmaxf(m, sk);
+          rescale = (m == -INFINITY) ? 0.f : exp2f(m - mf);
+          l = l * rescale + exp2f(sk - mf);
+        }
+        const float f = (l > 0.f) ? rescale / l : 0.f;
+        // The row goes to global memory through the row tile's query buffer (its last reader, S(nt - 1), is
+        // complete).  A full row tile is one box of the output tensor, as it was of the query tensor: every thread
+        // stages its row in that layout and one thread hands the tile to the TMA unit (two stores, one per
+        // 64-element half), which writes it while the CTA goes on.  A tile that the sequence's end cuts short (a
+        // box would reach into the next sequence's rows), odd group sizes and unaligned outputs take the second
+        // path: each thread stages its own 256-byte row, 16-byte pieces swizzled against bank conflicts, and the
+        // warp writes its 32 rows two at a time, 512 contiguous bytes per instruction where consecutive heads of
+        // a token are adjacent.
+        if (o_by_tma && rows_g == kPairRows) {  // uniform over the row tile's 128 threads
+          const uint32_t tile = smem_addr(s_q) + g * Cfg::kTileBytes;
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t acc[32];
+            tmem_ld_32x32(t_o + c * 32, acc);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 v;
+              v.x = pack2<TQ>(__uint_as_float(acc[8 * i]) * f, __uint_as_float(acc[8 * i + 1]) * f);
+              v.y = pack2<TQ>(__uint_as_float(acc[8 * i + 2]) * f, __uint_as_float(acc[8 * i + 3]) * f);
+              v.z = pack2<TQ>(__uint_as_float(acc[8 * i + 4]) * f, __uint_as_float(acc[8 * i + 5]) * f);
+              v.w = pack2<TQ>(__uint_as_float(acc[8 * i + 6]) * f, __uint_as_float(acc[8 * i + 7]) * f);
+              const int chunk = c * 4 + i;  // 16-byte chunk of the row: half chunk / 8
+              st_shared_v4(tile + (chunk >> 3) * Cfg::kHalfBytes + swizzled_offset(r, chunk & 7), v);
+            }
+          }
+          fence_smem_to_async_proxy();
+          named_bar_sync(2 + g, kPairRows);
+          if (r == 0) {
+            const int tok0 = w.q_start + (Rg0 >> g_shift);
+            tma_store_3d(&tmap_o, tile, 0, w.kvh * p.group, tok0);
+            tma_store_3d(&tmap_o, tile + Cfg::kHalfBytes, 64, w.kvh * p.group, tok0);
+            tma_store_commit_and_wait_read();  // shared memory has been read; the writes complete on their own
+          }
+        } else {
+          const uint32_t stage = smem_addr(s_q) + g * Cfg::kTileBytes + (warp & 3) * 32 * 256;  // this warp's 32 rows
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t acc[32];
+            tmem_ld_32x32(t_o + c * 32, acc);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 v;
+              v.x = pack2<TQ>(__uint_as_float(acc[8 * i]) * f, __uint_as_float(acc[8 * i + 1]) * f);
+              v.y = pack2<TQ>(__uint_as_float(acc[8 * i + 2]) * f, __uint_as_float(acc[8 * i + 3]) * f);
+              v.z = pack2<TQ>(__uint_as_float(acc[8 * i + 4]) * f, __uint_as_float(acc[8 * i + 5]) * f);
+              v.w = pack2<TQ>(__uint_as_float(acc[8 * i + 6]) * f, __uint_as_float(acc[8 * i + 7]) * f);
+              st_shared_v4(stage + lane * 256 + (((c * 4 + i) ^ (lane & 15)) << 4), v);
+            }
+          }
+          __syncwarp();
+          const bool vec16 = ((reinterpret_cast<uintptr_t>(p.out) | static_cast<uintptr_t>(p.out_stride_t * 2) |
+                               static_cast<uintptr_t>(p.out_stride_h * 2)) & 15u) == 0;
+          // (token, head) of the lane's first row once, then two rows further per step: no division in the loop
+          const int piece = lane & 15;  // 16-byte piece of the row
+          int rr = lane >> 4;           // row of the warp
+          int tok_r = row_token(Rg0 + (warp & 3) * 32 + rr);
+          int head_r = Rg0 + (warp & 3) * 32 + rr - tok_r * p.group;  // head within the group
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i, rr += 2) {
+            if ((warp & 3) * 32 + rr < rows_g) {
+              const uint4 v = ld_shared_v4(stage + rr * 256 + ((piece ^ (rr & 15)) << 4));
+              TQ* dst = static_cast<TQ*>(p.out) + static_cast<int64_t>(w.q_start + tok_r) * p.out_stride_t +
+                        static_cast<int64_t>(w.kvh * p.group + head_r) * p.out_stride_h + piece * 8;
+              if (vec16) {
+                *reinterpret_cast<uint4*>(dst) = v;
+              } else {
+                uint32_t* d32 = reinterpret_cast<uint32_t*>(dst);
+                d32[0] = v.x;
+                d32[1] = v.y;
+                d32[2] = v.z;
+                d32[3] = v.w;
+              }
+            }
+            head_r += 2;
+            while (head_r >= p.group) {
+              head_r -= p.group;
+              ++tok_r;
+            }
+          }
+        }
+      }
+      finish();
+    }
+    // the output tiles this thread handed to the TMA unit have been written
+    if ((tid & 127) == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+  fence_before_thread_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kPairTmemCols);
+}
+
+}  // namespace
+}  // namespace kvc

@@ -152,6 +152,9 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
 }
+__device__ __forceinline__ void mbar_inval(uint64_t* bar) {
+  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
 __device__ __forceinline__ void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
@@ -171,6 +174,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, ui
       : "memory");
   return done != 0;
 }
+// Non-blocking test: has the phase with the given parity completed?  (A few cycles, where a try_wait costs about
+// two hundred even when the phase is already complete.)
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
 // Waits until the phase with the given parity has completed, for at most kMaxTries tries of about 20 us each:
 // half a second in all, where a tile of work takes microseconds, so that a context that is switched out for a
 // while on a shared GPU does not trip it.  Returns false when it gave up or when *abort is already set, and sets
@@ -180,6 +198,7 @@ constexpr uint32_t kMaxTries = 25000;
 constexpr uint32_t kTryNs = 20000;
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile uint32_t* abort,
                                                   uint32_t max_tries = kMaxTries) {
+  if (mbar_test_wait(bar, parity)) return true;  // the common case: what is waited for happened long ago
   for (uint32_t i = 0; i < max_tries; ++i) {
     if (mbar_try_wait(bar, parity, kTryNs)) return true;
     if (*abort) return false;
