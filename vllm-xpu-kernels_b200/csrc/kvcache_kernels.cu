@@ -156,12 +156,11 @@ constexpr int kPagedThreads = 256;
 // 32 lines per instruction.  A warp that finds fewer than half of its tokens adjacent to their
 // successor therefore writes V in the transposed order: an instruction covers 32 / VEC tokens x VEC
 // consecutive d, i.e. per token one run of VEC sectors (bs elements apart in the cache, VEC * 32
-// bytes for 16-bit caches with 16-slot blocks), four sectors to a line.  The elements are fetched in
-// that order as well (a half-warp reads one 32-byte piece of a row), so no exchange between lanes is
-// needed beyond the owner lane's destination offset.  K is written by the owner lane either way:
-// its x-element groups are separate lines in both orders.
+// bytes for 16-bit caches with 16-slot blocks), four sectors to a line.  The elements still arrive by
+// one wide load per lane (lane = token) and change hands through a 1 KB tile of shared memory per warp.
+// K is written by the owner lane either way: its x-element groups are separate lines in both orders.
 template <typename Tin, int KV, int VEC>
-__global__ void __launch_bounds__(kPagedThreads, 4) paged_scatter_kernel(const PagedParams p) {
+__global__ void __launch_bounds__(kPagedThreads, 5) paged_scatter_kernel(const PagedParams p) {
   constexpr int ES = (int)sizeof(Tin);
   constexpr int IN_B = VEC * ES;
   constexpr int OUT_ES = (KV == KVC_KV_AUTO) ? ES : 1;
@@ -237,27 +236,28 @@ __global__ void __launch_bounds__(kPagedThreads, 4) paged_scatter_kernel(const P
 
   if constexpr (VEC > 1) {
     if (transposed) {
-      constexpr int TPI = 32 / VEC;         // tokens per instruction
-      constexpr int G = VEC < 4 ? VEC : 4;  // loads in flight per lane
+      // Each lane fetches its own token's VEC elements with one wide load (the memory-level parallelism of the
+      // other order), the warp's 32 x VEC tile goes through shared memory, and every store instruction then
+      // covers 32 / VEC tokens x VEC consecutive d.
+      constexpr int TPI = 32 / VEC;  // tokens per instruction
+      __shared__ __align__(16) unsigned char v_tile[kPagedThreads / 32][32 * IN_B];
+      unsigned char* tile = v_tile[threadIdx.x >> 5];
+      if (active) {
+        Chunk<IN_B> vin;
+        load_chunk(vin, vsrc, p.wide_loads);
+        *reinterpret_cast<Chunk<IN_B>*>(tile + lane * IN_B) = vin;
+      }
+      __syncwarp();
       const uint32_t sub = lane / VEC, e = lane % VEC;
-      const Tin* vrow = static_cast<const Tin*>(p.value) + head * p.value_stride_h + d0 + e;
 #pragma unroll
-      for (int i0 = 0; i0 < VEC; i0 += G) {
-        Chunk<ES> raw[G];
-        int64_t dst[G];
-#pragma unroll
-        for (int i = 0; i < G; ++i) {
-          const uint32_t owner = (i0 + i) * TPI + sub;
-          dst[i] = __shfl_sync(0xffffffffu, vbase, owner);
-          if (dst[i] >= 0) load_chunk(raw[i], vrow + (tok0 + owner) * p.value_stride_t, false);
-        }
-#pragma unroll
-        for (int i = 0; i < G; ++i) {
-          if (dst[i] >= 0) {
-            Chunk<OUT_ES> o;
-            convert_chunk<Tin, KV, 1>(raw[i], o, vs);
-            store_piece<OUT_ES>(vc + (dst[i] + static_cast<int64_t>(e) * bs) * OUT_ES, o, 0);
-          }
+      for (int i = 0; i < VEC; ++i) {
+        const uint32_t owner = i * TPI + sub;
+        const int64_t dst = __shfl_sync(0xffffffffu, vbase, owner);
+        if (dst >= 0) {
+          const Chunk<ES> raw = *reinterpret_cast<const Chunk<ES>*>(tile + owner * IN_B + e * ES);
+          Chunk<OUT_ES> o;
+          convert_chunk<Tin, KV, 1>(raw, o, vs);
+          store_piece<OUT_ES>(vc + (dst + static_cast<int64_t>(e) * bs) * OUT_ES, o, 0);
         }
       }
       if (!active) return;

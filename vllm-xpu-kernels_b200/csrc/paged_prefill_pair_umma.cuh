@@ -71,8 +71,9 @@ struct PairCfg {
   static constexpr int kOffQ = 0;                    // [row tile]
   static constexpr int kOffK = 2 * kTileBytes;       // [stage]
   static constexpr int kOffV = 4 * kTileBytes;       // [stage]
-  static constexpr int kOffBar = 6 * kTileBytes;     // 16 mbarriers, tensor-memory slot, abort word
-  static constexpr int kBarriers = 16;
+  static constexpr int kOffStage = 6 * kTileBytes;   // one row tile of results on its way out
+  static constexpr int kOffBar = 7 * kTileBytes;     // mbarriers, tensor-memory slot, abort word
+  static constexpr int kBarriers = 18;
   static constexpr int kSmemBytes = kOffBar + kBarriers * 8 + 16;  // + tensor-memory slot and abort word
   static_assert(kSmemBytes + 1024 <= 232448, "fits one SM");
   static_assert(2 * (kSmemBytes + 1024) > 233472, "one CTA per SM: it allocates all of the SM's tensor memory");
@@ -167,6 +168,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   unsigned char* s_q = smem + Cfg::kOffQ;
   unsigned char* s_k = smem + Cfg::kOffK;
   unsigned char* s_v = smem + Cfg::kOffV;
+  unsigned char* s_stage = smem + Cfg::kOffStage;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBar);
   uint64_t* bar_s = bars;          // [row tile]  S(j) of the row tile is complete
   uint64_t* bar_ready = bars + 2;  // [row tile]  its 128 softmax threads have stored P(j)
@@ -177,6 +179,8 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   uint64_t* bar_vfree = bars + 12;
   uint64_t* bar_xfree = bars + 14;  // the score columns have been read into registers (128 arrivals per use)
   uint64_t* bar_qfull = bars + 15;  // the query rows have landed (when they come by TMA)
+  uint64_t* bar_qfree = bars + 16;  // every product that reads the item's query rows is complete
+  uint64_t* bar_stage = bars + 17;  // the staging tile has been read by the TMA unit (or written out by its warps)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kBarriers);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
@@ -194,7 +198,21 @@ __global__ void __launch_bounds__(kPairThreads, 1)
     if (tid == 0) atomicMax(&g_umma_status, 2);
     return;
   }
-  if (tid == 0) *abort_word = 0;
+  if (tid == 0) {
+    *abort_word = 0;
+    mbar_init(bar_s, 1);
+    mbar_init(bar_s + 1, 1);
+    mbar_init(bar_ready, kPairRows);
+    mbar_init(bar_ready + 1, kPairRows);
+    mbar_init(bar_o, 1);
+    mbar_init(bar_o + 1, 1);
+    for (int i = 0; i < 8; ++i) mbar_init(bar_kfull + i, 1);  // kfull, vfull, kfree, vfree
+    mbar_init(bar_xfree, kPairRows);
+    mbar_init(bar_qfull, 1);
+    mbar_init(bar_qfree, 1);
+    mbar_init(bar_stage, 1);
+    mbar_init_fence();
+  }
   if (warp == 0) tmem_alloc(tmem_slot, kPairTmemCols);
   fence_before_thread_sync();
   __syncthreads();
@@ -222,68 +240,71 @@ __global__ void __launch_bounds__(kPairThreads, 1)
     return p.window_left >= 0 ? max(0, w.n - w.q_len + row_token(R) - p.window_left) : 0;
   };
 
-  // ---- one work item's set-up, run by all threads: what it covers, results of rows that see nothing, and the
-  // barriers, which start every item in phase 0 (the previous item ended with a barrier of the whole CTA, all of
-  // its products, copies and arrivals complete).  Returns false when the item has no work for the matrix
-  // products.  Items are numbered heaviest first: the last pair of row tiles of every sequence and kv head, then
-  // the pair before it, and so on.
-  auto setup = [&](int item, PairItem& w) -> bool {
-    const int per_pair = num_seqs * p.num_kv_heads;
+  // ---- what a work item covers; false when it has no work for the matrix products (each role decides this by
+  // itself, from the same numbers).  Items are numbered heaviest first: the last pair of row tiles of every
+  // sequence and kv head, then the pair before it, and so on.
+  // The three numbers of an item's sequence are fetched one item ahead (`fetch` at the top of the item before),
+  // so that their latency is not paid between two items.
+  struct SeqNumbers {
+    int q_start, q_end, n;
+  };
+  const int per_pair = num_seqs * p.num_kv_heads;
+  auto fetch = [&](int item) -> SeqNumbers {
+    SeqNumbers f{0, 0, 0};
+    if (item < num_items) {
+      const int seq = (item % per_pair) / p.num_kv_heads;
+      f.q_start = p.cu_seqlens_q ? __ldg(p.cu_seqlens_q + seq) : seq;
+      f.q_end = p.cu_seqlens_q ? __ldg(p.cu_seqlens_q + seq + 1) : seq + 1;
+      f.n = __ldg(p.seq_lens + seq);
+    }
+    return f;
+  };
+  auto setup = [&](int item, const SeqNumbers& f, PairItem& w) -> bool {
     const int pair = p.row_tiles - 1 - item / per_pair;
     const int rem = item - (item / per_pair) * per_pair;
     w.seq = rem / p.num_kv_heads;
     w.kvh = rem - w.seq * p.num_kv_heads;
     w.row0 = pair * 2 * kPairRows;
-    w.q_start = p.cu_seqlens_q ? p.cu_seqlens_q[w.seq] : w.seq;
-    w.q_len = p.cu_seqlens_q ? p.cu_seqlens_q[w.seq + 1] - w.q_start : 1;
+    w.q_start = f.q_start;
+    w.q_len = f.q_end - f.q_start;
+    w.nt = 0;
+    w.rows_all = 0;
     const int seq_rows = w.q_len * p.group;
     if (seq_rows <= kRows || w.row0 >= seq_rows) return false;  // the decode kernel's sequence, or no rows here
     w.rows_all = min(2 * kPairRows, seq_rows - w.row0);
     w.has_b = w.rows_all > kPairRows;
-    w.n = p.seq_lens[w.seq];
+    w.n = f.n;
     // both ends grow with the row: the CTA walks from its first row's start to its last row's end
     const int tile_end = (row_limit(w, w.row0 + w.rows_all - 1) + TN - 1) / TN;
     w.tile_begin = row_lo(w, w.row0) / TN;
     w.nt = tile_end - w.tile_begin;
-    if (w.nt <= 0) {  // no row sees any token
-      for (int i = tid; i < w.rows_all * D; i += kPairThreads) {
-        const int R = w.row0 + i / D;
-        static_cast<TQ*>(p.out)[static_cast<int64_t>(w.q_start + row_token(R)) * p.out_stride_t +
-                                row_head(w, R) * p.out_stride_h + i % D] = TQ(0.0f);
-      }
-      return false;
-    }
-    if (tid == 0) {
-      mbar_init(bar_s, 1);
-      mbar_init(bar_s + 1, 1);
-      mbar_init(bar_ready, kPairRows);
-      mbar_init(bar_ready + 1, kPairRows);
-      mbar_init(bar_o, 1);
-      mbar_init(bar_o + 1, 1);
-      for (int i = 0; i < 8; ++i) mbar_init(bar_kfull + i, 1);  // kfull, vfull, kfree, vfree
-      mbar_init(bar_xfree, kPairRows);
-      mbar_init(bar_qfull, 1);
-      mbar_init_fence();
-    }
-    __syncthreads();
-    return true;
+    return w.nt > 0;
   };
-  // ---- and its end: every role is done with shared memory, tensor memory and the barriers
-  auto finish = [&]() {
-    fence_before_thread_sync();
-    __syncthreads();
-    fence_after_thread_sync();
-    if (tid == 0) {
-      for (int i = 0; i < Cfg::kBarriers; ++i) mbar_inval(bars + i);
-    }
+  // The barriers run on across items: tile `it` of an item is phase (tiles of the role's earlier items + it) of
+  // the per-tile barriers, and so on.  The roles never meet between items, so the copy warp and the issuing warp
+  // start on the next item while the softmax threads still write the last one's results.
+  int tiles_done = 0;    // tiles of earlier items (row tile A takes part in every item)
+  int tiles_done_b = 0;  // ... of earlier items that had a row tile B
+  int uses_done = 0;     // uses of the score columns X by earlier items
+  int items_done = 0;    // earlier items with work
+  int stages_done = 0;   // uses of the staging tile by earlier items (one per row tile)
+  auto account = [&](const PairItem& w) {
+    stages_done += w.has_b ? 2 : 1;
+    tiles_done += w.nt;
+    if (w.has_b) tiles_done_b += w.nt;
+    uses_done += (w.has_b ? 2 : 1) * w.nt;
+    ++items_done;
   };
 
   if (warp >= 8) {
     warpgroup_give_registers<kPairOtherRegs>();
     PairItem w;
+    SeqNumbers next = fetch(pair_item_of(0, num_items));
     for (int round = 0; round * static_cast<int>(gridDim.x) < num_items; ++round) {
       const int item = pair_item_of(round, num_items);
-      if (item >= num_items || !setup(item, w)) continue;
+      const SeqNumbers cur = next;
+      next = fetch(pair_item_of(round + 1, num_items));
+      if (item >= num_items || !setup(item, cur, w)) continue;
       if (!q_by_tma && warp == 8) named_bar_sync(1, 9 * 32);  // the softmax warps have gathered the query rows
       if (warp == 9) {
         // ====================================================================================== copy warp
@@ -292,6 +313,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           // elements, rows in exactly the token-major order of the tile (rows past the tensor's end arrive as
           // zeros, rows of a following sequence are computed and never stored).
           const int tokens_per_tile = kPairRows >> g_shift;  // 128 / group
+          if (items_done > 0) mbar_wait_bounded(bar_qfree, static_cast<uint32_t>(items_done - 1) & 1u, abort_word);
           if (lane == 0) mbar_arrive_expect_tx(bar_qfull, 2u * Cfg::kTileBytes);
           __syncwarp();
           if (lane < 4)  // row tile lane / 2, half lane % 2
@@ -320,18 +342,20 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           }
         };
         for (int j = 0; j < w.nt; ++j) {
-          const int s = j & 1;
-          const uint32_t prev_use = static_cast<uint32_t>((j >> 1) - 1) & 1u;
-          if (j >= 2) mbar_wait_bounded(bar_kfree + s, prev_use, abort_word);
+          const int kt = tiles_done + j;  // the CTA's kt-th tile: stage kt & 1, that stage's use kt >> 1
+          const int s = kt & 1;
+          const uint32_t prev_use = static_cast<uint32_t>((kt >> 1) - 1) & 1u;
+          if (kt >= 2) mbar_wait_bounded(bar_kfree + s, prev_use, abort_word);
           load_tile(w.tile_begin + j, &tmap_k, s_k + s * Cfg::kTileBytes, bar_kfull + s);
-          if (j >= 2) mbar_wait_bounded(bar_vfree + s, prev_use, abort_word);
+          if (kt >= 2) mbar_wait_bounded(bar_vfree + s, prev_use, abort_word);
           load_tile(w.tile_begin + j, &tmap_v, s_v + s * Cfg::kTileBytes, bar_vfull + s);
         }
         if (*abort_word) {  // something gave up: let the copies that are still in flight land before going on
-          if (q_by_tma) mbar_wait_limited(bar_qfull, 0, 1000);
+          if (q_by_tma) mbar_wait_limited(bar_qfull, static_cast<uint32_t>(items_done) & 1u, 1000);
           for (int j = max(0, w.nt - 2); j < w.nt; ++j) {
-            mbar_wait_limited(bar_kfull + (j & 1), (j >> 1) & 1, 1000);
-            mbar_wait_limited(bar_vfull + (j & 1), (j >> 1) & 1, 1000);
+            const int kt = tiles_done + j;
+            mbar_wait_limited(bar_kfull + (kt & 1), (kt >> 1) & 1, 1000);
+            mbar_wait_limited(bar_vfull + (kt & 1), (kt >> 1) & 1, 1000);
           }
         }
       } else if (warp == 8) {
@@ -347,7 +371,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         const uint32_t v_lo0 = (smem_addr(s_v) >> 4) | kLboV;
         auto issue_qk = [&](int g, int j) {  // X = Q_g K(j)^T
           const uint32_t qa = q_lo + g * (Cfg::kTileBytes >> 4);
-          const uint32_t kb = k_lo0 + (j & 1) * (Cfg::kTileBytes >> 4);
+          const uint32_t kb = k_lo0 + ((tiles_done + j) & 1) * (Cfg::kTileBytes >> 4);
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint32_t step = ((kk >> 2) * Cfg::kHalfBytes + (kk & 3) * 32) >> 4;
@@ -355,7 +379,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           }
         };
         auto issue_pv = [&](int g, int j) {  // O_g (+)= P_g(j) V(j): P_g is 64 columns of two 16-bit values
-          const uint32_t vb = v_lo0 + (j & 1) * (Cfg::kTileBytes >> 4);
+          const uint32_t vb = v_lo0 + ((tiles_done + j) & 1) * (Cfg::kTileBytes >> 4);
 #pragma unroll
           for (int kk = 0; kk < TN / 16; ++kk)
             mma_f16_ts(tmem + kColO + g * 128, tmem + kColP + g * 64 + kk * 8, make_desc(vb + ((kk * 16 * 128) >> 4)),
@@ -366,14 +390,26 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         // (phase use - 1 of bar_xfree).  S_g(j + 1) is thereby computed while the softmax of S_g(j) is still
         // running, and a row tile's chain of dependent steps is its softmax alone.
         const int groups = w.has_b ? 2 : 1;
-        auto wait_x = [&](int use) { mbar_wait_bounded(bar_xfree, static_cast<uint32_t>(use - 1) & 1u, abort_word); };
-        if (q_by_tma) mbar_wait_bounded(bar_qfull, 0, abort_word);
-        mbar_wait_bounded(bar_kfull, 0, abort_word);
+        // local use u of this item is the CTA's use uses_done + u
+        auto wait_x = [&](int use) {
+          const int gu = uses_done + use;
+          if (gu > 0) mbar_wait_bounded(bar_xfree, static_cast<uint32_t>(gu - 1) & 1u, abort_word);
+        };
+        auto kfull_of = [&](int j) { return bar_kfull + ((tiles_done + j) & 1); };
+        auto kfree_of = [&](int j) { return bar_kfree + ((tiles_done + j) & 1); };
+        auto stage_parity = [&](int j) { return static_cast<uint32_t>((tiles_done + j) >> 1) & 1u; };
+        const bool last_s_in_prologue = w.nt == 1;  // a one-tile item: its only S batches are the first ones
+        if (q_by_tma) mbar_wait_bounded(bar_qfull, static_cast<uint32_t>(items_done) & 1u, abort_word);
+        mbar_wait_bounded(kfull_of(0), stage_parity(0), abort_word);
+        wait_x(0);
         fence_after_thread_sync();
         if (lane == 0) {
           issue_qk(0, 0);
           mma_commit(bar_s);
-          if (!w.has_b) mma_commit(bar_kfree);
+          if (!w.has_b) {
+            mma_commit(kfree_of(0));
+            if (last_s_in_prologue) mma_commit(bar_qfree);
+          }
         }
         __syncwarp();
         if (w.has_b) {
@@ -382,28 +418,32 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           if (lane == 0) {
             issue_qk(1, 0);
             mma_commit(bar_s + 1);
-            mma_commit(bar_kfree);
+            mma_commit(kfree_of(0));
+            if (last_s_in_prologue) mma_commit(bar_qfree);
           }
           __syncwarp();
         }
         for (int j = 0; j < w.nt; ++j) {
-          const int s = j & 1;
+          const int s = (tiles_done + j) & 1;
           for (int g = 0; g < groups; ++g) {
             // S_g(j + 1): as soon as the other row tile (or, alone, this one) has taken its scores out of X
             if (j + 1 < w.nt) {
-              if (g == 0) mbar_wait_bounded(bar_kfull + ((j + 1) & 1), ((j + 1) >> 1) & 1, abort_word);
+              if (g == 0) mbar_wait_bounded(kfull_of(j + 1), stage_parity(j + 1), abort_word);
               wait_x(groups * (j + 1) + g);
               fence_after_thread_sync();
               if (lane == 0) {
                 issue_qk(g, j + 1);
                 mma_commit(bar_s + g);
-                if (g == groups - 1) mma_commit(bar_kfree + ((j + 1) & 1));
+                if (g == groups - 1) {
+                  mma_commit(kfree_of(j + 1));
+                  if (j + 2 == w.nt) mma_commit(bar_qfree);  // the item's last S batch: its query rows are done with
+                }
               }
               __syncwarp();
             }
             // O_g += P_g(j) V(j)
             if (g == 0) {
-              mbar_wait_bounded(bar_vfull + s, (j >> 1) & 1, abort_word);
+              mbar_wait_bounded(bar_vfull + s, stage_parity(j), abort_word);
               const int valid_rows = w.n - (w.tile_begin + j) * TN;  // rows of the tile that hold tokens of the sequence
               if (valid_rows < TN) {
                 unsigned char* v = s_v + s * Cfg::kTileBytes;
@@ -416,7 +456,8 @@ __global__ void __launch_bounds__(kPairThreads, 1)
                 __syncwarp();
               }
             }
-            mbar_wait_bounded(bar_ready + g, j & 1, abort_word);
+            mbar_wait_bounded(bar_ready + g, static_cast<uint32_t>((g == 0 ? tiles_done : tiles_done_b) + j) & 1u,
+                              abort_word);
             fence_after_thread_sync();
             if (lane == 0) {
               issue_pv(g, j);
@@ -427,19 +468,32 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           }
         }
       }
-      finish();
+      account(w);
     }
   } else {
     warpgroup_take_registers<kPairSoftmaxRegs>();
     PairItem w;
+    SeqNumbers next = fetch(pair_item_of(0, num_items));
     for (int round = 0; round * static_cast<int>(gridDim.x) < num_items; ++round) {
       const int item = pair_item_of(round, num_items);
-      if (item >= num_items || !setup(item, w)) continue;
+      const SeqNumbers cur = next;
+      next = fetch(pair_item_of(round + 1, num_items));
+      if (item >= num_items) continue;
+      if (!setup(item, cur, w)) {
+        // rows that see no token at all (a window that ends before the cache begins): zeros
+        for (int i = tid; i < w.rows_all * D; i += 8 * 32) {
+          const int R = w.row0 + i / D;
+          static_cast<TQ*>(p.out)[static_cast<int64_t>(w.q_start + row_token(R)) * p.out_stride_t +
+                                  row_head(w, R) * p.out_stride_h + i % D] = TQ(0.0f);
+        }
+        continue;
+      }
       if (!q_by_tma) {
         // Odd group sizes: the softmax warps gather the query rows of both row tiles (zero rows past the end).
         // All of a thread's loads are issued before its first store, so that the rows are fetched at memory
         // latency once, not once per 16-byte piece.
         constexpr int kQThreads = 256, kPerThread = 2 * kPairRows * (D / 8) / kQThreads;  // 16 pieces of 16 bytes
+        if (items_done > 0) mbar_wait_bounded(bar_qfree, static_cast<uint32_t>(items_done - 1) & 1u, abort_word);
         uint4 piece[kPerThread];
 #pragma unroll
         for (int i = 0; i < kPerThread; ++i) {
@@ -479,10 +533,11 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         const uint32_t t_lanes = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);  // this warp's 32 lanes
         const uint32_t t_x = t_lanes + kColX, t_p = t_lanes + kColP + g * 64, t_o = t_lanes + kColO + g * 128;
         float m_run = -INFINITY, l_run = 0.f;
+        const int phase0 = g == 0 ? tiles_done : tiles_done_b;  // this row tile's earlier tiles
 
         for (int it = 0; it < w.nt; ++it) {
           const int tile = w.tile_begin + it;
-          mbar_wait_bounded(bar_s + g, it & 1, abort_word);
+          mbar_wait_bounded(bar_s + g, static_cast<uint32_t>(phase0 + it) & 1u, abort_word);
           fence_after_thread_sync();
           uint32_t sa[4][32];
 #pragma unroll
@@ -513,7 +568,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           const float neg_ms = (m_run == -INFINITY) ? 0.f : -m_run * scale2;
           l_run *= alpha;
           if (it > 0) {  // O += P(it - 1) V(it - 1) is complete: O is at rest and P's columns may be overwritten
-            mbar_wait_bounded(bar_o + g, (it - 1) & 1, abort_word);
+            mbar_wait_bounded(bar_o + g, static_cast<uint32_t>(phase0 + it - 1) & 1u, abort_word);
             fence_after_thread_sync();
           }
           if (it > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // rare: a reference maximum of the warp moved
@@ -551,7 +606,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           fence_before_thread_sync();
           mbar_arrive(bar_ready + g);
         }
-        const bool finished = mbar_wait_bounded(bar_o + g, (w.nt - 1) & 1, abort_word);
+        const bool finished = mbar_wait_bounded(bar_o + g, static_cast<uint32_t>(phase0 + w.nt - 1) & 1u, abort_word);
         fence_after_thread_sync();
         if (!finished && lane == 0) atomicMax(&g_umma_status, 1);
 
@@ -567,16 +622,18 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           l = l * rescale + exp2f(sk - mf);
         }
         const float f = (l > 0.f) ? rescale / l : 0.f;
-        // The row goes to global memory through the row tile's query buffer (its last reader, S(nt - 1), is
-        // complete).  A full row tile is one box of the output tensor, as it was of the query tensor: every thread
-        // stages its row in that layout and one thread hands the tile to the TMA unit (two stores, one per
-        // 64-element half), which writes it while the CTA goes on.  A tile that the sequence's end cuts short (a
-        // box would reach into the next sequence's rows), odd group sizes and unaligned outputs take the second
-        // path: each thread stages its own 256-byte row, 16-byte pieces swizzled against bank conflicts, and the
-        // warp writes its 32 rows two at a time, 512 contiguous bytes per instruction where consecutive heads of
-        // a token are adjacent.
+        // The row goes to global memory through the staging tile, which the two row tiles use in turn (use
+        // stages_done + g; a use may begin when the one before it has been read out).  A full row tile is one box
+        // of the output tensor, as it was of the query tensor: every thread stages its row in that layout and one
+        // thread hands the tile to the TMA unit (two stores, one per 64-element half), which writes it while the
+        // threads go on to the next item.  A tile that the sequence's end cuts short (a box would reach into the
+        // next sequence's rows), odd group sizes and unaligned outputs take the second path: each thread stages
+        // its own 256-byte row, 16-byte pieces swizzled against bank conflicts, and the warp writes its 32 rows two
+        // at a time, 512 contiguous bytes per instruction where consecutive heads of a token are adjacent.
+        const int stage_use = stages_done + g;
+        if (stage_use > 0) mbar_wait_bounded(bar_stage, static_cast<uint32_t>(stage_use - 1) & 1u, abort_word);
         if (o_by_tma && rows_g == kPairRows) {  // uniform over the row tile's 128 threads
-          const uint32_t tile = smem_addr(s_q) + g * Cfg::kTileBytes;
+          const uint32_t tile = smem_addr(s_stage);
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
             uint32_t acc[32];
@@ -600,9 +657,10 @@ __global__ void __launch_bounds__(kPairThreads, 1)
             tma_store_3d(&tmap_o, tile, 0, w.kvh * p.group, tok0);
             tma_store_3d(&tmap_o, tile + Cfg::kHalfBytes, 64, w.kvh * p.group, tok0);
             tma_store_commit_and_wait_read();  // shared memory has been read; the writes complete on their own
+            mbar_arrive(bar_stage);
           }
         } else {
-          const uint32_t stage = smem_addr(s_q) + g * Cfg::kTileBytes + (warp & 3) * 32 * 256;  // this warp's 32 rows
+          const uint32_t stage = smem_addr(s_stage) + (warp & 3) * 32 * 256;  // this warp's 32 rows
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
             uint32_t acc[32];
@@ -648,9 +706,11 @@ __global__ void __launch_bounds__(kPairThreads, 1)
               ++tok_r;
             }
           }
+          named_bar_sync(2 + g, kPairRows);  // all four warps have read their rows back
+          if (r == 0) mbar_arrive(bar_stage);
         }
       }
-      finish();
+      account(w);
     }
     // the output tiles this thread handed to the TMA unit have been written
     if ((tid & 127) == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
