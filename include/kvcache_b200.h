@@ -357,10 +357,12 @@ KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_h
  *
  * Sequences with at most 16 (token, head) rows per kv head run on the decode kernel, the others on a second
  * kernel launched beside it.  With head size 128 and some sequence of more than 64 rows per kv head that
- * second kernel runs on the tcgen05 tensor cores: a CTA owns 128 rows, both products are tcgen05.mma with keys
- * and values in 128-byte-swizzled shared memory (fp8 caches widened to fp16 on the way in), scores,
- * probabilities and accumulators in tensor memory, two CTAs per SM.  Otherwise (other head sizes, short runs)
- * it is the mma.sync kernel in which a CTA owns 64 rows.  In such a mixed call the decode part is not split over the sequence.  At most 65535 sequences per call.
+ * second kernel runs on the tcgen05 tensor cores: persistent CTAs own two tiles of 128 rows that share every
+ * key/value tile; queries, keys, values and results move by TMA tile copies (power-of-two block sizes of at
+ * least 8 tokens; other block sizes take a one-tile variant with ordinary asynchronous copies); both products
+ * are tcgen05.mma with scores, probabilities and accumulators in tensor memory; fp8 caches are widened to fp16
+ * in shared memory.  Otherwise (other head sizes, short runs) it is the mma.sync kernel in which a CTA owns 64
+ * rows.  In such a mixed call the decode part is not split over the sequence.  At most 65535 sequences per call.
  *
  * kvc_paged_attention_device_status waits for the device's earlier work and reads the tcgen05 kernel's status
  * word: 0 = fine; 1 = a bounded wait on an mbarrier gave up (results of that call are then undefined; the

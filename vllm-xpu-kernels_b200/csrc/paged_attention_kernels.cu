@@ -1285,25 +1285,31 @@ inline EncodeTiledFn tensor_map_encoder() {
 }
 
 inline bool prefill_uses_pair(int kv_dtype, int64_t head_size, int64_t max_rows_per_kv_head, int64_t block_size) {
-  return prefill_pair_enabled() && prefill_uses_umma(kv_dtype, head_size, max_rows_per_kv_head) &&
-         kv_dtype == KVC_KV_AUTO && head_size == 128 && pow2_shift(block_size) >= 3 && tensor_map_encoder() != nullptr;
+  (void)kv_dtype;  // 16-bit and fp8 caches alike
+  return prefill_pair_enabled() && prefill_uses_umma(kv_dtype, head_size, max_rows_per_kv_head) && head_size == 128 &&
+         pow2_shift(block_size) >= 3 && tensor_map_encoder() != nullptr;
 }
 
 // A tensor map over a paged cache [block][token in block][kv head][d] of 16-bit elements (any strides that are
 // multiples of 16 bytes): the box is min(block_size, 128) tokens x one head x 64 elements, stored with the
 // 128-byte swizzle.  The block dimension is given its largest legal extent: block numbers come from the block
 // table, and the map itself knows no allocation size.
-inline bool make_cache_tensor_map(CUtensorMap* map, const void* cache, int q_dtype, const DecodeParams& p) {
+// An fp8 cache is mapped as bytes: the box is the tokens' raw 128-byte rows, unswizzled (the kernel widens them).
+inline bool make_cache_tensor_map(CUtensorMap* map, const void* cache, int q_dtype, int kv_dtype, const DecodeParams& p) {
+  const bool fp8 = kv_dtype != KVC_KV_AUTO;
+  const cuuint64_t es = fp8 ? 1 : 2;
   const cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(p.num_kv_heads), static_cast<cuuint64_t>(p.block_size),
                               1ull << 31};
-  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(p.head_stride) * 2, static_cast<cuuint64_t>(p.page_stride) * 2,
-                                 static_cast<cuuint64_t>(p.block_stride) * 2};
-  const cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(p.block_size < kPairTile ? p.block_size : kPairTile), 1};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(p.head_stride) * es, static_cast<cuuint64_t>(p.page_stride) * es,
+                                 static_cast<cuuint64_t>(p.block_stride) * es};
+  const cuuint32_t box[4] = {fp8 ? 128u : 64u, 1, static_cast<cuuint32_t>(p.block_size < kPairTile ? p.block_size : kPairTile), 1};
   const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                     : (q_dtype == KVC_IN_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
   const CUresult r = tensor_map_encoder()(
-      map, q_dtype == KVC_IN_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
-      const_cast<void*>(cache), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      map, dt, 4, const_cast<void*>(cache), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      fp8 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
@@ -1323,7 +1329,7 @@ inline bool make_query_tensor_map(CUtensorMap* map, const void* base, int64_t st
   return r == CUDA_SUCCESS;
 }
 
-template <typename TQ>
+template <typename TQ, int KV>
 cudaError_t launch_prefill_pair(const DecodeParams& p, int q_dtype, int64_t total_q, int64_t num_seqs, cudaStream_t st) {
   static std::once_flag once[64];
   static cudaError_t attr_err[64];
@@ -1333,7 +1339,7 @@ cudaError_t launch_prefill_pair(const DecodeParams& p, int q_dtype, int64_t tota
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   static int sm_count[64];
   std::call_once(once[dev], [&] {
-    attr_err[dev] = cudaFuncSetAttribute(paged_prefill_pair_kernel<TQ>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err[dev] = cudaFuncSetAttribute(paged_prefill_pair_kernel<TQ, KV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          PairCfg::kSmemBytes);
     if (attr_err[dev] == cudaSuccess)
       attr_err[dev] = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
@@ -1346,11 +1352,14 @@ cudaError_t launch_prefill_pair(const DecodeParams& p, int q_dtype, int64_t tota
   if (items <= 0 || items > 0x7FFFFFFFll) return cudaErrorInvalidValue;
   const dim3 grid(static_cast<unsigned>(items < sm_count[dev] ? items : sm_count[dev]));
   CUtensorMap map_k, map_v, map_q, map_o;
-  if (!make_cache_tensor_map(&map_k, p.key_cache, q_dtype, p) || !make_cache_tensor_map(&map_v, p.value_cache, q_dtype, p))
+  if (!make_cache_tensor_map(&map_k, p.key_cache, q_dtype, KV, p) ||
+      !make_cache_tensor_map(&map_v, p.value_cache, q_dtype, KV, p))
     return cudaErrorInvalidValue;
-  // the query rows come by TMA where a row tile is a box: power-of-two groups of at most 128 heads
-  int q_by_tma = ((p.group & (p.group - 1)) == 0 && p.group <= kPairRows) ? 1 : 0;
-  int o_by_tma = q_by_tma && aligned(p.out, 16) && (p.out_stride_t * 2) % 16 == 0 && (p.out_stride_h * 2) % 16 == 0;
+  // the query rows come by TMA where a row tile is a box: power-of-two groups of at most 128 heads (and not a
+  // bf16 query over an fp8 cache, which is converted to fp16 on its way in); results likewise
+  const bool box_rows_ok = (p.group & (p.group - 1)) == 0 && p.group <= kPairRows;
+  int q_by_tma = (box_rows_ok && !(KV != KVC_KV_AUTO && q_dtype == KVC_IN_BF16)) ? 1 : 0;
+  int o_by_tma = box_rows_ok && aligned(p.out, 16) && (p.out_stride_t * 2) % 16 == 0 && (p.out_stride_h * 2) % 16 == 0;
   if (q_by_tma && !make_query_tensor_map(&map_q, p.query, p.query_stride_t, p.query_stride_h, q_dtype, p, total_q))
     q_by_tma = 0;
   if (o_by_tma && !make_query_tensor_map(&map_o, p.out, p.out_stride_t, p.out_stride_h, q_dtype, p, total_q))
@@ -1367,8 +1376,18 @@ cudaError_t launch_prefill_pair(const DecodeParams& p, int q_dtype, int64_t tota
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, paged_prefill_pair_kernel<TQ>, p, map_k, map_v, map_q, map_o, q_by_tma, o_by_tma,
+  return cudaLaunchKernelEx(&cfg, paged_prefill_pair_kernel<TQ, KV>, p, map_k, map_v, map_q, map_o, q_by_tma, o_by_tma,
                             static_cast<int>(num_seqs), static_cast<int>(items));
+}
+
+template <typename TQ>
+cudaError_t launch_prefill_pair_kv(int kv, const DecodeParams& p, int q_dtype, int64_t total_q, int64_t num_seqs,
+                                   cudaStream_t st) {
+  switch (kv) {
+    case KVC_KV_AUTO: return launch_prefill_pair<TQ, KVC_KV_AUTO>(p, q_dtype, total_q, num_seqs, st);
+    case KVC_KV_FP8_E4M3: return launch_prefill_pair<TQ, KVC_KV_FP8_E4M3>(p, q_dtype, total_q, num_seqs, st);
+    default: return launch_prefill_pair<TQ, KVC_KV_FP8_E5M2>(p, q_dtype, total_q, num_seqs, st);
+  }
 }
 
 struct DecodePlan {
@@ -1599,8 +1618,8 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
       fprintf(stderr, "kvc: many-rows attention on the %s kernel, grid %u x %u\n",
               use_pair ? "paired-tile tcgen05" : use_umma ? "one-tile tcgen05" : "mma.sync", pgrid.x, pgrid.y);
     if (use_pair)
-      e = (q_dtype == KVC_IN_F16) ? launch_prefill_pair<__half>(pp, q_dtype, total_q, num_seqs, st)
-                                  : launch_prefill_pair<__nv_bfloat16>(pp, q_dtype, total_q, num_seqs, st);
+      e = (q_dtype == KVC_IN_F16) ? launch_prefill_pair_kv<__half>(kv_dtype, pp, q_dtype, total_q, num_seqs, st)
+                                  : launch_prefill_pair_kv<__nv_bfloat16>(kv_dtype, pp, q_dtype, total_q, num_seqs, st);
     else if (use_umma)
       e = (q_dtype == KVC_IN_F16) ? launch_prefill_umma_kv<__half>(kv_dtype, pp, pgrid, st)
                                   : launch_prefill_umma_kv<__nv_bfloat16>(kv_dtype, pp, pgrid, st);

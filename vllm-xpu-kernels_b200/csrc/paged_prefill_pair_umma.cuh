@@ -1,4 +1,4 @@
-// The many-rows attention kernel for 16-bit caches, head size 128, on the fifth-generation tensor cores.
+// The many-rows attention kernel for head size 128 (16-bit and fp8 caches) on the fifth-generation tensor cores.
 // One CTA per SM walks work items -- a pair of row tiles of 128 query rows each (token-major (token, head) pairs
 // of one kv head of one sequence) that share every key/value tile -- in tiles of 128 cached tokens, and is
 // specialised by warp:
@@ -12,7 +12,9 @@
 //               swizzle, no multicast, this GPU's memory only).  Keys and values come straight from the paged
 //               cache: a tensor map over [block][token in block][kv head][d] makes a cache block's rows one box,
 //               the block table gives the block coordinate, one lane issues one box.
-//   warps 10-11 idle (they complete the third warpgroup, whose registers go to the softmax threads).
+//   warps 10-11 fp8 caches only: widen a tile's raw rows (which the copy warp drops into the upper half of the
+//               tile's slot) to fp16 in the operand layout; the products then run in fp16.  Idle for 16-bit
+//               caches.  (They complete the third warpgroup, whose registers go to the softmax threads.)
 //
 // Tensor memory (512 columns, all of the SM's): O_A | O_B | X | P_A | P_B with 128, 128, 128, 64, 64 columns.
 // X holds the scores of whichever row tile's turn it is: a softmax thread moves its row of X into registers
@@ -73,7 +75,7 @@ struct PairCfg {
   static constexpr int kOffV = 4 * kTileBytes;       // [stage]
   static constexpr int kOffStage = 6 * kTileBytes;   // one row tile of results on its way out
   static constexpr int kOffBar = 7 * kTileBytes;     // mbarriers, tensor-memory slot, abort word
-  static constexpr int kBarriers = 18;
+  static constexpr int kBarriers = 22;
   static constexpr int kSmemBytes = kOffBar + kBarriers * 8 + 16;  // + tensor-memory slot and abort word
   static_assert(kSmemBytes + 1024 <= 232448, "fits one SM");
   static_assert(2 * (kSmemBytes + 1024) > 233472, "one CTA per SM: it allocates all of the SM's tensor memory");
@@ -154,7 +156,7 @@ struct PairItem {
   bool has_b;
 };
 
-template <typename TQ>
+template <typename TQ, int KV>
 __global__ void __launch_bounds__(kPairThreads, 1)
     paged_prefill_pair_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tmap_k,
                               const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_q,
@@ -163,6 +165,12 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   using Cfg = PairCfg;
   using namespace umma;
   constexpr int D = Cfg::D, TN = kPairTile;
+  // fp8 caches: the copy warp brings a tile's raw rows (128 bytes each) into the upper half of the tile's slot,
+  // warps 10 and 11 widen them to fp16 (exact) in the swizzled operand layout, and the products run in fp16
+  // (a bf16 query is converted on its way into shared memory); k_descale folds into the softmax scale,
+  // v_descale into the output.
+  constexpr bool kFp8 = KV != KVC_KV_AUTO;
+  using T16 = std::conditional_t<kFp8, __half, TQ>;  // operand type of the matrix products
 
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* s_q = smem + Cfg::kOffQ;
@@ -181,6 +189,8 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   uint64_t* bar_qfull = bars + 15;  // the query rows have landed (when they come by TMA)
   uint64_t* bar_qfree = bars + 16;  // every product that reads the item's query rows is complete
   uint64_t* bar_stage = bars + 17;  // the staging tile has been read by the TMA unit (or written out by its warps)
+  uint64_t* bar_kconv = bars + 18;  // [stage]  fp8 caches: the K tile has been widened to fp16 (64 arrivals)
+  uint64_t* bar_vconv = bars + 20;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kBarriers);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
@@ -211,6 +221,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
     mbar_init(bar_qfull, 1);
     mbar_init(bar_qfree, 1);
     mbar_init(bar_stage, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(bar_kconv + i, 64);  // kconv, vconv
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(tmem_slot, kPairTmemCols);
@@ -324,11 +335,12 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         // A tile is 128 tokens: one box of 128 rows when a cache block holds at least 128 tokens, else 128 / bs
         // boxes of bs rows; every box exists twice, once per 64-element half of the head dimension.  Lane l
         // issues box l / 2, half l % 2.  Blocks that start at or beyond the sequence's end are not fetched.
+        // fp8 caches: a box is box_rows raw rows of 128 bytes, one per tile and block, in the slot's upper half.
         const int32_t* table = p.block_table + w.seq * p.block_table_stride;
         const int box_rows = min(p.block_size, TN);
-        const int ops = (TN / box_rows) * 2;
+        const int ops = (TN / box_rows) * (kFp8 ? 1 : 2);
         const uint32_t box_bytes = static_cast<uint32_t>(box_rows) * 128u;
-        const int b = lane >> 1, half = lane & 1;
+        const int b = kFp8 ? lane : lane >> 1, half = kFp8 ? 1 : lane & 1;
         auto load_tile = [&](int tile, const CUtensorMap* map, unsigned char* slot, uint64_t* full) {
           const int token0 = tile * TN + b * box_rows;
           const bool valid = lane < ops && token0 < w.n;
@@ -337,7 +349,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           __syncwarp();
           if (valid) {
             const int32_t blk = __ldg(table + (token0 >> p.bs_shift));
-            tma_load_4d(smem_addr(slot) + half * Cfg::kHalfBytes + b * box_bytes, map, full, half * 64, w.kvh,
+            tma_load_4d(smem_addr(slot) + half * Cfg::kHalfBytes + b * box_bytes, map, full, kFp8 ? 0 : half * 64, w.kvh,
                         token0 & (p.block_size - 1), blk);
           }
         };
@@ -360,8 +372,8 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         }
       } else if (warp == 8) {
         // ====================================================================================== issuing warp
-        constexpr uint32_t kIdescQK = instr_desc_f16<TQ>(kPairRows, TN, false, false);
-        constexpr uint32_t kIdescPV = instr_desc_f16<TQ>(kPairRows, D, false, true);
+        constexpr uint32_t kIdescQK = instr_desc_f16<T16>(kPairRows, TN, false, false);
+        constexpr uint32_t kIdescPV = instr_desc_f16<T16>(kPairRows, D, false, true);
         constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
         constexpr uint32_t kLboK = (16u >> 4) << 16;                          // K-major operands: unused
         constexpr uint32_t kLboV = (static_cast<uint32_t>(Cfg::kHalfBytes) >> 4) << 16;  // V: distance of the D halves
@@ -395,7 +407,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           const int gu = uses_done + use;
           if (gu > 0) mbar_wait_bounded(bar_xfree, static_cast<uint32_t>(gu - 1) & 1u, abort_word);
         };
-        auto kfull_of = [&](int j) { return bar_kfull + ((tiles_done + j) & 1); };
+        auto kfull_of = [&](int j) { return (kFp8 ? bar_kconv : bar_kfull) + ((tiles_done + j) & 1); };
         auto kfree_of = [&](int j) { return bar_kfree + ((tiles_done + j) & 1); };
         auto stage_parity = [&](int j) { return static_cast<uint32_t>((tiles_done + j) >> 1) & 1u; };
         const bool last_s_in_prologue = w.nt == 1;  // a one-tile item: its only S batches are the first ones
@@ -443,7 +455,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
             }
             // O_g += P_g(j) V(j)
             if (g == 0) {
-              mbar_wait_bounded(bar_vfull + s, stage_parity(j), abort_word);
+              mbar_wait_bounded((kFp8 ? bar_vconv : bar_vfull) + s, stage_parity(j), abort_word);
               const int valid_rows = w.n - (w.tile_begin + j) * TN;  // rows of the tile that hold tokens of the sequence
               if (valid_rows < TN) {
                 unsigned char* v = s_v + s * Cfg::kTileBytes;
@@ -466,6 +478,55 @@ __global__ void __launch_bounds__(kPairThreads, 1)
             }
             __syncwarp();
           }
+        }
+      } else if (kFp8 && warp >= 10) {
+        // ====================================================================================== widening warps
+        // Warps 10 and 11, 64 threads.  A tile's 128 raw rows are widened in two phases of 64 rows: a warp reads
+        // 4 rows x 8 sixteen-byte chunks per instruction (512 contiguous bytes), every thread holds 8 chunks,
+        // the 64 threads meet (everything a store of this phase can overwrite has been read: raw row r lies on
+        // the bytes of row r of the second D half), then each chunk becomes two swizzled fp16 chunks.
+        const int cw = warp - 10;
+        auto widen = [&](unsigned char* slot) {
+          const unsigned char* raw = slot + Cfg::kHalfBytes;
+#pragma unroll 1
+          for (int ph = 0; ph < 2; ++ph) {
+            uint4 c[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int row = ph * 64 + cw * 32 + 4 * i + (lane >> 3);
+              c[i] = *reinterpret_cast<const uint4*>(raw + row * 128 + (lane & 7) * 16);
+            }
+            named_bar_sync(4, 64);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int row = ph * 64 + cw * 32 + 4 * i + (lane >> 3), ch = lane & 7;  // raw chunk: d = 16 ch ..
+              const uint32_t src[4] = {c[i].x, c[i].y, c[i].z, c[i].w};
+              uint4 lo, hi;
+              lo.x = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[0]);
+              lo.y = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[0] >> 16);
+              lo.z = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[1]);
+              lo.w = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[1] >> 16);
+              hi.x = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2]);
+              hi.y = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2] >> 16);
+              hi.z = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[3]);
+              hi.w = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[3] >> 16);
+              unsigned char* dst = slot + (ch >> 2) * Cfg::kHalfBytes;  // fp16 chunks 2 ch, 2 ch + 1 of the row
+              *reinterpret_cast<uint4*>(dst + swizzled_offset(row, (2 * ch) & 7)) = lo;
+              *reinterpret_cast<uint4*>(dst + swizzled_offset(row, (2 * ch + 1) & 7)) = hi;
+            }
+          }
+        };
+        for (int j = 0; j < w.nt; ++j) {
+          const int kt = tiles_done + j, s = kt & 1;
+          const uint32_t par = static_cast<uint32_t>(kt >> 1) & 1u;
+          mbar_wait_bounded(bar_kfull + s, par, abort_word);
+          widen(s_k + s * Cfg::kTileBytes);
+          fence_smem_to_async_proxy();
+          mbar_arrive(bar_kconv + s);
+          mbar_wait_bounded(bar_vfull + s, par, abort_word);
+          widen(s_v + s * Cfg::kTileBytes);
+          fence_smem_to_async_proxy();
+          mbar_arrive(bar_vconv + s);
         }
       }
       account(w);
@@ -505,6 +566,14 @@ __global__ void __launch_bounds__(kPairThreads, 1)
             piece[i] = *reinterpret_cast<const uint4*>(static_cast<const TQ*>(p.query) +
                                                        static_cast<int64_t>(w.q_start + row_token(R)) * p.query_stride_t +
                                                        row_head(w, R) * p.query_stride_h + col * 8);
+            if constexpr (!std::is_same_v<TQ, T16>) {  // bf16 query over an fp8 cache: the products run in fp16
+              uint32_t* wq = reinterpret_cast<uint32_t*>(&piece[i]);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float lo = __uint_as_float(wq[k] << 16), hi = __uint_as_float(wq[k] & 0xFFFF0000u);
+                wq[k] = pack2<__half>(lo, hi);
+              }
+            }
           }
         }
 #pragma unroll
@@ -528,7 +597,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         const int lo = live ? row_lo(w, Rg0 + r) : 0;
         const int lim_min = row_limit(w, Rg0);
         const int lo_max = row_lo(w, Rg0 + rows_g - 1);
-        const float scale2 = p.softmax_scale * kLog2e;
+        const float scale2 = p.softmax_scale * kLog2e * ((kFp8 && p.k_descale) ? __ldg(p.k_descale) : 1.0f);
         const float lazy_margin = 8.0f / scale2;
         const uint32_t t_lanes = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);  // this warp's 32 lanes
         const uint32_t t_x = t_lanes + kColX, t_p = t_lanes + kColP + g * 64, t_o = t_lanes + kColO + g * 128;
@@ -596,7 +665,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
                 const float2 e = __ffma2_rn(make_float2(__uint_as_float(sa[c][i]), __uint_as_float(sa[c][i + 1])), sc2, nm2);
                 const float2 pr = make_float2(fast_exp2(e.x), fast_exp2(e.y));
                 l_add[(i >> 1) & 3] = __fadd2_rn(l_add[(i >> 1) & 3], pr);
-                wd[cc * 16 + (i >> 1)] = pack2<TQ>(pr.x, pr.y);
+                wd[cc * 16 + (i >> 1)] = pack2<T16>(pr.x, pr.y);
               }
             tmem_st_32x32(t_p + h * 32, wd);
           }
@@ -621,7 +690,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           rescale = (m == -INFINITY) ? 0.f : exp2f(m - mf);
           l = l * rescale + exp2f(sk - mf);
         }
-        const float f = (l > 0.f) ? rescale / l : 0.f;
+        const float f = (l > 0.f) ? rescale / l * ((kFp8 && p.v_descale) ? __ldg(p.v_descale) : 1.0f) : 0.f;
         // The row goes to global memory through the staging tile, which the two row tiles use in turn (use
         // stages_done + g; a use may begin when the one before it has been read out).  A full row tile is one box
         // of the output tensor, as it was of the query tensor: every thread stages its row in that layout and one
