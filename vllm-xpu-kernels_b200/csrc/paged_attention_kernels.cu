@@ -1355,10 +1355,10 @@ cudaError_t launch_prefill_pair(const DecodeParams& p, int q_dtype, int64_t tota
   if (!make_cache_tensor_map(&map_k, p.key_cache, q_dtype, KV, p) ||
       !make_cache_tensor_map(&map_v, p.value_cache, q_dtype, KV, p))
     return cudaErrorInvalidValue;
-  // the query rows come by TMA where a row tile is a box: power-of-two groups of at most 128 heads (and not a
-  // bf16 query over an fp8 cache, which is converted to fp16 on its way in); results likewise
+  // the query rows come by TMA where a row tile is a box: power-of-two groups of at most 128 heads (a bf16 query
+  // over an fp8 cache is then converted to fp16 in shared memory by the widening warps); results likewise
   const bool box_rows_ok = (p.group & (p.group - 1)) == 0 && p.group <= kPairRows;
-  int q_by_tma = (box_rows_ok && !(KV != KVC_KV_AUTO && q_dtype == KVC_IN_BF16)) ? 1 : 0;
+  int q_by_tma = box_rows_ok ? 1 : 0;
   int o_by_tma = box_rows_ok && aligned(p.out, 16) && (p.out_stride_t * 2) % 16 == 0 && (p.out_stride_h * 2) % 16 == 0;
   if (q_by_tma && !make_query_tensor_map(&map_q, p.query, p.query_stride_t, p.query_stride_h, q_dtype, p, total_q))
     q_by_tma = 0;

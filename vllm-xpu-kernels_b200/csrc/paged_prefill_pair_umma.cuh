@@ -75,7 +75,7 @@ struct PairCfg {
   static constexpr int kOffV = 4 * kTileBytes;       // [stage]
   static constexpr int kOffStage = 6 * kTileBytes;   // one row tile of results on its way out
   static constexpr int kOffBar = 7 * kTileBytes;     // mbarriers, tensor-memory slot, abort word
-  static constexpr int kBarriers = 22;
+  static constexpr int kBarriers = 23;
   static constexpr int kSmemBytes = kOffBar + kBarriers * 8 + 16;  // + tensor-memory slot and abort word
   static_assert(kSmemBytes + 1024 <= 232448, "fits one SM");
   static_assert(2 * (kSmemBytes + 1024) > 233472, "one CTA per SM: it allocates all of the SM's tensor memory");
@@ -171,6 +171,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   // v_descale into the output.
   constexpr bool kFp8 = KV != KVC_KV_AUTO;
   using T16 = std::conditional_t<kFp8, __half, TQ>;  // operand type of the matrix products
+  constexpr bool kConvQ = !std::is_same_v<TQ, T16>;  // a bf16 query that arrived by TMA is converted in place
 
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* s_q = smem + Cfg::kOffQ;
@@ -191,6 +192,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   uint64_t* bar_stage = bars + 17;  // the staging tile has been read by the TMA unit (or written out by its warps)
   uint64_t* bar_kconv = bars + 18;  // [stage]  fp8 caches: the K tile has been widened to fp16 (64 arrivals)
   uint64_t* bar_vconv = bars + 20;
+  uint64_t* bar_qconv = bars + 22;  // fp8 caches, bf16 queries: the query rows have been converted to fp16 (64 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kBarriers);
   volatile uint32_t* abort_word = tmem_slot + 1;
 
@@ -222,6 +224,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
     mbar_init(bar_qfree, 1);
     mbar_init(bar_stage, 1);
     for (int i = 0; i < 4; ++i) mbar_init(bar_kconv + i, 64);  // kconv, vconv
+    mbar_init(bar_qconv, 64);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(tmem_slot, kPairTmemCols);
@@ -411,7 +414,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         auto kfree_of = [&](int j) { return bar_kfree + ((tiles_done + j) & 1); };
         auto stage_parity = [&](int j) { return static_cast<uint32_t>((tiles_done + j) >> 1) & 1u; };
         const bool last_s_in_prologue = w.nt == 1;  // a one-tile item: its only S batches are the first ones
-        if (q_by_tma) mbar_wait_bounded(bar_qfull, static_cast<uint32_t>(items_done) & 1u, abort_word);
+        if (q_by_tma) mbar_wait_bounded(kConvQ ? bar_qconv : bar_qfull, static_cast<uint32_t>(items_done) & 1u, abort_word);
         mbar_wait_bounded(kfull_of(0), stage_parity(0), abort_word);
         wait_x(0);
         fence_after_thread_sync();
@@ -516,6 +519,24 @@ __global__ void __launch_bounds__(kPairThreads, 1)
             }
           }
         };
+        if (kConvQ && q_by_tma) {  // the item's query rows, bf16 as they came: to fp16, element for element in place
+          mbar_wait_bounded(bar_qfull, static_cast<uint32_t>(items_done) & 1u, abort_word);
+          const int t64 = cw * 32 + lane;
+#pragma unroll 4
+          for (int i = 0; i < 2 * Cfg::kTileBytes / 16 / 64; ++i) {
+            uint4* cell = reinterpret_cast<uint4*>(s_q) + i * 64 + t64;
+            uint4 v = *cell;
+            uint32_t* wq = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float lo = __uint_as_float(wq[k] << 16), hi = __uint_as_float(wq[k] & 0xFFFF0000u);
+              wq[k] = pack2<__half>(lo, hi);
+            }
+            *cell = v;
+          }
+          fence_smem_to_async_proxy();
+          mbar_arrive(bar_qconv);
+        }
         for (int j = 0; j < w.nt; ++j) {
           const int kt = tiles_done + j, s = kt & 1;
           const uint32_t par = static_cast<uint32_t>(kt >> 1) & 1u;
