@@ -356,7 +356,7 @@ KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_h
  *   window_right   pos + window_right; -1 leaves a side open (test_flash_attn_varlen_func.py:81-95)
  *
  * Sequences with at most 16 (token, head) rows per kv head run on the decode kernel, the others on a second
- * kernel launched beside it.  With head size 128 and some sequence of more than 64 rows per kv head that
+ * kernel launched beside it.  With head size 128 (or 64 over a 16-bit cache) and some sequence of more than 64 rows per kv head that
  * second kernel runs on the tcgen05 tensor cores: persistent CTAs own two tiles of 128 rows that share every
  * key/value tile; queries, keys, values and results move by TMA tile copies (power-of-two block sizes of at
  * least 8 tokens; other block sizes take a one-tile variant with ordinary asynchronous copies); both products

@@ -24,8 +24,7 @@ TOL = dict(atol=H.ATTN_ATOL, rtol=H.ATTN_RTOL)
 
 
 def run_case(dev, dtype, hq, hk, q_lens, kv_lens, bs, causal, sink, seed, window=(-1, -1), scale=None, out=None,
-             kv="auto", descale=1.0):
-    D = 128
+             kv="auto", descale=1.0, D=128):
     nb = max(64, sum((n + bs - 1) // bs for n in kv_lens) + 8)
     torch.manual_seed(seed)
     query = torch.randn(sum(q_lens), hq, D).to(dtype)
@@ -173,3 +172,16 @@ def test_a_bounded_wait_that_runs_out(cuda_device):
     # tensor memory was given back and nothing is stuck: a full-size call right behind it
     run_case(dev, torch.bfloat16, 8, 2, q_lens=[300, 140], kv_lens=[777, 1100], bs=64, causal=True, sink=False, seed=31)
     assert cabi.paged_attention_device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("heads", [(4, 4), (8, 2), (6, 2), (16, 1)])
+@pytest.mark.parametrize("bs", [16, 64])
+def test_prefill_head_size_64(dtype, heads, bs, cuda_device):
+    """Head size 64 over 16-bit caches runs on the paired-tile tcgen05 kernel too (one 64-element operand tile
+    per row instead of two): ragged lengths, groups that are and are not powers of two, a window, a sink."""
+    hq, hk = heads
+    run_case(cuda_device, dtype, hq, hk, q_lens=[200, 1, 70, 513], kv_lens=[777, 300, 70, 1500], bs=bs, causal=True,
+             sink=(hq == 8), seed=640 + hq + bs, D=64)
+    run_case(cuda_device, dtype, hq, hk, q_lens=[300, 129], kv_lens=[1000, 700], bs=bs, causal=(hq != 4), sink=False,
+             seed=650 + hq + bs, window=(127, -1) if hq == 16 else (-1, -1), D=64)

@@ -965,7 +965,7 @@ __global__ void __launch_bounds__(kAttnThreads, (D <= 128 ? 3 : 1)) paged_prefil
 
 }  // namespace kvc
 
-// the many-rows kernel on tcgen05 (16-bit cache, head size 128)
+// the many-rows kernels on tcgen05
 #include "paged_prefill_umma.cuh"
 #include "paged_prefill_pair_umma.cuh"
 
@@ -1257,7 +1257,7 @@ cudaError_t launch_prefill_umma_kv(int kv, const DecodeParams& p, dim3 grid, cud
   }
 }
 
-// ---- the paired-tile tcgen05 kernel (16-bit caches, head size 128, power-of-two blocks of at least 8 tokens) ----
+// ---- the paired-tile tcgen05 kernel (head size 128, or 64 over 16-bit caches; power-of-two blocks of at least 8 tokens) ----
 // KVC_PREFILL_PAIR=0 keeps such calls on the one-tile tcgen05 kernel (for comparisons).
 inline bool prefill_pair_enabled() {
   static const bool off = [] {
@@ -1284,9 +1284,10 @@ inline EncodeTiledFn tensor_map_encoder() {
   return fn;
 }
 
+// Head size 128 over 16-bit and fp8 caches, head size 64 over 16-bit caches.
 inline bool prefill_uses_pair(int kv_dtype, int64_t head_size, int64_t max_rows_per_kv_head, int64_t block_size) {
-  (void)kv_dtype;  // 16-bit and fp8 caches alike
-  return prefill_pair_enabled() && prefill_uses_umma(kv_dtype, head_size, max_rows_per_kv_head) && head_size == 128 &&
+  const bool shape_ok = head_size == 128 || (head_size == 64 && kv_dtype == KVC_KV_AUTO);
+  return prefill_pair_enabled() && prefill_umma_enabled() && shape_ok && max_rows_per_kv_head > kPrefillRows &&
          pow2_shift(block_size) >= 3 && tensor_map_encoder() != nullptr;
 }
 
@@ -1295,11 +1296,12 @@ inline bool prefill_uses_pair(int kv_dtype, int64_t head_size, int64_t max_rows_
 // 128-byte swizzle.  The block dimension is given its largest legal extent: block numbers come from the block
 // table, and the map itself knows no allocation size.
 // An fp8 cache is mapped as bytes: the box is the tokens' raw 128-byte rows, unswizzled (the kernel widens them).
-inline bool make_cache_tensor_map(CUtensorMap* map, const void* cache, int q_dtype, int kv_dtype, const DecodeParams& p) {
+inline bool make_cache_tensor_map(CUtensorMap* map, const void* cache, int q_dtype, int kv_dtype, int head_size,
+                                  const DecodeParams& p) {
   const bool fp8 = kv_dtype != KVC_KV_AUTO;
   const cuuint64_t es = fp8 ? 1 : 2;
-  const cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(p.num_kv_heads), static_cast<cuuint64_t>(p.block_size),
-                              1ull << 31};
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_size), static_cast<cuuint64_t>(p.num_kv_heads),
+                              static_cast<cuuint64_t>(p.block_size), 1ull << 31};
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>(p.head_stride) * es, static_cast<cuuint64_t>(p.page_stride) * es,
                                  static_cast<cuuint64_t>(p.block_stride) * es};
   const cuuint32_t box[4] = {fp8 ? 128u : 64u, 1, static_cast<cuuint32_t>(p.block_size < kPairTile ? p.block_size : kPairTile), 1};
@@ -1317,8 +1319,9 @@ inline bool make_cache_tensor_map(CUtensorMap* map, const void* cache, int q_dty
 // order, 128 / group tokens x group heads x 64 elements.  Tokens past the tensor's end read as zeros and are not
 // written.
 inline bool make_query_tensor_map(CUtensorMap* map, const void* base, int64_t stride_t, int64_t stride_h, int q_dtype,
-                                  const DecodeParams& p, int64_t total_q) {
-  const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(p.num_heads), static_cast<cuuint64_t>(total_q)};
+                                  int head_size, const DecodeParams& p, int64_t total_q) {
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_size), static_cast<cuuint64_t>(p.num_heads),
+                              static_cast<cuuint64_t>(total_q)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(stride_h) * 2, static_cast<cuuint64_t>(stride_t) * 2};
   const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(p.group), static_cast<cuuint32_t>(kPairRows / p.group)};
   const cuuint32_t elem_strides[3] = {1, 1, 1};
@@ -1329,7 +1332,7 @@ inline bool make_query_tensor_map(CUtensorMap* map, const void* base, int64_t st
   return r == CUDA_SUCCESS;
 }
 
-template <typename TQ, int KV>
+template <typename TQ, int KV, int D>
 cudaError_t launch_prefill_pair(const DecodeParams& p, int q_dtype, int64_t total_q, int64_t num_seqs, cudaStream_t st) {
   static std::once_flag once[64];
   static cudaError_t attr_err[64];
@@ -1339,8 +1342,8 @@ cudaError_t launch_prefill_pair(const DecodeParams& p, int q_dtype, int64_t tota
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   static int sm_count[64];
   std::call_once(once[dev], [&] {
-    attr_err[dev] = cudaFuncSetAttribute(paged_prefill_pair_kernel<TQ, KV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         PairCfg::kSmemBytes);
+    attr_err[dev] = cudaFuncSetAttribute(paged_prefill_pair_kernel<TQ, KV, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         PairCfg<D>::kSmemBytes);
     if (attr_err[dev] == cudaSuccess)
       attr_err[dev] = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
   });
@@ -1352,41 +1355,42 @@ cudaError_t launch_prefill_pair(const DecodeParams& p, int q_dtype, int64_t tota
   if (items <= 0 || items > 0x7FFFFFFFll) return cudaErrorInvalidValue;
   const dim3 grid(static_cast<unsigned>(items < sm_count[dev] ? items : sm_count[dev]));
   CUtensorMap map_k, map_v, map_q, map_o;
-  if (!make_cache_tensor_map(&map_k, p.key_cache, q_dtype, KV, p) ||
-      !make_cache_tensor_map(&map_v, p.value_cache, q_dtype, KV, p))
+  if (!make_cache_tensor_map(&map_k, p.key_cache, q_dtype, KV, D, p) ||
+      !make_cache_tensor_map(&map_v, p.value_cache, q_dtype, KV, D, p))
     return cudaErrorInvalidValue;
   // the query rows come by TMA where a row tile is a box: power-of-two groups of at most 128 heads (a bf16 query
   // over an fp8 cache is then converted to fp16 in shared memory by the widening warps); results likewise
   const bool box_rows_ok = (p.group & (p.group - 1)) == 0 && p.group <= kPairRows;
   int q_by_tma = box_rows_ok ? 1 : 0;
   int o_by_tma = box_rows_ok && aligned(p.out, 16) && (p.out_stride_t * 2) % 16 == 0 && (p.out_stride_h * 2) % 16 == 0;
-  if (q_by_tma && !make_query_tensor_map(&map_q, p.query, p.query_stride_t, p.query_stride_h, q_dtype, p, total_q))
+  if (q_by_tma && !make_query_tensor_map(&map_q, p.query, p.query_stride_t, p.query_stride_h, q_dtype, D, p, total_q))
     q_by_tma = 0;
-  if (o_by_tma && !make_query_tensor_map(&map_o, p.out, p.out_stride_t, p.out_stride_h, q_dtype, p, total_q))
+  if (o_by_tma && !make_query_tensor_map(&map_o, p.out, p.out_stride_t, p.out_stride_h, q_dtype, D, p, total_q))
     o_by_tma = 0;
   if (!q_by_tma) map_q = map_k;  // not read
   if (!o_by_tma) map_o = map_k;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(kPairThreads);
-  cfg.dynamicSmemBytes = PairCfg::kSmemBytes;
+  cfg.dynamicSmemBytes = PairCfg<D>::kSmemBytes;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, paged_prefill_pair_kernel<TQ, KV>, p, map_k, map_v, map_q, map_o, q_by_tma, o_by_tma,
+  return cudaLaunchKernelEx(&cfg, paged_prefill_pair_kernel<TQ, KV, D>, p, map_k, map_v, map_q, map_o, q_by_tma, o_by_tma,
                             static_cast<int>(num_seqs), static_cast<int>(items));
 }
 
 template <typename TQ>
-cudaError_t launch_prefill_pair_kv(int kv, const DecodeParams& p, int q_dtype, int64_t total_q, int64_t num_seqs,
-                                   cudaStream_t st) {
+cudaError_t launch_prefill_pair_kv(int kv, int head_size, const DecodeParams& p, int q_dtype, int64_t total_q,
+                                   int64_t num_seqs, cudaStream_t st) {
+  if (head_size == 64) return launch_prefill_pair<TQ, KVC_KV_AUTO, 64>(p, q_dtype, total_q, num_seqs, st);
   switch (kv) {
-    case KVC_KV_AUTO: return launch_prefill_pair<TQ, KVC_KV_AUTO>(p, q_dtype, total_q, num_seqs, st);
-    case KVC_KV_FP8_E4M3: return launch_prefill_pair<TQ, KVC_KV_FP8_E4M3>(p, q_dtype, total_q, num_seqs, st);
-    default: return launch_prefill_pair<TQ, KVC_KV_FP8_E5M2>(p, q_dtype, total_q, num_seqs, st);
+    case KVC_KV_AUTO: return launch_prefill_pair<TQ, KVC_KV_AUTO, 128>(p, q_dtype, total_q, num_seqs, st);
+    case KVC_KV_FP8_E4M3: return launch_prefill_pair<TQ, KVC_KV_FP8_E4M3, 128>(p, q_dtype, total_q, num_seqs, st);
+    default: return launch_prefill_pair<TQ, KVC_KV_FP8_E5M2, 128>(p, q_dtype, total_q, num_seqs, st);
   }
 }
 
@@ -1607,7 +1611,7 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
   if (max_seqlen_q * p.group > kRows) {  // sequences with more than 16 query rows per kv head
     DecodeParams pp = p;
     const bool use_umma = prefill_uses_umma(kv_dtype, head_size, max_seqlen_q * p.group);
-    const bool use_pair = use_umma && prefill_uses_pair(kv_dtype, head_size, max_seqlen_q * p.group, block_size);
+    const bool use_pair = prefill_uses_pair(kv_dtype, head_size, max_seqlen_q * p.group, block_size);
     const int64_t tile_rows = use_pair ? 2 * kPairRows : use_umma ? kUmmaRows : kPrefillRows;
     pp.row_tiles = static_cast<int32_t>((max_seqlen_q * p.group + tile_rows - 1) / tile_rows);
     const int64_t px = static_cast<int64_t>(pp.num_kv_heads) * pp.row_tiles;
@@ -1618,8 +1622,9 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
       fprintf(stderr, "kvc: many-rows attention on the %s kernel, grid %u x %u\n",
               use_pair ? "paired-tile tcgen05" : use_umma ? "one-tile tcgen05" : "mma.sync", pgrid.x, pgrid.y);
     if (use_pair)
-      e = (q_dtype == KVC_IN_F16) ? launch_prefill_pair_kv<__half>(kv_dtype, pp, q_dtype, total_q, num_seqs, st)
-                                  : launch_prefill_pair_kv<__nv_bfloat16>(kv_dtype, pp, q_dtype, total_q, num_seqs, st);
+      e = (q_dtype == KVC_IN_F16)
+              ? launch_prefill_pair_kv<__half>(kv_dtype, static_cast<int>(head_size), pp, q_dtype, total_q, num_seqs, st)
+              : launch_prefill_pair_kv<__nv_bfloat16>(kv_dtype, static_cast<int>(head_size), pp, q_dtype, total_q, num_seqs, st);
     else if (use_umma)
       e = (q_dtype == KVC_IN_F16) ? launch_prefill_umma_kv<__half>(kv_dtype, pp, pgrid, st)
                                   : launch_prefill_umma_kv<__nv_bfloat16>(kv_dtype, pp, pgrid, st);

@@ -1,4 +1,5 @@
-// The many-rows attention kernel for head size 128 (16-bit and fp8 caches) on the fifth-generation tensor cores.
+// The many-rows attention kernel for head size 128 (16-bit and fp8 caches) and head size 64 (16-bit caches) on the
+// fifth-generation tensor cores.
 // One CTA per SM walks work items -- a pair of row tiles of 128 query rows each (token-major (token, head) pairs
 // of one kv head of one sequence) that share every key/value tile -- in tiles of 128 cached tokens, and is
 // specialised by warp:
@@ -66,19 +67,26 @@ constexpr uint32_t kColO = 0;    // O_A, O_B: 128 columns each
 constexpr uint32_t kColX = 256;  // the scores of the row tile whose turn it is: 128 columns
 constexpr uint32_t kColP = 384;  // P_A, P_B: 64 columns each (two 16-bit probabilities per column)
 
+template <int HEAD>
 struct PairCfg {
-  static constexpr int D = 128;
+  static_assert(HEAD == 64 || HEAD == 128, "head size 64 or 128");
+  static constexpr int D = HEAD;
+  static constexpr int kHalves = D / 64;             // 64-element (128-byte) operand tiles per row
   static constexpr int kHalfBytes = 128 * 128;       // 128 rows x 64 sixteen-bit elements: 16 KB
-  static constexpr int kTileBytes = 2 * kHalfBytes;  // a Q row tile, a K tile or a V tile: 32 KB
+  static constexpr int kTileBytes = kHalves * kHalfBytes;  // a Q row tile, a K tile or a V tile
   static constexpr int kOffQ = 0;                    // [row tile]
   static constexpr int kOffK = 2 * kTileBytes;       // [stage]
   static constexpr int kOffV = 4 * kTileBytes;       // [stage]
   static constexpr int kOffStage = 6 * kTileBytes;   // one row tile of results on its way out
   static constexpr int kOffBar = 7 * kTileBytes;     // mbarriers, tensor-memory slot, abort word
   static constexpr int kBarriers = 23;
-  static constexpr int kSmemBytes = kOffBar + kBarriers * 8 + 16;  // + tensor-memory slot and abort word
+  static constexpr int kUsedBytes = kOffBar + kBarriers * 8 + 16;  // + tensor-memory slot and abort word
+  // One CTA per SM, whatever the head size: a CTA allocates all of the SM's tensor memory, and a second CTA on
+  // the same SM would wait for the first to end while another SM stays empty.  Asking for more than half of an
+  // SM's shared memory makes that impossible.
+  static constexpr int kSmemBytes = kUsedBytes > 120 * 1024 ? kUsedBytes : 120 * 1024;
   static_assert(kSmemBytes + 1024 <= 232448, "fits one SM");
-  static_assert(2 * (kSmemBytes + 1024) > 233472, "one CTA per SM: it allocates all of the SM's tensor memory");
+  static_assert(2 * (kSmemBytes + 1024) > 233472, "one CTA per SM");
 };
 
 // one box of a tiled 4-d tensor map -> shared memory of this CTA; completion is counted in bytes on `bar`
@@ -156,13 +164,14 @@ struct PairItem {
   bool has_b;
 };
 
-template <typename TQ, int KV>
+template <typename TQ, int KV, int HEAD>
 __global__ void __launch_bounds__(kPairThreads, 1)
     paged_prefill_pair_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tmap_k,
                               const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_q,
                               const __grid_constant__ CUtensorMap tmap_o, const int q_by_tma, const int o_by_tma,
                               const int num_seqs, const int num_items) {
-  using Cfg = PairCfg;
+  using Cfg = PairCfg<HEAD>;
+  static_assert(KV == KVC_KV_AUTO || HEAD == 128, "fp8 caches: head size 128 (a raw row is one 128-byte line)");
   using namespace umma;
   constexpr int D = Cfg::D, TN = kPairTile;
   // fp8 caches: the copy warp brings a tile's raw rows (128 bytes each) into the upper half of the tile's slot,
@@ -330,10 +339,10 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           if (items_done > 0) mbar_wait_bounded(bar_qfree, static_cast<uint32_t>(items_done - 1) & 1u, abort_word);
           if (lane == 0) mbar_arrive_expect_tx(bar_qfull, 2u * Cfg::kTileBytes);
           __syncwarp();
-          if (lane < 4)  // row tile lane / 2, half lane % 2
-            tma_load_3d(smem_addr(s_q) + (lane >> 1) * Cfg::kTileBytes + (lane & 1) * Cfg::kHalfBytes, &tmap_q,
-                        bar_qfull, (lane & 1) * 64, w.kvh * p.group,
-                        w.q_start + (w.row0 >> g_shift) + (lane >> 1) * tokens_per_tile);
+          if (lane < 2 * Cfg::kHalves)  // row tile lane / halves, half lane % halves
+            tma_load_3d(smem_addr(s_q) + (lane / Cfg::kHalves) * Cfg::kTileBytes + (lane % Cfg::kHalves) * Cfg::kHalfBytes,
+                        &tmap_q, bar_qfull, (lane % Cfg::kHalves) * 64, w.kvh * p.group,
+                        w.q_start + (w.row0 >> g_shift) + (lane / Cfg::kHalves) * tokens_per_tile);
         }
         // A tile is 128 tokens: one box of 128 rows when a cache block holds at least 128 tokens, else 128 / bs
         // boxes of bs rows; every box exists twice, once per 64-element half of the head dimension.  Lane l
@@ -341,9 +350,9 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         // fp8 caches: a box is box_rows raw rows of 128 bytes, one per tile and block, in the slot's upper half.
         const int32_t* table = p.block_table + w.seq * p.block_table_stride;
         const int box_rows = min(p.block_size, TN);
-        const int ops = (TN / box_rows) * (kFp8 ? 1 : 2);
+        const int ops = (TN / box_rows) * (kFp8 ? 1 : Cfg::kHalves);
         const uint32_t box_bytes = static_cast<uint32_t>(box_rows) * 128u;
-        const int b = kFp8 ? lane : lane >> 1, half = kFp8 ? 1 : lane & 1;
+        const int b = kFp8 ? lane : lane / Cfg::kHalves, half = kFp8 ? 1 : lane % Cfg::kHalves;
         auto load_tile = [&](int tile, const CUtensorMap* map, unsigned char* slot, uint64_t* full) {
           const int token0 = tile * TN + b * box_rows;
           const bool valid = lane < ops && token0 < w.n;
@@ -463,8 +472,8 @@ __global__ void __launch_bounds__(kPairThreads, 1)
               if (valid_rows < TN) {
                 unsigned char* v = s_v + s * Cfg::kTileBytes;
                 const int first = max(valid_rows, 0);
-                for (int i = lane; i < (TN - first) * 16; i += 32) {  // 8 chunks per row and half
-                  const int r = first + (i >> 4), c = i & 15;
+                for (int i = lane; i < (TN - first) * (D / 8); i += 32) {  // 8 chunks per row and half
+                  const int r = first + i / (D / 8), c = i % (D / 8);
                   *reinterpret_cast<uint4*>(v + (c >> 3) * Cfg::kHalfBytes + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
                 }
                 fence_smem_to_async_proxy();
@@ -482,7 +491,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
             __syncwarp();
           }
         }
-      } else if (kFp8 && warp >= 10) {
+      } else if (kFp8 && D == 128 && warp >= 10) {
         // ====================================================================================== widening warps
         // Warps 10 and 11, 64 threads.  A tile's 128 raw rows are widened in two phases of 64 rows: a warp reads
         // 4 rows x 8 sixteen-byte chunks per instruction (512 contiguous bytes), every thread holds 8 chunks,
@@ -744,13 +753,15 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           named_bar_sync(2 + g, kPairRows);
           if (r == 0) {
             const int tok0 = w.q_start + (Rg0 >> g_shift);
-            tma_store_3d(&tmap_o, tile, 0, w.kvh * p.group, tok0);
-            tma_store_3d(&tmap_o, tile + Cfg::kHalfBytes, 64, w.kvh * p.group, tok0);
+#pragma unroll
+            for (int h = 0; h < Cfg::kHalves; ++h)
+              tma_store_3d(&tmap_o, tile + h * Cfg::kHalfBytes, h * 64, w.kvh * p.group, tok0);
             tma_store_commit_and_wait_read();  // shared memory has been read; the writes complete on their own
             mbar_arrive(bar_stage);
           }
         } else {
-          const uint32_t stage = smem_addr(s_stage) + (warp & 3) * 32 * 256;  // this warp's 32 rows
+          constexpr int kRowBytes = D * 2, kPieces = D / 8, kRowsPerStore = 32 / kPieces;
+          const uint32_t stage = smem_addr(s_stage) + (warp & 3) * 32 * kRowBytes;  // this warp's 32 rows
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
             uint32_t acc[32];
@@ -763,21 +774,21 @@ __global__ void __launch_bounds__(kPairThreads, 1)
               v.y = pack2<TQ>(__uint_as_float(acc[8 * i + 2]) * f, __uint_as_float(acc[8 * i + 3]) * f);
               v.z = pack2<TQ>(__uint_as_float(acc[8 * i + 4]) * f, __uint_as_float(acc[8 * i + 5]) * f);
               v.w = pack2<TQ>(__uint_as_float(acc[8 * i + 6]) * f, __uint_as_float(acc[8 * i + 7]) * f);
-              st_shared_v4(stage + lane * 256 + (((c * 4 + i) ^ (lane & 15)) << 4), v);
+              st_shared_v4(stage + lane * kRowBytes + (((c * 4 + i) ^ (lane & (kPieces - 1))) << 4), v);
             }
           }
           __syncwarp();
           const bool vec16 = ((reinterpret_cast<uintptr_t>(p.out) | static_cast<uintptr_t>(p.out_stride_t * 2) |
                                static_cast<uintptr_t>(p.out_stride_h * 2)) & 15u) == 0;
-          // (token, head) of the lane's first row once, then two rows further per step: no division in the loop
-          const int piece = lane & 15;  // 16-byte piece of the row
-          int rr = lane >> 4;           // row of the warp
+          // (token, head) of the lane's first row once, then kRowsPerStore rows further per step: no division in the loop
+          const int piece = lane % kPieces;  // 16-byte piece of the row
+          int rr = lane / kPieces;           // row of the warp
           int tok_r = row_token(Rg0 + (warp & 3) * 32 + rr);
           int head_r = Rg0 + (warp & 3) * 32 + rr - tok_r * p.group;  // head within the group
 #pragma unroll 4
-          for (int i = 0; i < 16; ++i, rr += 2) {
+          for (int i = 0; i < 32 / kRowsPerStore; ++i, rr += kRowsPerStore) {
             if ((warp & 3) * 32 + rr < rows_g) {
-              const uint4 v = ld_shared_v4(stage + rr * 256 + ((piece ^ (rr & 15)) << 4));
+              const uint4 v = ld_shared_v4(stage + rr * kRowBytes + ((piece ^ (rr & (kPieces - 1))) << 4));
               TQ* dst = static_cast<TQ*>(p.out) + static_cast<int64_t>(w.q_start + tok_r) * p.out_stride_t +
                         static_cast<int64_t>(w.kvh * p.group + head_r) * p.out_stride_h + piece * 8;
               if (vec16) {
@@ -790,7 +801,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
                 d32[3] = v.w;
               }
             }
-            head_r += 2;
+            head_r += kRowsPerStore;
             while (head_r >= p.group) {
               head_r -= p.group;
               ++tok_r;
