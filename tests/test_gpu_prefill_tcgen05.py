@@ -185,3 +185,18 @@ def test_prefill_head_size_64(dtype, heads, bs, cuda_device):
              sink=(hq == 8), seed=640 + hq + bs, D=64)
     run_case(cuda_device, dtype, hq, hk, q_lens=[300, 129], kv_lens=[1000, 700], bs=bs, causal=(hq != 4), sink=False,
              seed=650 + hq + bs, window=(127, -1) if hq == 16 else (-1, -1), D=64)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D", [192, 256])
+@pytest.mark.parametrize("heads", [(4, 4), (8, 2), (6, 2), (16, 1)])
+@pytest.mark.parametrize("bs", [16, 64, 48])
+def test_prefill_head_sizes_192_and_256(dtype, D, heads, bs, cuda_device):
+    """Head sizes 192 and 256 over 16-bit caches run on the one-tile tcgen05 kernel (one CTA per SM, all 512
+    tensor-memory columns): ragged lengths, groups that are and are not powers of two, block sizes of either
+    copy path (48 looks every row up), a window, a sink."""
+    hq, hk = heads
+    run_case(cuda_device, dtype, hq, hk, q_lens=[200, 1, 70, 513], kv_lens=[777, 300, 70, 1500], bs=bs, causal=True,
+             sink=(hq == 8), seed=1920 + D + hq + bs, D=D)
+    run_case(cuda_device, dtype, hq, hk, q_lens=[300, 129], kv_lens=[1000, 700], bs=bs, causal=(hq != 4), sink=False,
+             seed=2560 + D + hq + bs, window=(127, -1) if hq == 16 else (-1, -1), D=D)

@@ -1196,8 +1196,8 @@ cudaError_t launch_prefill_kv(int kv, int head_size, const DecodeParams& p, dim3
   }
 }
 
-// The tcgen05 kernel serves calls whose cache holds the query's 16-bit type with head size 128, once some
-// sequence has more than 64 query rows per kv head (below that its 128-row tiles would be mostly padding).
+// The one-tile tcgen05 kernel serves head size 128 (16-bit and fp8 caches) and head sizes 192 and 256 (16-bit
+// caches), once some sequence has more than 64 query rows per kv head (below that its 128-row tiles would be mostly padding).
 // KVC_PREFILL_LEGACY=1 keeps every call on the mma.sync kernel (for comparisons).
 inline bool prefill_umma_enabled() {
   static const bool off = [] {
@@ -1207,13 +1207,13 @@ inline bool prefill_umma_enabled() {
   return !off;
 }
 inline bool prefill_uses_umma(int kv_dtype, int64_t head_size, int64_t max_rows_per_kv_head) {
-  (void)kv_dtype;  // 16-bit and fp8 caches alike
-  return prefill_umma_enabled() && head_size == 128 && max_rows_per_kv_head > kPrefillRows;
+  const bool shape_ok = head_size == 128 || ((head_size == 192 || head_size == 256) && kv_dtype == KVC_KV_AUTO);
+  return prefill_umma_enabled() && shape_ok && max_rows_per_kv_head > kPrefillRows;
 }
 
-template <typename TQ, int KV>
+template <typename TQ, int KV, int D>
 cudaError_t launch_prefill_umma(const DecodeParams& p, dim3 grid, cudaStream_t st) {
-  using Cfg = UmmaPrefillCfg<TQ, KV, 128>;
+  using Cfg = UmmaPrefillCfg<TQ, KV, D>;
   static std::once_flag once[64];
   static cudaError_t attr_err[64];
   int dev = 0;
@@ -1221,15 +1221,15 @@ cudaError_t launch_prefill_umma(const DecodeParams& p, dim3 grid, cudaStream_t s
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   std::call_once(once[dev], [&] {
-    attr_err[dev] = cudaFuncSetAttribute(paged_prefill_umma_kernel<TQ, KV, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err[dev] = cudaFuncSetAttribute(paged_prefill_umma_kernel<TQ, KV, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
-    // two CTAs per SM need the whole shared-memory carve-out
+    // two CTAs per SM (or one with 190 KB) need the whole shared-memory carve-out
     if (attr_err[dev] == cudaSuccess)
-      attr_err[dev] = cudaFuncSetAttribute(paged_prefill_umma_kernel<TQ, KV, 128>,
+      attr_err[dev] = cudaFuncSetAttribute(paged_prefill_umma_kernel<TQ, KV, D>,
                                            cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (getenv("KVC_DEBUG_OCCUPANCY")) {
       int ctas = -1;
-      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, paged_prefill_umma_kernel<TQ, KV, 128>, kUmmaThreads, Cfg::kSmemBytes);
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, paged_prefill_umma_kernel<TQ, KV, D>, kUmmaThreads, Cfg::kSmemBytes);
       fprintf(stderr, "kvc: paged_prefill_umma_kernel: %d CTAs per SM (%d bytes of shared memory each)\n", ctas,
               Cfg::kSmemBytes);
     }
@@ -1245,15 +1245,17 @@ cudaError_t launch_prefill_umma(const DecodeParams& p, dim3 grid, cudaStream_t s
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, paged_prefill_umma_kernel<TQ, KV, 128>, p);
+  return cudaLaunchKernelEx(&cfg, paged_prefill_umma_kernel<TQ, KV, D>, p);
 }
 
 template <typename TQ>
-cudaError_t launch_prefill_umma_kv(int kv, const DecodeParams& p, dim3 grid, cudaStream_t st) {
+cudaError_t launch_prefill_umma_kv(int kv, int head_size, const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  if (head_size == 192) return launch_prefill_umma<TQ, KVC_KV_AUTO, 192>(p, grid, st);
+  if (head_size == 256) return launch_prefill_umma<TQ, KVC_KV_AUTO, 256>(p, grid, st);
   switch (kv) {
-    case KVC_KV_AUTO: return launch_prefill_umma<TQ, KVC_KV_AUTO>(p, grid, st);
-    case KVC_KV_FP8_E4M3: return launch_prefill_umma<TQ, KVC_KV_FP8_E4M3>(p, grid, st);
-    default: return launch_prefill_umma<TQ, KVC_KV_FP8_E5M2>(p, grid, st);
+    case KVC_KV_AUTO: return launch_prefill_umma<TQ, KVC_KV_AUTO, 128>(p, grid, st);
+    case KVC_KV_FP8_E4M3: return launch_prefill_umma<TQ, KVC_KV_FP8_E4M3, 128>(p, grid, st);
+    default: return launch_prefill_umma<TQ, KVC_KV_FP8_E5M2, 128>(p, grid, st);
   }
 }
 
@@ -1626,8 +1628,9 @@ KVC_API int kvc_paged_attention(void* out, const void* query, const void* key_ca
               ? launch_prefill_pair_kv<__half>(kv_dtype, static_cast<int>(head_size), pp, q_dtype, total_q, num_seqs, st)
               : launch_prefill_pair_kv<__nv_bfloat16>(kv_dtype, static_cast<int>(head_size), pp, q_dtype, total_q, num_seqs, st);
     else if (use_umma)
-      e = (q_dtype == KVC_IN_F16) ? launch_prefill_umma_kv<__half>(kv_dtype, pp, pgrid, st)
-                                  : launch_prefill_umma_kv<__nv_bfloat16>(kv_dtype, pp, pgrid, st);
+      e = (q_dtype == KVC_IN_F16)
+              ? launch_prefill_umma_kv<__half>(kv_dtype, static_cast<int>(head_size), pp, pgrid, st)
+              : launch_prefill_umma_kv<__nv_bfloat16>(kv_dtype, static_cast<int>(head_size), pp, pgrid, st);
     else
       e = (q_dtype == KVC_IN_F16) ? launch_prefill_kv<__half>(kv_dtype, static_cast<int>(head_size), pp, pgrid, st)
                                   : launch_prefill_kv<__nv_bfloat16>(kv_dtype, static_cast<int>(head_size), pp, pgrid, st);

@@ -20,8 +20,11 @@
 //      S(i+2) = Q K(i+2)^T (M = 128, N = 64, K = 16, D / 16 instructions, both operands from shared memory), each
 //      followed by a commit to its mbarrier.  The tensor pipe runs one thread's instructions in order, which is
 //      what lets P(i) and S(i+2) share columns.
-// Two CTAs share an SM (shared memory is sized for exactly two, and each allocates 256 of the 512 tensor-memory
-// columns, so an allocation never waits).
+// Head size 128: two CTAs share an SM (shared memory is sized for exactly two, and each allocates 256 of the 512
+// tensor-memory columns, so an allocation never waits).  Head sizes 192 and 256 (16-bit caches): the accumulator
+// alone takes 192 or 256 columns and the operand tiles 144 or 192 KB, so an SM holds one CTA, which allocates
+// all 512 columns; each product O += P V then covers 192 or 256 columns, so the tensor pipe has two to three
+// times the work per score and the softmax threads are no longer what the tile waits for.
 //
 // Every wait on an mbarrier is bounded; a wait that gives up sets the CTA's abort word, the CTA runs to its
 // end, frees its tensor memory and raises g_umma_status.
@@ -35,7 +38,6 @@ namespace {
 constexpr int kUmmaRows = 128;
 constexpr int kUmmaSoftmaxThreads = 256;  // two warpgroups: both own all 128 rows, each one half of a tile's 64 columns
 constexpr int kUmmaThreads = kUmmaSoftmaxThreads + 32;  // and one warp that issues the matrix products
-constexpr uint32_t kUmmaTmemCols = 256;
 constexpr uint32_t kUmmaColS = 0;
 constexpr uint32_t kUmmaColO = 128;
 
@@ -56,27 +58,31 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 template <typename TQ, int KV, int D>
 struct UmmaPrefillCfg {
   using T16 = std::conditional_t<KV == KVC_KV_AUTO, TQ, __half>;  // operand type of the matrix products
-  static_assert(D == 128, "head size 128");
+  static_assert(D == 128 || ((D == 192 || D == 256) && KV == KVC_KV_AUTO),
+                "head size 128, or 192 / 256 over 16-bit caches");
+  static constexpr int kCtasPerSm = D == 128 ? 2 : 1;
+  static constexpr uint32_t kTmemCols = D == 128 ? 256 : 512;  // scores 128 + accumulator D, a power of two
   static constexpr int kTile = 64;
   static constexpr int kHalves = D / 64;                     // 128-byte-wide operand tiles per row
   static constexpr int kQHalfBytes = kUmmaRows * 128;        // 16 KB
-  static constexpr int kQBytes = kQHalfBytes * kHalves;      // 32 KB
+  static constexpr int kQBytes = kQHalfBytes * kHalves;      // 32 KB at head size 128
   static constexpr int kKVHalfBytes = kTile * 128;           // 8 KB
-  static constexpr int kKVBytes = kKVHalfBytes * kHalves;    // one K or V tile: 16 KB
+  static constexpr int kKVBytes = kKVHalfBytes * kHalves;    // one K or V tile: 16 KB at head size 128
   static constexpr int kStages = 2;
   static constexpr int kOffQ = 0;
   static constexpr int kOffKV = kOffQ + kQBytes;             // [stage][K, V]
   static constexpr int kOffBar = kOffKV + kStages * 2 * kKVBytes;  // four mbarriers, tensor-memory slot, abort word
   static constexpr int kOffXch = kOffBar + 48;               // the warpgroups' exchange: [tile parity][warpgroup][row]
   static constexpr int kSmemBytes = kOffXch + 4 * kUmmaRows * 4;
-  // two CTAs per SM: 2 x (bytes + 1 KB the system keeps per CTA) within the SM's 228 KB
-  static_assert(2 * (kSmemBytes + 1024) <= 233472, "two CTAs per SM");
-  // and never three, which could ask for more tensor memory than an SM has
-  static_assert(3 * (kSmemBytes + 1024) > 233472, "at most two CTAs per SM");
+  // kCtasPerSm CTAs per SM: each takes its bytes + 1 KB the system keeps per CTA out of the SM's 228 KB
+  static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 233472, "the CTAs of an SM fit its shared memory");
+  // and never one more, which could ask for more tensor memory than an SM has
+  static_assert((kCtasPerSm + 1) * (kSmemBytes + 1024) > 233472, "no further CTA fits");
+  static_assert(kCtasPerSm * kTmemCols <= 512 && kUmmaColO + D <= kTmemCols, "tensor-memory columns");
 };
 
 template <typename TQ, int KV, int D>
-__global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kUmmaThreads, (UmmaPrefillCfg<TQ, KV, D>::kCtasPerSm)) paged_prefill_umma_kernel(const DecodeParams p) {
   using Cfg = UmmaPrefillCfg<TQ, KV, D>;
   using T16 = typename Cfg::T16;
   constexpr bool kFp8 = KV != KVC_KV_AUTO;
@@ -153,16 +159,19 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
     *abort_word = 0;
     mbar_init_fence();
   }
-  if (warp == 0) tmem_alloc(tmem_slot, kUmmaTmemCols);
+  if (warp == 0) tmem_alloc(tmem_slot, Cfg::kTmemCols);
 
-  // ---- producer: thread t copies chunk t % 16 of rows t / 16 + 8 i of a K or a V tile ----------------------
+  // ---- producer: thread t copies chunk t % (D / 8) of rows t / (D / 8) + kRowsPerPass i of a K or a V tile -------
   const int32_t* table = p.block_table + seq * p.block_table_stride;
   const int64_t head_off = static_cast<int64_t>(kvh) * p.head_stride;
   // The thread's chunk of row r0 + 16 i sits 2048 i bytes after its chunk of row r0 (the swizzle repeats every
   // 8 rows).  With power-of-two blocks of at least 64 tokens a tile lies inside one block: one table lookup per
   // tile and a constant pointer step per row; other block sizes look every row up.
   constexpr int kChunks = D / 8;  // 16-byte chunks per row
-  constexpr int kRowsPerPass = kUmmaSoftmaxThreads / kChunks;
+  // rows per pass: a multiple of the swizzle period of 8 rows (16, 8, 8 for head sizes 128, 192, 256; at 192 the
+  // last 64 softmax threads copy nothing)
+  constexpr int kRowsPerPass = (kUmmaSoftmaxThreads / kChunks) / 8 * 8;
+  const bool loader = tid < kRowsPerPass * kChunks;
   const int ld_r0 = tid / kChunks, ld_col = tid % kChunks;
   const uint32_t ld_dst = (ld_col >> 3) * Cfg::kKVHalfBytes + swizzled_offset(ld_r0, ld_col & 7);
   const bool tile_in_block = p.bs_shift >= 6;
@@ -173,6 +182,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
     return (tile_in_block && tile < tile_end) ? __ldg(table + ((tile * TN) >> p.bs_shift)) : 0;
   };
   auto load_rows = [&](int tile, const void* cache, unsigned char* dst_tile, int32_t blk) {
+    if (!loader) return;
     const int rows_left = n - tile * TN;
     const uint32_t dst0 = smem_addr(dst_tile) + ld_dst;
     if (tile_in_block) {
@@ -533,7 +543,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 2) paged_prefill_umma_kernel(con
   }
   fence_before_thread_sync();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, kUmmaTmemCols);
+  if (warp == 0) tmem_dealloc(tmem, Cfg::kTmemCols);
 }
 
 // The give-up path of the bounded waits, run on purpose: one CTA allocates tensor memory, waits on an mbarrier
