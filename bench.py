@@ -28,7 +28,8 @@ on the data path; NCCL only carries the barrier and the max-over-ranks of the ti
 
 The ops around the cache write have workloads of their own, measured and reported the same way
 (--workload mla-fp8 | gather | quant-static | quant-token | rope | rope-cache-fp8 | decode-bf16 |
-decode-fp8 | prefill-bf16 | prefill-fp8; sizes in benchmark/op_workloads.py).  Their e2e figure moves the step's inputs from pinned
+decode-fp8 | prefill-bf16 | prefill-fp8 | ...; sizes in benchmark/op_workloads.py).  The default single-GPU C4 line
+carries a short figure of each of them under "ops" (and of the metric's other configurations under "also").  Their e2e figure moves the step's inputs from pinned
 host memory through torch copies, calls the C ABI and reads the step's result back.
 """
 from __future__ import annotations
@@ -670,6 +671,27 @@ def run_b200_arm(ns):
             del c
             torch.cuda.empty_cache()
 
+    # ---------------------------------------------------------------- N = 1: the ops around the cache write
+    ops = None
+    if also is not None:
+        ops = {}
+        tpeak, _ = measured_tensor_peak()
+        for name, make in op_workloads.BY_NAME.items():
+            ow = make()
+            ostep, oe2e, _, _ = ow.make_steps(dev, 2)
+            ot = time_passes(ostep, ns.steps, ns.warmup, None, local, 0.05)
+            sec = ot["ms_per_step"] * 1e-3
+            if ow.flops > 0:
+                ach, unit, bound, pk = ow.flops / sec / 1e12, "TFLOP/s", "tensor", tpeak
+            else:
+                ach, unit, bound, pk = ow.algorithmic_bytes / sec / 1e9, "GB/s", "hbm", peak
+            ops[name] = {"us_per_step": sec * 1e6, "tokens_per_s": ow.units_per_step / sec, "bound": bound,
+                         "achieved": ach, "unit": unit, "frac": ach / pk, "repeats": ot["repeats"],
+                         "workload": ow.describe}
+            launches += ot["launches"] * ow.launches_per_step
+            del ostep, oe2e, ow
+            torch.cuda.empty_cache()
+
     # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1)
     cpu = None
     if rank == 0 and world == 1 and not ns.no_cpu_baseline:
@@ -716,6 +738,8 @@ def run_b200_arm(ns):
             line["weak"] = weak
         if also is not None:
             line["also"] = also
+        if ops is not None:
+            line["ops"] = ops
         if ns.shard_of is not None:
             line["config"]["sharding"] += f" (one GPU running the share of rank 0 of {ns.shard_of})"
     if dist is not None:

@@ -317,10 +317,11 @@ def decode(kv: str) -> OpWorkload:
 
 
 # ---------------------------------------------------------------------------------------------- prefill attention
-def prefill(kv: str, S: int = 4, L: int = 2048) -> OpWorkload:
+def prefill(kv: str, S: int = 4, L: int = 2048, D: int = 128) -> OpWorkload:
     """Causal attention of S whole prompts of L tokens over their own paged keys/values (query length = cached
     length): the many-rows path of paged attention.  Compute-bound, unlike everything else here."""
-    hq, hk, D, bs = 64, 8, 128, 64
+    # 8 kv heads; the q heads shrink with the head size so that a token's query row stays 8192 elements wide
+    hq, hk, bs = {64: 64, 128: 64, 192: 48, 256: 32}[D], 8, 64
     es = 2 if kv == "auto" else 1
     blocks_per_seq = L // bs
 
@@ -377,7 +378,7 @@ def prefill(kv: str, S: int = 4, L: int = 2048) -> OpWorkload:
 
     tag = "bf16" if kv == "auto" else "fp8"
     return OpWorkload(
-        f"prefill-{tag}" + ("" if (S, L) == (4, 2048) else f"-{L // 1024}k"),
+        f"prefill-{tag}" + ("" if (S, L) == (4, 2048) else f"-{L // 1024}k") + ("" if D == 128 else f"-d{D}"),
         f"paged_attention_prefill_{tag}_cache_tokens_per_s",
         f"causal paged attention of {S} whole prompts of {L} tokens, {hq} q / {hk} kv heads x {D}, cache "
         f"{'bfloat16' if kv == 'auto' else 'fp8_e4m3'}, block_size={bs} (CPU oracle: a {256}-token prompt)",
@@ -398,6 +399,9 @@ BY_NAME: dict[str, Callable[[], OpWorkload]] = {
     "prefill-fp8": lambda: prefill("fp8"),
     "prefill-bf16-8k": lambda: prefill("auto", 1, 8192),
     "prefill-fp8-8k": lambda: prefill("fp8", 1, 8192),
+    "prefill-bf16-8k-d64": lambda: prefill("auto", 1, 8192, 64),
+    "prefill-bf16-8k-d192": lambda: prefill("auto", 1, 8192, 192),
+    "prefill-bf16-8k-d256": lambda: prefill("auto", 1, 8192, 256),
 }
 
 
