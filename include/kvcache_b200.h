@@ -361,9 +361,9 @@ KVC_API int64_t kvc_paged_decode_workspace_bytes(int64_t num_seqs, int64_t num_h
  * key/value tile; queries, keys, values and results move by TMA tile copies (power-of-two block sizes of at
  * least 8 tokens; other block sizes take a one-tile variant with ordinary asynchronous copies); both products
  * are tcgen05.mma with scores, probabilities and accumulators in tensor memory; fp8 caches are widened to fp16
- * in shared memory.  Head sizes 192 and 256 over 16-bit caches take the one-tile variant as well (one CTA per SM).
- * Otherwise (short runs, fp8 caches with head sizes other than 128) it is the mma.sync kernel in which a CTA
- * owns 64 rows.  In such a mixed call the decode part is not split over the sequence.  At most 65535 sequences per call.
+ * in shared memory.  Head sizes 192 and 256 (one CTA per SM) and fp8 caches of head size 64 take the one-tile
+ * variant as well.  Calls whose longest run has at most 64 rows per kv head take the mma.sync kernel in which a
+ * CTA owns 64 rows.  In such a mixed call the decode part is not split over the sequence.  At most 65535 sequences per call.
  *
  * kvc_paged_attention_device_status waits for the device's earlier work and reads the tcgen05 kernel's status
  * word: 0 = fine; 1 = a bounded wait on an mbarrier gave up (results of that call are then undefined; the

@@ -200,3 +200,27 @@ def test_prefill_head_sizes_192_and_256(dtype, D, heads, bs, cuda_device):
              sink=(hq == 8), seed=1920 + D + hq + bs, D=D)
     run_case(cuda_device, dtype, hq, hk, q_lens=[300, 129], kv_lens=[1000, 700], bs=bs, causal=(hq != 4), sink=False,
              seed=2560 + D + hq + bs, window=(127, -1) if hq == 16 else (-1, -1), D=D)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D", [64, 192, 256])
+@pytest.mark.parametrize("kv,descale", [("fp8", 0.04), ("fp8_e5m2", 0.002)])
+@pytest.mark.parametrize("bs", [16, 64, 48])
+def test_prefill_fp8_caches_other_head_sizes(dtype, D, kv, descale, bs, cuda_device):
+    """fp8 rows of 64, 192 and 256 bytes are widened in place like those of 128 (a thread owns a quarter of a row);
+    groups of 4 and 3, a sink, a window."""
+    run_case(cuda_device, dtype, 8, 2, q_lens=[300, 1, 70, 140], kv_lens=[777, 300, 70, 1100], bs=bs, causal=True,
+             sink=(bs == 64), seed=3000 + D + bs, kv=kv, descale=descale, D=D)
+    run_case(cuda_device, dtype, 6, 2, q_lens=[150, 260], kv_lens=[400, 900], bs=bs, causal=True, sink=False,
+             seed=3100 + D + bs, kv=kv, descale=descale, window=(200, -1), D=D)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("heads", [(8, 2), (6, 2)])
+def test_prefill_head_size_64_block_size_that_is_no_tma_box(dtype, heads, cuda_device):
+    """Head size 64 with 48-token blocks: the one-tile kernel (two CTAs per SM, 64 accumulator columns)."""
+    hq, hk = heads
+    run_case(cuda_device, dtype, hq, hk, q_lens=[200, 1, 70, 513], kv_lens=[777, 300, 70, 1500], bs=48, causal=True,
+             sink=(hq == 8), seed=6448 + hq, D=64)
+    run_case(cuda_device, dtype, hq, hk, q_lens=[300, 129], kv_lens=[1000, 700], bs=48, causal=False, sink=False,
+             seed=6449 + hq, D=64)

@@ -1196,8 +1196,8 @@ cudaError_t launch_prefill_kv(int kv, int head_size, const DecodeParams& p, dim3
   }
 }
 
-// The one-tile tcgen05 kernel serves head size 128 (16-bit and fp8 caches) and head sizes 192 and 256 (16-bit
-// caches), once some sequence has more than 64 query rows per kv head (below that its 128-row tiles would be mostly padding).
+// The one-tile tcgen05 kernel serves every head size (64, 128, 192, 256) over 16-bit and fp8 caches, once some
+// sequence has more than 64 query rows per kv head (below that its 128-row tiles would be mostly padding).
 // KVC_PREFILL_LEGACY=1 keeps every call on the mma.sync kernel (for comparisons).
 inline bool prefill_umma_enabled() {
   static const bool off = [] {
@@ -1207,7 +1207,8 @@ inline bool prefill_umma_enabled() {
   return !off;
 }
 inline bool prefill_uses_umma(int kv_dtype, int64_t head_size, int64_t max_rows_per_kv_head) {
-  const bool shape_ok = head_size == 128 || ((head_size == 192 || head_size == 256) && kv_dtype == KVC_KV_AUTO);
+  (void)kv_dtype;  // 16-bit and fp8 caches alike
+  const bool shape_ok = head_size == 64 || head_size == 128 || head_size == 192 || head_size == 256;
   return prefill_umma_enabled() && shape_ok && max_rows_per_kv_head > kPrefillRows;
 }
 
@@ -1248,14 +1249,22 @@ cudaError_t launch_prefill_umma(const DecodeParams& p, dim3 grid, cudaStream_t s
   return cudaLaunchKernelEx(&cfg, paged_prefill_umma_kernel<TQ, KV, D>, p);
 }
 
+template <typename TQ, int D>
+cudaError_t launch_prefill_umma_d(int kv, const DecodeParams& p, dim3 grid, cudaStream_t st) {
+  switch (kv) {
+    case KVC_KV_AUTO: return launch_prefill_umma<TQ, KVC_KV_AUTO, D>(p, grid, st);
+    case KVC_KV_FP8_E4M3: return launch_prefill_umma<TQ, KVC_KV_FP8_E4M3, D>(p, grid, st);
+    default: return launch_prefill_umma<TQ, KVC_KV_FP8_E5M2, D>(p, grid, st);
+  }
+}
+
 template <typename TQ>
 cudaError_t launch_prefill_umma_kv(int kv, int head_size, const DecodeParams& p, dim3 grid, cudaStream_t st) {
-  if (head_size == 192) return launch_prefill_umma<TQ, KVC_KV_AUTO, 192>(p, grid, st);
-  if (head_size == 256) return launch_prefill_umma<TQ, KVC_KV_AUTO, 256>(p, grid, st);
-  switch (kv) {
-    case KVC_KV_AUTO: return launch_prefill_umma<TQ, KVC_KV_AUTO, 128>(p, grid, st);
-    case KVC_KV_FP8_E4M3: return launch_prefill_umma<TQ, KVC_KV_FP8_E4M3, 128>(p, grid, st);
-    default: return launch_prefill_umma<TQ, KVC_KV_FP8_E5M2, 128>(p, grid, st);
+  switch (head_size) {
+    case 64: return launch_prefill_umma_d<TQ, 64>(kv, p, grid, st);
+    case 128: return launch_prefill_umma_d<TQ, 128>(kv, p, grid, st);
+    case 192: return launch_prefill_umma_d<TQ, 192>(kv, p, grid, st);
+    default: return launch_prefill_umma_d<TQ, 256>(kv, p, grid, st);
   }
 }
 

@@ -20,8 +20,8 @@
 //      S(i+2) = Q K(i+2)^T (M = 128, N = 64, K = 16, D / 16 instructions, both operands from shared memory), each
 //      followed by a commit to its mbarrier.  The tensor pipe runs one thread's instructions in order, which is
 //      what lets P(i) and S(i+2) share columns.
-// Head size 128: two CTAs share an SM (shared memory is sized for exactly two, and each allocates 256 of the 512
-// tensor-memory columns, so an allocation never waits).  Head sizes 192 and 256 (16-bit caches): the accumulator
+// Head sizes 64 and 128: two CTAs share an SM (shared memory is sized for exactly two, and each allocates 256 of the 512
+// tensor-memory columns, so an allocation never waits).  Head sizes 192 and 256: the accumulator
 // alone takes 192 or 256 columns and the operand tiles 144 or 192 KB, so an SM holds one CTA, which allocates
 // all 512 columns; each product O += P V then covers 192 or 256 columns, so the tensor pipe has two to three
 // times the work per score and the softmax threads are no longer what the tile waits for.
@@ -58,10 +58,9 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 template <typename TQ, int KV, int D>
 struct UmmaPrefillCfg {
   using T16 = std::conditional_t<KV == KVC_KV_AUTO, TQ, __half>;  // operand type of the matrix products
-  static_assert(D == 128 || ((D == 192 || D == 256) && KV == KVC_KV_AUTO),
-                "head size 128, or 192 / 256 over 16-bit caches");
-  static constexpr int kCtasPerSm = D == 128 ? 2 : 1;
-  static constexpr uint32_t kTmemCols = D == 128 ? 256 : 512;  // scores 128 + accumulator D, a power of two
+  static_assert(D == 64 || D == 128 || D == 192 || D == 256, "head sizes 64, 128, 192, 256");
+  static constexpr int kCtasPerSm = D <= 128 ? 2 : 1;
+  static constexpr uint32_t kTmemCols = D <= 128 ? 256 : 512;  // scores 128 + accumulator D, a power of two
   static constexpr int kTile = 64;
   static constexpr int kHalves = D / 64;                     // 128-byte-wide operand tiles per row
   static constexpr int kQHalfBytes = kUmmaRows * 128;        // 16 KB
@@ -73,7 +72,10 @@ struct UmmaPrefillCfg {
   static constexpr int kOffKV = kOffQ + kQBytes;             // [stage][K, V]
   static constexpr int kOffBar = kOffKV + kStages * 2 * kKVBytes;  // four mbarriers, tensor-memory slot, abort word
   static constexpr int kOffXch = kOffBar + 48;               // the warpgroups' exchange: [tile parity][warpgroup][row]
-  static constexpr int kSmemBytes = kOffXch + 4 * kUmmaRows * 4;
+  // head size 64 would leave room for more than two CTAs (which together could ask for more tensor memory than
+  // an SM has): its request is padded to the size that admits exactly two
+  static constexpr int kSmemUsed = kOffXch + 4 * kUmmaRows * 4;
+  static constexpr int kSmemBytes = (kCtasPerSm == 2 && 3 * (kSmemUsed + 1024) <= 233472) ? 233472 / 3 : kSmemUsed;
   // kCtasPerSm CTAs per SM: each takes its bytes + 1 KB the system keeps per CTA out of the SM's 228 KB
   static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 233472, "the CTAs of an SM fit its shared memory");
   // and never one more, which could ask for more tensor memory than an SM has
@@ -212,15 +214,18 @@ __global__ void __launch_bounds__(kUmmaThreads, (UmmaPrefillCfg<TQ, KV, D>::kCta
       }
     }
   };
-  // fp8 caches: a row is 128 bytes.  Thread t copies 32 of them (quarter t % 4 of row t / 4) with cp.async into
-  // the upper half of the tile's slot, where raw row r occupies the 128 bytes that row r of the second D half
-  // will occupy; later the same thread reads its 32 bytes back, widens them to fp16 (exact) and stores the 64
-  // bytes as four chunks of the swizzled 16-bit layout.  The only bytes a store can overwrite before they are
-  // read are those of the same row, which the same warp reads: a __syncwarp between the reads and the stores
-  // is all the ordering the conversion needs.
+  // fp8 caches: a row is D bytes.  Thread t copies a quarter of one (quarter t % 4 of row t / 4, D / 64 chunks of
+  // 16 bytes) with cp.async into the tile's slot as raw bytes, later reads them back, widens them to fp16 (exact)
+  // and stores them as chunks of the swizzled 16-bit layout.  Raw chunk k of row r lies in line r (128 bytes) of
+  // operand half kHalves - 1 - k / 8, at byte 16 (k % 8): all of a row's raw bytes sit on bytes of the same row's
+  // 16-bit lines, and the last half is overwritten by the widening of the last raw bytes.  The only bytes a store
+  // can overwrite before they are read are therefore those of the same row, which the same warp reads: a
+  // __syncwarp between the reads and the stores is all the ordering the conversion needs.
+  constexpr int kRawChunks = D / 64;  // 16-byte chunks of raw bytes per thread
   struct Fp8Quarter {
-    uint4 a, b;
+    uint4 c[kRawChunks];
   };
+  auto raw_offset = [](int r, int k) { return (Cfg::kHalves - 1 - (k >> 3)) * Cfg::kKVHalfBytes + r * 128 + (k & 7) * 16; };
   auto issue_raw_fp8 = [&](int tile, const void* cache, int32_t blk, unsigned char* dst_tile) {
     const int r = tid >> 2, token = tile * TN + r;
     const bool valid = token < n;
@@ -234,30 +239,33 @@ __global__ void __launch_bounds__(kUmmaThreads, (UmmaPrefillCfg<TQ, KV, D>::kCta
               static_cast<int64_t>(token - blk_idx * p.block_size) * p.page_stride;
       }
     }
-    const unsigned char* src = static_cast<const unsigned char*>(cache) + off + head_off + (tid & 3) * 32;
-    const uint32_t dst = smem_addr(dst_tile + Cfg::kKVHalfBytes) + r * 128 + (tid & 3) * 32;
-    cp_async_16(dst, src, valid ? 16 : 0);
-    cp_async_16(dst + 16, src + 16, valid ? 16 : 0);
+    const unsigned char* src = static_cast<const unsigned char*>(cache) + off + head_off + (tid & 3) * (D / 4);
+#pragma unroll
+    for (int i = 0; i < kRawChunks; ++i)
+      cp_async_16(smem_addr(dst_tile) + raw_offset(r, (tid & 3) * kRawChunks + i), src + 16 * i, valid ? 16 : 0);
   };
   auto read_raw_fp8 = [&](const unsigned char* dst_tile) {
-    const uint4* raw = reinterpret_cast<const uint4*>(dst_tile + Cfg::kKVHalfBytes + (tid >> 2) * 128 + (tid & 3) * 32);
     Fp8Quarter q;
-    q.a = raw[0];
-    q.b = raw[1];
+#pragma unroll
+    for (int i = 0; i < kRawChunks; ++i)
+      q.c[i] = *reinterpret_cast<const uint4*>(dst_tile + raw_offset(tid >> 2, (tid & 3) * kRawChunks + i));
     return q;
   };
   auto store_fp8 = [&](const Fp8Quarter& q, unsigned char* dst_tile) {
-    const int r = tid >> 2, qu = tid & 3;  // fp16 chunks 4 qu .. 4 qu + 3 of the row: half qu / 2
-    unsigned char* dst = dst_tile + (qu >> 1) * Cfg::kKVHalfBytes;
-    const uint32_t src[8] = {q.a.x, q.a.y, q.a.z, q.a.w, q.b.x, q.b.y, q.b.z, q.b.w};
+    const int r = tid >> 2;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      uint4 o;
-      o.x = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2 * k]);
-      o.y = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2 * k] >> 16);
-      o.z = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2 * k + 1]);
-      o.w = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2 * k + 1] >> 16);
-      *reinterpret_cast<uint4*>(dst + swizzled_offset(r, (qu & 1) * 4 + k)) = o;
+    for (int i = 0; i < kRawChunks; ++i) {
+      const uint32_t src[4] = {q.c[i].x, q.c[i].y, q.c[i].z, q.c[i].w};
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {  // raw chunk j holds the elements of 16-bit chunks 2 j and 2 j + 1
+        uint4 o;
+        o.x = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2 * k]);
+        o.y = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2 * k] >> 16);
+        o.z = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2 * k + 1]);
+        o.w = fp8x2_to_f16x2<kFp8 ? KV : KVC_KV_FP8_E4M3>(src[2 * k + 1] >> 16);
+        const int chunk = 2 * ((tid & 3) * kRawChunks + i) + k;  // 16-bit chunk of the row: half chunk / 8
+        *reinterpret_cast<uint4*>(dst_tile + (chunk >> 3) * Cfg::kKVHalfBytes + swizzled_offset(r, chunk & 7)) = o;
+      }
     }
   };
   auto k_slot = [&](int i) { return s_kv + (i & 1) * 2 * KVB; };

@@ -2,8 +2,8 @@
 there): paged keys/values (``block_table`` + ``seqused_k``) or the non-paged form (``cu_seqlens_k``), causal
 mask, sliding windows, sink -- decode (one query token per sequence) at HBM speed; several query tokens per
 sequence on the same kernel (runs of at most 16 rows per kv head), on a tcgen05 kernel with scores and
-accumulators in tensor memory (longer runs; every head size over 16-bit caches, head size 128 over fp8 caches) or on an
-mma.sync kernel (what is left).
+accumulators in tensor memory (runs of more than 64 rows per kv head; every head size, 16-bit and fp8 caches) or on an
+mma.sync kernel (runs of 17 to 64 rows).
 softcap, alibi, dropout and returning the softmax are not supported.  On top of the reference,
 the cache may hold fp8 bytes: pass ``k_descale`` / ``v_descale`` (the inverse of the k_scale / v_scale the
 cache was written with), which the reference's interface names but rejects."""
