@@ -164,11 +164,6 @@ struct PairItem {
   bool has_b;
 };
 
-#ifndef KVC_PAIR_EXP16
-#define KVC_PAIR_EXP16 1
-#endif
-constexpr bool kPairExp16 = KVC_PAIR_EXP16 != 0;  // fp16 products: exponentials as ex2.approx.f16x2
-
 template <typename TQ, int KV, int HEAD>
 __global__ void __launch_bounds__(kPairThreads, 1)
     paged_prefill_pair_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tmap_k,
@@ -688,56 +683,24 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           }
           // 64 scores become 32 words of two 16-bit probabilities, stored as soon as they are complete
           const float2 sc2 = make_float2(scale2, scale2), nm2 = make_float2(neg_ms, neg_ms);
-          if constexpr (kPairExp16 && std::is_same_v<T16, __half>) {
-            // fp16 probabilities: the exponent is rounded to fp16 first and one ex2.approx.f16x2 yields both
-            // probabilities of a pair already packed (half the special-function work, four instructions per pair
-            // instead of five; results below 2^-14 stay subnormal, not zero).  The row sum is taken over the very
-            // values the product will use, in eight fp16 pairs of partial sums (8 values each, at most 2^11).
-            uint32_t hs[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+          float2 l_add[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              uint32_t wd[32];
+          for (int h = 0; h < 2; ++h) {
+            uint32_t wd[32];
 #pragma unroll
-              for (int cc = 0; cc < 2; ++cc)
+            for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                  const int c = 2 * h + cc;
-                  const float2 e = __ffma2_rn(make_float2(__uint_as_float(sa[c][i]), __uint_as_float(sa[c][i + 1])), sc2, nm2);
-                  const uint32_t e16 = pack2<__half>(e.x, e.y);
-                  uint32_t pw;
-                  asm("ex2.approx.f16x2 %0, %1;" : "=r"(pw) : "r"(e16));
-                  asm("add.rn.f16x2 %0, %0, %1;" : "+r"(hs[(i >> 1) & 7]) : "r"(pw));
-                  wd[cc * 16 + (i >> 1)] = pw;
-                }
-              tmem_st_32x32(t_p + h * 32, wd);
-            }
-            float l_tile = 0.f;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&hs[k]));
-              l_tile += f2.x + f2.y;
-            }
-            l_run += l_tile;
-          } else {
-            float2 l_add[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              uint32_t wd[32];
-#pragma unroll
-              for (int cc = 0; cc < 2; ++cc)
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                  const int c = 2 * h + cc;
-                  const float2 e = __ffma2_rn(make_float2(__uint_as_float(sa[c][i]), __uint_as_float(sa[c][i + 1])), sc2, nm2);
-                  const float2 pr = make_float2(fast_exp2(e.x), fast_exp2(e.y));
-                  l_add[(i >> 1) & 3] = __fadd2_rn(l_add[(i >> 1) & 3], pr);
-                  wd[cc * 16 + (i >> 1)] = pack2<T16>(pr.x, pr.y);
-                }
-              tmem_st_32x32(t_p + h * 32, wd);
-            }
-            l_run += ((l_add[0].x + l_add[0].y) + (l_add[1].x + l_add[1].y)) +
-                     ((l_add[2].x + l_add[2].y) + (l_add[3].x + l_add[3].y));
+              for (int i = 0; i < 32; i += 2) {
+                const int c = 2 * h + cc;
+                const float2 e = __ffma2_rn(make_float2(__uint_as_float(sa[c][i]), __uint_as_float(sa[c][i + 1])), sc2, nm2);
+                const float2 pr = make_float2(fast_exp2(e.x), fast_exp2(e.y));
+                l_add[(i >> 1) & 3] = __fadd2_rn(l_add[(i >> 1) & 3], pr);
+                wd[cc * 16 + (i >> 1)] = pack2<T16>(pr.x, pr.y);
+              }
+            tmem_st_32x32(t_p + h * 32, wd);
           }
+          l_run += ((l_add[0].x + l_add[0].y) + (l_add[1].x + l_add[1].y)) +
+                   ((l_add[2].x + l_add[2].y) + (l_add[3].x + l_add[3].y));
           tmem_st_wait();
           fence_before_thread_sync();
           mbar_arrive(bar_ready + g);
