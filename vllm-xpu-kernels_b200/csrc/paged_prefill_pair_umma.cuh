@@ -6,9 +6,9 @@
 //
 //   warps 0-3   softmax of row tile A: thread r owns row r -- all 128 scores of a tile, the row's running
 //   warps 4-7   maximum and sum, its accumulator row (same for row tile B).  No value ever crosses threads.
-//   warp 8      issues the matrix products (tcgen05.mma, M = 128, N = 128, K = 16, fp32 accumulation in
-//               tensor memory): S = Q K^T with both operands in shared memory, O += P V with P read from tensor
-//               memory and V as an MN-major operand.
+//   warp 8      issues O += P V (tcgen05.mma, M = 128, N = 128, K = 16, fp32 accumulation in tensor memory; P
+//               read from tensor memory, V as an MN-major operand) and an item's first S = Q K^T (both operands
+//               in shared memory); every later S batch is issued by a softmax thread, see below.
 //   warp 9      brings query, key and value tiles in with TMA tile copies (cp.async.bulk.tensor, 128-byte
 //               swizzle, no multicast, this GPU's memory only).  Keys and values come straight from the paged
 //               cache: a tensor map over [block][token in block][kv head][d] makes a cache block's rows one box,
@@ -19,16 +19,21 @@
 //
 // Tensor memory (512 columns, all of the SM's): O_A | O_B | X | P_A | P_B with 128, 128, 128, 64, 64 columns.
 // X holds the scores of whichever row tile's turn it is: a softmax thread moves its row of X into registers
-// at once (128 of the 224 registers it owns) and reports X free, so the issuing warp computes the other row
-// tile's scores, and then this row tile's NEXT scores, while this softmax is still running.  A row tile's chain
-// of dependent steps is thus its softmax alone; the tensor pipe alternates
+// at once (128 of the 224 registers it owns); when the 128 threads of the row tile have done so (a named
+// barrier among them), one of them issues the next use of X itself -- the other row tile's scores of the same
+// key tile, or this row tile's NEXT scores -- while this softmax is still running.  A row tile's chain of
+// dependent steps is thus its softmax alone, and the chain X is handed along,
 //
-//   S_A(j+1)  PV_A(j)  S_B(j+1)  PV_B(j)  S_A(j+2)  PV_A(j+1) ...
+//   S_A(j) -> A reads -> S_B(j) -> B reads -> S_A(j+1) -> A reads -> ...
 //
-// each product batch (8 instructions) gated by one arrival of the softmax threads: X read (for an S batch) or P
-// stored (for a PV batch).  The probabilities have columns of their own, which PV(j) has finished reading before
-// the softmax of tile j + 1 stores into them (the wait for "O += P(j) V(j) complete" that a rescaling of O
-// needs anyway).
+// has one sleeping waiter per link (the readers, woken by the batch's commit) instead of two: with the issuing
+// warp as the middleman of every link, its four wake-ups of about 600 cycles each were what a step of 4 100
+// cycles waited for, not the tensor pipe (2 800) nor the softmax (2 250).  The issuing warp's own batches,
+// O_g += P_g(j) V(j), are gated by the softmax threads' arrival "P stored".  The probabilities have columns of
+// their own, which PV(j) has finished reading before the softmax of tile j + 1 stores into them (the wait for
+// "O += P(j) V(j) complete" that a rescaling of O needs anyway).  tcgen05.commit tracks the instructions of
+// the thread that executes it, so whoever issues a batch also commits it to the scores barrier, and after a
+// tile's last batch to "key slot free", after the item's last to "query rows free".
 //
 // A softmax thread costs about 3.5 instructions per score (one tcgen05.ld of 32 columns per 32 scores, packed
 // fp32 arithmetic, 3-input max, one ex2 per score, 16-bit packing); every fixed per-tile cost is spread over 128
@@ -79,7 +84,7 @@ struct PairCfg {
   static constexpr int kOffV = 4 * kTileBytes;       // [stage]
   static constexpr int kOffStage = 6 * kTileBytes;   // one row tile of results on its way out
   static constexpr int kOffBar = 7 * kTileBytes;     // mbarriers, tensor-memory slot, abort word
-  static constexpr int kBarriers = 23;
+  static constexpr int kBarriers = 24;
   static constexpr int kUsedBytes = kOffBar + kBarriers * 8 + 16;  // + tensor-memory slot and abort word
   // One CTA per SM, whatever the head size: a CTA allocates all of the SM's tensor memory, and a second CTA on
   // the same SM would wait for the first to end while another SM stays empty.  Asking for more than half of an
@@ -164,6 +169,29 @@ struct PairItem {
   bool has_b;
 };
 
+// S = Q_g K^T into the score columns: D / 16 instructions (M 128, N 128, K 16), both operands K-major in shared
+// memory with the 128-byte swizzle.  Built where it is used (the issuing warp and the softmax threads), so that
+// the roles that never issue it keep no registers for it.
+template <typename T16, int D, typename Cfg>
+struct PairScoresIssuer {
+  static constexpr uint32_t kIdesc = umma::instr_desc_f16<T16>(kPairRows, 128, false, false);
+  static constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
+  static constexpr uint32_t kLbo = (16u >> 4) << 16;                            // K-major operands: unused
+  uint32_t q_lo, k_lo0, x_col;
+  __device__ __forceinline__ PairScoresIssuer(const unsigned char* s_q, const unsigned char* s_k, uint32_t x)
+      : q_lo((umma::smem_addr(s_q) >> 4) | kLbo), k_lo0((umma::smem_addr(s_k) >> 4) | kLbo), x_col(x) {}
+  __device__ __forceinline__ void operator()(int g, int k_slot) const {
+    const uint32_t qa = q_lo + g * (Cfg::kTileBytes >> 4);
+    const uint32_t kb = k_lo0 + k_slot * (Cfg::kTileBytes >> 4);
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const uint32_t step = ((kk >> 2) * Cfg::kHalfBytes + (kk & 3) * 32) >> 4;
+      umma::mma_f16_ss(x_col, (static_cast<uint64_t>(kDescHi) << 32) | (qa + step),
+                       (static_cast<uint64_t>(kDescHi) << 32) | (kb + step), kIdesc, kk > 0 ? 1u : 0u);
+    }
+  }
+};
+
 template <typename TQ, int KV, int HEAD>
 __global__ void __launch_bounds__(kPairThreads, 1)
     paged_prefill_pair_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tmap_k,
@@ -195,7 +223,8 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   uint64_t* bar_vfull = bars + 8;
   uint64_t* bar_kfree = bars + 10;  // [stage]    every product that reads the K tile is complete
   uint64_t* bar_vfree = bars + 12;
-  uint64_t* bar_xfree = bars + 14;  // the score columns have been read into registers (128 arrivals per use)
+  uint64_t* bar_xfree = bars + 14;  // the row tile A has read its scores out of X into registers (128 arrivals)
+  uint64_t* bar_xfree_b = bars + 23;  // ... the row tile B
   uint64_t* bar_qfull = bars + 15;  // the query rows have landed (when they come by TMA)
   uint64_t* bar_qfree = bars + 16;  // every product that reads the item's query rows is complete
   uint64_t* bar_stage = bars + 17;  // the staging tile has been read by the TMA unit (or written out by its warps)
@@ -229,6 +258,7 @@ __global__ void __launch_bounds__(kPairThreads, 1)
     mbar_init(bar_o + 1, 1);
     for (int i = 0; i < 8; ++i) mbar_init(bar_kfull + i, 1);  // kfull, vfull, kfree, vfree
     mbar_init(bar_xfree, kPairRows);
+    mbar_init(bar_xfree_b, kPairRows);
     mbar_init(bar_qfull, 1);
     mbar_init(bar_qfree, 1);
     mbar_init(bar_stage, 1);
@@ -308,15 +338,29 @@ __global__ void __launch_bounds__(kPairThreads, 1)
   // start on the next item while the softmax threads still write the last one's results.
   int tiles_done = 0;    // tiles of earlier items (row tile A takes part in every item)
   int tiles_done_b = 0;  // ... of earlier items that had a row tile B
-  int uses_done = 0;     // uses of the score columns X by earlier items
   int items_done = 0;    // earlier items with work
   int stages_done = 0;   // uses of the staging tile by earlier items (one per row tile)
+  bool prev_had_b = false;  // the item before had a row tile B
   auto account = [&](const PairItem& w) {
     stages_done += w.has_b ? 2 : 1;
     tiles_done += w.nt;
     if (w.has_b) tiles_done_b += w.nt;
-    uses_done += (w.has_b ? 2 : 1) * w.nt;
     ++items_done;
+    prev_had_b = w.has_b;
+  };
+
+  auto kfull_of = [&](int j) { return (kFp8 ? bar_kconv : bar_kfull) + ((tiles_done + j) & 1); };
+  auto kfree_of = [&](int j) { return bar_kfree + ((tiles_done + j) & 1); };
+  auto stage_parity = [&](int j) { return static_cast<uint32_t>((tiles_done + j) >> 1) & 1u; };
+  // Use u of an item's score columns is S_A(u / groups) or, with two row tiles, S_B for odd u.  After the batch:
+  // the row tile's scores barrier; after a tile's last batch its K slot is free; after the item's last the query.
+  auto issue_use = [&](const PairScoresIssuer<T16, D, Cfg>& issue_qk, const PairItem& w, int g, int j) {
+    issue_qk(g, (tiles_done + j) & 1);
+    mma_commit(bar_s + g);
+    if (g == (w.has_b ? 1 : 0)) {
+      mma_commit(kfree_of(j));
+      if (j == w.nt - 1) mma_commit(bar_qfree);
+    }
   };
 
   if (warp >= 8) {
@@ -384,24 +428,12 @@ __global__ void __launch_bounds__(kPairThreads, 1)
         }
       } else if (warp == 8) {
         // ====================================================================================== issuing warp
-        constexpr uint32_t kIdescQK = instr_desc_f16<T16>(kPairRows, TN, false, false);
+        const PairScoresIssuer<T16, D, Cfg> issue_qk(s_q, s_k, tmem + kColX);
         constexpr uint32_t kIdescPV = instr_desc_f16<T16>(kPairRows, D, false, true);
         constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version 1, 128-byte swizzle
-        constexpr uint32_t kLboK = (16u >> 4) << 16;                          // K-major operands: unused
-        constexpr uint32_t kLboV = (static_cast<uint32_t>(Cfg::kHalfBytes) >> 4) << 16;  // V: distance of the D halves
         auto make_desc = [](uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; };
-        const uint32_t q_lo = (smem_addr(s_q) >> 4) | kLboK;
-        const uint32_t k_lo0 = (smem_addr(s_k) >> 4) | kLboK;
+        constexpr uint32_t kLboV = (static_cast<uint32_t>(Cfg::kHalfBytes) >> 4) << 16;  // V: distance of the D halves
         const uint32_t v_lo0 = (smem_addr(s_v) >> 4) | kLboV;
-        auto issue_qk = [&](int g, int j) {  // X = Q_g K(j)^T
-          const uint32_t qa = q_lo + g * (Cfg::kTileBytes >> 4);
-          const uint32_t kb = k_lo0 + ((tiles_done + j) & 1) * (Cfg::kTileBytes >> 4);
-#pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t step = ((kk >> 2) * Cfg::kHalfBytes + (kk & 3) * 32) >> 4;
-            mma_f16_ss(tmem + kColX, make_desc(qa + step), make_desc(kb + step), kIdescQK, kk > 0 ? 1u : 0u);
-          }
-        };
         auto issue_pv = [&](int g, int j) {  // O_g (+)= P_g(j) V(j): P_g is 64 columns of two 16-bit values
           const uint32_t vb = v_lo0 + ((tiles_done + j) & 1) * (Cfg::kTileBytes >> 4);
 #pragma unroll
@@ -410,61 +442,24 @@ __global__ void __launch_bounds__(kPairThreads, 1)
                        kIdescPV, (j > 0 || kk > 0) ? 1u : 0u);
         };
         // Uses of the score columns X are numbered in issue order: with both row tiles use 2j is S_A(j) and use
-        // 2j + 1 is S_B(j); a use may be issued once the threads of the use before it have read their scores
-        // (phase use - 1 of bar_xfree).  S_g(j + 1) is thereby computed while the softmax of S_g(j) is still
-        // running, and a row tile's chain of dependent steps is its softmax alone.
+        // 2j + 1 is S_B(j).  This warp issues an item's first use, once the threads of the use before it (the last
+        // of the item before) have read their scores (bar_xfree); every later use is issued by a thread of the row
+        // tile that has just taken its scores out of X, so that the chain X is handed along -- read, next batch,
+        // read -- has one sleeping waiter per link instead of two.  S_g(j + 1) is thereby computed while the
+        // softmax of S_g(j) is still running, and this warp's own waits are those of the second product alone.
         const int groups = w.has_b ? 2 : 1;
-        // local use u of this item is the CTA's use uses_done + u
-        auto wait_x = [&](int use) {
-          const int gu = uses_done + use;
-          if (gu > 0) mbar_wait_bounded(bar_xfree, static_cast<uint32_t>(gu - 1) & 1u, abort_word);
-        };
-        auto kfull_of = [&](int j) { return (kFp8 ? bar_kconv : bar_kfull) + ((tiles_done + j) & 1); };
-        auto kfree_of = [&](int j) { return bar_kfree + ((tiles_done + j) & 1); };
-        auto stage_parity = [&](int j) { return static_cast<uint32_t>((tiles_done + j) >> 1) & 1u; };
-        const bool last_s_in_prologue = w.nt == 1;  // a one-tile item: its only S batches are the first ones
         if (q_by_tma) mbar_wait_bounded(kConvQ ? bar_qconv : bar_qfull, static_cast<uint32_t>(items_done) & 1u, abort_word);
         mbar_wait_bounded(kfull_of(0), stage_parity(0), abort_word);
-        wait_x(0);
+        // the last use of X before this item: the last tile of the item before, by its row tile B if it had one
+        if (items_done > 0)
+          mbar_wait_bounded(prev_had_b ? bar_xfree_b : bar_xfree,
+                            static_cast<uint32_t>((prev_had_b ? tiles_done_b : tiles_done) - 1) & 1u, abort_word);
         fence_after_thread_sync();
-        if (lane == 0) {
-          issue_qk(0, 0);
-          mma_commit(bar_s);
-          if (!w.has_b) {
-            mma_commit(kfree_of(0));
-            if (last_s_in_prologue) mma_commit(bar_qfree);
-          }
-        }
+        if (lane == 0) issue_use(issue_qk, w, 0, 0);
         __syncwarp();
-        if (w.has_b) {
-          wait_x(1);
-          fence_after_thread_sync();
-          if (lane == 0) {
-            issue_qk(1, 0);
-            mma_commit(bar_s + 1);
-            mma_commit(kfree_of(0));
-            if (last_s_in_prologue) mma_commit(bar_qfree);
-          }
-          __syncwarp();
-        }
         for (int j = 0; j < w.nt; ++j) {
           const int s = (tiles_done + j) & 1;
           for (int g = 0; g < groups; ++g) {
-            // S_g(j + 1): as soon as the other row tile (or, alone, this one) has taken its scores out of X
-            if (j + 1 < w.nt) {
-              if (g == 0) mbar_wait_bounded(kfull_of(j + 1), stage_parity(j + 1), abort_word);
-              wait_x(groups * (j + 1) + g);
-              fence_after_thread_sync();
-              if (lane == 0) {
-                issue_qk(g, j + 1);
-                mma_commit(bar_s + g);
-                if (g == groups - 1) {
-                  mma_commit(kfree_of(j + 1));
-                  if (j + 2 == w.nt) mma_commit(bar_qfree);  // the item's last S batch: its query rows are done with
-                }
-              }
-              __syncwarp();
-            }
             // O_g += P_g(j) V(j)
             if (g == 0) {
               mbar_wait_bounded((kFp8 ? bar_vconv : bar_vfull) + s, stage_parity(j), abort_word);
@@ -643,7 +638,20 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_x + c * 32, sa[c]);
           tmem_ld_wait();
           fence_before_thread_sync();
-          mbar_arrive(bar_xfree);  // the scores are in registers: the other row tile's next product may have X
+          mbar_arrive(g == 0 ? bar_xfree : bar_xfree_b);  // the scores are in registers: the next use of X may begin
+          {
+            // the item's next use of X, if it has one: S_B(it) after S_A(it), S_A(it + 1) after S_B(it) (alone: S_A(it + 1))
+            const int ng = w.has_b ? g ^ 1 : 0;
+            const int nj = (w.has_b && g == 0) ? it : it + 1;
+            if (nj < w.nt) {
+              named_bar_sync(5 + g, kPairRows);  // all 128 threads of the row tile have their scores
+              if (r == 0) {
+                if (nj != it) mbar_wait_bounded(kfull_of(nj), stage_parity(nj), abort_word);  // a new key tile
+                fence_after_thread_sync();
+                issue_use(PairScoresIssuer<T16, D, Cfg>(s_q, s_k, tmem + kColX), w, ng, nj);
+              }
+            }
+          }
           if ((tile + 1) * TN > lim_min || tile * TN < lo_max) {  // some row of the tile has tokens to mask here
             const int tok0 = tile * TN;
 #pragma unroll
