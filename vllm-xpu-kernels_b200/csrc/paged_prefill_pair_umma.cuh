@@ -486,6 +486,26 @@ __global__ void __launch_bounds__(kPairThreads, 1)
             __syncwarp();
           }
         }
+      } else if (!kFp8 && warp >= 10) {
+        // ====================================================================================== scores issuers
+        // 16-bit caches.  Warp 10 follows the reads of row tile A, warp 11 those of row tile B: when the row
+        // tile's 128 threads have their scores in registers, it issues the item's next use of X -- S_B(it) after
+        // S_A(it), S_A(it + 1) after S_B(it) (alone: S_A(it + 1) after S_A(it)).  A named barrier hands over: the
+        // softmax warps arrive and go on, this warp is released with the last of them.
+        const int g = warp - 10;
+        if (g == 0 || w.has_b) {
+          const PairScoresIssuer<T16, D, Cfg> issue_qk(s_q, s_k, tmem + kColX);
+          for (int it = 0; it < w.nt; ++it) {
+            const int ng = w.has_b ? g ^ 1 : 0;
+            const int nj = (w.has_b && g == 0) ? it : it + 1;
+            if (nj >= w.nt) break;
+            if (nj != it) mbar_wait_bounded(kfull_of(nj), stage_parity(nj), abort_word);  // a new key tile: long there
+            named_bar_sync(5 + g, kPairRows + 32);
+            fence_after_thread_sync();
+            if (lane == 0) issue_use(issue_qk, w, ng, nj);
+            __syncwarp();
+          }
+        }
       } else if (kFp8 && D == 128 && warp >= 10) {
         // ====================================================================================== widening warps
         // Warps 10 and 11, 64 threads.  A tile's 128 raw rows are widened in two phases of 64 rows: a warp reads
@@ -644,11 +664,19 @@ __global__ void __launch_bounds__(kPairThreads, 1)
             const int ng = w.has_b ? g ^ 1 : 0;
             const int nj = (w.has_b && g == 0) ? it : it + 1;
             if (nj < w.nt) {
-              named_bar_sync(5 + g, kPairRows);  // all 128 threads of the row tile have their scores
-              if (r == 0) {
-                if (nj != it) mbar_wait_bounded(kfull_of(nj), stage_parity(nj), abort_word);  // a new key tile
-                fence_after_thread_sync();
-                issue_use(PairScoresIssuer<T16, D, Cfg>(s_q, s_k, tmem + kColX), w, ng, nj);
+              if constexpr (!kFp8) {
+                // 16-bit caches: warp 10 + g, idle otherwise, sleeps on this named barrier and issues the batch the
+                // moment the row tile's four warps have reported (which costs them one instruction)
+                asm volatile("bar.arrive %0, %1;" ::"r"(5 + g), "r"(kPairRows + 32) : "memory");
+              } else {
+                // fp8 caches (warps 10 and 11 widen): one of the row tile's threads issues it.  Its warp stands
+                // still for the 1 100 cycles in which the tensor pipe takes the eight instructions.
+                named_bar_sync(5 + g, kPairRows);  // all 128 threads of the row tile have their scores
+                if (r == 0) {
+                  if (nj != it) mbar_wait_bounded(kfull_of(nj), stage_parity(nj), abort_word);  // a new key tile
+                  fence_after_thread_sync();
+                  issue_use(PairScoresIssuer<T16, D, Cfg>(s_q, s_k, tmem + kColX), w, ng, nj);
+                }
               }
             }
           }
