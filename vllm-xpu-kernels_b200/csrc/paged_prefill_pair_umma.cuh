@@ -8,32 +8,41 @@
 //   warps 4-7   maximum and sum, its accumulator row (same for row tile B).  No value ever crosses threads.
 //   warp 8      issues O += P V (tcgen05.mma, M = 128, N = 128, K = 16, fp32 accumulation in tensor memory; P
 //               read from tensor memory, V as an MN-major operand) and an item's first S = Q K^T (both operands
-//               in shared memory); every later S batch is issued by a softmax thread, see below.
+//               in shared memory); every later S batch has another issuer, see below.
 //   warp 9      brings query, key and value tiles in with TMA tile copies (cp.async.bulk.tensor, 128-byte
 //               swizzle, no multicast, this GPU's memory only).  Keys and values come straight from the paged
 //               cache: a tensor map over [block][token in block][kv head][d] makes a cache block's rows one box,
 //               the block table gives the block coordinate, one lane issues one box.
 //   warps 10-11 fp8 caches only: widen a tile's raw rows (which the copy warp drops into the upper half of the
-//               tile's slot) to fp16 in the operand layout; the products then run in fp16.  Idle for 16-bit
-//               caches.  (They complete the third warpgroup, whose registers go to the softmax threads.)
+//               tile's slot) to fp16 in the operand layout; the products then run in fp16.  16-bit caches:
+//               they issue the later S batches, warp 10 those that follow a read by row tile A, warp 11 those
+//               that follow a read by row tile B.  (They complete the third warpgroup, whose registers go to
+//               the softmax threads.)
 //
 // Tensor memory (512 columns, all of the SM's): O_A | O_B | X | P_A | P_B with 128, 128, 128, 64, 64 columns.
 // X holds the scores of whichever row tile's turn it is: a softmax thread moves its row of X into registers
-// at once (128 of the 224 registers it owns); when the 128 threads of the row tile have done so (a named
-// barrier among them), one of them issues the next use of X itself -- the other row tile's scores of the same
-// key tile, or this row tile's NEXT scores -- while this softmax is still running.  A row tile's chain of
-// dependent steps is thus its softmax alone, and the chain X is handed along,
+// at once (128 of the 224 registers it owns), and when the 128 threads of the row tile have done so the next use
+// of X is issued -- the other row tile's scores of the same key tile, or this row tile's NEXT scores -- while
+// this softmax is still running.  A row tile's chain of dependent steps is thus its softmax alone; what a step
+// waits for is the chain X is handed along,
 //
 //   S_A(j) -> A reads -> S_B(j) -> B reads -> S_A(j+1) -> A reads -> ...
 //
-// has one sleeping waiter per link (the readers, woken by the batch's commit) instead of two: with the issuing
-// warp as the middleman of every link, its four wake-ups of about 600 cycles each were what a step of 4 100
-// cycles waited for, not the tensor pipe (2 800) nor the softmax (2 250).  The issuing warp's own batches,
-// O_g += P_g(j) V(j), are gated by the softmax threads' arrival "P stored".  The probabilities have columns of
-// their own, which PV(j) has finished reading before the softmax of tile j + 1 stores into them (the wait for
-// "O += P(j) V(j) complete" that a rescaling of O needs anyway).  tcgen05.commit tracks the instructions of
-// the thread that executes it, so whoever issues a batch also commits it to the scores barrier, and after a
-// tile's last batch to "key slot free", after the item's last to "query rows free".
+// and how long a link of it takes.  Three designs, in the order they were measured (a step is two row tiles x 128
+// tokens; the tensor pipe needs 2 800 cycles of it, a softmax 2 250):
+//   1. warp 8 issues everything, in a fixed order, and learns of each read and each "P stored" through an
+//      mbarrier: 4 100 cycles.  While its thread is held by one batch (the pipe takes eight instructions in 800 to
+//      1 100 cycles) it cannot answer the next event, and every link has two sleeping waiters.
+//   2. a thread of the row tile that has just read X issues the next use itself (a named barrier among the 128,
+//      then the batch): 3 800.  The link is short, but that thread's warp stands still for those 1 100 cycles
+//      and the row tile is as late as its latest warp.  fp8 caches, whose warps 10 and 11 are busy, run this way.
+//   3. 16-bit caches: warps 10 and 11 do nothing else than issue those uses.  They sleep on a named barrier at
+//      which the softmax warps only arrive (one instruction, no wait), so the issuer is released with the last
+//      arrival; warp 8 keeps O_g += P_g(j) V(j), released by a second such barrier when P is stored: 3 400.
+// The probabilities have columns of their own, which PV(j) has finished reading before the softmax of tile j + 1
+// stores into them (the wait for "O += P(j) V(j) complete" that a rescaling of O needs anyway).  tcgen05.commit
+// tracks the instructions of the thread that executes it, so whoever issues a batch also commits it to the
+// scores barrier, and after a tile's last batch to "key slot free", after the item's last to "query rows free".
 //
 // A softmax thread costs about 3.5 instructions per score (one tcgen05.ld of 32 columns per 32 scores, packed
 // fp32 arithmetic, 3-input max, one ex2 per score, 16-bit packing); every fixed per-tile cost is spread over 128
@@ -475,8 +484,14 @@ __global__ void __launch_bounds__(kPairThreads, 1)
                 __syncwarp();
               }
             }
-            mbar_wait_bounded(bar_ready + g, static_cast<uint32_t>((g == 0 ? tiles_done : tiles_done_b) + j) & 1u,
-                              abort_word);
+            // the row tile's 128 threads have stored P(j).  16-bit caches: a named barrier they only arrive at (this
+            // warp is released about 250 cycles sooner than an mbarrier wakes it); fp8 caches measured 4 % slower
+            // that way (the thread that issues the scores makes its warp a late arriver) and keep the mbarrier.
+            if constexpr (!kFp8)
+              named_bar_sync(7 + g, kPairRows + 32);
+            else
+              mbar_wait_bounded(bar_ready + g, static_cast<uint32_t>((g == 0 ? tiles_done : tiles_done_b) + j) & 1u,
+                                abort_word);
             fence_after_thread_sync();
             if (lane == 0) {
               issue_pv(g, j);
@@ -739,7 +754,10 @@ __global__ void __launch_bounds__(kPairThreads, 1)
                    ((l_add[2].x + l_add[2].y) + (l_add[3].x + l_add[3].y));
           tmem_st_wait();
           fence_before_thread_sync();
-          mbar_arrive(bar_ready + g);
+          if constexpr (!kFp8)
+            asm volatile("bar.arrive %0, %1;" ::"r"(7 + g), "r"(kPairRows + 32) : "memory");
+          else
+            mbar_arrive(bar_ready + g);
         }
         const bool finished = mbar_wait_bounded(bar_o + g, static_cast<uint32_t>(phase0 + w.nt - 1) & 1u, abort_word);
         fence_after_thread_sync();
