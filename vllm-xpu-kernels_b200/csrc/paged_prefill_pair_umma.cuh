@@ -717,27 +717,35 @@ __global__ void __launch_bounds__(kPairThreads, 1)
           m_run = move ? mx : m_run;
           const float neg_ms = (m_run == -INFINITY) ? 0.f : -m_run * scale2;
           l_run *= alpha;
-          if (it > 0) {  // O += P(it - 1) V(it - 1) is complete: O is at rest and P's columns may be overwritten
-            mbar_wait_bounded(bar_o + g, static_cast<uint32_t>(phase0 + it - 1) & 1u, abort_word);
-            fence_after_thread_sync();
-          }
-          if (it > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // rare: a reference maximum of the warp moved
-#pragma unroll 1
-            for (int c = 0; c < D / 32; ++c) {
-              uint32_t o[32];
-              tmem_ld_32x32(t_o + c * 32, o);
-              tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-              tmem_st_32x32(t_o + c * 32, o);
+          // O += P(it - 1) V(it - 1) must be complete before O is rescaled or P's columns are overwritten.  That
+          // product was issued when this row tile reported P(it - 1).  16-bit caches: the 128 scores first become 64
+          // words of two 16-bit probabilities in the registers the scores leave -- nothing in that touches tensor
+          // memory -- and the wait comes last (asked for before the exponentials it cost the row tile 290 cycles
+          // per tile, and the row tile's own time is what a step waits for there).  fp8 caches measured 3 % slower
+          // that way and wait first, storing each half of P as it is complete.
+          auto wait_for_previous_product = [&]() {
+            if (it > 0) {
+              mbar_wait_bounded(bar_o + g, static_cast<uint32_t>(phase0 + it - 1) & 1u, abort_word);
+              fence_after_thread_sync();
             }
-          }
-          // 64 scores become 32 words of two 16-bit probabilities, stored as soon as they are complete
+            if (it > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {  // rare: a reference maximum of the warp moved
+#pragma unroll 1
+              for (int c = 0; c < D / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld_32x32(t_o + c * 32, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                tmem_st_32x32(t_o + c * 32, o);
+              }
+            }
+          };
+          if constexpr (kFp8) wait_for_previous_product();
           const float2 sc2 = make_float2(scale2, scale2), nm2 = make_float2(neg_ms, neg_ms);
           float2 l_add[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+          uint32_t wd[2][32];
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            uint32_t wd[32];
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
@@ -746,9 +754,14 @@ __global__ void __launch_bounds__(kPairThreads, 1)
                 const float2 e = __ffma2_rn(make_float2(__uint_as_float(sa[c][i]), __uint_as_float(sa[c][i + 1])), sc2, nm2);
                 const float2 pr = make_float2(fast_exp2(e.x), fast_exp2(e.y));
                 l_add[(i >> 1) & 3] = __fadd2_rn(l_add[(i >> 1) & 3], pr);
-                wd[cc * 16 + (i >> 1)] = pack2<T16>(pr.x, pr.y);
+                wd[h][cc * 16 + (i >> 1)] = pack2<T16>(pr.x, pr.y);
               }
-            tmem_st_32x32(t_p + h * 32, wd);
+            if constexpr (kFp8) tmem_st_32x32(t_p + h * 32, wd[h]);
+          }
+          if constexpr (!kFp8) {
+            wait_for_previous_product();
+            tmem_st_32x32(t_p, wd[0]);
+            tmem_st_32x32(t_p + 32, wd[1]);
           }
           l_run += ((l_add[0].x + l_add[0].y) + (l_add[1].x + l_add[1].y)) +
                    ((l_add[2].x + l_add[2].y) + (l_add[3].x + l_add[3].y));
